@@ -1,0 +1,127 @@
+"""Pins the CPU oracle to the known-answer vectors of the reference's own tests.
+
+The vectors live in tests/golden/reference_known_answers.json (written by
+tests/golden/make_known_answers.py from the reference's test sources, cited per case).
+"""
+import json
+import math
+import os
+import struct
+
+import numpy as np
+import pytest
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+with open(os.path.join(HERE, "golden", "reference_known_answers.json")) as f:
+    KA = json.load(f)
+
+
+def bits(f):
+    return struct.unpack("<I", struct.pack("<f", f))[0]
+
+
+def test_q4k_decode_basic(oracle):
+    c = KA["q4k_decode_basic"]
+    out = oracle.dequant_q4_k(c["block"])
+    for i, v in c["expect"].items():
+        assert out[int(i)] == v
+
+
+def test_q4k_decode_all_subblocks(oracle):
+    c = KA["q4k_decode_all_subblocks"]
+    out = oracle.dequant_q4_k(c["block"])
+    assert out.tolist() == c["expect_all"]
+    sc, m = oracle.q4k_scales(c["block"])
+    assert sc.tolist() == c["expect_scales"] and m.tolist() == c["expect_mins"]
+    blk = np.array(c["block"], np.uint8)
+    import ctypes as C
+    for e in range(256):  # element-indexed form of the same decode
+        got = oracle.lib().gko_q4k_element(blk.ctypes.data_as(C.POINTER(C.c_uint8)), e)
+        assert got == c["expect_all"][e]
+
+
+@pytest.mark.parametrize("name", ["gemm_q4_basic", "gemm_q4_per_channel"])
+def test_gemm_q4(oracle, name):
+    c = KA[name]
+    out = oracle.gemm_q4(c["weight"], c["input"], c["scales"], c["m"], c["n"], c["k"])
+    assert out.reshape(-1).tolist() == c["expect"]
+
+
+def test_q8_0_decode(oracle):
+    c = KA["q8_0_decode_basic"]
+    out = oracle.dequant_q8_0(c["block"])
+    for i, v in c["expect"].items():
+        assert out[int(i)] == v
+    c = KA["q8_0_decode_extreme"]
+    assert oracle.dequant_q8_0(c["block"]).tolist() == c["expect_all"]
+
+
+def test_q8_0_dot_via_classic_matmul(oracle):
+    c = KA["q8_0_dot"]
+    out = oracle.quant_matmul(c["weight"], c["input"], oracle.Q8_0, c["m"], c["n"], c["k"])
+    assert out.reshape(-1).tolist() == c["expect"]
+
+
+@pytest.mark.parametrize("name", sorted(KA["mxfp4"].keys()))
+def test_mxfp4_known_answers(oracle, name):
+    c = KA["mxfp4"][name]
+    out = oracle.dequant_mxfp4(c["blocks"], c["scales"], c["block_size"])
+    if c.get("expect_all_nan"):
+        assert np.isnan(out).all()
+    else:
+        exp = np.array(c["expect"], np.float32)
+        assert out.shape == exp.shape
+        # bit-exact, including the sign of zero
+        assert (out.view(np.uint32) == exp.view(np.uint32)).all()
+
+
+def test_e2m1_and_e8m0(oracle):
+    lut = KA["e2m1_lut"]["values"]
+    for i, v in enumerate(lut):
+        assert bits(oracle.lib().gko_e2m1(i)) == bits(v)
+    for b, u in KA["e8m0_bits"]["byte_to_f32_bits"].items():
+        assert bits(oracle.lib().gko_decode_e8m0_scale(int(b))) == u
+    assert math.isnan(oracle.lib().gko_decode_e8m0_scale(KA["e8m0_bits"]["nan_byte"]))
+
+
+def test_metadata(oracle):
+    md = KA["metadata"]
+    L = oracle.lib()
+    assert [L.gko_block_size(oracle.Q4K, 0), L.gko_block_bytes(oracle.Q4K, 0)] == md["q4k"]
+    assert [L.gko_block_size(oracle.Q8_0, 0), L.gko_block_bytes(oracle.Q8_0, 0)] == md["q8_0"]
+    assert [L.gko_block_size(oracle.MXFP4, 32), L.gko_block_bytes(oracle.MXFP4, 32)] == md["mxfp4_32"]
+    assert [L.gko_block_size(oracle.NVFP4, 0), L.gko_block_bytes(oracle.NVFP4, 0)] == md["nvfp4"]
+
+
+def test_f16_codec_against_numpy(oracle):
+    L = oracle.lib()
+    allh = np.arange(65536, dtype=np.uint16)
+    ref = allh.view(np.float16).astype(np.float32)
+    for h in range(0, 65536, 7):
+        got = L.gko_f16_to_f32(h)
+        assert bits(got) == int(ref[h:h + 1].view(np.uint32)[0]) or (math.isnan(got) and np.isnan(ref[h]))
+    rng = np.random.default_rng(1)
+    xs = np.concatenate([rng.standard_normal(4000).astype(np.float32) * 10.0 ** rng.integers(-9, 6, 4000),
+                         np.array([0, -0.0, 65504, 65519.99, 65520, 1e-8, 5.96e-8, 2.98e-8, 2.9802322e-8, np.inf],
+                                  np.float32)]).astype(np.float32)
+    want = xs.astype(np.float16).view(np.uint16)
+    for x, w in zip(xs.tolist(), want.tolist()):
+        assert L.gko_f32_to_f16(x) == w, x
+
+
+def test_e4m3_codec_against_torch(oracle):
+    """OCP E4M3 decode of all 256 bytes equals torch.float8_e4m3fn; encode round-trips every code."""
+    import torch
+    L = oracle.lib()
+    allb = torch.arange(256, dtype=torch.uint8)
+    ref = allb.view(torch.float8_e4m3fn).to(torch.float32).numpy()
+    for b in range(256):
+        got = L.gko_e4m3_to_f32(b)
+        if math.isnan(ref[b]):
+            assert math.isnan(got)
+        else:
+            assert bits(got) == bits(float(ref[b]))
+            if (b & 0x7F) != 0 or b == 0:
+                assert L.gko_f32_to_e4m3(float(ref[b])) == b
+    assert L.gko_f32_to_e4m3(1000.0) == 0x7E  # saturates to 448
+    assert L.gko_e4m3_to_f32(0x7E) == 448.0
