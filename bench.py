@@ -1,0 +1,357 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-matmul hot path on B200.
+
+Headline workload ("step"): one decode pass (M = 1 token) over a stack of 70B-shaped Q4_K FFN
+layers — gate W[28672, 8192], up W[28672, 8192], down W[8192, 28672] per layer — i.e. BASELINE
+config 5 at M = 1.  Metric: quant GEMV weight-GB/s (reference-format weight bytes / time), reported
+with its fraction of the measured HBM copy bandwidth.  A stack of several layers keeps the per-GPU
+weight set larger than the 126 MB L2 at every GPU count, so no L2 flush is needed between steps.
+
+  python bench.py --gpus 1 --steps 50 --warmup 5             # this implementation
+  python bench.py --impl reference ...                       # the reference's CPU algorithm, host cores
+  torchrun ... bench.py --gpus N ...                         # N-wise sharded, one NCCL all-gather per GEMV
+
+One JSON line on stdout (rank 0).
+"""
+from __future__ import annotations
+
+import argparse
+import importlib
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+N_FF, D_MODEL = 28672, 8192
+Q4K_BLOCK_BYTES, Q4K_BLOCK = 144, 256
+METRIC = "quant GEMV weight-GB/s (Q4_K decode, 70B-shaped FFN)"
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self._stop_evt = threading.Event()
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def run(self):
+        if not self.nv:
+            return
+        nv = self.nv
+        names = {"hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+                 "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+                 "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+                 "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4)}
+        while not self._stop_evt.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for k, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            self._stop_evt.wait(0.02)
+
+    def stop(self):
+        self._stop_evt.set()
+        self.join(timeout=2)
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+def shard_rows(n: int, world: int, rank: int):
+    """N-wise split in multiples of 16 rows (the row-tile of the device layout)."""
+    tiles = n // 16
+    t0, t1 = tiles * rank // world, tiles * (rank + 1) // world
+    return 16 * t0, 16 * t1
+
+
+# ------------------------------------------------------------------------------------------------
+def run_ours(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    gk = importlib.import_module("gllm-kernels_b200")
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    K = gk.GpuKernels(local)
+    qt = gk.QuantType.q4k()
+    M, L = args.m, args.layers
+
+    # ---- synthetic weights: N(0, 0.02) f32 from the seed, quantized on the device, row-sharded ----
+    shapes = [("gate", N_FF, D_MODEL), ("up", N_FF, D_MODEL), ("down", D_MODEL, N_FF)]
+    weights, host_blocks = [], []
+    gen = torch.Generator(device=dev).manual_seed(20244)
+    keep_host = rank == 0 and world == 1 and not args.no_cpu_baseline
+    for layer in range(L):
+        for name, n, k in shapes:
+            W = torch.randn((n, k), generator=gen, device=dev) * 0.02  # same stream on every rank
+            r0, r1 = shard_rows(n, world, rank)
+            blocks = K.quantize(qt, W[r0:r1].contiguous())
+            del W
+            weights.append((name, K.upload(qt, r1 - r0, k, blocks), n, k, r0, r1))
+            if keep_host and layer == 0:
+                host_blocks.append((name, n, k, blocks.cpu().numpy()))
+            del blocks
+    torch.cuda.empty_cache()
+    x_model = torch.randn((M, D_MODEL), generator=gen, device=dev)
+    x_ff = torch.randn((M, N_FF), generator=gen, device=dev)
+    ys = [torch.empty((M, n), dtype=torch.float32, device=dev) for (_, _, n, _, _, _) in weights]
+    # sharded: each rank's GEMV writes its slice of a [world, M, n/world] gather buffer in place
+    gbufs = [torch.empty((world, M, (r1 - r0)), dtype=torch.float32, device=dev) for (_, _, n, _, r0, r1) in weights]
+
+    weight_bytes_local = sum(w.ref_bytes for (_, w, *_r) in weights)
+    weight_bytes_total = L * sum(n * (k // Q4K_BLOCK) * Q4K_BLOCK_BYTES for _, n, k in shapes)
+    algo_bytes_step = weight_bytes_total + L * sum(M * (k + n) * 4 for _, n, k in shapes)
+
+    def step():
+        for i, (name, w, n, k, r0, r1) in enumerate(weights):
+            x = x_ff if name == "down" else x_model
+            if world == 1:
+                K.gemv(w, x, y=ys[i])
+            else:
+                K.gemv(w, x, y=gbufs[i][rank])
+                dist.all_gather_into_tensor(gbufs[i].view(-1), gbufs[i][rank].view(-1))
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    ev0.record()
+    for _ in range(args.steps):
+        step()
+    ev1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ms = ev0.elapsed_time(ev1)
+    clocks = sampler.stop()
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = t.item()
+    ms_step = ms / args.steps
+    value = weight_bytes_total / (ms_step * 1e-3) / 1e9
+
+    # ---- end to end through the host-pointer call: pinned x -> device, GEMVs, y -> host, every step ----
+    xh_model = x_model.cpu().numpy()
+    xh_ff = x_ff.cpu().numpy()
+    e2e = None
+    if world == 1:
+        def step_host():
+            out = None
+            for (name, w, n, k, r0, r1) in weights:
+                out = K.matmul_host(w, xh_ff if name == "down" else xh_model)
+            return out
+        for _ in range(3):
+            step_host()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            step_host()
+        dt = (time.perf_counter() - t0) / args.steps
+        e2e = {"value": weight_bytes_total / dt / 1e9, "unit": "GB/s",
+               "h2d_bytes_per_step": L * sum(M * k * 4 for _, n, k in shapes),
+               "d2h_bytes_per_step": L * sum(M * n * 4 for _, n, k in shapes),
+               "note": "weights resident (uploaded once, like the reference's weights handle); activations and "
+                       "outputs are host buffers, copied inside the timed region, one synchronous call per GEMV"}
+
+    peak, peak_kind = measured_peaks()
+    out = {
+        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "u4 weights x f32 activations, f32 accumulate", "data": "synthetic",
+        "config": {"workload": f"config 5: 70B-shaped FFN decode, {L} layers x (gate, up, down) Q4_K, M={M}",
+                   "layers": L, "M": M, "N_ff": N_FF, "d_model": D_MODEL, "weight_bytes_per_step": weight_bytes_total,
+                   "l2": "per-GPU weight set larger than L2, no flush",
+                   "parallelism": "single GPU" if world == 1 else f"N-wise row shards x{world} + NCCL all-gather"},
+        "roofline": {"bound": "hbm", "achieved": algo_bytes_step / (ms_step * 1e-3) / 1e9 / world, "peak": peak,
+                     "unit": "GB/s", "frac": algo_bytes_step / (ms_step * 1e-3) / 1e9 / world / peak,
+                     "traffic": None, "peak_kind": peak_kind,
+                     "kernel": "gemv_q4k_kernel<1> (+ its activation staging kernel), per-GPU average"},
+        "gpu_launches": args.steps * len(weights) * 2,
+        "clocks": clocks,
+        "e2e": e2e,
+    }
+    if world == 1 and rank == 0 and not args.no_extra:
+        out["extra"] = extra_configs(K, gk, torch, dev, peak)
+    if keep_host:
+        out["cpu_baseline"] = cpu_baseline(host_blocks, xh_model, xh_ff, M, threads=1)
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def extra_configs(K, gk, torch, dev, peak):
+    """Configs 1 and 2 (small matrices): rotate over distinct weight copies totalling > 2x L2."""
+    res = {}
+    gen = torch.Generator(device=dev).manual_seed(20240)
+
+    def run(qt, n, k, ms, copies, name):
+        bs, bb = qt.block_size(), qt.block_bytes()
+        ws = []
+        for _ in range(copies):
+            W = torch.randn((n, k), generator=gen, device=dev) * 0.02
+            ws.append(K.upload(qt, n, k, K.quantize(qt, W)))
+            del W
+        wbytes = n * (k // bs) * bb
+        for m in ms:
+            x = torch.randn((m, k), generator=gen, device=dev)
+            y = torch.empty((m, n), dtype=torch.float32, device=dev)
+            reps = 20
+            for w in ws:
+                K.gemv(w, x, y=y)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                for w in ws:
+                    K.gemv(w, x, y=y)
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / (reps * copies)
+            res[f"{name}_M{m}"] = {"us_per_gemv": us, "weight_GBps": wbytes / us / 1e3, "frac_hbm": wbytes / us / 1e3 / peak,
+                                   "tflops": 2.0 * m * n * k / us / 1e6, "copies_rotated": copies}
+        for w in ws:
+            w.free()
+
+    run(gk.QuantType.q4k(), 4096, 4096, [1], 32, "cfg1_q4k_4096x4096")
+    run(gk.QuantType.q8_0(), 11008, 4096, [1, 4, 8, 16], 6, "cfg2_q8_0_11008x4096")
+    return res
+
+
+def cpu_baseline(host_blocks, xh_model, xh_ff, M, threads, reps=None):
+    """The oracle (a port of the reference's scalar path) on this box's host cores: one layer's gate, up and
+    down GEMVs — the same work as 1/L of a step."""
+    import numpy as np
+    from oracle import oracle as O
+    import numpy as _np
+    xt_model = _np.ascontiguousarray(xh_model.T)
+    xt_ff = _np.ascontiguousarray(xh_ff.T)
+    wbytes = sum(b.size for (_, _, _, b) in host_blocks)
+
+    def once():
+        for name, n, k, b in host_blocks:
+            O.quant_matmul(b, xt_ff if name == "down" else xt_model, O.Q4K, n, M, k, threads=threads)
+    once()
+    t0 = time.perf_counter()
+    once()
+    one = time.perf_counter() - t0
+    reps = reps or max(2, min(40, int(12.0 / max(one, 1e-3))))
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        once()
+    dt = (time.perf_counter() - t0) / reps
+    return {"value": wbytes / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+            "sample": f"{reps} passes over one layer (gate, up, down = {wbytes} weight bytes) of the same workload",
+            "cpu_count": os.cpu_count()}
+
+
+# ------------------------------------------------------------------------------------------------
+def run_reference(args):
+    """The reference's CPU algorithm for the same workload on the host cores (all threads, row-parallel).
+    The reference is Rust and cannot be built in this image, so this runs the C port in oracle/."""
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if rank != 0:
+        return
+    import numpy as np
+    from oracle import oracle as O
+    threads = os.cpu_count() or 1
+    M, L = args.m, args.layers
+    shapes = [("gate", N_FF, D_MODEL), ("up", N_FF, D_MODEL), ("down", D_MODEL, N_FF)]
+    rng = np.random.default_rng(20244)
+    # one layer of distinct weights, reused for every layer of the step (CPU caches are far smaller than a matrix)
+    host_blocks = []
+    for name, n, k in shapes:
+        W = (rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02))
+        host_blocks.append((name, n, k, O.quantize_q4_k(W)))
+        del W
+    x_model = rng.standard_normal((M, D_MODEL), dtype=np.float32)
+    x_ff = rng.standard_normal((M, N_FF), dtype=np.float32)
+    xt_model, xt_ff = np.ascontiguousarray(x_model.T), np.ascontiguousarray(x_ff.T)
+    layer_bytes = sum(b.size for (_, _, _, b) in host_blocks)
+
+    def step():  # bounded sample: one layer per step, scaled to the L-layer step below
+        for name, n, k, b in host_blocks:
+            O.quant_matmul(b, xt_ff if name == "down" else xt_model, O.Q4K, n, M, k, threads=threads)
+    for _ in range(max(args.warmup, 1)):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = (time.perf_counter() - t0) / args.steps
+    value = layer_bytes / dt / 1e9
+    out = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 1), "ms_per_step": dt * 1e3 * L, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "u4 weights x f32 activations, f32 accumulate", "data": "synthetic",
+        "config": {"workload": f"config 5: 70B-shaped FFN decode, {L} layers x (gate, up, down) Q4_K, M={M}",
+                   "layers": L, "M": M, "N_ff": N_FF, "d_model": D_MODEL},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port",
+                         "sample": f"each step = one layer (gate, up, down, {layer_bytes} weight bytes) of the "
+                                   f"{L}-layer step; ms_per_step is scaled x{L}"},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(out), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=4)
+    ap.add_argument("--m", type=int, default=1)
+    ap.add_argument("--no-extra", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,13 @@
+"""gllm-kernels_b200 — B200 (sm_100a) quantized-matmul operators behind the reference's operator API.
+
+Host-side mirror of the quant slice of gllm-kernels' `Kernels<E>` trait (src/traits.rs:473-608),
+of `QuantType` metadata (src/quant.rs:375-456) and of `quant_mxfp4` (src/quant_mxfp4.rs), bound to
+the C ABI in include/gllmk.h.  All compute happens in libgllmk.so (hand-written CUDA); there is no
+CPU fallback and importing the compute classes fails loudly if the library is missing.
+"""
+from .quant import QuantType, E2M1_LUT_F32, decode_e8m0_scale  # noqa: F401
+from ._lib import GllmkError, Status, lib, lib_path, build_library  # noqa: F401
+from .kernels import GpuKernels, Weight  # noqa: F401
+
+__all__ = ["QuantType", "E2M1_LUT_F32", "decode_e8m0_scale", "GllmkError", "Status", "lib", "lib_path",
+           "build_library", "GpuKernels", "Weight"]

@@ -1,0 +1,467 @@
+// extern "C" boundary of libgllmk.so (declared in include/gllmk.h).  Argument validation happens
+// here, before any launch; nothing below throws.
+#include "common.cuh"
+
+namespace gllmk {
+
+int32_t fail(Ctx *c, int32_t code, const char *fmt, ...) {
+    if (c) {
+        char buf[512];
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(buf, sizeof buf, fmt, ap);
+        va_end(ap);
+        c->err = buf;
+    }
+    return code;
+}
+
+int32_t cuda_fail(Ctx *c, cudaError_t e, const char *what) {
+    const int32_t code = (e == cudaErrorMemoryAllocation) ? GLLMK_STATUS_OUT_OF_MEMORY : GLLMK_STATUS_RUNTIME_ERROR;
+    (void)cudaGetLastError();  // clear the sticky-free error state
+    return fail(c, code, "CUDA error %d (%s) in %s", (int)e, cudaGetErrorString(e), what);
+}
+
+static int32_t grow(Ctx *c, void **p, size_t *have, size_t want, bool pinned) {
+    if (*have >= want) return GLLMK_STATUS_OK;
+    // every buffer is used stream-ordered on streams the caller may still have work on
+    GK_CUDA(c, cudaDeviceSynchronize());
+    if (*p) {
+        if (pinned) cudaFreeHost(*p);
+        else cudaFree(*p);
+        *p = nullptr;
+        *have = 0;
+    }
+    const size_t sz = (want + (1u << 20) - 1) & ~((size_t)(1u << 20) - 1);
+    if (pinned) GK_CUDA(c, cudaMallocHost(p, sz));
+    else GK_CUDA(c, cudaMalloc(p, sz));
+    *have = sz;
+    return GLLMK_STATUS_OK;
+}
+int32_t ensure_ws(Ctx *c, size_t bytes) { return grow(c, &c->ws, &c->ws_bytes, bytes, false); }
+int32_t ensure_pin(Ctx *c, size_t bytes) { return grow(c, &c->pin, &c->pin_bytes, bytes, true); }
+int32_t ensure_dev_io(Ctx *c, size_t bytes) { return grow(c, &c->dev_io, &c->dev_io_bytes, bytes, false); }
+
+static int block_size_of(int qt, int mx) {
+    switch (qt) {
+        case GLLMK_QUANT_Q4K: return 256;
+        case GLLMK_QUANT_Q8_0: return 32;
+        case GLLMK_QUANT_MXFP4: return mx;
+        case GLLMK_QUANT_NVFP4: return 64;
+    }
+    return 0;
+}
+static int block_bytes_of(int qt, int mx) {
+    switch (qt) {
+        case GLLMK_QUANT_Q4K: return 144;
+        case GLLMK_QUANT_Q8_0: return 34;
+        case GLLMK_QUANT_MXFP4: return 1 + mx / 2;
+        case GLLMK_QUANT_NVFP4: return 36;
+    }
+    return 0;
+}
+
+struct DeviceGuard {
+    int prev = -1;
+    bool ok = true;
+    explicit DeviceGuard(int dev) {
+        if (cudaGetDevice(&prev) != cudaSuccess) { ok = false; (void)cudaGetLastError(); return; }
+        if (prev != dev && cudaSetDevice(dev) != cudaSuccess) { ok = false; (void)cudaGetLastError(); }
+    }
+    ~DeviceGuard() {
+        if (ok && prev >= 0) cudaSetDevice(prev);
+    }
+};
+
+// Creates the handle and its device buffers for an n x k matrix of type qt (no data yet).
+static int32_t weight_alloc(Ctx *c, int32_t qt, int64_t n, int64_t k, int32_t mx_block, float global, Weight **out) {
+    if (qt != GLLMK_QUANT_Q4K && qt != GLLMK_QUANT_Q8_0 && qt != GLLMK_QUANT_MXFP4 && qt != GLLMK_QUANT_NVFP4)
+        return fail(c, GLLMK_STATUS_UNSUPPORTED, "unknown quant type %d", qt);
+    if (qt == GLLMK_QUANT_MXFP4 && mx_block != 32)
+        return fail(c, GLLMK_STATUS_UNSUPPORTED, "MXFP4 weights need block_size 32 (got %d)", mx_block);
+    if (n <= 0 || k <= 0) return fail(c, GLLMK_STATUS_INVALID_ARG, "n and k must be positive");
+    const int bs = block_size_of(qt, mx_block);
+    const int64_t kmul = (qt == GLLMK_QUANT_MXFP4) ? 128 : bs;  // FP4 scale planes come in atoms of 4
+    if (k % kmul) return fail(c, GLLMK_STATUS_INVALID_ARG, "k=%lld is not a multiple of %lld", (long long)k, (long long)kmul);
+    if (n > (int64_t)1 << 30 || k > (int64_t)1 << 30) return fail(c, GLLMK_STATUS_INVALID_ARG, "matrix too large");
+    Weight *w = new (std::nothrow) Weight();
+    if (!w) return fail(c, GLLMK_STATUS_OUT_OF_MEMORY, "host allocation failed");
+    w->qt = qt;
+    w->mx_block = (qt == GLLMK_QUANT_MXFP4) ? mx_block : 0;
+    w->n = n;
+    w->k = k;
+    w->nb = k / bs;
+    w->global_scale = global;
+    w->device = c->device;
+    w->ref_bytes = (uint64_t)n * (uint64_t)w->nb * (uint64_t)block_bytes_of(qt, mx_block);
+    if (qt == GLLMK_QUANT_Q4K) {
+        w->n_pad = (n + 15) / 16 * 16;
+        w->qs_bytes = (size_t)w->n_pad * w->nb * 128;
+        w->aux_bytes = (size_t)w->n_pad * w->nb * 16;
+    } else if (qt == GLLMK_QUANT_Q8_0) {
+        w->n_pad = (n + 15) / 16 * 16;
+        w->nb8 = (w->nb + 7) / 8;
+        w->qs_bytes = (size_t)w->n_pad * w->nb * 32;
+        w->aux_bytes = (size_t)w->n_pad * w->nb8 * 16;
+    } else {
+        w->n_pad = (n + 127) / 128 * 128;
+        w->qs_bytes = (size_t)w->n_pad * (k / 2);
+        w->aux_bytes = (size_t)w->n_pad * (k / (qt == GLLMK_QUANT_NVFP4 ? 16 : 32));
+    }
+    cudaError_t e = cudaMalloc(&w->qs, w->qs_bytes);
+    if (e == cudaSuccess) e = cudaMalloc(&w->aux, w->aux_bytes);
+    if (e != cudaSuccess) {
+        if (w->qs) cudaFree(w->qs);
+        delete w;
+        return cuda_fail(c, e, "cudaMalloc(weight)");
+    }
+    *out = w;
+    return GLLMK_STATUS_OK;
+}
+
+static void weight_destroy(Weight *w) {
+    if (!w) return;
+    DeviceGuard g(w->device);
+    if (w->qs) cudaFree(w->qs);
+    if (w->aux) cudaFree(w->aux);
+    delete w;
+}
+
+// blocks/scales: host or device according to on_device.  Synchronous: returns once repacked.
+static int32_t weight_fill(Ctx *c, Weight *w, const void *blocks, const void *scales, bool on_device) {
+    const size_t raw = (w->qt == GLLMK_QUANT_MXFP4 && scales) ? (size_t)w->n * (w->k / 2) : (size_t)w->ref_bytes;
+    const size_t sraw = (w->qt == GLLMK_QUANT_MXFP4 && scales) ? (size_t)w->n * (w->k / 32) : 0;
+    const void *bdev = blocks, *sdev = scales;
+    void *stage = nullptr;
+    if (!on_device) {
+        const size_t off = (raw + 255) & ~(size_t)255;
+        GK_CUDA(c, cudaMalloc(&stage, off + sraw + 256));
+        cudaError_t e = cudaMemcpyAsync(stage, blocks, raw, cudaMemcpyHostToDevice, c->stream);
+        if (e == cudaSuccess && sraw)
+            e = cudaMemcpyAsync(static_cast<char *>(stage) + off, scales, sraw, cudaMemcpyHostToDevice, c->stream);
+        if (e != cudaSuccess) { cudaFree(stage); return cuda_fail(c, e, "cudaMemcpyAsync(weight blocks)"); }
+        bdev = stage;
+        sdev = sraw ? static_cast<char *>(stage) + off : nullptr;
+    } else if (((uintptr_t)blocks & 15) != 0) {
+        return fail(c, GLLMK_STATUS_INVALID_ARG, "device block pointer must be 16-byte aligned");
+    }
+    int32_t rc = repack_upload(c, w, bdev, sdev, c->stream);
+    cudaError_t e = cudaStreamSynchronize(c->stream);
+    if (stage) cudaFree(stage);
+    if (rc) return rc;
+    if (e != cudaSuccess) return cuda_fail(c, e, "repack");
+    return GLLMK_STATUS_OK;
+}
+
+}  // namespace gllmk
+
+using namespace gllmk;
+
+extern "C" {
+
+const char *gllmk_version(void) { return "gllmk 0.1.0 (sm_100a)"; }
+
+int32_t gllmk_hw_info(char *buf, size_t len) {
+    if (!buf || len == 0) return GLLMK_STATUS_INVALID_ARG;
+    int ndev = 0;
+    cudaDeviceProp prop;
+    int n;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0 || cudaGetDeviceProperties(&prop, 0) != cudaSuccess) {
+        (void)cudaGetLastError();
+        n = snprintf(buf, len, "no CUDA device");
+    } else {
+        n = snprintf(buf, len, "%s sm_%d%d, %d SMs, %.1f GiB, L2 %d MiB, %d device(s)", prop.name, prop.major, prop.minor,
+                     prop.multiProcessorCount, (double)prop.totalGlobalMem / (1 << 30), prop.l2CacheSize >> 20, ndev);
+    }
+    if (n < 0) return GLLMK_STATUS_RUNTIME_ERROR;
+    return (int32_t)((size_t)n < len ? (size_t)n : len - 1);
+}
+
+int32_t gllmk_quant_block_size(int32_t qt, int32_t mx_block) { return block_size_of(qt, mx_block); }
+int32_t gllmk_quant_block_bytes(int32_t qt, int32_t mx_block) { return block_bytes_of(qt, mx_block); }
+
+int32_t gllmk_ctx_create(int32_t device, gllmk_ctx *out) {
+    if (!out) return GLLMK_STATUS_INVALID_ARG;
+    *out = nullptr;
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) {
+        (void)cudaGetLastError();
+        return GLLMK_STATUS_RUNTIME_ERROR;  // no CPU fallback
+    }
+    if (device < 0 || device >= ndev) return GLLMK_STATUS_INVALID_ARG;
+    DeviceGuard g(device);
+    if (!g.ok) return GLLMK_STATUS_RUNTIME_ERROR;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return GLLMK_STATUS_RUNTIME_ERROR;
+    if (prop.major != 10) return GLLMK_STATUS_UNSUPPORTED;  // kernels are sm_100a only
+    Ctx *c = new (std::nothrow) Ctx();
+    if (!c) return GLLMK_STATUS_OUT_OF_MEMORY;
+    c->device = device;
+    c->sm_count = prop.multiProcessorCount;
+    if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess) {
+        delete c;
+        return GLLMK_STATUS_RUNTIME_ERROR;
+    }
+    *out = c;
+    return GLLMK_STATUS_OK;
+}
+
+void gllmk_ctx_free(gllmk_ctx ctx) {
+    if (!ctx) return;
+    Ctx *c = static_cast<Ctx *>(ctx);
+    DeviceGuard g(c->device);
+    cudaDeviceSynchronize();
+    if (c->ws) cudaFree(c->ws);
+    if (c->dev_io) cudaFree(c->dev_io);
+    if (c->pin) cudaFreeHost(c->pin);
+    if (c->stream) cudaStreamDestroy(c->stream);
+    delete c;
+}
+
+const char *gllmk_last_error(gllmk_ctx ctx) {
+    if (!ctx) return "";
+    return static_cast<Ctx *>(ctx)->err.c_str();
+}
+
+int32_t gllmk_ctx_set(gllmk_ctx ctx, const char *key, int64_t value) {
+    if (!ctx || !key) return GLLMK_STATUS_INVALID_ARG;
+    Ctx *c = static_cast<Ctx *>(ctx);
+    if (!strcmp(key, "gemv_ksplit")) c->gemv_ksplit = value;
+    else if (!strcmp(key, "gemv_pdl")) c->gemv_pdl = value;
+    else return fail(c, GLLMK_STATUS_INVALID_ARG, "unknown key %s", key);
+    return GLLMK_STATUS_OK;
+}
+
+int32_t gllmk_weight_upload(gllmk_ctx ctx, int32_t quant_type, int64_t n, int64_t k, int32_t mx_block,
+                            const void *blocks, const void *scales, float global_scale, int32_t src_on_device,
+                            gllmk_weight *out) {
+    if (!ctx || !blocks || !out) return GLLMK_STATUS_INVALID_ARG;
+    *out = nullptr;
+    Ctx *c = static_cast<Ctx *>(ctx);
+    if (scales && quant_type != GLLMK_QUANT_MXFP4)
+        return fail(c, GLLMK_STATUS_INVALID_ARG, "scales must be NULL unless the type is MXFP4 (split form)");
+    DeviceGuard g(c->device);
+    Weight *w = nullptr;
+    int32_t rc = weight_alloc(c, quant_type, n, k, mx_block, global_scale, &w);
+    if (rc) return rc;
+    rc = weight_fill(c, w, blocks, scales, src_on_device != 0);
+    if (rc) { weight_destroy(w); return rc; }
+    *out = w;
+    return GLLMK_STATUS_OK;
+}
+
+void gllmk_weight_free(gllmk_weight w) { weight_destroy(static_cast<Weight *>(w)); }
+
+int32_t gllmk_weight_info(gllmk_weight wh, int32_t *quant_type, int64_t *n, int64_t *k, uint64_t *ref_bytes,
+                          uint64_t *dev_bytes) {
+    if (!wh) return GLLMK_STATUS_INVALID_ARG;
+    const Weight *w = static_cast<const Weight *>(wh);
+    if (quant_type) *quant_type = w->qt;
+    if (n) *n = w->n;
+    if (k) *k = w->k;
+    if (ref_bytes) *ref_bytes = w->ref_bytes;
+    if (dev_bytes) *dev_bytes = (uint64_t)w->qs_bytes + (uint64_t)w->aux_bytes;
+    return GLLMK_STATUS_OK;
+}
+
+int32_t gllmk_weight_unpack(gllmk_ctx ctx, gllmk_weight wh, void *blocks, void *scales, int32_t dst_on_device) {
+    if (!ctx || !wh || !blocks) return GLLMK_STATUS_INVALID_ARG;
+    Ctx *c = static_cast<Ctx *>(ctx);
+    const Weight *w = static_cast<const Weight *>(wh);
+    if (w->qt == GLLMK_QUANT_MXFP4 && !scales)
+        return fail(c, GLLMK_STATUS_INVALID_ARG, "MXFP4 unpack writes the split form and needs a scales buffer");
+    DeviceGuard g(c->device);
+    const bool split = w->qt == GLLMK_QUANT_MXFP4;
+    const size_t raw = split ? (size_t)w->n * (w->k / 2) : (size_t)w->ref_bytes;
+    const size_t sraw = split ? (size_t)w->n * (w->k / 32) : 0;
+    if (dst_on_device) {
+        int32_t rc = repack_unpack(c, w, blocks, scales, c->stream);
+        if (rc) return rc;
+        GK_CUDA(c, cudaStreamSynchronize(c->stream));
+        return GLLMK_STATUS_OK;
+    }
+    void *stage = nullptr;
+    const size_t off = (raw + 255) & ~(size_t)255;
+    GK_CUDA(c, cudaMalloc(&stage, off + sraw + 256));
+    int32_t rc = repack_unpack(c, w, stage, static_cast<char *>(stage) + off, c->stream);
+    cudaError_t e = cudaSuccess;
+    if (!rc) {
+        e = cudaMemcpyAsync(blocks, stage, raw, cudaMemcpyDeviceToHost, c->stream);
+        if (e == cudaSuccess && sraw)
+            e = cudaMemcpyAsync(scales, static_cast<char *>(stage) + off, sraw, cudaMemcpyDeviceToHost, c->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+    }
+    cudaFree(stage);
+    if (rc) return rc;
+    if (e != cudaSuccess) return cuda_fail(c, e, "unpack copy");
+    return GLLMK_STATUS_OK;
+}
+
+int32_t gllmk_dequant(gllmk_ctx ctx, gllmk_weight wh, float *out_dev, void *stream) {
+    if (!ctx || !wh || !out_dev) return GLLMK_STATUS_INVALID_ARG;
+    Ctx *c = static_cast<Ctx *>(ctx);
+    if (((uintptr_t)out_dev & 15) != 0) return fail(c, GLLMK_STATUS_INVALID_ARG, "out_dev must be 16-byte aligned");
+    DeviceGuard g(c->device);
+    return dequant_matrix(c, static_cast<const Weight *>(wh), out_dev, static_cast<cudaStream_t>(stream));
+}
+
+int32_t gllmk_gemv(gllmk_ctx ctx, gllmk_weight wh, const float *x_dev, int64_t x_stride_t, int64_t x_stride_k,
+                   int32_t m, float *y_dev, int64_t y_stride_t, int64_t y_stride_r, const float *row_scales,
+                   int64_t n_row_scales, void *stream) {
+    if (!ctx || !wh || !x_dev || !y_dev) return GLLMK_STATUS_INVALID_ARG;
+    Ctx *c = static_cast<Ctx *>(ctx);
+    const Weight *w = static_cast<const Weight *>(wh);
+    if (m < 1 || m > GLLMK_GEMV_MAX_M)
+        return fail(c, GLLMK_STATUS_INVALID_ARG, "gemv: m=%d outside 1..%d", m, GLLMK_GEMV_MAX_M);
+    if (row_scales && n_row_scales != 1 && n_row_scales != w->n) { row_scales = nullptr; n_row_scales = 0; }
+    if (w->device != c->device) return fail(c, GLLMK_STATUS_INVALID_ARG, "weight lives on another device");
+    DeviceGuard g(c->device);
+    return gemv_launch(c, w, x_dev, x_stride_t, x_stride_k, m, y_dev, y_stride_t, y_stride_r, row_scales, n_row_scales,
+                       static_cast<cudaStream_t>(stream));
+}
+
+// Shared body of the host-pointer matmuls: weight rows n_w, tokens m_t, reduction k.
+//   ref_layout: input [k, m_t], output [n_w, m_t]; else input [m_t, k], output [m_t, n_w].
+static int32_t matmul_host_impl(Ctx *c, const Weight *w, const float *x_host, int m_t, float *y_host, bool ref_layout,
+                                const float *scales_host, size_t n_scales) {
+    const int64_t n_w = w->n, k = w->k;
+    const size_t xb = (size_t)m_t * k * sizeof(float), yb = (size_t)m_t * n_w * sizeof(float);
+    const size_t sb = (n_scales == 1 || (int64_t)n_scales == n_w) ? n_scales * sizeof(float) : 0;
+    const size_t xo = 0, yo = (xb + 255) & ~(size_t)255, so = yo + ((yb + 255) & ~(size_t)255);
+    int32_t rc = ensure_pin(c, so + sb + 256);
+    if (!rc) rc = ensure_dev_io(c, so + sb + 256);
+    if (rc) return rc;
+    char *pin = static_cast<char *>(c->pin), *dev = static_cast<char *>(c->dev_io);
+    memcpy(pin + xo, x_host, xb);
+    if (sb) memcpy(pin + so, scales_host, sb);
+    GK_CUDA(c, cudaMemcpyAsync(dev + xo, pin + xo, xb, cudaMemcpyHostToDevice, c->stream));
+    if (sb) GK_CUDA(c, cudaMemcpyAsync(dev + so, pin + so, sb, cudaMemcpyHostToDevice, c->stream));
+    const float *xd = reinterpret_cast<const float *>(dev + xo);
+    float *yd = reinterpret_cast<float *>(dev + yo);
+    const float *sd = sb ? reinterpret_cast<const float *>(dev + so) : nullptr;
+    for (int t0 = 0; t0 < m_t; t0 += GLLMK_GEMV_MAX_M) {
+        const int mt = (m_t - t0 < GLLMK_GEMV_MAX_M) ? m_t - t0 : GLLMK_GEMV_MAX_M;
+        if (ref_layout)
+            rc = gemv_launch(c, w, xd + t0, 1, m_t, mt, yd + t0, 1, m_t, sd, (int64_t)n_scales, c->stream);
+        else
+            rc = gemv_launch(c, w, xd + (size_t)t0 * k, k, 1, mt, yd + (size_t)t0 * n_w, n_w, 1, sd, (int64_t)n_scales,
+                             c->stream);
+        if (rc) return rc;
+    }
+    GK_CUDA(c, cudaMemcpyAsync(pin + yo, dev + yo, yb, cudaMemcpyDeviceToHost, c->stream));
+    GK_CUDA(c, cudaStreamSynchronize(c->stream));
+    memcpy(y_host, pin + yo, yb);
+    return GLLMK_STATUS_OK;
+}
+
+int32_t gllmk_matmul_host(gllmk_ctx ctx, gllmk_weight wh, const float *x_host, int32_t m, float *y_host,
+                          int32_t ref_layout) {
+    if (!ctx || !wh || !x_host || !y_host) return GLLMK_STATUS_INVALID_ARG;
+    Ctx *c = static_cast<Ctx *>(ctx);
+    if (m < 1) return fail(c, GLLMK_STATUS_INVALID_ARG, "m must be positive");
+    const Weight *w = static_cast<const Weight *>(wh);
+    if (w->device != c->device) return fail(c, GLLMK_STATUS_INVALID_ARG, "weight lives on another device");
+    DeviceGuard g(c->device);
+    return matmul_host_impl(c, w, x_host, m, y_host, ref_layout != 0, nullptr, 0);
+}
+
+static int32_t family_matmul(gllmk_ctx ctx, const uint8_t *wb, const float *input, float *output, int32_t qt,
+                             int32_t want, size_t m, size_t n, size_t k) {
+    if (!ctx || !wb || !input || !output) return GLLMK_STATUS_INVALID_ARG;
+    Ctx *c = static_cast<Ctx *>(ctx);
+    if (qt != want)
+        return fail(c, GLLMK_STATUS_UNSUPPORTED, "quant type %d is not handled by this entry point", qt);
+    if (m == 0 || n == 0) return GLLMK_STATUS_OK;
+    if (n > 0x7fffffffu) return fail(c, GLLMK_STATUS_INVALID_ARG, "n too large");
+    DeviceGuard g(c->device);
+    Weight *w = nullptr;
+    int32_t rc = weight_alloc(c, qt, (int64_t)m, (int64_t)k, 0, 1.0f, &w);
+    if (rc) return rc;
+    rc = weight_fill(c, w, wb, nullptr, false);
+    if (!rc) rc = matmul_host_impl(c, w, input, (int)n, output, true, nullptr, 0);
+    weight_destroy(w);
+    return rc;
+}
+
+int32_t gllmk_kquant_matmul_f32(gllmk_ctx ctx, const uint8_t *weight_blocks, const float *input, float *output,
+                                int32_t quant_type, size_t m, size_t n, size_t k) {
+    return family_matmul(ctx, weight_blocks, input, output, quant_type, GLLMK_QUANT_Q4K, m, n, k);
+}
+int32_t gllmk_classic_matmul_f32(gllmk_ctx ctx, const uint8_t *weight_blocks, const float *input, float *output,
+                                 int32_t quant_type, size_t m, size_t n, size_t k) {
+    return family_matmul(ctx, weight_blocks, input, output, quant_type, GLLMK_QUANT_Q8_0, m, n, k);
+}
+
+int32_t gllmk_gemm_q4_f32(gllmk_ctx ctx, const uint8_t *weight, const float *input, float *output, const float *scales,
+                          size_t n_scales, size_t m, size_t n, size_t k) {
+    if (!ctx || !weight || !input || !output) return GLLMK_STATUS_INVALID_ARG;
+    Ctx *c = static_cast<Ctx *>(ctx);
+    if (n_scales && !scales) return GLLMK_STATUS_INVALID_ARG;
+    if (k % 256) return fail(c, GLLMK_STATUS_INVALID_ARG, "gemm_q4: k %% 256 != 0");
+    if (m == 0 || n == 0) return GLLMK_STATUS_OK;
+    if (m > 0x7fffffffu) return fail(c, GLLMK_STATUS_INVALID_ARG, "m too large");
+    DeviceGuard g(c->device);
+    Weight *w = nullptr;
+    int32_t rc = weight_alloc(c, GLLMK_QUANT_Q4K, (int64_t)n, (int64_t)k, 0, 1.0f, &w);
+    if (rc) return rc;
+    rc = weight_fill(c, w, weight, nullptr, false);
+    if (!rc) rc = matmul_host_impl(c, w, input, (int)m, output, false, scales, n_scales);
+    weight_destroy(w);
+    return rc;
+}
+
+static int32_t dequant_host(gllmk_ctx ctx, int32_t qt, const uint8_t *blocks, const uint8_t *scales, float global,
+                            float *out, size_t nblocks, size_t bs) {
+    if (!ctx || !blocks || !out) return GLLMK_STATUS_INVALID_ARG;
+    Ctx *c = static_cast<Ctx *>(ctx);
+    if (nblocks == 0) return GLLMK_STATUS_OK;
+    DeviceGuard g(c->device);
+    const size_t bbytes = (qt == GLLMK_QUANT_MXFP4) ? bs / 2 : (size_t)block_bytes_of(qt, 0);
+    const size_t raw = nblocks * bbytes, sraw = (qt == GLLMK_QUANT_MXFP4) ? nblocks : 0, ob = nblocks * bs * sizeof(float);
+    const size_t so = (raw + 255) & ~(size_t)255, oo = so + ((sraw + 255) & ~(size_t)255);
+    int32_t rc = ensure_dev_io(c, oo + ob + 256);
+    if (rc) return rc;
+    char *dev = static_cast<char *>(c->dev_io);
+    GK_CUDA(c, cudaMemcpyAsync(dev, blocks, raw, cudaMemcpyHostToDevice, c->stream));
+    if (sraw) GK_CUDA(c, cudaMemcpyAsync(dev + so, scales, sraw, cudaMemcpyHostToDevice, c->stream));
+    rc = dequant_raw(c, qt, reinterpret_cast<uint8_t *>(dev), reinterpret_cast<uint8_t *>(dev + so), global,
+                     reinterpret_cast<float *>(dev + oo), nblocks, bs, c->stream);
+    if (rc) return rc;
+    GK_CUDA(c, cudaMemcpyAsync(out, dev + oo, ob, cudaMemcpyDeviceToHost, c->stream));
+    GK_CUDA(c, cudaStreamSynchronize(c->stream));
+    return GLLMK_STATUS_OK;
+}
+
+int32_t gllmk_dequant_q4_k(gllmk_ctx ctx, const uint8_t *blocks, float *out, size_t nblocks) {
+    return dequant_host(ctx, GLLMK_QUANT_Q4K, blocks, nullptr, 1.0f, out, nblocks, 256);
+}
+int32_t gllmk_dequant_q8_0(gllmk_ctx ctx, const uint8_t *blocks, float *out, size_t nblocks) {
+    return dequant_host(ctx, GLLMK_QUANT_Q8_0, blocks, nullptr, 1.0f, out, nblocks, 32);
+}
+int32_t gllmk_dequant_mxfp4(gllmk_ctx ctx, const uint8_t *blocks, const uint8_t *scales, float *out, size_t num_blocks,
+                            size_t block_size) {
+    if (!ctx || !scales) return GLLMK_STATUS_INVALID_ARG;
+    if (block_size == 0 || (block_size & 1))
+        return fail(static_cast<Ctx *>(ctx), GLLMK_STATUS_INVALID_ARG, "mxfp4 block_size must be even and non-zero");
+    return dequant_host(ctx, GLLMK_QUANT_MXFP4, blocks, scales, 1.0f, out, num_blocks, block_size);
+}
+int32_t gllmk_dequant_nvfp4(gllmk_ctx ctx, const uint8_t *blocks, float global_scale, float *out, size_t nblocks) {
+    return dequant_host(ctx, GLLMK_QUANT_NVFP4, blocks, nullptr, global_scale, out, nblocks, 64);
+}
+
+int32_t gllmk_quantize(gllmk_ctx ctx, int32_t quant_type, const float *x_dev, int64_t rows, int64_t k, int32_t mx_block,
+                       void *blocks_dev, void *scales_dev, float *global_scale, void *stream) {
+    if (!ctx || !x_dev || !blocks_dev) return GLLMK_STATUS_INVALID_ARG;
+    Ctx *c = static_cast<Ctx *>(ctx);
+    if (rows <= 0 || k <= 0) return fail(c, GLLMK_STATUS_INVALID_ARG, "rows and k must be positive");
+    const int bs = block_size_of(quant_type, mx_block);
+    if (bs <= 0) return fail(c, GLLMK_STATUS_UNSUPPORTED, "unknown quant type %d", quant_type);
+    if (k % bs) return fail(c, GLLMK_STATUS_INVALID_ARG, "k=%lld is not a multiple of the block size %d", (long long)k, bs);
+    if (quant_type == GLLMK_QUANT_MXFP4 && !scales_dev) return GLLMK_STATUS_INVALID_ARG;
+    if (quant_type == GLLMK_QUANT_NVFP4 && !global_scale) return GLLMK_STATUS_INVALID_ARG;
+    DeviceGuard g(c->device);
+    return quantize_launch(c, quant_type, x_dev, rows, k, mx_block, blocks_dev, scales_dev, global_scale,
+                           static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

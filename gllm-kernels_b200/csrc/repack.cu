@@ -1,0 +1,365 @@
+// Weight repacker (reference block formats -> tiled device layouts, and back) and the
+// bit-exact decode kernels.  Layouts are described in common.cuh.
+#include "common.cuh"
+
+namespace gllmk {
+
+static inline unsigned grid_for(size_t n, unsigned block) { return (unsigned)((n + block - 1) / block); }
+
+// ================================ Q4_K =====================================================
+__global__ void repack_q4k_qs(const uint8_t *__restrict__ src, uint4 *__restrict__ qs, int64_t n, int64_t nb,
+                              size_t total) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int lane = (int)(idx & 31), j = (int)((idx >> 5) & 3);
+    const size_t tb = idx >> 7;  // T*nb + b
+    const int64_t T = (int64_t)(tb / (size_t)nb), b = (int64_t)(tb % (size_t)nb);
+    const int g = lane >> 2, t = lane & 3;
+    const int64_t row = 16 * T + g + 8 * (j >> 1);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (row < n) v = reinterpret_cast<const uint4 *>(src + ((size_t)row * nb + b) * 144)[1 + 2 * t + (j & 1)];
+    qs[idx] = v;
+}
+__global__ void repack_q4k_hdr(const uint8_t *__restrict__ src, uint4 *__restrict__ hdr, int64_t n, int64_t nb,
+                               size_t total) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int rr = (int)(idx & 15);
+    const size_t tb = idx >> 4;
+    const int64_t T = (int64_t)(tb / (size_t)nb), b = (int64_t)(tb % (size_t)nb);
+    const int64_t row = 16 * T + rr;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (row < n) v = reinterpret_cast<const uint4 *>(src + ((size_t)row * nb + b) * 144)[0];
+    hdr[idx] = v;
+}
+__global__ void unpack_q4k(const uint4 *__restrict__ qs, const uint4 *__restrict__ hdr, uint8_t *__restrict__ dst,
+                           int64_t n, int64_t nb, size_t total) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // (row*nb + b)*9 + u9
+    if (idx >= total) return;
+    const int u9 = (int)(idx % 9);
+    const size_t rb = idx / 9;
+    const int64_t row = (int64_t)(rb / (size_t)nb), b = (int64_t)(rb % (size_t)nb);
+    const int64_t T = row >> 4;
+    const int rr = (int)(row & 15);
+    uint4 v;
+    if (u9 == 0) v = hdr[((size_t)T * nb + b) * 16 + rr];
+    else {
+        const int u = u9 - 1, t = u >> 1, j = 2 * (rr >> 3) + (u & 1), lane = 4 * (rr & 7) + t;
+        v = qs[(((size_t)T * nb + b) * 4 + j) * 32 + lane];
+    }
+    reinterpret_cast<uint4 *>(dst + rb * 144)[u9] = v;
+    (void)n;
+}
+// out[row][256b + ...] following k_quant.rs:7-56; thread = one 32-bit word of qs (4 low + 4 high outputs)
+__global__ void dequant_q4k(const uint4 *__restrict__ qs, const uint4 *__restrict__ hdr, float *__restrict__ out,
+                            int64_t n, int64_t nb, size_t total) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // (row*nb + b)*32 + w, w = word 0..31 of qs
+    if (idx >= total) return;
+    const int wq = (int)(idx & 31);
+    const size_t rb = idx >> 5;
+    const int64_t row = (int64_t)(rb / (size_t)nb), b = (int64_t)(rb % (size_t)nb);
+    const int64_t T = row >> 4;
+    const int rr = (int)(row & 15);
+    const int u = wq >> 2, wi = wq & 3;  // uint4 index within the block, word within it
+    const int t = u >> 1, j = 2 * (rr >> 3) + (u & 1), lane = 4 * (rr & 7) + t;
+    const uint4 q4 = qs[(((size_t)T * nb + b) * 4 + j) * 32 + lane];
+    const uint32_t w = wi == 0 ? q4.x : (wi == 1 ? q4.y : (wi == 2 ? q4.z : q4.w));
+    const uint4 h = hdr[((size_t)T * nb + b) * 16 + rr];
+    const float d = __half2float(__ushort_as_half((unsigned short)(h.x & 0xFFFF)));
+    const float dmin = __half2float(__ushort_as_half((unsigned short)(h.x >> 16)));
+    uint8_t s[12];
+    *reinterpret_cast<uint32_t *>(s) = h.y;
+    *reinterpret_cast<uint32_t *>(s + 4) = h.z;
+    *reinterpret_cast<uint32_t *>(s + 8) = h.w;
+    const int group = u >> 1;  // 32 bytes per group
+    float sc[2], mn[2];
+#pragma unroll
+    for (int hs = 0; hs < 2; hs++) {
+        const int jj = 2 * group + hs;
+        if (jj < 4) { sc[hs] = (float)(s[jj] & 63); mn[hs] = (float)(s[jj + 4] & 63); }
+        else {
+            sc[hs] = (float)((s[jj + 4] & 0xF) | ((s[jj - 4] >> 6) << 4));
+            mn[hs] = (float)((s[jj + 4] >> 4) | ((s[jj] >> 6) << 4));
+        }
+    }
+    const float d1 = __fmul_rn(d, sc[0]), nm1 = __fmul_rn(dmin, mn[0]);
+    const float d2 = __fmul_rn(d, sc[1]), nm2 = __fmul_rn(dmin, mn[1]);
+    const int l = 16 * (u & 1) + 4 * wi;
+    float4 lo, hi;
+    lo.x = __fsub_rn(__fmul_rn(d1, (float)(w & 15u)), nm1);
+    lo.y = __fsub_rn(__fmul_rn(d1, (float)((w >> 8) & 15u)), nm1);
+    lo.z = __fsub_rn(__fmul_rn(d1, (float)((w >> 16) & 15u)), nm1);
+    lo.w = __fsub_rn(__fmul_rn(d1, (float)((w >> 24) & 15u)), nm1);
+    hi.x = __fsub_rn(__fmul_rn(d2, (float)((w >> 4) & 15u)), nm2);
+    hi.y = __fsub_rn(__fmul_rn(d2, (float)((w >> 12) & 15u)), nm2);
+    hi.z = __fsub_rn(__fmul_rn(d2, (float)((w >> 20) & 15u)), nm2);
+    hi.w = __fsub_rn(__fmul_rn(d2, (float)((w >> 28) & 15u)), nm2);
+    float *o = out + ((size_t)row * nb + b) * 256 + 64 * group + l;
+    *reinterpret_cast<float4 *>(o) = lo;
+    *reinterpret_cast<float4 *>(o + 32) = hi;
+    (void)n;
+}
+
+// ================================ Q8_0 =====================================================
+__global__ void repack_q80_qs(const uint8_t *__restrict__ src, uint4 *__restrict__ qs, int64_t n, int64_t nb,
+                              size_t total) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // (T*nb + b)*32 + lane
+    if (idx >= total) return;
+    const int lane = (int)(idx & 31);
+    const size_t tb = idx >> 5;
+    const int64_t T = (int64_t)(tb / (size_t)nb), b = (int64_t)(tb % (size_t)nb);
+    const int g = lane >> 2, t = lane & 3;
+    uint32_t v[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        const int64_t row = 16 * T + g + 8 * h;
+        if (row < n) {
+            const unsigned short *p =
+                reinterpret_cast<const unsigned short *>(src + ((size_t)row * nb + b) * 34 + 2 + 8 * t);
+            v[2 * h] = (uint32_t)p[0] | ((uint32_t)p[1] << 16);
+            v[2 * h + 1] = (uint32_t)p[2] | ((uint32_t)p[3] << 16);
+        }
+    }
+    qs[idx] = make_uint4(v[0], v[1], v[2], v[3]);
+}
+__global__ void repack_q80_d(const uint8_t *__restrict__ src, unsigned short *__restrict__ d, int64_t n, int64_t nb,
+                             int64_t nb8, size_t total) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // ((T*nb8 + b8)*16 + rr)*8 + bb
+    if (idx >= total) return;
+    const int bb = (int)(idx & 7), rr = (int)((idx >> 3) & 15);
+    const size_t tb = idx >> 7;
+    const int64_t T = (int64_t)(tb / (size_t)nb8), b8 = (int64_t)(tb % (size_t)nb8);
+    const int64_t row = 16 * T + rr, b = 8 * b8 + bb;
+    unsigned short v = 0;
+    if (row < n && b < nb) v = *reinterpret_cast<const unsigned short *>(src + ((size_t)row * nb + b) * 34);
+    d[idx] = v;
+}
+__global__ void unpack_q80(const uint4 *__restrict__ qs, const unsigned short *__restrict__ d,
+                           uint8_t *__restrict__ dst, int64_t n, int64_t nb, int64_t nb8, size_t total) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // (row*nb + b)*4 + t
+    if (idx >= total) return;
+    const int t = (int)(idx & 3);
+    const size_t rb = idx >> 2;
+    const int64_t row = (int64_t)(rb / (size_t)nb), b = (int64_t)(rb % (size_t)nb);
+    const int64_t T = row >> 4;
+    const int rr = (int)(row & 15), g = rr & 7, h = rr >> 3;
+    const uint4 q = qs[((size_t)T * nb + b) * 32 + 4 * g + t];
+    const uint32_t w0 = h ? q.z : q.x, w1 = h ? q.w : q.y;
+    unsigned short *p = reinterpret_cast<unsigned short *>(dst + rb * 34 + 2 + 8 * t);
+    p[0] = (unsigned short)(w0 & 0xFFFF); p[1] = (unsigned short)(w0 >> 16);
+    p[2] = (unsigned short)(w1 & 0xFFFF); p[3] = (unsigned short)(w1 >> 16);
+    if (t == 0)
+        *reinterpret_cast<unsigned short *>(dst + rb * 34) = d[(((size_t)T * nb8 + (b >> 3)) * 16 + rr) * 8 + (b & 7)];
+    (void)n;
+}
+// classic.rs:860-868: out = d * q; thread = 8 elements
+__global__ void dequant_q80(const uint4 *__restrict__ qs, const unsigned short *__restrict__ d, float *__restrict__ out,
+                            int64_t n, int64_t nb, int64_t nb8, size_t total) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // (row*nb + b)*4 + t
+    if (idx >= total) return;
+    const int t = (int)(idx & 3);
+    const size_t rb = idx >> 2;
+    const int64_t row = (int64_t)(rb / (size_t)nb), b = (int64_t)(rb % (size_t)nb);
+    const int64_t T = row >> 4;
+    const int rr = (int)(row & 15), g = rr & 7, h = rr >> 3;
+    const uint4 q = qs[((size_t)T * nb + b) * 32 + 4 * g + t];
+    const uint32_t w0 = h ? q.z : q.x, w1 = h ? q.w : q.y;
+    const float dv =
+        __half2float(__ushort_as_half(d[(((size_t)T * nb8 + (b >> 3)) * 16 + rr) * 8 + (b & 7)]));
+    float4 a, c;
+    a.x = __fmul_rn(dv, (float)(int8_t)(w0 & 0xFF)); a.y = __fmul_rn(dv, (float)(int8_t)((w0 >> 8) & 0xFF));
+    a.z = __fmul_rn(dv, (float)(int8_t)((w0 >> 16) & 0xFF)); a.w = __fmul_rn(dv, (float)(int8_t)(w0 >> 24));
+    c.x = __fmul_rn(dv, (float)(int8_t)(w1 & 0xFF)); c.y = __fmul_rn(dv, (float)(int8_t)((w1 >> 8) & 0xFF));
+    c.z = __fmul_rn(dv, (float)(int8_t)((w1 >> 16) & 0xFF)); c.w = __fmul_rn(dv, (float)(int8_t)(w1 >> 24));
+    float *o = out + rb * 32 + 8 * t;
+    *reinterpret_cast<float4 *>(o) = a;
+    *reinterpret_cast<float4 *>(o + 4) = c;
+    (void)n;
+}
+
+// ================================ MXFP4 / NVFP4 ============================================
+__device__ __forceinline__ size_t sf_offset(int64_t row, int64_t s, int64_t s_per_row) {
+    const int64_t atoms_per_rowtile = s_per_row >> 2;
+    const size_t atom = (size_t)(row >> 7) * (size_t)atoms_per_rowtile + (size_t)(s >> 2);
+    return atom * 512 + (size_t)(row & 31) * 16 + (size_t)((row & 127) >> 5) * 4 + (size_t)(s & 3);
+}
+// mode 0: MXFP4 split (blocks [n][k/2], scales [n][k/32]); mode 1: MXFP4 inline 17-byte blocks;
+// mode 2: NVFP4 36-byte blocks.  Thread = 4 data bytes (8 elements).
+__global__ void repack_fp4_data(const uint8_t *__restrict__ blocks, uint32_t *__restrict__ data, int64_t n,
+                                int64_t k, int mode, size_t total) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // row_pad * (k/8) + w
+    if (idx >= total) return;
+    const int64_t wpr = k >> 3;
+    const int64_t row = (int64_t)(idx / (size_t)wpr), w = (int64_t)(idx % (size_t)wpr);
+    uint32_t v = 0;
+    if (row < n) {
+        const uint8_t *p;
+        if (mode == 0) p = blocks + (size_t)row * (k >> 1) + 4 * w;
+        else if (mode == 1) p = blocks + ((size_t)row * (k >> 5) + (w >> 2)) * 17 + 1 + 4 * (w & 3);
+        else p = blocks + ((size_t)row * (k >> 6) + (w >> 3)) * 36 + 4 + 4 * (w & 7);
+        v = (uint32_t)p[0] | ((uint32_t)p[1] << 8) | ((uint32_t)p[2] << 16) | ((uint32_t)p[3] << 24);
+    }
+    data[idx] = v;
+}
+__global__ void repack_fp4_sf(const uint8_t *__restrict__ blocks, const uint8_t *__restrict__ scales,
+                              uint8_t *__restrict__ sf, int64_t n, int64_t k, int mode, size_t total) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // row_pad * s_per_row + s
+    if (idx >= total) return;
+    const int64_t spr = (mode == 2) ? (k >> 4) : (k >> 5);
+    const int64_t row = (int64_t)(idx / (size_t)spr), s = (int64_t)(idx % (size_t)spr);
+    uint8_t v = 0;
+    if (row < n) {
+        if (mode == 0) v = scales[(size_t)row * spr + s];
+        else if (mode == 1) v = blocks[((size_t)row * spr + s) * 17];
+        else v = blocks[((size_t)row * (k >> 6) + (s >> 2)) * 36 + (s & 3)];
+    }
+    sf[sf_offset(row, s, spr)] = v;
+}
+__global__ void unpack_fp4(const uint8_t *__restrict__ data, const uint8_t *__restrict__ sf, uint8_t *__restrict__ blocks,
+                           uint8_t *__restrict__ scales, int64_t n, int64_t k, int nv, size_t total) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // row * (k/2) + byte
+    if (idx >= total) return;
+    const int64_t bpr = k >> 1;
+    const int64_t row = (int64_t)(idx / (size_t)bpr), by = (int64_t)(idx % (size_t)bpr);
+    const uint8_t v = data[idx];
+    if (!nv) {
+        blocks[idx] = v;
+        if ((by & 15) == 0) scales[(size_t)row * (k >> 5) + (by >> 4)] = sf[sf_offset(row, by >> 4, k >> 5)];
+    } else {
+        uint8_t *blk = blocks + ((size_t)row * (k >> 6) + (by >> 5)) * 36;
+        blk[4 + (by & 31)] = v;
+        if ((by & 7) == 0) blk[(by & 31) >> 3] = sf[sf_offset(row, by >> 3, k >> 4)];
+    }
+    (void)n;
+}
+// thread = 4 data bytes -> 8 f32.  MXFP4: LUT[code] * e8m0 (quant_mxfp4.rs:95-108);
+// NVFP4: (global * e4m3(sub)) * LUT[code] (quant.rs:77-86).
+__global__ void dequant_fp4(const uint32_t *__restrict__ data, const uint8_t *__restrict__ sf, float *__restrict__ out,
+                            int64_t n, int64_t k, int nv, float global, size_t total) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // row * (k/8) + w
+    if (idx >= total) return;
+    const int64_t wpr = k >> 3;
+    const int64_t row = (int64_t)(idx / (size_t)wpr), w = (int64_t)(idx % (size_t)wpr);
+    const uint32_t v = data[idx];
+    float s;
+    if (!nv) s = e8m0_to_f32(sf[sf_offset(row, w >> 2, k >> 5)]);
+    else s = __fmul_rn(global, e4m3_to_f32(sf[sf_offset(row, w >> 1, k >> 4)]));
+    float r[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const float c = e2m1_to_f32((v >> (4 * i)) & 15u);
+        r[i] = nv ? __fmul_rn(s, c) : __fmul_rn(c, s);
+    }
+    float *o = out + (size_t)row * k + 8 * w;
+    *reinterpret_cast<float4 *>(o) = make_float4(r[0], r[1], r[2], r[3]);
+    *reinterpret_cast<float4 *>(o + 4) = make_float4(r[4], r[5], r[6], r[7]);
+    (void)n;
+}
+
+// ================================ raw-block decode (host-pointer drop-ins) ===================
+__global__ void dequant_raw_kernel(int qt, const uint8_t *__restrict__ blocks, const uint8_t *__restrict__ scales,
+                                   float global, float *__restrict__ out, size_t bs, size_t total) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // output element
+    if (idx >= total) return;
+    const size_t blk = idx / bs;
+    const int e = (int)(idx % bs);
+    float r;
+    if (qt == GLLMK_QUANT_Q4K) {
+        const uint8_t *b = blocks + blk * 144;
+        const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(b)));
+        const float dmin = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(b + 2)));
+        const uint8_t *s = b + 4;
+        const int mini = e >> 5, l = e & 31, g = mini >> 1;
+        const uint8_t byte = b[16 + 32 * g + l];
+        const float q = (float)((mini & 1) ? (byte >> 4) : (byte & 15));
+        float sc, m;
+        if (mini < 4) { sc = (float)(s[mini] & 63); m = (float)(s[mini + 4] & 63); }
+        else {
+            sc = (float)((s[mini + 4] & 0xF) | ((s[mini - 4] >> 6) << 4));
+            m = (float)((s[mini + 4] >> 4) | ((s[mini] >> 6) << 4));
+        }
+        r = __fsub_rn(__fmul_rn(__fmul_rn(d, sc), q), __fmul_rn(dmin, m));
+    } else if (qt == GLLMK_QUANT_Q8_0) {
+        const uint8_t *b = blocks + blk * 34;
+        const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(b)));
+        r = __fmul_rn(d, (float)(int8_t)b[2 + e]);
+    } else if (qt == GLLMK_QUANT_MXFP4) {
+        const uint8_t byte = blocks[blk * (bs / 2) + (e >> 1)];
+        r = __fmul_rn(e2m1_to_f32((e & 1) ? (byte >> 4) : (byte & 15)), e8m0_to_f32(scales[blk]));
+    } else {
+        const uint8_t *b = blocks + blk * 36;
+        const uint8_t byte = b[4 + (e >> 1)];
+        const float s = __fmul_rn(global, e4m3_to_f32(b[e >> 4]));
+        r = __fmul_rn(s, e2m1_to_f32((e & 1) ? (byte >> 4) : (byte & 15)));
+    }
+    out[idx] = r;
+}
+
+// ================================ host side ================================================
+int32_t repack_upload(Ctx *c, Weight *w, const void *blocks, const void *scales, cudaStream_t s) {
+    const uint8_t *src = static_cast<const uint8_t *>(blocks);
+    if (w->qt == GLLMK_QUANT_Q4K) {
+        const size_t tq = (size_t)(w->n_pad / 16) * w->nb * 128, th = (size_t)(w->n_pad / 16) * w->nb * 16;
+        repack_q4k_qs<<<grid_for(tq, 256), 256, 0, s>>>(src, (uint4 *)w->qs, w->n, w->nb, tq);
+        repack_q4k_hdr<<<grid_for(th, 256), 256, 0, s>>>(src, (uint4 *)w->aux, w->n, w->nb, th);
+    } else if (w->qt == GLLMK_QUANT_Q8_0) {
+        const size_t tq = (size_t)(w->n_pad / 16) * w->nb * 32, td = (size_t)(w->n_pad / 16) * w->nb8 * 128;
+        repack_q80_qs<<<grid_for(tq, 256), 256, 0, s>>>(src, (uint4 *)w->qs, w->n, w->nb, tq);
+        repack_q80_d<<<grid_for(td, 256), 256, 0, s>>>(src, (unsigned short *)w->aux, w->n, w->nb, w->nb8, td);
+    } else {
+        const int mode = (w->qt == GLLMK_QUANT_NVFP4) ? 2 : (scales ? 0 : 1);
+        const int64_t spr = (mode == 2) ? (w->k >> 4) : (w->k >> 5);
+        const size_t td = (size_t)w->n_pad * (w->k >> 3), ts = (size_t)w->n_pad * spr;
+        repack_fp4_data<<<grid_for(td, 256), 256, 0, s>>>(src, (uint32_t *)w->qs, w->n, w->k, mode, td);
+        repack_fp4_sf<<<grid_for(ts, 256), 256, 0, s>>>(src, (const uint8_t *)scales, (uint8_t *)w->aux, w->n, w->k,
+                                                        mode, ts);
+    }
+    GK_CUDA(c, cudaGetLastError());
+    return GLLMK_STATUS_OK;
+}
+
+int32_t repack_unpack(Ctx *c, const Weight *w, void *blocks, void *scales, cudaStream_t s) {
+    uint8_t *dst = static_cast<uint8_t *>(blocks);
+    if (w->qt == GLLMK_QUANT_Q4K) {
+        const size_t t = (size_t)w->n * w->nb * 9;
+        unpack_q4k<<<grid_for(t, 256), 256, 0, s>>>((const uint4 *)w->qs, (const uint4 *)w->aux, dst, w->n, w->nb, t);
+    } else if (w->qt == GLLMK_QUANT_Q8_0) {
+        const size_t t = (size_t)w->n * w->nb * 4;
+        unpack_q80<<<grid_for(t, 256), 256, 0, s>>>((const uint4 *)w->qs, (const unsigned short *)w->aux, dst, w->n,
+                                                    w->nb, w->nb8, t);
+    } else {
+        const size_t t = (size_t)w->n * (w->k >> 1);
+        unpack_fp4<<<grid_for(t, 256), 256, 0, s>>>((const uint8_t *)w->qs, (const uint8_t *)w->aux, dst,
+                                                    (uint8_t *)scales, w->n, w->k, w->qt == GLLMK_QUANT_NVFP4, t);
+    }
+    GK_CUDA(c, cudaGetLastError());
+    return GLLMK_STATUS_OK;
+}
+
+int32_t dequant_matrix(Ctx *c, const Weight *w, float *out, cudaStream_t s) {
+    if (w->qt == GLLMK_QUANT_Q4K) {
+        const size_t t = (size_t)w->n * w->nb * 32;
+        dequant_q4k<<<grid_for(t, 256), 256, 0, s>>>((const uint4 *)w->qs, (const uint4 *)w->aux, out, w->n, w->nb, t);
+    } else if (w->qt == GLLMK_QUANT_Q8_0) {
+        const size_t t = (size_t)w->n * w->nb * 4;
+        dequant_q80<<<grid_for(t, 256), 256, 0, s>>>((const uint4 *)w->qs, (const unsigned short *)w->aux, out, w->n,
+                                                     w->nb, w->nb8, t);
+    } else {
+        const size_t t = (size_t)w->n * (w->k >> 3);
+        dequant_fp4<<<grid_for(t, 256), 256, 0, s>>>((const uint32_t *)w->qs, (const uint8_t *)w->aux, out, w->n, w->k,
+                                                     w->qt == GLLMK_QUANT_NVFP4, w->global_scale, t);
+    }
+    GK_CUDA(c, cudaGetLastError());
+    return GLLMK_STATUS_OK;
+}
+
+int32_t dequant_raw(Ctx *c, int32_t qt, const uint8_t *blocks, const uint8_t *scales, float global, float *out,
+                    size_t nblocks, size_t block_size, cudaStream_t s) {
+    const size_t total = nblocks * block_size;
+    if (total == 0) return GLLMK_STATUS_OK;
+    dequant_raw_kernel<<<grid_for(total, 256), 256, 0, s>>>(qt, blocks, scales, global, out, block_size, total);
+    GK_CUDA(c, cudaGetLastError());
+    return GLLMK_STATUS_OK;
+}
+
+}  // namespace gllmk

@@ -1,0 +1,245 @@
+"""Host-side mirror of the quant slice of gllm-kernels' operator trait, bound to libgllmk.so.
+
+`GpuKernels` carries the same method names, argument order and shape conventions as the reference's
+`Kernels<f32>` quant methods (src/traits.rs:473-608; CPU implementation src/cpu_kernels/mod.rs) so
+code and tests written against the reference read the same here.  Host-array methods take numpy
+arrays where the reference takes slices.  The resident-weight methods (`upload`, `gemv`, ...) are
+the additions a GPU needs: weights are repacked once and stay in HBM.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import quant as Q
+from ._lib import GllmkError, Status, lib
+from .quant import QuantType
+
+
+def _np(a, dtype, writable=False):
+    if not isinstance(a, np.ndarray) or a.dtype != dtype or not a.flags.c_contiguous:
+        if writable:
+            raise TypeError(f"output must be a C-contiguous numpy array of {np.dtype(dtype).name}")
+        a = np.ascontiguousarray(a, dtype=dtype)
+    return a
+
+
+def _ptr(a) -> int:
+    """Address of a numpy array, a torch tensor, or a raw integer device pointer."""
+    if a is None:
+        return 0
+    if isinstance(a, np.ndarray):
+        return a.ctypes.data
+    if isinstance(a, int):
+        return a
+    return a.data_ptr()
+
+
+def _stream(stream) -> int:
+    if stream is None:
+        import torch
+        return torch.cuda.current_stream().cuda_stream
+    if isinstance(stream, int):
+        return stream
+    return stream.cuda_stream
+
+
+class Weight:
+    """A weight matrix resident on the device in the kernels' tiled layout (opaque gllmk_weight)."""
+
+    def __init__(self, owner: "GpuKernels", handle: int, qt: QuantType, n: int, k: int):
+        self._owner, self._h, self.quant_type, self.n, self.k = owner, handle, qt, n, k
+
+    def info(self) -> dict:
+        qt, n, k = C.c_int32(), C.c_int64(), C.c_int64()
+        rb, db = C.c_uint64(), C.c_uint64()
+        self._owner._check(lib().gllmk_weight_info(self._h, C.byref(qt), C.byref(n), C.byref(k), C.byref(rb),
+                                                   C.byref(db)), "weight_info")
+        return {"quant_type": qt.value, "n": n.value, "k": k.value, "ref_bytes": rb.value, "dev_bytes": db.value}
+
+    @property
+    def ref_bytes(self) -> int:
+        return self.info()["ref_bytes"]
+
+    def free(self) -> None:
+        if self._h:
+            lib().gllmk_weight_free(self._h)
+            self._h = 0
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class GpuKernels:
+    """B200 implementation of the reference's quantized operators (one context = one device)."""
+
+    GEMV_MAX_M = 16
+
+    def __init__(self, device: int = 0):
+        h = C.c_void_p()
+        rc = lib().gllmk_ctx_create(device, C.byref(h))
+        if rc:
+            raise GllmkError(rc, "gllmk_ctx_create", "no usable CUDA device (there is no CPU fallback)")
+        self._ctx = h.value
+        self.device = device
+
+    # ---- plumbing ---------------------------------------------------------------------------
+    def close(self) -> None:
+        if getattr(self, "_ctx", None):
+            lib().gllmk_ctx_free(self._ctx)
+            self._ctx = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, rc: int, what: str) -> None:
+        if rc:
+            raise GllmkError(rc, what, (lib().gllmk_last_error(self._ctx) or b"").decode())
+
+    def set(self, key: str, value: int) -> None:
+        self._check(lib().gllmk_ctx_set(self._ctx, key.encode(), int(value)), "ctx_set")
+
+    # ---- resident weights -------------------------------------------------------------------
+    def upload(self, quant_type: QuantType, n: int, k: int, blocks, scales=None, global_scale: float = 1.0) -> Weight:
+        """Repack reference-format blocks ([n rows][k/bs blocks]) into HBM.  `blocks`/`scales` may be numpy
+        arrays (host) or CUDA torch tensors (device)."""
+        on_dev = not isinstance(blocks, np.ndarray)
+        if not on_dev:
+            blocks = _np(blocks, np.uint8)
+            scales = _np(scales, np.uint8) if scales is not None else None
+            expect = n * (k // quant_type.block_size()) * quant_type.block_bytes() if quant_type.block_size() else 0
+            if quant_type.id == Q.MXFP4 and scales is not None:
+                expect = n * k // 2
+            if expect and blocks.size != expect:
+                raise GllmkError(Status.INVALID_ARG, "upload", f"blocks holds {blocks.size} bytes, expected {expect}")
+        h = C.c_void_p()
+        rc = lib().gllmk_weight_upload(self._ctx, quant_type.id, n, k, quant_type.mx_block, _ptr(blocks), _ptr(scales),
+                                       float(global_scale), int(on_dev), C.byref(h))
+        self._check(rc, "gllmk_weight_upload")
+        return Weight(self, h.value, quant_type, n, k)
+
+    def unpack(self, w: Weight):
+        """Inverse of the repack: reference-format bytes (numpy).  MXFP4 returns (blocks, scales)."""
+        qt = w.quant_type
+        if qt.id == Q.MXFP4:
+            blocks = np.empty(w.n * w.k // 2, np.uint8)
+            scales = np.empty(w.n * w.k // 32, np.uint8)
+            self._check(lib().gllmk_weight_unpack(self._ctx, w._h, _ptr(blocks), _ptr(scales), 0), "weight_unpack")
+            return blocks, scales
+        blocks = np.empty(w.n * (w.k // qt.block_size()) * qt.block_bytes(), np.uint8)
+        self._check(lib().gllmk_weight_unpack(self._ctx, w._h, _ptr(blocks), 0, 0), "weight_unpack")
+        return blocks
+
+    def dequant(self, w: Weight, out=None, stream=None):
+        """Whole-matrix decode to f32 [n, k] on the device (bit-exact with the reference's scalar decode)."""
+        import torch
+        if out is None:
+            out = torch.empty((w.n, w.k), dtype=torch.float32, device=f"cuda:{self.device}")
+        self._check(lib().gllmk_dequant(self._ctx, w._h, _ptr(out), _stream(stream)), "gllmk_dequant")
+        return out
+
+    def gemv(self, w: Weight, x, y=None, ref_layout: bool = False, row_scales=None, stream=None):
+        """Decode product with device tensors.  ref_layout=False: x [m, k] -> y [m, n] (gemm_q4 convention);
+        ref_layout=True: x [k, m] -> y [n, m] (kquant_matmul / classic_matmul convention)."""
+        import torch
+        m = x.shape[1] if ref_layout else x.shape[0]
+        if y is None:
+            y = torch.empty((w.n, m) if ref_layout else (m, w.n), dtype=torch.float32, device=x.device)
+        if ref_layout:
+            xs, ys = (1, m), (1, m)
+        else:
+            xs, ys = (w.k, 1), (w.n, 1)
+        ns = 0 if row_scales is None else row_scales.numel()
+        rc = lib().gllmk_gemv(self._ctx, w._h, _ptr(x), xs[0], xs[1], m, _ptr(y), ys[0], ys[1], _ptr(row_scales), ns,
+                              _stream(stream))
+        self._check(rc, "gllmk_gemv")
+        return y
+
+    def matmul_host(self, w: Weight, x, ref_layout: bool = False) -> np.ndarray:
+        """Resident weight, HOST activations and outputs (numpy): the call timed end to end."""
+        x = _np(x, np.float32)
+        m = x.shape[1] if ref_layout else x.shape[0]
+        y = np.empty((w.n, m) if ref_layout else (m, w.n), np.float32)
+        self._check(lib().gllmk_matmul_host(self._ctx, w._h, _ptr(x), m, _ptr(y), int(ref_layout)), "gllmk_matmul_host")
+        return y
+
+    def quantize(self, quant_type: QuantType, x, global_scale: float = 0.0, stream=None):
+        """f32 [rows, k] CUDA tensor -> reference-format blocks (CUDA uint8 tensors).
+        Returns blocks for Q4K/Q8_0, (blocks, scales) for MXFP4, (blocks, global_scale) for NVFP4."""
+        import torch
+        rows, k = x.shape
+        bs, bb = quant_type.block_size(), quant_type.block_bytes()
+        nblk = rows * k // bs
+        g = C.c_float(global_scale)
+        if quant_type.id == Q.MXFP4:
+            blocks = torch.empty(nblk * bs // 2, dtype=torch.uint8, device=x.device)
+            scales = torch.empty(nblk, dtype=torch.uint8, device=x.device)
+        else:
+            blocks = torch.empty(nblk * bb, dtype=torch.uint8, device=x.device)
+            scales = None
+        rc = lib().gllmk_quantize(self._ctx, quant_type.id, _ptr(x), rows, k, quant_type.mx_block, _ptr(blocks),
+                                  _ptr(scales), C.byref(g), _stream(stream))
+        self._check(rc, "gllmk_quantize")
+        if quant_type.id == Q.MXFP4:
+            return blocks, scales
+        if quant_type.id == Q.NVFP4:
+            return blocks, g.value
+        return blocks
+
+    # ---- the reference's operator methods (host arrays, E = f32) -------------------------------
+    def dequant_q4_k(self, block, out) -> None:
+        """Kernels::dequant_q4_k(block, out) (src/traits.rs:476)."""
+        block, out = _np(block, np.uint8), _np(out, np.float32, True)
+        self._check(lib().gllmk_dequant_q4_k(self._ctx, _ptr(block), _ptr(out), block.size // 144), "dequant_q4_k")
+
+    def dequant_q8_0(self, block, out) -> None:
+        """Kernels::dequant_q8_0(block, out) (src/traits.rs:488)."""
+        block, out = _np(block, np.uint8), _np(out, np.float32, True)
+        self._check(lib().gllmk_dequant_q8_0(self._ctx, _ptr(block), _ptr(out), block.size // 34), "dequant_q8_0")
+
+    def dequant_mxfp4(self, blocks, scales, output, block_size: int) -> None:
+        """quant_mxfp4::dequant_mxfp4(blocks, scales, output, block_size) (src/quant_mxfp4.rs:267-292)."""
+        blocks, scales, output = _np(blocks, np.uint8), _np(scales, np.uint8), _np(output, np.float32, True)
+        if block_size <= 0 or block_size % 2 or blocks.size != scales.size * block_size // 2 \
+                or output.size != scales.size * block_size:
+            raise GllmkError(Status.INVALID_ARG, "dequant_mxfp4", "length mismatch")  # reference returns Err
+        self._check(lib().gllmk_dequant_mxfp4(self._ctx, _ptr(blocks), _ptr(scales), _ptr(output), scales.size,
+                                              block_size), "dequant_mxfp4")
+
+    def dequant_nvfp4(self, blocks, global_scale: float, output) -> None:
+        blocks, output = _np(blocks, np.uint8), _np(output, np.float32, True)
+        self._check(lib().gllmk_dequant_nvfp4(self._ctx, _ptr(blocks), float(global_scale), _ptr(output),
+                                              blocks.size // 36), "dequant_nvfp4")
+
+    def kquant_matmul(self, weight_blocks, input, output, quant_type: QuantType, m: int, n: int, k: int) -> None:
+        """Kernels::kquant_matmul (src/traits.rs:543-551): m weight rows, n batch columns, input [k, n],
+        output [m, n]."""
+        w, x, y = _np(weight_blocks, np.uint8), _np(input, np.float32), _np(output, np.float32, True)
+        self._check(lib().gllmk_kquant_matmul_f32(self._ctx, _ptr(w), _ptr(x), _ptr(y), quant_type.id, m, n, k),
+                    "kquant_matmul")
+
+    def classic_matmul(self, weight_blocks, input, output, quant_type: QuantType, m: int, n: int, k: int) -> None:
+        """Kernels::classic_matmul (src/traits.rs:553-563)."""
+        w, x, y = _np(weight_blocks, np.uint8), _np(input, np.float32), _np(output, np.float32, True)
+        self._check(lib().gllmk_classic_matmul_f32(self._ctx, _ptr(w), _ptr(x), _ptr(y), quant_type.id, m, n, k),
+                    "classic_matmul")
+
+    def gemm_q4(self, weight, input, output, scales, m: int, n: int, k: int) -> None:
+        """Kernels::gemm_q4 (src/traits.rs:511-520): m batch rows, n features, input [m, k], output [m, n]."""
+        w, x, y = _np(weight, np.uint8), _np(input, np.float32), _np(output, np.float32, True)
+        s = _np(scales, np.float32) if scales is not None and len(scales) else None
+        self._check(lib().gllmk_gemm_q4_f32(self._ctx, _ptr(w), _ptr(x), _ptr(y), _ptr(s), 0 if s is None else s.size,
+                                            m, n, k), "gemm_q4")
+
+    def gemv_q4(self, weight, input, scale: float, n: int) -> float:
+        """Kernels::gemv_q4 (src/traits.rs:501): one Q4_K row of n elements, result * scale."""
+        out = np.empty(1, np.float32)
+        self.gemm_q4(weight, input, out, [scale], 1, 1, n)
+        return float(out[0])

@@ -1,0 +1,179 @@
+/*
+ * gllmk — B200 (sm_100a) implementation of the quantized-matmul operators of gllm-kernels.
+ *
+ * C ABI in the conventions of the reference's own FFI (gllm-kernels src/ffi/mod.rs,
+ * src/ffi/types.rs:4-14,31-41): every entry point returns an int32 status with the reference's
+ * values, results come back through out-pointers, every pointer is null-checked first
+ * (-> GLLMK_STATUS_INVALID_ARG), handles are opaque `void*`, `*_free(NULL)` is a no-op and no
+ * function panics or throws across the boundary.  No existing `gllm_*` symbol is replaced: the
+ * reference's FFI has no quant-matmul entry point, so these are the symbols a Rust
+ * `impl Kernels<f32>` shim binds for the quant slice of the operator trait
+ * (src/traits.rs:473-608).  Each declaration names the reference interface it stands in for.
+ *
+ * Dimension names follow the benchmark: M = tokens, N = weight rows (output features),
+ * K = reduction length.  The reference's `kquant_matmul(m, n, k)` calls these (N, M, K).
+ *
+ * There is no CPU fallback: without a CUDA device every compute entry returns
+ * GLLMK_STATUS_RUNTIME_ERROR.
+ */
+#ifndef GLLMK_H
+#define GLLMK_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define GLLMK_API __attribute__((visibility("default")))
+#else
+#define GLLMK_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* src/ffi/types.rs:4-14 (GllmStatus), same integers. */
+enum {
+    GLLMK_STATUS_OK = 0,
+    GLLMK_STATUS_INVALID_ARG = -1,
+    GLLMK_STATUS_OUT_OF_MEMORY = -2,
+    GLLMK_STATUS_COMPILE_ERROR = -3,
+    GLLMK_STATUS_RUNTIME_ERROR = -4,
+    GLLMK_STATUS_UNSUPPORTED = -5,
+    GLLMK_STATUS_IO_ERROR = -6
+};
+
+/* The formats of the path out of src/quant.rs:8-87 (QuantType).  The Rust enum has no stable
+ * discriminants, so the ids are this boundary's. */
+enum {
+    GLLMK_QUANT_Q4K = 1,   /* QuantType::Q4K    256 el / 144 B  (src/quant.rs:122-127) */
+    GLLMK_QUANT_Q8_0 = 2,  /* QuantType::Q8_0    32 el /  34 B  (src/quant.rs:290-293) */
+    GLLMK_QUANT_MXFP4 = 3, /* QuantType::Mxfp4{block_size}      (src/quant.rs:66-76)   */
+    GLLMK_QUANT_NVFP4 = 4  /* QuantType::Nvfp4   64 el /  36 B  (src/quant.rs:366-371) */
+};
+
+/* Element type of an activation / output matrix handed to gllmk_gemm. */
+enum { GLLMK_DTYPE_F32 = 0, GLLMK_DTYPE_BF16 = 1 };
+
+typedef void *gllmk_ctx;    /* opaque, like GllmBackend (src/ffi/types.rs:31-32) */
+typedef void *gllmk_weight; /* opaque, like GllmWeights (src/ffi/types.rs:40-41) */
+
+/* ---- library / device information ------------------------------------------------------- */
+
+/* gllm_version (src/ffi/mod.rs:198-201): static NUL-terminated string. */
+GLLMK_API const char *gllmk_version(void);
+/* gllm_hw_info (src/ffi/mod.rs:209-222): writes a NUL-terminated description of device 0 (or
+ * "no CUDA device"), returns the bytes written (excluding NUL) or INVALID_ARG. */
+GLLMK_API int32_t gllmk_hw_info(char *buf, size_t len);
+/* QuantType::block_size / block_bytes (src/quant.rs:375-456); 0 for an unknown id.
+ * `mx_block` is Mxfp4's block_size and ignored otherwise. */
+GLLMK_API int32_t gllmk_quant_block_size(int32_t quant_type, int32_t mx_block);
+GLLMK_API int32_t gllmk_quant_block_bytes(int32_t quant_type, int32_t mx_block);
+
+/* ---- context ---------------------------------------------------------------------------- */
+
+/* gllm_backend_create / gllm_backend_free (src/ffi/mod.rs:25-57).  Binds to CUDA device
+ * `device`; owns the activation staging workspace shared by all calls made with it.  Calls on
+ * one context must not overlap in time (use one context per stream / thread). */
+GLLMK_API int32_t gllmk_ctx_create(int32_t device, gllmk_ctx *out);
+GLLMK_API void gllmk_ctx_free(gllmk_ctx ctx);
+/* Text of the last error raised through this context ("" if none).  Never NULL. */
+GLLMK_API const char *gllmk_last_error(gllmk_ctx ctx);
+/* Tuning knobs, for experiments.  key: "gemv_ksplit" (0 = auto, else 1,2,4,8),
+ * "gemv_pdl" (1 = overlap the activation staging kernel with the weight stream). */
+GLLMK_API int32_t gllmk_ctx_set(gllmk_ctx ctx, const char *key, int64_t value);
+
+/* ---- weights: upload + repack, the inverse, and the bit-exact decode ----------------------- */
+
+/* gllm_weights_create + gllm_weights_get_ptr fill (src/ffi/mod.rs:228-345): takes a weight
+ * matrix of `n` rows x `k` columns as the reference stores it — row-major runs of k/block_size
+ * blocks (src/cpu_kernels/mod.rs:476) — and repacks it on the device into the 16-byte-aligned
+ * tiled layout the kernels stream.
+ *   Q4K / Q8_0 / NVFP4: `blocks` holds n*(k/bs)*block_bytes bytes, `scales` must be NULL.
+ *   MXFP4: split form of dequant_mxfp4 (src/quant_mxfp4.rs:72) — `blocks` holds n*k/2 nibble
+ *          bytes and `scales` n*k/mx_block E8M0 bytes; or, with scales == NULL, the GGUF inline
+ *          form (17-byte blocks, scale first; src/quant.rs:427).  mx_block must be 32.
+ *   `global_scale` is NVFP4's out-of-band per-tensor f32 (src/quant.rs:77-86); pass 1 otherwise.
+ *   `src_on_device` != 0 means `blocks`/`scales` are device pointers (16-byte aligned).
+ * Errors: INVALID_ARG (null, n<=0, k not a multiple of the block size / of 256 for FP4 formats),
+ * UNSUPPORTED (unknown type, mx_block != 32), OUT_OF_MEMORY, RUNTIME_ERROR. */
+GLLMK_API int32_t gllmk_weight_upload(gllmk_ctx ctx, int32_t quant_type, int64_t n, int64_t k, int32_t mx_block,
+                            const void *blocks, const void *scales, float global_scale,
+                            int32_t src_on_device, gllmk_weight *out);
+/* gllm_weights_free (src/ffi/mod.rs:262-266). */
+GLLMK_API void gllmk_weight_free(gllmk_weight w);
+/* Shape / size query.  Any out-pointer may be NULL.  `ref_bytes` = bytes of the reference-format
+ * blocks (the algorithmic weight bytes), `dev_bytes` = bytes held on the device. */
+GLLMK_API int32_t gllmk_weight_info(gllmk_weight w, int32_t *quant_type, int64_t *n, int64_t *k, uint64_t *ref_bytes,
+                          uint64_t *dev_bytes);
+/* Inverse of the repack: writes the reference-format bytes back (same forms as upload; for MXFP4
+ * always the split form).  Bit-exact round trip. `dst_on_device` as above. */
+GLLMK_API int32_t gllmk_weight_unpack(gllmk_ctx ctx, gllmk_weight w, void *blocks, void *scales, int32_t dst_on_device);
+/* Kernels::dequant_q4_k / dequant_q8_0 (src/traits.rs:476,488), dequant_mxfp4_scalar
+ * (src/quant_mxfp4.rs:72-109) and the NVFP4 formula (src/quant.rs:77-86) over the whole matrix:
+ * f32 [n, k] row-major into device memory, bit-exact with the reference's scalar decode. */
+GLLMK_API int32_t gllmk_dequant(gllmk_ctx ctx, gllmk_weight w, float *out_dev, void *stream);
+
+/* ---- decode: fused dequantize + GEMV (M <= 16 tokens) -------------------------------------- */
+
+/* Kernels::kquant_matmul / classic_matmul (src/traits.rs:543-563) and gemm_q4
+ * (src/traits.rs:511-520) for small batches, on device memory with resident weights.
+ *   y[t, r] = sum_k W[r, k] * x[t, k],  t < m <= GLLMK_GEMV_MAX_M, r < n.
+ * Element (t, k) of x is x_dev[t*x_stride_t + k*x_stride_k]; element (t, r) of y is
+ * y_dev[t*y_stride_t + r*y_stride_r] — so the reference's [k, n]-input / [m, n]-output convention
+ * is strides (1, n_ref) / (1, n_ref) and gemm_q4's [m, k] / [m, n] is (k, 1) / (n, 1).
+ * `row_scales` (NULL, 1 or n entries on the device) multiplies row r's result like gemm_q4's
+ * `scales`.  f32 accumulation; result within 2e-3 of the reference's sequential f32 sum. */
+#define GLLMK_GEMV_MAX_M 16
+GLLMK_API int32_t gllmk_gemv(gllmk_ctx ctx, gllmk_weight w, const float *x_dev, int64_t x_stride_t, int64_t x_stride_k,
+                   int32_t m, float *y_dev, int64_t y_stride_t, int64_t y_stride_r, const float *row_scales,
+                   int64_t n_row_scales, void *stream);
+
+/* ---- host-pointer drop-ins of the reference operator API ----------------------------------- */
+
+/* Kernels::kquant_matmul(weight_blocks, input, output, QuantType::Q4K, m, n, k) and
+ * Kernels::classic_matmul(.., QuantType::Q8_0, ..) with E = f32 (src/traits.rs:543-563; CPU
+ * implementation src/cpu_kernels/mod.rs:3226-3394).  All three pointers are HOST memory, exactly
+ * as the reference takes slices: m weight rows, n batch columns, input [k, n], output [m, n].
+ * Uploads and repacks the weight on every call; callers that reuse a weight should hold a
+ * gllmk_weight and call gllmk_matmul_host.  UNSUPPORTED for a type of the other family
+ * (the reference panics there, src/cpu_kernels/mod.rs:3335-3352). */
+GLLMK_API int32_t gllmk_kquant_matmul_f32(gllmk_ctx ctx, const uint8_t *weight_blocks, const float *input, float *output,
+                                int32_t quant_type, size_t m, size_t n, size_t k);
+GLLMK_API int32_t gllmk_classic_matmul_f32(gllmk_ctx ctx, const uint8_t *weight_blocks, const float *input, float *output,
+                                 int32_t quant_type, size_t m, size_t n, size_t k);
+/* Kernels::gemm_q4 with E = f32 (src/traits.rs:511-520; src/cpu_kernels/mod.rs:2934-2981):
+ * m batch rows, n output features, Q4_K rows of k/256 blocks, input [m, k], output [m, n],
+ * scales: n_scales == n per channel, == 1 per tensor, else none.  INVALID_ARG if k % 256 != 0
+ * (the reference asserts). */
+GLLMK_API int32_t gllmk_gemm_q4_f32(gllmk_ctx ctx, const uint8_t *weight, const float *input, float *output,
+                          const float *scales, size_t n_scales, size_t m, size_t n, size_t k);
+/* The same two conventions against a resident weight; x / y are HOST memory.
+ * `ref_layout` != 0: kquant_matmul's input [k, m] / output [n, m]; 0: gemm_q4's [m, k] / [m, n]. */
+GLLMK_API int32_t gllmk_matmul_host(gllmk_ctx ctx, gllmk_weight w, const float *x_host, int32_t m, float *y_host,
+                          int32_t ref_layout);
+/* Kernels::dequant_q4_k(block, out) / dequant_q8_0 (src/traits.rs:476,488): `nblocks` consecutive
+ * blocks -> nblocks*block_size f32, host pointers. */
+GLLMK_API int32_t gllmk_dequant_q4_k(gllmk_ctx ctx, const uint8_t *blocks, float *out, size_t nblocks);
+GLLMK_API int32_t gllmk_dequant_q8_0(gllmk_ctx ctx, const uint8_t *blocks, float *out, size_t nblocks);
+/* quant_mxfp4::dequant_mxfp4(blocks, scales, output, block_size) (src/quant_mxfp4.rs:267-292):
+ * any even block_size; host pointers; INVALID_ARG where the reference returns Err / asserts. */
+GLLMK_API int32_t gllmk_dequant_mxfp4(gllmk_ctx ctx, const uint8_t *blocks, const uint8_t *scales, float *out,
+                            size_t num_blocks, size_t block_size);
+/* NVFP4 decode of `nblocks` 36-byte blocks, formula of src/quant.rs:77-86 (host pointers). */
+GLLMK_API int32_t gllmk_dequant_nvfp4(gllmk_ctx ctx, const uint8_t *blocks, float global_scale, float *out, size_t nblocks);
+
+/* ---- on-device quantizers ------------------------------------------------------------------ */
+
+/* f32 [rows, k] (device) -> reference-format blocks (device).  The reference has no encoder for
+ * these formats (its only quantizer is per-tensor amax/127, src/compiler/quant_convert.rs:17-31);
+ * these are this library's own, used for NVFP4 activations and to make synthetic weights.
+ * MXFP4 writes the split form (blocks + scales).  NVFP4: *global_scale > 0 is used as given,
+ * otherwise amax/(6*448) of the whole input is computed, used and written back. */
+GLLMK_API int32_t gllmk_quantize(gllmk_ctx ctx, int32_t quant_type, const float *x_dev, int64_t rows, int64_t k,
+                       int32_t mx_block, void *blocks_dev, void *scales_dev, float *global_scale, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GLLMK_H */

@@ -1,0 +1,336 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU oracle.  Needs a B200.
+
+Bars: repack round trip, decoded weights, quantizer bytes — bit-exact.  GEMV outputs —
+max_i |y_i - ref_i| / max(|ref_i|, rms(ref)) <= 2e-3 against the oracle's sequential f32 sum.
+"""
+import json
+import os
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+TOL = 2e-3
+HERE = os.path.dirname(os.path.abspath(__file__))
+with open(os.path.join(HERE, "golden", "reference_known_answers.json")) as f:
+    KA = json.load(f)
+
+
+@pytest.fixture(scope="module")
+def K(gk):
+    k = gk.GpuKernels(0)
+    yield k
+    k.close()
+
+
+@pytest.fixture(scope="module")
+def torch():
+    import torch as t
+    assert t.cuda.is_available()
+    return t
+
+
+def same_bits(a, b):
+    a = np.ascontiguousarray(a, np.float32).reshape(-1)
+    b = np.ascontiguousarray(b, np.float32).reshape(-1)
+    nan = np.isnan(a) & np.isnan(b)
+    return bool(((a.view(np.uint32) == b.view(np.uint32)) | nan).all())
+
+
+def make(oracle, fmt, n, k, seed, random_bytes=False):
+    """Returns (quant_type_name, oracle id, blocks, scales, global)."""
+    rng = np.random.default_rng(seed)
+    W = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    if fmt == "q4k":
+        b = oracle.quantize_q4_k(W)
+        if random_bytes:
+            b = rng.integers(0, 256, b.size, dtype=np.uint8)
+            v = b.reshape(-1, 144)
+            v[:, 0:4] = np.frombuffer(rng.uniform(-0.05, 0.05, 2 * v.shape[0]).astype(np.float16).tobytes(),
+                                      np.uint8).reshape(-1, 4)
+        return oracle.Q4K, b, None, 1.0
+    if fmt == "q8_0":
+        b = oracle.quantize_q8_0(W)
+        if random_bytes:
+            b = rng.integers(0, 256, b.size, dtype=np.uint8)
+            v = b.reshape(-1, 34)
+            v[:, 0:2] = np.frombuffer(rng.uniform(-0.05, 0.05, v.shape[0]).astype(np.float16).tobytes(),
+                                      np.uint8).reshape(-1, 2)
+        return oracle.Q8_0, b, None, 1.0
+    if fmt == "mxfp4":
+        b, s = oracle.quantize_mxfp4(W)
+        if random_bytes:
+            b = rng.integers(0, 256, b.size, dtype=np.uint8)
+            s = rng.integers(0, 256, s.size, dtype=np.uint8)  # includes 0 (2^-127) and 255 (NaN)
+        return oracle.MXFP4, b, s, 1.0
+    b, g = oracle.quantize_nvfp4(W)
+    if random_bytes:
+        b = rng.integers(0, 256, b.size, dtype=np.uint8)
+        g = 0.37
+    return oracle.NVFP4, b, None, g
+
+
+def qt_of(gk, fmt):
+    return {"q4k": gk.QuantType.q4k(), "q8_0": gk.QuantType.q8_0(), "mxfp4": gk.QuantType.mxfp4(32),
+            "nvfp4": gk.QuantType.nvfp4()}[fmt]
+
+
+# ---- repack / decode -------------------------------------------------------------------------
+@pytest.mark.parametrize("fmt,n,k", [("q4k", 16, 256), ("q4k", 100, 1024), ("q4k", 1, 256), ("q8_0", 16, 32),
+                                     ("q8_0", 37, 416), ("q8_0", 5, 2048), ("mxfp4", 128, 128), ("mxfp4", 70, 640),
+                                     ("nvfp4", 128, 64), ("nvfp4", 200, 448)])
+@pytest.mark.parametrize("random_bytes", [False, True])
+def test_repack_roundtrip_and_decode_bit_exact(gk, K, oracle, fmt, n, k, random_bytes):
+    oid, blocks, scales, g = make(oracle, fmt, n, k, seed=n * 7 + k, random_bytes=random_bytes)
+    w = K.upload(qt_of(gk, fmt), n, k, blocks, scales, g)
+    info = w.info()
+    assert info["n"] == n and info["k"] == k and info["dev_bytes"] >= info["ref_bytes"] - n * (k // 32)
+    back = K.unpack(w)
+    if fmt == "mxfp4":
+        assert np.array_equal(back[0], blocks) and np.array_equal(back[1], scales)
+    else:
+        assert np.array_equal(back, blocks)
+    dec = K.dequant(w).cpu().numpy()
+    ref = oracle.dequant_matrix(oid, blocks, n, k, scales=scales, global_scale=g)
+    assert same_bits(dec, ref)
+    w.free()
+
+
+def test_mxfp4_inline_form_upload(gk, K, oracle):
+    n, k = 130, 256
+    _, blocks, scales, _ = make(oracle, "mxfp4", n, k, seed=4, random_bytes=True)
+    inline = np.concatenate([scales.reshape(-1, 1), blocks.reshape(-1, 16)], axis=1).reshape(-1)
+    w = K.upload(gk.QuantType.mxfp4(32), n, k, inline, None)
+    b2, s2 = K.unpack(w)
+    assert np.array_equal(b2, blocks) and np.array_equal(s2, scales)
+    w.free()
+
+
+def test_upload_from_device_memory(gk, K, oracle, torch):
+    oid, blocks, _, _ = make(oracle, "q4k", 48, 512, seed=11)
+    dev = torch.from_numpy(blocks).cuda()
+    w = K.upload(gk.QuantType.q4k(), 48, 512, dev)
+    assert np.array_equal(K.unpack(w), blocks)
+    w.free()
+
+
+def test_host_dropin_decoders_on_reference_known_answers(gk, K):
+    c = KA["q4k_decode_basic"]
+    out = np.zeros(256, np.float32)
+    K.dequant_q4_k(np.array(c["block"], np.uint8), out)
+    for i, v in c["expect"].items():
+        assert out[int(i)] == v
+    c = KA["q4k_decode_all_subblocks"]
+    K.dequant_q4_k(np.array(c["block"], np.uint8), out)
+    assert out.tolist() == c["expect_all"]
+    out = np.zeros(32, np.float32)
+    c = KA["q8_0_decode_basic"]
+    K.dequant_q8_0(np.array(c["block"], np.uint8), out)
+    for i, v in c["expect"].items():
+        assert out[int(i)] == v
+    c = KA["q8_0_decode_extreme"]
+    K.dequant_q8_0(np.array(c["block"], np.uint8), out)
+    assert out.tolist() == c["expect_all"]
+    for name, c in KA["mxfp4"].items():
+        exp_n = len(c["scales"]) * c["block_size"]
+        out = np.zeros(exp_n, np.float32)
+        K.dequant_mxfp4(np.array(c["blocks"], np.uint8), np.array(c["scales"], np.uint8), out, c["block_size"])
+        if c.get("expect_all_nan"):
+            assert np.isnan(out).all(), name
+        else:
+            assert same_bits(out, np.array(c["expect"], np.float32)), name
+    with pytest.raises(gk.GllmkError):  # the reference returns Err on inconsistent lengths
+        K.dequant_mxfp4(np.zeros(15, np.uint8), np.zeros(1, np.uint8), np.zeros(32, np.float32), 32)
+
+
+def test_host_dropin_nvfp4_decode(gk, K, oracle):
+    rng = np.random.default_rng(2)
+    blocks = rng.integers(0, 256, 36 * 9, dtype=np.uint8)
+    out = np.zeros(64 * 9, np.float32)
+    K.dequant_nvfp4(blocks, 0.25, out)
+    assert same_bits(out, oracle.dequant_nvfp4(blocks, 0.25))
+
+
+# ---- quantizers ------------------------------------------------------------------------------
+@pytest.mark.parametrize("fmt", ["q4k", "q8_0", "mxfp4", "nvfp4"])
+def test_device_quantizers_match_oracle_bytes(gk, K, oracle, torch, fmt):
+    rng = np.random.default_rng(21)
+    n, k = 64, 1024
+    W = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    W[3] = 0.0                      # all-zero blocks
+    W[5, :256] = 0.013              # constant block
+    W[7] *= 1e-6                    # tiny values
+    W[9, 17] = 3.0                  # outlier
+    Wd = torch.from_numpy(W).cuda()
+    res = K.quantize(qt_of(gk, fmt), Wd)
+    if fmt == "q4k":
+        assert np.array_equal(res.cpu().numpy(), oracle.quantize_q4_k(W))
+    elif fmt == "q8_0":
+        assert np.array_equal(res.cpu().numpy(), oracle.quantize_q8_0(W))
+    elif fmt == "mxfp4":
+        b, s = oracle.quantize_mxfp4(W)
+        assert np.array_equal(res[0].cpu().numpy(), b) and np.array_equal(res[1].cpu().numpy(), s)
+    else:
+        b, g = oracle.quantize_nvfp4(W)
+        assert res[1] == pytest.approx(g, rel=0, abs=0)
+        assert np.array_equal(res[0].cpu().numpy(), b)
+
+
+# ---- GEMV ------------------------------------------------------------------------------------
+def gemv_case(gk, K, oracle, torch, fmt, n, k, m, seed, ref_layout=False, ksplit=0, row_scales=None):
+    oid, blocks, _, _ = make(oracle, fmt, n, k, seed)
+    rng = np.random.default_rng(seed + 1)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    w = K.upload(qt_of(gk, fmt), n, k, blocks)
+    K.set("gemv_ksplit", ksplit)
+    xin = torch.from_numpy(np.ascontiguousarray(x.T) if ref_layout else x).cuda()
+    rs = None if row_scales is None else torch.from_numpy(row_scales).cuda()
+    y = K.gemv(w, xin, ref_layout=ref_layout, row_scales=rs).cpu().numpy()
+    K.set("gemv_ksplit", 0)
+    ref = oracle.quant_matmul(blocks, np.ascontiguousarray(x.T), oid, n, m, k, threads=8)  # [n, m]
+    if row_scales is not None:
+        ref = ref * (row_scales.reshape(-1, 1) if row_scales.size > 1 else row_scales[0])
+    if not ref_layout:
+        ref = ref.T
+    assert y.shape == ref.shape
+    err = oracle.rel_err(y, ref)
+    w.free()
+    return err
+
+
+def test_gemv_q4k_config1_shape(gk, K, oracle, torch):
+    """BASELINE config 1: W[4096,4096] Q4_K, x[1,4096]."""
+    assert gemv_case(gk, K, oracle, torch, "q4k", 4096, 4096, 1, seed=20240) <= TOL
+
+
+@pytest.mark.parametrize("m", [1, 4, 8, 16])
+def test_gemv_q8_0_config2_shape(gk, K, oracle, torch, m):
+    """BASELINE config 2: W[11008,4096] Q8_0, x[M,4096], M in {1,4,8,16}."""
+    assert gemv_case(gk, K, oracle, torch, "q8_0", 11008, 4096, m, seed=20241) <= TOL
+
+
+@pytest.mark.parametrize("fmt,n,k,m", [("q4k", 1, 256, 1), ("q4k", 17, 512, 3), ("q4k", 100, 1280, 16),
+                                       ("q4k", 333, 2048, 5), ("q8_0", 1, 32, 1), ("q8_0", 50, 96, 2),
+                                       ("q8_0", 129, 4000, 16), ("q8_0", 16, 288, 9)])
+@pytest.mark.parametrize("ref_layout", [False, True])
+def test_gemv_ragged_shapes_both_layouts(gk, K, oracle, torch, fmt, n, k, m, ref_layout):
+    assert gemv_case(gk, K, oracle, torch, fmt, n, k, m, seed=n + k + m, ref_layout=ref_layout) <= TOL
+
+
+@pytest.mark.parametrize("ksplit", [1, 2, 4, 8])
+@pytest.mark.parametrize("fmt", ["q4k", "q8_0"])
+def test_gemv_every_ksplit(gk, K, oracle, torch, fmt, ksplit):
+    assert gemv_case(gk, K, oracle, torch, fmt, 272, 2048, 7, seed=77, ksplit=ksplit) <= TOL
+
+
+def test_gemv_row_scales(gk, K, oracle, torch):
+    rs = np.random.default_rng(1).uniform(0.5, 2.0, 96).astype(np.float32)
+    assert gemv_case(gk, K, oracle, torch, "q4k", 96, 512, 2, seed=5, row_scales=rs) <= TOL
+    assert gemv_case(gk, K, oracle, torch, "q4k", 96, 512, 2, seed=5, row_scales=np.array([3.0], np.float32)) <= TOL
+
+
+def test_gemv_is_deterministic_and_rejects_bad_m(gk, K, oracle, torch):
+    oid, blocks, _, _ = make(oracle, "q4k", 256, 1024, 3)
+    w = K.upload(gk.QuantType.q4k(), 256, 1024, blocks)
+    x = torch.randn(4, 1024, device="cuda")
+    a = K.gemv(w, x).clone()
+    b = K.gemv(w, x)
+    assert torch.equal(a, b)
+    with pytest.raises(gk.GllmkError) as e:
+        K.gemv(w, torch.randn(17, 1024, device="cuda"))
+    assert e.value.status == gk.Status.INVALID_ARG
+    w.free()
+
+
+def test_gemv_scale_extremes_zero_and_nan(gk, K, oracle, torch):
+    """Tokens of very different magnitude, an all-zero token, and a NaN that must reach every output."""
+    n, k = 64, 512
+    oid, blocks, _, _ = make(oracle, "q4k", n, k, 8)
+    rng = np.random.default_rng(8)
+    x = rng.standard_normal((4, k)).astype(np.float32)
+    x[0] *= 1e-20
+    x[1] *= 1e15
+    x[2] = 0.0
+    w = K.upload(gk.QuantType.q4k(), n, k, blocks)
+    y = K.gemv(w, torch.from_numpy(x).cuda()).cpu().numpy()
+    ref = oracle.quant_matmul(blocks, np.ascontiguousarray(x.T), oid, n, 4, k).T
+    for t in (0, 1, 3):
+        assert oracle.rel_err(y[t], ref[t]) <= TOL
+    assert not y[2].any()
+    x[3, 100] = np.nan
+    y = K.gemv(w, torch.from_numpy(x).cuda()).cpu().numpy()
+    assert np.isnan(y[3]).all() and not np.isnan(y[:3]).any()
+    w.free()
+
+
+def test_gemv_linearity_at_config5_size(gk, K, oracle, torch):
+    """70B-shaped gate/up matrix W[28672, 8192] Q4_K quantized on the device: a sample of rows against the
+    oracle, and linearity y(a*x1 + x2) = a*y(x1) + y(x2) over the whole output."""
+    n, k = 28672, 8192
+    g = torch.Generator(device="cuda").manual_seed(20244)
+    W = torch.randn((n, k), generator=g, device="cuda") * 0.02
+    qt = gk.QuantType.q4k()
+    blocks = K.quantize(qt, W)
+    del W
+    w = K.upload(qt, n, k, blocks)
+    x = torch.randn((2, k), generator=g, device="cuda")
+    y = K.gemv(w, x)
+    xc = (2.0 * x[0] + x[1]).reshape(1, k)
+    yc = K.gemv(w, xc)
+    lin = (2.0 * y[0] + y[1] - yc[0]).abs().max().item() / yc.abs().max().item()
+    assert lin < 1e-5
+    rows = np.r_[0:16, 14000:14016, n - 16:n]
+    hb = blocks.reshape(n, -1)[torch.from_numpy(rows).cuda()].cpu().numpy().reshape(-1)
+    ref = oracle.quant_matmul(hb, np.ascontiguousarray(x.cpu().numpy().T), oracle.Q4K, rows.size, 2, k).T
+    assert oracle.rel_err(y.cpu().numpy()[:, rows], ref) <= TOL
+    w.free()
+
+
+# ---- host-pointer drop-ins of the reference operator API --------------------------------------
+def test_reference_known_answers_through_the_dropins(gk, K):
+    c = KA["gemm_q4_basic"]
+    out = np.zeros(c["m"] * c["n"], np.float32)
+    K.gemm_q4(np.array(c["weight"], np.uint8), np.array(c["input"], np.float32), out, c["scales"], c["m"], c["n"], c["k"])
+    assert out.tolist() == c["expect"]
+    c = KA["gemm_q4_per_channel"]
+    out = np.zeros(c["m"] * c["n"], np.float32)
+    K.gemm_q4(np.array(c["weight"], np.uint8), np.array(c["input"], np.float32), out, c["scales"], c["m"], c["n"], c["k"])
+    assert out.tolist() == c["expect"]
+    c = KA["q8_0_dot"]
+    out = np.zeros(1, np.float32)
+    K.classic_matmul(np.array(c["weight"], np.uint8), np.array(c["input"], np.float32), out, gk.QuantType.q8_0(),
+                     c["m"], c["n"], c["k"])
+    assert abs(out[0] - c["expect"][0]) < 1e-2  # the reference's own tolerance (src/tests_quant.rs:672-676)
+
+
+def test_kquant_and_classic_matmul_dropins(gk, K, oracle):
+    rng = np.random.default_rng(31)
+    for fmt, fn, qt in (("q4k", K.kquant_matmul, gk.QuantType.q4k()), ("q8_0", K.classic_matmul, gk.QuantType.q8_0())):
+        m, n, k = 200, 21, 1024  # reference naming: m weight rows, n batch columns (> 16: chunked internally)
+        oid, blocks, _, _ = make(oracle, fmt, m, k, 31)
+        x = rng.standard_normal((k, n)).astype(np.float32)
+        out = np.zeros((m, n), np.float32)
+        fn(blocks, x, out, qt, m, n, k)
+        ref = oracle.quant_matmul(blocks, x, oid, m, n, k)
+        assert oracle.rel_err(out, ref) <= TOL
+    # wrong family: the reference panics (unimplemented!), the C ABI returns Unsupported
+    with pytest.raises(gk.GllmkError) as e:
+        K.kquant_matmul(blocks, x, out, gk.QuantType.q8_0(), m, n, k)
+    assert e.value.status == gk.Status.UNSUPPORTED
+    with pytest.raises(gk.GllmkError) as e:
+        K.gemm_q4(np.zeros(144, np.uint8), np.zeros(100, np.float32), np.zeros(1, np.float32), None, 1, 1, 100)
+    assert e.value.status == gk.Status.INVALID_ARG  # k % 256 != 0: the reference asserts
+
+
+def test_matmul_host_resident_weight(gk, K, oracle):
+    oid, blocks, _, _ = make(oracle, "q4k", 512, 1024, 41)
+    w = K.upload(gk.QuantType.q4k(), 512, 1024, blocks)
+    x = np.random.default_rng(41).standard_normal((3, 1024)).astype(np.float32)
+    y = K.matmul_host(w, x)
+    ref = oracle.gemm_q4(blocks, x, None, 3, 512, 1024)
+    assert oracle.rel_err(y, ref) <= TOL
+    y2 = K.matmul_host(w, np.ascontiguousarray(x.T), ref_layout=True)
+    assert oracle.rel_err(y2, ref.T) <= TOL
+    assert K.gemv_q4(blocks[:4 * 144], x[0], 2.0, 1024) == pytest.approx(2.0 * ref[0, 0], rel=2e-3, abs=1e-6)
+    w.free()
