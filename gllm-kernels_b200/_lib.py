@@ -50,6 +50,7 @@ _SIGS = {
     "gllmk_ctx_free": (None, [_vp]),
     "gllmk_last_error": (C.c_char_p, [_vp]),
     "gllmk_ctx_set": (_i32, [_vp, C.c_char_p, _i64]),
+    "gllmk_ctx_status": (_i32, [_vp, C.POINTER(_i32)]),
     "gllmk_weight_upload": (_i32, [_vp, _i32, _i64, _i64, _i32, _vp, _vp, _f32, _i32, C.POINTER(_vp)]),
     "gllmk_weight_free": (None, [_vp]),
     "gllmk_weight_info": (_i32, [_vp, C.POINTER(_i32), C.POINTER(_i64), C.POINTER(_i64), C.POINTER(_u64),

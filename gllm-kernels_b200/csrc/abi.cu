@@ -39,6 +39,13 @@ static int32_t grow(Ctx *c, void **p, size_t *have, size_t want, bool pinned) {
     return GLLMK_STATUS_OK;
 }
 int32_t ensure_ws(Ctx *c, size_t bytes) { return grow(c, &c->ws, &c->ws_bytes, bytes, false); }
+int32_t ensure_red(Ctx *c, size_t bytes) {
+    if (c->red_bytes >= bytes) return GLLMK_STATUS_OK;
+    int32_t rc = grow(c, &c->red, &c->red_bytes, bytes, false);
+    if (rc) return rc;
+    GK_CUDA(c, cudaMemset(c->red, 0, c->red_bytes));  // arrival counters start at zero and reset themselves
+    return GLLMK_STATUS_OK;
+}
 int32_t ensure_pin(Ctx *c, size_t bytes) { return grow(c, &c->pin, &c->pin_bytes, bytes, true); }
 int32_t ensure_dev_io(Ctx *c, size_t bytes) { return grow(c, &c->dev_io, &c->dev_io_bytes, bytes, false); }
 
@@ -95,21 +102,21 @@ static int32_t weight_alloc(Ctx *c, int32_t qt, int64_t n, int64_t k, int32_t mx
     w->device = c->device;
     w->ref_bytes = (uint64_t)n * (uint64_t)w->nb * (uint64_t)block_bytes_of(qt, mx_block);
     if (qt == GLLMK_QUANT_Q4K) {
-        w->n_pad = (n + 15) / 16 * 16;
-        w->qs_bytes = (size_t)w->n_pad * w->nb * 128;
-        w->aux_bytes = (size_t)w->n_pad * w->nb * 16;
+        w->n_pad = (n + 127) / 128 * 128;
+        w->qs_bytes = (size_t)(w->n_pad / 16) * w->nb * Q4K_CHUNK;
+        w->aux_bytes = 0;
     } else if (qt == GLLMK_QUANT_Q8_0) {
-        w->n_pad = (n + 15) / 16 * 16;
+        w->n_pad = (n + 127) / 128 * 128;
         w->nb8 = (w->nb + 7) / 8;
-        w->qs_bytes = (size_t)w->n_pad * w->nb * 32;
-        w->aux_bytes = (size_t)w->n_pad * w->nb8 * 16;
+        w->qs_bytes = (size_t)(w->n_pad / 16) * w->nb8 * Q80_CHUNK;
+        w->aux_bytes = 0;
     } else {
         w->n_pad = (n + 127) / 128 * 128;
         w->qs_bytes = (size_t)w->n_pad * (k / 2);
         w->aux_bytes = (size_t)w->n_pad * (k / (qt == GLLMK_QUANT_NVFP4 ? 16 : 32));
     }
     cudaError_t e = cudaMalloc(&w->qs, w->qs_bytes);
-    if (e == cudaSuccess) e = cudaMalloc(&w->aux, w->aux_bytes);
+    if (e == cudaSuccess && w->aux_bytes) e = cudaMalloc(&w->aux, w->aux_bytes);
     if (e != cudaSuccess) {
         if (w->qs) cudaFree(w->qs);
         delete w;
@@ -198,7 +205,11 @@ int32_t gllmk_ctx_create(int32_t device, gllmk_ctx *out) {
     if (!c) return GLLMK_STATUS_OUT_OF_MEMORY;
     c->device = device;
     c->sm_count = prop.multiProcessorCount;
-    if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess) {
+    if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaMalloc(reinterpret_cast<void **>(&c->status_dev), 16384) != cudaSuccess ||
+        cudaMemset(c->status_dev, 0, 16384) != cudaSuccess) {
+        (void)cudaGetLastError();
+        if (c->stream) cudaStreamDestroy(c->stream);
         delete c;
         return GLLMK_STATUS_RUNTIME_ERROR;
     }
@@ -212,6 +223,8 @@ void gllmk_ctx_free(gllmk_ctx ctx) {
     DeviceGuard g(c->device);
     cudaDeviceSynchronize();
     if (c->ws) cudaFree(c->ws);
+    if (c->red) cudaFree(c->red);
+    if (c->status_dev) cudaFree(c->status_dev);
     if (c->dev_io) cudaFree(c->dev_io);
     if (c->pin) cudaFreeHost(c->pin);
     if (c->stream) cudaStreamDestroy(c->stream);
@@ -223,10 +236,25 @@ const char *gllmk_last_error(gllmk_ctx ctx) {
     return static_cast<Ctx *>(ctx)->err.c_str();
 }
 
+int32_t gllmk_ctx_status(gllmk_ctx ctx, int32_t *device_status) {
+    if (!ctx || !device_status) return GLLMK_STATUS_INVALID_ARG;
+    Ctx *c = static_cast<Ctx *>(ctx);
+    DeviceGuard g(c->device);
+    GK_CUDA(c, cudaDeviceSynchronize());
+    int v = 0;
+    GK_CUDA(c, cudaMemcpy(&v, c->status_dev, sizeof(int), cudaMemcpyDeviceToHost));
+    *device_status = v;
+    if (v) {
+        GK_CUDA(c, cudaMemset(c->status_dev, 0, sizeof(int)));
+        return fail(c, GLLMK_STATUS_RUNTIME_ERROR, "a kernel gave up a bounded wait (status word %d)", v);
+    }
+    return GLLMK_STATUS_OK;
+}
+
 int32_t gllmk_ctx_set(gllmk_ctx ctx, const char *key, int64_t value) {
     if (!ctx || !key) return GLLMK_STATUS_INVALID_ARG;
     Ctx *c = static_cast<Ctx *>(ctx);
-    if (!strcmp(key, "gemv_ksplit")) c->gemv_ksplit = value;
+    if (!strcmp(key, "gemv_ctas_per_sm")) c->gemv_ctas_per_sm = value;
     else if (!strcmp(key, "gemv_pdl")) c->gemv_pdl = value;
     else return fail(c, GLLMK_STATUS_INVALID_ARG, "unknown key %s", key);
     return GLLMK_STATUS_OK;

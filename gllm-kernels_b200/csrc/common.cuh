@@ -14,18 +14,32 @@
 
 namespace gllmk {
 
+constexpr int Q4K_CHUNK = 2368;
+constexpr int Q80_CHUNK = 4352;
+// chunk order of the Q4_K plane: [tile group TG = T / 8][k-block b][tile in group T % 8]
+__host__ __device__ inline size_t q4k_chunk_index(int64_t T, int64_t b, int64_t nb) {
+    return ((size_t)(T >> 3) * (size_t)nb + (size_t)b) * 8 + (size_t)(T & 7);
+}
+
 // ---- device layouts -------------------------------------------------------------------------
 //
-// Q4_K (256 el / 144 B), rows padded to a multiple of 16, T = row / 16, b = k-block:
-//   qs  : uint4 [T][b][j = 0..3][lane = 0..31]   (2048 B per (T, b), one warp-wide 512 B run per j)
-//         lane = 4*g + t holds, for row 16T + g + 8*(j >> 1), the 16 bytes qs[16*(2t + (j & 1)) ..]
-//         i.e. thread t of quad g owns sub-block pair (2t, 2t+1) of rows g and g+8 — the
-//         m16n8k16 A-fragment ownership, so unpacked nibbles land in fragment registers.
-//   hdr : uint4 [T][b][16 rows]                  (d, dmin, scales[12] exactly as in the block)
+// Q4_K (256 el / 144 B), rows padded to a multiple of 128, T = row / 16, b = k-block.  One plane of
+// 2368-byte chunks in the order [T / 8][b][T % 8]: the eight 16-row tiles a CTA works on side by side
+// sit next to each other for one k-block ("super-chunk"), and a CTA's whole stream is one contiguous
+// byte range.  Inside a chunk, with lane = 4*g + t of a warp:
+//   [0, 2048)    uint4 [p = 0..3][lane] = {W(g,p,2t), W(g,p,2t+1), W(g+8,p,2t), W(g+8,p,2t+1)}, W(r,p,i) the
+//                i-th 32-bit word of the 32-byte group p of row 16T+r's qs: masking a word with
+//                0x0F0F0F0F (after a shift by 4 for the odd sub-block) IS an A-fragment register of
+//                mma.m16n8k32.u8 for sub-block 2p (2p+1), k-slot 4t+j <-> element 8t+j of the sub-block
+//   [2048, 2304) uint4 [row 0..15] = bytes {sc_0..sc_7, m_0..m_7}: the 6-bit scales and mins unpacked to
+//                bytes (re-packed bit-exactly on the way out)
+//   [2304, 2368) uint32 [g][h]: d | dmin << 16 (f16 bits) of row 16T + g + 8h
 //
-// Q8_0 (32 el / 34 B), rows padded to 16, blocks padded to a multiple of 8 (nb8 groups):
-//   qs  : uint4 [T][b][lane]                     lane = 4g+t: {row g bytes 8t..8t+7, row g+8 bytes 8t..8t+7}
-//   d   : half  [T][b8][16 rows][8 blocks]       (f16 scale bits, 0 for padding)
+// Q8_0 (32 el / 34 B), rows padded to 128, blocks padded to groups of 8 (nb8 per row).  One plane of
+// 4352-byte chunks in the order [T / 8][b8][T % 8]:
+//   [0, 4096)    uint4 [block 0..7][lane] = {row g bytes 8t..8t+7, row g+8 bytes 8t..8t+7}: the four words
+//                are the A-fragment registers a0, a2, a1, a3 of mma.m16n8k32.s8 for that block
+//   [4096, 4352) half  [row 0..15][block 0..7]  f16 scale bits (0 for padding blocks)
 //
 // MXFP4 (block 32) and NVFP4 (block 64 = 4 x 16), rows padded to 128, k % 256 == 0:
 //   data: uint8 [n_pad][k / 2]                   nibbles as in the reference (low nibble = even element),
@@ -57,19 +71,25 @@ struct Ctx {
     // activation staging workspace (global scratch written by the staging kernel, read by the GEMV)
     void *ws = nullptr;
     size_t ws_bytes = 0;
+    int64_t ws_k = -1;  // K the workspace is currently laid out (and zero-padded) for
+    // split-k partial sums + per-tile arrival counters (zeroed at allocation, self-resetting) + status word
+    void *red = nullptr;
+    size_t red_bytes = 0;
+    int *status_dev = nullptr;
     // pinned host staging + device staging for the host-pointer entry points
     void *pin = nullptr;
     size_t pin_bytes = 0;
     void *dev_io = nullptr;
     size_t dev_io_bytes = 0;
     cudaStream_t stream = nullptr;  // the context's own stream for host-pointer entry points
-    int64_t gemv_ksplit = 0;
     int64_t gemv_pdl = 1;
+    int64_t gemv_ctas_per_sm = 0;  // 0 = what the occupancy calculator allows
 };
 
 int32_t fail(Ctx *c, int32_t code, const char *fmt, ...);
 int32_t cuda_fail(Ctx *c, cudaError_t e, const char *what);
 int32_t ensure_ws(Ctx *c, size_t bytes);
+int32_t ensure_red(Ctx *c, size_t bytes);
 int32_t ensure_pin(Ctx *c, size_t bytes);
 int32_t ensure_dev_io(Ctx *c, size_t bytes);
 

@@ -1,450 +1,502 @@
 // Decode path: fused dequantize + GEMV for M <= 16 tokens over the tiled Q4_K / Q8_0 layouts.
 //
-// The kernels are HBM-bound by design: each warp streams its 16-row tile of packed weights with
-// 128-bit coalesced loads (512 contiguous bytes per warp instruction), unpacks nibbles / bytes to
-// exact fp16 integers with one logic op + one half2 op per pair, and feeds them as the A operand
-// of mma.sync.m16n8k16 (f32 accumulate).  The activations are the B operand: each token is split
-// into an fp16 "hi" and a 2^11-scaled fp16 "lo" column (22 significant bits together) after a
-// per-token power-of-two normalisation, so products are exact and all rounding happens in the
-// f32 accumulators.  Using the tensor pipe for an M=1 product wastes MMA columns on purpose: what
-// it buys is issue slots — a scalar-FMA formulation needs ~3 issue slots per nibble, more than the
-// ~2.8 per nibble an SM has at full HBM rate.
+// The kernels are HBM-bound by design and built around the instruction budget that leaves: at full
+// HBM rate an SM has fewer than three issue slots per weight nibble.  So
+//   * the packed integers are never converted: a 32-bit word of Q4_K nibbles masked with 0x0F0F0F0F (a
+//     Q8_0 word as it is) IS an A-fragment register of mma.sync.m16n8k32 (u8/s8 x s8 -> s32);
+//   * activations are the B operand as two int8 "digit" columns per token: per 256-element block
+//     x = amax/127 * (d1 + d2/254) with |d1|, |d2| <= 127 (error <= amax * 1.6e-5), written once per
+//     call by a small staging kernel, so every product is an exact integer;
+//   * Q4_K's 6-bit sub-block scales multiply the s32 sub-block sums (one IMAD each) and only the per-block
+//     totals are converted to f32 and multiplied by d, dmin and the activation scale.
+// Weights stream through shared memory with bulk copies (cp.async.bulk + mbarrier), one 18.9 KB / 34.8 KB
+// "super-chunk" (8 row tiles x one k-block) per stage, so the copy engine, not the warps, keeps HBM busy.
 //
 // Q4_K algebra per 256-block and row (reference: k_quant.rs:502-547, sum of (d*sc*q - dmin*m)*x):
 //     y += d * sum_sub sc_sub * (q . x)_sub  -  dmin * sum_sub m_sub * (sum x)_sub
-// sc*q <= 945 and m <= 63 are exact in fp16; the per-sub-block sums of x are precomputed by the
-// staging kernel and enter through one extra MMA per block.
+// Q8_0 per 32-block and row (classic.rs:870-881):  y += d * (q . x)
 #include "common.cuh"
 
 namespace gllmk {
 
+constexpr int FMT_Q4K = 0, FMT_Q80 = 1;
+
 // ---------------------------------------------------------------------------------------------
-// Activation staging: x (f32, strided) -> workspace
-//   xs  : half [cols_pad][K]     column 2t = hi(token t), 2t+1 = lo(token t); for Q4_K each aligned
-//                                quad of k is stored in order (0,2,1,3) to match the nibble unpack
-//   ss  : half [cols_pad][K/32]  hi/lo split of the per-32 sums of the normalised token (Q4_K only)
-//   tsc : float[16]              2^e per token, undoes the normalisation
+// Activation image: one slice per 256 elements of k, the exact bytes a CTA copies into shared memory.
+//   [col < 2m][288 B] : int8 digits, column 2*tok = d1, 2*tok+1 = d2, natural k order (256 B used; the
+//                       288-byte pitch makes the B-fragment reads bank-conflict free)
+//   [col < 2m][16 B]  : per 32-element sub-block sums of the column's digits, S = 64*hi + lo:
+//                       bytes 0..7 = hi (s8), bytes 8..15 = lo (0..63)
+//   [tok < m] f32     : amax/127 of the token's block (NaN if the block holds a non-finite value),
+//                       padded to 16 bytes
 // ---------------------------------------------------------------------------------------------
+__host__ __device__ inline uint32_t slice_bytes(int m) { return (uint32_t)(2 * m) * 304u + 16u * (uint32_t)((m + 3) / 4); }
+
 struct StageParams {
     const float *x;
     int64_t xst, xsk;
     int m;
     int64_t K;
-    __half *xs;
-    __half *ss;
-    float *tsc;
-    int perm;  // 1: Q4_K quad permutation + sums
+    uint8_t *img;
 };
 
 __global__ void __launch_bounds__(256) stage_x_kernel(StageParams p) {
-    __shared__ float red[8];
+    __shared__ float wmax[8];
+    __shared__ int wbad[8];
     // Let the dependent GEMV grid start streaming weights now; it waits (griddepcontrol.wait) for
-    // this grid to finish before it touches the workspace.
+    // this grid to finish before it touches the image.
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
-    const int tok = blockIdx.y;
+    const int tok = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t k0 = ((int64_t)blockIdx.x * 256 + threadIdx.x) * 4;
     const float *xr = p.x + (int64_t)tok * p.xst;
-    // per-token amax (every CTA of the token recomputes it; K*4 bytes from L2)
-    float amax = 0.0f;
-    for (int64_t k = threadIdx.x; k < p.K; k += 256) amax = fmaxf(amax, fabsf(xr[k * p.xsk]));
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (k0 < p.K) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) v[i] = xr[(k0 + i) * p.xsk];
+    }
+    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+    const float inf = __int_as_float(0x7F800000);
+    int bad = !(fabsf(v[0]) < inf) || !(fabsf(v[1]) < inf) || !(fabsf(v[2]) < inf) || !(fabsf(v[3]) < inf);
 #pragma unroll
     for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    bad = __any_sync(0xffffffffu, bad);
+    if (lane == 0) { wmax[warp] = amax; wbad[warp] = bad; }
     __syncthreads();
-    amax = red[0];
-#pragma unroll
-    for (int i = 1; i < 8; i++) amax = fmaxf(amax, red[i]);
-    int e = 0;
-    if (amax > 0.0f && amax < __int_as_float(0x7F800000)) {
-        (void)frexpf(amax, &e);  // amax = f * 2^e, f in [0.5, 1)
-        e = max(-126, min(126, e));
-    }
-    const float inv = ldexpf(1.0f, -e);
-    if (blockIdx.x == 0 && threadIdx.x == 0) p.tsc[tok] = ldexpf(1.0f, e);
-    // NaN anywhere in the token must reach every output like in the reference (fmaxf drops NaNs,
-    // but the converted values themselves carry it into the MMA).
-    const int64_t k0 = ((int64_t)blockIdx.x * 256 + threadIdx.x) * 4;
-    float v[4] = {0.f, 0.f, 0.f, 0.f};
-    const bool live = k0 < p.K;
-    if (live) {
-#pragma unroll
-        for (int i = 0; i < 4; i++) v[i] = xr[(k0 + i) * p.xsk] * inv;
-    }
-    __half hi[4], lo[4];
+    amax = fmaxf(wmax[warp & ~1], wmax[warp | 1]);  // a 256-block is two warps
+    bad = wbad[warp & ~1] | wbad[warp | 1];
+    // tiny blocks are pre-scaled by 2^64 so that 127/amax stays finite
+    const float pre = amax < 1e-20f ? 18446744073709551616.0f : 1.0f;
+    const float inv = (amax > 0.0f && !bad) ? 127.0f / (amax * pre) : 0.0f;
+    int d1[4], d2[4];
 #pragma unroll
     for (int i = 0; i < 4; i++) {
-        hi[i] = __float2half_rn(v[i]);
-        lo[i] = __float2half_rn((v[i] - __half2float(hi[i])) * 2048.0f);
+        const float s = (v[i] * pre) * inv;
+        const float r1 = fminf(fmaxf(rintf(s), -127.0f), 127.0f);
+        const float r2 = fminf(fmaxf(rintf((s - r1) * 254.0f), -127.0f), 127.0f);
+        d1[i] = (int)r1;
+        d2[i] = (int)r2;
     }
-    if (live) {
-        __half *ph = p.xs + (int64_t)(2 * tok) * p.K + k0;
-        __half *pl = p.xs + (int64_t)(2 * tok + 1) * p.K + k0;
-        if (p.perm) {
-            *reinterpret_cast<uint2 *>(ph) = make_uint2(
-                (uint32_t)__half_as_ushort(hi[0]) | ((uint32_t)__half_as_ushort(hi[2]) << 16),
-                (uint32_t)__half_as_ushort(hi[1]) | ((uint32_t)__half_as_ushort(hi[3]) << 16));
-            *reinterpret_cast<uint2 *>(pl) = make_uint2(
-                (uint32_t)__half_as_ushort(lo[0]) | ((uint32_t)__half_as_ushort(lo[2]) << 16),
-                (uint32_t)__half_as_ushort(lo[1]) | ((uint32_t)__half_as_ushort(lo[3]) << 16));
-        } else {
-            *reinterpret_cast<uint2 *>(ph) = make_uint2(
-                (uint32_t)__half_as_ushort(hi[0]) | ((uint32_t)__half_as_ushort(hi[1]) << 16),
-                (uint32_t)__half_as_ushort(hi[2]) | ((uint32_t)__half_as_ushort(hi[3]) << 16));
-            *reinterpret_cast<uint2 *>(pl) = make_uint2(
-                (uint32_t)__half_as_ushort(lo[0]) | ((uint32_t)__half_as_ushort(lo[1]) << 16),
-                (uint32_t)__half_as_ushort(lo[2]) | ((uint32_t)__half_as_ushort(lo[3]) << 16));
-        }
+    const bool inr = k0 < (((p.K + 255) >> 8) << 8);  // inside the last (zero-padded) slice
+    uint8_t *slice = p.img + (k0 >> 8) * (int64_t)slice_bytes(p.m);
+    const int kk = (int)(k0 & 255), sub = kk >> 5;
+    const uint32_t w1 = (uint32_t)(d1[0] & 0xFF) | ((uint32_t)(d1[1] & 0xFF) << 8) | ((uint32_t)(d1[2] & 0xFF) << 16) |
+                        ((uint32_t)(d1[3] & 0xFF) << 24);
+    const uint32_t w2 = (uint32_t)(d2[0] & 0xFF) | ((uint32_t)(d2[1] & 0xFF) << 8) | ((uint32_t)(d2[2] & 0xFF) << 16) |
+                        ((uint32_t)(d2[3] & 0xFF) << 24);
+    // k beyond K inside the last slice is written as zero digits (v = 0 above)
+    if (inr) {
+        *reinterpret_cast<uint32_t *>(slice + (2 * tok) * 288 + kk) = w1;
+        *reinterpret_cast<uint32_t *>(slice + (2 * tok + 1) * 288 + kk) = w2;
     }
-    if (p.perm) {
-        float s = (v[0] + v[1]) + (v[2] + v[3]);
-        s += __shfl_xor_sync(0xffffffffu, s, 1);
-        s += __shfl_xor_sync(0xffffffffu, s, 2);
-        s += __shfl_xor_sync(0xffffffffu, s, 4);
-        if (live && (threadIdx.x & 7) == 0) {
-            const __half sh = __float2half_rn(s);
-            const __half sl = __float2half_rn((s - __half2float(sh)) * 2048.0f);
-            p.ss[(int64_t)(2 * tok) * (p.K >> 5) + (k0 >> 5)] = sh;
-            p.ss[(int64_t)(2 * tok + 1) * (p.K >> 5) + (k0 >> 5)] = sl;
-        }
+    int s1 = d1[0] + d1[1] + d1[2] + d1[3], s2 = d2[0] + d2[1] + d2[2] + d2[3];
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) {
+        s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+        s2 += __shfl_xor_sync(0xffffffffu, s2, o);
     }
+    if (inr && (lane & 7) == 0) {
+        uint8_t *sp = slice + (2 * p.m) * 288;
+        sp[(2 * tok) * 16 + sub] = (uint8_t)(int8_t)(s1 >> 6);
+        sp[(2 * tok) * 16 + 8 + sub] = (uint8_t)(s1 & 63);
+        sp[(2 * tok + 1) * 16 + sub] = (uint8_t)(int8_t)(s2 >> 6);
+        sp[(2 * tok + 1) * 16 + 8 + sub] = (uint8_t)(s2 & 63);
+    }
+    if (inr && (threadIdx.x & 63) == 0)
+        reinterpret_cast<float *>(slice + (2 * p.m) * 304)[tok] = bad ? __int_as_float(0x7FC00000) : amax / 127.0f;
 }
 
 // ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                         uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+// PTX helpers: integer tensor-core MMA, shared-memory loads, mbarrier + bulk copy (every wait bounded)
+// ---------------------------------------------------------------------------------------------
+template <bool A_SIGNED>
+__device__ __forceinline__ void imma16832(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                          uint32_t b1) {
+    if (A_SIGNED)
+        asm volatile(
+            "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+            : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+    else
+        asm volatile(
+            "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+            : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
-__device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
-__device__ __forceinline__ __half2 u32_as_h2(uint32_t u) { return *reinterpret_cast<__half2 *>(&u); }
-__device__ __forceinline__ uint4 ldg_stream(const uint4 *p) {
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
     uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p));
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
     return v;
 }
-// (w & mask) | 0x64006400: two fp16 values 1024 + field
-__device__ __forceinline__ uint32_t magic_and(uint32_t w, uint32_t mask) {
-    uint32_t r;
-    asm("lop3.b32 %0, %1, %2, %3, 0xEA;\n" : "=r"(r) : "r"(w), "r"(mask), "r"(0x64006400u));
-    return r;
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
 }
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Slow path, out of line: bounded spin (a copy lands in microseconds, the bound is on the order of a
+// second); false if the barrier never flipped.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity) {
+    for (uint32_t it = 0; it < (1u << 22); it++)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity);
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ uint32_t byte_of(uint32_t w, int i) { return __byte_perm(w, 0u, 0x4440u + (uint32_t)i); }
 
 struct GemvParams {
-    const uint4 *qs;
-    const uint4 *aux;     // Q4_K headers / Q8_0 scales (as uint4 = 8 halves)
-    const __half *xs;
-    const __half *ss;
-    const float *tsc;
+    const uint8_t *chunks;  // weight plane (Q4K_CHUNK / Q80_CHUNK byte chunks, 8 per super-chunk)
+    const uint8_t *img;     // activation image
     float *y;
     int64_t yst, ysr;
     const float *row_scales;
     int64_t n_row_scales;
-    int64_t n, K;
-    int ntiles;  // 16-row tiles
-    int nb;      // Q4_K: 256-blocks per row;  Q8_0: 32-blocks per row
-    int nb8;     // Q8_0: groups of 8 blocks
+    int64_t n;
+    int nk;            // k-steps per row: Q4_K blocks of 256 / Q8_0 groups of 8 blocks
     int m;
-    int ksplit;  // warps per row tile: 1, 2, 4, 8
+    int64_t nsuper;    // tile groups * nk
+    int per_cta;       // super-chunks per CTA
+    int maxslot;       // partial-sum slots per tile
+    float *partial;    // [tiles][maxslot][16 tokens][16 rows]
+    int *counters;     // [tiles] arrivals, zero between launches
+    int *status;       // device status word
 };
 
-// Per-row Q4_K scale constants for the sub-block pair (2t, 2t+1) owned by this thread.
-struct Q4KRow {
-    __half2 mul_lo, add_lo, mul_hi, add_hi;  // fma constants turning 1024+q / 1024+16q into sc*q
-    uint32_t mm;                             // half2 {m_2t, m_2t+1}
-    float d, dmin;
-};
-__device__ __forceinline__ Q4KRow q4k_row(const uint4 h, const int t) {
-    Q4KRow r;
-    const int sh = (t & 1) * 16;
-    const uint32_t A0 = (h.y >> sh) & 0xFFFFu, A1 = (h.z >> sh) & 0xFFFFu, A2 = (h.w >> sh) & 0xFFFFu;
-    uint32_t scp, mp;  // [sub 2t | sub 2t+1 << 8]
-    if (t < 2) {
-        scp = A0 & 0x3F3Fu;
-        mp = A1 & 0x3F3Fu;
-    } else {
-        scp = (A2 & 0x0F0Fu) | ((A0 >> 2) & 0x3030u);
-        mp = ((A2 >> 4) & 0x0F0Fu) | ((A1 >> 2) & 0x3030u);
-    }
-    const __half2 k1024 = __float2half2_rn(1024.0f);
-    const __half2 sca = __hsub2(u32_as_h2(__byte_perm(scp, 0x64u, 0x4040)), k1024);
-    const __half2 scb = __hsub2(u32_as_h2(__byte_perm(scp, 0x64u, 0x4141)), k1024);
-    r.mm = h2_as_u32(__hsub2(u32_as_h2(__byte_perm(mp, 0x64u, 0x4140)), k1024));
-    r.mul_lo = sca;
-    r.add_lo = __hmul2(sca, __float2half2_rn(-1024.0f));
-    r.mul_hi = __hmul2(scb, __float2half2_rn(0.0625f));
-    r.add_hi = __hmul2(scb, __float2half2_rn(-64.0f));
-    r.d = __half2float(__ushort_as_half((unsigned short)(h.x & 0xFFFFu)));
-    r.dmin = __half2float(__ushort_as_half((unsigned short)(h.x >> 16)));
-    return r;
+constexpr int GEMV_STAGES = 3;  // pipeline depth (stages of one super-chunk + its activation slice)
+constexpr int GEMV_WARPS = 8;
+constexpr int GEMV_ZERO = 512;  // zero region read by the lanes of unused MMA columns
+template <int FMT>
+__host__ __device__ constexpr int chunk_bytes() { return FMT == FMT_Q4K ? Q4K_CHUNK : Q80_CHUNK; }
+// shared memory: [GEMV_STAGES][8 chunks + slice] | zero [512] | full[GEMV_STAGES], empty[GEMV_STAGES]
+template <int FMT>
+static inline size_t gemv_smem_bytes(int m) {
+    return (size_t)GEMV_STAGES * (GEMV_WARPS * chunk_bytes<FMT>() + slice_bytes(m)) + GEMV_ZERO + 2 * GEMV_STAGES * 8;
 }
 
+// ---- one 16-row x 256-k chunk of Q4_K -------------------------------------------------------
+// ch: this warp's chunk in shared memory; xb[nt]: this lane's digit column (or the zero region);
+// sb[nt]: its sub-block sums; xs[nt]: activation scale of the lane's token.  tot[nt][h]: row g + 8h.
 template <int NT>
-__global__ void __launch_bounds__(256) gemv_q4k_kernel(const GemvParams p) {
-    __shared__ float red[8][NT * 4][32];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+__device__ __forceinline__ void q4k_chunk(uint32_t ch, int lane, const uint32_t (&xb)[NT], const uint32_t (&sb)[NT],
+                                          const float (&xs)[NT], float (&tot)[NT][2]) {
     const int g = lane >> 2, t = lane & 3;
-    const int S = p.ksplit;
-    const int tile = blockIdx.x * (8 / S) + warp / S;
-    const int split = warp % S;
-    float tot[NT][4];
+    uint4 q[4];
 #pragma unroll
-    for (int nt = 0; nt < NT; nt++) tot[nt][0] = tot[nt][1] = tot[nt][2] = tot[nt][3] = 0.f;
-
-    // Everything up to here is independent of the staging kernel's output.
-    asm volatile("griddepcontrol.wait;\n" ::: "memory");
-
-    if (tile < p.ntiles) {
-        const int b0 = (int)((int64_t)p.nb * split / S), b1 = (int)((int64_t)p.nb * (split + 1) / S);
-        const uint4 *qp = p.qs + ((size_t)tile * p.nb + b0) * 128 + lane;
-        const uint4 *hp = p.aux + ((size_t)tile * p.nb + b0) * 16 + g;
-        const int ncols = 2 * p.m;
-        uint4 q[4], h[2];
-        if (b0 < b1) {
+    for (int pg = 0; pg < 4; pg++) q[pg] = lds128(ch + (pg * 32 + lane) * 16);
+    const uint4 h0 = lds128(ch + 2048 + g * 16), h1 = lds128(ch + 2048 + (g + 8) * 16);
+    const uint2 dd = lds64(ch + 2304 + g * 8);
+    int acc[NT][4];
 #pragma unroll
-            for (int j = 0; j < 4; j++) q[j] = ldg_stream(qp + 32 * j);
-            h[0] = __ldg(hp);
-            h[1] = __ldg(hp + 8);
-        }
-        for (int b = b0; b < b1; b++) {
-            uint4 qn[4], hn[2];
-            if (b + 1 < b1) {
+    for (int nt = 0; nt < NT; nt++) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0;
 #pragma unroll
-                for (int j = 0; j < 4; j++) qn[j] = ldg_stream(qp + 128 + 32 * j);
-                hn[0] = __ldg(hp + 16);
-                hn[1] = __ldg(hp + 24);
-            }
-            const Q4KRow r0 = q4k_row(h[0], t), r1 = q4k_row(h[1], t);
-            float cq[NT][4], cm[NT][4];
+    for (int pg = 0; pg < 4; pg++) {
+#pragma unroll
+        for (int hs = 0; hs < 2; hs++) {
+            const int sub = 2 * pg + hs;
+            const uint32_t a0 = (hs ? q[pg].x >> 4 : q[pg].x) & 0x0F0F0F0Fu, a2 = (hs ? q[pg].y >> 4 : q[pg].y) & 0x0F0F0F0Fu;
+            const uint32_t a1 = (hs ? q[pg].z >> 4 : q[pg].z) & 0x0F0F0F0Fu, a3 = (hs ? q[pg].w >> 4 : q[pg].w) & 0x0F0F0F0Fu;
+            const int sc0 = (int)byte_of(sub < 4 ? h0.x : h0.y, sub & 3), sc1 = (int)byte_of(sub < 4 ? h1.x : h1.y, sub & 3);
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) {
-                cq[nt][0] = cq[nt][1] = cq[nt][2] = cq[nt][3] = 0.f;
-                cm[nt][0] = cm[nt][1] = cm[nt][2] = cm[nt][3] = 0.f;
+                const uint2 b = lds64(xb[nt] + 32 * sub);
+                int c[4];
+                imma16832<false>(c, a0, a1, a2, a3, b.x, b.y);
+                acc[nt][0] += sc0 * c[0];
+                acc[nt][1] += sc0 * c[1];
+                acc[nt][2] += sc1 * c[2];
+                acc[nt][3] += sc1 * c[3];
             }
-            // mins: one MMA per n-tile, A = {m_2t, m_2t+1} in k-slots (2t, 2t+1), upper k half zero
-#pragma unroll
-            for (int nt = 0; nt < NT; nt++) {
-                const int col = nt * 8 + g;
-                uint32_t sb = 0;
-                if (col < ncols)
-                    sb = __ldg(reinterpret_cast<const uint32_t *>(p.ss + (size_t)col * (p.K >> 5) + 8 * b + 2 * t));
-                mma16816(cm[nt], r0.mm, r1.mm, 0u, 0u, sb, 0u);
-            }
-#pragma unroll
-            for (int jj = 0; jj < 2; jj++) {
-                const uint32_t w0[4] = {q[jj].x, q[jj].y, q[jj].z, q[jj].w};              // row g
-                const uint32_t w1[4] = {q[2 + jj].x, q[2 + jj].y, q[2 + jj].z, q[2 + jj].w};  // row g + 8
-                uint32_t alo[4][4], ahi[4][4];
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const uint32_t s0 = w0[i] >> 8, s1 = w1[i] >> 8;
-                    alo[i][0] = h2_as_u32(__hfma2(u32_as_h2(magic_and(w0[i], 0x000F000Fu)), r0.mul_lo, r0.add_lo));
-                    alo[i][1] = h2_as_u32(__hfma2(u32_as_h2(magic_and(w1[i], 0x000F000Fu)), r1.mul_lo, r1.add_lo));
-                    alo[i][2] = h2_as_u32(__hfma2(u32_as_h2(magic_and(s0, 0x000F000Fu)), r0.mul_lo, r0.add_lo));
-                    alo[i][3] = h2_as_u32(__hfma2(u32_as_h2(magic_and(s1, 0x000F000Fu)), r1.mul_lo, r1.add_lo));
-                    ahi[i][0] = h2_as_u32(__hfma2(u32_as_h2(magic_and(w0[i], 0x00F000F0u)), r0.mul_hi, r0.add_hi));
-                    ahi[i][1] = h2_as_u32(__hfma2(u32_as_h2(magic_and(w1[i], 0x00F000F0u)), r1.mul_hi, r1.add_hi));
-                    ahi[i][2] = h2_as_u32(__hfma2(u32_as_h2(magic_and(s0, 0x00F000F0u)), r0.mul_hi, r0.add_hi));
-                    ahi[i][3] = h2_as_u32(__hfma2(u32_as_h2(magic_and(s1, 0x00F000F0u)), r1.mul_hi, r1.add_hi));
-                }
-#pragma unroll
-                for (int nt = 0; nt < NT; nt++) {
-                    const int col = nt * 8 + g;
-                    uint4 xl[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
-                    uint4 xh[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
-                    if (col < ncols) {
-                        const uint4 *xp = reinterpret_cast<const uint4 *>(p.xs + (size_t)col * p.K +
-                                                                          (size_t)256 * b + 64 * t + 16 * jj);
-                        xl[0] = __ldg(xp);
-                        xl[1] = __ldg(xp + 1);
-                        xh[0] = __ldg(xp + 4);
-                        xh[1] = __ldg(xp + 5);
-                    }
-                    mma16816(cq[nt], alo[0][0], alo[0][1], alo[0][2], alo[0][3], xl[0].x, xl[0].y);
-                    mma16816(cq[nt], alo[1][0], alo[1][1], alo[1][2], alo[1][3], xl[0].z, xl[0].w);
-                    mma16816(cq[nt], alo[2][0], alo[2][1], alo[2][2], alo[2][3], xl[1].x, xl[1].y);
-                    mma16816(cq[nt], alo[3][0], alo[3][1], alo[3][2], alo[3][3], xl[1].z, xl[1].w);
-                    mma16816(cq[nt], ahi[0][0], ahi[0][1], ahi[0][2], ahi[0][3], xh[0].x, xh[0].y);
-                    mma16816(cq[nt], ahi[1][0], ahi[1][1], ahi[1][2], ahi[1][3], xh[0].z, xh[0].w);
-                    mma16816(cq[nt], ahi[2][0], ahi[2][1], ahi[2][2], ahi[2][3], xh[1].x, xh[1].y);
-                    mma16816(cq[nt], ahi[3][0], ahi[3][1], ahi[3][2], ahi[3][3], xh[1].z, xh[1].w);
-                }
-            }
-#pragma unroll
-            for (int nt = 0; nt < NT; nt++) {
-                tot[nt][0] = fmaf(r0.d, cq[nt][0], tot[nt][0]);
-                tot[nt][1] = fmaf(r0.d, cq[nt][1], tot[nt][1]);
-                tot[nt][2] = fmaf(r1.d, cq[nt][2], tot[nt][2]);
-                tot[nt][3] = fmaf(r1.d, cq[nt][3], tot[nt][3]);
-                tot[nt][0] = fmaf(-r0.dmin, cm[nt][0], tot[nt][0]);
-                tot[nt][1] = fmaf(-r0.dmin, cm[nt][1], tot[nt][1]);
-                tot[nt][2] = fmaf(-r1.dmin, cm[nt][2], tot[nt][2]);
-                tot[nt][3] = fmaf(-r1.dmin, cm[nt][3], tot[nt][3]);
-            }
-#pragma unroll
-            for (int j = 0; j < 4; j++) q[j] = qn[j];
-            h[0] = hn[0];
-            h[1] = hn[1];
-            qp += 128;
-            hp += 16;
         }
     }
-    // reduce the k-splits of a tile (fixed order -> deterministic), then write
-    if (S > 1) {
+    // mins: A = m_sub in k-slots 0..7 (rows g, g+8), B = the sub-block sums split as 64*hi + lo
+    const uint32_t ma0 = t == 0 ? h0.z : (t == 1 ? h0.w : 0u), ma1 = t == 0 ? h1.z : (t == 1 ? h1.w : 0u);
+    const __half2 dd0 = *reinterpret_cast<const __half2 *>(&dd.x), dd1 = *reinterpret_cast<const __half2 *>(&dd.y);
+    const float d0 = __low2float(dd0), m0 = __high2float(dd0), d1 = __low2float(dd1), m1 = __high2float(dd1);
 #pragma unroll
-        for (int nt = 0; nt < NT; nt++)
+    for (int nt = 0; nt < NT; nt++) {
+        int chi[4], clo[4];
+        imma16832<false>(chi, ma0, ma1, 0u, 0u, lds32(sb[nt] + 4 * (t & 1)), 0u);
+        imma16832<false>(clo, ma0, ma1, 0u, 0u, lds32(sb[nt] + 8 + 4 * (t & 1)), 0u);
+        const float k254 = 1.0f / 254.0f;
+        const float f0 = fmaf((float)acc[nt][1], k254, (float)acc[nt][0]);
+        const float f1 = fmaf((float)acc[nt][3], k254, (float)acc[nt][2]);
+        const float n0 = fmaf((float)(64 * chi[1] + clo[1]), k254, (float)(64 * chi[0] + clo[0]));
+        const float n1 = fmaf((float)(64 * chi[3] + clo[3]), k254, (float)(64 * chi[2] + clo[2]));
+        tot[nt][0] = fmaf(xs[nt], fmaf(d0, f0, -(m0 * n0)), tot[nt][0]);
+        tot[nt][1] = fmaf(xs[nt], fmaf(d1, f1, -(m1 * n1)), tot[nt][1]);
+    }
+}
+
+// ---- one 16-row x 256-k chunk (8 blocks) of Q8_0; tot[nt][2h + digit] ------------------------
+template <int NT>
+__device__ __forceinline__ void q80_chunk(uint32_t ch, int lane, const uint32_t (&xb)[NT], const float (&xs)[NT],
+                                          float (&tot)[NT][4]) {
+    const int g = lane >> 2;
+    const uint4 dg0 = lds128(ch + 4096 + g * 16), dg1 = lds128(ch + 4096 + (g + 8) * 16);
+    const uint32_t dw0[4] = {dg0.x, dg0.y, dg0.z, dg0.w}, dw1[4] = {dg1.x, dg1.y, dg1.z, dg1.w};
+    float cs[NT][4];
 #pragma unroll
-            for (int i = 0; i < 4; i++) red[warp][nt * 4 + i][lane] = tot[nt][i];
-        __syncthreads();
-        if (split == 0) {
-            for (int s = 1; s < S; s++)
+    for (int nt = 0; nt < NT; nt++) cs[nt][0] = cs[nt][1] = cs[nt][2] = cs[nt][3] = 0.f;
 #pragma unroll
-                for (int nt = 0; nt < NT; nt++)
+    for (int bb = 0; bb < 8; bb++) {
+        const uint4 q = lds128(ch + (bb * 32 + lane) * 16);
+        const __half2 h0 = *reinterpret_cast<const __half2 *>(&dw0[bb >> 1]), h1 = *reinterpret_cast<const __half2 *>(&dw1[bb >> 1]);
+        const float d0 = (bb & 1) ? __high2float(h0) : __low2float(h0), d1 = (bb & 1) ? __high2float(h1) : __low2float(h1);
 #pragma unroll
-                    for (int i = 0; i < 4; i++) tot[nt][i] += red[warp + s][nt * 4 + i][lane];
+        for (int nt = 0; nt < NT; nt++) {
+            const uint2 b = lds64(xb[nt] + 32 * bb);
+            int c[4];
+            imma16832<true>(c, q.x, q.z, q.y, q.w, b.x, b.y);
+            cs[nt][0] = fmaf(d0, (float)c[0], cs[nt][0]);
+            cs[nt][1] = fmaf(d0, (float)c[1], cs[nt][1]);
+            cs[nt][2] = fmaf(d1, (float)c[2], cs[nt][2]);
+            cs[nt][3] = fmaf(d1, (float)c[3], cs[nt][3]);
         }
     }
-    if (split == 0 && tile < p.ntiles) {
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) tot[nt][j] = fmaf(xs[nt], cs[nt][j], tot[nt][j]);
+}
+
+// Completes this warp's tile: the last contributing CTA adds the partial sums in slot order (so the
+// result does not depend on arrival order) and writes y.  Out of line: it runs once per row tile.
+template <int NT>
+__device__ __noinline__ void gemv_flush(const GemvParams &p, int tile, int slot, int nsl, float (&v)[NT][2]) {
+    const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    bool finish = true;
+    if (nsl > 1) {
+        float *mine = p.partial + ((size_t)tile * p.maxslot + slot) * 256;
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) {
             const int tok = nt * 4 + t;
             if (tok < p.m) {
-                const float ts = p.tsc[tok];
+                __stcg(mine + tok * 16 + g, v[nt][0]);
+                __stcg(mine + tok * 16 + g + 8, v[nt][1]);
+            }
+        }
+        __threadfence();
+        __syncwarp();
+        int arrived = 0;
+        if (lane == 0) arrived = atomicAdd(p.counters + tile, 1);
+        arrived = __shfl_sync(0xffffffffu, arrived, 0);
+        finish = (arrived == nsl - 1);
+        if (finish) {
+            __threadfence();
+            const float *base = p.partial + (size_t)tile * p.maxslot * 256;
 #pragma unroll
-                for (int hrow = 0; hrow < 2; hrow++) {
-                    const int64_t row = (int64_t)tile * 16 + g + 8 * hrow;
-                    if (row < p.n) {
-                        float v = fmaf(tot[nt][2 * hrow + 1], 1.0f / 2048.0f, tot[nt][2 * hrow]) * ts;
-                        if (p.n_row_scales == 1) v *= p.row_scales[0];
-                        else if (p.n_row_scales > 1) v *= p.row_scales[row];
-                        p.y[(int64_t)tok * p.yst + row * p.ysr] = v;
+            for (int nt = 0; nt < NT; nt++) {
+                const int tok = nt * 4 + t;
+                float a0 = 0.f, a1 = 0.f;
+                if (tok < p.m)
+                    for (int s = 0; s < nsl; s++) {
+                        a0 += __ldcg(base + s * 256 + tok * 16 + g);
+                        a1 += __ldcg(base + s * 256 + tok * 16 + g + 8);
                     }
+                v[nt][0] = a0;
+                v[nt][1] = a1;
+            }
+            if (lane == 0) p.counters[tile] = 0;  // ready for the next launch
+        }
+    }
+    if (!finish) return;
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+        const int tok = nt * 4 + t;
+        if (tok < p.m) {
+#pragma unroll
+            for (int hrow = 0; hrow < 2; hrow++) {
+                const int64_t row = (int64_t)tile * 16 + g + 8 * hrow;
+                if (row < p.n) {
+                    float o = v[nt][hrow];
+                    if (p.n_row_scales == 1) o *= p.row_scales[0];
+                    else if (p.n_row_scales > 1) o *= p.row_scales[row];
+                    p.y[(int64_t)tok * p.yst + row * p.ysr] = o;
                 }
             }
         }
     }
 }
 
-// Q8_0: per 32-block and row  y += d * (q . x)   (classic.rs:870-881)
-template <int NT>
-__global__ void __launch_bounds__(256) gemv_q80_kernel(const GemvParams p) {
-    __shared__ float red[8][NT * 4][32];
+// Stream-k over the flattened (tile group, k-step) sequence of super-chunks (8 row tiles x one k-step,
+// contiguous in memory): CTA c owns super-chunks [c*per_cta, (c+1)*per_cta), one contiguous byte range.
+// Thread 0 is the producer: per step it issues two bulk copies (the super-chunk and the activation slice
+// of its k-step) into a ring stage; the 8 warps, each working on row tile 8*TG + warp, consume it.
+template <int FMT, int NT>
+__global__ void __launch_bounds__(256) gemv_kernel(const __grid_constant__ GemvParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int CHUNK = chunk_bytes<FMT>();
+    constexpr int SUPER = GEMV_WARPS * CHUNK;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int S = p.ksplit;
-    const int tile = blockIdx.x * (8 / S) + warp / S;
-    const int split = warp % S;
-    float tot[NT][4];
-#pragma unroll
-    for (int nt = 0; nt < NT; nt++) tot[nt][0] = tot[nt][1] = tot[nt][2] = tot[nt][3] = 0.f;
+    const uint32_t xbytes = slice_bytes(p.m);
+    const uint32_t stage_bytes = SUPER + xbytes;
+    const uint32_t smem_s = smem_u32(smem);
+    const uint32_t zero_s = smem_s + GEMV_STAGES * stage_bytes;
+    const uint32_t full = zero_s + GEMV_ZERO, empty = full + GEMV_STAGES * 8;
 
-    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    const int per_cta = p.per_cta, nk = p.nk;
+    const int64_t sc0 = min(p.nsuper, (int64_t)blockIdx.x * per_cta), sc1 = min(p.nsuper, sc0 + per_cta);
+    const int n = (int)(sc1 - sc0);
+    const uint8_t *wsrc = p.chunks + (size_t)sc0 * SUPER;
+    int TG = (int)(sc0 / nk), b = (int)(sc0 % nk);
 
-    if (tile < p.ntiles) {
-        const int g0 = (int)((int64_t)p.nb8 * split / S), g1 = (int)((int64_t)p.nb8 * (split + 1) / S);
-        const int ncols = 2 * p.m;
-        const __half2 k1152 = __float2half2_rn(1152.0f);
-        for (int g8 = g0; g8 < g1; g8++) {
-            const uint4 *dp = p.aux + ((size_t)tile * p.nb8 + g8) * 16;
-            const uint4 dg0 = __ldg(dp + g), dg1 = __ldg(dp + g + 8);
-            const uint32_t dw0[4] = {dg0.x, dg0.y, dg0.z, dg0.w}, dw1[4] = {dg1.x, dg1.y, dg1.z, dg1.w};
-            const int nblk = min(8, p.nb - 8 * g8);
-            const uint4 *qp = p.qs + ((size_t)tile * p.nb + 8 * g8) * 32 + lane;
-            uint4 q[8];
+    if (threadIdx.x == 0) {
 #pragma unroll
-            for (int bb = 0; bb < 8; bb++)
-                if (bb < nblk) q[bb] = ldg_stream(qp + 32 * bb);
+        for (int s = 0; s < GEMV_STAGES; s++) {
+            mbar_init(full + 8 * s, 1);
+            mbar_init(empty + 8 * s, GEMV_WARPS);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        // weights of the first stages: independent of the activation staging kernel
 #pragma unroll
-            for (int bb = 0; bb < 8; bb++) {
-                if (bb < nblk) {
-                    const int b = 8 * g8 + bb;
-                    const uint32_t u0 = q[bb].x ^ 0x80808080u, u1 = q[bb].y ^ 0x80808080u;
-                    const uint32_t u2 = q[bb].z ^ 0x80808080u, u3 = q[bb].w ^ 0x80808080u;
-                    // MMA 1: bytes 0..3 of each row's 8; MMA 2: bytes 4..7
-                    const uint32_t a0 = h2_as_u32(__hsub2(u32_as_h2(__byte_perm(u0, 0x64646464u, 0x4140)), k1152));
-                    const uint32_t a2 = h2_as_u32(__hsub2(u32_as_h2(__byte_perm(u0, 0x64646464u, 0x4342)), k1152));
-                    const uint32_t a1 = h2_as_u32(__hsub2(u32_as_h2(__byte_perm(u2, 0x64646464u, 0x4140)), k1152));
-                    const uint32_t a3 = h2_as_u32(__hsub2(u32_as_h2(__byte_perm(u2, 0x64646464u, 0x4342)), k1152));
-                    const uint32_t c0 = h2_as_u32(__hsub2(u32_as_h2(__byte_perm(u1, 0x64646464u, 0x4140)), k1152));
-                    const uint32_t c2 = h2_as_u32(__hsub2(u32_as_h2(__byte_perm(u1, 0x64646464u, 0x4342)), k1152));
-                    const uint32_t c1 = h2_as_u32(__hsub2(u32_as_h2(__byte_perm(u3, 0x64646464u, 0x4140)), k1152));
-                    const uint32_t c3 = h2_as_u32(__hsub2(u32_as_h2(__byte_perm(u3, 0x64646464u, 0x4342)), k1152));
-                    const uint32_t dsel0 = dw0[bb >> 1], dsel1 = dw1[bb >> 1];
-                    const float d0 = __half2float(
-                        __ushort_as_half((unsigned short)((bb & 1) ? (dsel0 >> 16) : (dsel0 & 0xFFFFu))));
-                    const float d1 = __half2float(
-                        __ushort_as_half((unsigned short)((bb & 1) ? (dsel1 >> 16) : (dsel1 & 0xFFFFu))));
-#pragma unroll
-                    for (int nt = 0; nt < NT; nt++) {
-                        const int col = nt * 8 + g;
-                        uint4 xv = make_uint4(0, 0, 0, 0);
-                        if (col < ncols)
-                            xv = __ldg(reinterpret_cast<const uint4 *>(p.xs + (size_t)col * p.K + (size_t)32 * b + 8 * t));
-                        float c[4] = {0.f, 0.f, 0.f, 0.f};
-                        mma16816(c, a0, a1, a2, a3, xv.x, xv.y);
-                        mma16816(c, c0, c1, c2, c3, xv.z, xv.w);
-                        tot[nt][0] = fmaf(d0, c[0], tot[nt][0]);
-                        tot[nt][1] = fmaf(d0, c[1], tot[nt][1]);
-                        tot[nt][2] = fmaf(d1, c[2], tot[nt][2]);
-                        tot[nt][3] = fmaf(d1, c[3], tot[nt][3]);
-                    }
-                }
+        for (int s = 0; s < GEMV_STAGES; s++)
+            if (s < n) {
+                mbar_expect_tx(full + 8 * s, stage_bytes);
+                bulk_g2s(smem_s + s * stage_bytes, wsrc + (size_t)s * SUPER, SUPER, full + 8 * s);
             }
+    }
+    if (threadIdx.x < GEMV_ZERO / 4) reinterpret_cast<uint32_t *>(smem + (zero_s - smem_s))[threadIdx.x] = 0u;
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");  // the activation image is complete from here on
+    if (threadIdx.x == 0) {
+        int bb = b;
+#pragma unroll
+        for (int s = 0; s < GEMV_STAGES; s++) {
+            if (s < n) bulk_g2s(smem_s + s * stage_bytes + SUPER, p.img + (size_t)bb * xbytes, xbytes, full + 8 * s);
+            if (++bb == nk) bb = 0;
         }
     }
-    if (S > 1) {
+    __syncthreads();
+
+    // Per-lane addresses inside stage 0.  Lanes of MMA columns >= 2m read the zero region (stride 0).
+    uint32_t xb0[NT], sb0[NT], xs0[NT], xstride[NT], xsstride[NT];
 #pragma unroll
-        for (int nt = 0; nt < NT; nt++)
-#pragma unroll
-            for (int i = 0; i < 4; i++) red[warp][nt * 4 + i][lane] = tot[nt][i];
-        __syncthreads();
-        if (split == 0) {
-            for (int s = 1; s < S; s++)
-#pragma unroll
-                for (int nt = 0; nt < NT; nt++)
-#pragma unroll
-                    for (int i = 0; i < 4; i++) tot[nt][i] += red[warp + s][nt * 4 + i][lane];
-        }
+    for (int nt = 0; nt < NT; nt++) {
+        const int col = nt * 8 + g, tok = nt * 4 + t;
+        const bool act = col < 2 * p.m;
+        xstride[nt] = act ? stage_bytes : 0u;
+        xb0[nt] = act ? smem_s + SUPER + col * 288 + 8 * t : zero_s;
+        sb0[nt] = act ? smem_s + SUPER + (2 * p.m) * 288 + col * 16 : zero_s;
+        xsstride[nt] = (tok < p.m) ? stage_bytes : 0u;
+        xs0[nt] = (tok < p.m) ? smem_s + SUPER + (2 * p.m) * 304 + tok * 4 : zero_s;
     }
-    if (split == 0 && tile < p.ntiles) {
+    int st = 0;                // stage of step i
+    uint32_t ph = 0;           // its parity
+    int bx = b + GEMV_STAGES;  // k-step of the next activation slice to request
+    while (bx >= nk) bx -= nk;
+    constexpr int NTOT = (FMT == FMT_Q4K) ? 2 : 4;
+    float tot[NT][NTOT];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+        for (int j = 0; j < NTOT; j++) tot[nt][j] = 0.f;
+
+    int i = 0;
+    while (i < n) {
+        const int steps = min(nk - b, n - i);
+        for (int s = 0; s < steps; s++, i++) {
+            // producer: refill the stage released at step i-1 with step i-1+STAGES
+            if (threadIdx.x == 0 && i > 0 && i - 1 + GEMV_STAGES < n) {
+                const int ps = (st == 0) ? GEMV_STAGES - 1 : st - 1;
+                const uint32_t pph = (st == 0) ? ph ^ 1u : ph;
+                if (!mbar_wait(empty + 8 * ps, pph)) {
+                    atomicExch(p.status, 2);
+                } else {
+                    mbar_expect_tx(full + 8 * ps, stage_bytes);
+                    bulk_g2s(smem_s + ps * stage_bytes, wsrc + (size_t)(i - 1 + GEMV_STAGES) * SUPER, SUPER, full + 8 * ps);
+                    bulk_g2s(smem_s + ps * stage_bytes + SUPER, p.img + (size_t)bx * xbytes, xbytes, full + 8 * ps);
+                }
+                if (++bx == nk) bx = 0;
+            }
+            if (!mbar_wait(full + 8 * st, ph)) {
+                if (lane == 0) atomicExch(p.status, 1);
+                return;  // give up instead of hanging; the host sees the status word
+            }
+            uint32_t xb[NT], sb[NT];
+            float xs[NT];
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                xb[nt] = xb0[nt] + st * xstride[nt];
+                sb[nt] = sb0[nt] + st * xstride[nt];
+                xs[nt] = __uint_as_float(lds32(xs0[nt] + st * xsstride[nt]));
+            }
+            const uint32_t ch = smem_s + st * stage_bytes + warp * CHUNK;
+            if constexpr (FMT == FMT_Q4K) q4k_chunk<NT>(ch, lane, xb, sb, xs, tot);
+            else q80_chunk<NT>(ch, lane, xb, xs, tot);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty + 8 * st);
+            if (++st == GEMV_STAGES) { st = 0; ph ^= 1u; }
+        }
+        // ---- this CTA's share of tile group TG is complete; each warp finishes its own tile ----
+        const int64_t first = (int64_t)TG * nk, last = first + nk - 1;
+        const int slot0 = (int)(first / per_cta), nsl = (int)(last / per_cta) - slot0 + 1;
+        float v[NT][2];
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) {
-            const int tok = nt * 4 + t;
-            if (tok < p.m) {
-                const float ts = p.tsc[tok];
-#pragma unroll
-                for (int hrow = 0; hrow < 2; hrow++) {
-                    const int64_t row = (int64_t)tile * 16 + g + 8 * hrow;
-                    if (row < p.n) {
-                        float v = fmaf(tot[nt][2 * hrow + 1], 1.0f / 2048.0f, tot[nt][2 * hrow]) * ts;
-                        if (p.n_row_scales == 1) v *= p.row_scales[0];
-                        else if (p.n_row_scales > 1) v *= p.row_scales[row];
-                        p.y[(int64_t)tok * p.yst + row * p.ysr] = v;
-                    }
-                }
+            if constexpr (FMT == FMT_Q4K) {
+                v[nt][0] = tot[nt][0];
+                v[nt][1] = tot[nt][1];
+            } else {
+                v[nt][0] = fmaf(tot[nt][1], 1.0f / 254.0f, tot[nt][0]);
+                v[nt][1] = fmaf(tot[nt][3], 1.0f / 254.0f, tot[nt][2]);
             }
+#pragma unroll
+            for (int j = 0; j < NTOT; j++) tot[nt][j] = 0.f;
         }
+        gemv_flush<NT>(p, TG * 8 + warp, (int)blockIdx.x - slot0, nsl, v);
+        TG++;
+        b = 0;
     }
 }
 
 // ---------------------------------------------------------------------------------------------
 static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-// workspace: xs [32][K] half | ss [32][K/32] half | tsc [16] float
+// workspace: the activation image, ceil(K/256) slices
 size_t gemv_ws_bytes(const Weight *w, int m) {
-    (void)m;
-    const size_t K = (size_t)w->k;
-    return align_up(32 * K * 2, 256) + align_up(32 * (K / 32) * 2, 256) + 256;
+    const size_t nk = ((size_t)w->k + 255) / 256;
+    return align_up(nk * slice_bytes(m), 256);
 }
 
 template <typename Kern>
-static cudaError_t launch_pdl(Kern kern, dim3 grid, dim3 block, cudaStream_t s, bool pdl, const GemvParams &p) {
+static cudaError_t launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t s, bool pdl,
+                              const GemvParams &p) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
-    cfg.dynamicSmemBytes = 0;
+    cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -454,67 +506,78 @@ static cudaError_t launch_pdl(Kern kern, dim3 grid, dim3 block, cudaStream_t s, 
     return cudaLaunchKernelEx(&cfg, kern, p);
 }
 
+template <int FMT, int NT>
+static cudaError_t configure_and_launch(Ctx *c, GemvParams &p, int64_t ntg, cudaStream_t s, int32_t *rc_out) {
+    const size_t smem = gemv_smem_bytes<FMT>(p.m);
+    cudaError_t e = cudaFuncSetAttribute(gemv_kernel<FMT, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    int per_sm = 0;
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemv_kernel<FMT, NT>, 256, smem);
+    if (e != cudaSuccess) return e;
+    if (per_sm < 1) per_sm = 1;
+    if (c->gemv_ctas_per_sm > 0 && c->gemv_ctas_per_sm < per_sm) per_sm = (int)c->gemv_ctas_per_sm;
+    p.nsuper = ntg * p.nk;
+    const int64_t ctas = (int64_t)c->sm_count * per_sm;
+    p.per_cta = (int)((p.nsuper + ctas - 1) / ctas);
+    if (p.per_cta < 1) p.per_cta = 1;
+    const unsigned grid = (unsigned)((p.nsuper + p.per_cta - 1) / p.per_cta);
+    p.maxslot = (p.nk - 1) / p.per_cta + 2;
+    const int64_t tiles = ntg * 8;
+    const size_t part_bytes = align_up((size_t)tiles * p.maxslot * 256 * sizeof(float), 256);
+    *rc_out = ensure_red(c, part_bytes + (size_t)tiles * sizeof(int));
+    if (*rc_out) return cudaSuccess;
+    p.partial = static_cast<float *>(c->red);
+    // counters live at the end of the buffer so a larger partial area never overlaps live counters
+    p.counters = reinterpret_cast<int *>(static_cast<char *>(c->red) + c->red_bytes) - tiles;
+    return launch_pdl(gemv_kernel<FMT, NT>, grid, 256, smem, s, c->gemv_pdl != 0, p);
+}
+
 int32_t gemv_launch(Ctx *c, const Weight *w, const float *x, int64_t xst, int64_t xsk, int m, float *y, int64_t yst,
                     int64_t ysr, const float *row_scales, int64_t n_row_scales, cudaStream_t s) {
     if (w->qt != GLLMK_QUANT_Q4K && w->qt != GLLMK_QUANT_Q8_0)
         return fail(c, GLLMK_STATUS_UNSUPPORTED, "gemv: quant type %d has no decode kernel", w->qt);
     int32_t rc = ensure_ws(c, gemv_ws_bytes(w, m));
     if (rc) return rc;
-    const size_t K = (size_t)w->k;
-    char *base = static_cast<char *>(c->ws);
-    __half *xs = reinterpret_cast<__half *>(base);
-    __half *ss = reinterpret_cast<__half *>(base + align_up(32 * K * 2, 256));
-    float *tsc = reinterpret_cast<float *>(base + align_up(32 * K * 2, 256) + align_up(32 * (K / 32) * 2, 256));
-
-    StageParams sp{x, xst, xsk, m, (int64_t)K, xs, ss, tsc, w->qt == GLLMK_QUANT_Q4K ? 1 : 0};
-    dim3 sgrid((unsigned)((K + 1023) / 1024), (unsigned)m);
-    stage_x_kernel<<<sgrid, 256, 0, s>>>(sp);
-    GK_CUDA(c, cudaGetLastError());
+    const int nk = (int)((w->k + 255) / 256);
 
     GemvParams p{};
-    p.qs = static_cast<const uint4 *>(w->qs);
-    p.aux = static_cast<const uint4 *>(w->aux);
-    p.xs = xs;
-    p.ss = ss;
-    p.tsc = tsc;
+    p.chunks = static_cast<const uint8_t *>(w->qs);
+    p.img = static_cast<const uint8_t *>(c->ws);
     p.y = y;
     p.yst = yst;
     p.ysr = ysr;
     p.row_scales = row_scales;
     p.n_row_scales = row_scales ? n_row_scales : 0;
     p.n = w->n;
-    p.K = w->k;
-    p.ntiles = (int)(w->n_pad / 16);
-    p.nb = (int)w->nb;
-    p.nb8 = (int)w->nb8;
+    p.nk = nk;
     p.m = m;
-    const int units = (w->qt == GLLMK_QUANT_Q4K) ? p.nb : p.nb8;  // what a k-split divides
-    int S = (int)c->gemv_ksplit;
-    if (S != 1 && S != 2 && S != 4 && S != 8) {
-        S = 1;
-        while (S < 8 && (int64_t)p.ntiles * S < 4096) S *= 2;
-    }
-    while (S > 1 && S > units) S /= 2;
-    p.ksplit = S;
-    const unsigned grid = (unsigned)((p.ntiles + (8 / S) - 1) / (8 / S));
+    p.status = c->status_dev;
+
+    StageParams sp{x, xst, xsk, m, w->k, static_cast<uint8_t *>(c->ws)};
+    dim3 sgrid((unsigned)(((size_t)nk * 256 + 1023) / 1024), (unsigned)m);
+    stage_x_kernel<<<sgrid, 256, 0, s>>>(sp);
+    GK_CUDA(c, cudaGetLastError());
+
+    const int64_t ntg = w->n_pad / 128;
     const int NT = (2 * m + 7) / 8;
-    const bool pdl = c->gemv_pdl != 0;
     cudaError_t e;
+    rc = 0;
     if (w->qt == GLLMK_QUANT_Q4K) {
         switch (NT) {
-            case 1: e = launch_pdl(gemv_q4k_kernel<1>, grid, 256, s, pdl, p); break;
-            case 2: e = launch_pdl(gemv_q4k_kernel<2>, grid, 256, s, pdl, p); break;
-            case 3: e = launch_pdl(gemv_q4k_kernel<3>, grid, 256, s, pdl, p); break;
-            default: e = launch_pdl(gemv_q4k_kernel<4>, grid, 256, s, pdl, p); break;
+            case 1: e = configure_and_launch<FMT_Q4K, 1>(c, p, ntg, s, &rc); break;
+            case 2: e = configure_and_launch<FMT_Q4K, 2>(c, p, ntg, s, &rc); break;
+            case 3: e = configure_and_launch<FMT_Q4K, 3>(c, p, ntg, s, &rc); break;
+            default: e = configure_and_launch<FMT_Q4K, 4>(c, p, ntg, s, &rc); break;
         }
     } else {
         switch (NT) {
-            case 1: e = launch_pdl(gemv_q80_kernel<1>, grid, 256, s, pdl, p); break;
-            case 2: e = launch_pdl(gemv_q80_kernel<2>, grid, 256, s, pdl, p); break;
-            case 3: e = launch_pdl(gemv_q80_kernel<3>, grid, 256, s, pdl, p); break;
-            default: e = launch_pdl(gemv_q80_kernel<4>, grid, 256, s, pdl, p); break;
+            case 1: e = configure_and_launch<FMT_Q80, 1>(c, p, ntg, s, &rc); break;
+            case 2: e = configure_and_launch<FMT_Q80, 2>(c, p, ntg, s, &rc); break;
+            case 3: e = configure_and_launch<FMT_Q80, 3>(c, p, ntg, s, &rc); break;
+            default: e = configure_and_launch<FMT_Q80, 4>(c, p, ntg, s, &rc); break;
         }
     }
+    if (rc) return rc;
     GK_CUDA(c, e);
     return GLLMK_STATUS_OK;
 }

@@ -205,10 +205,8 @@ int32_t quantize_launch(Ctx *c, int32_t qt, const float *x, int64_t rows, int64_
         const size_t nb = count / 32;
         quantize_mxfp4_kernel<<<(unsigned)((nb + 7) / 8), 256, 0, s>>>(x, (uint8_t *)blocks, (uint8_t *)scales, nb);
     } else if (qt == GLLMK_QUANT_NVFP4) {
-        // workspace: [0] = global scale, [64..] partial maxima
-        int32_t rc = ensure_ws(c, 8192);
-        if (rc) return rc;
-        float *gdev = static_cast<float *>(c->ws);
+        // scratch behind the status word (16 KiB block owned by the context): global scale + partial maxima
+        float *gdev = reinterpret_cast<float *>(c->status_dev) + 64;
         float *partial = gdev + 64;
         if (*global_scale > 0.0f) {
             GK_CUDA(c, cudaMemcpyAsync(gdev, global_scale, sizeof(float), cudaMemcpyHostToDevice, s));

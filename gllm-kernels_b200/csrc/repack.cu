@@ -7,22 +7,43 @@ namespace gllmk {
 static inline unsigned grid_for(size_t n, unsigned block) { return (unsigned)((n + block - 1) / block); }
 
 // ================================ Q4_K =====================================================
-__global__ void repack_q4k_qs(const uint8_t *__restrict__ src, uint4 *__restrict__ qs, int64_t n, int64_t nb,
+// chunk (T, b) = 2368 bytes, layout in common.cuh.
+__device__ __forceinline__ void q4k_fields(const uint8_t *s, uint32_t *sc, uint32_t *mn) {
+    // get_scale_min_k4, src/macros/quant_primitive/k_quant.rs:13-23
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        if (j < 4) { sc[j] = s[j] & 63u; mn[j] = s[j + 4] & 63u; }
+        else {
+            sc[j] = (s[j + 4] & 0xFu) | ((uint32_t)(s[j - 4] >> 6) << 4);
+            mn[j] = (uint32_t)(s[j + 4] >> 4) | ((uint32_t)(s[j] >> 6) << 4);
+        }
+    }
+}
+// thread = one uint4 of the nibble area: (T, b, p, lane)
+__global__ void repack_q4k_qs(const uint8_t *__restrict__ src, uint8_t *__restrict__ chunks, int64_t n, int64_t nb,
                               size_t total) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
-    const int lane = (int)(idx & 31), j = (int)((idx >> 5) & 3);
+    const int lane = (int)(idx & 31), pgrp = (int)((idx >> 5) & 3);
     const size_t tb = idx >> 7;  // T*nb + b
     const int64_t T = (int64_t)(tb / (size_t)nb), b = (int64_t)(tb % (size_t)nb);
     const int g = lane >> 2, t = lane & 3;
-    const int64_t row = 16 * T + g + 8 * (j >> 1);
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (row < n) v = reinterpret_cast<const uint4 *>(src + ((size_t)row * nb + b) * 144)[1 + 2 * t + (j & 1)];
-    qs[idx] = v;
+    uint32_t v[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        const int64_t row = 16 * T + g + 8 * h;
+        if (row < n) {
+            const uint2 w = *reinterpret_cast<const uint2 *>(src + ((size_t)row * nb + b) * 144 + 16 + 32 * pgrp + 8 * t);
+            v[2 * h] = w.x;
+            v[2 * h + 1] = w.y;
+        }
+    }
+    reinterpret_cast<uint4 *>(chunks + q4k_chunk_index(T, b, nb) * Q4K_CHUNK)[pgrp * 32 + lane] =
+        make_uint4(v[0], v[1], v[2], v[3]);
 }
-__global__ void repack_q4k_hdr(const uint8_t *__restrict__ src, uint4 *__restrict__ hdr, int64_t n, int64_t nb,
+__global__ void repack_q4k_hdr(const uint8_t *__restrict__ src, uint8_t *__restrict__ chunks, int64_t n, int64_t nb,
                                size_t total) {
-    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // (T*nb + b)*16 + rr
     if (idx >= total) return;
     const int rr = (int)(idx & 15);
     const size_t tb = idx >> 4;
@@ -30,10 +51,27 @@ __global__ void repack_q4k_hdr(const uint8_t *__restrict__ src, uint4 *__restric
     const int64_t row = 16 * T + rr;
     uint4 v = make_uint4(0, 0, 0, 0);
     if (row < n) v = reinterpret_cast<const uint4 *>(src + ((size_t)row * nb + b) * 144)[0];
-    hdr[idx] = v;
+    uint8_t s[12];
+    *reinterpret_cast<uint32_t *>(s) = v.y;
+    *reinterpret_cast<uint32_t *>(s + 4) = v.z;
+    *reinterpret_cast<uint32_t *>(s + 8) = v.w;
+    uint32_t sc[8], mn[8];
+    q4k_fields(s, sc, mn);
+    uint8_t *chunk = chunks + q4k_chunk_index(T, b, nb) * Q4K_CHUNK;
+    reinterpret_cast<uint4 *>(chunk + 2048)[rr] =
+        make_uint4(sc[0] | (sc[1] << 8) | (sc[2] << 16) | (sc[3] << 24), sc[4] | (sc[5] << 8) | (sc[6] << 16) | (sc[7] << 24),
+                   mn[0] | (mn[1] << 8) | (mn[2] << 16) | (mn[3] << 24), mn[4] | (mn[5] << 8) | (mn[6] << 16) | (mn[7] << 24));
+    reinterpret_cast<uint32_t *>(chunk + 2304)[(rr & 7) * 2 + (rr >> 3)] = v.x;
 }
-__global__ void unpack_q4k(const uint4 *__restrict__ qs, const uint4 *__restrict__ hdr, uint8_t *__restrict__ dst,
-                           int64_t n, int64_t nb, size_t total) {
+// reads back 32-bit word `wi` (0..31) of the nibble bytes of (row, b)
+__device__ __forceinline__ uint32_t q4k_word(const uint8_t *chunk, int rr, int wi) {
+    const int pgrp = wi >> 3, i = wi & 7, t = i >> 1, lane = 4 * (rr & 7) + t;
+    const uint4 q = reinterpret_cast<const uint4 *>(chunk)[pgrp * 32 + lane];
+    const int sel = 2 * (rr >> 3) + (i & 1);
+    return sel == 0 ? q.x : (sel == 1 ? q.y : (sel == 2 ? q.z : q.w));
+}
+__global__ void unpack_q4k(const uint8_t *__restrict__ chunks, uint8_t *__restrict__ dst, int64_t n, int64_t nb,
+                           size_t total) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // (row*nb + b)*9 + u9
     if (idx >= total) return;
     const int u9 = (int)(idx % 9);
@@ -41,18 +79,38 @@ __global__ void unpack_q4k(const uint4 *__restrict__ qs, const uint4 *__restrict
     const int64_t row = (int64_t)(rb / (size_t)nb), b = (int64_t)(rb % (size_t)nb);
     const int64_t T = row >> 4;
     const int rr = (int)(row & 15);
+    const uint8_t *chunk = chunks + q4k_chunk_index(T, b, nb) * Q4K_CHUNK;
     uint4 v;
-    if (u9 == 0) v = hdr[((size_t)T * nb + b) * 16 + rr];
-    else {
-        const int u = u9 - 1, t = u >> 1, j = 2 * (rr >> 3) + (u & 1), lane = 4 * (rr & 7) + t;
-        v = qs[(((size_t)T * nb + b) * 4 + j) * 32 + lane];
+    if (u9 == 0) {
+        const uint4 h = reinterpret_cast<const uint4 *>(chunk + 2048)[rr];
+        uint32_t sc[8], mn[8];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            sc[j] = (h.x >> (8 * j)) & 0xFF; sc[j + 4] = (h.y >> (8 * j)) & 0xFF;
+            mn[j] = (h.z >> (8 * j)) & 0xFF; mn[j + 4] = (h.w >> (8 * j)) & 0xFF;
+        }
+        uint8_t s[12];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {  // inverse of get_scale_min_k4
+            s[j] = (uint8_t)(sc[j] | ((sc[j + 4] >> 4) << 6));
+            s[j + 4] = (uint8_t)(mn[j] | ((mn[j + 4] >> 4) << 6));
+            s[j + 8] = (uint8_t)((sc[j + 4] & 15) | ((mn[j + 4] & 15) << 4));
+        }
+        v.x = reinterpret_cast<const uint32_t *>(chunk + 2304)[(rr & 7) * 2 + (rr >> 3)];
+        v.y = *reinterpret_cast<uint32_t *>(s);
+        v.z = *reinterpret_cast<uint32_t *>(s + 4);
+        v.w = *reinterpret_cast<uint32_t *>(s + 8);
+    } else {
+        const int w0 = 4 * (u9 - 1);
+        v = make_uint4(q4k_word(chunk, rr, w0), q4k_word(chunk, rr, w0 + 1), q4k_word(chunk, rr, w0 + 2),
+                       q4k_word(chunk, rr, w0 + 3));
     }
     reinterpret_cast<uint4 *>(dst + rb * 144)[u9] = v;
     (void)n;
 }
 // out[row][256b + ...] following k_quant.rs:7-56; thread = one 32-bit word of qs (4 low + 4 high outputs)
-__global__ void dequant_q4k(const uint4 *__restrict__ qs, const uint4 *__restrict__ hdr, float *__restrict__ out,
-                            int64_t n, int64_t nb, size_t total) {
+__global__ void dequant_q4k(const uint8_t *__restrict__ chunks, float *__restrict__ out, int64_t n, int64_t nb,
+                            size_t total) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // (row*nb + b)*32 + w, w = word 0..31 of qs
     if (idx >= total) return;
     const int wq = (int)(idx & 31);
@@ -60,31 +118,18 @@ __global__ void dequant_q4k(const uint4 *__restrict__ qs, const uint4 *__restric
     const int64_t row = (int64_t)(rb / (size_t)nb), b = (int64_t)(rb % (size_t)nb);
     const int64_t T = row >> 4;
     const int rr = (int)(row & 15);
-    const int u = wq >> 2, wi = wq & 3;  // uint4 index within the block, word within it
-    const int t = u >> 1, j = 2 * (rr >> 3) + (u & 1), lane = 4 * (rr & 7) + t;
-    const uint4 q4 = qs[(((size_t)T * nb + b) * 4 + j) * 32 + lane];
-    const uint32_t w = wi == 0 ? q4.x : (wi == 1 ? q4.y : (wi == 2 ? q4.z : q4.w));
-    const uint4 h = hdr[((size_t)T * nb + b) * 16 + rr];
-    const float d = __half2float(__ushort_as_half((unsigned short)(h.x & 0xFFFF)));
-    const float dmin = __half2float(__ushort_as_half((unsigned short)(h.x >> 16)));
-    uint8_t s[12];
-    *reinterpret_cast<uint32_t *>(s) = h.y;
-    *reinterpret_cast<uint32_t *>(s + 4) = h.z;
-    *reinterpret_cast<uint32_t *>(s + 8) = h.w;
-    const int group = u >> 1;  // 32 bytes per group
-    float sc[2], mn[2];
-#pragma unroll
-    for (int hs = 0; hs < 2; hs++) {
-        const int jj = 2 * group + hs;
-        if (jj < 4) { sc[hs] = (float)(s[jj] & 63); mn[hs] = (float)(s[jj + 4] & 63); }
-        else {
-            sc[hs] = (float)((s[jj + 4] & 0xF) | ((s[jj - 4] >> 6) << 4));
-            mn[hs] = (float)((s[jj + 4] >> 4) | ((s[jj] >> 6) << 4));
-        }
-    }
-    const float d1 = __fmul_rn(d, sc[0]), nm1 = __fmul_rn(dmin, mn[0]);
-    const float d2 = __fmul_rn(d, sc[1]), nm2 = __fmul_rn(dmin, mn[1]);
-    const int l = 16 * (u & 1) + 4 * wi;
+    const uint8_t *chunk = chunks + q4k_chunk_index(T, b, nb) * Q4K_CHUNK;
+    const uint32_t w = q4k_word(chunk, rr, wq);
+    const int group = wq >> 3;  // 32 bytes per group = sub-block pair (2*group, 2*group + 1)
+    const uint4 h = reinterpret_cast<const uint4 *>(chunk + 2048)[rr];
+    const uint32_t scw = group < 2 ? h.x : h.y, mnw = group < 2 ? h.z : h.w;
+    const int sh = 16 * (group & 1);
+    const uint32_t dd = reinterpret_cast<const uint32_t *>(chunk + 2304)[(rr & 7) * 2 + (rr >> 3)];
+    const float d = __half2float(__ushort_as_half((unsigned short)(dd & 0xFFFF)));
+    const float dmin = __half2float(__ushort_as_half((unsigned short)(dd >> 16)));
+    const float d1 = __fmul_rn(d, (float)((scw >> sh) & 0xFF)), nm1 = __fmul_rn(dmin, (float)((mnw >> sh) & 0xFF));
+    const float d2 = __fmul_rn(d, (float)((scw >> (sh + 8)) & 0xFF)), nm2 = __fmul_rn(dmin, (float)((mnw >> (sh + 8)) & 0xFF));
+    const int l = 4 * (wq & 7);
     float4 lo, hi;
     lo.x = __fsub_rn(__fmul_rn(d1, (float)(w & 15u)), nm1);
     lo.y = __fsub_rn(__fmul_rn(d1, (float)((w >> 8) & 15u)), nm1);
@@ -101,28 +146,32 @@ __global__ void dequant_q4k(const uint4 *__restrict__ qs, const uint4 *__restric
 }
 
 // ================================ Q8_0 =====================================================
-__global__ void repack_q80_qs(const uint8_t *__restrict__ src, uint4 *__restrict__ qs, int64_t n, int64_t nb,
-                              size_t total) {
-    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // (T*nb + b)*32 + lane
+// chunk (T, b8) = 4352 bytes: 8 blocks x 512 bytes of int8 in fragment order + 16 rows x 8 f16 scales.
+// thread = one uint4 of the int8 area: (T, b8, bb, lane)
+__global__ void repack_q80_qs(const uint8_t *__restrict__ src, uint8_t *__restrict__ chunks, int64_t n, int64_t nb,
+                              int64_t nb8, size_t total) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // ((T*nb8 + b8)*8 + bb)*32 + lane
     if (idx >= total) return;
-    const int lane = (int)(idx & 31);
-    const size_t tb = idx >> 5;
-    const int64_t T = (int64_t)(tb / (size_t)nb), b = (int64_t)(tb % (size_t)nb);
+    const int lane = (int)(idx & 31), bb = (int)((idx >> 5) & 7);
+    const size_t tb = idx >> 8;
+    const int64_t T = (int64_t)(tb / (size_t)nb8), b8 = (int64_t)(tb % (size_t)nb8);
+    const int64_t b = 8 * b8 + bb;
     const int g = lane >> 2, t = lane & 3;
     uint32_t v[4] = {0, 0, 0, 0};
 #pragma unroll
     for (int h = 0; h < 2; h++) {
         const int64_t row = 16 * T + g + 8 * h;
-        if (row < n) {
+        if (row < n && b < nb) {
             const unsigned short *p =
                 reinterpret_cast<const unsigned short *>(src + ((size_t)row * nb + b) * 34 + 2 + 8 * t);
             v[2 * h] = (uint32_t)p[0] | ((uint32_t)p[1] << 16);
             v[2 * h + 1] = (uint32_t)p[2] | ((uint32_t)p[3] << 16);
         }
     }
-    qs[idx] = make_uint4(v[0], v[1], v[2], v[3]);
+    reinterpret_cast<uint4 *>(chunks + q4k_chunk_index(T, b8, nb8) * Q80_CHUNK)[bb * 32 + lane] =
+        make_uint4(v[0], v[1], v[2], v[3]);
 }
-__global__ void repack_q80_d(const uint8_t *__restrict__ src, unsigned short *__restrict__ d, int64_t n, int64_t nb,
+__global__ void repack_q80_d(const uint8_t *__restrict__ src, uint8_t *__restrict__ chunks, int64_t n, int64_t nb,
                              int64_t nb8, size_t total) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // ((T*nb8 + b8)*16 + rr)*8 + bb
     if (idx >= total) return;
@@ -132,10 +181,10 @@ __global__ void repack_q80_d(const uint8_t *__restrict__ src, unsigned short *__
     const int64_t row = 16 * T + rr, b = 8 * b8 + bb;
     unsigned short v = 0;
     if (row < n && b < nb) v = *reinterpret_cast<const unsigned short *>(src + ((size_t)row * nb + b) * 34);
-    d[idx] = v;
+    reinterpret_cast<unsigned short *>(chunks + q4k_chunk_index(T, b8, nb8) * Q80_CHUNK + 4096)[rr * 8 + bb] = v;
 }
-__global__ void unpack_q80(const uint4 *__restrict__ qs, const unsigned short *__restrict__ d,
-                           uint8_t *__restrict__ dst, int64_t n, int64_t nb, int64_t nb8, size_t total) {
+__global__ void unpack_q80(const uint8_t *__restrict__ chunks, uint8_t *__restrict__ dst, int64_t n, int64_t nb,
+                           int64_t nb8, size_t total) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // (row*nb + b)*4 + t
     if (idx >= total) return;
     const int t = (int)(idx & 3);
@@ -143,18 +192,20 @@ __global__ void unpack_q80(const uint4 *__restrict__ qs, const unsigned short *_
     const int64_t row = (int64_t)(rb / (size_t)nb), b = (int64_t)(rb % (size_t)nb);
     const int64_t T = row >> 4;
     const int rr = (int)(row & 15), g = rr & 7, h = rr >> 3;
-    const uint4 q = qs[((size_t)T * nb + b) * 32 + 4 * g + t];
+    const uint8_t *chunk = chunks + q4k_chunk_index(T, b >> 3, nb8) * Q80_CHUNK;
+    const uint4 q = reinterpret_cast<const uint4 *>(chunk)[(b & 7) * 32 + 4 * g + t];
     const uint32_t w0 = h ? q.z : q.x, w1 = h ? q.w : q.y;
     unsigned short *p = reinterpret_cast<unsigned short *>(dst + rb * 34 + 2 + 8 * t);
     p[0] = (unsigned short)(w0 & 0xFFFF); p[1] = (unsigned short)(w0 >> 16);
     p[2] = (unsigned short)(w1 & 0xFFFF); p[3] = (unsigned short)(w1 >> 16);
     if (t == 0)
-        *reinterpret_cast<unsigned short *>(dst + rb * 34) = d[(((size_t)T * nb8 + (b >> 3)) * 16 + rr) * 8 + (b & 7)];
+        *reinterpret_cast<unsigned short *>(dst + rb * 34) =
+            reinterpret_cast<const unsigned short *>(chunk + 4096)[rr * 8 + (b & 7)];
     (void)n;
 }
 // classic.rs:860-868: out = d * q; thread = 8 elements
-__global__ void dequant_q80(const uint4 *__restrict__ qs, const unsigned short *__restrict__ d, float *__restrict__ out,
-                            int64_t n, int64_t nb, int64_t nb8, size_t total) {
+__global__ void dequant_q80(const uint8_t *__restrict__ chunks, float *__restrict__ out, int64_t n, int64_t nb,
+                            int64_t nb8, size_t total) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // (row*nb + b)*4 + t
     if (idx >= total) return;
     const int t = (int)(idx & 3);
@@ -162,10 +213,10 @@ __global__ void dequant_q80(const uint4 *__restrict__ qs, const unsigned short *
     const int64_t row = (int64_t)(rb / (size_t)nb), b = (int64_t)(rb % (size_t)nb);
     const int64_t T = row >> 4;
     const int rr = (int)(row & 15), g = rr & 7, h = rr >> 3;
-    const uint4 q = qs[((size_t)T * nb + b) * 32 + 4 * g + t];
+    const uint8_t *chunk = chunks + q4k_chunk_index(T, b >> 3, nb8) * Q80_CHUNK;
+    const uint4 q = reinterpret_cast<const uint4 *>(chunk)[(b & 7) * 32 + 4 * g + t];
     const uint32_t w0 = h ? q.z : q.x, w1 = h ? q.w : q.y;
-    const float dv =
-        __half2float(__ushort_as_half(d[(((size_t)T * nb8 + (b >> 3)) * 16 + rr) * 8 + (b & 7)]));
+    const float dv = __half2float(__ushort_as_half(reinterpret_cast<const unsigned short *>(chunk + 4096)[rr * 8 + (b & 7)]));
     float4 a, c;
     a.x = __fmul_rn(dv, (float)(int8_t)(w0 & 0xFF)); a.y = __fmul_rn(dv, (float)(int8_t)((w0 >> 8) & 0xFF));
     a.z = __fmul_rn(dv, (float)(int8_t)((w0 >> 16) & 0xFF)); a.w = __fmul_rn(dv, (float)(int8_t)(w0 >> 24));
@@ -299,13 +350,14 @@ __global__ void dequant_raw_kernel(int qt, const uint8_t *__restrict__ blocks, c
 int32_t repack_upload(Ctx *c, Weight *w, const void *blocks, const void *scales, cudaStream_t s) {
     const uint8_t *src = static_cast<const uint8_t *>(blocks);
     if (w->qt == GLLMK_QUANT_Q4K) {
+        // n_pad is a multiple of 128: tiles beyond n are written as zero chunks
         const size_t tq = (size_t)(w->n_pad / 16) * w->nb * 128, th = (size_t)(w->n_pad / 16) * w->nb * 16;
-        repack_q4k_qs<<<grid_for(tq, 256), 256, 0, s>>>(src, (uint4 *)w->qs, w->n, w->nb, tq);
-        repack_q4k_hdr<<<grid_for(th, 256), 256, 0, s>>>(src, (uint4 *)w->aux, w->n, w->nb, th);
+        repack_q4k_qs<<<grid_for(tq, 256), 256, 0, s>>>(src, (uint8_t *)w->qs, w->n, w->nb, tq);
+        repack_q4k_hdr<<<grid_for(th, 256), 256, 0, s>>>(src, (uint8_t *)w->qs, w->n, w->nb, th);
     } else if (w->qt == GLLMK_QUANT_Q8_0) {
-        const size_t tq = (size_t)(w->n_pad / 16) * w->nb * 32, td = (size_t)(w->n_pad / 16) * w->nb8 * 128;
-        repack_q80_qs<<<grid_for(tq, 256), 256, 0, s>>>(src, (uint4 *)w->qs, w->n, w->nb, tq);
-        repack_q80_d<<<grid_for(td, 256), 256, 0, s>>>(src, (unsigned short *)w->aux, w->n, w->nb, w->nb8, td);
+        const size_t tq = (size_t)(w->n_pad / 16) * w->nb8 * 256, td = (size_t)(w->n_pad / 16) * w->nb8 * 128;
+        repack_q80_qs<<<grid_for(tq, 256), 256, 0, s>>>(src, (uint8_t *)w->qs, w->n, w->nb, w->nb8, tq);
+        repack_q80_d<<<grid_for(td, 256), 256, 0, s>>>(src, (uint8_t *)w->qs, w->n, w->nb, w->nb8, td);
     } else {
         const int mode = (w->qt == GLLMK_QUANT_NVFP4) ? 2 : (scales ? 0 : 1);
         const int64_t spr = (mode == 2) ? (w->k >> 4) : (w->k >> 5);
@@ -322,11 +374,10 @@ int32_t repack_unpack(Ctx *c, const Weight *w, void *blocks, void *scales, cudaS
     uint8_t *dst = static_cast<uint8_t *>(blocks);
     if (w->qt == GLLMK_QUANT_Q4K) {
         const size_t t = (size_t)w->n * w->nb * 9;
-        unpack_q4k<<<grid_for(t, 256), 256, 0, s>>>((const uint4 *)w->qs, (const uint4 *)w->aux, dst, w->n, w->nb, t);
+        unpack_q4k<<<grid_for(t, 256), 256, 0, s>>>((const uint8_t *)w->qs, dst, w->n, w->nb, t);
     } else if (w->qt == GLLMK_QUANT_Q8_0) {
         const size_t t = (size_t)w->n * w->nb * 4;
-        unpack_q80<<<grid_for(t, 256), 256, 0, s>>>((const uint4 *)w->qs, (const unsigned short *)w->aux, dst, w->n,
-                                                    w->nb, w->nb8, t);
+        unpack_q80<<<grid_for(t, 256), 256, 0, s>>>((const uint8_t *)w->qs, dst, w->n, w->nb, w->nb8, t);
     } else {
         const size_t t = (size_t)w->n * (w->k >> 1);
         unpack_fp4<<<grid_for(t, 256), 256, 0, s>>>((const uint8_t *)w->qs, (const uint8_t *)w->aux, dst,
@@ -339,11 +390,10 @@ int32_t repack_unpack(Ctx *c, const Weight *w, void *blocks, void *scales, cudaS
 int32_t dequant_matrix(Ctx *c, const Weight *w, float *out, cudaStream_t s) {
     if (w->qt == GLLMK_QUANT_Q4K) {
         const size_t t = (size_t)w->n * w->nb * 32;
-        dequant_q4k<<<grid_for(t, 256), 256, 0, s>>>((const uint4 *)w->qs, (const uint4 *)w->aux, out, w->n, w->nb, t);
+        dequant_q4k<<<grid_for(t, 256), 256, 0, s>>>((const uint8_t *)w->qs, out, w->n, w->nb, t);
     } else if (w->qt == GLLMK_QUANT_Q8_0) {
         const size_t t = (size_t)w->n * w->nb * 4;
-        dequant_q80<<<grid_for(t, 256), 256, 0, s>>>((const uint4 *)w->qs, (const unsigned short *)w->aux, out, w->n,
-                                                     w->nb, w->nb8, t);
+        dequant_q80<<<grid_for(t, 256), 256, 0, s>>>((const uint8_t *)w->qs, out, w->n, w->nb, w->nb8, t);
     } else {
         const size_t t = (size_t)w->n * (w->k >> 3);
         dequant_fp4<<<grid_for(t, 256), 256, 0, s>>>((const uint32_t *)w->qs, (const uint8_t *)w->aux, out, w->n, w->k,

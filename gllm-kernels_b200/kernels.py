@@ -103,6 +103,12 @@ class GpuKernels:
         if rc:
             raise GllmkError(rc, what, (lib().gllmk_last_error(self._ctx) or b"").decode())
 
+    def status(self) -> int:
+        """Synchronises and returns the device status word (0 = no kernel gave up a bounded wait)."""
+        v = C.c_int32()
+        self._check(lib().gllmk_ctx_status(self._ctx, C.byref(v)), "gllmk_ctx_status")
+        return v.value
+
     def set(self, key: str, value: int) -> None:
         self._check(lib().gllmk_ctx_set(self._ctx, key.encode(), int(value)), "ctx_set")
 

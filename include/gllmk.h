@@ -79,8 +79,13 @@ GLLMK_API int32_t gllmk_ctx_create(int32_t device, gllmk_ctx *out);
 GLLMK_API void gllmk_ctx_free(gllmk_ctx ctx);
 /* Text of the last error raised through this context ("" if none).  Never NULL. */
 GLLMK_API const char *gllmk_last_error(gllmk_ctx ctx);
-/* Tuning knobs, for experiments.  key: "gemv_ksplit" (0 = auto, else 1,2,4,8),
- * "gemv_pdl" (1 = overlap the activation staging kernel with the weight stream). */
+/* Waits for the device and reads the context's device-side status word: every wait inside a kernel
+ * (on a bulk-copy barrier) is bounded, and a kernel that gives one up records a non-zero code there
+ * and returns instead of hanging.  Returns RUNTIME_ERROR (and clears the word) if it was set. */
+GLLMK_API int32_t gllmk_ctx_status(gllmk_ctx ctx, int32_t *device_status);
+/* Tuning knobs, for experiments.  key: "gemv_ctas_per_sm" (resident CTAs per SM the decode grid is
+ * sized for; 0 = occupancy limit), "gemv_pdl" (1 = overlap the activation staging kernel with the
+ * weight stream). */
 GLLMK_API int32_t gllmk_ctx_set(gllmk_ctx ctx, const char *key, int64_t value);
 
 /* ---- weights: upload + repack, the inverse, and the bit-exact decode ----------------------- */
@@ -95,7 +100,7 @@ GLLMK_API int32_t gllmk_ctx_set(gllmk_ctx ctx, const char *key, int64_t value);
  *          form (17-byte blocks, scale first; src/quant.rs:427).  mx_block must be 32.
  *   `global_scale` is NVFP4's out-of-band per-tensor f32 (src/quant.rs:77-86); pass 1 otherwise.
  *   `src_on_device` != 0 means `blocks`/`scales` are device pointers (16-byte aligned).
- * Errors: INVALID_ARG (null, n<=0, k not a multiple of the block size / of 256 for FP4 formats),
+ * Errors: INVALID_ARG (null, n<=0, k not a multiple of the block size, or of 128 for MXFP4),
  * UNSUPPORTED (unknown type, mx_block != 32), OUT_OF_MEMORY, RUNTIME_ERROR. */
 GLLMK_API int32_t gllmk_weight_upload(gllmk_ctx ctx, int32_t quant_type, int64_t n, int64_t k, int32_t mx_block,
                             const void *blocks, const void *scales, float global_scale,

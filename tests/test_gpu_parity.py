@@ -178,16 +178,16 @@ def test_device_quantizers_match_oracle_bytes(gk, K, oracle, torch, fmt):
 
 
 # ---- GEMV ------------------------------------------------------------------------------------
-def gemv_case(gk, K, oracle, torch, fmt, n, k, m, seed, ref_layout=False, ksplit=0, row_scales=None):
+def gemv_case(gk, K, oracle, torch, fmt, n, k, m, seed, ref_layout=False, ctas_per_sm=0, row_scales=None):
     oid, blocks, _, _ = make(oracle, fmt, n, k, seed)
     rng = np.random.default_rng(seed + 1)
     x = rng.standard_normal((m, k)).astype(np.float32)
     w = K.upload(qt_of(gk, fmt), n, k, blocks)
-    K.set("gemv_ksplit", ksplit)
+    K.set("gemv_ctas_per_sm", ctas_per_sm)
     xin = torch.from_numpy(np.ascontiguousarray(x.T) if ref_layout else x).cuda()
     rs = None if row_scales is None else torch.from_numpy(row_scales).cuda()
     y = K.gemv(w, xin, ref_layout=ref_layout, row_scales=rs).cpu().numpy()
-    K.set("gemv_ksplit", 0)
+    K.set("gemv_ctas_per_sm", 0)
     ref = oracle.quant_matmul(blocks, np.ascontiguousarray(x.T), oid, n, m, k, threads=8)  # [n, m]
     if row_scales is not None:
         ref = ref * (row_scales.reshape(-1, 1) if row_scales.size > 1 else row_scales[0])
@@ -218,10 +218,12 @@ def test_gemv_ragged_shapes_both_layouts(gk, K, oracle, torch, fmt, n, k, m, ref
     assert gemv_case(gk, K, oracle, torch, fmt, n, k, m, seed=n + k + m, ref_layout=ref_layout) <= TOL
 
 
-@pytest.mark.parametrize("ksplit", [1, 2, 4, 8])
+@pytest.mark.parametrize("ctas_per_sm", [1, 2, 3])
 @pytest.mark.parametrize("fmt", ["q4k", "q8_0"])
-def test_gemv_every_ksplit(gk, K, oracle, torch, fmt, ksplit):
-    assert gemv_case(gk, K, oracle, torch, fmt, 272, 2048, 7, seed=77, ksplit=ksplit) <= TOL
+def test_gemv_stream_k_partitions(gk, K, oracle, torch, fmt, ctas_per_sm):
+    """Different grid sizes cut the (tile group, k-step) sequence at different places: row tiles are
+    completed by 1, 2 or 3 CTAs and the slot-ordered reduction must give the same parity."""
+    assert gemv_case(gk, K, oracle, torch, fmt, 5000, 4096, 3, seed=77, ctas_per_sm=ctas_per_sm) <= TOL
 
 
 def test_gemv_row_scales(gk, K, oracle, torch):
@@ -278,8 +280,10 @@ def test_gemv_linearity_at_config5_size(gk, K, oracle, torch):
     y = K.gemv(w, x)
     xc = (2.0 * x[0] + x[1]).reshape(1, k)
     yc = K.gemv(w, xc)
+    # activations enter as two int8 digits per 256-block (error <= amax * 1.6e-5 per element), so
+    # linearity holds to that precision, far inside the 2e-3 bar
     lin = (2.0 * y[0] + y[1] - yc[0]).abs().max().item() / yc.abs().max().item()
-    assert lin < 1e-5
+    assert lin < 2e-4
     rows = np.r_[0:16, 14000:14016, n - 16:n]
     hb = blocks.reshape(n, -1)[torch.from_numpy(rows).cuda()].cpu().numpy().reshape(-1)
     ref = oracle.quant_matmul(hb, np.ascontiguousarray(x.cpu().numpy().T), oracle.Q4K, rows.size, 2, k).T
