@@ -39,11 +39,12 @@ static int32_t grow(Ctx *c, void **p, size_t *have, size_t want, bool pinned) {
     return GLLMK_STATUS_OK;
 }
 int32_t ensure_ws(Ctx *c, size_t bytes) { return grow(c, &c->ws, &c->ws_bytes, bytes, false); }
-int32_t ensure_red(Ctx *c, size_t bytes) {
-    if (c->red_bytes >= bytes) return GLLMK_STATUS_OK;
-    int32_t rc = grow(c, &c->red, &c->red_bytes, bytes, false);
+int32_t ensure_red(Ctx *c, size_t bytes) { return grow(c, &c->red, &c->red_bytes, bytes, false); }
+int32_t ensure_cnt(Ctx *c, size_t bytes) {
+    if (c->cnt_bytes >= bytes) return GLLMK_STATUS_OK;
+    int32_t rc = grow(c, &c->cnt, &c->cnt_bytes, bytes, false);
     if (rc) return rc;
-    GK_CUDA(c, cudaMemset(c->red, 0, c->red_bytes));  // arrival counters start at zero and reset themselves
+    GK_CUDA(c, cudaMemset(c->cnt, 0, c->cnt_bytes));  // arrival counters start at zero and reset themselves
     return GLLMK_STATUS_OK;
 }
 int32_t ensure_pin(Ctx *c, size_t bytes) { return grow(c, &c->pin, &c->pin_bytes, bytes, true); }
@@ -224,6 +225,7 @@ void gllmk_ctx_free(gllmk_ctx ctx) {
     cudaDeviceSynchronize();
     if (c->ws) cudaFree(c->ws);
     if (c->red) cudaFree(c->red);
+    if (c->cnt) cudaFree(c->cnt);
     if (c->status_dev) cudaFree(c->status_dev);
     if (c->dev_io) cudaFree(c->dev_io);
     if (c->pin) cudaFreeHost(c->pin);

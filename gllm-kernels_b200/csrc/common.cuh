@@ -72,9 +72,11 @@ struct Ctx {
     void *ws = nullptr;
     size_t ws_bytes = 0;
     int64_t ws_k = -1;  // K the workspace is currently laid out (and zero-padded) for
-    // split-k partial sums + per-tile arrival counters (zeroed at allocation, self-resetting) + status word
+    // split-k partial sums; per-tile arrival counters (zeroed at allocation, self-resetting); status word
     void *red = nullptr;
     size_t red_bytes = 0;
+    void *cnt = nullptr;
+    size_t cnt_bytes = 0;
     int *status_dev = nullptr;
     // pinned host staging + device staging for the host-pointer entry points
     void *pin = nullptr;
@@ -90,6 +92,7 @@ int32_t fail(Ctx *c, int32_t code, const char *fmt, ...);
 int32_t cuda_fail(Ctx *c, cudaError_t e, const char *what);
 int32_t ensure_ws(Ctx *c, size_t bytes);
 int32_t ensure_red(Ctx *c, size_t bytes);
+int32_t ensure_cnt(Ctx *c, size_t bytes);
 int32_t ensure_pin(Ctx *c, size_t bytes);
 int32_t ensure_dev_io(Ctx *c, size_t bytes);
 

@@ -44,8 +44,10 @@ __global__ void __launch_bounds__(256) stage_x_kernel(StageParams p) {
     __shared__ float wmax[8];
     __shared__ int wbad[8];
     // Let the dependent GEMV grid start streaming weights now; it waits (griddepcontrol.wait) for
-    // this grid to finish before it touches the image.
+    // this grid to finish before it touches the image.  This grid is itself launched early: it may
+    // only read x and overwrite the image once everything before it in the stream has completed.
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
     const int tok = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t k0 = ((int64_t)blockIdx.x * 256 + threadIdx.x) * 4;
     const float *xr = p.x + (int64_t)tok * p.xst;
@@ -187,7 +189,8 @@ struct GemvParams {
     int nk;            // k-steps per row: Q4_K blocks of 256 / Q8_0 groups of 8 blocks
     int m;
     int64_t nsuper;    // tile groups * nk
-    int per_cta;       // super-chunks per CTA
+    int per_cta;       // super-chunks per CTA: the first `rem` CTAs own per_cta + 1, the others per_cta
+    int rem;
     int maxslot;       // partial-sum slots per tile
     float *partial;    // [tiles][maxslot][16 tokens][16 rows]
     int *counters;     // [tiles] arrivals, zero between launches
@@ -350,6 +353,15 @@ __device__ __noinline__ void gemv_flush(const GemvParams &p, int tile, int slot,
     }
 }
 
+// Balanced partition of the super-chunk sequence: CTA c owns [cta_first(c), cta_first(c + 1)).
+__device__ __forceinline__ int64_t cta_first(const GemvParams &p, int c) {
+    return (int64_t)c * p.per_cta + min(c, p.rem);
+}
+__device__ __forceinline__ int cta_of(const GemvParams &p, int64_t sc) {
+    const int64_t big = (int64_t)p.rem * (p.per_cta + 1);
+    return sc < big ? (int)(sc / (p.per_cta + 1)) : p.rem + (int)((sc - big) / p.per_cta);
+}
+
 // Stream-k over the flattened (tile group, k-step) sequence of super-chunks (8 row tiles x one k-step,
 // contiguous in memory): CTA c owns super-chunks [c*per_cta, (c+1)*per_cta), one contiguous byte range.
 // Thread 0 is the producer: per step it issues two bulk copies (the super-chunk and the activation slice
@@ -367,8 +379,11 @@ __global__ void __launch_bounds__(256) gemv_kernel(const __grid_constant__ GemvP
     const uint32_t zero_s = smem_s + GEMV_STAGES * stage_bytes;
     const uint32_t full = zero_s + GEMV_ZERO, empty = full + GEMV_STAGES * 8;
 
-    const int per_cta = p.per_cta, nk = p.nk;
-    const int64_t sc0 = min(p.nsuper, (int64_t)blockIdx.x * per_cta), sc1 = min(p.nsuper, sc0 + per_cta);
+    // Whatever follows in the stream (the next call's staging kernel, then its GEMV grid) may be
+    // scheduled as this grid's CTAs retire; it orders itself after this grid with griddepcontrol.wait.
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    const int nk = p.nk;
+    const int64_t sc0 = cta_first(p, (int)blockIdx.x), sc1 = cta_first(p, (int)blockIdx.x + 1);
     const int n = (int)(sc1 - sc0);
     const uint8_t *wsrc = p.chunks + (size_t)sc0 * SUPER;
     int TG = (int)(sc0 / nk), b = (int)(sc0 % nk);
@@ -461,7 +476,7 @@ __global__ void __launch_bounds__(256) gemv_kernel(const __grid_constant__ GemvP
         }
         // ---- this CTA's share of tile group TG is complete; each warp finishes its own tile ----
         const int64_t first = (int64_t)TG * nk, last = first + nk - 1;
-        const int slot0 = (int)(first / per_cta), nsl = (int)(last / per_cta) - slot0 + 1;
+        const int slot0 = cta_of(p, first), nsl = cta_of(p, last) - slot0 + 1;
         float v[NT][2];
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) {
@@ -490,9 +505,8 @@ size_t gemv_ws_bytes(const Weight *w, int m) {
     return align_up(nk * slice_bytes(m), 256);
 }
 
-template <typename Kern>
-static cudaError_t launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t s, bool pdl,
-                              const GemvParams &p) {
+template <typename Kern, typename Params>
+static cudaError_t launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t s, bool pdl, const Params &p) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -506,29 +520,47 @@ static cudaError_t launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, cud
     return cudaLaunchKernelEx(&cfg, kern, p);
 }
 
+// Resident CTAs per SM for (format, n-tiles, m): set up once per device, then cached.
+template <int FMT, int NT>
+static cudaError_t gemv_occupancy(int device, int m, size_t smem, int *per_sm) {
+    static int cache[16][GLLMK_GEMV_MAX_M + 1];  // [device][m], 0 = not yet queried
+    if (device >= 0 && device < 16 && cache[device][m]) {
+        *per_sm = cache[device][m];
+        return cudaSuccess;
+    }
+    cudaError_t e = cudaFuncSetAttribute(gemv_kernel<FMT, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)gemv_smem_bytes<FMT>(GLLMK_GEMV_MAX_M));
+    if (e != cudaSuccess) return e;
+    int n = 0;
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, gemv_kernel<FMT, NT>, 256, smem);
+    if (e != cudaSuccess) return e;
+    if (n < 1) n = 1;
+    if (device >= 0 && device < 16) cache[device][m] = n;
+    *per_sm = n;
+    return cudaSuccess;
+}
+
 template <int FMT, int NT>
 static cudaError_t configure_and_launch(Ctx *c, GemvParams &p, int64_t ntg, cudaStream_t s, int32_t *rc_out) {
     const size_t smem = gemv_smem_bytes<FMT>(p.m);
-    cudaError_t e = cudaFuncSetAttribute(gemv_kernel<FMT, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
     int per_sm = 0;
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemv_kernel<FMT, NT>, 256, smem);
+    cudaError_t e = gemv_occupancy<FMT, NT>(c->device, p.m, smem, &per_sm);
     if (e != cudaSuccess) return e;
-    if (per_sm < 1) per_sm = 1;
     if (c->gemv_ctas_per_sm > 0 && c->gemv_ctas_per_sm < per_sm) per_sm = (int)c->gemv_ctas_per_sm;
     p.nsuper = ntg * p.nk;
-    const int64_t ctas = (int64_t)c->sm_count * per_sm;
-    p.per_cta = (int)((p.nsuper + ctas - 1) / ctas);
-    if (p.per_cta < 1) p.per_cta = 1;
-    const unsigned grid = (unsigned)((p.nsuper + p.per_cta - 1) / p.per_cta);
+    int64_t ctas = (int64_t)c->sm_count * per_sm;
+    if (ctas > p.nsuper) ctas = p.nsuper;
+    p.per_cta = (int)(p.nsuper / ctas);
+    p.rem = (int)(p.nsuper % ctas);
+    const unsigned grid = (unsigned)ctas;
     p.maxslot = (p.nk - 1) / p.per_cta + 2;
     const int64_t tiles = ntg * 8;
     const size_t part_bytes = align_up((size_t)tiles * p.maxslot * 256 * sizeof(float), 256);
-    *rc_out = ensure_red(c, part_bytes + (size_t)tiles * sizeof(int));
+    *rc_out = ensure_red(c, part_bytes);
+    if (!*rc_out) *rc_out = ensure_cnt(c, (size_t)tiles * sizeof(int));
     if (*rc_out) return cudaSuccess;
     p.partial = static_cast<float *>(c->red);
-    // counters live at the end of the buffer so a larger partial area never overlaps live counters
-    p.counters = reinterpret_cast<int *>(static_cast<char *>(c->red) + c->red_bytes) - tiles;
+    p.counters = static_cast<int *>(c->cnt);
     return launch_pdl(gemv_kernel<FMT, NT>, grid, 256, smem, s, c->gemv_pdl != 0, p);
 }
 
@@ -555,8 +587,14 @@ int32_t gemv_launch(Ctx *c, const Weight *w, const float *x, int64_t xst, int64_
 
     StageParams sp{x, xst, xsk, m, w->k, static_cast<uint8_t *>(c->ws)};
     dim3 sgrid((unsigned)(((size_t)nk * 256 + 1023) / 1024), (unsigned)m);
-    stage_x_kernel<<<sgrid, 256, 0, s>>>(sp);
-    GK_CUDA(c, cudaGetLastError());
+    static bool stage_carveout_set = false;
+    if (!stage_carveout_set) {
+        // same shared-memory carve-out as the GEMV grid that follows, so the SMs are not reconfigured in between
+        (void)cudaFuncSetAttribute(stage_x_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+        (void)cudaGetLastError();
+        stage_carveout_set = true;
+    }
+    GK_CUDA(c, launch_pdl(stage_x_kernel, sgrid, 256, 0, s, c->gemv_pdl != 0, sp));
 
     const int64_t ntg = w->n_pad / 128;
     const int NT = (2 * m + 7) / 8;
