@@ -69,7 +69,9 @@ _SIGS = {
     "gllmk_quantize": (_i32, [_vp, _i32, _vp, _i64, _i64, _i32, _vp, _vp, C.POINTER(_f32), _vp]),
 }
 # Entry points added after the first release of the header are listed here as they land.
-_OPTIONAL_SIGS: dict = {}
+_OPTIONAL_SIGS: dict = {
+    "gllmk_gemv_static": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _vp, _i64, _i64, _vp, _i64, _vp]),
+}
 
 _lib = None
 

@@ -620,4 +620,139 @@ int32_t gemv_launch(Ctx *c, const Weight *w, const float *x, int64_t xst, int64_
     return GLLMK_STATUS_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Decode GEMV for callers that must not allocate.
+//
+// Some hosts of this library run their decode step where device allocation is off limits: inside a
+// latency-critical serving loop that has pre-reserved all of HBM for weights and KV pages, under an
+// allocator that owns the whole device, or in a callback where cudaMalloc's implicit synchronisation
+// is not acceptable.  gllmk_gemv grows context-owned buffers on demand; this variant never does.  All of
+// the kernel's scratch (activation image, split-k partial sums, arrival counters, status word) lives in
+// one fixed array inside the library image, so every GPU that loads the library holds these 8 MiB until
+// the process exits.
+// ---------------------------------------------------------------------------------------------
+constexpr size_t GEMV_STATIC_BYTES = (size_t)8 << 20;
+constexpr size_t GEMV_STATIC_MAX_TILES = 8192;  // counters area: rows up to 131072
+static __device__ __align__(256) unsigned char g_gemv_static_scratch[GEMV_STATIC_BYTES];
+
+// The array's name is only a host-side handle; the device address comes from cudaGetSymbolAddress,
+// looked up once per device with that device current.
+static cudaError_t gemv_static_base(int device, unsigned char **base) {
+    static unsigned char *cached[16] = {};
+    if (device < 0 || device >= 16) return cudaErrorInvalidDevice;
+    if (!cached[device]) {
+        void *ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&ptr, g_gemv_static_scratch);
+        if (e != cudaSuccess) return e;
+        cached[device] = static_cast<unsigned char *>(ptr);
+    }
+    *base = cached[device];
+    return cudaSuccess;
+}
+
+template <int FMT, int NT>
+static cudaError_t launch_static(Ctx *c, GemvParams &p, int64_t ntg, unsigned char *base, size_t img_bytes,
+                                 cudaStream_t s, int32_t *rc_out) {
+    const size_t smem = gemv_smem_bytes<FMT>(p.m);
+    int per_sm = 0;
+    cudaError_t e = gemv_occupancy<FMT, NT>(c->device, p.m, smem, &per_sm);
+    if (e != cudaSuccess) return e;
+    if (c->gemv_ctas_per_sm > 0 && c->gemv_ctas_per_sm < per_sm) per_sm = (int)c->gemv_ctas_per_sm;
+    p.nsuper = ntg * p.nk;
+    int64_t ctas = (int64_t)c->sm_count * per_sm;
+    if (ctas > p.nsuper) ctas = p.nsuper;
+    p.per_cta = (int)(p.nsuper / ctas);
+    p.rem = (int)(p.nsuper % ctas);
+    p.maxslot = (p.nk - 1) / p.per_cta + 2;
+    const size_t tiles = (size_t)ntg * 8;
+    // layout: status word [256] | counters [GEMV_STATIC_MAX_TILES ints] | activation image | partial sums
+    const size_t cnt_off = 256, img_off = cnt_off + GEMV_STATIC_MAX_TILES * sizeof(int);
+    const size_t part_off = align_up(img_off + img_bytes, 256);
+    const size_t part_bytes = tiles * (size_t)p.maxslot * 256 * sizeof(float);
+    if (tiles > GEMV_STATIC_MAX_TILES || part_off + part_bytes > GEMV_STATIC_BYTES) {
+        *rc_out = fail(c, GLLMK_STATUS_INVALID_ARG,
+                       "gemv_static: this shape needs %zu bytes of scratch (%zu row tiles), the built-in area holds %zu "
+                       "bytes (%zu row tiles); use gllmk_gemv",
+                       part_off + part_bytes, tiles, GEMV_STATIC_BYTES, GEMV_STATIC_MAX_TILES);
+        return cudaSuccess;
+    }
+    p.status = reinterpret_cast<int *>(base);
+    p.counters = reinterpret_cast<int *>(base + cnt_off);
+    p.img = base + img_off;
+    p.partial = reinterpret_cast<float *>(base + part_off);
+    // The area keeps whatever the previous call left: the counters must start at zero (a call that gave up
+    // a bounded wait may have left some non-zero).  Stream-ordered, no allocation.
+    e = cudaMemsetAsync(p.counters, 0, tiles * sizeof(int), s);
+    if (e != cudaSuccess) return e;
+    return launch_pdl(gemv_kernel<FMT, NT>, (unsigned)ctas, 256, smem, s, false, p);
+}
+
 }  // namespace gllmk
+
+using namespace gllmk;
+
+extern "C" int32_t gllmk_gemv_static(gllmk_ctx ctx, gllmk_weight wh, const float *x_dev, int64_t x_stride_t,
+                                     int64_t x_stride_k, int32_t m, float *y_dev, int64_t y_stride_t, int64_t y_stride_r,
+                                     const float *row_scales, int64_t n_row_scales, void *stream) {
+    if (!ctx || !wh || !x_dev || !y_dev) return GLLMK_STATUS_INVALID_ARG;
+    Ctx *c = static_cast<Ctx *>(ctx);
+    const Weight *w = static_cast<const Weight *>(wh);
+    if (m < 1 || m > GLLMK_GEMV_MAX_M)
+        return fail(c, GLLMK_STATUS_INVALID_ARG, "gemv_static: m=%d outside 1..%d", m, GLLMK_GEMV_MAX_M);
+    if (w->qt != GLLMK_QUANT_Q4K && w->qt != GLLMK_QUANT_Q8_0)
+        return fail(c, GLLMK_STATUS_UNSUPPORTED, "gemv_static: quant type %d has no decode kernel", w->qt);
+    if (w->device != c->device) return fail(c, GLLMK_STATUS_INVALID_ARG, "weight lives on another device");
+    if (row_scales && n_row_scales != 1 && n_row_scales != w->n) { row_scales = nullptr; n_row_scales = 0; }
+    int prev = -1;
+    GK_CUDA(c, cudaGetDevice(&prev));
+    if (prev != c->device) GK_CUDA(c, cudaSetDevice(c->device));
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    unsigned char *base = nullptr;
+    cudaError_t e = gemv_static_base(c->device, &base);  // first call on a device: symbol address look-up
+    int32_t rc = GLLMK_STATUS_OK;
+    if (e == cudaSuccess) {
+        const int nk = (int)((w->k + 255) / 256);
+        const size_t img_bytes = align_up((size_t)nk * slice_bytes(m), 256);
+        GemvParams p{};
+        p.chunks = static_cast<const uint8_t *>(w->qs);
+        p.y = y_dev;
+        p.yst = y_stride_t;
+        p.ysr = y_stride_r;
+        p.row_scales = row_scales;
+        p.n_row_scales = row_scales ? n_row_scales : 0;
+        p.n = w->n;
+        p.nk = nk;
+        p.m = m;
+        const size_t img_off = 256 + GEMV_STATIC_MAX_TILES * sizeof(int);
+        if (img_off + img_bytes > GEMV_STATIC_BYTES) {
+            rc = fail(c, GLLMK_STATUS_INVALID_ARG, "gemv_static: k=%lld with m=%d needs a %zu-byte activation image, "
+                      "more than the built-in %zu-byte area; use gllmk_gemv", (long long)w->k, m, img_bytes, GEMV_STATIC_BYTES);
+        } else {
+            StageParams sp{x_dev, x_stride_t, x_stride_k, m, w->k, base + img_off};
+            dim3 sgrid((unsigned)(((size_t)nk * 256 + 1023) / 1024), (unsigned)m);
+            e = launch_pdl(stage_x_kernel, sgrid, 256, 0, s, false, sp);
+            const int64_t ntg = w->n_pad / 128;
+            const int NT = (2 * m + 7) / 8;
+            if (e == cudaSuccess) {
+                if (w->qt == GLLMK_QUANT_Q4K) {
+                    switch (NT) {
+                        case 1: e = launch_static<FMT_Q4K, 1>(c, p, ntg, base, img_bytes, s, &rc); break;
+                        case 2: e = launch_static<FMT_Q4K, 2>(c, p, ntg, base, img_bytes, s, &rc); break;
+                        case 3: e = launch_static<FMT_Q4K, 3>(c, p, ntg, base, img_bytes, s, &rc); break;
+                        default: e = launch_static<FMT_Q4K, 4>(c, p, ntg, base, img_bytes, s, &rc); break;
+                    }
+                } else {
+                    switch (NT) {
+                        case 1: e = launch_static<FMT_Q80, 1>(c, p, ntg, base, img_bytes, s, &rc); break;
+                        case 2: e = launch_static<FMT_Q80, 2>(c, p, ntg, base, img_bytes, s, &rc); break;
+                        case 3: e = launch_static<FMT_Q80, 3>(c, p, ntg, base, img_bytes, s, &rc); break;
+                        default: e = launch_static<FMT_Q80, 4>(c, p, ntg, base, img_bytes, s, &rc); break;
+                    }
+                }
+            }
+        }
+    }
+    if (prev != c->device) cudaSetDevice(prev);
+    if (e != cudaSuccess) return cuda_fail(c, e, "gemv_static");
+    return rc;
+}

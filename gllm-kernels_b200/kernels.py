@@ -168,6 +168,18 @@ class GpuKernels:
         self._check(rc, "gllmk_gemv")
         return y
 
+    def gemv_static(self, w: Weight, x, y, ref_layout: bool = False, row_scales=None, stream=None):
+        """gemv for callers that may not allocate device memory: scratch is a fixed 8 MiB area inside the
+        library (shared by every call on the device — do not overlap calls).  `y` must be preallocated.
+        Raises INVALID_ARG for shapes whose scratch does not fit."""
+        m = x.shape[1] if ref_layout else x.shape[0]
+        xs, ys = ((1, m), (1, m)) if ref_layout else ((w.k, 1), (w.n, 1))
+        ns = 0 if row_scales is None else row_scales.numel()
+        rc = lib().gllmk_gemv_static(self._ctx, w._h, _ptr(x), xs[0], xs[1], m, _ptr(y), ys[0], ys[1],
+                                     _ptr(row_scales), ns, _stream(stream))
+        self._check(rc, "gllmk_gemv_static")
+        return y
+
     def matmul_host(self, w: Weight, x, ref_layout: bool = False) -> np.ndarray:
         """Resident weight, HOST activations and outputs (numpy): the call timed end to end."""
         x = _np(x, np.float32)

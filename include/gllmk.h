@@ -134,6 +134,26 @@ GLLMK_API int32_t gllmk_gemv(gllmk_ctx ctx, gllmk_weight w, const float *x_dev, 
                    int32_t m, float *y_dev, int64_t y_stride_t, int64_t y_stride_r, const float *row_scales,
                    int64_t n_row_scales, void *stream);
 
+/* Same product as gllmk_gemv for callers that are not allowed to allocate device memory while they run:
+ * a serving loop whose allocator has already claimed all of HBM for weights and KV pages, code running
+ * under a pool allocator that owns the device, or a latency-critical section where cudaMalloc's implicit
+ * device synchronisation is unacceptable.  This entry point has no counterpart in the reference (its CPU
+ * path keeps scratch in a thread_local Vec).  It calls no cudaMalloc / cudaFree and no allocating library
+ * routine: the activation image, the split-k partial sums, the arrival counters and the status word all
+ * live in one 8 MiB array compiled into the library, which every GPU that loads the library holds until the
+ * process exits.
+ *   - Shapes whose scratch does not fit (more than 8192 row tiles = 131072 rows, or image + partial sums
+ *     over 8 MiB; the message gives the byte count) are rejected with INVALID_ARG: use gllmk_gemv there.
+ *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress); make that
+ *     first call before any stream capture begins.
+ *   - All calls on a device share the array, whatever context they use.  Calls that overlap in time on
+ *     the GPU (different streams, different contexts) race on it; serialise them.  The array keeps the
+ *     previous call's contents; the part that must start at zero is cleared on the caller's stream.
+ * Arguments, results and accuracy are those of gllmk_gemv (the same kernels run). */
+GLLMK_API int32_t gllmk_gemv_static(gllmk_ctx ctx, gllmk_weight w, const float *x_dev, int64_t x_stride_t,
+                                    int64_t x_stride_k, int32_t m, float *y_dev, int64_t y_stride_t,
+                                    int64_t y_stride_r, const float *row_scales, int64_t n_row_scales, void *stream);
+
 /* ---- host-pointer drop-ins of the reference operator API ----------------------------------- */
 
 /* Kernels::kquant_matmul(weight_blocks, input, output, QuantType::Q4K, m, n, k) and
