@@ -350,6 +350,21 @@ int32_t gllmk_gemv(gllmk_ctx ctx, gllmk_weight wh, const float *x_dev, int64_t x
                        static_cast<cudaStream_t>(stream));
 }
 
+int32_t gllmk_gemm(gllmk_ctx ctx, gllmk_weight wh, const void *a_dev, int32_t a_dtype, int64_t lda, int32_t m, void *y_dev,
+                   int32_t y_dtype, int64_t ldy, void *stream) {
+    if (!ctx || !wh || !a_dev || !y_dev) return GLLMK_STATUS_INVALID_ARG;
+    Ctx *c = static_cast<Ctx *>(ctx);
+    const Weight *w = static_cast<const Weight *>(wh);
+    if (m < 1) return fail(c, GLLMK_STATUS_INVALID_ARG, "gemm: m must be positive");
+    if ((a_dtype != GLLMK_DTYPE_F32 && a_dtype != GLLMK_DTYPE_BF16) || (y_dtype != GLLMK_DTYPE_F32 && y_dtype != GLLMK_DTYPE_BF16))
+        return fail(c, GLLMK_STATUS_UNSUPPORTED, "gemm: dtype must be f32 or bf16");
+    if (lda < w->k || ldy < w->n) return fail(c, GLLMK_STATUS_INVALID_ARG, "gemm: leading dimension smaller than the row");
+    if (w->device != c->device) return fail(c, GLLMK_STATUS_INVALID_ARG, "weight lives on another device");
+    DeviceGuard g(c->device);
+    return gemm_launch(c, w, a_dev, a_dtype == GLLMK_DTYPE_BF16, lda, m, y_dev, y_dtype == GLLMK_DTYPE_BF16, ldy,
+                       static_cast<cudaStream_t>(stream));
+}
+
 // Shared body of the host-pointer matmuls: weight rows n_w, tokens m_t, reduction k.
 //   ref_layout: input [k, m_t], output [n_w, m_t]; else input [m_t, k], output [m_t, n_w].
 static int32_t matmul_host_impl(Ctx *c, const Weight *w, const float *x_host, int m_t, float *y_host, bool ref_layout,

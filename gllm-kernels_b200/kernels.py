@@ -168,6 +168,18 @@ class GpuKernels:
         self._check(rc, "gllmk_gemv")
         return y
 
+    def gemm(self, w: Weight, a, y=None, out_dtype=None, stream=None):
+        """Prefill product with device tensors: a [m, k] (f32 or bf16, row-major) -> y [m, n] (f32 or bf16)."""
+        import torch
+        m = a.shape[0]
+        if y is None:
+            y = torch.empty((m, w.n), dtype=out_dtype or torch.float32, device=a.device)
+        dt = {torch.float32: 0, torch.bfloat16: 1}
+        rc = lib().gllmk_gemm(self._ctx, w._h, _ptr(a), dt[a.dtype], a.stride(0), m, _ptr(y), dt[y.dtype], y.stride(0),
+                              _stream(stream))
+        self._check(rc, "gllmk_gemm")
+        return y
+
     def gemv_static(self, w: Weight, x, y, ref_layout: bool = False, row_scales=None, stream=None):
         """gemv for callers that may not allocate device memory: scratch is a fixed 8 MiB area inside the
         library (shared by every call on the device — do not overlap calls).  `y` must be preallocated.

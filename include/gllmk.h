@@ -134,6 +134,18 @@ GLLMK_API int32_t gllmk_gemv(gllmk_ctx ctx, gllmk_weight w, const float *x_dev, 
                    int32_t m, float *y_dev, int64_t y_stride_t, int64_t y_stride_r, const float *row_scales,
                    int64_t n_row_scales, void *stream);
 
+/* ---- prefill: fused dequantize + GEMM on tcgen05 tensor cores (any M) --------------------------- */
+
+/* Kernels::gemm_q4 / kquant_matmul / classic_matmul for large batches, and the matmul the reference
+ * leaves unimplemented for MXFP4 / NVFP4 weights (src/cpu_kernels/mod.rs:3347-3348; oracle = its dequant
+ * followed by scalar_gemm, scalar-ops/src/blas.rs:116-135), on device memory with resident weights:
+ *   y[t, r] = sum_k W[r, k] * a[t, k],  a [m, k] row-major (leading dimension lda), y [m, n] (ldy).
+ * a_dtype / y_dtype: GLLMK_DTYPE_F32 or GLLMK_DTYPE_BF16.  Weights and activations are staged in bf16
+ * and accumulated in f32 (results within 1e-2 of the reference's f32 evaluation).  k must be a multiple
+ * of 64; a and its rows 16-byte aligned. */
+GLLMK_API int32_t gllmk_gemm(gllmk_ctx ctx, gllmk_weight w, const void *a_dev, int32_t a_dtype, int64_t lda, int32_t m,
+                             void *y_dev, int32_t y_dtype, int64_t ldy, void *stream);
+
 /* Same product as gllmk_gemv for callers that are not allowed to allocate device memory while they run:
  * a serving loop whose allocator has already claimed all of HBM for weights and KV pages, code running
  * under a pool allocator that owns the device, or a latency-critical section where cudaMalloc's implicit

@@ -1,0 +1,82 @@
+"""Prefill GEMM (tcgen05) against the CPU oracle: decode of the packed bytes (reference formulas) followed by
+the reference's f32 GEMM loop order.  Bar: max_i |y_i - ref_i| / max(|ref_i|, rms(ref)) <= 1e-2 (weights and
+activations are staged in bf16, accumulation is f32)."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2
+
+
+@pytest.fixture(scope="module")
+def K(gk):
+    k = gk.GpuKernels(0)
+    yield k
+    k.close()
+
+
+def quantized(oracle, gk, fmt, n, k, seed):
+    rng = np.random.default_rng(seed)
+    W = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    if fmt == "q4k":
+        b = oracle.quantize_q4_k(W)
+        return gk.QuantType.q4k(), b, None, 1.0, oracle.dequant_matrix(oracle.Q4K, b, n, k)
+    if fmt == "q8_0":
+        b = oracle.quantize_q8_0(W)
+        return gk.QuantType.q8_0(), b, None, 1.0, oracle.dequant_matrix(oracle.Q8_0, b, n, k)
+    if fmt == "mxfp4":
+        b, s = oracle.quantize_mxfp4(W)
+        return gk.QuantType.mxfp4(32), b, s, 1.0, oracle.dequant_matrix(oracle.MXFP4, b, n, k, scales=s)
+    b, g = oracle.quantize_nvfp4(W)
+    return gk.QuantType.nvfp4(), b, None, g, oracle.dequant_matrix(oracle.NVFP4, b, n, k, global_scale=g)
+
+
+def run_case(gk, K, oracle, fmt, n, k, m, seed, a_bf16=False, y_bf16=False):
+    import torch
+    qt, blocks, scales, g, wd = quantized(oracle, gk, fmt, n, k, seed)
+    w = K.upload(qt, n, k, blocks, scales, g)
+    x = np.random.default_rng(seed + 1).standard_normal((m, k)).astype(np.float32)
+    xd = torch.from_numpy(x).cuda()
+    if a_bf16:
+        xd = xd.to(torch.bfloat16)
+        x = xd.to(torch.float32).cpu().numpy()
+    y = K.gemm(w, xd, out_dtype=torch.bfloat16 if y_bf16 else torch.float32)
+    torch.cuda.synchronize()
+    assert K.status() == 0
+    ref = oracle.gemm_f32_nt(x, wd) if m * n * k <= 2_000_000_000 else (x.astype(np.float64) @ wd.T.astype(np.float64))
+    err = oracle.rel_err(y.to(torch.float32).cpu().numpy(), ref)
+    w.free()
+    return err
+
+
+def test_gemm_single_tile_single_stage(gk, K, oracle):
+    assert run_case(gk, K, oracle, "q8_0", 128, 64, 32, seed=1) <= TOL
+
+
+def test_gemm_single_tile_pipeline_wraps(gk, K, oracle):
+    assert run_case(gk, K, oracle, "q8_0", 128, 1024, 64, seed=2) <= TOL
+
+
+@pytest.mark.parametrize("fmt", ["q4k", "q8_0", "mxfp4", "nvfp4"])
+def test_gemm_formats(gk, K, oracle, fmt):
+    assert run_case(gk, K, oracle, fmt, 384, 512, 256, seed=3) <= TOL
+
+
+@pytest.mark.parametrize("fmt,n,k,m", [("q4k", 100, 256, 17), ("q4k", 300, 1280, 300), ("q8_0", 129, 192, 33),
+                                       ("mxfp4", 200, 384, 513), ("nvfp4", 77, 448, 40)])
+def test_gemm_ragged_shapes(gk, K, oracle, fmt, n, k, m):
+    assert run_case(gk, K, oracle, fmt, n, k, m, seed=n + m) <= TOL
+
+
+def test_gemm_bf16_in_bf16_out(gk, K, oracle):
+    assert run_case(gk, K, oracle, "q4k", 256, 512, 96, seed=9, a_bf16=True, y_bf16=True) <= 1.5e-2
+
+
+def test_gemm_rejects_bad_arguments(gk, K, oracle):
+    import torch
+    qt, blocks, _, _, _ = quantized(oracle, gk, "q8_0", 16, 96, 5)
+    w = K.upload(qt, 16, 96, blocks)
+    with pytest.raises(gk.GllmkError) as e:  # k % 64 != 0
+        K.gemm(w, torch.zeros((32, 96), device="cuda"))
+    assert e.value.status == gk.Status.INVALID_ARG
+    w.free()
