@@ -59,6 +59,7 @@ _SIGS = {
     "gllmk_dequant": (_i32, [_vp, _vp, _vp, _vp]),
     "gllmk_gemv": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _vp, _i64, _i64, _vp, _i64, _vp]),
     "gllmk_gemm": (_i32, [_vp, _vp, _vp, _i32, _i64, _i32, _vp, _i32, _i64, _vp]),
+    "gllmk_gemm_fp4": (_i32, [_vp, _vp, _vp, _vp, _i32, _i64, _vp]),
     "gllmk_kquant_matmul_f32": (_i32, [_vp, _vp, _vp, _vp, _i32, _sz, _sz, _sz]),
     "gllmk_classic_matmul_f32": (_i32, [_vp, _vp, _vp, _vp, _i32, _sz, _sz, _sz]),
     "gllmk_gemm_q4_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz]),

@@ -365,6 +365,17 @@ int32_t gllmk_gemm(gllmk_ctx ctx, gllmk_weight wh, const void *a_dev, int32_t a_
                        static_cast<cudaStream_t>(stream));
 }
 
+int32_t gllmk_gemm_fp4(gllmk_ctx ctx, gllmk_weight wh, gllmk_weight xh, void *y_dev, int32_t y_dtype, int64_t ldy, void *stream) {
+    if (!ctx || !wh || !xh || !y_dev) return GLLMK_STATUS_INVALID_ARG;
+    Ctx *c = static_cast<Ctx *>(ctx);
+    const Weight *w = static_cast<const Weight *>(wh), *x = static_cast<const Weight *>(xh);
+    if (y_dtype != GLLMK_DTYPE_F32 && y_dtype != GLLMK_DTYPE_BF16) return fail(c, GLLMK_STATUS_UNSUPPORTED, "gemm_fp4: y dtype");
+    if (ldy < w->n) return fail(c, GLLMK_STATUS_INVALID_ARG, "gemm_fp4: ldy smaller than n");
+    if (w->device != c->device || x->device != c->device) return fail(c, GLLMK_STATUS_INVALID_ARG, "operand lives on another device");
+    DeviceGuard g(c->device);
+    return gemm_fp4_launch(c, w, x, y_dev, y_dtype == GLLMK_DTYPE_BF16, ldy, static_cast<cudaStream_t>(stream));
+}
+
 // Shared body of the host-pointer matmuls: weight rows n_w, tokens m_t, reduction k.
 //   ref_layout: input [k, m_t], output [n_w, m_t]; else input [m_t, k], output [m_t, n_w].
 static int32_t matmul_host_impl(Ctx *c, const Weight *w, const float *x_host, int m_t, float *y_host, bool ref_layout,

@@ -115,6 +115,8 @@ size_t gemv_ws_bytes(const Weight *w, int m);
 // ---- gemm.cu ----
 int32_t gemm_launch(Ctx *c, const Weight *w, const void *a, int a_bf16, int64_t lda, int m, void *y, int y_bf16, int64_t ldy,
                     cudaStream_t s);
+// ---- gemm_fp4.cu ----
+int32_t gemm_fp4_launch(Ctx *c, const Weight *w, const Weight *x, void *y, int y_bf16, int64_t ldy, cudaStream_t s);
 // ---- quantize.cu ----
 int32_t quantize_launch(Ctx *c, int32_t qt, const float *x, int64_t rows, int64_t k, int mx_block, void *blocks,
                         void *scales, float *global_scale, cudaStream_t s);

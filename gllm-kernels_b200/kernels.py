@@ -180,6 +180,16 @@ class GpuKernels:
         self._check(rc, "gllmk_gemm")
         return y
 
+    def gemm_fp4(self, w: Weight, x: Weight, y=None, out_dtype=None, stream=None):
+        """Native FP4 x FP4 product: `x` is the activation matrix [m, k] quantized and uploaded like a weight."""
+        import torch
+        if y is None:
+            y = torch.empty((x.n, w.n), dtype=out_dtype or torch.float32, device=f"cuda:{self.device}")
+        dt = {torch.float32: 0, torch.bfloat16: 1}
+        rc = lib().gllmk_gemm_fp4(self._ctx, w._h, x._h, _ptr(y), dt[y.dtype], y.stride(0), _stream(stream))
+        self._check(rc, "gllmk_gemm_fp4")
+        return y
+
     def gemv_static(self, w: Weight, x, y, ref_layout: bool = False, row_scales=None, stream=None):
         """gemv for callers that may not allocate device memory: scratch is a fixed 8 MiB area inside the
         library (shared by every call on the device — do not overlap calls).  `y` must be preallocated.

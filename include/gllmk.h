@@ -146,6 +146,16 @@ GLLMK_API int32_t gllmk_gemv(gllmk_ctx ctx, gllmk_weight w, const float *x_dev, 
 GLLMK_API int32_t gllmk_gemm(gllmk_ctx ctx, gllmk_weight w, const void *a_dev, int32_t a_dtype, int64_t lda, int32_t m,
                              void *y_dev, int32_t y_dtype, int64_t ldy, void *stream);
 
+/* Both operands in FP4 (config "NVFP4 prefill GEMM": weights and activations quantized the same way;
+ * the reference declares the format, src/quant.rs:357-371, and a native-FP4 capability,
+ * DotProductCap::NativeFp4 / Tcgen05Fp4 in src/quant_format.rs:1007-1027, but ships no kernel).
+ * `x` is the activation matrix [m, k] quantized with gllmk_quantize and uploaded with
+ * gllmk_weight_upload like a weight (same type as `w`, NVFP4 or MXFP4; k a multiple of 256).
+ *   y[t, r] = gW * gX * sum_k W4[r, k] * X4[t, k]   -> y [m, n] row-major (ldy), f32 or bf16.
+ * Products of the decoded FP4 values and their block scales are exact; accumulation is f32. */
+GLLMK_API int32_t gllmk_gemm_fp4(gllmk_ctx ctx, gllmk_weight w, gllmk_weight x, void *y_dev, int32_t y_dtype, int64_t ldy,
+                                 void *stream);
+
 /* Same product as gllmk_gemv for callers that are not allowed to allocate device memory while they run:
  * a serving loop whose allocator has already claimed all of HBM for weights and KV pages, code running
  * under a pool allocator that owns the device, or a latency-critical section where cudaMalloc's implicit

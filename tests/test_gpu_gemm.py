@@ -80,3 +80,51 @@ def test_gemm_rejects_bad_arguments(gk, K, oracle):
         K.gemm(w, torch.zeros((32, 96), device="cuda"))
     assert e.value.status == gk.Status.INVALID_ARG
     w.free()
+
+
+# ---- both operands FP4: native block-scaled MMA ---------------------------------------------------
+def run_fp4_case(gk, K, oracle, fmt, n, k, m, seed):
+    import torch
+    rng = np.random.default_rng(seed)
+    W = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    X = rng.standard_normal((m, k)).astype(np.float32)
+    if fmt == "nvfp4":
+        qt = gk.QuantType.nvfp4()
+        wb, gw = oracle.quantize_nvfp4(W)
+        xb, gx = oracle.quantize_nvfp4(X)
+        wd = oracle.dequant_matrix(oracle.NVFP4, wb, n, k, global_scale=gw)
+        xd = oracle.dequant_matrix(oracle.NVFP4, xb, m, k, global_scale=gx)
+        w, x = K.upload(qt, n, k, wb, None, gw), K.upload(qt, m, k, xb, None, gx)
+    else:
+        qt = gk.QuantType.mxfp4(32)
+        wb, ws = oracle.quantize_mxfp4(W)
+        xb, xs = oracle.quantize_mxfp4(X)
+        wd = oracle.dequant_matrix(oracle.MXFP4, wb, n, k, scales=ws)
+        xd = oracle.dequant_matrix(oracle.MXFP4, xb, m, k, scales=xs)
+        w, x = K.upload(qt, n, k, wb, ws), K.upload(qt, m, k, xb, xs)
+    y = K.gemm_fp4(w, x)
+    torch.cuda.synchronize()
+    assert K.status() == 0
+    ref = oracle.gemm_f32_nt(xd, wd) if m * n * k <= 2_000_000_000 else (xd.astype(np.float64) @ wd.T.astype(np.float64))
+    err = oracle.rel_err(y.cpu().numpy(), ref)
+    w.free()
+    x.free()
+    return err
+
+
+def test_gemm_fp4_nvfp4_single_tile(gk, K, oracle):
+    assert run_fp4_case(gk, K, oracle, "nvfp4", 128, 256, 128, seed=1) <= 2e-3
+
+
+def test_gemm_fp4_nvfp4_two_token_groups(gk, K, oracle):
+    assert run_fp4_case(gk, K, oracle, "nvfp4", 128, 512, 256, seed=2) <= 2e-3
+
+
+@pytest.mark.parametrize("n,k,m", [(384, 2048, 512), (200, 768, 300), (130, 1280, 77)])
+def test_gemm_fp4_nvfp4_shapes(gk, K, oracle, n, k, m):
+    assert run_fp4_case(gk, K, oracle, "nvfp4", n, k, m, seed=n + m) <= 2e-3
+
+
+@pytest.mark.parametrize("n,k,m", [(128, 256, 128), (300, 1024, 384)])
+def test_gemm_fp4_mxfp4(gk, K, oracle, n, k, m):
+    assert run_fp4_case(gk, K, oracle, "mxfp4", n, k, m, seed=n + m) <= 2e-3
