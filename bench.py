@@ -225,6 +225,7 @@ def extra_configs(K, gk, torch, dev, peak):
     """Configs 1 and 2 (small matrices): rotate over distinct weight copies totalling > 2x L2."""
     res = {}
     gen = torch.Generator(device=dev).manual_seed(20240)
+    torch.cuda.empty_cache()
 
     def run(qt, n, k, ms, copies, name):
         bs, bb = qt.block_size(), qt.block_bytes()
@@ -256,6 +257,79 @@ def extra_configs(K, gk, torch, dev, peak):
 
     run(gk.QuantType.q4k(), 4096, 4096, [1], 32, "cfg1_q4k_4096x4096")
     run(gk.QuantType.q8_0(), 11008, 4096, [1, 4, 8, 16], 6, "cfg2_q8_0_11008x4096")
+    res.update(extra_gemm(K, gk, torch, dev, gen))
+    return res
+
+
+def extra_gemm(K, gk, torch, dev, gen):
+    """Prefill configs: 3 (MXFP4 MoE experts, bf16 activations), 4 (NVFP4 x NVFP4), 5 at M = 32 / 512 (Q4_K)."""
+    res = {}
+    QT = gk.QuantType
+
+    def upload(qt, n, k):
+        W = torch.randn((n, k), generator=gen, device=dev) * 0.02
+        q = K.quantize(qt, W)
+        del W
+        if qt.id == 3:
+            return K.upload(qt, n, k, q[0], q[1])
+        if qt.id == 4:
+            return K.upload(qt, n, k, q[0], None, q[1])
+        return K.upload(qt, n, k, q)
+
+    def timeit(fn, reps):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / reps
+
+    # config 5 prefill: gate/up-shaped and down-shaped Q4_K, f32 activations
+    for n, k in ((28672, 8192), (8192, 28672)):
+        w = upload(QT.q4k(), n, k)
+        for m in (32, 512):
+            a = torch.randn((m, k), generator=gen, device=dev)
+            y = torch.empty((m, n), dtype=torch.float32, device=dev)
+            us = timeit(lambda: K.gemm(w, a, y=y), 5)
+            res[f"cfg5_q4k_{n}x{k}_M{m}"] = {"us": us, "tflops": 2.0 * m * n * k / us / 1e6, "weight_GBps": w.ref_bytes / us / 1e3,
+                                            "staging": "fp16 x fp16 -> f32 (kind::f16)"}
+        w.free()
+    # config 3: 8 experts MXFP4 [14336, 4096], 512 tokens top-2 -> 1024 rows grouped per expert, bf16 activations
+    experts = [upload(QT.mxfp4(32), 14336, 4096) for _ in range(8)]
+    ids = torch.stack([torch.randperm(8, generator=gen, device=dev)[:2] for _ in range(512)]).reshape(-1)
+    counts = torch.bincount(ids, minlength=8).cpu().tolist()
+    a = torch.randn((1024, 4096), generator=gen, device=dev).to(torch.bfloat16)
+    y = torch.empty((1024, 14336), dtype=torch.bfloat16, device=dev)
+    offs = [0]
+    for cnt in counts:
+        offs.append(offs[-1] + cnt)
+
+    def moe():
+        for e, w in enumerate(experts):
+            if counts[e]:
+                K.gemm(w, a[offs[e]:offs[e + 1]], y=y[offs[e]:offs[e + 1]])
+    us = timeit(moe, 5)
+    res["cfg3_mxfp4_moe_8x14336x4096_M512_top2"] = {"us": us, "tflops": 2.0 * 1024 * 14336 * 4096 / us / 1e6,
+                                                     "weight_GBps": sum(w.ref_bytes for w in experts) / us / 1e3,
+                                                     "rows_per_expert": counts, "staging": "fp16 x fp16 -> f32 (kind::f16)"}
+    for w in experts:
+        w.free()
+    # config 4: NVFP4 weights x NVFP4 activations, bf16 out, native block-scaled MMA
+    n, k, m = 14336, 4096, 2048
+    w = upload(QT.nvfp4(), n, k)
+    X = torch.randn((m, k), generator=gen, device=dev)
+    xb, gx = K.quantize(QT.nvfp4(), X)
+    x = K.upload(QT.nvfp4(), m, k, xb, None, gx)
+    y = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+    us = timeit(lambda: K.gemm_fp4(w, x, y=y), 20)
+    res["cfg4_nvfp4_14336x4096_M2048"] = {"us": us, "tflops": 2.0 * m * n * k / us / 1e6, "frac_of_nominal_fp4_9000": 2.0 * m * n * k / us / 1e6 / 9000.0,
+                                          "mma": "tcgen05 kind::mxf4nvf4 block_scale"}
+    w.free()
+    x.free()
     return res
 
 

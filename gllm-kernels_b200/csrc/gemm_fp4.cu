@@ -27,8 +27,8 @@ constexpr int F4_SFB_BYTES = 4096;
 constexpr int F4_STAGE_BYTES = F4_A_BYTES + F4_B_BYTES + F4_SFA_BYTES + F4_SFB_BYTES;
 constexpr int F4_THREADS = 192;             // warp 0: TMA, warp 1: MMA + TMEM, warps 2-5: epilogue
 constexpr size_t F4_SMEM = (size_t)F4_STAGES * F4_STAGE_BYTES + 1024;
-constexpr uint32_t F4_TMEM_COLS = 512;      // 256 accumulator + 16 (SFA) + 32 (SFB), power of two
-constexpr uint32_t F4_TMEM_SFA = 256, F4_TMEM_SFB = 272;
+constexpr uint32_t F4_TMEM_COLS = 512;      // 256 accumulator + 2 x (16 SFA + 32 SFB), power of two
+constexpr uint32_t F4_TMEM_SF = 256;        // scale-factor columns, two sets of 48 used by alternate k-steps
 
 struct Fp4Params {
     const uint8_t *sfw;  // weight scale plane
@@ -130,6 +130,9 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
             const uint32_t st = smem_s + s * F4_STAGE_BYTES;
             const uint32_t sfa = st + F4_A_BYTES + F4_B_BYTES, sfb = sfa + F4_SFA_BYTES;
             const uint64_t ad = tc::smem_desc_sw128(st), bd = tc::smem_desc_sw128(st + F4_A_BYTES);
+            // alternate scale-factor column sets so the copies of this k-step do not have to wait for the
+            // MMAs of the previous one to finish reading theirs
+            const uint32_t F4_TMEM_SFA = F4_TMEM_SF + 48u * (uint32_t)(ks & 1), F4_TMEM_SFB = F4_TMEM_SFA + 16u;
             if (p.nv) {
                 // atom j holds the four 16-element scales of MMA j (K = 64): 4 TMEM columns each
 #pragma unroll
