@@ -40,6 +40,7 @@ static int32_t grow(Ctx *c, void **p, size_t *have, size_t want, bool pinned) {
 }
 int32_t ensure_ws(Ctx *c, size_t bytes) { return grow(c, &c->ws, &c->ws_bytes, bytes, false); }
 int32_t ensure_red(Ctx *c, size_t bytes) { return grow(c, &c->red, &c->red_bytes, bytes, false); }
+int32_t ensure_act(Ctx *c, size_t bytes) { return grow(c, &c->act, &c->act_bytes, bytes, false); }
 int32_t ensure_cnt(Ctx *c, size_t bytes) {
     if (c->cnt_bytes >= bytes) return GLLMK_STATUS_OK;
     int32_t rc = grow(c, &c->cnt, &c->cnt_bytes, bytes, false);
@@ -89,7 +90,7 @@ static int32_t weight_alloc(Ctx *c, int32_t qt, int64_t n, int64_t k, int32_t mx
         return fail(c, GLLMK_STATUS_UNSUPPORTED, "MXFP4 weights need block_size 32 (got %d)", mx_block);
     if (n <= 0 || k <= 0) return fail(c, GLLMK_STATUS_INVALID_ARG, "n and k must be positive");
     const int bs = block_size_of(qt, mx_block);
-    const int64_t kmul = (qt == GLLMK_QUANT_MXFP4) ? 128 : bs;  // FP4 scale planes come in atoms of 4
+    const int64_t kmul = bs;
     if (k % kmul) return fail(c, GLLMK_STATUS_INVALID_ARG, "k=%lld is not a multiple of %lld", (long long)k, (long long)kmul);
     if (n > (int64_t)1 << 30 || k > (int64_t)1 << 30) return fail(c, GLLMK_STATUS_INVALID_ARG, "matrix too large");
     Weight *w = new (std::nothrow) Weight();
@@ -98,6 +99,7 @@ static int32_t weight_alloc(Ctx *c, int32_t qt, int64_t n, int64_t k, int32_t mx
     w->mx_block = (qt == GLLMK_QUANT_MXFP4) ? mx_block : 0;
     w->n = n;
     w->k = k;
+    w->k_pad = k;
     w->nb = k / bs;
     w->global_scale = global;
     w->device = c->device;
@@ -112,9 +114,11 @@ static int32_t weight_alloc(Ctx *c, int32_t qt, int64_t n, int64_t k, int32_t mx
         w->qs_bytes = (size_t)(w->n_pad / 16) * w->nb8 * Q80_CHUNK;
         w->aux_bytes = 0;
     } else {
+        // FP4 planes are tiled in 256-element k-steps: k is padded with zero codes and zero scale bytes
         w->n_pad = (n + 127) / 128 * 128;
-        w->qs_bytes = (size_t)w->n_pad * (k / 2);
-        w->aux_bytes = (size_t)w->n_pad * (k / (qt == GLLMK_QUANT_NVFP4 ? 16 : 32));
+        w->k_pad = (k + 255) / 256 * 256;
+        w->qs_bytes = (size_t)w->n_pad * (w->k_pad / 2);
+        w->aux_bytes = (size_t)w->n_pad * (w->k_pad / (qt == GLLMK_QUANT_NVFP4 ? 16 : 32));
     }
     cudaError_t e = cudaMalloc(&w->qs, w->qs_bytes);
     if (e == cudaSuccess && w->aux_bytes) e = cudaMalloc(&w->aux, w->aux_bytes);
@@ -225,6 +229,7 @@ void gllmk_ctx_free(gllmk_ctx ctx) {
     cudaDeviceSynchronize();
     if (c->ws) cudaFree(c->ws);
     if (c->red) cudaFree(c->red);
+    if (c->act) cudaFree(c->act);
     if (c->cnt) cudaFree(c->cnt);
     if (c->status_dev) cudaFree(c->status_dev);
     if (c->dev_io) cudaFree(c->dev_io);

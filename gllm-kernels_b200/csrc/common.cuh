@@ -41,10 +41,13 @@ __host__ __device__ inline size_t q4k_chunk_index(int64_t T, int64_t b, int64_t 
 //                are the A-fragment registers a0, a2, a1, a3 of mma.m16n8k32.s8 for that block
 //   [4096, 4352) half  [row 0..15][block 0..7]  f16 scale bits (0 for padding blocks)
 //
-// MXFP4 (block 32) and NVFP4 (block 64 = 4 x 16), rows padded to 128, k % 256 == 0:
-//   data: uint8 [n_pad][k / 2]                   nibbles as in the reference (low nibble = even element),
-//                                                a plain 2-D byte matrix a TMA tensor map can tile
-//   sf   : uint8 [n_pad / 128][k / (4*sfb)][512] one scale byte per sfb = 32 (MXFP4, E8M0) or 16 (NVFP4,
+// MXFP4 (block 32) and NVFP4 (block 64 = 4 x 16), rows padded to 128, k padded to 256 (k_pad):
+//   data: uint8 [n_pad / 128][k_pad / 256][16384]   nibbles as in the reference (low nibble = even element), in
+//                                                tiles of 128 rows x 128 bytes (256 elements) stored as the
+//                                                128-byte-swizzled shared-memory image the tensor core reads:
+//                                                byte j of row r at r*128 + (((j/16) ^ (r%8)) * 16) + j%16;
+//                                                one bulk copy of 16 KB brings a tile in ready to use
+//   sf   : uint8 [n_pad / 128][k_pad / (4*sfb)][512] one scale byte per sfb = 32 (MXFP4, E8M0) or 16 (NVFP4,
 //                                                UE4M3) elements, in 128-row x 4-scale atoms:
 //                                                offset = (r % 32) * 16 + ((r % 128) / 32) * 4 + (s % 4)
 //                                                (the tile order tcgen05 block-scaled MMA takes its
@@ -54,6 +57,7 @@ struct Weight {
     int32_t mx_block = 0;
     int64_t n = 0, k = 0;
     int64_t n_pad = 0;
+    int64_t k_pad = 0;  // FP4 planes: k rounded up to 256
     int64_t nb = 0;   // blocks per row
     int64_t nb8 = 0;  // Q8_0: groups of 8 blocks per row
     float global_scale = 1.0f;
@@ -72,6 +76,9 @@ struct Ctx {
     void *ws = nullptr;
     size_t ws_bytes = 0;
     int64_t ws_k = -1;  // K the workspace is currently laid out (and zero-padded) for
+    // prefill: activations converted to fp16 shared-memory tile images
+    void *act = nullptr;
+    size_t act_bytes = 0;
     // split-k partial sums; per-tile arrival counters (zeroed at allocation, self-resetting); status word
     void *red = nullptr;
     size_t red_bytes = 0;
@@ -92,6 +99,7 @@ int32_t fail(Ctx *c, int32_t code, const char *fmt, ...);
 int32_t cuda_fail(Ctx *c, cudaError_t e, const char *what);
 int32_t ensure_ws(Ctx *c, size_t bytes);
 int32_t ensure_red(Ctx *c, size_t bytes);
+int32_t ensure_act(Ctx *c, size_t bytes);
 int32_t ensure_cnt(Ctx *c, size_t bytes);
 int32_t ensure_pin(Ctx *c, size_t bytes);
 int32_t ensure_dev_io(Ctx *c, size_t bytes);
@@ -120,6 +128,19 @@ int32_t gemm_fp4_launch(Ctx *c, const Weight *w, const Weight *x, void *y, int y
 // ---- quantize.cu ----
 int32_t quantize_launch(Ctx *c, int32_t qt, const float *x, int64_t rows, int64_t k, int mx_block, void *blocks,
                         void *scales, float *global_scale, cudaStream_t s);
+
+// ---- FP4 plane addressing ----
+// byte offset of byte `j` of row `row` in the tiled, swizzled data plane (k elements per row)
+__host__ __device__ inline size_t fp4_data_offset(int64_t row, int64_t j, int64_t k) {
+    const size_t tile = (size_t)(row >> 7) * (size_t)(k >> 8) + (size_t)(j >> 7);
+    const int r = (int)(row & 127), c = (int)((j >> 4) & 7);
+    return tile * 16384 + (size_t)r * 128 + (size_t)(((c ^ (r & 7)) << 4) + (int)(j & 15));
+}
+// byte offset of scale `s` of row `row` in the scale-factor plane (s_per_row scales per row)
+__host__ __device__ inline size_t fp4_sf_offset(int64_t row, int64_t s, int64_t s_per_row) {
+    const size_t atom = (size_t)(row >> 7) * (size_t)(s_per_row >> 2) + (size_t)(s >> 2);
+    return atom * 512 + (size_t)(row & 31) * 16 + (size_t)((row & 127) >> 5) * 4 + (size_t)(s & 3);
+}
 
 // ---- small device helpers ----
 __device__ __forceinline__ float e8m0_to_f32(uint32_t b) {

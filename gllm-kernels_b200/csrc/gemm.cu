@@ -2,16 +2,19 @@
 //
 //   Y[t, r] = sum_k W[r, k] * X[t, k]        t < M tokens (M > 16), r < N weight rows
 //
-// Weight-only formats (Q4_K, Q8_0, MXFP4, NVFP4 weights with bf16/f32 activations), gemm_wq_kernel:
-//   UMMA operand A = 128 weight rows x 64 k, dequantized to fp16 by four producer warps straight into the
-//   128-byte-swizzled K-major shared-memory layout the tensor core reads (one thread = one weight row);
-//   operand B = up to 256 tokens x 64 k of activations (f32 or bf16 in memory, fp16 in shared memory:
-//   kind::f16 takes one 16-bit format for both operands; mixing f16 and bf16 is an illegal instruction);
-//   D = 128 lanes (weight rows) x up to 256 columns (tokens) of f32 in tensor memory.
-//   Putting the weights on the M side means a CTA dequantizes its weight tile once for all of its tokens
-//   and the epilogue's warp-wide stores (lane = consecutive r) are coalesced in Y's row-major layout.
-//   One elected thread issues tcgen05.mma (kind::f16); tcgen05.commit releases the shared-memory stage.
-//   Staging: weights fp16, activations fp16/bf16, accumulate f32 (parity bar 1e-2; measured ~1e-3).
+// Weight-only formats (Q4_K, Q8_0, MXFP4, NVFP4 weights with bf16/f32 activations), gemm_wq_kernel.
+// A CTA owns 128 weight rows (UMMA M) x up to 256 tokens (UMMA N) and walks K in steps of 64 (64 fp16 = one 128-byte swizzle row):
+//   * the RAW quantized weights of its 128 rows arrive as one bulk copy per 256 k ("super-chunk": the same
+//     contiguous byte range the decode GEMV streams) into a shared-memory ring, mbarrier-tracked;
+//   * four dequant warps turn a quarter of a super-chunk (64 k) into fp16 with packed half2 arithmetic and
+//     store it as the 128-byte-swizzled K-major operand A tile the tensor core reads;
+//   * the activations were converted once per call to fp16 tile images (stage_act_kernel), so operand B
+//     of a k-step is one or two bulk copies of 16 KB;
+//   * one elected thread issues tcgen05.mma (kind::f16, f32 accumulate in TMEM); tcgen05.commit hands the
+//     A and B stages back; after the last k-step the dequant warps read the accumulator (tcgen05.ld:
+//     lane = weight row, so the warp-wide stores are coalesced in Y's row-major layout).
+// kind::f16 takes one 16-bit format for both operands (mixing f16 and bf16 is an illegal instruction), so
+// weights and activations are both staged in fp16: 11 significant bits, accumulate f32 (parity bar 1e-2).
 // No cluster-multicast load is used anywhere (the same kernel serves the multi-GPU configuration).
 #include <cuda_bf16.h>
 
@@ -20,296 +23,445 @@
 
 namespace gllmk {
 
-constexpr int GEMM_BM = 128;     // weight rows per CTA (UMMA M)
-constexpr int GEMM_BN = 256;     // tokens per CTA (UMMA N, <= 256)
-constexpr int GEMM_BK = 64;      // k per stage: 64 bf16 = one 128-byte swizzle row
-constexpr int GEMM_STAGES = 4;
-constexpr int GEMM_A_BYTES = GEMM_BM * 128, GEMM_B_BYTES = GEMM_BN * 128;
-constexpr int GEMM_STAGE_BYTES = GEMM_A_BYTES + GEMM_B_BYTES;
-constexpr int GEMM_THREADS = 160;  // warps 0-3: producers, then epilogue; warp 4: MMA issue + TMEM
-constexpr size_t GEMM_SMEM = (size_t)GEMM_STAGES * GEMM_STAGE_BYTES + 1024;
+constexpr int WQ_BM = 128;         // weight rows per CTA (UMMA M)
+constexpr int WQ_BN = 256;         // tokens per CTA (UMMA N, <= 256)
+constexpr int WQ_TILE = 16384;     // one operand tile: 128 rows x 128 bytes
+constexpr int WQ_SA = 3;           // operand A (dequantized weights) stages
+constexpr int WQ_MAX_SB = 4;       // operand B (activation) stages, at most
+constexpr int WQ_MAX_R = 4;        // raw super-chunk ring, at most
+constexpr int WQ_DW = 16;          // dequant warps
+constexpr int WQ_THREADS = 96 + 32 * WQ_DW;  // warp 0: raw copies, warp 1: activation copies, warp 2: MMA + TMEM, then dequant / epilogue warps
+constexpr int WQ_SMEM_LIMIT = 232448 - 1024 - 1024;  // ring space: 227 KB less the static variables' share and the alignment slack
+
+enum { FMT_Q4K = 0, FMT_Q80 = 1, FMT_NVFP4 = 2, FMT_MXFP4 = 3 };
+__host__ __device__ constexpr int wq_raw_bytes(int fmt) {
+    return fmt == FMT_Q4K ? 8 * Q4K_CHUNK : (fmt == FMT_Q80 ? 8 * Q80_CHUNK : (fmt == FMT_NVFP4 ? WQ_TILE + 2048 : WQ_TILE + 1024));
+}
 
 struct GemmParams {
     const uint8_t *qs;   // weight plane (format-specific, see common.cuh)
     const uint8_t *aux;  // FP4 scale-factor plane
-    int qt;
-    int64_t n, k, nb;    // nb: blocks per row (Q4_K 256-blocks, Q8_0 groups of 8 blocks)
+    int64_t n;
+    int nsc;             // super-chunks (256 k) per row
     float global_scale;
-    const void *a;       // activations [m, k] row-major, leading dimension lda (elements)
-    int a_bf16;          // 1: bf16, 0: f32
-    int64_t lda;
+    const uint8_t *xt;   // fp16 activation tile images [token tile of 128][k-step of 64][16384]
     int m;
     void *y;             // [m, n] row-major, leading dimension ldy
     int y_bf16;
     int64_t ldy;
+    int ntok;            // MMA N of this launch (multiple of 32, <= 256)
+    int sb, r;           // ring depths
     int *status;
 };
 
-// weights are staged in fp16 (11 significant bits; |w| of these formats is far inside its range)
-__device__ __forceinline__ uint32_t pack_w(float a, float b) {
-    __half2 v = __floats2half2_rn(a, b);
-    return *reinterpret_cast<uint32_t *>(&v);
-}
-// activations are staged in fp16 too, saturating at +-65504
-__device__ __forceinline__ uint32_t pack_x(float a, float b) {
-    uint32_t r;
-    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;\n" : "=r"(r) : "f"(b), "f"(a));
-    return r;
-}
-__device__ __forceinline__ size_t fp4_sf_offset(int64_t row, int64_t s, int64_t s_per_row) {
-    const size_t atom = (size_t)(row >> 7) * (size_t)(s_per_row >> 2) + (size_t)(s >> 2);
-    return atom * 512 + (size_t)(row & 31) * 16 + (size_t)((row & 127) >> 5) * 4 + (size_t)(s & 3);
+// ---- activations -> fp16 tile images ------------------------------------------------------------
+// grid (k-steps, token tiles of 128); rows >= m and k >= k_valid are zero
+__global__ void __launch_bounds__(256) stage_act_kernel(const void *__restrict__ a, int a_bf16, int64_t lda, int m, int64_t k_valid,
+                                                        uint8_t *__restrict__ xt) {
+    const int ks = blockIdx.x, tile = blockIdx.y;
+    uint8_t *dst = xt + ((size_t)tile * gridDim.x + ks) * WQ_TILE;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int item = threadIdx.x + 256 * i, row = item >> 3, chunk = item & 7;
+        const int64_t tok = (int64_t)tile * 128 + row, k0 = (int64_t)ks * 64 + chunk * 8;
+        uint4 o = make_uint4(0, 0, 0, 0);
+        if (tok < m && k0 < k_valid) {
+            if (a_bf16) {
+                // bf16 -> fp16 through f32, saturating at +-65504
+                const uint4 v = __ldg(reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(a) + tok * lda + k0));
+                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+                uint32_t r[4];
+#pragma unroll
+                for (int q = 0; q < 4; q++)
+                    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;\n" : "=r"(r[q]) : "f"(__uint_as_float(w[q] & 0xFFFF0000u)), "f"(__uint_as_float(w[q] << 16)));
+                o = make_uint4(r[0], r[1], r[2], r[3]);
+            } else {
+                const float4 *src = reinterpret_cast<const float4 *>(static_cast<const float *>(a) + tok * lda + k0);
+                const float4 x0 = __ldg(src), x1 = __ldg(src + 1);
+                uint32_t r[4];
+                asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;\n" : "=r"(r[0]) : "f"(x0.y), "f"(x0.x));
+                asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;\n" : "=r"(r[1]) : "f"(x0.w), "f"(x0.z));
+                asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;\n" : "=r"(r[2]) : "f"(x1.y), "f"(x1.x));
+                asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;\n" : "=r"(r[3]) : "f"(x1.w), "f"(x1.z));
+                o = make_uint4(r[0], r[1], r[2], r[3]);
+            }
+        }
+        *reinterpret_cast<uint4 *>(dst + tc::sw128_offset(row, chunk)) = o;
+    }
 }
 
-// Decodes 64 consecutive k (stage ks) of weight row `row` to fp16: out[c] = 16-byte chunk c (8 values).
-// Values are d*sc*q - dmin*m etc. evaluated in f32 and rounded once to fp16.
-__device__ __forceinline__ void dequant_row64(const GemmParams &p, int64_t row, int ks, uint4 (&out)[8]) {
-    const int64_t T = row >> 4;
-    const int rr = (int)(row & 15), g = rr & 7, h = rr >> 3;
-    if (p.qt == GLLMK_QUANT_Q4K) {
-        const int64_t b = ks >> 2;
-        const int pg = ks & 3;
-        const uint8_t *chunk = p.qs + q4k_chunk_index(T, b, p.nb) * Q4K_CHUNK;
-        const uint4 hd = *reinterpret_cast<const uint4 *>(chunk + 2048 + rr * 16);
+// ---- packed dequant arithmetic --------------------------------------------------------------------
+__device__ __forceinline__ __half2 u32_as_h2(uint32_t v) { return *reinterpret_cast<__half2 *>(&v); }
+__device__ __forceinline__ uint32_t h2_as_u32(__half2 v) { return *reinterpret_cast<uint32_t *>(&v); }
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst), "l"(src),
+                 "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+// Four unsigned bytes (each < 256) -> their values as two half2, exactly: the byte becomes the low mantissa
+// bits of 1024.0 (0x6400) and 1024 is subtracted again.
+__device__ __forceinline__ void bytes_to_h2(uint32_t b, float bias, __half2 &lo, __half2 &hi) {
+    const __half2 off = __float2half2_rn(bias);
+    lo = __hsub2(u32_as_h2(__byte_perm(b, 0x64646464u, 0x5140)), off);
+    hi = __hsub2(u32_as_h2(__byte_perm(b, 0x64646464u, 0x5342)), off);
+}
+// Q4_K: one 32-bit word = 4 low-nibble elements (sub-block 2p) and 4 high-nibble elements (sub-block 2p+1);
+// e = (d*sc, -dmin*m) of the sub-block: value = q * d*sc - dmin*m, one fp16 rounding after the product
+__device__ __forceinline__ void q4k_word(uint32_t w, __half2 e_lo, __half2 e_hi, uint32_t &lo01, uint32_t &lo23, uint32_t &hi01,
+                                         uint32_t &hi23) {
+    __half2 a, b;
+    bytes_to_h2(w & 0x0F0F0F0Fu, 1024.0f, a, b);
+    lo01 = h2_as_u32(__hfma2(a, __low2half2(e_lo), __high2half2(e_lo)));
+    lo23 = h2_as_u32(__hfma2(b, __low2half2(e_lo), __high2half2(e_lo)));
+    bytes_to_h2((w >> 4) & 0x0F0F0F0Fu, 1024.0f, a, b);
+    hi01 = h2_as_u32(__hfma2(a, __low2half2(e_hi), __high2half2(e_hi)));
+    hi23 = h2_as_u32(__hfma2(b, __low2half2(e_hi), __high2half2(e_hi)));
+}
+// Q8_0: four int8 of one word times the block scale
+__device__ __forceinline__ void q80_word(uint32_t w, __half2 d2, uint32_t &o01, uint32_t &o23) {
+    __half2 a, b;
+    bytes_to_h2(w ^ 0x80808080u, 1152.0f, a, b);  // (q + 128) + 1024 - 1152 = q
+    o01 = h2_as_u32(__hmul2(a, d2));
+    o23 = h2_as_u32(__hmul2(b, d2));
+}
+// FP4: eight E2M1 codes of one word -> fp16 (hardware conversion, exact), times the scale
+__device__ __forceinline__ uint4 fp4_word(uint32_t w, __half2 s2) {
+    uint32_t o0, o1, o2, o3;
+    asm("{\n.reg .b8 a, b, c, d;\nmov.b32 {a, b, c, d}, %4;\n"
+        "cvt.rn.f16x2.e2m1x2 %0, a;\ncvt.rn.f16x2.e2m1x2 %1, b;\ncvt.rn.f16x2.e2m1x2 %2, c;\ncvt.rn.f16x2.e2m1x2 %3, d;\n}\n"
+        : "=r"(o0), "=r"(o1), "=r"(o2), "=r"(o3)
+        : "r"(w));
+    return make_uint4(h2_as_u32(__hmul2(u32_as_h2(o0), s2)), h2_as_u32(__hmul2(u32_as_h2(o1), s2)),
+                      h2_as_u32(__hmul2(u32_as_h2(o2), s2)), h2_as_u32(__hmul2(u32_as_h2(o3), s2)));
+}
+__device__ __forceinline__ __half2 scale_h2(float s) {
+    uint32_t r;
+    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %1;\n" : "=r"(r) : "f"(s));
+    return u32_as_h2(r);
+}
+
+// ---- dequant of one k-step (64 k) of the CTA's 128 weight rows into an operand A tile ----------------
+// Sixteen dequant warps (four per scheduler, so that the short dependent chains of one warp hide behind the
+// others); dw = dequant warp 0..15, lane = 4*g + t.  `raw` is the super-chunk in shared memory, p = k-step
+// inside it (0..3), `at` the A tile.
+//
+// Q4_K / Q8_0: warp dw handles the 16-row chunk c = dw % 8, rows g + 8h with h = dw / 8; its lane reads its
+// half of the uint4 the device layout keeps for lane (bytes 8t..8t+7 of the row's 32-byte group) and
+// produces the 16-byte fp16 groups t (low nibbles / even block) and 4 + t (high nibbles / odd block).
+template <int FMT>
+struct Dequant;
+
+template <>
+struct Dequant<FMT_Q4K> {
+    // (d*sc, -dmin*m) of sub-blocks 2t and 2t+1 of this thread's row; the k-step p needs sub-blocks 2p and
+    // 2p+1, which lane (lane & ~3) | p holds
+    __half2 ent[2];
+    float global;
+    __device__ __forceinline__ void begin(const uint8_t *raw, int dw, int lane) {
+        const int g = lane >> 2, t = lane & 3, c = dw & 7, h = dw >> 3, rr = g + 8 * h;
+        const uint8_t *chunk = raw + c * Q4K_CHUNK;
         const uint32_t dd = *reinterpret_cast<const uint32_t *>(chunk + 2304 + (g * 2 + h) * 4);
         const float d = __half2float(__ushort_as_half((unsigned short)(dd & 0xFFFFu)));
         const float dmin = __half2float(__ushort_as_half((unsigned short)(dd >> 16)));
-        const uint32_t scw = pg < 2 ? hd.x : hd.y, mnw = pg < 2 ? hd.z : hd.w;
-        const int sh = 16 * (pg & 1);
-        const float d1 = d * (float)((scw >> sh) & 0xFFu), m1 = dmin * (float)((mnw >> sh) & 0xFFu);
-        const float d2 = d * (float)((scw >> (sh + 8)) & 0xFFu), m2 = dmin * (float)((mnw >> (sh + 8)) & 0xFFu);
-#pragma unroll
-        for (int t = 0; t < 4; t++) {
-            const uint2 w = *reinterpret_cast<const uint2 *>(chunk + (pg * 32 + 4 * g + t) * 16 + h * 8);
-            uint32_t lo[4], hi[4];
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const uint32_t word = j < 2 ? w.x : w.y;
-                const int s0 = 16 * (j & 1);
-                lo[j] = pack_w(fmaf(d1, (float)((word >> s0) & 15u), -m1), fmaf(d1, (float)((word >> (s0 + 8)) & 15u), -m1));
-                hi[j] = pack_w(fmaf(d2, (float)((word >> (s0 + 4)) & 15u), -m2), fmaf(d2, (float)((word >> (s0 + 12)) & 15u), -m2));
-            }
-            out[t] = make_uint4(lo[0], lo[1], lo[2], lo[3]);      // elements 8t .. 8t+7 (low nibbles, sub-block 2pg)
-            out[4 + t] = make_uint4(hi[0], hi[1], hi[2], hi[3]);  // elements 32+8t .. (high nibbles, sub-block 2pg+1)
-        }
-    } else if (p.qt == GLLMK_QUANT_Q8_0) {
-        const int64_t b8 = ks >> 2;
-        const int bb0 = (2 * ks) & 7;
-        const uint8_t *chunk = p.qs + q4k_chunk_index(T, b8, p.nb) * Q80_CHUNK;
-#pragma unroll
-        for (int j = 0; j < 2; j++) {
-            const int bb = bb0 + j;
-            const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(chunk + 4096 + (rr * 8 + bb) * 2)));
-#pragma unroll
-            for (int t = 0; t < 4; t++) {
-                const uint2 w = *reinterpret_cast<const uint2 *>(chunk + (bb * 32 + 4 * g + t) * 16 + h * 8);
-                uint32_t o[4];
-#pragma unroll
-                for (int q = 0; q < 4; q++) {
-                    const uint32_t word = q < 2 ? w.x : w.y;
-                    const int s0 = 16 * (q & 1);
-                    o[q] = pack_w(d * (float)(int8_t)((word >> s0) & 0xFFu), d * (float)(int8_t)((word >> (s0 + 8)) & 0xFFu));
-                }
-                out[4 * j + t] = make_uint4(o[0], o[1], o[2], o[3]);
-            }
-        }
-    } else {
-        const bool nv = p.qt == GLLMK_QUANT_NVFP4;
-        const uint4 *src = reinterpret_cast<const uint4 *>(p.qs + (size_t)row * (p.k >> 1) + 32 * ks);
-        const uint4 raw[2] = {src[0], src[1]};
-#pragma unroll
-        for (int c = 0; c < 8; c++) {
-            const uint4 r4 = raw[c >> 2];
-            const uint32_t word = (c & 3) == 0 ? r4.x : ((c & 3) == 1 ? r4.y : ((c & 3) == 2 ? r4.z : r4.w));
-            float s;
-            if (nv) s = p.global_scale * e4m3_to_f32(p.aux[fp4_sf_offset(row, 4 * ks + (c >> 1), p.k >> 4)]);
-            else s = e8m0_to_f32(p.aux[fp4_sf_offset(row, 2 * ks + (c >> 2), p.k >> 5)]);
-            uint32_t o[4];
-#pragma unroll
-            for (int q = 0; q < 4; q++)
-                o[q] = pack_w(e2m1_to_f32((word >> (8 * q)) & 15u) * s, e2m1_to_f32((word >> (8 * q + 4)) & 15u) * s);
-            out[c] = make_uint4(o[0], o[1], o[2], o[3]);
-        }
+        const uint32_t sc = *reinterpret_cast<const unsigned short *>(chunk + 2048 + rr * 16 + 2 * t);
+        const uint32_t mn = *reinterpret_cast<const unsigned short *>(chunk + 2048 + rr * 16 + 8 + 2 * t);
+        ent[0] = __floats2half2_rn(d * (float)(sc & 0xFFu), -(dmin * (float)(mn & 0xFFu)));
+        ent[1] = __floats2half2_rn(d * (float)(sc >> 8), -(dmin * (float)(mn >> 8)));
     }
-}
-
-// Loads 64 k of one activation row (token) as bf16 chunks; rows >= m give zeros.
-__device__ __forceinline__ void load_act_row64(const GemmParams &p, int64_t tok, int ks, uint4 (&out)[8]) {
-    if (tok >= p.m) {
-#pragma unroll
-        for (int c = 0; c < 8; c++) out[c] = make_uint4(0, 0, 0, 0);
-        return;
+    __device__ __forceinline__ void step(const uint8_t *raw, int p, uint8_t *at, int dw, int lane) {
+        const int g = lane >> 2, t = lane & 3, c = dw & 7, h = dw >> 3, src = (lane & ~3) | p;
+        const uint2 q = *reinterpret_cast<const uint2 *>(raw + c * Q4K_CHUNK + (p * 32 + lane) * 16 + 8 * h);
+        const __half2 e_lo = u32_as_h2(__shfl_sync(0xffffffffu, h2_as_u32(ent[0]), src));
+        const __half2 e_hi = u32_as_h2(__shfl_sync(0xffffffffu, h2_as_u32(ent[1]), src));
+        uint4 lo, hi;
+        q4k_word(q.x, e_lo, e_hi, lo.x, lo.y, hi.x, hi.y);
+        q4k_word(q.y, e_lo, e_hi, lo.z, lo.w, hi.z, hi.w);
+        uint8_t *rowp = at + (16 * c + 8 * h + g) * 128;  // (row & 7) == g
+        *reinterpret_cast<uint4 *>(rowp + ((t ^ g) << 4)) = lo;
+        *reinterpret_cast<uint4 *>(rowp + (((4 + t) ^ g) << 4)) = hi;
     }
-    if (p.a_bf16) {
-        const uint4 *src = reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(p.a) + tok * p.lda + (int64_t)ks * 64);
-#pragma unroll
-        for (int c = 0; c < 8; c++) {
-            // bf16 -> fp16 (exact inside fp16's range): kind::f16 wants both operands in one 16-bit format
-            const uint4 v = __ldg(src + c);
-            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-            uint32_t o[4];
-#pragma unroll
-            for (int q = 0; q < 4; q++) o[q] = pack_x(__uint_as_float(w[q] << 16), __uint_as_float(w[q] & 0xFFFF0000u));
-            out[c] = make_uint4(o[0], o[1], o[2], o[3]);
-        }
-    } else {
-        const float4 *src = reinterpret_cast<const float4 *>(static_cast<const float *>(p.a) + tok * p.lda + (int64_t)ks * 64);
-#pragma unroll
-        for (int c = 0; c < 8; c++) {
-            const float4 a = __ldg(src + 2 * c), b = __ldg(src + 2 * c + 1);
-            out[c] = make_uint4(pack_x(a.x, a.y), pack_x(a.z, a.w), pack_x(b.x, b.y), pack_x(b.z, b.w));
-        }
+};
+
+template <>
+struct Dequant<FMT_Q80> {
+    float global;
+    __device__ __forceinline__ void begin(const uint8_t *, int, int) {}
+    __device__ __forceinline__ void step(const uint8_t *raw, int p, uint8_t *at, int dw, int lane) {
+        const int g = lane >> 2, t = lane & 3, c = dw & 7, h = dw >> 3, rr = g + 8 * h;
+        const uint8_t *chunk = raw + c * Q80_CHUNK;
+        const uint2 q0 = *reinterpret_cast<const uint2 *>(chunk + ((2 * p) * 32 + lane) * 16 + 8 * h);
+        const uint2 q1 = *reinterpret_cast<const uint2 *>(chunk + ((2 * p + 1) * 32 + lane) * 16 + 8 * h);
+        const __half2 dd = u32_as_h2(*reinterpret_cast<const uint32_t *>(chunk + 4096 + (rr * 8 + 2 * p) * 2));
+        uint4 lo, hi;
+        q80_word(q0.x, __low2half2(dd), lo.x, lo.y);
+        q80_word(q0.y, __low2half2(dd), lo.z, lo.w);
+        q80_word(q1.x, __high2half2(dd), hi.x, hi.y);
+        q80_word(q1.y, __high2half2(dd), hi.z, hi.w);
+        uint8_t *rowp = at + (16 * c + 8 * h + g) * 128;
+        *reinterpret_cast<uint4 *>(rowp + ((t ^ g) << 4)) = lo;
+        *reinterpret_cast<uint4 *>(rowp + (((4 + t) ^ g) << 4)) = hi;
     }
-}
+};
 
-__device__ __forceinline__ void store_row_sw128(uint8_t *tile, int row, const uint4 (&v)[8]) {
-#pragma unroll
-    for (int c = 0; c < 8; c++) *reinterpret_cast<uint4 *>(tile + tc::sw128_offset(row, c)) = v[c];
-}
+// FP4: the raw super-chunk is the row tile's swizzled data image (16 KB) followed by its scale atoms (512 B
+// each: [row % 32][row / 32][4 scales]).  Thread = (weight row r = 32 * (dw % 4) + lane, quarter = dw / 4):
+// 16 of the row's 64 elements of this k-step.
+template <int FMT>
+struct DequantFp4 {
+    float global;
+    __device__ __forceinline__ void begin(const uint8_t *, int, int) {}
+    __device__ __forceinline__ void step(const uint8_t *raw, int p, uint8_t *at, int dw, int lane) {
+        const int rq = dw & 3, r = 32 * rq + lane, qtr = dw >> 2;
+        const uint2 v = *reinterpret_cast<const uint2 *>(raw + tc::sw128_offset(r, 2 * p + (qtr >> 1)) + 8 * (qtr & 1));
+        __half2 s;
+        if (FMT == FMT_NVFP4) s = scale_h2(global * e4m3_to_f32(raw[WQ_TILE + p * 512 + lane * 16 + rq * 4 + qtr]));
+        else s = scale_h2(e8m0_to_f32(raw[WQ_TILE + (p >> 1) * 512 + lane * 16 + rq * 4 + 2 * (p & 1) + (qtr >> 1)]));
+        uint8_t *rowp = at + r * 128;
+        *reinterpret_cast<uint4 *>(rowp + (((2 * qtr) ^ (r & 7)) << 4)) = fp4_word(v.x, s);
+        *reinterpret_cast<uint4 *>(rowp + (((2 * qtr + 1) ^ (r & 7)) << 4)) = fp4_word(v.y, s);
+    }
+};
+template <>
+struct Dequant<FMT_NVFP4> : DequantFp4<FMT_NVFP4> {};
+template <>
+struct Dequant<FMT_MXFP4> : DequantFp4<FMT_MXFP4> {};
 
-// grid: (weight-row tiles of 128, token tiles of 256).  ntok = MMA N of this launch (multiple of 16, <= 256).
-__global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_wq_kernel(const __grid_constant__ GemmParams p, const int ntok) {
+// ---- the kernel -----------------------------------------------------------------------------------
+// grid: (token tiles, weight-row tiles of 128): CTAs that share a weight tile run side by side, so its
+// second reader finds the raw bytes in L2.
+template <int FMT>
+__global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_constant__ GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bars[2 * GEMM_STAGES + 1];
+    // barriers: fullA, emptyA [WQ_SA]; fullB, emptyB [WQ_MAX_SB]; rawfull, rawempty [WQ_MAX_R]; accum
+    __shared__ __align__(8) uint64_t bars[2 * WQ_SA + 2 * WQ_MAX_SB + 2 * WQ_MAX_R + 1];
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s;
-    uint8_t *smem = smem_raw + ((1024u - (tc::smem_u32(smem_raw) & 1023u)) & 1023u);
-    const uint32_t smem_s = tc::smem_u32(smem);
-    const uint32_t full = tc::smem_u32(&bars[0]), empty = tc::smem_u32(&bars[GEMM_STAGES]),
-                   accum = tc::smem_u32(&bars[2 * GEMM_STAGES]);
+    constexpr int RAW = wq_raw_bytes(FMT);
+    const uint32_t smem_s = (tc::smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *smem = smem_raw + (smem_s - tc::smem_u32(smem_raw));
+    const int bstage = p.ntok * 128;
+    const uint32_t a_off = 0, b_off = WQ_SA * WQ_TILE, raw_off = b_off + (uint32_t)(p.sb * bstage);
+    const uint32_t fullA = tc::smem_u32(&bars[0]), emptyA = fullA + 8 * WQ_SA, fullB = emptyA + 8 * WQ_SA,
+                   emptyB = fullB + 8 * WQ_MAX_SB, rawfull = emptyB + 8 * WQ_MAX_SB, rawempty = rawfull + 8 * WQ_MAX_R,
+                   accum = rawempty + 8 * WQ_MAX_R;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int64_t row0 = (int64_t)blockIdx.x * GEMM_BM, tok0 = (int64_t)blockIdx.y * GEMM_BN;
-    const int nks = (int)(p.k / GEMM_BK);
+    const int64_t row0 = (int64_t)blockIdx.y * WQ_BM, tok0 = (int64_t)blockIdx.x * WQ_BN;
+    const int nks = 4 * p.nsc;
     volatile int *abort_flag = &abort_s;
 
     if (threadIdx.x == 0) {
         abort_s = 0;
-        for (int s = 0; s < GEMM_STAGES; s++) {
-            tc::mbar_init(full + 8 * s, 128);
-            tc::mbar_init(empty + 8 * s, 1);
+        for (int s = 0; s < WQ_SA; s++) {
+            tc::mbar_init(fullA + 8 * s, WQ_DW);  // one arrival per dequant warp
+            tc::mbar_init(emptyA + 8 * s, 1);
+        }
+        for (int s = 0; s < WQ_MAX_SB; s++) {
+            tc::mbar_init(fullB + 8 * s, 1);
+            tc::mbar_init(emptyB + 8 * s, 1);
+        }
+        for (int s = 0; s < WQ_MAX_R; s++) {
+            tc::mbar_init(rawfull + 8 * s, 1);
+            tc::mbar_init(rawempty + 8 * s, WQ_DW);
         }
         tc::mbar_init(accum, 1);
         tc::mbar_init_fence();
     }
-    if (warp == 4) tc::tmem_alloc(tc::smem_u32(&tmem_base_s), 256);
+    if (warp == 2) tc::tmem_alloc(tc::smem_u32(&tmem_base_s), 256);
     tc::fence_before_sync();
     __syncthreads();
     tc::fence_after_sync();
     const uint32_t tmem_d = tmem_base_s;
 
-    if (warp < 4) {
-        // ---------------- producers: one weight row and up to two token rows per thread ----------------
-        const int r = threadIdx.x;
-        for (int ks = 0; ks < nks; ks++) {
-            const int s = ks % GEMM_STAGES;
-            if (ks >= GEMM_STAGES && !tc::mbar_wait(empty + 8 * s, (uint32_t)((ks / GEMM_STAGES - 1) & 1), abort_flag)) {
-                abort_s = 1;
-                atomicExch(p.status, 11);
-                break;
-            }
-            uint8_t *at = smem + s * GEMM_STAGE_BYTES, *bt = at + GEMM_A_BYTES;
-            uint4 v[8];
-            dequant_row64(p, row0 + r, ks, v);
-            store_row_sw128(at, r, v);
-#pragma unroll 1
-            for (int half = 0; half < 2; half++) {
-                const int tr = r + 128 * half;
-                if (tr < ntok) {
-                    load_act_row64(p, tok0 + tr, ks, v);
-                    store_row_sw128(bt, tr, v);
+    if (warp == 0) {
+        // ---------------- raw weight super-chunks: one thread, bulk copies ----------------
+        if (lane == 0) {
+            for (int j = 0; j < p.nsc; j++) {
+                const int s = j % p.r;
+                if (j >= p.r && !tc::mbar_wait(rawempty + 8 * s, (uint32_t)((j / p.r - 1) & 1), abort_flag)) {
+                    abort_s = 1;
+                    atomicExch(p.status, 10);
+                    break;
+                }
+                const uint32_t dst = smem_s + raw_off + (uint32_t)(s * RAW);
+                tc::mbar_expect_tx(rawfull + 8 * s, RAW);
+                if (FMT == FMT_Q4K || FMT == FMT_Q80) {
+                    // the eight 16-row chunks of row-tile group blockIdx.y for k-block j are contiguous
+                    bulk_g2s(dst, p.qs + ((size_t)blockIdx.y * p.nsc + j) * RAW, RAW, rawfull + 8 * s);
+                } else {
+                    constexpr int SFB = RAW - WQ_TILE;
+                    bulk_g2s(dst, p.qs + ((size_t)blockIdx.y * p.nsc + j) * WQ_TILE, WQ_TILE, rawfull + 8 * s);
+                    bulk_g2s(dst + WQ_TILE, p.aux + ((size_t)blockIdx.y * p.nsc + j) * SFB, SFB, rawfull + 8 * s);
                 }
             }
-            tc::fence_proxy_async();
-            tc::mbar_arrive(full + 8 * s);
         }
-    } else if (lane == 0) {
+    } else if (warp == 1) {
+        // ---------------- activation tiles: one thread, bulk copies ----------------
+        if (lane == 0) {
+            const int halves = (p.ntok + 127) / 128;
+            const uint32_t hbytes = (uint32_t)(p.ntok > 128 ? WQ_TILE : bstage);
+            for (int ks = 0; ks < nks; ks++) {
+                const int s = ks % p.sb;
+                if (ks >= p.sb && !tc::mbar_wait(emptyB + 8 * s, (uint32_t)((ks / p.sb - 1) & 1), abort_flag)) {
+                    abort_s = 1;
+                    atomicExch(p.status, 11);
+                    break;
+                }
+                const uint32_t dst = smem_s + b_off + (uint32_t)(s * bstage);
+                tc::mbar_expect_tx(fullB + 8 * s, (uint32_t)bstage);
+                for (int h = 0; h < halves; h++)
+                    bulk_g2s(dst + h * WQ_TILE, p.xt + ((size_t)((tok0 >> 7) + h) * nks + ks) * WQ_TILE, hbytes, fullB + 8 * s);
+            }
+        }
+    } else if (warp == 2) {
         // ---------------- MMA issue: one thread ----------------
-        const uint32_t idesc = tc::idesc_f16(GEMM_BM, ntok, 0, 0);  // fp16 x fp16 -> f32
-        for (int ks = 0; ks < nks; ks++) {
-            const int s = ks % GEMM_STAGES;
-            if (!tc::mbar_wait(full + 8 * s, (uint32_t)((ks / GEMM_STAGES) & 1), abort_flag)) {
-                abort_s = 1;
-                atomicExch(p.status, 12);
+        if (lane == 0) {
+            const uint32_t idesc = tc::idesc_f16(WQ_BM, p.ntok, 0, 0);  // fp16 x fp16 -> f32
+            bool ok = true;
+            for (int ks = 0; ks < nks && ok; ks++) {
+                const int sa = ks % WQ_SA, sb = ks % p.sb;
+                ok = tc::mbar_wait(fullB + 8 * sb, (uint32_t)((ks / p.sb) & 1), abort_flag) &&
+                     tc::mbar_wait(fullA + 8 * sa, (uint32_t)((ks / WQ_SA) & 1), abort_flag);
+                if (!ok) {
+                    abort_s = 1;
+                    atomicExch(p.status, 12);
+                    break;
+                }
+                tc::fence_after_sync();
+                const uint64_t ad = tc::smem_desc_sw128(smem_s + a_off + sa * WQ_TILE);
+                const uint64_t bd = tc::smem_desc_sw128(smem_s + b_off + (uint32_t)(sb * bstage));
+#pragma unroll
+                for (int k4 = 0; k4 < 4; k4++) tc::mma_f16(tmem_d, ad + 2 * k4, bd + 2 * k4, idesc, (uint32_t)((ks | k4) != 0));
+                tc::mma_commit(emptyA + 8 * sa);  // both stages are free when these MMAs have read them
+                tc::mma_commit(emptyB + 8 * sb);
+            }
+            if (ok) tc::mma_commit(accum);
+        }
+    } else {
+        // ---------------- dequant warps, then epilogue ----------------
+        const int dw = warp - 3;
+        Dequant<FMT> dq;
+        dq.global = p.global_scale;
+        bool ok = true;
+        for (int j = 0; j < p.nsc && ok; j++) {
+            const int rs = j % p.r;
+            // waits are made warp-uniform: the dequant steps shuffle across the whole warp
+            if (!__all_sync(0xffffffffu, tc::mbar_wait(rawfull + 8 * rs, (uint32_t)((j / p.r) & 1), abort_flag))) {
+                ok = false;
                 break;
             }
-            tc::fence_after_sync();
-            const uint64_t ad = tc::smem_desc_sw128(smem_s + s * GEMM_STAGE_BYTES);
-            const uint64_t bd = tc::smem_desc_sw128(smem_s + s * GEMM_STAGE_BYTES + GEMM_A_BYTES);
-#pragma unroll
-            for (int k4 = 0; k4 < 4; k4++) tc::mma_f16(tmem_d, ad + 2 * k4, bd + 2 * k4, idesc, (uint32_t)((ks | k4) != 0));
-            tc::mma_commit(empty + 8 * s);  // frees the stage when these MMAs have read it
+            const uint8_t *raw = smem + raw_off + rs * RAW;
+            dq.begin(raw, dw, lane);
+#pragma unroll 1
+            for (int pp = 0; pp < 4; pp++) {
+                const int ks = 4 * j + pp, sa = ks % WQ_SA;
+                const bool freed = ks < WQ_SA || tc::mbar_wait(emptyA + 8 * sa, (uint32_t)((ks / WQ_SA - 1) & 1), abort_flag);
+                if (!__all_sync(0xffffffffu, freed)) {
+                    ok = false;
+                    break;
+                }
+                dq.step(raw, pp, smem + a_off + sa * WQ_TILE, dw, lane);
+                tc::fence_proxy_async();  // every writer makes its own stores visible to the tensor core's proxy
+                __syncwarp();
+                if (lane == 0) tc::mbar_arrive(fullA + 8 * sa);
+            }
+            if (ok && lane == 0) tc::mbar_arrive(rawempty + 8 * rs);  // the warp's reads of the super-chunk are done
         }
-        tc::mma_commit(accum);
-    }
-    __syncwarp();
-
-    if (warp < 4) {
-        // ---------------- epilogue: warp w owns TMEM lanes 32w .. 32w+31 = weight rows ----------------
-        bool ok = !abort_s && tc::mbar_wait(accum, 0u, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
         if (!ok && !abort_s) {
             abort_s = 1;
             atomicExch(p.status, 13);
         }
+        ok = ok && !abort_s && tc::mbar_wait(accum, 0u, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (ok) {
+            // warp w may read TMEM lanes 32 * (w % 4) .. + 31 = weight rows; the four warps of a quadrant take
+            // every fourth group of 32 token columns
             tc::fence_after_sync();
-            const int64_t row = row0 + threadIdx.x;
-            for (int c = 0; c < ntok; c += 32) {
+            const int quad = warp & 3;
+            const int64_t row = row0 + 32 * quad + lane;
+            for (int c = 32 * (dw >> 2); c < p.ntok; c += 32 * (WQ_DW / 4)) {
                 uint32_t v[32];
-                tc::tmem_ld32(tmem_d + ((uint32_t)(32 * warp) << 16) + (uint32_t)c, v);
+                tc::tmem_ld32(tmem_d + ((uint32_t)(32 * quad) << 16) + (uint32_t)c, v);
                 tc::tmem_ld_wait();
                 if (row < p.n) {
 #pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        const int64_t tok = tok0 + c + j;
-                        if (tok < p.m && c + j < ntok) {
-                            if (p.y_bf16) static_cast<__nv_bfloat16 *>(p.y)[tok * p.ldy + row] = __float2bfloat16_rn(__uint_as_float(v[j]));
-                            else static_cast<float *>(p.y)[tok * p.ldy + row] = __uint_as_float(v[j]);
+                    for (int jj = 0; jj < 32; jj++) {
+                        const int64_t tok = tok0 + c + jj;
+                        if (tok < p.m) {
+                            if (p.y_bf16) static_cast<__nv_bfloat16 *>(p.y)[tok * p.ldy + row] = __float2bfloat16_rn(__uint_as_float(v[jj]));
+                            else static_cast<float *>(p.y)[tok * p.ldy + row] = __uint_as_float(v[jj]);
                         }
                     }
                 }
             }
+        } else if (!abort_s) {
+            abort_s = 1;
+            atomicExch(p.status, 14);
         }
     }
     tc::fence_before_sync();
     __syncthreads();
-    if (warp == 4) tc::tmem_dealloc(tmem_d, 256);
+    if (warp == 2) tc::tmem_dealloc(tmem_d, 256);
 }
 
 // ---------------------------------------------------------------------------------------------
-int32_t gemm_launch(Ctx *c, const Weight *w, const void *a, int a_bf16, int64_t lda, int m, void *y, int y_bf16, int64_t ldy,
-                    cudaStream_t s) {
-    if (w->k % GEMM_BK) return fail(c, GLLMK_STATUS_INVALID_ARG, "gemm: k=%lld is not a multiple of %d", (long long)w->k, GEMM_BK);
-    const int align = a_bf16 ? 8 : 4;
-    if (((uintptr_t)a & 15) || (lda % align)) return fail(c, GLLMK_STATUS_INVALID_ARG, "gemm: activations must be 16-byte aligned rows");
+template <int FMT>
+static int32_t launch_wq(Ctx *c, const GemmParams &p, dim3 grid, size_t smem, cudaStream_t s) {
     static bool attr_set = false;
     if (!attr_set) {
-        GK_CUDA(c, cudaFuncSetAttribute(gemm_wq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM));
+        GK_CUDA(c, cudaFuncSetAttribute(gemm_wq_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, WQ_SMEM_LIMIT + 1024));
         attr_set = true;
     }
+    gemm_wq_kernel<FMT><<<grid, WQ_THREADS, smem, s>>>(p);
+    GK_CUDA(c, cudaGetLastError());
+    return GLLMK_STATUS_OK;
+}
+
+int32_t gemm_launch(Ctx *c, const Weight *w, const void *a, int a_bf16, int64_t lda, int m, void *y, int y_bf16, int64_t ldy,
+                    cudaStream_t s) {
+    const int align = a_bf16 ? 8 : 4;
+    if (((uintptr_t)a & 15) || (lda % align)) return fail(c, GLLMK_STATUS_INVALID_ARG, "gemm: activations must be 16-byte aligned rows");
+    if (w->k % 8) return fail(c, GLLMK_STATUS_INVALID_ARG, "gemm: k=%lld is not a multiple of 8", (long long)w->k);
+    const int fmt = w->qt == GLLMK_QUANT_Q4K ? FMT_Q4K : (w->qt == GLLMK_QUANT_Q8_0 ? FMT_Q80 : (w->qt == GLLMK_QUANT_NVFP4 ? FMT_NVFP4 : FMT_MXFP4));
+    const int raw = wq_raw_bytes(fmt);
     GemmParams p{};
     p.qs = static_cast<const uint8_t *>(w->qs);
     p.aux = static_cast<const uint8_t *>(w->aux);
-    p.qt = w->qt;
     p.n = w->n;
-    p.k = w->k;
-    p.nb = (w->qt == GLLMK_QUANT_Q8_0) ? w->nb8 : w->nb;
+    p.nsc = (int)((w->k + 255) / 256);
     p.global_scale = w->global_scale;
-    p.a = a;
-    p.a_bf16 = a_bf16;
-    p.lda = lda;
     p.m = m;
     p.y = y;
     p.y_bf16 = y_bf16;
     p.ldy = ldy;
     p.status = c->status_dev;
-    const int mtiles = (m + GEMM_BN - 1) / GEMM_BN;
-    // MMA N: the whole 256-token tile, or the remainder rounded up to a multiple of 32 when m is small
-    const int ntok = (m >= GEMM_BN) ? GEMM_BN : ((m + 31) / 32) * 32;
-    dim3 grid((unsigned)(w->n_pad / GEMM_BM), (unsigned)mtiles);
-    gemm_wq_kernel<<<grid, GEMM_THREADS, GEMM_SMEM, s>>>(p, ntok);
+    // MMA N: whole 256-token tiles, or the tokens rounded up to a multiple of 32 when there are at most 128
+    p.ntok = (m > 128) ? WQ_BN : ((m + 31) / 32) * 32;
+    const int mtiles = (m + WQ_BN - 1) / WQ_BN;
+    const int bstage = p.ntok * 128;
+    p.sb = WQ_MAX_SB;
+    if (WQ_SA * WQ_TILE + p.sb * bstage + 2 * raw > WQ_SMEM_LIMIT) p.sb = 3;
+    p.r = (WQ_SMEM_LIMIT - WQ_SA * WQ_TILE - p.sb * bstage) / raw;
+    if (p.r > WQ_MAX_R) p.r = WQ_MAX_R;
+    if (p.r > p.nsc) p.r = p.nsc;
+    if (p.r < 1) return fail(c, GLLMK_STATUS_RUNTIME_ERROR, "gemm: shared-memory plan does not fit");
+    const size_t smem = 1024 + (size_t)WQ_SA * WQ_TILE + (size_t)p.sb * bstage + (size_t)p.r * raw;
+    // activations -> fp16 tile images in the context's scratch
+    const int atiles = (p.ntok > 128) ? 2 * mtiles : 1;
+    const int nks = 4 * p.nsc;
+    int32_t rc = ensure_act(c, (size_t)atiles * nks * WQ_TILE);
+    if (rc) return rc;
+    p.xt = static_cast<const uint8_t *>(c->act);
+    stage_act_kernel<<<dim3((unsigned)nks, (unsigned)atiles), 256, 0, s>>>(a, a_bf16, lda, m, w->k, static_cast<uint8_t *>(c->act));
     GK_CUDA(c, cudaGetLastError());
-    return GLLMK_STATUS_OK;
+    dim3 grid((unsigned)mtiles, (unsigned)(w->n_pad / WQ_BM));
+    switch (fmt) {
+        case FMT_Q4K: return launch_wq<FMT_Q4K>(c, p, grid, smem, s);
+        case FMT_Q80: return launch_wq<FMT_Q80>(c, p, grid, smem, s);
+        case FMT_NVFP4: return launch_wq<FMT_NVFP4>(c, p, grid, smem, s);
+        default: return launch_wq<FMT_MXFP4>(c, p, grid, smem, s);
+    }
 }
 
 }  // namespace gllmk

@@ -3,14 +3,14 @@
 //   Y[t, r] = gW * gX * sum_k W4[r, k] * X4[t, k]      (NVFP4: E2M1 values, UE4M3 scale per 16 elements)
 //             (MXFP4: E2M1 values, UE8M0 scale per 32 elements, gW = gX = 1)
 //
-// Both operands are resident in the FP4 plane layout of common.cuh (packed nibbles [rows][k/2] + scale
-// bytes in 128-row x 4-scale atoms).  Per k-step of 256 elements (= one 128-byte swizzled row) a CTA
-// brings in, with TMA tile loads and bulk copies (no multicast):
-//   A = 128 weight rows x 128 B, B = up to 256 activation rows x 128 B, and their scale atoms;
+// Both operands are resident in the FP4 plane layout of common.cuh: packed nibbles stored as ready-made
+// 128-byte-swizzled shared-memory tile images (128 rows x 256 elements = 16 KB, contiguous) + scale bytes in
+// 128-row x 4-scale atoms.  Per k-step of 256 elements a CTA brings in, with plain bulk copies (no tensor
+// map, no multicast):
+//   A = one weight tile, B = one or two activation tiles, and their scale atoms;
 // one thread copies the scale atoms to tensor memory (tcgen05.cp) and issues four
 // tcgen05.mma.kind::mxf4nvf4.block_scale (K = 64 each; kind::mxf4 for MXFP4) into a 128 x 256 f32
 // accumulator in TMEM; four warps read it back, apply the two per-tensor scales and store Y.
-#include <cuda.h>
 #include <cuda_bf16.h>
 
 #include "common.cuh"
@@ -19,7 +19,6 @@
 namespace gllmk {
 
 constexpr int F4_BM = 128, F4_BN = 256;
-constexpr int F4_BK_BYTES = 128;            // 256 FP4 elements per stage
 constexpr int F4_STAGES = 4;
 constexpr int F4_A_BYTES = F4_BM * 128, F4_B_BYTES = F4_BN * 128;
 constexpr int F4_SFA_BYTES = 2048;          // 4 atoms (128 rows x 16 scales of 16 el; MXFP4 uses 2 of them)
@@ -31,6 +30,7 @@ constexpr uint32_t F4_TMEM_COLS = 512;      // 256 accumulator + 2 x (16 SFA + 3
 constexpr uint32_t F4_TMEM_SF = 256;        // scale-factor columns, two sets of 48 used by alternate k-steps
 
 struct Fp4Params {
+    const uint8_t *qw, *qx;  // data planes (tile images)
     const uint8_t *sfw;  // weight scale plane
     const uint8_t *sfx;  // activation scale plane
     int nv;              // 1: NVFP4 (scale per 16, UE4M3), 0: MXFP4 (scale per 32, UE8M0)
@@ -44,11 +44,6 @@ struct Fp4Params {
     int *status;
 };
 
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *tmap, int x, int y, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(dst),
-                 "l"(tmap), "r"(x), "r"(y), "r"(bar)
-                 : "memory");
-}
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst), "l"(src),
                  "r"(bytes), "r"(bar)
@@ -61,8 +56,7 @@ __device__ __forceinline__ uint64_t sf_desc(uint32_t smem_addr) {
 }
 
 __global__ void __launch_bounds__(F4_THREADS, 1)
-gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
-                const __grid_constant__ Fp4Params p, const int ntok) {
+gemm_fp4_kernel(const __grid_constant__ Fp4Params p, const int ntok) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bars[2 * F4_STAGES + 1];
     __shared__ uint32_t tmem_base_s;
@@ -94,10 +88,11 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     if (warp == 0 && lane == 0) {
         // ---------------- TMA producer ----------------
         const uint32_t sf_bytes = (uint32_t)atoms_per_stage * 512u;
-        // 128-row groups of the activation tile that exist in the scale plane (the data rows beyond it are
-        // zero-filled by TMA; their stale scales only reach output columns that are never stored)
+        // 128-row groups of the activation tile that exist in the planes (rows beyond them keep whatever the
+        // stage held: they only reach output columns that are never stored)
         const int btiles = min((ntok + 127) / 128, (int)(p.x_row_tiles - (tok0 >> 7)));
-        const uint32_t tx = F4_A_BYTES + (uint32_t)ntok * 128u + sf_bytes * (1u + (uint32_t)btiles);
+        const uint32_t tx = F4_A_BYTES + (16384u + sf_bytes) * (uint32_t)btiles + sf_bytes;
+        const size_t ktiles = (size_t)nks;
         for (int ks = 0; ks < nks; ks++) {
             const int s = ks % F4_STAGES;
             if (ks >= F4_STAGES && !tc::mbar_wait(empty + 8 * s, (uint32_t)((ks / F4_STAGES - 1) & 1), abort_flag)) {
@@ -107,9 +102,9 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
             }
             const uint32_t st = smem_s + s * F4_STAGE_BYTES;
             tc::mbar_expect_tx(full + 8 * s, tx);
-            tma_load_2d(st, &tmap_w, ks * 128, (int)row0, full + 8 * s);
-            // the activation tensor map has a box of `ntok` rows (128 or 256): one load
-            tma_load_2d(st + F4_A_BYTES, &tmap_x, ks * 128, (int)tok0, full + 8 * s);
+            bulk_load(st, p.qw + ((size_t)blockIdx.x * ktiles + ks) * 16384, 16384u, full + 8 * s);
+            for (int bt = 0; bt < btiles; bt++)
+                bulk_load(st + F4_A_BYTES + bt * 16384, p.qx + (((size_t)(tok0 >> 7) + bt) * ktiles + ks) * 16384, 16384u, full + 8 * s);
             bulk_load(st + F4_A_BYTES + F4_B_BYTES,
                       p.sfw + ((size_t)blockIdx.x * atoms_per_row_tile + (size_t)ks * atoms_per_stage) * 512, sf_bytes, full + 8 * s);
             for (int bt = 0; bt < btiles; bt++)
@@ -203,35 +198,11 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
 }
 
 // ---------------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-// Tensor map over an FP4 data plane [rows][k/2] bytes: boxes of 128 bytes x box_rows rows, 128-byte swizzle.
-static int32_t make_plane_tmap(Ctx *c, const Weight *w, int box_rows, CUtensorMap *out) {
-    static EncodeTiledFn encode = nullptr;
-    if (!encode) {
-        void *fn = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        GK_CUDA(c, cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
-        if (!fn || q != cudaDriverEntryPointSuccess) return fail(c, GLLMK_STATUS_RUNTIME_ERROR, "cuTensorMapEncodeTiled not available");
-        encode = reinterpret_cast<EncodeTiledFn>(fn);
-    }
-    const cuuint64_t dims[2] = {(cuuint64_t)(w->k / 2), (cuuint64_t)w->n_pad};
-    const cuuint64_t strides[1] = {(cuuint64_t)(w->k / 2)};
-    const cuuint32_t box[2] = {128u, (cuuint32_t)box_rows};
-    const cuuint32_t estr[2] = {1u, 1u};
-    const CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w->qs, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(c, GLLMK_STATUS_RUNTIME_ERROR, "cuTensorMapEncodeTiled failed (%d)", (int)r);
-    return GLLMK_STATUS_OK;
-}
-
 // w: weights [n, k]; x: activations [m, k] in the same FP4 format, uploaded like a weight.
 int32_t gemm_fp4_launch(Ctx *c, const Weight *w, const Weight *x, void *y, int y_bf16, int64_t ldy, cudaStream_t s) {
     if (w->qt != x->qt || (w->qt != GLLMK_QUANT_NVFP4 && w->qt != GLLMK_QUANT_MXFP4))
         return fail(c, GLLMK_STATUS_UNSUPPORTED, "gemm_fp4: both operands must be NVFP4 or both MXFP4");
-    if (w->k != x->k || (w->k % 256)) return fail(c, GLLMK_STATUS_INVALID_ARG, "gemm_fp4: k must match and be a multiple of 256");
+    if (w->k != x->k) return fail(c, GLLMK_STATUS_INVALID_ARG, "gemm_fp4: k of the two operands must match");
     static bool attr_set = false;
     if (!attr_set) {
         GK_CUDA(c, cudaFuncSetAttribute(gemm_fp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)F4_SMEM));
@@ -239,16 +210,14 @@ int32_t gemm_fp4_launch(Ctx *c, const Weight *w, const Weight *x, void *y, int y
     }
     const int m = (int)x->n;
     const int ntok = (m > 128) ? 256 : 128;
-    CUtensorMap tw, tx;
-    int32_t rc = make_plane_tmap(c, w, F4_BM, &tw);
-    if (!rc) rc = make_plane_tmap(c, x, ntok, &tx);
-    if (rc) return rc;
     Fp4Params p{};
+    p.qw = static_cast<const uint8_t *>(w->qs);
+    p.qx = static_cast<const uint8_t *>(x->qs);
     p.sfw = static_cast<const uint8_t *>(w->aux);
     p.sfx = static_cast<const uint8_t *>(x->aux);
     p.nv = w->qt == GLLMK_QUANT_NVFP4;
     p.n = w->n;
-    p.k = w->k;
+    p.k = w->k_pad;
     p.m = m;
     p.x_row_tiles = x->n_pad / 128;
     p.scale = w->global_scale * x->global_scale;
@@ -257,7 +226,7 @@ int32_t gemm_fp4_launch(Ctx *c, const Weight *w, const Weight *x, void *y, int y
     p.ldy = ldy;
     p.status = c->status_dev;
     dim3 grid((unsigned)(w->n_pad / F4_BM), (unsigned)((m + F4_BN - 1) / F4_BN));
-    gemm_fp4_kernel<<<grid, F4_THREADS, F4_SMEM, s>>>(tw, tx, p, ntok);
+    gemm_fp4_kernel<<<grid, F4_THREADS, F4_SMEM, s>>>(p, ntok);
     GK_CUDA(c, cudaGetLastError());
     return GLLMK_STATUS_OK;
 }

@@ -229,72 +229,68 @@ __global__ void dequant_q80(const uint8_t *__restrict__ chunks, float *__restric
 }
 
 // ================================ MXFP4 / NVFP4 ============================================
-__device__ __forceinline__ size_t sf_offset(int64_t row, int64_t s, int64_t s_per_row) {
-    const int64_t atoms_per_rowtile = s_per_row >> 2;
-    const size_t atom = (size_t)(row >> 7) * (size_t)atoms_per_rowtile + (size_t)(s >> 2);
-    return atom * 512 + (size_t)(row & 31) * 16 + (size_t)((row & 127) >> 5) * 4 + (size_t)(s & 3);
-}
+__device__ __forceinline__ size_t sf_offset(int64_t row, int64_t s, int64_t s_per_row) { return fp4_sf_offset(row, s, s_per_row); }
 // mode 0: MXFP4 split (blocks [n][k/2], scales [n][k/32]); mode 1: MXFP4 inline 17-byte blocks;
 // mode 2: NVFP4 36-byte blocks.  Thread = 4 data bytes (8 elements).
 __global__ void repack_fp4_data(const uint8_t *__restrict__ blocks, uint32_t *__restrict__ data, int64_t n,
-                                int64_t k, int mode, size_t total) {
-    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // row_pad * (k/8) + w
+                                int64_t k, int64_t k_pad, int mode, size_t total) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // row_pad * (k_pad/8) + w
     if (idx >= total) return;
-    const int64_t wpr = k >> 3;
+    const int64_t wpr = k_pad >> 3;
     const int64_t row = (int64_t)(idx / (size_t)wpr), w = (int64_t)(idx % (size_t)wpr);
     uint32_t v = 0;
-    if (row < n) {
+    if (row < n && w < (k >> 3)) {
         const uint8_t *p;
         if (mode == 0) p = blocks + (size_t)row * (k >> 1) + 4 * w;
         else if (mode == 1) p = blocks + ((size_t)row * (k >> 5) + (w >> 2)) * 17 + 1 + 4 * (w & 3);
         else p = blocks + ((size_t)row * (k >> 6) + (w >> 3)) * 36 + 4 + 4 * (w & 7);
         v = (uint32_t)p[0] | ((uint32_t)p[1] << 8) | ((uint32_t)p[2] << 16) | ((uint32_t)p[3] << 24);
     }
-    data[idx] = v;
+    data[fp4_data_offset(row, 4 * w, k_pad) >> 2] = v;
 }
 __global__ void repack_fp4_sf(const uint8_t *__restrict__ blocks, const uint8_t *__restrict__ scales,
-                              uint8_t *__restrict__ sf, int64_t n, int64_t k, int mode, size_t total) {
-    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // row_pad * s_per_row + s
+                              uint8_t *__restrict__ sf, int64_t n, int64_t k, int64_t k_pad, int mode, size_t total) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // row_pad * padded s_per_row + s
     if (idx >= total) return;
-    const int64_t spr = (mode == 2) ? (k >> 4) : (k >> 5);
-    const int64_t row = (int64_t)(idx / (size_t)spr), s = (int64_t)(idx % (size_t)spr);
+    const int64_t spr = (mode == 2) ? (k >> 4) : (k >> 5), spr_pad = (mode == 2) ? (k_pad >> 4) : (k_pad >> 5);
+    const int64_t row = (int64_t)(idx / (size_t)spr_pad), s = (int64_t)(idx % (size_t)spr_pad);
     uint8_t v = 0;
-    if (row < n) {
+    if (row < n && s < spr) {
         if (mode == 0) v = scales[(size_t)row * spr + s];
         else if (mode == 1) v = blocks[((size_t)row * spr + s) * 17];
         else v = blocks[((size_t)row * (k >> 6) + (s >> 2)) * 36 + (s & 3)];
     }
-    sf[sf_offset(row, s, spr)] = v;
+    sf[sf_offset(row, s, spr_pad)] = v;
 }
 __global__ void unpack_fp4(const uint8_t *__restrict__ data, const uint8_t *__restrict__ sf, uint8_t *__restrict__ blocks,
-                           uint8_t *__restrict__ scales, int64_t n, int64_t k, int nv, size_t total) {
+                           uint8_t *__restrict__ scales, int64_t n, int64_t k, int64_t k_pad, int nv, size_t total) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // row * (k/2) + byte
     if (idx >= total) return;
     const int64_t bpr = k >> 1;
     const int64_t row = (int64_t)(idx / (size_t)bpr), by = (int64_t)(idx % (size_t)bpr);
-    const uint8_t v = data[idx];
+    const uint8_t v = data[fp4_data_offset(row, by, k_pad)];
     if (!nv) {
         blocks[idx] = v;
-        if ((by & 15) == 0) scales[(size_t)row * (k >> 5) + (by >> 4)] = sf[sf_offset(row, by >> 4, k >> 5)];
+        if ((by & 15) == 0) scales[(size_t)row * (k >> 5) + (by >> 4)] = sf[sf_offset(row, by >> 4, k_pad >> 5)];
     } else {
         uint8_t *blk = blocks + ((size_t)row * (k >> 6) + (by >> 5)) * 36;
         blk[4 + (by & 31)] = v;
-        if ((by & 7) == 0) blk[(by & 31) >> 3] = sf[sf_offset(row, by >> 3, k >> 4)];
+        if ((by & 7) == 0) blk[(by & 31) >> 3] = sf[sf_offset(row, by >> 3, k_pad >> 4)];
     }
     (void)n;
 }
 // thread = 4 data bytes -> 8 f32.  MXFP4: LUT[code] * e8m0 (quant_mxfp4.rs:95-108);
 // NVFP4: (global * e4m3(sub)) * LUT[code] (quant.rs:77-86).
 __global__ void dequant_fp4(const uint32_t *__restrict__ data, const uint8_t *__restrict__ sf, float *__restrict__ out,
-                            int64_t n, int64_t k, int nv, float global, size_t total) {
+                            int64_t n, int64_t k, int64_t k_pad, int nv, float global, size_t total) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // row * (k/8) + w
     if (idx >= total) return;
     const int64_t wpr = k >> 3;
     const int64_t row = (int64_t)(idx / (size_t)wpr), w = (int64_t)(idx % (size_t)wpr);
-    const uint32_t v = data[idx];
+    const uint32_t v = data[fp4_data_offset(row, 4 * w, k_pad) >> 2];
     float s;
-    if (!nv) s = e8m0_to_f32(sf[sf_offset(row, w >> 2, k >> 5)]);
-    else s = __fmul_rn(global, e4m3_to_f32(sf[sf_offset(row, w >> 1, k >> 4)]));
+    if (!nv) s = e8m0_to_f32(sf[sf_offset(row, w >> 2, k_pad >> 5)]);
+    else s = __fmul_rn(global, e4m3_to_f32(sf[sf_offset(row, w >> 1, k_pad >> 4)]));
     float r[8];
 #pragma unroll
     for (int i = 0; i < 8; i++) {
@@ -360,11 +356,11 @@ int32_t repack_upload(Ctx *c, Weight *w, const void *blocks, const void *scales,
         repack_q80_d<<<grid_for(td, 256), 256, 0, s>>>(src, (uint8_t *)w->qs, w->n, w->nb, w->nb8, td);
     } else {
         const int mode = (w->qt == GLLMK_QUANT_NVFP4) ? 2 : (scales ? 0 : 1);
-        const int64_t spr = (mode == 2) ? (w->k >> 4) : (w->k >> 5);
-        const size_t td = (size_t)w->n_pad * (w->k >> 3), ts = (size_t)w->n_pad * spr;
-        repack_fp4_data<<<grid_for(td, 256), 256, 0, s>>>(src, (uint32_t *)w->qs, w->n, w->k, mode, td);
+        const int64_t spr = (mode == 2) ? (w->k_pad >> 4) : (w->k_pad >> 5);
+        const size_t td = (size_t)w->n_pad * (w->k_pad >> 3), ts = (size_t)w->n_pad * spr;
+        repack_fp4_data<<<grid_for(td, 256), 256, 0, s>>>(src, (uint32_t *)w->qs, w->n, w->k, w->k_pad, mode, td);
         repack_fp4_sf<<<grid_for(ts, 256), 256, 0, s>>>(src, (const uint8_t *)scales, (uint8_t *)w->aux, w->n, w->k,
-                                                        mode, ts);
+                                                        w->k_pad, mode, ts);
     }
     GK_CUDA(c, cudaGetLastError());
     return GLLMK_STATUS_OK;
@@ -381,7 +377,7 @@ int32_t repack_unpack(Ctx *c, const Weight *w, void *blocks, void *scales, cudaS
     } else {
         const size_t t = (size_t)w->n * (w->k >> 1);
         unpack_fp4<<<grid_for(t, 256), 256, 0, s>>>((const uint8_t *)w->qs, (const uint8_t *)w->aux, dst,
-                                                    (uint8_t *)scales, w->n, w->k, w->qt == GLLMK_QUANT_NVFP4, t);
+                                                    (uint8_t *)scales, w->n, w->k, w->k_pad, w->qt == GLLMK_QUANT_NVFP4, t);
     }
     GK_CUDA(c, cudaGetLastError());
     return GLLMK_STATUS_OK;
@@ -397,7 +393,7 @@ int32_t dequant_matrix(Ctx *c, const Weight *w, float *out, cudaStream_t s) {
     } else {
         const size_t t = (size_t)w->n * (w->k >> 3);
         dequant_fp4<<<grid_for(t, 256), 256, 0, s>>>((const uint32_t *)w->qs, (const uint8_t *)w->aux, out, w->n, w->k,
-                                                     w->qt == GLLMK_QUANT_NVFP4, w->global_scale, t);
+                                                     w->k_pad, w->qt == GLLMK_QUANT_NVFP4, w->global_scale, t);
     }
     GK_CUDA(c, cudaGetLastError());
     return GLLMK_STATUS_OK;

@@ -1,6 +1,6 @@
 """Prefill GEMM (tcgen05) against the CPU oracle: decode of the packed bytes (reference formulas) followed by
 the reference's f32 GEMM loop order.  Bar: max_i |y_i - ref_i| / max(|ref_i|, rms(ref)) <= 1e-2 (weights and
-activations are staged in bf16, accumulation is f32)."""
+activations are staged in fp16, accumulation is f32)."""
 import numpy as np
 import pytest
 
@@ -76,10 +76,21 @@ def test_gemm_rejects_bad_arguments(gk, K, oracle):
     import torch
     qt, blocks, _, _, _ = quantized(oracle, gk, "q8_0", 16, 96, 5)
     w = K.upload(qt, 16, 96, blocks)
-    with pytest.raises(gk.GllmkError) as e:  # k % 64 != 0
-        K.gemm(w, torch.zeros((32, 96), device="cuda"))
+    with pytest.raises(gk.GllmkError) as e:  # activation rows must be 16-byte aligned: lda % 4 for f32
+        K.gemm(w, torch.zeros((32, 98), device="cuda")[:, :96])
     assert e.value.status == gk.Status.INVALID_ARG
     w.free()
+
+
+def test_gemm_q8_0_ragged_k(gk, K, oracle):
+    # k = 96: three blocks of a group of eight; the rest of the 256-wide k-step is zero padding
+    assert run_case(gk, K, oracle, "q8_0", 144, 96, 40, seed=15) <= 1e-2
+
+
+def test_gemm_fp4_weights_ragged_k(gk, K, oracle):
+    # k not a multiple of 256: the FP4 planes are padded with zero codes
+    assert run_case(gk, K, oracle, "mxfp4", 128, 320, 64, seed=16, a_bf16=True) <= 1e-2
+    assert run_case(gk, K, oracle, "nvfp4", 128, 192, 64, seed=17, a_bf16=True) <= 1e-2
 
 
 # ---- both operands FP4: native block-scaled MMA ---------------------------------------------------
