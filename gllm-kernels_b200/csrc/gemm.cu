@@ -3,7 +3,10 @@
 //   Y[t, r] = sum_k W[r, k] * X[t, k]        t < M tokens (M > 16), r < N weight rows
 //
 // Weight-only formats (Q4_K, Q8_0, MXFP4, NVFP4 weights with bf16/f32 activations), gemm_wq_kernel.
-// A CTA owns 128 weight rows (UMMA M) x up to 256 tokens (UMMA N) and walks K in steps of 64 (64 fp16 = one 128-byte swizzle row):
+// A CTA owns MT (1 or 2) tiles of 128 weight rows (UMMA M, one TMEM accumulator each) x up to 256 tokens
+// (UMMA N) and walks K in steps of 64 (64 fp16 = one 128-byte swizzle row).  With MT = 2 one activation tile
+// feeds two MMAs, which halves the shared-memory fill traffic per flop (the L2 -> SM path, not the tensor
+// core, is what bounds a 128 x 256 tile):
 //   * the RAW quantized weights of its 128 rows arrive as one bulk copy per 256 k ("super-chunk": the same
 //     contiguous byte range the decode GEMV streams) into a shared-memory ring, mbarrier-tracked;
 //   * four dequant warps turn a quarter of a super-chunk (64 k) into fp16 with packed half2 arithmetic and
@@ -26,9 +29,9 @@ namespace gllmk {
 constexpr int WQ_BM = 128;         // weight rows per CTA (UMMA M)
 constexpr int WQ_BN = 256;         // tokens per CTA (UMMA N, <= 256)
 constexpr int WQ_TILE = 16384;     // one operand tile: 128 rows x 128 bytes
-constexpr int WQ_SA = 3;           // operand A (dequantized weights) stages
-constexpr int WQ_MAX_SB = 4;       // operand B (activation) stages, at most
-constexpr int WQ_MAX_R = 4;        // raw super-chunk ring, at most
+constexpr int WQ_SA = 4;           // operand A (dequantized weight tiles) ring: one slot per dequant group
+constexpr int WQ_MAX_SB = 12;      // operand B (activation) stages, at most
+constexpr int WQ_MAX_R = 6;        // raw super-chunk ring, at most
 constexpr int WQ_DW = 16;          // dequant warps
 constexpr int WQ_THREADS = 96 + 32 * WQ_DW;  // warp 0: raw copies, warp 1: activation copies, warp 2: MMA + TMEM, then dequant / epilogue warps
 constexpr int WQ_SMEM_LIMIT = 232448 - 1024 - 1024;  // ring space: 227 KB less the static variables' share and the alignment slack
@@ -50,7 +53,8 @@ struct GemmParams {
     int y_bf16;
     int64_t ldy;
     int ntok;            // MMA N of this launch (multiple of 32, <= 256)
-    int sb, r;           // ring depths
+    int row_tiles;       // 128-row tiles of the weight matrix
+    int sb, r;           // ring depths: B stages, raw super-chunks
     int *status;
 };
 
@@ -141,85 +145,109 @@ __device__ __forceinline__ __half2 scale_h2(float s) {
     return u32_as_h2(r);
 }
 
-// ---- dequant of one k-step (64 k) of the CTA's 128 weight rows into an operand A tile ----------------
-// Sixteen dequant warps (four per scheduler, so that the short dependent chains of one warp hide behind the
-// others); dw = dequant warp 0..15, lane = 4*g + t.  `raw` is the super-chunk in shared memory, p = k-step
+// ---- dequant of one k-step (64 k) of a 128-row weight tile into an operand A tile --------------------
+// The sixteen dequant warps form four groups of four; a group turns out a whole A tile (128 rows x 64 k) on
+// its own and the groups work on four consecutive tiles at once, so the latency of one tile's chain (wait,
+// shared-memory loads, shuffles, half2 arithmetic, stores, proxy fence, arrive) is overlapped four ways.
+// wg = warp inside the group (0..3), lane = 4*g + t.  `raw` is the super-chunk in shared memory, p = k-step
 // inside it (0..3), `at` the A tile.
 //
-// Q4_K / Q8_0: warp dw handles the 16-row chunk c = dw % 8, rows g + 8h with h = dw / 8; its lane reads its
-// half of the uint4 the device layout keeps for lane (bytes 8t..8t+7 of the row's 32-byte group) and
-// produces the 16-byte fp16 groups t (low nibbles / even block) and 4 + t (high nibbles / odd block).
+// Q4_K / Q8_0: warp wg handles the 16-row chunks wg and wg + 4; its lane reads the uint4 the device layout
+// keeps for it (rows g and g + 8, bytes 8t..8t+7 of the 32-byte group) and produces, for both rows, the
+// 16-byte fp16 groups t (low nibbles / even block) and 4 + t (high nibbles / odd block).
 template <int FMT>
 struct Dequant;
 
 template <>
 struct Dequant<FMT_Q4K> {
-    // (d*sc, -dmin*m) of sub-blocks 2t and 2t+1 of this thread's row; the k-step p needs sub-blocks 2p and
-    // 2p+1, which lane (lane & ~3) | p holds
-    __half2 ent[2];
     float global;
-    __device__ __forceinline__ void begin(const uint8_t *raw, int dw, int lane) {
-        const int g = lane >> 2, t = lane & 3, c = dw & 7, h = dw >> 3, rr = g + 8 * h;
-        const uint8_t *chunk = raw + c * Q4K_CHUNK;
-        const uint32_t dd = *reinterpret_cast<const uint32_t *>(chunk + 2304 + (g * 2 + h) * 4);
-        const float d = __half2float(__ushort_as_half((unsigned short)(dd & 0xFFFFu)));
-        const float dmin = __half2float(__ushort_as_half((unsigned short)(dd >> 16)));
-        const uint32_t sc = *reinterpret_cast<const unsigned short *>(chunk + 2048 + rr * 16 + 2 * t);
-        const uint32_t mn = *reinterpret_cast<const unsigned short *>(chunk + 2048 + rr * 16 + 8 + 2 * t);
-        ent[0] = __floats2half2_rn(d * (float)(sc & 0xFFu), -(dmin * (float)(mn & 0xFFu)));
-        ent[1] = __floats2half2_rn(d * (float)(sc >> 8), -(dmin * (float)(mn >> 8)));
-    }
-    __device__ __forceinline__ void step(const uint8_t *raw, int p, uint8_t *at, int dw, int lane) {
-        const int g = lane >> 2, t = lane & 3, c = dw & 7, h = dw >> 3, src = (lane & ~3) | p;
-        const uint2 q = *reinterpret_cast<const uint2 *>(raw + c * Q4K_CHUNK + (p * 32 + lane) * 16 + 8 * h);
-        const __half2 e_lo = u32_as_h2(__shfl_sync(0xffffffffu, h2_as_u32(ent[0]), src));
-        const __half2 e_hi = u32_as_h2(__shfl_sync(0xffffffffu, h2_as_u32(ent[1]), src));
-        uint4 lo, hi;
-        q4k_word(q.x, e_lo, e_hi, lo.x, lo.y, hi.x, hi.y);
-        q4k_word(q.y, e_lo, e_hi, lo.z, lo.w, hi.z, hi.w);
-        uint8_t *rowp = at + (16 * c + 8 * h + g) * 128;  // (row & 7) == g
-        *reinterpret_cast<uint4 *>(rowp + ((t ^ g) << 4)) = lo;
-        *reinterpret_cast<uint4 *>(rowp + (((4 + t) ^ g) << 4)) = hi;
+    __device__ __forceinline__ void step(const uint8_t *raw, int p, uint8_t *at, int wg, int lane) {
+        const int g = lane >> 2, t = lane & 3;
+        // (d*sc, -dmin*m) of sub-blocks 2p and 2p+1: lane t works them out for (chunk, row) pair t of the four
+        // pairs its quad shares; everyone fetches all four pairs with shuffles
+        __half2 mine_lo, mine_hi;
+        {
+            const uint8_t *chunk = raw + (wg + 4 * (t >> 1)) * Q4K_CHUNK;
+            const int h = t & 1, rr = g + 8 * h;
+            const uint32_t dd = *reinterpret_cast<const uint32_t *>(chunk + 2304 + (g * 2 + h) * 4);
+            const float d = __half2float(__ushort_as_half((unsigned short)(dd & 0xFFFFu)));
+            const float dmin = __half2float(__ushort_as_half((unsigned short)(dd >> 16)));
+            const uint32_t sc = *reinterpret_cast<const unsigned short *>(chunk + 2048 + rr * 16 + 2 * p);
+            const uint32_t mn = *reinterpret_cast<const unsigned short *>(chunk + 2048 + rr * 16 + 8 + 2 * p);
+            mine_lo = __floats2half2_rn(d * (float)(sc & 0xFFu), -(dmin * (float)(mn & 0xFFu)));
+            mine_hi = __floats2half2_rn(d * (float)(sc >> 8), -(dmin * (float)(mn >> 8)));
+        }
+#pragma unroll
+        for (int ci = 0; ci < 2; ci++) {
+            const int c = wg + 4 * ci;
+            const uint4 q = *reinterpret_cast<const uint4 *>(raw + c * Q4K_CHUNK + (p * 32 + lane) * 16);
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const int src = (lane & ~3) | (2 * ci + h);
+                const __half2 e_lo = u32_as_h2(__shfl_sync(0xffffffffu, h2_as_u32(mine_lo), src));
+                const __half2 e_hi = u32_as_h2(__shfl_sync(0xffffffffu, h2_as_u32(mine_hi), src));
+                uint4 lo, hi;
+                q4k_word(h ? q.z : q.x, e_lo, e_hi, lo.x, lo.y, hi.x, hi.y);
+                q4k_word(h ? q.w : q.y, e_lo, e_hi, lo.z, lo.w, hi.z, hi.w);
+                uint8_t *rowp = at + (16 * c + 8 * h + g) * 128;  // (row & 7) == g
+                *reinterpret_cast<uint4 *>(rowp + ((t ^ g) << 4)) = lo;
+                *reinterpret_cast<uint4 *>(rowp + (((4 + t) ^ g) << 4)) = hi;
+            }
+        }
     }
 };
 
 template <>
 struct Dequant<FMT_Q80> {
     float global;
-    __device__ __forceinline__ void begin(const uint8_t *, int, int) {}
-    __device__ __forceinline__ void step(const uint8_t *raw, int p, uint8_t *at, int dw, int lane) {
-        const int g = lane >> 2, t = lane & 3, c = dw & 7, h = dw >> 3, rr = g + 8 * h;
-        const uint8_t *chunk = raw + c * Q80_CHUNK;
-        const uint2 q0 = *reinterpret_cast<const uint2 *>(chunk + ((2 * p) * 32 + lane) * 16 + 8 * h);
-        const uint2 q1 = *reinterpret_cast<const uint2 *>(chunk + ((2 * p + 1) * 32 + lane) * 16 + 8 * h);
-        const __half2 dd = u32_as_h2(*reinterpret_cast<const uint32_t *>(chunk + 4096 + (rr * 8 + 2 * p) * 2));
-        uint4 lo, hi;
-        q80_word(q0.x, __low2half2(dd), lo.x, lo.y);
-        q80_word(q0.y, __low2half2(dd), lo.z, lo.w);
-        q80_word(q1.x, __high2half2(dd), hi.x, hi.y);
-        q80_word(q1.y, __high2half2(dd), hi.z, hi.w);
-        uint8_t *rowp = at + (16 * c + 8 * h + g) * 128;
-        *reinterpret_cast<uint4 *>(rowp + ((t ^ g) << 4)) = lo;
-        *reinterpret_cast<uint4 *>(rowp + (((4 + t) ^ g) << 4)) = hi;
+    __device__ __forceinline__ void step(const uint8_t *raw, int p, uint8_t *at, int wg, int lane) {
+        const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+        for (int ci = 0; ci < 2; ci++) {
+            const int c = wg + 4 * ci;
+            const uint8_t *chunk = raw + c * Q80_CHUNK;
+            const uint4 q0 = *reinterpret_cast<const uint4 *>(chunk + ((2 * p) * 32 + lane) * 16);
+            const uint4 q1 = *reinterpret_cast<const uint4 *>(chunk + ((2 * p + 1) * 32 + lane) * 16);
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const int rr = g + 8 * h;
+                const __half2 dd = u32_as_h2(*reinterpret_cast<const uint32_t *>(chunk + 4096 + (rr * 8 + 2 * p) * 2));
+                uint4 lo, hi;
+                q80_word(h ? q0.z : q0.x, __low2half2(dd), lo.x, lo.y);
+                q80_word(h ? q0.w : q0.y, __low2half2(dd), lo.z, lo.w);
+                q80_word(h ? q1.z : q1.x, __high2half2(dd), hi.x, hi.y);
+                q80_word(h ? q1.w : q1.y, __high2half2(dd), hi.z, hi.w);
+                uint8_t *rowp = at + (16 * c + 8 * h + g) * 128;
+                *reinterpret_cast<uint4 *>(rowp + ((t ^ g) << 4)) = lo;
+                *reinterpret_cast<uint4 *>(rowp + (((4 + t) ^ g) << 4)) = hi;
+            }
+        }
     }
 };
 
 // FP4: the raw super-chunk is the row tile's swizzled data image (16 KB) followed by its scale atoms (512 B
-// each: [row % 32][row / 32][4 scales]).  Thread = (weight row r = 32 * (dw % 4) + lane, quarter = dw / 4):
-// 16 of the row's 64 elements of this k-step.
+// each: [row % 32][row / 32][4 scales]).  Thread = weight row 32 * wg + lane.
 template <int FMT>
 struct DequantFp4 {
     float global;
-    __device__ __forceinline__ void begin(const uint8_t *, int, int) {}
-    __device__ __forceinline__ void step(const uint8_t *raw, int p, uint8_t *at, int dw, int lane) {
-        const int rq = dw & 3, r = 32 * rq + lane, qtr = dw >> 2;
-        const uint2 v = *reinterpret_cast<const uint2 *>(raw + tc::sw128_offset(r, 2 * p + (qtr >> 1)) + 8 * (qtr & 1));
-        __half2 s;
-        if (FMT == FMT_NVFP4) s = scale_h2(global * e4m3_to_f32(raw[WQ_TILE + p * 512 + lane * 16 + rq * 4 + qtr]));
-        else s = scale_h2(e8m0_to_f32(raw[WQ_TILE + (p >> 1) * 512 + lane * 16 + rq * 4 + 2 * (p & 1) + (qtr >> 1)]));
+    __device__ __forceinline__ void step(const uint8_t *raw, int p, uint8_t *at, int wg, int lane) {
+        const int r = 32 * wg + lane;
+        const uint4 v0 = *reinterpret_cast<const uint4 *>(raw + tc::sw128_offset(r, 2 * p));
+        const uint4 v1 = *reinterpret_cast<const uint4 *>(raw + tc::sw128_offset(r, 2 * p + 1));
+        const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+        __half2 s[4];
+        if (FMT == FMT_NVFP4) {
+            const uint32_t sf = *reinterpret_cast<const uint32_t *>(raw + WQ_TILE + p * 512 + lane * 16 + wg * 4);
+#pragma unroll
+            for (int j = 0; j < 4; j++) s[j] = scale_h2(global * e4m3_to_f32((sf >> (8 * j)) & 0xFFu));
+        } else {
+            const uint32_t sf = *reinterpret_cast<const unsigned short *>(raw + WQ_TILE + (p >> 1) * 512 + lane * 16 + wg * 4 + 2 * (p & 1));
+            s[0] = s[1] = scale_h2(e8m0_to_f32(sf & 0xFFu));
+            s[2] = s[3] = scale_h2(e8m0_to_f32(sf >> 8));
+        }
         uint8_t *rowp = at + r * 128;
-        *reinterpret_cast<uint4 *>(rowp + (((2 * qtr) ^ (r & 7)) << 4)) = fp4_word(v.x, s);
-        *reinterpret_cast<uint4 *>(rowp + (((2 * qtr + 1) ^ (r & 7)) << 4)) = fp4_word(v.y, s);
+#pragma unroll
+        for (int c = 0; c < 8; c++) *reinterpret_cast<uint4 *>(rowp + ((c ^ (r & 7)) << 4)) = fp4_word(w[c], s[c >> 1]);
     }
 };
 template <>
@@ -228,32 +256,36 @@ template <>
 struct Dequant<FMT_MXFP4> : DequantFp4<FMT_MXFP4> {};
 
 // ---- the kernel -----------------------------------------------------------------------------------
-// grid: (token tiles, weight-row tiles of 128): CTAs that share a weight tile run side by side, so its
+// grid: (token tiles, groups of MT weight-row tiles): CTAs that share weight tiles run side by side, so the
 // second reader finds the raw bytes in L2.
-template <int FMT>
+// Sequence numbers: raw super-chunk q = j * mt + i (k-block j, row tile i of the CTA), A tile a = ks * mt + i
+// (k-step ks); B stage = ks.  Each ring slot is sequence % depth with the usual phase parity.
+template <int FMT, int MT>
 __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_constant__ GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
-    // barriers: fullA, emptyA [WQ_SA]; fullB, emptyB [WQ_MAX_SB]; rawfull, rawempty [WQ_MAX_R]; accum
     __shared__ __align__(8) uint64_t bars[2 * WQ_SA + 2 * WQ_MAX_SB + 2 * WQ_MAX_R + 1];
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s;
     constexpr int RAW = wq_raw_bytes(FMT);
+    constexpr uint32_t TMEM_COLS = MT == 2 ? 512 : 256;
     const uint32_t smem_s = (tc::smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *smem = smem_raw + (smem_s - tc::smem_u32(smem_raw));
     const int bstage = p.ntok * 128;
-    const uint32_t a_off = 0, b_off = WQ_SA * WQ_TILE, raw_off = b_off + (uint32_t)(p.sb * bstage);
+    const uint32_t a_off = 0, b_off = (uint32_t)(WQ_SA * WQ_TILE), raw_off = b_off + (uint32_t)(p.sb * bstage);
     const uint32_t fullA = tc::smem_u32(&bars[0]), emptyA = fullA + 8 * WQ_SA, fullB = emptyA + 8 * WQ_SA,
                    emptyB = fullB + 8 * WQ_MAX_SB, rawfull = emptyB + 8 * WQ_MAX_SB, rawempty = rawfull + 8 * WQ_MAX_R,
                    accum = rawempty + 8 * WQ_MAX_R;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int64_t row0 = (int64_t)blockIdx.y * WQ_BM, tok0 = (int64_t)blockIdx.x * WQ_BN;
+    const int tile0 = blockIdx.y * MT;
+    const int mt = min(MT, p.row_tiles - tile0);  // row tiles this CTA really has
+    const int64_t tok0 = (int64_t)blockIdx.x * WQ_BN;
     const int nks = 4 * p.nsc;
     volatile int *abort_flag = &abort_s;
 
     if (threadIdx.x == 0) {
         abort_s = 0;
         for (int s = 0; s < WQ_SA; s++) {
-            tc::mbar_init(fullA + 8 * s, WQ_DW);  // one arrival per dequant warp
+            tc::mbar_init(fullA + 8 * s, WQ_DW / 4);  // one arrival per warp of the slot's dequant group
             tc::mbar_init(emptyA + 8 * s, 1);
         }
         for (int s = 0; s < WQ_MAX_SB; s++) {
@@ -262,12 +294,12 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
         }
         for (int s = 0; s < WQ_MAX_R; s++) {
             tc::mbar_init(rawfull + 8 * s, 1);
-            tc::mbar_init(rawempty + 8 * s, WQ_DW);
+            tc::mbar_init(rawempty + 8 * s, WQ_DW / mt);  // the warps that read a super-chunk
         }
         tc::mbar_init(accum, 1);
         tc::mbar_init_fence();
     }
-    if (warp == 2) tc::tmem_alloc(tc::smem_u32(&tmem_base_s), 256);
+    if (warp == 2) tc::tmem_alloc(tc::smem_u32(&tmem_base_s), TMEM_COLS);
     tc::fence_before_sync();
     __syncthreads();
     tc::fence_after_sync();
@@ -276,22 +308,27 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
     if (warp == 0) {
         // ---------------- raw weight super-chunks: one thread, bulk copies ----------------
         if (lane == 0) {
-            for (int j = 0; j < p.nsc; j++) {
-                const int s = j % p.r;
-                if (j >= p.r && !tc::mbar_wait(rawempty + 8 * s, (uint32_t)((j / p.r - 1) & 1), abort_flag)) {
-                    abort_s = 1;
-                    atomicExch(p.status, 10);
-                    break;
-                }
-                const uint32_t dst = smem_s + raw_off + (uint32_t)(s * RAW);
-                tc::mbar_expect_tx(rawfull + 8 * s, RAW);
-                if (FMT == FMT_Q4K || FMT == FMT_Q80) {
-                    // the eight 16-row chunks of row-tile group blockIdx.y for k-block j are contiguous
-                    bulk_g2s(dst, p.qs + ((size_t)blockIdx.y * p.nsc + j) * RAW, RAW, rawfull + 8 * s);
-                } else {
-                    constexpr int SFB = RAW - WQ_TILE;
-                    bulk_g2s(dst, p.qs + ((size_t)blockIdx.y * p.nsc + j) * WQ_TILE, WQ_TILE, rawfull + 8 * s);
-                    bulk_g2s(dst + WQ_TILE, p.aux + ((size_t)blockIdx.y * p.nsc + j) * SFB, SFB, rawfull + 8 * s);
+            int slot = 0, round = 0;
+            for (int jb = 0; jb < p.nsc; jb++) {
+                for (int ti = 0; ti < mt; ti++) {
+                    if (round > 0 && !tc::mbar_wait(rawempty + 8 * slot, (uint32_t)((round - 1) & 1), abort_flag)) {
+                        abort_s = 1;
+                        atomicExch(p.status, 10);
+                        jb = p.nsc;
+                        break;
+                    }
+                    const int tile = tile0 + ti;
+                    const uint32_t dst = smem_s + raw_off + (uint32_t)(slot * RAW);
+                    tc::mbar_expect_tx(rawfull + 8 * slot, RAW);
+                    if (FMT == FMT_Q4K || FMT == FMT_Q80) {
+                        // the eight 16-row chunks of a 128-row tile for k-block jb are contiguous
+                        bulk_g2s(dst, p.qs + ((size_t)tile * p.nsc + jb) * RAW, RAW, rawfull + 8 * slot);
+                    } else {
+                        constexpr int SFB = RAW - WQ_TILE;
+                        bulk_g2s(dst, p.qs + ((size_t)tile * p.nsc + jb) * WQ_TILE, WQ_TILE, rawfull + 8 * slot);
+                        bulk_g2s(dst + WQ_TILE, p.aux + ((size_t)tile * p.nsc + jb) * SFB, SFB, rawfull + 8 * slot);
+                    }
+                    if (++slot == p.r) slot = 0, round++;
                 }
             }
         }
@@ -300,17 +337,18 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
         if (lane == 0) {
             const int halves = (p.ntok + 127) / 128;
             const uint32_t hbytes = (uint32_t)(p.ntok > 128 ? WQ_TILE : bstage);
+            int slot = 0, round = 0;
             for (int ks = 0; ks < nks; ks++) {
-                const int s = ks % p.sb;
-                if (ks >= p.sb && !tc::mbar_wait(emptyB + 8 * s, (uint32_t)((ks / p.sb - 1) & 1), abort_flag)) {
+                if (round > 0 && !tc::mbar_wait(emptyB + 8 * slot, (uint32_t)((round - 1) & 1), abort_flag)) {
                     abort_s = 1;
                     atomicExch(p.status, 11);
                     break;
                 }
-                const uint32_t dst = smem_s + b_off + (uint32_t)(s * bstage);
-                tc::mbar_expect_tx(fullB + 8 * s, (uint32_t)bstage);
+                const uint32_t dst = smem_s + b_off + (uint32_t)(slot * bstage);
+                tc::mbar_expect_tx(fullB + 8 * slot, (uint32_t)bstage);
                 for (int h = 0; h < halves; h++)
-                    bulk_g2s(dst + h * WQ_TILE, p.xt + ((size_t)((tok0 >> 7) + h) * nks + ks) * WQ_TILE, hbytes, fullB + 8 * s);
+                    bulk_g2s(dst + h * WQ_TILE, p.xt + ((size_t)((tok0 >> 7) + h) * nks + ks) * WQ_TILE, hbytes, fullB + 8 * slot);
+                if (++slot == p.sb) slot = 0, round++;
             }
         }
     } else if (warp == 2) {
@@ -318,56 +356,69 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
         if (lane == 0) {
             const uint32_t idesc = tc::idesc_f16(WQ_BM, p.ntok, 0, 0);  // fp16 x fp16 -> f32
             bool ok = true;
+            int sb = 0, bround = 0;
             for (int ks = 0; ks < nks && ok; ks++) {
-                const int sa = ks % WQ_SA, sb = ks % p.sb;
-                ok = tc::mbar_wait(fullB + 8 * sb, (uint32_t)((ks / p.sb) & 1), abort_flag) &&
-                     tc::mbar_wait(fullA + 8 * sa, (uint32_t)((ks / WQ_SA) & 1), abort_flag);
+                ok = tc::mbar_wait(fullB + 8 * sb, (uint32_t)(bround & 1), abort_flag);
+                const uint64_t bd = tc::smem_desc_sw128(smem_s + b_off + (uint32_t)(sb * bstage));
+                for (int i = 0; i < mt && ok; i++) {
+                    const int a = ks * mt + i, sa = a % WQ_SA;
+                    ok = tc::mbar_wait(fullA + 8 * sa, (uint32_t)((a / WQ_SA) & 1), abort_flag);
+                    if (!ok) break;
+                    tc::fence_after_sync();
+                    const uint64_t ad = tc::smem_desc_sw128(smem_s + a_off + sa * WQ_TILE);
+#pragma unroll
+                    for (int k4 = 0; k4 < 4; k4++)
+                        tc::mma_f16(tmem_d + 256u * (uint32_t)i, ad + 2 * k4, bd + 2 * k4, idesc, (uint32_t)((ks | k4) != 0));
+                    tc::mma_commit(emptyA + 8 * sa);  // the A tile is free when these MMAs have read it
+                }
                 if (!ok) {
                     abort_s = 1;
                     atomicExch(p.status, 12);
                     break;
                 }
-                tc::fence_after_sync();
-                const uint64_t ad = tc::smem_desc_sw128(smem_s + a_off + sa * WQ_TILE);
-                const uint64_t bd = tc::smem_desc_sw128(smem_s + b_off + (uint32_t)(sb * bstage));
-#pragma unroll
-                for (int k4 = 0; k4 < 4; k4++) tc::mma_f16(tmem_d, ad + 2 * k4, bd + 2 * k4, idesc, (uint32_t)((ks | k4) != 0));
-                tc::mma_commit(emptyA + 8 * sa);  // both stages are free when these MMAs have read them
                 tc::mma_commit(emptyB + 8 * sb);
+                if (++sb == p.sb) sb = 0, bround++;
             }
             if (ok) tc::mma_commit(accum);
         }
     } else {
         // ---------------- dequant warps, then epilogue ----------------
-        const int dw = warp - 3;
+        const int dw = warp - 3, grp = dw >> 2, wg = dw & 3;
         Dequant<FMT> dq;
         dq.global = p.global_scale;
         bool ok = true;
-        for (int j = 0; j < p.nsc && ok; j++) {
-            const int rs = j % p.r;
-            // waits are made warp-uniform: the dequant steps shuffle across the whole warp
-            if (!__all_sync(0xffffffffu, tc::mbar_wait(rawfull + 8 * rs, (uint32_t)((j / p.r) & 1), abort_flag))) {
-                ok = false;
-                break;
+        // group grp makes the A tiles a = grp, grp + 4, ... (slot grp of the A ring); a = ks * mt + i.
+        // mt == 1: the group always has quarter grp of every super-chunk; mt == 2: row tile i = grp % 2 and
+        // the quarters grp / 2 and grp / 2 + 2.
+        const int na = nks * mt;
+        const int qstep = (MT == 2 && mt == 2) ? 2 : 1;  // raw sequence numbers between this group's super-chunks
+        int rslot = (MT == 2 && mt == 2) ? (grp & 1) : 0, rround = 0;
+        if (rslot >= p.r) rslot -= p.r, rround++;
+        for (int a = grp, it = 0; a < na && ok; a += 4, it++) {
+            const int ks = (MT == 2 && mt == 2) ? (a >> 1) : a;
+            const int pp = ks & 3;
+            // the group's first warp waits for the raw super-chunk and for the group's A slot; the other three
+            // sleep on a hardware barrier instead of polling (polling warps take issue slots from working ones)
+            if (wg == 0) {
+                const bool ready = tc::mbar_wait(rawfull + 8 * rslot, (uint32_t)(rround & 1), abort_flag) &&
+                                   (it == 0 || tc::mbar_wait(emptyA + 8 * grp, (uint32_t)((it - 1) & 1), abort_flag));
+                if (!ready) abort_s = 1;
             }
-            const uint8_t *raw = smem + raw_off + rs * RAW;
-            dq.begin(raw, dw, lane);
-#pragma unroll 1
-            for (int pp = 0; pp < 4; pp++) {
-                const int ks = 4 * j + pp, sa = ks % WQ_SA;
-                const bool freed = ks < WQ_SA || tc::mbar_wait(emptyA + 8 * sa, (uint32_t)((ks / WQ_SA - 1) & 1), abort_flag);
-                if (!__all_sync(0xffffffffu, freed)) {
-                    ok = false;
-                    break;
-                }
-                dq.step(raw, pp, smem + a_off + sa * WQ_TILE, dw, lane);
-                tc::fence_proxy_async();  // every writer makes its own stores visible to the tensor core's proxy
-                __syncwarp();
-                if (lane == 0) tc::mbar_arrive(fullA + 8 * sa);
+            tc::named_bar_sync(1 + grp, 128);
+            ok = !*abort_flag;
+            if (!ok) break;
+            dq.step(smem + raw_off + rslot * RAW, pp, smem + a_off + grp * WQ_TILE, wg, lane);
+            tc::fence_proxy_async();  // every writer makes its own stores visible to the tensor core's proxy
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(fullA + 8 * grp);
+            // last quarter this warp reads of the super-chunk: hand the slot back and move to the next one
+            const bool last = !(MT == 2 && mt == 2) || pp >= 2;
+            if (last) {
+                if (lane == 0) tc::mbar_arrive(rawempty + 8 * rslot);
+                rslot += qstep;
+                if (rslot >= p.r) rslot -= p.r, rround++;
             }
-            if (ok && lane == 0) tc::mbar_arrive(rawempty + 8 * rs);  // the warp's reads of the super-chunk are done
         }
-        ok = __all_sync(0xffffffffu, ok);
         if (!ok && !abort_s) {
             abort_s = 1;
             atomicExch(p.status, 13);
@@ -379,18 +430,20 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
             // every fourth group of 32 token columns
             tc::fence_after_sync();
             const int quad = warp & 3;
-            const int64_t row = row0 + 32 * quad + lane;
-            for (int c = 32 * (dw >> 2); c < p.ntok; c += 32 * (WQ_DW / 4)) {
-                uint32_t v[32];
-                tc::tmem_ld32(tmem_d + ((uint32_t)(32 * quad) << 16) + (uint32_t)c, v);
-                tc::tmem_ld_wait();
-                if (row < p.n) {
+            for (int i = 0; i < mt; i++) {
+                const int64_t row = (int64_t)(tile0 + i) * WQ_BM + 32 * quad + lane;
+                for (int c = 32 * (dw >> 2); c < p.ntok; c += 32 * (WQ_DW / 4)) {
+                    uint32_t v[32];
+                    tc::tmem_ld32(tmem_d + ((uint32_t)(32 * quad) << 16) + 256u * (uint32_t)i + (uint32_t)c, v);
+                    tc::tmem_ld_wait();
+                    if (row < p.n) {
 #pragma unroll
-                    for (int jj = 0; jj < 32; jj++) {
-                        const int64_t tok = tok0 + c + jj;
-                        if (tok < p.m) {
-                            if (p.y_bf16) static_cast<__nv_bfloat16 *>(p.y)[tok * p.ldy + row] = __float2bfloat16_rn(__uint_as_float(v[jj]));
-                            else static_cast<float *>(p.y)[tok * p.ldy + row] = __uint_as_float(v[jj]);
+                        for (int jj = 0; jj < 32; jj++) {
+                            const int64_t tok = tok0 + c + jj;
+                            if (tok < p.m) {
+                                if (p.y_bf16) static_cast<__nv_bfloat16 *>(p.y)[tok * p.ldy + row] = __float2bfloat16_rn(__uint_as_float(v[jj]));
+                                else static_cast<float *>(p.y)[tok * p.ldy + row] = __uint_as_float(v[jj]);
+                            }
                         }
                     }
                 }
@@ -402,20 +455,24 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
     }
     tc::fence_before_sync();
     __syncthreads();
-    if (warp == 2) tc::tmem_dealloc(tmem_d, 256);
+    if (warp == 2) tc::tmem_dealloc(tmem_d, TMEM_COLS);
 }
 
 // ---------------------------------------------------------------------------------------------
-template <int FMT>
+template <int FMT, int MT>
 static int32_t launch_wq(Ctx *c, const GemmParams &p, dim3 grid, size_t smem, cudaStream_t s) {
     static bool attr_set = false;
     if (!attr_set) {
-        GK_CUDA(c, cudaFuncSetAttribute(gemm_wq_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, WQ_SMEM_LIMIT + 1024));
+        GK_CUDA(c, cudaFuncSetAttribute(gemm_wq_kernel<FMT, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, WQ_SMEM_LIMIT + 1024));
         attr_set = true;
     }
-    gemm_wq_kernel<FMT><<<grid, WQ_THREADS, smem, s>>>(p);
+    gemm_wq_kernel<FMT, MT><<<grid, WQ_THREADS, smem, s>>>(p);
     GK_CUDA(c, cudaGetLastError());
     return GLLMK_STATUS_OK;
+}
+template <int FMT>
+static int32_t launch_wq_mt(Ctx *c, const GemmParams &p, int mt, dim3 grid, size_t smem, cudaStream_t s) {
+    return mt == 2 ? launch_wq<FMT, 2>(c, p, grid, smem, s) : launch_wq<FMT, 1>(c, p, grid, smem, s);
 }
 
 int32_t gemm_launch(Ctx *c, const Weight *w, const void *a, int a_bf16, int64_t lda, int m, void *y, int y_bf16, int64_t ldy,
@@ -436,16 +493,25 @@ int32_t gemm_launch(Ctx *c, const Weight *w, const void *a, int a_bf16, int64_t 
     p.y_bf16 = y_bf16;
     p.ldy = ldy;
     p.status = c->status_dev;
+    p.row_tiles = (int)(w->n_pad / WQ_BM);
     // MMA N: whole 256-token tiles, or the tokens rounded up to a multiple of 32 when there are at most 128
     p.ntok = (m > 128) ? WQ_BN : ((m + 31) / 32) * 32;
     const int mtiles = (m + WQ_BN - 1) / WQ_BN;
     const int bstage = p.ntok * 128;
-    p.sb = WQ_MAX_SB;
-    if (WQ_SA * WQ_TILE + p.sb * bstage + 2 * raw > WQ_SMEM_LIMIT) p.sb = 3;
-    p.r = (WQ_SMEM_LIMIT - WQ_SA * WQ_TILE - p.sb * bstage) / raw;
-    if (p.r > WQ_MAX_R) p.r = WQ_MAX_R;
-    if (p.r > p.nsc) p.r = p.nsc;
-    if (p.r < 1) return fail(c, GLLMK_STATUS_RUNTIME_ERROR, "gemm: shared-memory plan does not fit");
+    // two row tiles per CTA when that still leaves at least one CTA per SM
+    int mt = ((p.row_tiles + 1) / 2) * mtiles >= c->sm_count ? 2 : 1;
+    // shared-memory plan: four A tiles, at least mt + 1 raw super-chunks, the rest goes to B stages
+    p.r = mt + 1;
+    p.sb = (WQ_SMEM_LIMIT - WQ_SA * WQ_TILE - p.r * raw) / bstage;
+    if (p.sb < 2 && mt == 2) {  // big raw super-chunks (Q8_0) with a 256-token tile: one row tile per CTA
+        mt = 1;
+        p.r = 2;
+        p.sb = (WQ_SMEM_LIMIT - WQ_SA * WQ_TILE - p.r * raw) / bstage;
+    }
+    if (p.sb > WQ_MAX_SB) p.sb = WQ_MAX_SB;
+    if (p.sb < 2) return fail(c, GLLMK_STATUS_RUNTIME_ERROR, "gemm: shared-memory plan does not fit");
+    const int more_r = (WQ_SMEM_LIMIT - WQ_SA * WQ_TILE - p.sb * bstage) / raw;
+    p.r = more_r > WQ_MAX_R ? WQ_MAX_R : more_r;
     const size_t smem = 1024 + (size_t)WQ_SA * WQ_TILE + (size_t)p.sb * bstage + (size_t)p.r * raw;
     // activations -> fp16 tile images in the context's scratch
     const int atiles = (p.ntok > 128) ? 2 * mtiles : 1;
@@ -455,12 +521,12 @@ int32_t gemm_launch(Ctx *c, const Weight *w, const void *a, int a_bf16, int64_t 
     p.xt = static_cast<const uint8_t *>(c->act);
     stage_act_kernel<<<dim3((unsigned)nks, (unsigned)atiles), 256, 0, s>>>(a, a_bf16, lda, m, w->k, static_cast<uint8_t *>(c->act));
     GK_CUDA(c, cudaGetLastError());
-    dim3 grid((unsigned)mtiles, (unsigned)(w->n_pad / WQ_BM));
+    dim3 grid((unsigned)mtiles, (unsigned)((p.row_tiles + mt - 1) / mt));
     switch (fmt) {
-        case FMT_Q4K: return launch_wq<FMT_Q4K>(c, p, grid, smem, s);
-        case FMT_Q80: return launch_wq<FMT_Q80>(c, p, grid, smem, s);
-        case FMT_NVFP4: return launch_wq<FMT_NVFP4>(c, p, grid, smem, s);
-        default: return launch_wq<FMT_MXFP4>(c, p, grid, smem, s);
+        case FMT_Q4K: return launch_wq_mt<FMT_Q4K>(c, p, mt, grid, smem, s);
+        case FMT_Q80: return launch_wq_mt<FMT_Q80>(c, p, mt, grid, smem, s);
+        case FMT_NVFP4: return launch_wq_mt<FMT_NVFP4>(c, p, mt, grid, smem, s);
+        default: return launch_wq_mt<FMT_MXFP4>(c, p, mt, grid, smem, s);
     }
 }
 

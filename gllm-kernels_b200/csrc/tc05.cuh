@@ -20,25 +20,32 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+// One try: the thread may be suspended by the hardware for up to `hint_ns` while the phase is pending.
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity, uint32_t hint_ns = 2000u) {
     uint32_t ok;
     asm volatile(
         "{\n.reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
         "selp.u32 %0, 1, 0, p;\n}\n"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(hint_ns)
         : "memory");
     return ok != 0;
 }
-// Bounded wait; also gives up early when another role of the CTA has raised `*abort_flag`.
+// Bounded wait; also gives up early when another role of the CTA has raised `*abort_flag`.  The first tries
+// are back to back (the common case: the phase completes within a few hundred cycles); after that the flag
+// is looked at between tries.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
-    for (uint32_t it = 0; it < (1u << 22); it++) {
+#pragma unroll 1
+    for (uint32_t it = 0; it < (1u << 21); it++) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 255u) == 255u && *abort_flag) return false;
+        if (it >= 64u && *abort_flag) return false;
     }
     return false;
 }
+
+// named barrier among `nthreads` threads of the CTA (ids 1..15; 0 is __syncthreads)
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) { asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(nthreads) : "memory"); }
 
 // generic-proxy writes to shared memory -> visible to the async proxy (tensor core / bulk copies)
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }

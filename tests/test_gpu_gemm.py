@@ -82,6 +82,13 @@ def test_gemm_rejects_bad_arguments(gk, K, oracle):
     w.free()
 
 
+@pytest.mark.parametrize("fmt,n,k,m", [("q4k", 37966, 256, 200), ("q8_0", 19008, 320, 300), ("nvfp4", 37966, 256, 130)])
+def test_gemm_two_row_tiles_per_cta(gk, K, oracle, fmt, n, k, m):
+    # enough 128-row tiles that a CTA takes two of them (one activation tile feeds two accumulators);
+    # 297 tiles: the last CTA has a single tile
+    assert run_case(gk, K, oracle, fmt, n, k, m, seed=n % 1000 + m, a_bf16=(fmt == "nvfp4")) <= TOL
+
+
 def test_gemm_q8_0_ragged_k(gk, K, oracle):
     # k = 96: three blocks of a group of eight; the rest of the 256-wide k-step is zero padding
     assert run_case(gk, K, oracle, "q8_0", 144, 96, 40, seed=15) <= 1e-2
