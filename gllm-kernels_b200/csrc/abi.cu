@@ -366,6 +366,19 @@ int32_t gllmk_gemm(gllmk_ctx ctx, gllmk_weight wh, const void *a_dev, int32_t a_
     if (lda < w->k || ldy < w->n) return fail(c, GLLMK_STATUS_INVALID_ARG, "gemm: leading dimension smaller than the row");
     if (w->device != c->device) return fail(c, GLLMK_STATUS_INVALID_ARG, "weight lives on another device");
     DeviceGuard g(c->device);
+    // A few dozen tokens are still bound by the weight stream, which the decode kernel reads at several times
+    // the rate the tensor-core pipeline reaches with a nearly empty N: run them as passes of up to 16 tokens.
+    if (m <= GLLMK_GEMM_GEMV_MAX_M && a_dtype == GLLMK_DTYPE_F32 && y_dtype == GLLMK_DTYPE_F32 &&
+        (w->qt == GLLMK_QUANT_Q4K || w->qt == GLLMK_QUANT_Q8_0)) {
+        for (int t0 = 0; t0 < m; t0 += GLLMK_GEMV_MAX_M) {
+            const int mm = m - t0 < GLLMK_GEMV_MAX_M ? m - t0 : GLLMK_GEMV_MAX_M;
+            const int32_t rc = gemv_launch(c, w, static_cast<const float *>(a_dev) + (int64_t)t0 * lda, lda, 1, mm,
+                                           static_cast<float *>(y_dev) + (int64_t)t0 * ldy, ldy, 1, nullptr, 0,
+                                           static_cast<cudaStream_t>(stream));
+            if (rc) return rc;
+        }
+        return GLLMK_STATUS_OK;
+    }
     return gemm_launch(c, w, a_dev, a_dtype == GLLMK_DTYPE_BF16, lda, m, y_dev, y_dtype == GLLMK_DTYPE_BF16, ldy,
                        static_cast<cudaStream_t>(stream));
 }

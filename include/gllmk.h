@@ -140,9 +140,12 @@ GLLMK_API int32_t gllmk_gemv(gllmk_ctx ctx, gllmk_weight w, const float *x_dev, 
  * leaves unimplemented for MXFP4 / NVFP4 weights (src/cpu_kernels/mod.rs:3347-3348; oracle = its dequant
  * followed by scalar_gemm, scalar-ops/src/blas.rs:116-135), on device memory with resident weights:
  *   y[t, r] = sum_k W[r, k] * a[t, k],  a [m, k] row-major (leading dimension lda), y [m, n] (ldy).
- * a_dtype / y_dtype: GLLMK_DTYPE_F32 or GLLMK_DTYPE_BF16.  Weights and activations are staged in bf16
- * and accumulated in f32 (results within 1e-2 of the reference's f32 evaluation).  k must be a multiple
- * of 64; a and its rows 16-byte aligned. */
+ * a_dtype / y_dtype: GLLMK_DTYPE_F32 or GLLMK_DTYPE_BF16.  Weights and activations are staged in fp16
+ * (activations saturate at +-65504) and accumulated in f32: results within 1e-2 of the reference's f32
+ * evaluation.  a and its rows must be 16-byte aligned.  With f32 in and out, Q4_K / Q8_0 weights and
+ * m <= GLLMK_GEMM_GEMV_MAX_M the call runs as passes of the decode kernel (gllmk_gemv), which is faster
+ * there and meets its tighter bound. */
+#define GLLMK_GEMM_GEMV_MAX_M 48
 GLLMK_API int32_t gllmk_gemm(gllmk_ctx ctx, gllmk_weight w, const void *a_dev, int32_t a_dtype, int64_t lda, int32_t m,
                              void *y_dev, int32_t y_dtype, int64_t ldy, void *stream);
 

@@ -68,6 +68,20 @@ def test_gemm_ragged_shapes(gk, K, oracle, fmt, n, k, m):
     assert run_case(gk, K, oracle, fmt, n, k, m, seed=n + m) <= TOL
 
 
+@pytest.mark.parametrize("fmt,n,k,m", [("q4k", 100, 256, 17), ("q8_0", 128, 1024, 32), ("q4k", 260, 768, 48), ("q8_0", 129, 192, 33)])
+def test_gemm_few_tokens_tensor_core_path(gk, K, oracle, fmt, n, k, m):
+    # with f32 in and out a few dozen tokens run as passes of the decode kernel; bf16 activations keep the
+    # call on the tcgen05 kernel with a narrow MMA N (32 / 64)
+    assert run_case(gk, K, oracle, fmt, n, k, m, seed=n + m + 1, a_bf16=True) <= TOL
+
+
+@pytest.mark.parametrize("m", [17, 32, 47, 48])
+def test_gemm_few_tokens_decode_passes(gk, K, oracle, m):
+    # f32, m <= 48: ceil(m / 16) passes of the decode kernel, tighter bound
+    assert run_case(gk, K, oracle, "q4k", 200, 512, m, seed=m) <= 2e-3
+    assert run_case(gk, K, oracle, "q8_0", 200, 160, m, seed=m + 100) <= 2e-3
+
+
 def test_gemm_bf16_in_bf16_out(gk, K, oracle):
     assert run_case(gk, K, oracle, "q4k", 256, 512, 96, seed=9, a_bf16=True, y_bf16=True) <= 1.5e-2
 
@@ -77,7 +91,7 @@ def test_gemm_rejects_bad_arguments(gk, K, oracle):
     qt, blocks, _, _, _ = quantized(oracle, gk, "q8_0", 16, 96, 5)
     w = K.upload(qt, 16, 96, blocks)
     with pytest.raises(gk.GllmkError) as e:  # activation rows must be 16-byte aligned: lda % 4 for f32
-        K.gemm(w, torch.zeros((32, 98), device="cuda")[:, :96])
+        K.gemm(w, torch.zeros((64, 98), device="cuda")[:, :96])
     assert e.value.status == gk.Status.INVALID_ARG
     w.free()
 
