@@ -206,7 +206,7 @@ def run_ours(args):
         "roofline": {"bound": "hbm", "achieved": algo_bytes_step / (ms_step * 1e-3) / 1e9 / world, "peak": peak,
                      "unit": "GB/s", "frac": algo_bytes_step / (ms_step * 1e-3) / 1e9 / world / peak,
                      "traffic": None, "peak_kind": peak_kind,
-                     "kernel": "gemv_q4k_kernel<1> (+ its activation staging kernel), per-GPU average"},
+                     "kernel": "gemv_kernel<Q4_K, 1 n-tile> (+ stage_x_kernel), per-GPU average"},
         "gpu_launches": args.steps * len(weights) * 2,
         "clocks": clocks,
         "e2e": e2e,
@@ -410,6 +410,62 @@ def run_reference(args):
     print(json.dumps(out), flush=True)
 
 
+def run_prefill_case(args):
+    """One prefill kernel on its own: `prefill_q4k` = config 5 gate matrix at M = 512 (tcgen05 kind::f16 with fused
+    Q4_K dequant), `prefill_nvfp4` = config 4 (NVFP4 x NVFP4, block-scaled tcgen05).  One JSON line."""
+    import torch
+    gk = importlib.import_module("gllm-kernels_b200")
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    K = gk.GpuKernels(0)
+    gen = torch.Generator(device=dev).manual_seed(20245)
+    QT = gk.QuantType
+    if args.case == "prefill_q4k":
+        n, k, m = N_FF, D_MODEL, 512
+        W = torch.randn((n, k), generator=gen, device=dev) * 0.02
+        w = K.upload(QT.q4k(), n, k, K.quantize(QT.q4k(), W))
+        del W
+        a = torch.randn((m, k), generator=gen, device=dev)
+        y = torch.empty((m, n), dtype=torch.float32, device=dev)
+        fn = lambda: K.gemm(w, a, y=y)
+        kernel, peak_key, launches = "gemm_wq_kernel<Q4_K, 2 row tiles> (+ stage_act_kernel)", "bf16_tflops", 2
+    else:
+        n, k, m = 14336, 4096, 2048
+        W = torch.randn((n, k), generator=gen, device=dev) * 0.02
+        X = torch.randn((m, k), generator=gen, device=dev)
+        wb, gw = K.quantize(QT.nvfp4(), W)
+        xb, gx = K.quantize(QT.nvfp4(), X)
+        w, x = K.upload(QT.nvfp4(), n, k, wb, None, gw), K.upload(QT.nvfp4(), m, k, xb, None, gx)
+        y = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+        fn = lambda: K.gemm_fp4(w, x, y=y)
+        kernel, peak_key, launches = "gemm_fp4_kernel", None, 1
+    for _ in range(max(args.warmup, 3)):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    tflops = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+    peak, kind = 9000.0, "nominal dense FP4"
+    if peak_key:
+        pth = os.path.join(ROOT, "MEASURED_PEAKS.json")
+        if os.path.exists(pth):
+            with open(pth) as f:
+                peak, kind = float(json.load(f)[peak_key]), "measured (cuBLAS bf16, burst)"
+        else:
+            peak, kind = 1590.0, "fallback"
+    print(json.dumps({"metric": f"prefill GEMM TFLOP/s ({args.case})", "value": tflops, "unit": "TFLOP/s", "n_gpus": 1,
+                      "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+                      "data": "synthetic", "config": {"workload": args.case, "n": n, "k": k, "m": m},
+                      "roofline": {"bound": "tensor", "achieved": tflops, "peak": peak, "unit": "TFLOP/s", "frac": tflops / peak,
+                                   "traffic": None, "peak_kind": kind, "kernel": kernel},
+                      "gpu_launches": args.steps * launches, "status": K.status()}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -420,8 +476,12 @@ def main():
     ap.add_argument("--m", type=int, default=1)
     ap.add_argument("--no-extra", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--case", default="decode", choices=["decode", "prefill_q4k", "prefill_nvfp4"],
+                    help="decode = the headline workload; prefill_* = one prefill kernel on its own (1 GPU)")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.case != "decode":
+        run_prefill_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
