@@ -30,6 +30,7 @@ if ROOT not in sys.path:
 N_FF, D_MODEL = 28672, 8192
 Q4K_BLOCK_BYTES, Q4K_BLOCK = 144, 256
 METRIC = "quant GEMV weight-GB/s (Q4_K decode, 70B-shaped FFN)"
+GEMV_DRAM_TRAFFIC_PER_LAUNCH = 140.02e6
 
 
 def measured_peaks():
@@ -205,7 +206,11 @@ def run_ours(args):
                    "parallelism": "single GPU" if world == 1 else f"N-wise row shards x{world} + NCCL all-gather"},
         "roofline": {"bound": "hbm", "achieved": algo_bytes_step / (ms_step * 1e-3) / 1e9 / world, "peak": peak,
                      "unit": "GB/s", "frac": algo_bytes_step / (ms_step * 1e-3) / 1e9 / world / peak,
-                     "traffic": None, "peak_kind": peak_kind,
+                     # dram__bytes_read + dram__bytes_write of one gemv_kernel launch on the 132.1 MB gate matrix,
+                     # from the ncu capture summarised in profiles/gemv_kernel_q4k_m1_gate28672x8192.md
+                     "traffic": GEMV_DRAM_TRAFFIC_PER_LAUNCH if (M == 1 and world == 1) else None,
+                     "traffic_note": "bytes per gemv_kernel launch on one 28672x8192 matrix (algorithmic 132.27e6), ncu",
+                     "peak_kind": peak_kind,
                      "kernel": "gemv_kernel<Q4_K, 1 n-tile> (+ stage_x_kernel), per-GPU average"},
         "gpu_launches": args.steps * len(weights) * 2,
         "clocks": clocks,
