@@ -89,10 +89,8 @@ class ClockSampler(threading.Thread):
 
 
 def shard_rows(n: int, world: int, rank: int):
-    """N-wise split in multiples of 16 rows (the row-tile of the device layout)."""
-    tiles = n // 16
-    t0, t1 = tiles * rank // world, tiles * (rank + 1) // world
-    return 16 * t0, 16 * t1
+    """N-wise split in multiples of 16 rows (the row tile of the device layout); the package's rule."""
+    return importlib.import_module("gllm-kernels_b200").shard_rows(n, world, rank)
 
 
 # ------------------------------------------------------------------------------------------------
@@ -132,8 +130,14 @@ def run_ours(args):
     x_model = torch.randn((M, D_MODEL), generator=gen, device=dev)
     x_ff = torch.randn((M, N_FF), generator=gen, device=dev)
     ys = [torch.empty((M, n), dtype=torch.float32, device=dev) for (_, _, n, _, _, _) in weights]
-    # sharded: each rank's GEMV writes its slice of a [world, M, n/world] gather buffer in place
-    gbufs = [torch.empty((world, M, (r1 - r0)), dtype=torch.float32, device=dev) for (_, _, n, _, r0, r1) in weights]
+    # sharded, default: every rank's GEMV stores its band of y into all ranks' copies of y over NVLink peer
+    # pointers and a flag barrier follows (no library collective on the data path).
+    # --exchange nccl: each rank's GEMV writes its slice of a [world, M, n/world] buffer, then one all-gather.
+    gbufs, ex = [], None
+    if world > 1 and args.exchange == "peer":
+        ex = gk.PeerExchange(K, world, rank, slots=len(weights), slot_floats=M * N_FF)
+    elif world > 1:
+        gbufs = [torch.empty((world, M, (r1 - r0)), dtype=torch.float32, device=dev) for (_, _, n, _, r0, r1) in weights]
 
     weight_bytes_local = sum(w.ref_bytes for (_, w, *_r) in weights)
     weight_bytes_total = L * sum(n * (k // Q4K_BLOCK) * Q4K_BLOCK_BYTES for _, n, k in shapes)
@@ -144,6 +148,9 @@ def run_ours(args):
             x = x_ff if name == "down" else x_model
             if world == 1:
                 K.gemv(w, x, y=ys[i])
+            elif ex is not None:
+                ex.gemv(w, x, i, r0, n)
+                ex.barrier()
             else:
                 K.gemv(w, x, y=gbufs[i][rank])
                 dist.all_gather_into_tensor(gbufs[i].view(-1), gbufs[i][rank].view(-1))
@@ -203,7 +210,9 @@ def run_ours(args):
         "config": {"workload": f"config 5: 70B-shaped FFN decode, {L} layers x (gate, up, down) Q4_K, M={M}",
                    "layers": L, "M": M, "N_ff": N_FF, "d_model": D_MODEL, "weight_bytes_per_step": weight_bytes_total,
                    "l2": "per-GPU weight set larger than L2, no flush",
-                   "parallelism": "single GPU" if world == 1 else f"N-wise row shards x{world} + NCCL all-gather"},
+                   "parallelism": "single GPU" if world == 1 else (
+                       f"N-wise row shards x{world}, GEMV stores its band into every rank's y over NVLink peer pointers + flag barrier"
+                       if ex is not None else f"N-wise row shards x{world} + NCCL all-gather")},
         "roofline": {"bound": "hbm", "achieved": algo_bytes_step / (ms_step * 1e-3) / 1e9 / world, "peak": peak,
                      "unit": "GB/s", "frac": algo_bytes_step / (ms_step * 1e-3) / 1e9 / world / peak,
                      # dram__bytes_read + dram__bytes_write of one gemv_kernel launch on the 132.1 MB gate matrix,
@@ -212,7 +221,8 @@ def run_ours(args):
                      "traffic_note": "bytes per gemv_kernel launch on one 28672x8192 matrix (algorithmic 132.27e6), ncu",
                      "peak_kind": peak_kind,
                      "kernel": "gemv_kernel<Q4_K, 1 n-tile> (+ stage_x_kernel), per-GPU average"},
-        "gpu_launches": args.steps * len(weights) * 2,
+        "gpu_launches": args.steps * len(weights) * (2 if world == 1 else (3 if ex is not None else 2)),
+        "device_status": K.status(),
         "clocks": clocks,
         "e2e": e2e,
     }
@@ -223,6 +233,9 @@ def run_ours(args):
     if rank == 0:
         print(json.dumps(out), flush=True)
     if world > 1:
+        dist.barrier()
+        if ex is not None:
+            ex.close()
         dist.destroy_process_group()
 
 
@@ -481,6 +494,8 @@ def main():
     ap.add_argument("--m", type=int, default=1)
     ap.add_argument("--no-extra", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: how the bands of y reach every rank (peer stores fused into the GEMV, or NCCL all-gather)")
     ap.add_argument("--case", default="decode", choices=["decode", "prefill_q4k", "prefill_nvfp4"],
                     help="decode = the headline workload; prefill_* = one prefill kernel on its own (1 GPU)")
     args = ap.parse_args()

@@ -355,6 +355,24 @@ int32_t gllmk_gemv(gllmk_ctx ctx, gllmk_weight wh, const float *x_dev, int64_t x
                        static_cast<cudaStream_t>(stream));
 }
 
+int32_t gllmk_gemv_allgather(gllmk_ctx ctx, gllmk_weight wh, const float *x_dev, int64_t x_stride_t, int64_t x_stride_k, int32_t m,
+                             float *y_local, int64_t y_stride_t, int64_t y_stride_r, void *const *y_peers, int32_t n_peers,
+                             void *stream) {
+    if (!ctx || !wh || !x_dev || !y_local || (n_peers > 0 && !y_peers)) return GLLMK_STATUS_INVALID_ARG;
+    Ctx *c = static_cast<Ctx *>(ctx);
+    const Weight *w = static_cast<const Weight *>(wh);
+    if (m < 1 || m > GLLMK_GEMV_MAX_M)
+        return fail(c, GLLMK_STATUS_INVALID_ARG, "gemv_allgather: m=%d outside 1..%d", m, GLLMK_GEMV_MAX_M);
+    if (n_peers < 0 || n_peers > GLLMK_MAX_PEERS)
+        return fail(c, GLLMK_STATUS_INVALID_ARG, "gemv_allgather: %d peers (at most %d)", n_peers, GLLMK_MAX_PEERS);
+    for (int q = 0; q < n_peers; q++)
+        if (!y_peers[q]) return fail(c, GLLMK_STATUS_INVALID_ARG, "gemv_allgather: null peer pointer");
+    if (w->device != c->device) return fail(c, GLLMK_STATUS_INVALID_ARG, "weight lives on another device");
+    DeviceGuard g(c->device);
+    return gemv_launch(c, w, x_dev, x_stride_t, x_stride_k, m, y_local, y_stride_t, y_stride_r, nullptr, 0,
+                       static_cast<cudaStream_t>(stream), y_peers, n_peers);
+}
+
 int32_t gllmk_gemm(gllmk_ctx ctx, gllmk_weight wh, const void *a_dev, int32_t a_dtype, int64_t lda, int32_t m, void *y_dev,
                    int32_t y_dtype, int64_t ldy, void *stream) {
     if (!ctx || !wh || !a_dev || !y_dev) return GLLMK_STATUS_INVALID_ARG;

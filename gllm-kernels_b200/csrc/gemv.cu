@@ -183,6 +183,8 @@ struct GemvParams {
     const uint8_t *img;     // activation image
     float *y;
     int64_t yst, ysr;
+    float *ypeer[GLLMK_MAX_PEERS];  // the same element positions in other GPUs' buffers (peer-mapped), npeer of them
+    int npeer;
     const float *row_scales;
     int64_t n_row_scales;
     int64_t n;
@@ -346,7 +348,10 @@ __device__ __noinline__ void gemv_flush(const GemvParams &p, int tile, int slot,
                     float o = v[nt][hrow];
                     if (p.n_row_scales == 1) o *= p.row_scales[0];
                     else if (p.n_row_scales > 1) o *= p.row_scales[row];
-                    p.y[(int64_t)tok * p.yst + row * p.ysr] = o;
+                    const int64_t at = (int64_t)tok * p.yst + row * p.ysr;
+                    p.y[at] = o;
+                    // fused all-gather: the band also goes straight into the peers' copies of y over NVLink
+                    for (int q = 0; q < p.npeer; q++) p.ypeer[q][at] = o;
                 }
             }
         }
@@ -565,7 +570,8 @@ static cudaError_t configure_and_launch(Ctx *c, GemvParams &p, int64_t ntg, cuda
 }
 
 int32_t gemv_launch(Ctx *c, const Weight *w, const float *x, int64_t xst, int64_t xsk, int m, float *y, int64_t yst,
-                    int64_t ysr, const float *row_scales, int64_t n_row_scales, cudaStream_t s) {
+                    int64_t ysr, const float *row_scales, int64_t n_row_scales, cudaStream_t s, void *const *y_peers,
+                    int n_peers) {
     if (w->qt != GLLMK_QUANT_Q4K && w->qt != GLLMK_QUANT_Q8_0)
         return fail(c, GLLMK_STATUS_UNSUPPORTED, "gemv: quant type %d has no decode kernel", w->qt);
     int32_t rc = ensure_ws(c, gemv_ws_bytes(w, m));
@@ -578,6 +584,8 @@ int32_t gemv_launch(Ctx *c, const Weight *w, const float *x, int64_t xst, int64_
     p.y = y;
     p.yst = yst;
     p.ysr = ysr;
+    p.npeer = n_peers;
+    for (int q = 0; q < n_peers; q++) p.ypeer[q] = static_cast<float *>(y_peers[q]);
     p.row_scales = row_scales;
     p.n_row_scales = row_scales ? n_row_scales : 0;
     p.n = w->n;

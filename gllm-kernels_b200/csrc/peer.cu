@@ -1,0 +1,126 @@
+// Multi-GPU output exchange without a library collective: buffers that every rank of a node can address
+// (CUDA IPC), the decode GEMV storing its band of y into all of them (see gemv.cu: GemvParams::ypeer), and a
+// flag barrier that tells each rank when every band has landed.
+//
+// One process per GPU.  Each rank allocates one exchange buffer (gllmk_shared_alloc), publishes its 64-byte
+// handle through the host framework's process group, and opens the other ranks' handles (gllmk_shared_open).
+// The first GLLMK_PEER_FLAG_BYTES of every buffer are its flag words: flags[src] = last sequence number rank
+// `src` signalled.  Plain peer stores and loads only: no multicast object, no cluster-multicast load.
+#include "common.cuh"
+
+namespace gllmk {
+
+struct PeerBarrierParams {
+    uint32_t *mine;                      // this rank's flag words
+    uint32_t *peer[GLLMK_MAX_PEERS];     // the other ranks' flag words (peer-mapped)
+    int npeer, rank;
+    uint32_t seq;
+    int *status;
+};
+
+// thread q talks to the q-th other rank (rank numbers skip this rank)
+__global__ void peer_barrier_kernel(const __grid_constant__ PeerBarrierParams p) {
+    const int q = threadIdx.x;
+    if (q >= p.npeer) return;
+    const int src = q < p.rank ? q : q + 1;
+    // everything this GPU wrote before this kernel (its GEMV's stores into the peers' buffers) is ordered
+    // before the flag at system scope
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(p.peer[q] + p.rank), "r"(p.seq) : "memory");
+    // bounded wait for the same sequence number from that rank (it can be at most one barrier ahead)
+    const uint32_t *flag = p.mine + src;
+    bool seen = false;
+    for (uint32_t it = 0; it < (1u << 22) && !seen; it++) {
+        uint32_t v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(flag) : "memory");
+        seen = (int32_t)(v - p.seq) >= 0;
+        if (!seen && it > 64) __nanosleep(200);
+    }
+    if (!seen) atomicExch(p.status, 31);  // the host reads it with gllmk_ctx_status; the kernel just returns
+}
+
+int32_t peer_barrier_launch(Ctx *c, uint32_t *mine, uint32_t *const *peers, int n_peers, int rank, uint32_t seq, cudaStream_t s) {
+    PeerBarrierParams p{};
+    p.mine = mine;
+    for (int q = 0; q < n_peers; q++) p.peer[q] = peers[q];
+    p.npeer = n_peers;
+    p.rank = rank;
+    p.seq = seq;
+    p.status = c->status_dev;
+    peer_barrier_kernel<<<1, 32, 0, s>>>(p);
+    GK_CUDA(c, cudaGetLastError());
+    return GLLMK_STATUS_OK;
+}
+
+}  // namespace gllmk
+
+using namespace gllmk;
+
+extern "C" int32_t gllmk_shared_alloc(gllmk_ctx ctx, size_t bytes, void **dev_ptr, uint8_t *handle) {
+    if (!ctx || !dev_ptr || !handle || bytes == 0) return GLLMK_STATUS_INVALID_ARG;
+    Ctx *c = static_cast<Ctx *>(ctx);
+    static_assert(sizeof(cudaIpcMemHandle_t) == GLLMK_IPC_HANDLE_BYTES, "handle size");
+    int prev = -1;
+    cudaGetDevice(&prev);
+    GK_CUDA(c, cudaSetDevice(c->device));
+    void *p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes);
+    if (e == cudaSuccess) e = cudaMemset(p, 0, bytes);  // flag words start at zero
+    cudaIpcMemHandle_t h;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) {
+        if (p) cudaFree(p);
+        if (prev >= 0) cudaSetDevice(prev);
+        return cuda_fail(c, e, "gllmk_shared_alloc");
+    }
+    memcpy(handle, &h, sizeof(h));
+    *dev_ptr = p;
+    if (prev >= 0) cudaSetDevice(prev);
+    return GLLMK_STATUS_OK;
+}
+
+extern "C" int32_t gllmk_shared_open(gllmk_ctx ctx, const uint8_t *handle, void **peer_ptr) {
+    if (!ctx || !handle || !peer_ptr) return GLLMK_STATUS_INVALID_ARG;
+    Ctx *c = static_cast<Ctx *>(ctx);
+    int prev = -1;
+    cudaGetDevice(&prev);
+    GK_CUDA(c, cudaSetDevice(c->device));
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    void *p = nullptr;
+    const cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (prev >= 0) cudaSetDevice(prev);
+    if (e != cudaSuccess) return cuda_fail(c, e, "cudaIpcOpenMemHandle");
+    *peer_ptr = p;
+    return GLLMK_STATUS_OK;
+}
+
+extern "C" int32_t gllmk_shared_close(gllmk_ctx ctx, void *peer_ptr) {
+    if (!ctx) return GLLMK_STATUS_INVALID_ARG;
+    if (!peer_ptr) return GLLMK_STATUS_OK;
+    Ctx *c = static_cast<Ctx *>(ctx);
+    GK_CUDA(c, cudaIpcCloseMemHandle(peer_ptr));
+    return GLLMK_STATUS_OK;
+}
+
+extern "C" int32_t gllmk_shared_free(gllmk_ctx ctx, void *dev_ptr) {
+    if (!ctx) return GLLMK_STATUS_INVALID_ARG;
+    if (!dev_ptr) return GLLMK_STATUS_OK;
+    Ctx *c = static_cast<Ctx *>(ctx);
+    GK_CUDA(c, cudaDeviceSynchronize());
+    GK_CUDA(c, cudaFree(dev_ptr));
+    return GLLMK_STATUS_OK;
+}
+
+extern "C" int32_t gllmk_peer_barrier(gllmk_ctx ctx, void *flags_local, void *const *flags_peers, int32_t n_peers, int32_t rank,
+                                      uint32_t seq, void *stream) {
+    if (!ctx || !flags_local || (n_peers > 0 && !flags_peers)) return GLLMK_STATUS_INVALID_ARG;
+    Ctx *c = static_cast<Ctx *>(ctx);
+    if (n_peers < 0 || n_peers > GLLMK_MAX_PEERS || rank < 0 || rank > n_peers)
+        return fail(c, GLLMK_STATUS_INVALID_ARG, "peer_barrier: %d peers / rank %d out of range", n_peers, rank);
+    for (int q = 0; q < n_peers; q++)
+        if (!flags_peers[q]) return fail(c, GLLMK_STATUS_INVALID_ARG, "peer_barrier: null peer pointer");
+    if (n_peers == 0) return GLLMK_STATUS_OK;
+    return peer_barrier_launch(c, static_cast<uint32_t *>(flags_local), reinterpret_cast<uint32_t *const *>(flags_peers), n_peers, rank,
+                               seq, static_cast<cudaStream_t>(stream));
+}

@@ -158,10 +158,11 @@ class GpuKernels:
         m = x.shape[1] if ref_layout else x.shape[0]
         if y is None:
             y = torch.empty((w.n, m) if ref_layout else (m, w.n), dtype=torch.float32, device=x.device)
+        # (token stride, k stride) of x and (token stride, row stride) of y, in elements: views are fine
         if ref_layout:
-            xs, ys = (1, m), (1, m)
+            xs, ys = (x.stride(1), x.stride(0)), (y.stride(1), y.stride(0))
         else:
-            xs, ys = (w.k, 1), (w.n, 1)
+            xs, ys = (x.stride(0), x.stride(1)), (y.stride(0), y.stride(1))
         ns = 0 if row_scales is None else row_scales.numel()
         rc = lib().gllmk_gemv(self._ctx, w._h, _ptr(x), xs[0], xs[1], m, _ptr(y), ys[0], ys[1], _ptr(row_scales), ns,
                               _stream(stream))
@@ -189,6 +190,37 @@ class GpuKernels:
         rc = lib().gllmk_gemm_fp4(self._ctx, w._h, x._h, _ptr(y), dt[y.dtype], y.stride(0), _stream(stream))
         self._check(rc, "gllmk_gemm_fp4")
         return y
+
+    # ---- multi-GPU exchange buffers (one process per GPU, same node) ----
+    def shared_alloc(self, nbytes: int):
+        """Device buffer other ranks can map: returns (device pointer, 64-byte handle to send to them)."""
+        ptr, handle = C.c_void_p(), C.create_string_buffer(64)
+        self._check(lib().gllmk_shared_alloc(self._ctx, nbytes, C.byref(ptr), handle), "gllmk_shared_alloc")
+        return ptr.value, handle.raw
+
+    def shared_open(self, handle: bytes) -> int:
+        ptr = C.c_void_p()
+        self._check(lib().gllmk_shared_open(self._ctx, C.create_string_buffer(handle, 64), C.byref(ptr)), "gllmk_shared_open")
+        return ptr.value
+
+    def shared_close(self, ptr: int) -> None:
+        self._check(lib().gllmk_shared_close(self._ctx, ptr), "gllmk_shared_close")
+
+    def shared_free(self, ptr: int) -> None:
+        self._check(lib().gllmk_shared_free(self._ctx, ptr), "gllmk_shared_free")
+
+    def gemv_allgather(self, w: Weight, x, y_local: int, y_peers, y_stride_t: int, m: int, stream=None) -> None:
+        """Decode product whose band of y is stored at `y_local` and at every pointer of `y_peers` (raw device
+        addresses of the band's position in each rank's y; row stride 1, token stride y_stride_t)."""
+        arr = (C.c_void_p * max(len(y_peers), 1))(*y_peers)
+        rc = lib().gllmk_gemv_allgather(self._ctx, w._h, _ptr(x), x.stride(0), x.stride(1), m, y_local, y_stride_t, 1,
+                                        arr, len(y_peers), _stream(stream))
+        self._check(rc, "gllmk_gemv_allgather")
+
+    def peer_barrier(self, flags_local: int, flags_peers, rank: int, seq: int, stream=None) -> None:
+        arr = (C.c_void_p * max(len(flags_peers), 1))(*flags_peers)
+        rc = lib().gllmk_peer_barrier(self._ctx, flags_local, arr, len(flags_peers), rank, seq & 0xFFFFFFFF, _stream(stream))
+        self._check(rc, "gllmk_peer_barrier")
 
     def gemv_static(self, w: Weight, x, y, ref_layout: bool = False, row_scales=None, stream=None):
         """gemv for callers that may not allocate device memory: scratch is a fixed 8 MiB area inside the

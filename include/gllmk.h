@@ -134,6 +134,38 @@ GLLMK_API int32_t gllmk_gemv(gllmk_ctx ctx, gllmk_weight w, const float *x_dev, 
                    int32_t m, float *y_dev, int64_t y_stride_t, int64_t y_stride_r, const float *row_scales,
                    int64_t n_row_scales, void *stream);
 
+/* ---- multi-GPU: row-sharded decode with the all-gather fused into the GEMV -------------------------- */
+
+/* No counterpart in the reference (single device).  Weights are sharded by rows over the GPUs of one node
+ * (one process per GPU); every rank needs the whole y.  Instead of a collective after each product, the
+ * decode kernel stores its band of y into EVERY rank's copy of y through peer-mapped pointers, and a flag
+ * barrier tells each rank when all bands have landed.
+ *
+ * gllmk_shared_alloc: device buffer other processes of the node can map; `handle` (GLLMK_IPC_HANDLE_BYTES
+ *   bytes) is what the host framework sends to the other ranks.  The buffer starts zeroed; its first
+ *   GLLMK_PEER_FLAG_BYTES bytes are the barrier's flag words, the rest is the caller's (y copies).
+ * gllmk_shared_open / _close: map / unmap another rank's buffer from its handle.  _free: release one's own.
+ * gllmk_gemv_allgather: gllmk_gemv (no row scales) whose result element (t, r) is also stored at the same
+ *   element offset from each of `y_peers[0..n_peers)`.  Every pointer is the position of this rank's band
+ *   inside that rank's y.
+ * gllmk_peer_barrier: on `stream`, after this rank's products: signal sequence number `seq` to every peer and
+ *   wait (bounded, about a second; on time-out the context's status word becomes 31 and the kernel returns)
+ *   until every peer has signalled `seq`.  `flags_peers[q]` is the q-th OTHER rank's flag words in rank
+ *   order, `rank` this rank's number.  `seq` must grow by one per barrier, starting at 1.  After it, y is
+ *   complete on this rank.  A buffer may be rewritten by peers one barrier after its last reader finished. */
+#define GLLMK_MAX_PEERS 7
+#define GLLMK_IPC_HANDLE_BYTES 64
+#define GLLMK_PEER_FLAG_BYTES 256
+GLLMK_API int32_t gllmk_shared_alloc(gllmk_ctx ctx, size_t bytes, void **dev_ptr, uint8_t *handle);
+GLLMK_API int32_t gllmk_shared_open(gllmk_ctx ctx, const uint8_t *handle, void **peer_ptr);
+GLLMK_API int32_t gllmk_shared_close(gllmk_ctx ctx, void *peer_ptr);
+GLLMK_API int32_t gllmk_shared_free(gllmk_ctx ctx, void *dev_ptr);
+GLLMK_API int32_t gllmk_gemv_allgather(gllmk_ctx ctx, gllmk_weight w, const float *x_dev, int64_t x_stride_t, int64_t x_stride_k,
+                             int32_t m, float *y_local, int64_t y_stride_t, int64_t y_stride_r, void *const *y_peers,
+                             int32_t n_peers, void *stream);
+GLLMK_API int32_t gllmk_peer_barrier(gllmk_ctx ctx, void *flags_local, void *const *flags_peers, int32_t n_peers, int32_t rank,
+                           uint32_t seq, void *stream);
+
 /* ---- prefill: fused dequantize + GEMM on tcgen05 tensor cores (any M) --------------------------- */
 
 /* Kernels::gemm_q4 / kquant_matmul / classic_matmul for large batches, and the matmul the reference

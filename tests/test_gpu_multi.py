@@ -1,0 +1,78 @@
+"""Row-sharded decode on 2 GPUs: the GEMV stores its band of y into both ranks' copies over peer pointers and
+a flag barrier says when they are complete.  One child process per GPU; skipped on a single-GPU box."""
+import importlib
+import os
+import socket
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import torch
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        gk = importlib.import_module("gllm-kernels_b200")
+        from oracle import oracle as O
+        K = gk.GpuKernels(rank)
+        cases = [("q4k", 256, 512, 1), ("q4k", 200, 256, 3), ("q8_0", 176, 96, 16)]
+        ex = gk.PeerExchange(K, world, rank, slots=len(cases), slot_floats=16 * 256)
+        for rep in range(3):  # the same slots are rewritten: sequence numbers and flag reuse
+            for slot, (fmt, n, k, m) in enumerate(cases):
+                rng = np.random.default_rng(n + k + m + rep)
+                W = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+                x = rng.standard_normal((m, k)).astype(np.float32)
+                qt, oid, blocks = ((gk.QuantType.q4k(), O.Q4K, O.quantize_q4_k(W)) if fmt == "q4k" else
+                                   (gk.QuantType.q8_0(), O.Q8_0, O.quantize_q8_0(W)))
+                r0, r1 = gk.shard_rows(n, world, rank)
+                w = K.upload(qt, r1 - r0, k, gk.slice_blocks(qt, blocks, n, k, r0, r1))
+                ex.gemv(w, torch.from_numpy(x).cuda(), slot, r0, n)
+                ex.barrier()
+                torch.cuda.synchronize()
+                assert K.status() == 0
+                y = ex.local_tensor(slot, (m, n)).cpu().numpy()
+                ref = O.quant_matmul(blocks, np.ascontiguousarray(x.T), oid, n, m, k).T
+                err = O.rel_err(y, ref)
+                assert err <= 2e-3, f"rank {rank} {fmt} n={n} m={m} rep={rep}: {err}"
+                w.free()
+                dist.barrier()  # nobody rewrites a slot another rank is still reading back to the host
+        ex.close()
+        K.close()
+        q.put((rank, "ok"))
+    except Exception as e:
+        q.put((rank, f"{type(e).__name__}: {e}"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_gemv_allgather_two_gpus():
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = dict(q.get(timeout=240) for _ in procs)
+    for p in procs:
+        p.join(timeout=30)
+    assert res == {0: "ok", 1: "ok"}, res
