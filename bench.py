@@ -149,8 +149,10 @@ def run_ours(args):
             if world == 1:
                 K.gemv(w, x, y=ys[i])
             elif ex is not None:
+                # gate and up read the same x and nothing reads them before down: one barrier covers both
                 ex.gemv(w, x, i, r0, n)
-                ex.barrier()
+                if name != "gate":
+                    ex.barrier()
             else:
                 K.gemv(w, x, y=gbufs[i][rank])
                 dist.all_gather_into_tensor(gbufs[i].view(-1), gbufs[i][rank].view(-1))
@@ -158,6 +160,26 @@ def run_ours(args):
     for _ in range(max(args.warmup, 3)):
         step()
     torch.cuda.synchronize()
+    graphed = False
+    if not args.no_graph and (world == 1 or ex is not None):
+        # one decode step = 12 x (staging, GEMV[, barrier]) launches of ~10-30 us each: replayed as a CUDA graph so
+        # that the host's launch cost does not bound the step (all context buffers exist after the warm-up)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            step()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step()
+        eager_step, step = step, graph.replay
+        graphed = True
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     sampler = ClockSampler(local)
@@ -209,7 +231,7 @@ def run_ours(args):
         "vs_baseline": None, "dtype": "u4 weights x f32 activations, f32 accumulate", "data": "synthetic",
         "config": {"workload": f"config 5: 70B-shaped FFN decode, {L} layers x (gate, up, down) Q4_K, M={M}",
                    "layers": L, "M": M, "N_ff": N_FF, "d_model": D_MODEL, "weight_bytes_per_step": weight_bytes_total,
-                   "l2": "per-GPU weight set larger than L2, no flush",
+                   "l2": "per-GPU weight set larger than L2, no flush", "cuda_graph": graphed,
                    "parallelism": "single GPU" if world == 1 else (
                        f"N-wise row shards x{world}, GEMV stores its band into every rank's y over NVLink peer pointers + flag barrier"
                        if ex is not None else f"N-wise row shards x{world} + NCCL all-gather")},
@@ -221,7 +243,7 @@ def run_ours(args):
                      "traffic_note": "bytes per gemv_kernel launch on one 28672x8192 matrix (algorithmic 132.27e6), ncu",
                      "peak_kind": peak_kind,
                      "kernel": "gemv_kernel<Q4_K, 1 n-tile> (+ stage_x_kernel), per-GPU average"},
-        "gpu_launches": args.steps * len(weights) * (2 if world == 1 else (3 if ex is not None else 2)),
+        "gpu_launches": args.steps * len(weights) * 2 if ex is None else args.steps * (len(weights) * 2 + 2 * L),
         "device_status": K.status(),
         "clocks": clocks,
         "e2e": e2e,
@@ -494,6 +516,7 @@ def main():
     ap.add_argument("--m", type=int, default=1)
     ap.add_argument("--no-extra", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying a CUDA graph")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="N > 1: how the bands of y reach every rank (peer stores fused into the GEMV, or NCCL all-gather)")
     ap.add_argument("--case", default="decode", choices=["decode", "prefill_q4k", "prefill_nvfp4"],

@@ -21,19 +21,33 @@ struct PeerBarrierParams {
 // thread q talks to the q-th other rank (rank numbers skip this rank)
 __global__ void peer_barrier_kernel(const __grid_constant__ PeerBarrierParams p) {
     const int q = threadIdx.x;
+    // seq == 0: the sequence number lives in this rank's flag area (word 16) and advances by one per barrier,
+    // so that a captured graph can be replayed
+    __shared__ uint32_t seq_s;
+    if (q == 0) {
+        uint32_t sq = p.seq;
+        if (sq == 0) {
+            sq = p.mine[16] + 1;
+            if (sq == 0) sq = 1;
+            p.mine[16] = sq;
+        }
+        seq_s = sq;
+    }
+    __syncthreads();
+    const uint32_t seq = seq_s;
     if (q >= p.npeer) return;
     const int src = q < p.rank ? q : q + 1;
     // everything this GPU wrote before this kernel (its GEMV's stores into the peers' buffers) is ordered
     // before the flag at system scope
     __threadfence_system();
-    asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(p.peer[q] + p.rank), "r"(p.seq) : "memory");
+    asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(p.peer[q] + p.rank), "r"(seq) : "memory");
     // bounded wait for the same sequence number from that rank (it can be at most one barrier ahead)
     const uint32_t *flag = p.mine + src;
     bool seen = false;
     for (uint32_t it = 0; it < (1u << 22) && !seen; it++) {
         uint32_t v;
         asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(flag) : "memory");
-        seen = (int32_t)(v - p.seq) >= 0;
+        seen = (int32_t)(v - seq) >= 0;
         if (!seen && it > 64) __nanosleep(200);
     }
     if (!seen) atomicExch(p.status, 31);  // the host reads it with gllmk_ctx_status; the kernel just returns

@@ -151,8 +151,9 @@ GLLMK_API int32_t gllmk_gemv(gllmk_ctx ctx, gllmk_weight w, const float *x_dev, 
  * gllmk_peer_barrier: on `stream`, after this rank's products: signal sequence number `seq` to every peer and
  *   wait (bounded, about a second; on time-out the context's status word becomes 31 and the kernel returns)
  *   until every peer has signalled `seq`.  `flags_peers[q]` is the q-th OTHER rank's flag words in rank
- *   order, `rank` this rank's number.  `seq` must grow by one per barrier, starting at 1.  After it, y is
- *   complete on this rank.  A buffer may be rewritten by peers one barrier after its last reader finished. */
+ *   order, `rank` this rank's number.  `seq` must grow by one per barrier, starting at 1; seq = 0 means
+ *   "use and advance the counter kept in this rank's flag area", which is what a captured CUDA graph
+ *   needs (every rank must then use 0 for every barrier).  After the barrier, y is complete on this rank.  A buffer may be rewritten by peers one barrier after its last reader finished. */
 #define GLLMK_MAX_PEERS 7
 #define GLLMK_IPC_HANDLE_BYTES 64
 #define GLLMK_PEER_FLAG_BYTES 256
