@@ -30,7 +30,7 @@ if ROOT not in sys.path:
 N_FF, D_MODEL = 28672, 8192
 Q4K_BLOCK_BYTES, Q4K_BLOCK = 144, 256
 METRIC = "quant GEMV weight-GB/s (Q4_K decode, 70B-shaped FFN)"
-GEMV_DRAM_TRAFFIC_PER_LAUNCH = 140.02e6
+GEMV_DRAM_TRAFFIC_PER_LAUNCH = 276.03e6
 
 
 def measured_peaks():
@@ -78,7 +78,7 @@ class ClockSampler(threading.Thread):
                         self.reasons.add(k)
             except Exception:
                 pass
-            self._stop_evt.wait(0.02)
+            self._stop_evt.wait(0.002)
 
     def stop(self):
         self._stop_evt.set()
@@ -112,7 +112,11 @@ def run_ours(args):
     M, L = args.m, args.layers
 
     # ---- synthetic weights: N(0, 0.02) f32 from the seed, quantized on the device, row-sharded ----
-    shapes = [("gate", N_FF, D_MODEL), ("up", N_FF, D_MODEL), ("down", D_MODEL, N_FF)]
+    # gate and up read the same x: by default they are stored as ONE weight of 2*N_ff rows (a load-time layout
+    # choice like the repack itself: same bytes, same arithmetic, y = gate || up), so a layer is two products
+    fused = not args.separate_gate_up
+    shapes = ([("gate_up", 2 * N_FF, D_MODEL), ("down", D_MODEL, N_FF)] if fused else
+              [("gate", N_FF, D_MODEL), ("up", N_FF, D_MODEL), ("down", D_MODEL, N_FF)])
     weights, host_blocks = [], []
     gen = torch.Generator(device=dev).manual_seed(20244)
     keep_host = rank == 0 and world == 1 and not args.no_cpu_baseline
@@ -135,7 +139,7 @@ def run_ours(args):
     # --exchange nccl: each rank's GEMV writes its slice of a [world, M, n/world] buffer, then one all-gather.
     gbufs, ex = [], None
     if world > 1 and args.exchange == "peer":
-        ex = gk.PeerExchange(K, world, rank, slots=len(weights), slot_floats=M * N_FF)
+        ex = gk.PeerExchange(K, world, rank, slots=len(weights), slot_floats=M * 2 * N_FF)
     elif world > 1:
         gbufs = [torch.empty((world, M, (r1 - r0)), dtype=torch.float32, device=dev) for (_, _, n, _, r0, r1) in weights]
 
@@ -229,7 +233,9 @@ def run_ours(args):
         "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "u4 weights x f32 activations, f32 accumulate", "data": "synthetic",
-        "config": {"workload": f"config 5: 70B-shaped FFN decode, {L} layers x (gate, up, down) Q4_K, M={M}",
+        "config": {"workload": f"config 5: 70B-shaped FFN decode, {L} layers x (gate, up, down) Q4_K, M={M}; " +
+                               ("gate and up stored as one 57344-row weight (2 products per layer)" if fused
+                                else "one product per matrix (3 per layer)"),
                    "layers": L, "M": M, "N_ff": N_FF, "d_model": D_MODEL, "weight_bytes_per_step": weight_bytes_total,
                    "l2": "per-GPU weight set larger than L2, no flush", "cuda_graph": graphed,
                    "parallelism": "single GPU" if world == 1 else (
@@ -237,10 +243,10 @@ def run_ours(args):
                        if ex is not None else f"N-wise row shards x{world} + NCCL all-gather")},
         "roofline": {"bound": "hbm", "achieved": algo_bytes_step / (ms_step * 1e-3) / 1e9 / world, "peak": peak,
                      "unit": "GB/s", "frac": algo_bytes_step / (ms_step * 1e-3) / 1e9 / world / peak,
-                     # dram__bytes_read + dram__bytes_write of one gemv_kernel launch on the 132.1 MB gate matrix,
-                     # from the ncu capture summarised in profiles/gemv_kernel_q4k_m1_gate28672x8192.md
-                     "traffic": GEMV_DRAM_TRAFFIC_PER_LAUNCH if (M == 1 and world == 1) else None,
-                     "traffic_note": "bytes per gemv_kernel launch on one 28672x8192 matrix (algorithmic 132.27e6), ncu",
+                     # dram__bytes_read + dram__bytes_write of one gemv_kernel launch on the 264.2 MB gate||up weight,
+                     # from the ncu capture summarised in profiles/gemv_kernel_q4k_m1_decode_cfg5.md
+                     "traffic": GEMV_DRAM_TRAFFIC_PER_LAUNCH if (M == 1 and world == 1 and fused) else None,
+                     "traffic_note": "bytes per gemv_kernel launch on the 57344x8192 gate||up weight (algorithmic 264.50e6), ncu",
                      "peak_kind": peak_kind,
                      "kernel": "gemv_kernel<Q4_K, 1 n-tile> (+ stage_x_kernel), per-GPU average"},
         "gpu_launches": args.steps * len(weights) * 2 if ex is None else args.steps * (len(weights) * 2 + 2 * L),
@@ -295,10 +301,57 @@ def extra_configs(K, gk, torch, dev, peak):
         for w in ws:
             w.free()
 
+    res["cfg5_decode_separate_gate_up"] = decode_layers(K, gk, torch, dev, gen, peak, fused=False)
     run(gk.QuantType.q4k(), 4096, 4096, [1], 32, "cfg1_q4k_4096x4096")
     run(gk.QuantType.q8_0(), 11008, 4096, [1, 4, 8, 16], 6, "cfg2_q8_0_11008x4096")
     res.update(extra_gemm(K, gk, torch, dev, gen))
     return res
+
+
+def decode_layers(K, gk, torch, dev, gen, peak, fused, layers=4):
+    """The headline workload with gate and up as two weights (fused=False: 3 products per layer) or as one weight
+    of 57344 rows (fused=True), graph replay."""
+    qt = gk.QuantType.q4k()
+    ws = []
+    for _ in range(layers):
+        for n, k in (((2 * N_FF, D_MODEL), (D_MODEL, N_FF)) if fused else ((N_FF, D_MODEL), (N_FF, D_MODEL), (D_MODEL, N_FF))):
+            W = torch.randn((n, k), generator=gen, device=dev) * 0.02
+            ws.append(K.upload(qt, n, k, K.quantize(qt, W)))
+            del W
+    torch.cuda.empty_cache()
+    xs = {D_MODEL: torch.randn((1, D_MODEL), generator=gen, device=dev), N_FF: torch.randn((1, N_FF), generator=gen, device=dev)}
+    ys = [torch.empty((1, w.n), dtype=torch.float32, device=dev) for w in ws]
+
+    def step():
+        for w, y in zip(ws, ys):
+            K.gemv(w, xs[w.k], y=y)
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 30
+    e0.record()
+    for _ in range(reps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    wbytes = sum(w.ref_bytes for w in ws)
+    for w in ws:
+        w.free()
+    return {"ms_per_step": ms, "weight_GBps": wbytes / ms / 1e6, "frac_hbm": wbytes / ms / 1e6 / peak, "products_per_step": len(ws)}
 
 
 def extra_gemm(K, gk, torch, dev, gen):
@@ -412,7 +465,11 @@ def run_reference(args):
     from oracle import oracle as O
     threads = os.cpu_count() or 1
     M, L = args.m, args.layers
-    shapes = [("gate", N_FF, D_MODEL), ("up", N_FF, D_MODEL), ("down", D_MODEL, N_FF)]
+    # gate and up read the same x: by default they are stored as ONE weight of 2*N_ff rows (a load-time layout
+    # choice like the repack itself: same bytes, same arithmetic, y = gate || up), so a layer is two products
+    fused = not args.separate_gate_up
+    shapes = ([("gate_up", 2 * N_FF, D_MODEL), ("down", D_MODEL, N_FF)] if fused else
+              [("gate", N_FF, D_MODEL), ("up", N_FF, D_MODEL), ("down", D_MODEL, N_FF)])
     rng = np.random.default_rng(20244)
     # one layer of distinct weights, reused for every layer of the step (CPU caches are far smaller than a matrix)
     host_blocks = []
@@ -439,7 +496,9 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 1), "ms_per_step": dt * 1e3 * L, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "u4 weights x f32 activations, f32 accumulate", "data": "synthetic",
-        "config": {"workload": f"config 5: 70B-shaped FFN decode, {L} layers x (gate, up, down) Q4_K, M={M}",
+        "config": {"workload": f"config 5: 70B-shaped FFN decode, {L} layers x (gate, up, down) Q4_K, M={M}; " +
+                               ("gate and up stored as one 57344-row weight (2 products per layer)" if fused
+                                else "one product per matrix (3 per layer)"),
                    "layers": L, "M": M, "N_ff": N_FF, "d_model": D_MODEL},
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port",
                          "sample": f"each step = one layer (gate, up, down, {layer_bytes} weight bytes) of the "
@@ -516,6 +575,7 @@ def main():
     ap.add_argument("--m", type=int, default=1)
     ap.add_argument("--no-extra", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--separate-gate-up", action="store_true", help="keep gate and up as two weights (3 products per layer)")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying a CUDA graph")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="N > 1: how the bands of y reach every rank (peer stores fused into the GEMV, or NCCL all-gather)")
