@@ -52,6 +52,7 @@ struct GemmParams {
     void *y;             // [m, n] row-major, leading dimension ldy
     int y_bf16;
     int64_t ldy;
+    int vec;             // Y allows 16-byte stores
     int ntok;            // MMA N of this launch (multiple of 32, <= 256)
     int row_tiles;       // 128-row tiles of the weight matrix
     int sb, r;           // ring depths: B stages, raw super-chunks
@@ -430,22 +431,19 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
             // every fourth group of 32 token columns
             tc::fence_after_sync();
             const int quad = warp & 3;
+            // all MMAs have completed, so the rings are free: each warp stages its blocks in 4 KB of the A ring
+            uint8_t *stage = smem + a_off + dw * 4096;
             for (int i = 0; i < mt; i++) {
-                const int64_t row = (int64_t)(tile0 + i) * WQ_BM + 32 * quad + lane;
+                const int64_t row_base = (int64_t)(tile0 + i) * WQ_BM + 32 * quad;
                 for (int c = 32 * (dw >> 2); c < p.ntok; c += 32 * (WQ_DW / 4)) {
                     uint32_t v[32];
                     tc::tmem_ld32(tmem_d + ((uint32_t)(32 * quad) << 16) + 256u * (uint32_t)i + (uint32_t)c, v);
                     tc::tmem_ld_wait();
-                    if (row < p.n) {
+                    float o[32];
 #pragma unroll
-                        for (int jj = 0; jj < 32; jj++) {
-                            const int64_t tok = tok0 + c + jj;
-                            if (tok < p.m) {
-                                if (p.y_bf16) static_cast<__nv_bfloat16 *>(p.y)[tok * p.ldy + row] = __float2bfloat16_rn(__uint_as_float(v[jj]));
-                                else static_cast<float *>(p.y)[tok * p.ldy + row] = __uint_as_float(v[jj]);
-                            }
-                        }
-                    }
+                    for (int jj = 0; jj < 32; jj++) o[jj] = __uint_as_float(v[jj]);
+                    if (p.y_bf16) tc::store_block_32x32<true>(p.y, p.ldy, row_base, tok0 + c, p.n, p.m, o, stage, lane, p.vec);
+                    else tc::store_block_32x32<false>(p.y, p.ldy, row_base, tok0 + c, p.n, p.m, o, stage, lane, p.vec);
                 }
             }
         } else if (!abort_s) {
@@ -492,6 +490,7 @@ int32_t gemm_launch(Ctx *c, const Weight *w, const void *a, int a_bf16, int64_t 
     p.y = y;
     p.y_bf16 = y_bf16;
     p.ldy = ldy;
+    p.vec = (((uintptr_t)y & 15) == 0 && (ldy * (y_bf16 ? 2 : 4)) % 16 == 0) ? 1 : 0;
     p.status = c->status_dev;
     p.row_tiles = (int)(w->n_pad / WQ_BM);
     // MMA N: whole 256-token tiles, or the tokens rounded up to a multiple of 32 when there are at most 128

@@ -10,7 +10,8 @@
 //   A = one weight tile, B = one or two activation tiles, and their scale atoms;
 // one thread copies the scale atoms to tensor memory (tcgen05.cp) and issues four
 // tcgen05.mma.kind::mxf4nvf4.block_scale (K = 64 each; kind::mxf4 for MXFP4) into a 128 x 256 f32
-// accumulator in TMEM; four warps read it back, apply the two per-tensor scales and store Y.
+// accumulator in TMEM; eight warps read it back, apply the two per-tensor scales and store Y (transposed through shared
+// memory, 16 bytes per lane).
 #include <cuda_bf16.h>
 
 #include "common.cuh"
@@ -24,7 +25,8 @@ constexpr int F4_A_BYTES = F4_BM * 128, F4_B_BYTES = F4_BN * 128;
 constexpr int F4_SFA_BYTES = 2048;          // 4 atoms (128 rows x 16 scales of 16 el; MXFP4 uses 2 of them)
 constexpr int F4_SFB_BYTES = 4096;
 constexpr int F4_STAGE_BYTES = F4_A_BYTES + F4_B_BYTES + F4_SFA_BYTES + F4_SFB_BYTES;
-constexpr int F4_THREADS = 192;             // warp 0: TMA, warp 1: MMA + TMEM, warps 2-5: epilogue
+constexpr int F4_EPI_WARPS = 8;              // two per TMEM lane quadrant, each takes every other block of 32 tokens
+constexpr int F4_THREADS = 64 + 32 * F4_EPI_WARPS;  // warp 0: copies, warp 1: MMA + TMEM, then the epilogue warps
 constexpr size_t F4_SMEM = (size_t)F4_STAGES * F4_STAGE_BYTES + 1024;
 constexpr uint32_t F4_TMEM_COLS = 512;      // 256 accumulator + 2 x (16 SFA + 32 SFB), power of two
 constexpr uint32_t F4_TMEM_SF = 256;        // scale-factor columns, two sets of 48 used by alternate k-steps
@@ -41,6 +43,7 @@ struct Fp4Params {
     void *y;
     int y_bf16;
     int64_t ldy;
+    int vec;             // Y allows 16-byte stores
     int *status;
 };
 
@@ -173,22 +176,18 @@ gemm_fp4_kernel(const __grid_constant__ Fp4Params p, const int ntok) {
         ok = __all_sync(0xffffffffu, ok);
         if (ok) {
             tc::fence_after_sync();
-            const int64_t row = row0 + 32 * quad + lane;
-            for (int c = 0; c < ntok; c += 32) {
+            // all MMAs have completed, so the pipeline stages are free: each epilogue warp stages its blocks in 4 KB
+            // of stage 0
+            uint8_t *stage = smem_raw + (smem_s - tc::smem_u32(smem_raw)) + (warp - 2) * 4096;
+            for (int c = 32 * ((warp - 2) >> 2); c < ntok; c += 32 * (F4_EPI_WARPS / 4)) {
                 uint32_t v[32];
                 tc::tmem_ld32(tmem + ((uint32_t)(32 * quad) << 16) + (uint32_t)c, v);
                 tc::tmem_ld_wait();
-                if (row < p.n) {
+                float o[32];
 #pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        const int64_t tok = tok0 + c + j;
-                        if (tok < p.m) {
-                            const float o = __uint_as_float(v[j]) * p.scale;
-                            if (p.y_bf16) static_cast<__nv_bfloat16 *>(p.y)[tok * p.ldy + row] = __float2bfloat16_rn(o);
-                            else static_cast<float *>(p.y)[tok * p.ldy + row] = o;
-                        }
-                    }
-                }
+                for (int j = 0; j < 32; j++) o[j] = __uint_as_float(v[j]) * p.scale;
+                if (p.y_bf16) tc::store_block_32x32<true>(p.y, p.ldy, row0 + 32 * quad, tok0 + c, p.n, p.m, o, stage, lane, p.vec);
+                else tc::store_block_32x32<false>(p.y, p.ldy, row0 + 32 * quad, tok0 + c, p.n, p.m, o, stage, lane, p.vec);
             }
         }
     }
@@ -224,6 +223,7 @@ int32_t gemm_fp4_launch(Ctx *c, const Weight *w, const Weight *x, void *y, int y
     p.y = y;
     p.y_bf16 = y_bf16;
     p.ldy = ldy;
+    p.vec = (((uintptr_t)y & 15) == 0 && (ldy * (y_bf16 ? 2 : 4)) % 16 == 0) ? 1 : 0;
     p.status = c->status_dev;
     dim3 grid((unsigned)(w->n_pad / F4_BM), (unsigned)((m + F4_BN - 1) / F4_BN));
     gemm_fp4_kernel<<<grid, F4_THREADS, F4_SMEM, s>>>(p, ntok);

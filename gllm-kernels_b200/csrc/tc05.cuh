@@ -2,6 +2,8 @@
 // Every wait is bounded: a wait that runs out returns false and the caller leaves through the
 // kernel's common exit (which still releases TMEM).
 #pragma once
+#include <cuda_bf16.h>
+
 #include <cstdint>
 
 namespace gllmk {
@@ -129,6 +131,63 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
 // four 32-lane quadrants
 __device__ __forceinline__ void tmem_cp_sf(uint32_t tmem_dst, uint64_t sdesc) {
     asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;\n" ::"r"(tmem_dst), "l"(sdesc) : "memory");
+}
+
+// ---- epilogue store of a 32-row x 32-token accumulator block ----
+// v[j] = value of (row row_base + lane, token tok_base + j), as tcgen05.ld hands it out (lane = row).  Y is
+// [tokens][rows] row-major, so lanes writing their own row would store 2- or 4-byte elements one token at a
+// time; instead the block goes through `stage` (4 KB of shared memory private to the warp) transposed, and
+// every lane stores 16 bytes of consecutive rows of one token.  `vec` = the 16-byte path is legal (Y base and
+// leading dimension 16-byte aligned); rows >= n or tokens >= m are skipped.
+template <bool BF16>
+__device__ __forceinline__ void store_block_32x32(void *y, int64_t ldy, int64_t row_base, int64_t tok_base, int64_t n, int64_t m,
+                                                  const float (&v)[32], uint8_t *stage, int lane, bool vec) {
+    if (!vec || row_base + 32 > n) {
+        const int64_t row = row_base + lane;
+        if (row < n) {
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+                const int64_t tok = tok_base + j;
+                if (tok < m) {
+                    if (BF16) static_cast<__nv_bfloat16 *>(y)[tok * ldy + row] = __float2bfloat16_rn(v[j]);
+                    else static_cast<float *>(y)[tok * ldy + row] = v[j];
+                }
+            }
+        }
+        return;
+    }
+    if (BF16) {
+        __nv_bfloat16 *st = reinterpret_cast<__nv_bfloat16 *>(stage);
+#pragma unroll
+        for (int j = 0; j < 32; j++) st[j * 32 + lane] = __float2bfloat16_rn(v[j]);
+        __syncwarp();
+        // a token's 32 rows are 64 bytes: 4 lanes x 16 bytes, 8 tokens per pass
+        const int part = lane & 3;
+#pragma unroll
+        for (int pass = 0; pass < 4; pass++) {
+            const int j = pass * 8 + (lane >> 2);
+            const int64_t tok = tok_base + j;
+            if (tok < m)
+                *reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(y) + tok * ldy + row_base + part * 8) =
+                    *reinterpret_cast<const uint4 *>(st + j * 32 + part * 8);
+        }
+    } else {
+        float *st = reinterpret_cast<float *>(stage);
+#pragma unroll
+        for (int j = 0; j < 32; j++) st[j * 32 + lane] = v[j];
+        __syncwarp();
+        // a token's 32 rows are 128 bytes: 8 lanes x 16 bytes, 4 tokens per pass
+        const int part = lane & 7;
+#pragma unroll
+        for (int pass = 0; pass < 8; pass++) {
+            const int j = pass * 4 + (lane >> 3);
+            const int64_t tok = tok_base + j;
+            if (tok < m)
+                *reinterpret_cast<uint4 *>(static_cast<float *>(y) + tok * ldy + row_base + part * 4) =
+                    *reinterpret_cast<const uint4 *>(st + j * 32 + part * 4);
+        }
+    }
+    __syncwarp();  // the staging block is rewritten by the next call
 }
 
 }  // namespace tc
