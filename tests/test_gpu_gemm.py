@@ -160,3 +160,32 @@ def test_gemm_fp4_nvfp4_shapes(gk, K, oracle, n, k, m):
 @pytest.mark.parametrize("n,k,m", [(128, 256, 128), (300, 1024, 384)])
 def test_gemm_fp4_mxfp4(gk, K, oracle, n, k, m):
     assert run_fp4_case(gk, K, oracle, "mxfp4", n, k, m, seed=n + m) <= 2e-3
+
+
+# ---- decode and host-pointer calls that land on the tensor-core kernel ------------------------------
+@pytest.mark.parametrize("fmt", ["mxfp4", "nvfp4"])
+def test_fp4_weights_decode_through_gemv_and_matmul_host(gk, K, oracle, fmt):
+    import torch
+    n, k = 200, 384
+    qt, blocks, scales, g, wd = quantized(oracle, gk, fmt, n, k, 21)
+    w = K.upload(qt, n, k, blocks, scales, g)
+    for m in (1, 5, 16):
+        x = np.random.default_rng(m).standard_normal((m, k)).astype(np.float32)
+        ref = oracle.gemm_f32_nt(x, wd)
+        y = K.gemv(w, torch.from_numpy(x).cuda()).cpu().numpy()
+        assert oracle.rel_err(y, ref) <= TOL
+        assert oracle.rel_err(K.matmul_host(w, x), ref) <= TOL
+    with pytest.raises(gk.GllmkError) as e:  # the [k, m] convention has no FP4 counterpart in the reference
+        K.matmul_host(w, np.zeros((k, 2), np.float32), ref_layout=True)
+    assert e.value.status == gk.Status.UNSUPPORTED
+    assert K.status() == 0
+    w.free()
+
+
+def test_matmul_host_prefill_batch_uses_one_gemm(gk, K, oracle):
+    n, k, m = 300, 512, 130
+    qt, blocks, _, _, wd = quantized(oracle, gk, "q4k", n, k, 22)
+    w = K.upload(qt, n, k, blocks)
+    x = np.random.default_rng(5).standard_normal((m, k)).astype(np.float32)
+    assert oracle.rel_err(K.matmul_host(w, x), oracle.gemm_f32_nt(x, wd)) <= TOL
+    w.free()
