@@ -1,5 +1,7 @@
 // extern "C" boundary of libgllmk.so (declared in include/gllmk.h).  Argument validation happens
 // here, before any launch; nothing below throws.
+#include <vector>
+
 #include "common.cuh"
 
 namespace gllmk {
@@ -406,6 +408,32 @@ int32_t gllmk_gemm(gllmk_ctx ctx, gllmk_weight wh, const void *a_dev, int32_t a_
     }
     return gemm_launch(c, w, a_dev, a_dtype == GLLMK_DTYPE_BF16, lda, m, y_dev, y_dtype == GLLMK_DTYPE_BF16, ldy,
                        static_cast<cudaStream_t>(stream));
+}
+
+int32_t gllmk_gemm_grouped(gllmk_ctx ctx, int32_t n_groups, const gllmk_weight *weights, const void *a_dev, int32_t a_dtype,
+                           int64_t lda, const int64_t *row_offsets, void *y_dev, int32_t y_dtype, int64_t ldy, void *stream) {
+    if (!ctx || !weights || !a_dev || !y_dev || !row_offsets) return GLLMK_STATUS_INVALID_ARG;
+    Ctx *c = static_cast<Ctx *>(ctx);
+    if (n_groups < 1 || n_groups > 4096) return fail(c, GLLMK_STATUS_INVALID_ARG, "gemm_grouped: n_groups=%d", n_groups);
+    if ((a_dtype != GLLMK_DTYPE_F32 && a_dtype != GLLMK_DTYPE_BF16) || (y_dtype != GLLMK_DTYPE_F32 && y_dtype != GLLMK_DTYPE_BF16))
+        return fail(c, GLLMK_STATUS_UNSUPPORTED, "gemm_grouped: dtype must be f32 or bf16");
+    const Weight *w0 = static_cast<const Weight *>(weights[0]);
+    if (!w0) return GLLMK_STATUS_INVALID_ARG;
+    std::vector<const Weight *> ws((size_t)n_groups);
+    for (int g = 0; g < n_groups; g++) {
+        const Weight *w = static_cast<const Weight *>(weights[g]);
+        if (!w) return GLLMK_STATUS_INVALID_ARG;
+        if (w->qt != w0->qt || w->n != w0->n || w->k != w0->k || w->mx_block != w0->mx_block)
+            return fail(c, GLLMK_STATUS_INVALID_ARG, "gemm_grouped: weight %d differs in type or shape from weight 0", g);
+        if (w->device != c->device) return fail(c, GLLMK_STATUS_INVALID_ARG, "weight lives on another device");
+        if (row_offsets[g + 1] < row_offsets[g] || row_offsets[g] < 0 || row_offsets[g + 1] > 0x7fffffff)
+            return fail(c, GLLMK_STATUS_INVALID_ARG, "gemm_grouped: row_offsets must be non-decreasing and fit 31 bits");
+        ws[(size_t)g] = w;
+    }
+    if (lda < w0->k || ldy < w0->n) return fail(c, GLLMK_STATUS_INVALID_ARG, "gemm_grouped: leading dimension smaller than the row");
+    DeviceGuard g(c->device);
+    return gemm_grouped_launch(c, ws.data(), n_groups, a_dev, a_dtype == GLLMK_DTYPE_BF16, lda, row_offsets, y_dev,
+                               y_dtype == GLLMK_DTYPE_BF16, ldy, static_cast<cudaStream_t>(stream));
 }
 
 int32_t gllmk_gemm_fp4(gllmk_ctx ctx, gllmk_weight wh, gllmk_weight xh, void *y_dev, int32_t y_dtype, int64_t ldy, void *stream) {

@@ -124,6 +124,8 @@ size_t gemv_ws_bytes(const Weight *w, int m);
 // ---- gemm.cu ----
 int32_t gemm_launch(Ctx *c, const Weight *w, const void *a, int a_bf16, int64_t lda, int m, void *y, int y_bf16, int64_t ldy,
                     cudaStream_t s);
+int32_t gemm_grouped_launch(Ctx *c, const Weight *const *ws, int n_groups, const void *a, int a_bf16, int64_t lda,
+                            const int64_t *row_offsets, void *y, int y_bf16, int64_t ldy, cudaStream_t s);
 // ---- gemm_fp4.cu ----
 int32_t gemm_fp4_launch(Ctx *c, const Weight *w, const Weight *x, void *y, int y_bf16, int64_t ldy, cudaStream_t s);
 // ---- quantize.cu ----

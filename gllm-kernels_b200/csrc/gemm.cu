@@ -41,15 +41,31 @@ __host__ __device__ constexpr int wq_raw_bytes(int fmt) {
     return fmt == FMT_Q4K ? 8 * Q4K_CHUNK : (fmt == FMT_Q80 ? 8 * Q80_CHUNK : (fmt == FMT_NVFP4 ? WQ_TILE + 2048 : WQ_TILE + 1024));
 }
 
+constexpr int WQ_MAX_GROUPS = 32;      // weights (experts) per launch
+constexpr int WQ_MAX_TOK_TILES = 64;   // token tiles per launch
+constexpr int WQ_MAX_IMG_TILES = 128;  // 128-row activation images per launch
+
+// One launch serves up to WQ_MAX_GROUPS weights of the same shape and format, each with its own rows of the
+// activation matrix (a mixture-of-experts layer; a plain GEMM is one group).  blockIdx.x walks the token tiles.
+struct GemmGroups {
+    const uint8_t *qs[WQ_MAX_GROUPS];   // weight plane (format-specific, see common.cuh)
+    const uint8_t *aux[WQ_MAX_GROUPS];  // FP4 scale-factor plane
+    float gs[WQ_MAX_GROUPS];            // NVFP4 per-tensor scale
+    int tile_group[WQ_MAX_TOK_TILES];   // which weight
+    int tile_tok0[WQ_MAX_TOK_TILES];    // first row of a / y
+    int tile_cnt[WQ_MAX_TOK_TILES];     // rows (<= ntok)
+    int tile_img[WQ_MAX_TOK_TILES];     // first activation image of the tile
+};
+struct ImgTiles {
+    int tok0[WQ_MAX_IMG_TILES];  // first row of a in the image
+    int cnt[WQ_MAX_IMG_TILES];   // rows present (the rest of the 128 are zero)
+};
+
 struct GemmParams {
-    const uint8_t *qs;   // weight plane (format-specific, see common.cuh)
-    const uint8_t *aux;  // FP4 scale-factor plane
     int64_t n;
     int nsc;             // super-chunks (256 k) per row
-    float global_scale;
-    const uint8_t *xt;   // fp16 activation tile images [token tile of 128][k-step of 64][16384]
-    int m;
-    void *y;             // [m, n] row-major, leading dimension ldy
+    const uint8_t *xt;   // fp16 activation tile images [image][k-step of 64][16384]
+    void *y;             // [tokens, n] row-major, leading dimension ldy
     int y_bf16;
     int64_t ldy;
     int vec;             // Y allows 16-byte stores
@@ -60,17 +76,19 @@ struct GemmParams {
 };
 
 // ---- activations -> fp16 tile images ------------------------------------------------------------
-// grid (k-steps, token tiles of 128); rows >= m and k >= k_valid are zero
-__global__ void __launch_bounds__(256) stage_act_kernel(const void *__restrict__ a, int a_bf16, int64_t lda, int m, int64_t k_valid,
-                                                        uint8_t *__restrict__ xt) {
+// grid (k-steps, images of 128 rows); rows past an image's count and k >= k_valid are zero
+__global__ void __launch_bounds__(256) stage_act_kernel(const void *__restrict__ a, int a_bf16, int64_t lda, int64_t k_valid,
+                                                        uint8_t *__restrict__ xt, const __grid_constant__ ImgTiles imgs) {
     const int ks = blockIdx.x, tile = blockIdx.y;
+    const int64_t img_tok0 = imgs.tok0[tile];
+    const int img_cnt = imgs.cnt[tile];
     uint8_t *dst = xt + ((size_t)tile * gridDim.x + ks) * WQ_TILE;
 #pragma unroll
     for (int i = 0; i < 4; i++) {
         const int item = threadIdx.x + 256 * i, row = item >> 3, chunk = item & 7;
-        const int64_t tok = (int64_t)tile * 128 + row, k0 = (int64_t)ks * 64 + chunk * 8;
+        const int64_t tok = img_tok0 + row, k0 = (int64_t)ks * 64 + chunk * 8;
         uint4 o = make_uint4(0, 0, 0, 0);
-        if (tok < m && k0 < k_valid) {
+        if (row < img_cnt && k0 < k_valid) {
             if (a_bf16) {
                 // bf16 -> fp16 through f32, saturating at +-65504
                 const uint4 v = __ldg(reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(a) + tok * lda + k0));
@@ -262,7 +280,7 @@ struct Dequant<FMT_MXFP4> : DequantFp4<FMT_MXFP4> {};
 // Sequence numbers: raw super-chunk q = j * mt + i (k-block j, row tile i of the CTA), A tile a = ks * mt + i
 // (k-step ks); B stage = ks.  Each ring slot is sequence % depth with the usual phase parity.
 template <int FMT, int MT>
-__global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_constant__ GemmParams p) {
+__global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ GemmGroups G) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bars[2 * WQ_SA + 2 * WQ_MAX_SB + 2 * WQ_MAX_R + 1];
     __shared__ uint32_t tmem_base_s;
@@ -279,7 +297,8 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile0 = blockIdx.y * MT;
     const int mt = min(MT, p.row_tiles - tile0);  // row tiles this CTA really has
-    const int64_t tok0 = (int64_t)blockIdx.x * WQ_BN;
+    const int grp_id = G.tile_group[blockIdx.x];
+    const int64_t tok0 = G.tile_tok0[blockIdx.x], tok_end = tok0 + G.tile_cnt[blockIdx.x];
     const int nks = 4 * p.nsc;
     volatile int *abort_flag = &abort_s;
 
@@ -323,11 +342,11 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
                     tc::mbar_expect_tx(rawfull + 8 * slot, RAW);
                     if (FMT == FMT_Q4K || FMT == FMT_Q80) {
                         // the eight 16-row chunks of a 128-row tile for k-block jb are contiguous
-                        bulk_g2s(dst, p.qs + ((size_t)tile * p.nsc + jb) * RAW, RAW, rawfull + 8 * slot);
+                        bulk_g2s(dst, G.qs[grp_id] + ((size_t)tile * p.nsc + jb) * RAW, RAW, rawfull + 8 * slot);
                     } else {
                         constexpr int SFB = RAW - WQ_TILE;
-                        bulk_g2s(dst, p.qs + ((size_t)tile * p.nsc + jb) * WQ_TILE, WQ_TILE, rawfull + 8 * slot);
-                        bulk_g2s(dst + WQ_TILE, p.aux + ((size_t)tile * p.nsc + jb) * SFB, SFB, rawfull + 8 * slot);
+                        bulk_g2s(dst, G.qs[grp_id] + ((size_t)tile * p.nsc + jb) * WQ_TILE, WQ_TILE, rawfull + 8 * slot);
+                        bulk_g2s(dst + WQ_TILE, G.aux[grp_id] + ((size_t)tile * p.nsc + jb) * SFB, SFB, rawfull + 8 * slot);
                     }
                     if (++slot == p.r) slot = 0, round++;
                 }
@@ -336,8 +355,9 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
     } else if (warp == 1) {
         // ---------------- activation tiles: one thread, bulk copies ----------------
         if (lane == 0) {
-            const int halves = (p.ntok + 127) / 128;
-            const uint32_t hbytes = (uint32_t)(p.ntok > 128 ? WQ_TILE : bstage);
+            // a tile of more than 128 tokens is two activation images: a whole one and the first ntok - 128 rows
+            const int halves = (p.ntok + 127) / 128, img0 = G.tile_img[blockIdx.x];
+            const uint32_t hbytes[2] = {(uint32_t)(p.ntok > 128 ? WQ_TILE : bstage), (uint32_t)(bstage - WQ_TILE)};
             int slot = 0, round = 0;
             for (int ks = 0; ks < nks; ks++) {
                 if (round > 0 && !tc::mbar_wait(emptyB + 8 * slot, (uint32_t)((round - 1) & 1), abort_flag)) {
@@ -348,7 +368,7 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
                 const uint32_t dst = smem_s + b_off + (uint32_t)(slot * bstage);
                 tc::mbar_expect_tx(fullB + 8 * slot, (uint32_t)bstage);
                 for (int h = 0; h < halves; h++)
-                    bulk_g2s(dst + h * WQ_TILE, p.xt + ((size_t)((tok0 >> 7) + h) * nks + ks) * WQ_TILE, hbytes, fullB + 8 * slot);
+                    bulk_g2s(dst + h * WQ_TILE, p.xt + ((size_t)(img0 + h) * nks + ks) * WQ_TILE, hbytes[h], fullB + 8 * slot);
                 if (++slot == p.sb) slot = 0, round++;
             }
         }
@@ -386,7 +406,7 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
         // ---------------- dequant warps, then epilogue ----------------
         const int dw = warp - 3, grp = dw >> 2, wg = dw & 3;
         Dequant<FMT> dq;
-        dq.global = p.global_scale;
+        dq.global = G.gs[grp_id];
         bool ok = true;
         // group grp makes the A tiles a = grp, grp + 4, ... (slot grp of the A ring); a = ks * mt + i.
         // mt == 1: the group always has quarter grp of every super-chunk; mt == 2: row tile i = grp % 2 and
@@ -442,8 +462,8 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
                     float o[32];
 #pragma unroll
                     for (int jj = 0; jj < 32; jj++) o[jj] = __uint_as_float(v[jj]);
-                    if (p.y_bf16) tc::store_block_32x32<true>(p.y, p.ldy, row_base, tok0 + c, p.n, p.m, o, stage, lane, p.vec);
-                    else tc::store_block_32x32<false>(p.y, p.ldy, row_base, tok0 + c, p.n, p.m, o, stage, lane, p.vec);
+                    if (p.y_bf16) tc::store_block_32x32<true>(p.y, p.ldy, row_base, tok0 + c, p.n, tok_end, o, stage, lane, p.vec);
+                    else tc::store_block_32x32<false>(p.y, p.ldy, row_base, tok0 + c, p.n, tok_end, o, stage, lane, p.vec);
                 }
             }
         } else if (!abort_s) {
@@ -458,47 +478,73 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
 
 // ---------------------------------------------------------------------------------------------
 template <int FMT, int MT>
-static int32_t launch_wq(Ctx *c, const GemmParams &p, dim3 grid, size_t smem, cudaStream_t s) {
+static int32_t launch_wq(Ctx *c, const GemmParams &p, const GemmGroups &G, dim3 grid, size_t smem, cudaStream_t s) {
     static bool attr_set = false;
     if (!attr_set) {
         GK_CUDA(c, cudaFuncSetAttribute(gemm_wq_kernel<FMT, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, WQ_SMEM_LIMIT + 1024));
         attr_set = true;
     }
-    gemm_wq_kernel<FMT, MT><<<grid, WQ_THREADS, smem, s>>>(p);
+    gemm_wq_kernel<FMT, MT><<<grid, WQ_THREADS, smem, s>>>(p, G);
     GK_CUDA(c, cudaGetLastError());
     return GLLMK_STATUS_OK;
 }
 template <int FMT>
-static int32_t launch_wq_mt(Ctx *c, const GemmParams &p, int mt, dim3 grid, size_t smem, cudaStream_t s) {
-    return mt == 2 ? launch_wq<FMT, 2>(c, p, grid, smem, s) : launch_wq<FMT, 1>(c, p, grid, smem, s);
+static int32_t launch_wq_mt(Ctx *c, const GemmParams &p, const GemmGroups &G, int mt, dim3 grid, size_t smem, cudaStream_t s) {
+    return mt == 2 ? launch_wq<FMT, 2>(c, p, G, grid, smem, s) : launch_wq<FMT, 1>(c, p, G, grid, smem, s);
 }
 
-int32_t gemm_launch(Ctx *c, const Weight *w, const void *a, int a_bf16, int64_t lda, int m, void *y, int y_bf16, int64_t ldy,
-                    cudaStream_t s) {
-    const int align = a_bf16 ? 8 : 4;
-    if (((uintptr_t)a & 15) || (lda % align)) return fail(c, GLLMK_STATUS_INVALID_ARG, "gemm: activations must be 16-byte aligned rows");
-    if (w->k % 8) return fail(c, GLLMK_STATUS_INVALID_ARG, "gemm: k=%lld is not a multiple of 8", (long long)w->k);
+// One launch: groups [g0, g1) with their token ranges cut into tiles of `ntok` tokens.
+static int32_t gemm_groups_chunk(Ctx *c, const Weight *const *ws, int ng, const void *a, int a_bf16, int64_t lda,
+                                 const int64_t *tok_begin, const int64_t *tok_count, int ntok, void *y, int y_bf16, int64_t ldy,
+                                 cudaStream_t s) {
+    const Weight *w = ws[0];
     const int fmt = w->qt == GLLMK_QUANT_Q4K ? FMT_Q4K : (w->qt == GLLMK_QUANT_Q8_0 ? FMT_Q80 : (w->qt == GLLMK_QUANT_NVFP4 ? FMT_NVFP4 : FMT_MXFP4));
     const int raw = wq_raw_bytes(fmt);
     GemmParams p{};
-    p.qs = static_cast<const uint8_t *>(w->qs);
-    p.aux = static_cast<const uint8_t *>(w->aux);
+    GemmGroups G{};
+    ImgTiles imgs{};
     p.n = w->n;
     p.nsc = (int)((w->k + 255) / 256);
-    p.global_scale = w->global_scale;
-    p.m = m;
     p.y = y;
     p.y_bf16 = y_bf16;
     p.ldy = ldy;
     p.vec = (((uintptr_t)y & 15) == 0 && (ldy * (y_bf16 ? 2 : 4)) % 16 == 0) ? 1 : 0;
     p.status = c->status_dev;
-    p.row_tiles = (int)(w->n_pad / WQ_BM);
-    // MMA N: whole 256-token tiles, or the tokens rounded up to a multiple of 32 when there are at most 128
-    p.ntok = (m > 128) ? WQ_BN : ((m + 31) / 32) * 32;
-    const int mtiles = (m + WQ_BN - 1) / WQ_BN;
-    const int bstage = p.ntok * 128;
-    // two row tiles per CTA when that still leaves at least one CTA per SM
-    int mt = ((p.row_tiles + 1) / 2) * mtiles >= c->sm_count ? 2 : 1;
+    p.ntok = ntok;
+    const int halves = (ntok + 127) / 128;
+    int ntiles = 0, nimg = 0;
+    for (int g = 0; g < ng; g++) {
+        G.qs[g] = static_cast<const uint8_t *>(ws[g]->qs);
+        G.aux[g] = static_cast<const uint8_t *>(ws[g]->aux);
+        G.gs[g] = ws[g]->global_scale;
+        for (int64_t t0 = 0; t0 < tok_count[g]; t0 += ntok) {
+            const int cnt = (int)(tok_count[g] - t0 < ntok ? tok_count[g] - t0 : ntok);
+            G.tile_group[ntiles] = g;
+            G.tile_tok0[ntiles] = (int)(tok_begin[g] + t0);
+            G.tile_cnt[ntiles] = cnt;
+            G.tile_img[ntiles] = nimg;
+            for (int h = 0; h < halves; h++) {
+                imgs.tok0[nimg] = (int)(tok_begin[g] + t0 + 128 * h);
+                imgs.cnt[nimg] = cnt - 128 * h < 0 ? 0 : (cnt - 128 * h > 128 ? 128 : cnt - 128 * h);
+                nimg++;
+            }
+            ntiles++;
+        }
+    }
+    if (ntiles == 0) return GLLMK_STATUS_OK;
+    const int row_tiles = (int)(w->n_pad / WQ_BM);
+    const int bstage = ntok * 128;
+    // Row tiles per CTA: two share one activation stage (less shared-memory fill traffic per flop, fixed costs
+    // paid once), but halve the CTA count.  Estimated time = waves x (tile steps per CTA x relative step cost +
+    // a fixed prologue / epilogue worth ~16 steps).
+    int mt = 1;
+    if (row_tiles % 2 == 0) {
+        const double step2 = ntok > 128 ? 0.8 : 0.9;
+        const int nks = 4 * p.nsc;
+        const auto waves = [&](int ctas) { return (double)((ctas + c->sm_count - 1) / c->sm_count); };
+        const double t1 = waves(ntiles * row_tiles) * (nks + 16.0), t2 = waves(ntiles * row_tiles / 2) * (2.0 * nks * step2 + 16.0);
+        if (t2 < t1) mt = 2;
+    }
     // shared-memory plan: four A tiles, at least mt + 1 raw super-chunks, the rest goes to B stages
     p.r = mt + 1;
     p.sb = (WQ_SMEM_LIMIT - WQ_SA * WQ_TILE - p.r * raw) / bstage;
@@ -512,21 +558,72 @@ int32_t gemm_launch(Ctx *c, const Weight *w, const void *a, int a_bf16, int64_t 
     const int more_r = (WQ_SMEM_LIMIT - WQ_SA * WQ_TILE - p.sb * bstage) / raw;
     p.r = more_r > WQ_MAX_R ? WQ_MAX_R : more_r;
     const size_t smem = 1024 + (size_t)WQ_SA * WQ_TILE + (size_t)p.sb * bstage + (size_t)p.r * raw;
+    p.row_tiles = row_tiles;
     // activations -> fp16 tile images in the context's scratch
-    const int atiles = (p.ntok > 128) ? 2 * mtiles : 1;
     const int nks = 4 * p.nsc;
-    int32_t rc = ensure_act(c, (size_t)atiles * nks * WQ_TILE);
+    int32_t rc = ensure_act(c, (size_t)nimg * nks * WQ_TILE);
     if (rc) return rc;
     p.xt = static_cast<const uint8_t *>(c->act);
-    stage_act_kernel<<<dim3((unsigned)nks, (unsigned)atiles), 256, 0, s>>>(a, a_bf16, lda, m, w->k, static_cast<uint8_t *>(c->act));
+    stage_act_kernel<<<dim3((unsigned)nks, (unsigned)nimg), 256, 0, s>>>(a, a_bf16, lda, w->k, static_cast<uint8_t *>(c->act), imgs);
     GK_CUDA(c, cudaGetLastError());
-    dim3 grid((unsigned)mtiles, (unsigned)((p.row_tiles + mt - 1) / mt));
+    dim3 grid((unsigned)ntiles, (unsigned)((row_tiles + mt - 1) / mt));
     switch (fmt) {
-        case FMT_Q4K: return launch_wq_mt<FMT_Q4K>(c, p, mt, grid, smem, s);
-        case FMT_Q80: return launch_wq_mt<FMT_Q80>(c, p, mt, grid, smem, s);
-        case FMT_NVFP4: return launch_wq_mt<FMT_NVFP4>(c, p, mt, grid, smem, s);
-        default: return launch_wq_mt<FMT_MXFP4>(c, p, mt, grid, smem, s);
+        case FMT_Q4K: return launch_wq_mt<FMT_Q4K>(c, p, G, mt, grid, smem, s);
+        case FMT_Q80: return launch_wq_mt<FMT_Q80>(c, p, G, mt, grid, smem, s);
+        case FMT_NVFP4: return launch_wq_mt<FMT_NVFP4>(c, p, G, mt, grid, smem, s);
+        default: return launch_wq_mt<FMT_MXFP4>(c, p, G, mt, grid, smem, s);
     }
+}
+
+// Groups g use rows [row_offsets[g], row_offsets[g + 1]) of a and y with weight ws[g] (all of one shape and type).
+int32_t gemm_grouped_launch(Ctx *c, const Weight *const *ws, int n_groups, const void *a, int a_bf16, int64_t lda,
+                            const int64_t *row_offsets, void *y, int y_bf16, int64_t ldy, cudaStream_t s) {
+    const int align = a_bf16 ? 8 : 4;
+    if (((uintptr_t)a & 15) || (lda % align)) return fail(c, GLLMK_STATUS_INVALID_ARG, "gemm: activations must be 16-byte aligned rows");
+    if (ws[0]->k % 8) return fail(c, GLLMK_STATUS_INVALID_ARG, "gemm: k=%lld is not a multiple of 8", (long long)ws[0]->k);
+    // MMA N: 256-token tiles, or the largest group rounded up to a multiple of 32 when no group has more
+    int64_t most = 0;
+    for (int g = 0; g < n_groups; g++) most = most > row_offsets[g + 1] - row_offsets[g] ? most : row_offsets[g + 1] - row_offsets[g];
+    if (most <= 0) return GLLMK_STATUS_OK;
+    const int ntok = most >= WQ_BN ? WQ_BN : (int)((most + 31) / 32 * 32);
+    const int halves = (ntok + 127) / 128;
+    // launches of at most WQ_MAX_GROUPS groups, WQ_MAX_TOK_TILES token tiles, WQ_MAX_IMG_TILES images
+    const Weight *cw[WQ_MAX_GROUPS];
+    int64_t cb[WQ_MAX_GROUPS], cc[WQ_MAX_GROUPS];
+    int ng = 0, tiles = 0;
+    const auto flush = [&]() -> int32_t {
+        if (ng == 0) return GLLMK_STATUS_OK;
+        const int32_t rc = gemm_groups_chunk(c, cw, ng, a, a_bf16, lda, cb, cc, ntok, y, y_bf16, ldy, s);
+        ng = 0;
+        tiles = 0;
+        return rc;
+    };
+    const int tile_cap = WQ_MAX_IMG_TILES / halves < WQ_MAX_TOK_TILES ? WQ_MAX_IMG_TILES / halves : WQ_MAX_TOK_TILES;
+    for (int g = 0; g < n_groups; g++) {
+        int64_t begin = row_offsets[g], left = row_offsets[g + 1] - row_offsets[g];
+        while (left > 0) {
+            if (ng == WQ_MAX_GROUPS || tiles == tile_cap) {
+                const int32_t rc = flush();
+                if (rc) return rc;
+            }
+            const int64_t room = (int64_t)(tile_cap - tiles) * ntok;
+            const int64_t take = left < room ? left : room;
+            cw[ng] = ws[g];
+            cb[ng] = begin;
+            cc[ng] = take;
+            ng++;
+            tiles += (int)((take + ntok - 1) / ntok);
+            begin += take;
+            left -= take;
+        }
+    }
+    return flush();
+}
+
+int32_t gemm_launch(Ctx *c, const Weight *w, const void *a, int a_bf16, int64_t lda, int m, void *y, int y_bf16, int64_t ldy,
+                    cudaStream_t s) {
+    const int64_t offs[2] = {0, m};
+    return gemm_grouped_launch(c, &w, 1, a, a_bf16, lda, offs, y, y_bf16, ldy, s);
 }
 
 }  // namespace gllmk

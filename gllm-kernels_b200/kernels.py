@@ -181,6 +181,20 @@ class GpuKernels:
         self._check(rc, "gllmk_gemm")
         return y
 
+    def gemm_grouped(self, weights, a, row_offsets, y=None, out_dtype=None, stream=None):
+        """Mixture-of-experts product in one launch: rows [row_offsets[g], row_offsets[g+1]) of `a` times weights[g]."""
+        import torch
+        ng = len(weights)
+        if y is None:
+            y = torch.empty((a.shape[0], weights[0].n), dtype=out_dtype or torch.float32, device=a.device)
+        dt = {torch.float32: 0, torch.bfloat16: 1}
+        hs = (C.c_void_p * ng)(*[w._h for w in weights])
+        offs = (C.c_int64 * (ng + 1))(*[int(o) for o in row_offsets])
+        rc = lib().gllmk_gemm_grouped(self._ctx, ng, hs, _ptr(a), dt[a.dtype], a.stride(0), offs, _ptr(y), dt[y.dtype],
+                                      y.stride(0), _stream(stream))
+        self._check(rc, "gllmk_gemm_grouped")
+        return y
+
     def gemm_fp4(self, w: Weight, x: Weight, y=None, out_dtype=None, stream=None):
         """Native FP4 x FP4 product: `x` is the activation matrix [m, k] quantized and uploaded like a weight."""
         import torch

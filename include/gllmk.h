@@ -184,11 +184,18 @@ GLLMK_API int32_t gllmk_peer_barrier(gllmk_ctx ctx, void *flags_local, void *con
 GLLMK_API int32_t gllmk_gemm(gllmk_ctx ctx, gllmk_weight w, const void *a_dev, int32_t a_dtype, int64_t lda, int32_t m,
                              void *y_dev, int32_t y_dtype, int64_t ldy, void *stream);
 
+/* A mixture-of-experts layer in one launch (no counterpart in the reference, which would loop over experts):
+ * group g multiplies rows [row_offsets[g], row_offsets[g+1]) of a (tokens already gathered per expert) by
+ * weights[g] and writes the same rows of y.  `row_offsets` is a HOST array of n_groups + 1 non-decreasing
+ * entries; all weights must have one type and shape; empty groups are allowed.  Same numerics as gllmk_gemm. */
+GLLMK_API int32_t gllmk_gemm_grouped(gllmk_ctx ctx, int32_t n_groups, const gllmk_weight *weights, const void *a_dev, int32_t a_dtype,
+                           int64_t lda, const int64_t *row_offsets, void *y_dev, int32_t y_dtype, int64_t ldy, void *stream);
+
 /* Both operands in FP4 (config "NVFP4 prefill GEMM": weights and activations quantized the same way;
  * the reference declares the format, src/quant.rs:357-371, and a native-FP4 capability,
  * DotProductCap::NativeFp4 / Tcgen05Fp4 in src/quant_format.rs:1007-1027, but ships no kernel).
  * `x` is the activation matrix [m, k] quantized with gllmk_quantize and uploaded with
- * gllmk_weight_upload like a weight (same type as `w`, NVFP4 or MXFP4; k a multiple of 256).
+ * gllmk_weight_upload like a weight (same type as `w`, NVFP4 or MXFP4).
  *   y[t, r] = gW * gX * sum_k W4[r, k] * X4[t, k]   -> y [m, n] row-major (ldy), f32 or bf16.
  * Products of the decoded FP4 values and their block scales are exact; accumulation is f32. */
 GLLMK_API int32_t gllmk_gemm_fp4(gllmk_ctx ctx, gllmk_weight w, gllmk_weight x, void *y_dev, int32_t y_dtype, int64_t ldy,

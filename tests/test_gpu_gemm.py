@@ -189,3 +189,43 @@ def test_matmul_host_prefill_batch_uses_one_gemm(gk, K, oracle):
     x = np.random.default_rng(5).standard_normal((m, k)).astype(np.float32)
     assert oracle.rel_err(K.matmul_host(w, x), oracle.gemm_f32_nt(x, wd)) <= TOL
     w.free()
+
+
+# ---- mixture of experts: several weights, one launch ---------------------------------------------------
+@pytest.mark.parametrize("fmt,counts,a_bf16", [("mxfp4", [70, 0, 128, 33, 129], True), ("q4k", [300, 17, 256], False),
+                                               ("nvfp4", [5, 5, 5, 5], True), ("q8_0", [40] * 34, False)])
+def test_gemm_grouped_matches_per_expert_products(gk, K, oracle, fmt, counts, a_bf16):
+    import torch
+    n, k = 200, 256
+    experts = [quantized(oracle, gk, fmt, n, k, 100 + e) for e in range(len(counts))]
+    ws = [K.upload(qt, n, k, b, s, g) for (qt, b, s, g, _) in experts]
+    offs = np.concatenate([[0], np.cumsum(counts)]).astype(np.int64)
+    x = np.random.default_rng(77).standard_normal((int(offs[-1]), k)).astype(np.float32)
+    xd = torch.from_numpy(x).cuda()
+    if a_bf16:
+        xd = xd.to(torch.bfloat16)
+        x = xd.to(torch.float32).cpu().numpy()
+    y = K.gemm_grouped(ws, xd, offs).cpu().numpy()
+    torch.cuda.synchronize()
+    assert K.status() == 0
+    for e, (_, _, _, _, wd) in enumerate(experts):
+        if counts[e]:
+            ref = oracle.gemm_f32_nt(x[offs[e]:offs[e + 1]], wd)
+            assert oracle.rel_err(y[offs[e]:offs[e + 1]], ref) <= TOL, (fmt, e)
+    for w in ws:
+        w.free()
+
+
+def test_gemm_grouped_rejects_mismatched_weights(gk, K, oracle):
+    import torch
+    qa, ba, _, _, _ = quantized(oracle, gk, "q8_0", 64, 64, 1)
+    qb, bb, _, _, _ = quantized(oracle, gk, "q8_0", 80, 64, 2)
+    wa, wb = K.upload(qa, 64, 64, ba), K.upload(qb, 80, 64, bb)
+    with pytest.raises(gk.GllmkError) as e:
+        K.gemm_grouped([wa, wb], torch.zeros((8, 64), device="cuda"), [0, 4, 8])
+    assert e.value.status == gk.Status.INVALID_ARG
+    with pytest.raises(gk.GllmkError) as e:
+        K.gemm_grouped([wa, wa], torch.zeros((8, 64), device="cuda"), [0, 5, 3])
+    assert e.value.status == gk.Status.INVALID_ARG
+    wa.free()
+    wb.free()
