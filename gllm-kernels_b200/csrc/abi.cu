@@ -353,13 +353,6 @@ int32_t gllmk_gemv(gllmk_ctx ctx, gllmk_weight wh, const float *x_dev, int64_t x
     if (row_scales && n_row_scales != 1 && n_row_scales != w->n) { row_scales = nullptr; n_row_scales = 0; }
     if (w->device != c->device) return fail(c, GLLMK_STATUS_INVALID_ARG, "weight lives on another device");
     DeviceGuard g(c->device);
-    if (w->qt == GLLMK_QUANT_MXFP4 || w->qt == GLLMK_QUANT_NVFP4) {
-        // no dedicated decode kernel for the FP4 formats: the tensor-core kernel with a 32-token tile serves them
-        // (row-major x and y, no row scales)
-        if (x_stride_k != 1 || y_stride_r != 1 || row_scales)
-            return fail(c, GLLMK_STATUS_UNSUPPORTED, "gemv on MXFP4 / NVFP4 weights needs unit k / row strides and no row scales");
-        return gemm_launch(c, w, x_dev, 0, x_stride_t, m, y_dev, 0, y_stride_t, static_cast<cudaStream_t>(stream));
-    }
     return gemv_launch(c, w, x_dev, x_stride_t, x_stride_k, m, y_dev, y_stride_t, y_stride_r, row_scales, n_row_scales,
                        static_cast<cudaStream_t>(stream));
 }
@@ -395,8 +388,7 @@ int32_t gllmk_gemm(gllmk_ctx ctx, gllmk_weight wh, const void *a_dev, int32_t a_
     DeviceGuard g(c->device);
     // A few dozen tokens are still bound by the weight stream, which the decode kernel reads at several times
     // the rate the tensor-core pipeline reaches with a nearly empty N: run them as passes of up to 16 tokens.
-    if (m <= GLLMK_GEMM_GEMV_MAX_M && a_dtype == GLLMK_DTYPE_F32 && y_dtype == GLLMK_DTYPE_F32 &&
-        (w->qt == GLLMK_QUANT_Q4K || w->qt == GLLMK_QUANT_Q8_0)) {
+    if (m <= GLLMK_GEMM_GEMV_MAX_M && a_dtype == GLLMK_DTYPE_F32 && y_dtype == GLLMK_DTYPE_F32) {
         for (int t0 = 0; t0 < m; t0 += GLLMK_GEMV_MAX_M) {
             const int mm = m - t0 < GLLMK_GEMV_MAX_M ? m - t0 : GLLMK_GEMV_MAX_M;
             const int32_t rc = gemv_launch(c, w, static_cast<const float *>(a_dev) + (int64_t)t0 * lda, lda, 1, mm,
@@ -466,11 +458,8 @@ static int32_t matmul_host_impl(Ctx *c, const Weight *w, const float *x_host, in
     const float *xd = reinterpret_cast<const float *>(dev + xo);
     float *yd = reinterpret_cast<float *>(dev + yo);
     const float *sd = sb ? reinterpret_cast<const float *>(dev + so) : nullptr;
-    const bool fp4 = w->qt == GLLMK_QUANT_MXFP4 || w->qt == GLLMK_QUANT_NVFP4;
-    if (fp4 && (ref_layout || sb))
-        return fail(c, GLLMK_STATUS_UNSUPPORTED, "MXFP4 / NVFP4 products take [m, k] activations and no row scales");
-    if (!ref_layout && !sb && (fp4 || m_t > GLLMK_GEMM_GEMV_MAX_M)) {
-        // prefill-sized batch (or a format without a decode kernel): one tensor-core GEMM
+    if (!ref_layout && !sb && m_t > GLLMK_GEMM_GEMV_MAX_M) {
+        // prefill-sized batch: one tensor-core GEMM
         rc = gemm_launch(c, w, xd, 0, k, m_t, yd, 0, n_w, c->stream);
         if (rc) return rc;
     } else

@@ -19,7 +19,7 @@
 
 namespace gllmk {
 
-constexpr int FMT_Q4K = 0, FMT_Q80 = 1;
+constexpr int FMT_Q4K = 0, FMT_Q80 = 1, FMT_MXFP4 = 2, FMT_NVFP4 = 3;
 
 // ---------------------------------------------------------------------------------------------
 // Activation image: one slice per 256 elements of k, the exact bytes a CTA copies into shared memory.
@@ -179,7 +179,9 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
 __device__ __forceinline__ uint32_t byte_of(uint32_t w, int i) { return __byte_perm(w, 0u, 0x4440u + (uint32_t)i); }
 
 struct GemvParams {
-    const uint8_t *chunks;  // weight plane (Q4K_CHUNK / Q80_CHUNK byte chunks, 8 per super-chunk)
+    const uint8_t *chunks;  // weight plane (Q4K_CHUNK / Q80_CHUNK byte chunks, 8 per super-chunk; FP4: 16 KB tile images)
+    const uint8_t *sf;      // FP4 scale-factor plane (1 KB / 2 KB of atoms per super-chunk)
+    float wscale;           // FP4: per-tensor scale x 1/2 (the int8 codes are twice the E2M1 values)
     const uint8_t *img;     // activation image
     float *y;
     int64_t yst, ysr;
@@ -203,11 +205,14 @@ constexpr int GEMV_STAGES = 3;  // pipeline depth (stages of one super-chunk + i
 constexpr int GEMV_WARPS = 8;
 constexpr int GEMV_ZERO = 512;  // zero region read by the lanes of unused MMA columns
 template <int FMT>
-__host__ __device__ constexpr int chunk_bytes() { return FMT == FMT_Q4K ? Q4K_CHUNK : Q80_CHUNK; }
+__host__ __device__ constexpr int chunk_bytes() { return FMT == FMT_Q4K ? Q4K_CHUNK : (FMT == FMT_Q80 ? Q80_CHUNK : 2048); }
+// FP4: a super-chunk is one tile image (128 rows x 256 k, 16 KB = 8 x 2048) plus its scale atoms
+template <int FMT>
+__host__ __device__ constexpr int sf_bytes() { return FMT == FMT_MXFP4 ? 1024 : (FMT == FMT_NVFP4 ? 2048 : 0); }
 // shared memory: [GEMV_STAGES][8 chunks + slice] | zero [512] | full[GEMV_STAGES], empty[GEMV_STAGES]
 template <int FMT>
 static inline size_t gemv_smem_bytes(int m) {
-    return (size_t)GEMV_STAGES * (GEMV_WARPS * chunk_bytes<FMT>() + slice_bytes(m)) + GEMV_ZERO + 2 * GEMV_STAGES * 8;
+    return (size_t)GEMV_STAGES * (GEMV_WARPS * chunk_bytes<FMT>() + sf_bytes<FMT>() + slice_bytes(m)) + GEMV_ZERO + 2 * GEMV_STAGES * 8;
 }
 
 // ---- one 16-row x 256-k chunk of Q4_K -------------------------------------------------------
@@ -358,6 +363,97 @@ __device__ __noinline__ void gemv_flush(const GemvParams &p, int tile, int slot,
     }
 }
 
+// ---- FP4 (MXFP4 / NVFP4): 16 rows x 256 k of a swizzled tile image ------------------------------------
+// Eight E2M1 codes of one word -> int8 values of TWICE the element (0, 1, 2, 3, 4, 6, 8, 12 with sign): byte
+// tables through prmt (3-bit index), the sign picks between the positive and the negative table.
+// lo = elements 0..3, hi = elements 4..7.
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;\n" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+__device__ __forceinline__ void fp4_to_s8(uint32_t w, uint32_t &lo, uint32_t &hi) {
+    const uint32_t POS_A = 0x03020100u, POS_B = 0x0C080604u, NEG_A = 0xFDFEFF00u, NEG_B = 0xF4F8FAFCu;
+    const uint32_t sel = w & 0x77777777u;
+    const uint32_t te = (w << 4) & 0x80808080u;  // byte m, bit 7 = sign of nibble 2m
+    const uint32_t to = w & 0x80808080u;         // byte m, bit 7 = sign of nibble 2m + 1
+    // selector nibbles with bit 3 set replicate the chosen byte's sign bit: 0xFF where the element is negative
+    const uint32_t m_lo = prmt(te, to, 0xD9C8u), m_hi = prmt(te, to, 0xFBEAu);
+    lo = (prmt(POS_A, POS_B, sel) & ~m_lo) | (prmt(NEG_A, NEG_B, sel) & m_lo);
+    hi = (prmt(POS_A, POS_B, sel >> 16) & ~m_hi) | (prmt(NEG_A, NEG_B, sel >> 16) & m_hi);
+}
+__device__ __forceinline__ float2 e4m3x2_to_f32(uint32_t two) {
+    uint32_t h;
+    asm("{\n.reg .b16 lo, hi;\nmov.b32 {lo, hi}, %1;\ncvt.rn.f16x2.e4m3x2 %0, lo;\n}\n" : "=r"(h) : "r"(two));
+    return __half22float2(*reinterpret_cast<const __half2 *>(&h));
+}
+// st: the stage (tile image, then the scale atoms); the warp owns rows 16*warp .. +15 of the tile.  Lane
+// (g, t) holds elements 8t..8t+7 of each 32-element block of rows g and g + 8: word t of 16-byte chunk bb.
+// tot[nt][2h + digit] as for Q8_0.  NVFP4 has a scale per 16 elements = lanes t < 2 / t >= 2 of a block, so
+// each block takes two MMAs with the other half's lanes supplying zeros.
+template <int FMT, int NT>
+__device__ __forceinline__ void fp4_chunk(uint32_t st, int warp, int lane, const uint32_t (&xb)[NT], const float (&xs)[NT],
+                                          float (&tot)[NT][4]) {
+    const int g = lane >> 2, t = lane & 3;
+    const int r0 = 16 * warp + g;  // r0 & 7 == (r0 + 8) & 7 == g
+    const uint32_t row0 = st + r0 * 128 + 4 * t, row1 = row0 + 8 * 128;
+    const uint32_t sfa = st + 16384 + (r0 & 31) * 16 + (r0 >> 5) * 4;  // rows r0 and r0 + 8 share r >> 5
+    float cs[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) cs[nt][0] = cs[nt][1] = cs[nt][2] = cs[nt][3] = 0.f;
+    if constexpr (FMT == FMT_MXFP4) {
+        // 8 scales per row: two atoms of 4
+        const uint32_t s0w[2] = {lds32(sfa), lds32(sfa + 512)}, s1w[2] = {lds32(sfa + 8 * 16), lds32(sfa + 512 + 8 * 16)};
+#pragma unroll
+        for (int bb = 0; bb < 8; bb++) {
+            uint32_t a0, a1, a2, a3;
+            fp4_to_s8(lds32(row0 + ((bb ^ g) << 4)), a0, a2);
+            fp4_to_s8(lds32(row1 + ((bb ^ g) << 4)), a1, a3);
+            const float d0 = e8m0_to_f32((s0w[bb >> 2] >> (8 * (bb & 3))) & 0xFFu), d1 = e8m0_to_f32((s1w[bb >> 2] >> (8 * (bb & 3))) & 0xFFu);
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                const uint2 b = lds64(xb[nt] + 32 * bb);
+                int c[4];
+                imma16832<true>(c, a0, a1, a2, a3, b.x, b.y);
+                cs[nt][0] = fmaf(d0, (float)c[0], cs[nt][0]);
+                cs[nt][1] = fmaf(d0, (float)c[1], cs[nt][1]);
+                cs[nt][2] = fmaf(d1, (float)c[2], cs[nt][2]);
+                cs[nt][3] = fmaf(d1, (float)c[3], cs[nt][3]);
+            }
+        }
+    } else {
+        const bool first = t < 2;  // this lane's 8 elements belong to the block's first 16
+#pragma unroll
+        for (int bb = 0; bb < 8; bb++) {
+            uint32_t a0, a1, a2, a3;
+            fp4_to_s8(lds32(row0 + ((bb ^ g) << 4)), a0, a2);
+            fp4_to_s8(lds32(row1 + ((bb ^ g) << 4)), a1, a3);
+            // 16 scales per row: atom bb / 2, scales 2 * (bb % 2) and + 1
+            const uint32_t s0 = lds32(sfa + (bb >> 1) * 512) >> (16 * (bb & 1)), s1 = lds32(sfa + (bb >> 1) * 512 + 8 * 16) >> (16 * (bb & 1));
+            // two UE4M3 scales at once with the hardware conversion (exact; 0x7F / 0xFF are NaN as in the reference)
+            const float2 dr0 = e4m3x2_to_f32(s0), dr1 = e4m3x2_to_f32(s1);
+            const float d00 = dr0.x, d01 = dr0.y, d10 = dr1.x, d11 = dr1.y;
+            const uint32_t f0 = first ? a0 : 0u, f1 = first ? a1 : 0u, f2 = first ? a2 : 0u, f3 = first ? a3 : 0u;
+            const uint32_t e0 = first ? 0u : a0, e1 = first ? 0u : a1, e2 = first ? 0u : a2, e3 = first ? 0u : a3;
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                const uint2 b = lds64(xb[nt] + 32 * bb);
+                int c[4], d[4];
+                imma16832<true>(c, f0, f1, f2, f3, b.x, b.y);
+                imma16832<true>(d, e0, e1, e2, e3, b.x, b.y);
+                cs[nt][0] = fmaf(d00, (float)c[0], fmaf(d01, (float)d[0], cs[nt][0]));
+                cs[nt][1] = fmaf(d00, (float)c[1], fmaf(d01, (float)d[1], cs[nt][1]));
+                cs[nt][2] = fmaf(d10, (float)c[2], fmaf(d11, (float)d[2], cs[nt][2]));
+                cs[nt][3] = fmaf(d10, (float)c[3], fmaf(d11, (float)d[3], cs[nt][3]));
+            }
+        }
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) tot[nt][j] = fmaf(xs[nt], cs[nt][j], tot[nt][j]);
+}
+
 // Balanced partition of the super-chunk sequence: CTA c owns [cta_first(c), cta_first(c + 1)).
 __device__ __forceinline__ int64_t cta_first(const GemvParams &p, int c) {
     return (int64_t)c * p.per_cta + min(c, p.rem);
@@ -375,7 +471,9 @@ template <int FMT, int NT>
 __global__ void __launch_bounds__(256) gemv_kernel(const __grid_constant__ GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int CHUNK = chunk_bytes<FMT>();
-    constexpr int SUPER = GEMV_WARPS * CHUNK;
+    constexpr int SFB = sf_bytes<FMT>();           // FP4 scale atoms of a super-chunk (own plane, own copy)
+    constexpr int WDATA = GEMV_WARPS * CHUNK;      // weight bytes of a super-chunk in the main plane
+    constexpr int SUPER = WDATA + SFB;             // weight bytes of a stage
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const uint32_t xbytes = slice_bytes(p.m);
@@ -390,7 +488,8 @@ __global__ void __launch_bounds__(256) gemv_kernel(const __grid_constant__ GemvP
     const int nk = p.nk;
     const int64_t sc0 = cta_first(p, (int)blockIdx.x), sc1 = cta_first(p, (int)blockIdx.x + 1);
     const int n = (int)(sc1 - sc0);
-    const uint8_t *wsrc = p.chunks + (size_t)sc0 * SUPER;
+    const uint8_t *wsrc = p.chunks + (size_t)sc0 * WDATA;
+    const uint8_t *sfsrc = SFB ? p.sf + (size_t)sc0 * SFB : nullptr;
     int TG = (int)(sc0 / nk), b = (int)(sc0 % nk);
 
     if (threadIdx.x == 0) {
@@ -405,7 +504,8 @@ __global__ void __launch_bounds__(256) gemv_kernel(const __grid_constant__ GemvP
         for (int s = 0; s < GEMV_STAGES; s++)
             if (s < n) {
                 mbar_expect_tx(full + 8 * s, stage_bytes);
-                bulk_g2s(smem_s + s * stage_bytes, wsrc + (size_t)s * SUPER, SUPER, full + 8 * s);
+                bulk_g2s(smem_s + s * stage_bytes, wsrc + (size_t)s * WDATA, WDATA, full + 8 * s);
+                if constexpr (SFB != 0) bulk_g2s(smem_s + s * stage_bytes + WDATA, sfsrc + (size_t)s * SFB, SFB, full + 8 * s);
             }
     }
     if (threadIdx.x < GEMV_ZERO / 4) reinterpret_cast<uint32_t *>(smem + (zero_s - smem_s))[threadIdx.x] = 0u;
@@ -455,7 +555,9 @@ __global__ void __launch_bounds__(256) gemv_kernel(const __grid_constant__ GemvP
                     atomicExch(p.status, 2);
                 } else {
                     mbar_expect_tx(full + 8 * ps, stage_bytes);
-                    bulk_g2s(smem_s + ps * stage_bytes, wsrc + (size_t)(i - 1 + GEMV_STAGES) * SUPER, SUPER, full + 8 * ps);
+                    bulk_g2s(smem_s + ps * stage_bytes, wsrc + (size_t)(i - 1 + GEMV_STAGES) * WDATA, WDATA, full + 8 * ps);
+                    if constexpr (SFB != 0)
+                        bulk_g2s(smem_s + ps * stage_bytes + WDATA, sfsrc + (size_t)(i - 1 + GEMV_STAGES) * SFB, SFB, full + 8 * ps);
                     bulk_g2s(smem_s + ps * stage_bytes + SUPER, p.img + (size_t)bx * xbytes, xbytes, full + 8 * ps);
                 }
                 if (++bx == nk) bx = 0;
@@ -474,7 +576,8 @@ __global__ void __launch_bounds__(256) gemv_kernel(const __grid_constant__ GemvP
             }
             const uint32_t ch = smem_s + st * stage_bytes + warp * CHUNK;
             if constexpr (FMT == FMT_Q4K) q4k_chunk<NT>(ch, lane, xb, sb, xs, tot);
-            else q80_chunk<NT>(ch, lane, xb, xs, tot);
+            else if constexpr (FMT == FMT_Q80) q80_chunk<NT>(ch, lane, xb, xs, tot);
+            else fp4_chunk<FMT, NT>(smem_s + st * stage_bytes, warp, lane, xb, xs, tot);
             __syncwarp();
             if (lane == 0) mbar_arrive(empty + 8 * st);
             if (++st == GEMV_STAGES) { st = 0; ph ^= 1u; }
@@ -491,6 +594,10 @@ __global__ void __launch_bounds__(256) gemv_kernel(const __grid_constant__ GemvP
             } else {
                 v[nt][0] = fmaf(tot[nt][1], 1.0f / 254.0f, tot[nt][0]);
                 v[nt][1] = fmaf(tot[nt][3], 1.0f / 254.0f, tot[nt][2]);
+                if constexpr (FMT == FMT_MXFP4 || FMT == FMT_NVFP4) {
+                    v[nt][0] *= p.wscale;
+                    v[nt][1] *= p.wscale;
+                }
             }
 #pragma unroll
             for (int j = 0; j < NTOT; j++) tot[nt][j] = 0.f;
@@ -572,7 +679,7 @@ static cudaError_t configure_and_launch(Ctx *c, GemvParams &p, int64_t ntg, cuda
 int32_t gemv_launch(Ctx *c, const Weight *w, const float *x, int64_t xst, int64_t xsk, int m, float *y, int64_t yst,
                     int64_t ysr, const float *row_scales, int64_t n_row_scales, cudaStream_t s, void *const *y_peers,
                     int n_peers) {
-    if (w->qt != GLLMK_QUANT_Q4K && w->qt != GLLMK_QUANT_Q8_0)
+    if (w->qt != GLLMK_QUANT_Q4K && w->qt != GLLMK_QUANT_Q8_0 && w->qt != GLLMK_QUANT_MXFP4 && w->qt != GLLMK_QUANT_NVFP4)
         return fail(c, GLLMK_STATUS_UNSUPPORTED, "gemv: quant type %d has no decode kernel", w->qt);
     int32_t rc = ensure_ws(c, gemv_ws_bytes(w, m));
     if (rc) return rc;
@@ -581,6 +688,8 @@ int32_t gemv_launch(Ctx *c, const Weight *w, const float *x, int64_t xst, int64_
     GemvParams p{};
     p.chunks = static_cast<const uint8_t *>(w->qs);
     p.img = static_cast<const uint8_t *>(c->ws);
+    p.sf = static_cast<const uint8_t *>(w->aux);
+    p.wscale = 0.5f * w->global_scale;
     p.y = y;
     p.yst = yst;
     p.ysr = ysr;
@@ -615,12 +724,26 @@ int32_t gemv_launch(Ctx *c, const Weight *w, const float *x, int64_t xst, int64_
             case 3: e = configure_and_launch<FMT_Q4K, 3>(c, p, ntg, s, &rc); break;
             default: e = configure_and_launch<FMT_Q4K, 4>(c, p, ntg, s, &rc); break;
         }
-    } else {
+    } else if (w->qt == GLLMK_QUANT_Q8_0) {
         switch (NT) {
             case 1: e = configure_and_launch<FMT_Q80, 1>(c, p, ntg, s, &rc); break;
             case 2: e = configure_and_launch<FMT_Q80, 2>(c, p, ntg, s, &rc); break;
             case 3: e = configure_and_launch<FMT_Q80, 3>(c, p, ntg, s, &rc); break;
             default: e = configure_and_launch<FMT_Q80, 4>(c, p, ntg, s, &rc); break;
+        }
+    } else if (w->qt == GLLMK_QUANT_MXFP4) {
+        switch (NT) {
+            case 1: e = configure_and_launch<FMT_MXFP4, 1>(c, p, ntg, s, &rc); break;
+            case 2: e = configure_and_launch<FMT_MXFP4, 2>(c, p, ntg, s, &rc); break;
+            case 3: e = configure_and_launch<FMT_MXFP4, 3>(c, p, ntg, s, &rc); break;
+            default: e = configure_and_launch<FMT_MXFP4, 4>(c, p, ntg, s, &rc); break;
+        }
+    } else {
+        switch (NT) {
+            case 1: e = configure_and_launch<FMT_NVFP4, 1>(c, p, ntg, s, &rc); break;
+            case 2: e = configure_and_launch<FMT_NVFP4, 2>(c, p, ntg, s, &rc); break;
+            case 3: e = configure_and_launch<FMT_NVFP4, 3>(c, p, ntg, s, &rc); break;
+            default: e = configure_and_launch<FMT_NVFP4, 4>(c, p, ntg, s, &rc); break;
         }
     }
     if (rc) return rc;

@@ -128,9 +128,9 @@ GLLMK_API int32_t gllmk_dequant(gllmk_ctx ctx, gllmk_weight w, float *out_dev, v
  * y_dev[t*y_stride_t + r*y_stride_r] — so the reference's [k, n]-input / [m, n]-output convention
  * is strides (1, n_ref) / (1, n_ref) and gemm_q4's [m, k] / [m, n] is (k, 1) / (n, 1).
  * `row_scales` (NULL, 1 or n entries on the device) multiplies row r's result like gemm_q4's
- * `scales`.  f32 accumulation; result within 2e-3 of the reference's sequential f32 sum.
- * MXFP4 / NVFP4 weights have no dedicated decode kernel yet: the call is served by the tensor-core kernel of
- * gllmk_gemm with a 32-token tile (unit k / row strides, no row scales, result within 1e-2). */
+ * `scales`.  f32 accumulation; result within 2e-3 of the reference's sequential f32 sum.  All four
+ * weight types (for MXFP4 / NVFP4 the reference has no matmul; the oracle is its dequant followed by the
+ * same f32 sum). */
 #define GLLMK_GEMV_MAX_M 16
 GLLMK_API int32_t gllmk_gemv(gllmk_ctx ctx, gllmk_weight w, const float *x_dev, int64_t x_stride_t, int64_t x_stride_k,
                    int32_t m, float *y_dev, int64_t y_stride_t, int64_t y_stride_r, const float *row_scales,
@@ -177,7 +177,7 @@ GLLMK_API int32_t gllmk_peer_barrier(gllmk_ctx ctx, void *flags_local, void *con
  *   y[t, r] = sum_k W[r, k] * a[t, k],  a [m, k] row-major (leading dimension lda), y [m, n] (ldy).
  * a_dtype / y_dtype: GLLMK_DTYPE_F32 or GLLMK_DTYPE_BF16.  Weights and activations are staged in fp16
  * (activations saturate at +-65504) and accumulated in f32: results within 1e-2 of the reference's f32
- * evaluation.  a and its rows must be 16-byte aligned.  With f32 in and out, Q4_K / Q8_0 weights and
+ * evaluation.  a and its rows must be 16-byte aligned.  With f32 in and out and
  * m <= GLLMK_GEMM_GEMV_MAX_M the call runs as passes of the decode kernel (gllmk_gemv), which is faster
  * there and meets its tighter bound. */
 #define GLLMK_GEMM_GEMV_MAX_M 48

@@ -162,23 +162,46 @@ def test_gemm_fp4_mxfp4(gk, K, oracle, n, k, m):
     assert run_fp4_case(gk, K, oracle, "mxfp4", n, k, m, seed=n + m) <= 2e-3
 
 
-# ---- decode and host-pointer calls that land on the tensor-core kernel ------------------------------
+# ---- FP4 weights on the decode kernel, and host batches that land on the tensor-core kernel -------------
 @pytest.mark.parametrize("fmt", ["mxfp4", "nvfp4"])
-def test_fp4_weights_decode_through_gemv_and_matmul_host(gk, K, oracle, fmt):
+@pytest.mark.parametrize("n,k", [(200, 384), (128, 256), (1000, 2048)])
+def test_fp4_weights_decode_kernel(gk, K, oracle, fmt, n, k):
     import torch
-    n, k = 200, 384
-    qt, blocks, scales, g, wd = quantized(oracle, gk, fmt, n, k, 21)
+    qt, blocks, scales, g, wd = quantized(oracle, gk, fmt, n, k, 21 + n)
     w = K.upload(qt, n, k, blocks, scales, g)
-    for m in (1, 5, 16):
+    for m in (1, 3, 5, 8, 16):
         x = np.random.default_rng(m).standard_normal((m, k)).astype(np.float32)
         ref = oracle.gemm_f32_nt(x, wd)
         y = K.gemv(w, torch.from_numpy(x).cuda()).cpu().numpy()
-        assert oracle.rel_err(y, ref) <= TOL
-        assert oracle.rel_err(K.matmul_host(w, x), ref) <= TOL
-    with pytest.raises(gk.GllmkError) as e:  # the [k, m] convention has no FP4 counterpart in the reference
-        K.matmul_host(w, np.zeros((k, 2), np.float32), ref_layout=True)
-    assert e.value.status == gk.Status.UNSUPPORTED
+        assert oracle.rel_err(y, ref) <= 2e-3, (fmt, m)
+    x = np.random.default_rng(99).standard_normal((5, k)).astype(np.float32)
+    ref = oracle.gemm_f32_nt(x, wd)
+    assert oracle.rel_err(K.matmul_host(w, x), ref) <= 2e-3
+    assert oracle.rel_err(K.matmul_host(w, np.ascontiguousarray(x.T), ref_layout=True), ref.T) <= 2e-3
+    # 33 f32 tokens through gllmk_gemm: three passes of the decode kernel
+    x = np.random.default_rng(98).standard_normal((33, k)).astype(np.float32)
+    assert oracle.rel_err(K.gemm(w, torch.from_numpy(x).cuda()).cpu().numpy(), oracle.gemm_f32_nt(x, wd)) <= 2e-3
     assert K.status() == 0
+    w.free()
+
+
+def test_fp4_decode_negative_zero_codes_and_scale_specials(gk, K, oracle):
+    """Every E2M1 code (incl. -0) in every position, E8M0 scales 0 (2^-127) and 254, NaN scale -> NaN row."""
+    import torch
+    n, k = 16, 256
+    rng = np.random.default_rng(4)
+    codes = rng.integers(0, 256, size=(n, k // 2), dtype=np.uint8)
+    codes[0, :16] = np.arange(16, dtype=np.uint8) * 17  # both nibbles run through all 16 codes
+    scales = rng.integers(118, 132, size=(n, k // 32), dtype=np.uint8)
+    scales[1, 0], scales[2, 3], scales[3, 1] = 0, 200, 255
+    w = K.upload(gk.QuantType.mxfp4(32), n, k, codes, scales)
+    wd = oracle.dequant_matrix(oracle.MXFP4, codes, n, k, scales=scales)
+    x = rng.standard_normal((2, k)).astype(np.float32)
+    y = K.gemv(w, torch.from_numpy(x).cuda()).cpu().numpy()
+    ref = oracle.gemm_f32_nt(x, wd)
+    assert np.isnan(y[:, 3]).all() and np.isnan(ref[:, 3]).all()
+    ok = [r for r in range(n) if r != 3]
+    assert oracle.rel_err(y[:, ok], ref[:, ok]) <= 2e-3
     w.free()
 
 
