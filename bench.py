@@ -278,8 +278,10 @@ def extra_configs(K, gk, torch, dev, peak):
         ws = []
         for _ in range(copies):
             W = torch.randn((n, k), generator=gen, device=dev) * 0.02
-            ws.append(K.upload(qt, n, k, K.quantize(qt, W)))
-            del W
+            q = K.quantize(qt, W)
+            ws.append(K.upload(qt, n, k, q[0], q[1]) if qt.id == 3 else (K.upload(qt, n, k, q[0], None, q[1]) if qt.id == 4
+                                                                           else K.upload(qt, n, k, q)))
+            del W, q
         wbytes = n * (k // bs) * bb
         for m in ms:
             x = torch.randn((m, k), generator=gen, device=dev)
@@ -304,6 +306,9 @@ def extra_configs(K, gk, torch, dev, peak):
     res["cfg5_decode_separate_gate_up"] = decode_layers(K, gk, torch, dev, gen, peak, fused=False)
     run(gk.QuantType.q4k(), 4096, 4096, [1], 32, "cfg1_q4k_4096x4096")
     run(gk.QuantType.q8_0(), 11008, 4096, [1, 4, 8, 16], 6, "cfg2_q8_0_11008x4096")
+    run(gk.QuantType.mxfp4(32), 14336, 4096, [1], 10, "cfg3_mxfp4_expert_decode_14336x4096")
+    run(gk.QuantType.nvfp4(), 14336, 4096, [1], 10, "cfg4_nvfp4_decode_14336x4096")
+    run(gk.QuantType.q4k(), N_FF, D_MODEL, [16], 3, "cfg5_q4k_28672x8192")
     res.update(extra_gemm(K, gk, torch, dev, gen))
     return res
 
