@@ -453,9 +453,12 @@ static int32_t matmul_host_impl(Ctx *c, const Weight *w, const float *x_host, in
     char *pin = static_cast<char *>(c->pin), *dev = static_cast<char *>(c->dev_io);
     memcpy(pin + xo, x_host, xb);
     if (sb) memcpy(pin + so, scales_host, sb);
-    GK_CUDA(c, cudaMemcpyAsync(dev + xo, pin + xo, xb, cudaMemcpyHostToDevice, c->stream));
+    // Small activation blocks are read by the staging kernel straight from the pinned buffer (mapped into the
+    // device's address space): one copy call and its latency less per product.  Larger ones go through HBM.
+    const bool zero_copy_x = xb <= (size_t)256 * 1024;
+    if (!zero_copy_x) GK_CUDA(c, cudaMemcpyAsync(dev + xo, pin + xo, xb, cudaMemcpyHostToDevice, c->stream));
     if (sb) GK_CUDA(c, cudaMemcpyAsync(dev + so, pin + so, sb, cudaMemcpyHostToDevice, c->stream));
-    const float *xd = reinterpret_cast<const float *>(dev + xo);
+    const float *xd = reinterpret_cast<const float *>(zero_copy_x ? pin + xo : dev + xo);
     float *yd = reinterpret_cast<float *>(dev + yo);
     const float *sd = sb ? reinterpret_cast<const float *>(dev + so) : nullptr;
     if (!ref_layout && !sb && m_t > GLLMK_GEMM_GEMV_MAX_M) {
