@@ -479,10 +479,11 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
 // ---------------------------------------------------------------------------------------------
 template <int FMT, int MT>
 static int32_t launch_wq(Ctx *c, const GemmParams &p, const GemmGroups &G, dim3 grid, size_t smem, cudaStream_t s) {
-    static bool attr_set = false;
-    if (!attr_set) {
+    static bool attr_set[64] = {};  // function attributes are per device
+    const int dev_slot = c->device & 63;
+    if (!attr_set[dev_slot]) {
         GK_CUDA(c, cudaFuncSetAttribute(gemm_wq_kernel<FMT, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, WQ_SMEM_LIMIT + 1024));
-        attr_set = true;
+        attr_set[dev_slot] = true;
     }
     gemm_wq_kernel<FMT, MT><<<grid, WQ_THREADS, smem, s>>>(p, G);
     GK_CUDA(c, cudaGetLastError());

@@ -202,10 +202,11 @@ int32_t gemm_fp4_launch(Ctx *c, const Weight *w, const Weight *x, void *y, int y
     if (w->qt != x->qt || (w->qt != GLLMK_QUANT_NVFP4 && w->qt != GLLMK_QUANT_MXFP4))
         return fail(c, GLLMK_STATUS_UNSUPPORTED, "gemm_fp4: both operands must be NVFP4 or both MXFP4");
     if (w->k != x->k) return fail(c, GLLMK_STATUS_INVALID_ARG, "gemm_fp4: k of the two operands must match");
-    static bool attr_set = false;
-    if (!attr_set) {
+    static bool attr_set[64] = {};  // function attributes are per device
+    const int dev_slot = c->device & 63;
+    if (!attr_set[dev_slot]) {
         GK_CUDA(c, cudaFuncSetAttribute(gemm_fp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)F4_SMEM));
-        attr_set = true;
+        attr_set[dev_slot] = true;
     }
     const int m = (int)x->n;
     const int ntok = (m > 128) ? 256 : 128;
