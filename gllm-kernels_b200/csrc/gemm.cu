@@ -31,7 +31,7 @@ constexpr int WQ_BN = 256;         // tokens per CTA (UMMA N, <= 256)
 constexpr int WQ_TILE = 16384;     // one operand tile: 128 rows x 128 bytes
 constexpr int WQ_SA = 4;           // operand A (dequantized weight tiles) ring: one slot per dequant group
 constexpr int WQ_MAX_SB = 12;      // operand B (activation) stages, at most
-constexpr int WQ_MAX_R = 6;        // raw super-chunk ring, at most
+constexpr int WQ_MAX_R = 8;        // raw super-chunk ring, at most
 constexpr int WQ_DW = 16;          // dequant warps
 constexpr int WQ_THREADS = 96 + 32 * WQ_DW;  // warp 0: raw copies, warp 1: activation copies, warp 2: MMA + TMEM, then dequant / epilogue warps
 constexpr int WQ_SMEM_LIMIT = 232448 - 1024 - 1024;  // ring space: 227 KB less the static variables' share and the alignment slack
@@ -546,18 +546,21 @@ static int32_t gemm_groups_chunk(Ctx *c, const Weight *const *ws, int ng, const 
         const double t1 = waves(ntiles * row_tiles) * (nks + 16.0), t2 = waves(ntiles * row_tiles / 2) * (2.0 * nks * step2 + 16.0);
         if (t2 < t1) mt = 2;
     }
-    // shared-memory plan: four A tiles, at least mt + 1 raw super-chunks, the rest goes to B stages
-    p.r = mt + 1;
-    p.sb = (WQ_SMEM_LIMIT - WQ_SA * WQ_TILE - p.r * raw) / bstage;
-    if (p.sb < 2 && mt == 2) {  // big raw super-chunks (Q8_0) with a 256-token tile: one row tile per CTA
-        mt = 1;
-        p.r = 2;
-        p.sb = (WQ_SMEM_LIMIT - WQ_SA * WQ_TILE - p.r * raw) / bstage;
+    // Shared-memory plan: four A tiles; three B stages (activation tiles come from L2: ~1 us of latency against
+    // 0.2 - 0.5 us per k-step); everything else goes to the raw ring, because the weight stream comes from HBM and
+    // with few tokens a k-step is short: two super-chunks in flight per SM cap the stream at ~15 GB/s per SM.
+    p.sb = 3;
+    p.r = (WQ_SMEM_LIMIT - WQ_SA * WQ_TILE - p.sb * bstage) / raw;
+    if (p.r < mt + 1) {  // big raw super-chunks (Q8_0) with a 256-token tile
+        p.sb = 2;
+        p.r = (WQ_SMEM_LIMIT - WQ_SA * WQ_TILE - p.sb * bstage) / raw;
+        if (p.r < mt + 1) mt = 1;
     }
-    if (p.sb > WQ_MAX_SB) p.sb = WQ_MAX_SB;
-    if (p.sb < 2) return fail(c, GLLMK_STATUS_RUNTIME_ERROR, "gemm: shared-memory plan does not fit");
-    const int more_r = (WQ_SMEM_LIMIT - WQ_SA * WQ_TILE - p.sb * bstage) / raw;
-    p.r = more_r > WQ_MAX_R ? WQ_MAX_R : more_r;
+    if (p.r > WQ_MAX_R) p.r = WQ_MAX_R;
+    if (p.r < mt + 1) return fail(c, GLLMK_STATUS_RUNTIME_ERROR, "gemm: shared-memory plan does not fit");
+    // what the raw ring cannot use goes back to B stages
+    const int more_sb = (WQ_SMEM_LIMIT - WQ_SA * WQ_TILE - p.r * raw) / bstage;
+    p.sb = more_sb > WQ_MAX_SB ? WQ_MAX_SB : more_sb;
     const size_t smem = 1024 + (size_t)WQ_SA * WQ_TILE + (size_t)p.sb * bstage + (size_t)p.r * raw;
     p.row_tiles = row_tiles;
     // activations -> fp16 tile images in the context's scratch
