@@ -321,6 +321,7 @@ def extra_configs(K, gk, torch, dev, peak):
             w.free()
 
     res["cfg5_decode_separate_gate_up"] = decode_layers(K, gk, torch, dev, gen, peak, fused=False)
+    res["cfg5_ffn_decode_swiglu"] = decode_layers(K, gk, torch, dev, gen, peak, fused=True, ffn=True)
     run(gk.QuantType.q4k(), 4096, 4096, [1], 32, "cfg1_q4k_4096x4096")
     run(gk.QuantType.q8_0(), 11008, 4096, [1, 4, 8, 16], 6, "cfg2_q8_0_11008x4096")
     run(gk.QuantType.mxfp4(32), 14336, 4096, [1], 10, "cfg3_mxfp4_expert_decode_14336x4096")
@@ -330,9 +331,10 @@ def extra_configs(K, gk, torch, dev, peak):
     return res
 
 
-def decode_layers(K, gk, torch, dev, gen, peak, fused, layers=4):
+def decode_layers(K, gk, torch, dev, gen, peak, fused, layers=4, ffn=False):
     """The headline workload with gate and up as two weights (fused=False: 3 products per layer) or as one weight
-    of 57344 rows (fused=True), graph replay."""
+    of 57344 rows (fused=True), graph replay.  ffn=True: the layers as real gated feed-forward blocks
+    (gllmk_ffn_decode: the down product reads silu(gate) * up, each layer's output feeds the next)."""
     qt = gk.QuantType.q4k()
     ws = []
     for _ in range(layers):
@@ -344,7 +346,14 @@ def decode_layers(K, gk, torch, dev, gen, peak, fused, layers=4):
     xs = {D_MODEL: torch.randn((1, D_MODEL), generator=gen, device=dev), N_FF: torch.randn((1, N_FF), generator=gen, device=dev)}
     ys = [torch.empty((1, w.n), dtype=torch.float32, device=dev) for w in ws]
 
+    hs = [torch.empty((1, 2 * N_FF), dtype=torch.float32, device=dev) for _ in range(layers)] if ffn else []
+
     def step():
+        if ffn:
+            x = xs[D_MODEL]
+            for layer in range(layers):
+                x = K.ffn_decode(ws[2 * layer], ws[2 * layer + 1], x, h=hs[layer], y=ys[2 * layer + 1])
+            return
         for w, y in zip(ws, ys):
             K.gemv(w, xs[w.k], y=y)
     for _ in range(3):

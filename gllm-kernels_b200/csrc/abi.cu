@@ -357,6 +357,26 @@ int32_t gllmk_gemv(gllmk_ctx ctx, gllmk_weight wh, const float *x_dev, int64_t x
                        static_cast<cudaStream_t>(stream));
 }
 
+int32_t gllmk_ffn_decode(gllmk_ctx ctx, gllmk_weight w_gate_up, gllmk_weight w_down, const float *x_dev, int32_t m, float *h_dev,
+                         float *y_dev, void *stream) {
+    if (!ctx || !w_gate_up || !w_down || !x_dev || !h_dev || !y_dev) return GLLMK_STATUS_INVALID_ARG;
+    Ctx *c = static_cast<Ctx *>(ctx);
+    const Weight *wg = static_cast<const Weight *>(w_gate_up), *wd = static_cast<const Weight *>(w_down);
+    if (m < 1 || m > GLLMK_GEMV_MAX_M) return fail(c, GLLMK_STATUS_INVALID_ARG, "ffn_decode: m=%d outside 1..%d", m, GLLMK_GEMV_MAX_M);
+    if (wg->n % 2 || wg->n / 2 != wd->k || wd->n != wg->k)
+        return fail(c, GLLMK_STATUS_INVALID_ARG, "ffn_decode: shapes do not chain: gate||up [%lld, %lld], down [%lld, %lld]",
+                    (long long)wg->n, (long long)wg->k, (long long)wd->n, (long long)wd->k);
+    if (wg->device != c->device || wd->device != c->device) return fail(c, GLLMK_STATUS_INVALID_ARG, "weight lives on another device");
+    DeviceGuard g(c->device);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int64_t f = wd->k;
+    // h = [gate | up] = W_gate_up x : [m, 2f]
+    int32_t rc = gemv_launch(c, wg, x_dev, wg->k, 1, m, h_dev, 2 * f, 1, nullptr, 0, s);
+    if (rc) return rc;
+    // y = W_down (silu(gate) * up): the activation staging of the second product applies SwiGLU while it reads h
+    return gemv_launch(c, wd, h_dev, 2 * f, 1, m, y_dev, wd->n, 1, nullptr, 0, s, nullptr, 0, h_dev + f);
+}
+
 int32_t gllmk_gemv_allgather(gllmk_ctx ctx, gllmk_weight wh, const float *x_dev, int64_t x_stride_t, int64_t x_stride_k, int32_t m,
                              float *y_local, int64_t y_stride_t, int64_t y_stride_r, void *const *y_peers, int32_t n_peers,
                              void *stream) {

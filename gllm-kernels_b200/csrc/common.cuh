@@ -119,7 +119,7 @@ int32_t dequant_raw(Ctx *c, int32_t qt, const uint8_t *blocks_dev, const uint8_t
 // ---- gemv.cu ----
 int32_t gemv_launch(Ctx *c, const Weight *w, const float *x, int64_t xst, int64_t xsk, int m, float *y, int64_t yst,
                     int64_t ysr, const float *row_scales, int64_t n_row_scales, cudaStream_t s, void *const *y_peers = nullptr,
-                    int n_peers = 0);
+                    int n_peers = 0, const float *x_up = nullptr);
 size_t gemv_ws_bytes(const Weight *w, int m);
 // ---- gemm.cu ----
 int32_t gemm_launch(Ctx *c, const Weight *w, const void *a, int a_bf16, int64_t lda, int m, void *y, int y_bf16, int64_t ldy,

@@ -34,6 +34,7 @@ __host__ __device__ inline uint32_t slice_bytes(int m) { return (uint32_t)(2 * m
 
 struct StageParams {
     const float *x;
+    const float *x_up;  // not null: the activation is silu(x[k]) * x_up[k] (SwiGLU of a gate || up product's halves)
     int64_t xst, xsk;
     int m;
     int64_t K;
@@ -55,6 +56,12 @@ __global__ void __launch_bounds__(256) stage_x_kernel(StageParams p) {
     if (k0 < p.K) {
 #pragma unroll
         for (int i = 0; i < 4; i++) v[i] = xr[(k0 + i) * p.xsk];
+        if (p.x_up) {
+            // swiglu (scalar-ops/src/activations.rs:57-66): out = g / (1 + exp(-g)) * u, in f32
+            const float *ur = p.x_up + (int64_t)tok * p.xst;
+#pragma unroll
+            for (int i = 0; i < 4; i++) v[i] = (v[i] / (1.0f + expf(-v[i]))) * ur[(k0 + i) * p.xsk];
+        }
     }
     float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
     const float inf = __int_as_float(0x7F800000);
@@ -678,7 +685,7 @@ static cudaError_t configure_and_launch(Ctx *c, GemvParams &p, int64_t ntg, cuda
 
 int32_t gemv_launch(Ctx *c, const Weight *w, const float *x, int64_t xst, int64_t xsk, int m, float *y, int64_t yst,
                     int64_t ysr, const float *row_scales, int64_t n_row_scales, cudaStream_t s, void *const *y_peers,
-                    int n_peers) {
+                    int n_peers, const float *x_up) {
     if (w->qt != GLLMK_QUANT_Q4K && w->qt != GLLMK_QUANT_Q8_0 && w->qt != GLLMK_QUANT_MXFP4 && w->qt != GLLMK_QUANT_NVFP4)
         return fail(c, GLLMK_STATUS_UNSUPPORTED, "gemv: quant type %d has no decode kernel", w->qt);
     int32_t rc = ensure_ws(c, gemv_ws_bytes(w, m));
@@ -702,7 +709,7 @@ int32_t gemv_launch(Ctx *c, const Weight *w, const float *x, int64_t xst, int64_
     p.m = m;
     p.status = c->status_dev;
 
-    StageParams sp{x, xst, xsk, m, w->k, static_cast<uint8_t *>(c->ws)};
+    StageParams sp{x, x_up, xst, xsk, m, w->k, static_cast<uint8_t *>(c->ws)};
     dim3 sgrid((unsigned)(((size_t)nk * 256 + 1023) / 1024), (unsigned)m);
     static bool stage_carveout_set = false;
     if (!stage_carveout_set) {
@@ -859,7 +866,7 @@ extern "C" int32_t gllmk_gemv_static(gllmk_ctx ctx, gllmk_weight wh, const float
             rc = fail(c, GLLMK_STATUS_INVALID_ARG, "gemv_static: k=%lld with m=%d needs a %zu-byte activation image, "
                       "more than the built-in %zu-byte area; use gllmk_gemv", (long long)w->k, m, img_bytes, GEMV_STATIC_BYTES);
         } else {
-            StageParams sp{x_dev, x_stride_t, x_stride_k, m, w->k, base + img_off};
+            StageParams sp{x_dev, nullptr, x_stride_t, x_stride_k, m, w->k, base + img_off};
             dim3 sgrid((unsigned)(((size_t)nk * 256 + 1023) / 1024), (unsigned)m);
             e = launch_pdl(stage_x_kernel, sgrid, 256, 0, s, false, sp);
             const int64_t ntg = w->n_pad / 128;

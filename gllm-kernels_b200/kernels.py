@@ -181,6 +181,18 @@ class GpuKernels:
         self._check(rc, "gllmk_gemm")
         return y
 
+    def ffn_decode(self, w_gate_up: Weight, w_down: Weight, x, h=None, y=None, stream=None):
+        """y = W_down (silu(gate) * up) with [gate | up] = W_gate_up x, for m <= 16 tokens (x [m, k] f32 CUDA)."""
+        import torch
+        m = x.shape[0]
+        if h is None:
+            h = torch.empty((m, w_gate_up.n), dtype=torch.float32, device=x.device)
+        if y is None:
+            y = torch.empty((m, w_down.n), dtype=torch.float32, device=x.device)
+        rc = lib().gllmk_ffn_decode(self._ctx, w_gate_up._h, w_down._h, _ptr(x), m, _ptr(h), _ptr(y), _stream(stream))
+        self._check(rc, "gllmk_ffn_decode")
+        return y
+
     def gemm_grouped(self, weights, a, row_offsets, y=None, out_dtype=None, stream=None):
         """Mixture-of-experts product in one launch: rows [row_offsets[g], row_offsets[g+1]) of `a` times weights[g]."""
         import torch

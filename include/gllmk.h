@@ -136,6 +136,17 @@ GLLMK_API int32_t gllmk_gemv(gllmk_ctx ctx, gllmk_weight w, const float *x_dev, 
                    int32_t m, float *y_dev, int64_t y_stride_t, int64_t y_stride_r, const float *row_scales,
                    int64_t n_row_scales, void *stream);
 
+/* One gated feed-forward block for m <= GLLMK_GEMV_MAX_M tokens: the step on either side of the decode
+ * products (Activation::is_gated, src/traits.rs:16-25; Kernels::swiglu, src/traits.rs:446;
+ * scalar_swiglu, scalar-ops/src/activations.rs:57-66):
+ *   h = W_gate_up x        h [m, 2f]: columns [0, f) = gate, [f, 2f) = up (gate and up stored as one weight)
+ *   y = W_down (silu(gate) * up),  silu(g) = g / (1 + exp(-g)) in f32
+ * Two decode products; SwiGLU is applied by the second product's activation staging while it reads h, so
+ * there is no separate activation kernel and no third buffer.  x [m, k] and y [m, k] row-major, h is
+ * caller-provided scratch of m * 2f floats (it holds gate || up afterwards). */
+GLLMK_API int32_t gllmk_ffn_decode(gllmk_ctx ctx, gllmk_weight w_gate_up, gllmk_weight w_down, const float *x_dev, int32_t m,
+                         float *h_dev, float *y_dev, void *stream);
+
 /* ---- multi-GPU: row-sharded decode with the all-gather fused into the GEMV -------------------------- */
 
 /* No counterpart in the reference (single device).  Weights are sharded by rows over the GPUs of one node

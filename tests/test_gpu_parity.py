@@ -338,3 +338,53 @@ def test_matmul_host_resident_weight(gk, K, oracle):
     assert oracle.rel_err(y2, ref.T) <= TOL
     assert K.gemv_q4(blocks[:4 * 144], x[0], 2.0, 1024) == pytest.approx(2.0 * ref[0, 0], rel=2e-3, abs=1e-6)
     w.free()
+
+
+# ---- gated feed-forward block: two decode products with SwiGLU fused into the second one's staging ------
+@pytest.mark.parametrize("fmt,d,f,m", [("q4k", 256, 512, 1), ("q4k", 512, 768, 5), ("q8_0", 128, 160, 16)])
+def test_ffn_decode_swiglu(gk, K, oracle, torch, fmt, d, f, m):
+    oid, b_gu, _, _ = make(oracle, fmt, 2 * f, d, 61)
+    _, b_dn, _, _ = make(oracle, fmt, d, f, 62)
+    qt = gk.QuantType.q4k() if fmt == "q4k" else gk.QuantType.q8_0()
+    w_gu, w_dn = K.upload(qt, 2 * f, d, b_gu), K.upload(qt, d, f, b_dn)
+    x = np.random.default_rng(63).standard_normal((m, d)).astype(np.float32)
+    xd = torch.from_numpy(x).cuda()
+    h = torch.empty((m, 2 * f), dtype=torch.float32, device="cuda")
+    y = K.ffn_decode(w_gu, w_dn, xd, h=h).cpu().numpy()
+    # oracle chain: the reference's matmul, scalar_swiglu (g / (1 + exp(-g)) * u in f32), the reference's matmul
+    h_ref = oracle.quant_matmul(b_gu, np.ascontiguousarray(x.T), oid, 2 * f, m, d).T
+    g, u = h_ref[:, :f], h_ref[:, f:]
+    act = ((g / (np.float32(1.0) + np.exp(-g, dtype=np.float32))) * u).astype(np.float32)
+    y_ref = oracle.quant_matmul(b_dn, np.ascontiguousarray(act.T), oid, d, m, f).T
+    assert oracle.rel_err(h.cpu().numpy(), h_ref) <= TOL
+    assert oracle.rel_err(y, y_ref) <= TOL
+    assert K.status() == 0
+    with pytest.raises(gk.GllmkError) as e:  # shapes that do not chain
+        K.ffn_decode(w_dn, w_dn, xd)
+    assert e.value.status == gk.Status.INVALID_ARG
+    w_gu.free()
+    w_dn.free()
+
+
+def test_swiglu_known_answers_through_ffn_decode(gk, K, oracle, torch):
+    """scalar-ops/src/activations.rs:157-167: swiglu(0, 1) = 0, swiglu(1, 2) = 2 * silu(1).  Identity-like Q8_0
+    weights (one 1.0 per row) pass x through the products unchanged, so y is the SwiGLU of x's two halves."""
+    f = 32
+    def unit_rows(rows, cols, picks):
+        W = np.zeros((rows, cols), np.float32)
+        for r, ccol in enumerate(picks):
+            W[r, ccol] = 1.0
+        return oracle.quantize_q8_0(W)
+    qt = gk.QuantType.q8_0()
+    w_gu = K.upload(qt, 2 * f, 2 * f, unit_rows(2 * f, 2 * f, range(2 * f)))  # h = x: gate = x[:f], up = x[f:]
+    # the block maps back to the model width (2f here): rows 0..f-1 of the down weight copy act, the rest repeat act[0]
+    w_dn = K.upload(qt, 2 * f, f, unit_rows(2 * f, f, list(range(f)) + [0] * f))
+    x = np.zeros((1, 2 * f), np.float32)
+    x[0, :4] = [0.0, 1.0, 2.0, -1.0]        # gate
+    x[0, f:f + 4] = [1.0, 2.0, 3.0, 4.0]    # up
+    y = K.ffn_decode(w_gu, w_dn, torch.from_numpy(x).cuda()).cpu().numpy()[0]
+    silu = lambda g: g / (1.0 + np.exp(-g))
+    want = [0.0, silu(1.0) * 2.0, silu(2.0) * 3.0, silu(-1.0) * 4.0]
+    assert np.allclose(y[:4], want, rtol=2e-3, atol=1e-6), (y[:4], want)
+    w_gu.free()
+    w_dn.free()
