@@ -260,6 +260,7 @@ def run_ours(args):
         out["extra"] = extra_configs(K, gk, torch, dev, peak)
     if keep_host:
         out["cpu_baseline"] = cpu_baseline(host_blocks, xh_model, xh_ff, M, threads=1)
+        out["parity"] = parity_record(K, weights[0][1], host_blocks[0], x_model, xh_model, M)
     if rank == 0:
         print(json.dumps(out), flush=True)
     if world > 1:
@@ -485,6 +486,21 @@ def cpu_baseline(host_blocks, xh_model, xh_ff, M, threads, reps=None):
     return {"value": wbytes / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
             "sample": f"{reps} passes over one layer (gate, up, down = {wbytes} weight bytes) of the same workload",
             "cpu_count": os.cpu_count()}
+
+
+def parity_record(K, w, host, x_dev, x_host, M, rows=2048):
+    """The first product of the step on its first `rows` weight rows: this implementation and the CPU port of the
+    reference, each against the other and against an f64-accumulated evaluation of the decoded weights."""
+    import numpy as np
+    from oracle import oracle as O
+    name, n, k, blocks = host
+    sub = np.ascontiguousarray(blocks.reshape(n, -1)[:rows]).reshape(-1)
+    y_gpu = K.gemv(w, x_dev).cpu().numpy()[:, :rows]
+    y_cpu = O.quant_matmul(sub, np.ascontiguousarray(x_host.T), O.Q4K, rows, M, k).T
+    y_f64 = x_host.astype(np.float64) @ O.dequant_matrix(O.Q4K, sub, rows, k).astype(np.float64).T
+    return {"metric": "max_i |y_i - ref_i| / max(|ref_i|, rms(ref))", "rows": rows, "matrix": name,
+            "gpu_vs_cpu_port": O.rel_err(y_gpu, y_cpu), "gpu_vs_f64": O.rel_err(y_gpu, y_f64),
+            "cpu_port_vs_f64": O.rel_err(y_cpu, y_f64), "bar": 2e-3}
 
 
 # ------------------------------------------------------------------------------------------------
