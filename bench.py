@@ -261,6 +261,7 @@ def run_ours(args):
     if keep_host:
         out["cpu_baseline"] = cpu_baseline(host_blocks, xh_model, xh_ff, M, threads=1)
         out["parity"] = parity_record(K, weights[0][1], host_blocks[0], x_model, xh_model, M)
+        out["cpu_bench_quant_path"] = bench_quant_cpu()
     if rank == 0:
         print(json.dumps(out), flush=True)
     if world > 1:
@@ -486,6 +487,27 @@ def cpu_baseline(host_blocks, xh_model, xh_ff, M, threads, reps=None):
     return {"value": wbytes / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
             "sample": f"{reps} passes over one layer (gate, up, down = {wbytes} weight bytes) of the same workload",
             "cpu_count": os.cpu_count()}
+
+
+def bench_quant_cpu():
+    """The reference's own micro-benchmark loop for a 4-bit GEMV (benches/bench_quant.rs, quant/gemv_q4 at
+    K = N = 4096: simplified nibble format, one scalar call per row), restated in C and built -O1 like the
+    reference's bench profile, one thread.  Reported beside config 1, which has the same shape."""
+    import numpy as np
+    from oracle import oracle as O
+    k = n = 4096
+    rng = np.random.default_rng(20241)
+    w = rng.integers(0, 256, size=n * k // 2, dtype=np.uint8)
+    x = rng.standard_normal(k, dtype=np.float32)
+    sc = rng.random(n, dtype=np.float32)
+    O.bench_gemv_q4_rows(w, x, sc, n, k)
+    reps, t0 = 0, time.perf_counter()
+    while time.perf_counter() - t0 < 2.0:
+        O.bench_gemv_q4_rows(w, x, sc, n, k)
+        reps += 1
+    dt = (time.perf_counter() - t0) / reps
+    return {"kernel": "scalar_gemv_q4 row loop, 1x4096x4096, -O1, 1 thread", "us": dt * 1e6, "gflops": 2.0 * n * k / dt / 1e9,
+            "weight_GBps": n * k / 2 / dt / 1e9, "reps": reps}
 
 
 def parity_record(K, w, host, x_dev, x_host, M, rows=2048):

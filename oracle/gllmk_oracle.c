@@ -461,6 +461,10 @@ API float gko_scalar_gemv_q4(const uint8_t *w, const float *x, float scale, size
     }
     return acc * scale;
 }
+/* The row loop benches/bench_quant.rs:84-96 times: one scalar_gemv_q4 call per output row. */
+API void gko_bench_gemv_q4_rows(const uint8_t *w, const float *x, const float *scales, float *out, size_t n, size_t k) {
+    for (size_t j = 0; j < n; j++) out[j] = gko_scalar_gemv_q4(w + j * (k / 2), x, scales[j], k);
+}
 API void gko_scalar_gemm_q8(const int8_t *w, const float *x, float *out, const float *scales, size_t m,
                             size_t n, size_t k) {
     for (size_t i = 0; i < m; i++)

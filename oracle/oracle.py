@@ -232,6 +232,18 @@ def quantize_nvfp4(x, global_scale: float | None = None):
     return out, g
 
 
+def bench_gemv_q4_rows(w, x, scales, n: int, k: int, o1: bool = True) -> np.ndarray:
+    """The loop benches/bench_quant.rs times for quant/gemv_q4 (simplified nibble-8 format, per-row scale),
+    by default from the -O1 build that mirrors the reference's bench profile."""
+    out = np.empty(n, np.float32)
+    L = lib(o1)
+    L.gko_bench_gemv_q4_rows.restype = None
+    L.gko_bench_gemv_q4_rows.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t]
+    w, x, scales = _u8(w), _f32(x), _f32(scales)
+    L.gko_bench_gemv_q4_rows(w.ctypes.data, x.ctypes.data, scales.ctypes.data, out.ctypes.data, n, k)
+    return out
+
+
 def rel_err(y, ref) -> float:
     """Parity metric: max_i |y_i - ref_i| / max(|ref_i|, rms(ref))."""
     y = np.asarray(y, np.float64).reshape(-1)
