@@ -447,6 +447,18 @@ def extra_gemm(K, gk, torch, dev, gen):
                                                      "us_one_call_per_expert": us_loop}
     for w in experts:
         w.free()
+    # W8A8: s8 weights x u8 activations -> s32 (exact), tcgen05 kind::i8, at config 2's matrix and a 70B-shaped one
+    for n, k, m in ((11008, 4096, 2048), (28672, 8192, 2048)):
+        b = torch.randint(-128, 128, (n, k), generator=gen, device=dev, dtype=torch.int8)
+        w = K.upload_int8(b, layout_kn=False)
+        del b
+        a8 = torch.randint(0, 256, (m, k), generator=gen, device=dev, dtype=torch.uint8)
+        c32 = torch.empty((m, n), dtype=torch.int32, device=dev)
+        us = timeit(lambda: K.gemm_int8(w, a8, c=c32), 10)
+        res[f"w8a8_int8_{n}x{k}_M{m}"] = {"us": us, "tops": 2.0 * m * n * k / us / 1e6, "frac_of_nominal_int8_4500": 2.0 * m * n * k / us / 1e6 / 4500.0,
+                                          "mma": "tcgen05 kind::i8, s32 accumulate (bit-exact)"}
+        w.free()
+        del a8, c32
     # config 4: NVFP4 weights x NVFP4 activations, bf16 out, native block-scaled MMA
     n, k, m = 14336, 4096, 2048
     w = upload(QT.nvfp4(), n, k)

@@ -305,6 +305,7 @@ int32_t gllmk_weight_unpack(gllmk_ctx ctx, gllmk_weight wh, void *blocks, void *
     if (!ctx || !wh || !blocks) return GLLMK_STATUS_INVALID_ARG;
     Ctx *c = static_cast<Ctx *>(ctx);
     const Weight *w = static_cast<const Weight *>(wh);
+    if (w->qt == GLLMK_QUANT_INT8) return fail(c, GLLMK_STATUS_UNSUPPORTED, "unpack: not a block-quantized weight");
     if (w->qt == GLLMK_QUANT_MXFP4 && !scales)
         return fail(c, GLLMK_STATUS_INVALID_ARG, "MXFP4 unpack writes the split form and needs a scales buffer");
     DeviceGuard g(c->device);
@@ -338,6 +339,8 @@ int32_t gllmk_dequant(gllmk_ctx ctx, gllmk_weight wh, float *out_dev, void *stre
     if (!ctx || !wh || !out_dev) return GLLMK_STATUS_INVALID_ARG;
     Ctx *c = static_cast<Ctx *>(ctx);
     if (((uintptr_t)out_dev & 15) != 0) return fail(c, GLLMK_STATUS_INVALID_ARG, "out_dev must be 16-byte aligned");
+    if (static_cast<const Weight *>(wh)->qt == GLLMK_QUANT_INT8)
+        return fail(c, GLLMK_STATUS_UNSUPPORTED, "dequant: not a block-quantized weight");
     DeviceGuard g(c->device);
     return dequant_matrix(c, static_cast<const Weight *>(wh), out_dev, static_cast<cudaStream_t>(stream));
 }
@@ -446,6 +449,114 @@ int32_t gllmk_gemm_grouped(gllmk_ctx ctx, int32_t n_groups, const gllmk_weight *
     DeviceGuard g(c->device);
     return gemm_grouped_launch(c, ws.data(), n_groups, a_dev, a_dtype == GLLMK_DTYPE_BF16, lda, row_offsets, y_dev,
                                y_dtype == GLLMK_DTYPE_BF16, ldy, static_cast<cudaStream_t>(stream));
+}
+
+// ---- W8A8 integer path ----
+static int32_t int8_weight_create(Ctx *c, int64_t n, int64_t k, const int8_t *b, int layout, bool on_device, Weight **out) {
+    if (n <= 0 || k <= 0 || n > (int64_t)1 << 30 || k > (int64_t)1 << 30) return fail(c, GLLMK_STATUS_INVALID_ARG, "int8 weight: bad shape");
+    if (layout != 0 && layout != 1) return fail(c, GLLMK_STATUS_INVALID_ARG, "int8 weight: layout must be 0 ([k, n]) or 1 ([n, k])");
+    Weight *w = new (std::nothrow) Weight();
+    if (!w) return fail(c, GLLMK_STATUS_OUT_OF_MEMORY, "host allocation failed");
+    w->qt = GLLMK_QUANT_INT8;
+    w->n = n;
+    w->k = k;
+    w->n_pad = (n + 127) / 128 * 128;
+    w->k_pad = (k + 127) / 128 * 128;
+    w->device = c->device;
+    w->ref_bytes = (uint64_t)n * (uint64_t)k;
+    w->qs_bytes = (size_t)w->n_pad * (size_t)w->k_pad;
+    cudaError_t e = cudaMalloc(&w->qs, w->qs_bytes);
+    if (e != cudaSuccess) {
+        delete w;
+        return cuda_fail(c, e, "cudaMalloc(int8 weight)");
+    }
+    const int8_t *bdev = b;
+    void *stage = nullptr;
+    if (!on_device) {
+        e = cudaMalloc(&stage, (size_t)n * (size_t)k);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(stage, b, (size_t)n * (size_t)k, cudaMemcpyHostToDevice, c->stream);
+        if (e != cudaSuccess) {
+            if (stage) cudaFree(stage);
+            weight_destroy(w);
+            return cuda_fail(c, e, "upload(int8 weight)");
+        }
+        bdev = static_cast<const int8_t *>(stage);
+    }
+    int32_t rc = i8_weight_fill(c, w, bdev, layout, c->stream);
+    e = cudaStreamSynchronize(c->stream);
+    if (stage) cudaFree(stage);
+    if (!rc && e != cudaSuccess) rc = cuda_fail(c, e, "repack(int8 weight)");
+    if (rc) {
+        weight_destroy(w);
+        return rc;
+    }
+    *out = w;
+    return GLLMK_STATUS_OK;
+}
+
+int32_t gllmk_int8_weight_upload(gllmk_ctx ctx, int64_t n, int64_t k, const int8_t *b, int32_t layout, int32_t src_on_device,
+                                 gllmk_weight *out) {
+    if (!ctx || !b || !out) return GLLMK_STATUS_INVALID_ARG;
+    *out = nullptr;
+    Ctx *c = static_cast<Ctx *>(ctx);
+    DeviceGuard g(c->device);
+    Weight *w = nullptr;
+    const int32_t rc = int8_weight_create(c, n, k, b, layout, src_on_device != 0, &w);
+    if (!rc) *out = w;
+    return rc;
+}
+
+int32_t gllmk_gemm_int8(gllmk_ctx ctx, gllmk_weight wh, const uint8_t *a_dev, int64_t lda, int32_t m, int32_t *c_dev, int64_t ldc,
+                        void *stream) {
+    if (!ctx || !wh || !a_dev || !c_dev) return GLLMK_STATUS_INVALID_ARG;
+    Ctx *c = static_cast<Ctx *>(ctx);
+    const Weight *w = static_cast<const Weight *>(wh);
+    if (w->qt != GLLMK_QUANT_INT8) return fail(c, GLLMK_STATUS_INVALID_ARG, "gemm_int8: the weight was not uploaded with gllmk_int8_weight_upload");
+    if (m < 1) return fail(c, GLLMK_STATUS_INVALID_ARG, "gemm_int8: m must be positive");
+    if (lda < w->k || ldc < w->n) return fail(c, GLLMK_STATUS_INVALID_ARG, "gemm_int8: leading dimension smaller than the row");
+    if (w->device != c->device) return fail(c, GLLMK_STATUS_INVALID_ARG, "weight lives on another device");
+    DeviceGuard g(c->device);
+    return gemm_i8_launch(c, w, a_dev, lda, m, c_dev, ldc, static_cast<cudaStream_t>(stream));
+}
+
+int32_t gllmk_dequantize_i32_f32(gllmk_ctx ctx, const int32_t *c_dev, float *out_dev, int64_t m, int64_t n, float scale_a, float scale_b,
+                                 const float *bias_dev, int32_t activation, void *stream) {
+    if (!ctx || !c_dev || !out_dev) return GLLMK_STATUS_INVALID_ARG;
+    Ctx *c = static_cast<Ctx *>(ctx);
+    if (m < 0 || n < 0) return fail(c, GLLMK_STATUS_INVALID_ARG, "dequantize: negative shape");
+    if (activation < 0 || activation > 4) return fail(c, GLLMK_STATUS_UNSUPPORTED, "dequantize: activation %d", activation);
+    DeviceGuard g(c->device);
+    return dequant_i32_launch(c, c_dev, out_dev, m, n, n, n, scale_a, scale_b, bias_dev, activation, static_cast<cudaStream_t>(stream));
+}
+
+int32_t gllmk_gemm_int8_host(gllmk_ctx ctx, const uint8_t *a, const int8_t *b_kn, int32_t *c_out, size_t m, size_t n, size_t k) {
+    if (!ctx || !a || !b_kn || !c_out) return GLLMK_STATUS_INVALID_ARG;
+    Ctx *c = static_cast<Ctx *>(ctx);
+    if (m == 0 || n == 0) return GLLMK_STATUS_OK;
+    if (k == 0) {
+        memset(c_out, 0, m * n * sizeof(int32_t));
+        return GLLMK_STATUS_OK;
+    }
+    if (m > 0x7fffffffu) return fail(c, GLLMK_STATUS_INVALID_ARG, "gemm_int8: m too large");
+    DeviceGuard g(c->device);
+    Weight *w = nullptr;
+    int32_t rc = int8_weight_create(c, (int64_t)n, (int64_t)k, b_kn, 0, false, &w);
+    if (rc) return rc;
+    const size_t ab = m * k, cb = m * n * sizeof(int32_t), co = (ab + 255) & ~(size_t)255;
+    rc = ensure_dev_io(c, co + cb);
+    if (!rc) {
+        char *dev = static_cast<char *>(c->dev_io);
+        cudaError_t e = cudaMemcpyAsync(dev, a, ab, cudaMemcpyHostToDevice, c->stream);
+        if (e == cudaSuccess) {
+            rc = gemm_i8_launch(c, w, reinterpret_cast<const uint8_t *>(dev), (int64_t)k, (int)m, reinterpret_cast<int32_t *>(dev + co),
+                                (int64_t)n, c->stream);
+            if (!rc) e = cudaMemcpyAsync(c_out, dev + co, cb, cudaMemcpyDeviceToHost, c->stream);
+        }
+        if (!rc && e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+        if (!rc && e != cudaSuccess) rc = cuda_fail(c, e, "gemm_int8_host");
+    }
+    weight_destroy(w);
+    return rc;
 }
 
 int32_t gllmk_gemm_fp4(gllmk_ctx ctx, gllmk_weight wh, gllmk_weight xh, void *y_dev, int32_t y_dtype, int64_t ldy, void *stream) {

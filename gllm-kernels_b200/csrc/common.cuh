@@ -128,6 +128,11 @@ int32_t gemm_grouped_launch(Ctx *c, const Weight *const *ws, int n_groups, const
                             const int64_t *row_offsets, void *y, int y_bf16, int64_t ldy, cudaStream_t s);
 // ---- gemm_fp4.cu ----
 int32_t gemm_fp4_launch(Ctx *c, const Weight *w, const Weight *x, void *y, int y_bf16, int64_t ldy, cudaStream_t s);
+// ---- gemm_i8.cu ----
+int32_t i8_weight_fill(Ctx *c, Weight *w, const int8_t *b_dev, int layout, cudaStream_t s);
+int32_t gemm_i8_launch(Ctx *c, const Weight *w, const uint8_t *a, int64_t lda, int m, int32_t *out, int64_t ldc, cudaStream_t s);
+int32_t dequant_i32_launch(Ctx *c, const int32_t *ci, float *out, int64_t m, int64_t n, int64_t ldc, int64_t ldo, float scale_a,
+                           float scale_b, const float *bias, int act, cudaStream_t s);
 // ---- quantize.cu ----
 int32_t quantize_launch(Ctx *c, int32_t qt, const float *x, int64_t rows, int64_t k, int mx_block, void *blocks,
                         void *scales, float *global_scale, cudaStream_t s);

@@ -583,6 +583,8 @@ static int32_t gemm_groups_chunk(Ctx *c, const Weight *const *ws, int ng, const 
 int32_t gemm_grouped_launch(Ctx *c, const Weight *const *ws, int n_groups, const void *a, int a_bf16, int64_t lda,
                             const int64_t *row_offsets, void *y, int y_bf16, int64_t ldy, cudaStream_t s) {
     const int align = a_bf16 ? 8 : 4;
+    if (ws[0]->qt < GLLMK_QUANT_Q4K || ws[0]->qt > GLLMK_QUANT_NVFP4)
+        return fail(c, GLLMK_STATUS_UNSUPPORTED, "gemm: weight type %d is not block-quantized (use gllmk_gemm_int8)", ws[0]->qt);
     if (((uintptr_t)a & 15) || (lda % align)) return fail(c, GLLMK_STATUS_INVALID_ARG, "gemm: activations must be 16-byte aligned rows");
     if (ws[0]->k % 8) return fail(c, GLLMK_STATUS_INVALID_ARG, "gemm: k=%lld is not a multiple of 8", (long long)ws[0]->k);
     // MMA N: 256-token tiles, or the largest group rounded up to a multiple of 32 when no group has more

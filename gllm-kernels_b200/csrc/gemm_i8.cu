@@ -1,0 +1,243 @@
+// W8A8 integer GEMM: C (s32) = A (u8 activations) x W (s8 weights), exact, on tcgen05 (kind::i8) with the
+// accumulator in tensor memory; plus the dequantize epilogue of the reference as a separate element-wise pass.
+//
+//   C[t, r] = sum_k A[t, k] * W[r, k]          t < M tokens, r < N weight rows        (all integers, no rounding)
+//
+// Counterpart: avx512_int8::gemm_int8 / dequantize_i32_to_f32 (src/macros/matmul_x86_int8.rs:307-440), whose B
+// operand is [K, N] row-major s8 (and a packed copy of it).  Here the weight is repacked once into 16 KB tile
+// images (128 rows x 128 k, 128-byte swizzle, order [row tile][k-step]) and the u8 activations are turned into
+// the same kind of images per call, so every operand stage is a plain bulk copy; one thread issues four
+// tcgen05.mma of K = 32 per stage into a 128 x N s32 accumulator; eight warps store it (transposed through
+// shared memory, 16 bytes per lane).  Weights on the M side as in the other prefill kernels.
+#include "common.cuh"
+#include "tc05.cuh"
+
+namespace gllmk {
+
+constexpr int I8_BM = 128, I8_BN = 256, I8_TILE = 16384, I8_STAGES = 4;
+constexpr int I8_STAGE_BYTES = I8_TILE + 2 * I8_TILE;  // weight tile + up to two activation tiles
+constexpr int I8_EPI_WARPS = 8;
+constexpr int I8_THREADS = 64 + 32 * I8_EPI_WARPS;     // warp 0: copies, warp 1: MMA + TMEM, then the epilogue warps
+constexpr size_t I8_SMEM = (size_t)I8_STAGES * I8_STAGE_BYTES + 1024;
+
+struct I8Params {
+    const uint8_t *w;   // weight tile images
+    const uint8_t *xt;  // activation tile images [token tile of 128][k-step][16384]
+    int64_t n;
+    int nks;            // k-steps of 128
+    int m;
+    int32_t *c;         // [m, n] row-major, leading dimension ldc
+    int64_t ldc;
+    int vec;
+    int *status;
+};
+
+__device__ __forceinline__ void i8_bulk(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst), "l"(src),
+                 "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+// ---- repack: s8 weights [K, N] (layout 0, the reference's B) or [N, K] (layout 1) -> tile images; thread = 16 k of a row
+__global__ void __launch_bounds__(256) repack_i8_kernel(const int8_t *__restrict__ b, uint8_t *__restrict__ out, int64_t n, int64_t k,
+                                                        int64_t k_pad, int layout, size_t total) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // (k chunk, padded row): rows fastest for layout 0
+    if (idx >= total) return;
+    const int64_t n_pad = (n + 127) / 128 * 128;
+    const int64_t row = (int64_t)(idx % (size_t)n_pad), kc = (int64_t)(idx / (size_t)n_pad);
+    uint32_t v[4] = {0, 0, 0, 0};
+    if (row < n) {
+        for (int i = 0; i < 16; i++) {
+            const int64_t kk = kc * 16 + i;
+            if (kk < k) {
+                const uint8_t by = (uint8_t)(layout == 0 ? b[kk * n + row] : b[row * k + kk]);
+                v[i >> 2] |= (uint32_t)by << (8 * (i & 3));
+            }
+        }
+    }
+    const size_t tile = (size_t)(row >> 7) * (size_t)(k_pad >> 7) + (size_t)(kc >> 3);
+    *reinterpret_cast<uint4 *>(out + tile * I8_TILE + tc::sw128_offset((int)(row & 127), (int)(kc & 7))) = make_uint4(v[0], v[1], v[2], v[3]);
+}
+
+// ---- u8 activations [m, k] (leading dimension lda, any alignment) -> tile images; grid (k-steps, token tiles of 128)
+__global__ void __launch_bounds__(256) stage_act_u8_kernel(const uint8_t *__restrict__ a, int64_t lda, int m, int64_t k,
+                                                           uint8_t *__restrict__ xt) {
+    const int ks = blockIdx.x, tile = blockIdx.y;
+    uint8_t *dst = xt + ((size_t)tile * gridDim.x + ks) * I8_TILE;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int item = threadIdx.x + 256 * i, row = item >> 3, chunk = item & 7;
+        const int64_t tok = (int64_t)tile * 128 + row, k0 = (int64_t)ks * 128 + chunk * 16;
+        uint32_t v[4] = {0, 0, 0, 0};
+        if (tok < m) {
+            const uint8_t *src = a + tok * lda + k0;
+            for (int j = 0; j < 16; j++)
+                if (k0 + j < k) v[j >> 2] |= (uint32_t)src[j] << (8 * (j & 3));
+        }
+        *reinterpret_cast<uint4 *>(dst + tc::sw128_offset(row, chunk)) = make_uint4(v[0], v[1], v[2], v[3]);
+    }
+}
+
+// grid (weight-row tiles, token tiles of 256); ntok = MMA N (multiple of 32, <= 256)
+__global__ void __launch_bounds__(I8_THREADS, 1) gemm_i8_kernel(const __grid_constant__ I8Params p, const int ntok) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bars[2 * I8_STAGES + 1];
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int abort_s;
+    const uint32_t smem_s = (tc::smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t full = tc::smem_u32(&bars[0]), empty = tc::smem_u32(&bars[I8_STAGES]), accum = tc::smem_u32(&bars[2 * I8_STAGES]);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t row0 = (int64_t)blockIdx.x * I8_BM, tok0 = (int64_t)blockIdx.y * I8_BN;
+    volatile int *abort_flag = &abort_s;
+
+    if (threadIdx.x == 0) {
+        abort_s = 0;
+        for (int s = 0; s < I8_STAGES; s++) {
+            tc::mbar_init(full + 8 * s, 1);
+            tc::mbar_init(empty + 8 * s, 1);
+        }
+        tc::mbar_init(accum, 1);
+        tc::mbar_init_fence();
+    }
+    if (warp == 1) tc::tmem_alloc(tc::smem_u32(&tmem_base_s), 256);
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem = tmem_base_s;
+
+    if (warp == 0 && lane == 0) {
+        // ---------------- copies: one weight tile and one or two activation tiles per k-step ----------------
+        const int halves = (ntok + 127) / 128;
+        const uint32_t bbytes = (uint32_t)ntok * 128u;
+        const uint32_t hb[2] = {ntok > 128 ? (uint32_t)I8_TILE : bbytes, bbytes - (uint32_t)I8_TILE};
+        for (int ks = 0; ks < p.nks; ks++) {
+            const int s = ks % I8_STAGES;
+            if (ks >= I8_STAGES && !tc::mbar_wait(empty + 8 * s, (uint32_t)((ks / I8_STAGES - 1) & 1), abort_flag)) {
+                abort_s = 1;
+                atomicExch(p.status, 41);
+                break;
+            }
+            const uint32_t st = smem_s + s * I8_STAGE_BYTES;
+            tc::mbar_expect_tx(full + 8 * s, (uint32_t)I8_TILE + bbytes);
+            i8_bulk(st, p.w + ((size_t)blockIdx.x * p.nks + ks) * I8_TILE, I8_TILE, full + 8 * s);
+            for (int h = 0; h < halves; h++)
+                i8_bulk(st + I8_TILE + h * I8_TILE, p.xt + ((size_t)((tok0 >> 7) + h) * p.nks + ks) * I8_TILE, hb[h], full + 8 * s);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---------------- MMA issue: weights signed (operand A), activations unsigned (operand B) ----------------
+        const uint32_t idesc = tc::idesc_i8(I8_BM, ntok, 1, 0);
+        bool ok = true;
+        for (int ks = 0; ks < p.nks; ks++) {
+            const int s = ks % I8_STAGES;
+            if (!tc::mbar_wait(full + 8 * s, (uint32_t)((ks / I8_STAGES) & 1), abort_flag)) {
+                abort_s = 1;
+                atomicExch(p.status, 42);
+                ok = false;
+                break;
+            }
+            tc::fence_after_sync();
+            const uint32_t st = smem_s + s * I8_STAGE_BYTES;
+            const uint64_t ad = tc::smem_desc_sw128(st), bd = tc::smem_desc_sw128(st + I8_TILE);
+#pragma unroll
+            for (int j = 0; j < 4; j++) tc::mma_i8(tmem, ad + 2 * j, bd + 2 * j, idesc, (uint32_t)((ks | j) != 0));
+            tc::mma_commit(empty + 8 * s);
+        }
+        if (ok) tc::mma_commit(accum);
+    }
+    __syncwarp();
+
+    if (warp >= 2) {
+        // ---------------- epilogue: warp w reads TMEM lane quadrant w % 4 = weight rows ----------------
+        const int quad = warp & 3;
+        bool ok = !abort_s && tc::mbar_wait(accum, 0u, abort_flag);
+        if (!ok && !abort_s) {
+            abort_s = 1;
+            atomicExch(p.status, 43);
+        }
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
+            tc::fence_after_sync();
+            // all MMAs have completed, so the stages are free: each warp stages its blocks in 4 KB of stage 0
+            uint8_t *stage = smem_raw + (smem_s - tc::smem_u32(smem_raw)) + (warp - 2) * 4096;
+            for (int c = 32 * ((warp - 2) >> 2); c < ntok; c += 32 * (I8_EPI_WARPS / 4)) {
+                uint32_t v[32];
+                tc::tmem_ld32(tmem + ((uint32_t)(32 * quad) << 16) + (uint32_t)c, v);
+                tc::tmem_ld_wait();
+                float o[32];  // the s32 bit patterns travel through the 32-bit store helper unchanged
+#pragma unroll
+                for (int j = 0; j < 32; j++) o[j] = __uint_as_float(v[j]);
+                tc::store_block_32x32<false>(p.c, p.ldc, row0 + 32 * quad, tok0 + c, p.n, p.m, o, stage, lane, p.vec);
+            }
+        }
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tc::tmem_dealloc(tmem, 256);
+}
+
+// dequantize_i32_to_f32 (src/macros/matmul_x86_int8.rs:414-456, scalar tail semantics): (c as f32) * scale_a * scale_b
+// (+ bias[j]), then the activation of src/macros/gemm_epilogue.rs:131-152
+__global__ void __launch_bounds__(256) dequant_i32_kernel(const int32_t *__restrict__ c, float *__restrict__ out, int64_t n, int64_t ldc,
+                                                          int64_t ldo, float scale_a, float scale_b, const float *__restrict__ bias,
+                                                          int act, size_t total) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int64_t i = (int64_t)(idx / (size_t)n), j = (int64_t)(idx % (size_t)n);
+    float v = __fmul_rn(__fmul_rn((float)c[i * ldc + j], scale_a), scale_b);
+    if (bias) v = __fadd_rn(v, bias[j]);
+    if (act == 1) v = v < 0.0f ? 0.0f : v;
+    else if (act == 2) v = v / (1.0f + expf(-v));
+    else if (act == 3 || act == 4) {
+        const float inner = 0.7978845608f * (v + 0.044715f * v * v * v);
+        v = 0.5f * v * (1.0f + tanhf(inner));
+    }
+    out[i * ldo + j] = v;
+}
+
+// ---------------------------------------------------------------------------------------------
+int32_t i8_weight_fill(Ctx *c, Weight *w, const int8_t *b_dev, int layout, cudaStream_t s) {
+    const size_t total = (size_t)w->n_pad * (size_t)(w->k_pad / 16);
+    repack_i8_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(b_dev, static_cast<uint8_t *>(w->qs), w->n, w->k, w->k_pad, layout, total);
+    GK_CUDA(c, cudaGetLastError());
+    return GLLMK_STATUS_OK;
+}
+
+int32_t gemm_i8_launch(Ctx *c, const Weight *w, const uint8_t *a, int64_t lda, int m, int32_t *out, int64_t ldc, cudaStream_t s) {
+    static bool attr_set[64] = {};  // function attributes are per device
+    const int dev_slot = c->device & 63;
+    if (!attr_set[dev_slot]) {
+        GK_CUDA(c, cudaFuncSetAttribute(gemm_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)I8_SMEM));
+        attr_set[dev_slot] = true;
+    }
+    const int ntok = m > 128 ? I8_BN : (m + 31) / 32 * 32;
+    const int mtiles = (m + I8_BN - 1) / I8_BN;
+    const int atiles = ntok > 128 ? 2 * mtiles : 1;
+    I8Params p{};
+    p.w = static_cast<const uint8_t *>(w->qs);
+    p.n = w->n;
+    p.nks = (int)(w->k_pad / 128);
+    p.m = m;
+    p.c = out;
+    p.ldc = ldc;
+    p.vec = (((uintptr_t)out & 15) == 0 && (ldc * 4) % 16 == 0) ? 1 : 0;
+    p.status = c->status_dev;
+    int32_t rc = ensure_act(c, (size_t)atiles * p.nks * I8_TILE);
+    if (rc) return rc;
+    p.xt = static_cast<const uint8_t *>(c->act);
+    stage_act_u8_kernel<<<dim3((unsigned)p.nks, (unsigned)atiles), 256, 0, s>>>(a, lda, m, w->k, static_cast<uint8_t *>(c->act));
+    GK_CUDA(c, cudaGetLastError());
+    gemm_i8_kernel<<<dim3((unsigned)(w->n_pad / I8_BM), (unsigned)mtiles), I8_THREADS, I8_SMEM, s>>>(p, ntok);
+    GK_CUDA(c, cudaGetLastError());
+    return GLLMK_STATUS_OK;
+}
+
+int32_t dequant_i32_launch(Ctx *c, const int32_t *ci, float *out, int64_t m, int64_t n, int64_t ldc, int64_t ldo, float scale_a,
+                           float scale_b, const float *bias, int act, cudaStream_t s) {
+    const size_t total = (size_t)m * (size_t)n;
+    if (total == 0) return GLLMK_STATUS_OK;
+    dequant_i32_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(ci, out, n, ldc, ldo, scale_a, scale_b, bias, act, total);
+    GK_CUDA(c, cudaGetLastError());
+    return GLLMK_STATUS_OK;
+}
+
+}  // namespace gllmk

@@ -92,6 +92,10 @@ __device__ __forceinline__ uint32_t sw128_offset(int row, int chunk) { return (u
 __host__ __device__ constexpr uint32_t idesc_f16(int M, int N, int a_fmt, int b_fmt) {
     return (1u << 4) | ((uint32_t)a_fmt << 7) | ((uint32_t)b_fmt << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
+// kind::i8: 8-bit integer operands (format 0 = unsigned, 1 = signed) -> s32 (accumulator format 2), both K-major.
+__host__ __device__ constexpr uint32_t idesc_i8(int M, int N, int a_signed, int b_signed) {
+    return (2u << 4) | ((uint32_t)a_signed << 7) | ((uint32_t)b_signed << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
 // Block-scaled kinds (mxf4 / mxf4nvf4): E2M1 operands (format 1), scale format bit 23 (0 = UE4M3, 1 = UE8M0),
 // scale-factor ids at [4,6) (B) and [29,31) (A).
 __host__ __device__ constexpr uint32_t idesc_fp4(int M, int N, int scale_e8m0, int a_sf_id, int b_sf_id) {
@@ -104,6 +108,13 @@ __device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t adesc, uint64_
     asm volatile(
         "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void mma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
         "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }

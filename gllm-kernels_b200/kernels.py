@@ -181,6 +181,49 @@ class GpuKernels:
         self._check(rc, "gllmk_gemm")
         return y
 
+    # ---- W8A8 integer path (avx512_int8::gemm_int8 / dequantize_i32_to_f32, src/macros/matmul_x86_int8.rs) ----
+    def upload_int8(self, b, layout_kn: bool = True) -> Weight:
+        """s8 weight matrix -> resident tiles.  layout_kn=True: b is [k, n] row-major as in the reference's B;
+        False: [n, k] row-major.  numpy (host) or CUDA torch int8 tensor."""
+        on_dev = not isinstance(b, np.ndarray)
+        if not on_dev:
+            b = _np(b, np.int8)
+        k, n = (b.shape[0], b.shape[1]) if layout_kn else (b.shape[1], b.shape[0])
+        h = C.c_void_p()
+        rc = lib().gllmk_int8_weight_upload(self._ctx, n, k, _ptr(b), 0 if layout_kn else 1, int(on_dev), C.byref(h))
+        self._check(rc, "gllmk_int8_weight_upload")
+        return Weight(self, h.value, None, n, k)
+
+    def gemm_int8(self, w: Weight, a, c=None, stream=None):
+        """C (int32) [m, n] = a (uint8 CUDA tensor [m, k]) x W, exact."""
+        import torch
+        m = a.shape[0]
+        if c is None:
+            c = torch.empty((m, w.n), dtype=torch.int32, device=a.device)
+        rc = lib().gllmk_gemm_int8(self._ctx, w._h, _ptr(a), a.stride(0), m, _ptr(c), c.stride(0), _stream(stream))
+        self._check(rc, "gllmk_gemm_int8")
+        return c
+
+    def dequantize_i32(self, c, scale_a: float, scale_b: float, bias=None, activation: int = 0, out=None, stream=None):
+        """(c as f32) * scale_a * scale_b (+ bias[j]) then the activation (0 none, 1 relu, 2 silu, 3 gelu, 4 geglu)."""
+        import torch
+        m, n = c.shape
+        if out is None:
+            out = torch.empty((m, n), dtype=torch.float32, device=c.device)
+        rc = lib().gllmk_dequantize_i32_f32(self._ctx, _ptr(c), _ptr(out), m, n, float(scale_a), float(scale_b), _ptr(bias),
+                                            int(activation), _stream(stream))
+        self._check(rc, "gllmk_dequantize_i32_f32")
+        return out
+
+    def gemm_int8_host(self, a, b_kn) -> np.ndarray:
+        """The reference call with host arrays: a uint8 [m, k], b int8 [k, n] -> int32 [m, n]."""
+        a, b = _np(a, np.uint8), _np(b_kn, np.int8)
+        m, k = a.shape
+        n = b.shape[1]
+        c = np.empty((m, n), np.int32)
+        self._check(lib().gllmk_gemm_int8_host(self._ctx, _ptr(a), _ptr(b), _ptr(c), m, n, k), "gllmk_gemm_int8_host")
+        return c
+
     def ffn_decode(self, w_gate_up: Weight, w_down: Weight, x, h=None, y=None, stream=None):
         """y = W_down (silu(gate) * up) with [gate | up] = W_gate_up x, for m <= 16 tokens (x [m, k] f32 CUDA)."""
         import torch

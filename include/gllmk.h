@@ -49,7 +49,8 @@ enum {
     GLLMK_QUANT_Q4K = 1,   /* QuantType::Q4K    256 el / 144 B  (src/quant.rs:122-127) */
     GLLMK_QUANT_Q8_0 = 2,  /* QuantType::Q8_0    32 el /  34 B  (src/quant.rs:290-293) */
     GLLMK_QUANT_MXFP4 = 3, /* QuantType::Mxfp4{block_size}      (src/quant.rs:66-76)   */
-    GLLMK_QUANT_NVFP4 = 4  /* QuantType::Nvfp4   64 el /  36 B  (src/quant.rs:366-371) */
+    GLLMK_QUANT_NVFP4 = 4, /* QuantType::Nvfp4   64 el /  36 B  (src/quant.rs:366-371) */
+    GLLMK_QUANT_INT8 = 5   /* plain s8 matrix of the W8A8 path (gllmk_int8_weight_upload); not a block format */
 };
 
 /* Element type of an activation / output matrix handed to gllmk_gemm. */
@@ -146,6 +147,27 @@ GLLMK_API int32_t gllmk_gemv(gllmk_ctx ctx, gllmk_weight w, const float *x_dev, 
  * caller-provided scratch of m * 2f floats (it holds gate || up afterwards). */
 GLLMK_API int32_t gllmk_ffn_decode(gllmk_ctx ctx, gllmk_weight w_gate_up, gllmk_weight w_down, const float *x_dev, int32_t m,
                          float *h_dev, float *y_dev, void *stream);
+
+/* ---- W8A8 integer path ------------------------------------------------------------------------------ */
+
+/* avx512_int8::gemm_int8 and dequantize_i32_to_f32 (src/macros/matmul_x86_int8.rs:307-456; tests
+ * src/tests_int8.rs:21-136):  C (s32) [m, n] = A (u8) [m, k] x B (s8) [k, n], exact integers, then
+ * out = (C as f32) * scale_a * scale_b (+ bias[j]) followed by an activation.
+ * gllmk_int8_weight_upload: B once -> resident tile images.  layout 0: B is [k, n] row-major as in the
+ *   reference; layout 1: [n, k] row-major (one weight row after the other).  Freed with gllmk_weight_free.
+ * gllmk_gemm_int8: device A (leading dimension lda, any alignment) and device C (ldc); tcgen05 kind::i8 with
+ *   an s32 accumulator in tensor memory: bit-exact for every shape (|sum| stays below 2^31 for k < 66000).
+ * gllmk_dequantize_i32_f32: element-wise epilogue on device buffers (contiguous [m, n]); bias_dev may be NULL;
+ *   activation: GLLMK_ACT_* (the reference's Activation, src/traits.rs:7-15).
+ * gllmk_gemm_int8_host: the reference call with host slices (its packed copy of B is not needed). */
+enum { GLLMK_ACT_NONE = 0, GLLMK_ACT_RELU = 1, GLLMK_ACT_SILU = 2, GLLMK_ACT_GELU = 3, GLLMK_ACT_GEGLU = 4 };
+GLLMK_API int32_t gllmk_int8_weight_upload(gllmk_ctx ctx, int64_t n, int64_t k, const int8_t *b, int32_t layout, int32_t src_on_device,
+                                 gllmk_weight *out);
+GLLMK_API int32_t gllmk_gemm_int8(gllmk_ctx ctx, gllmk_weight w, const uint8_t *a_dev, int64_t lda, int32_t m, int32_t *c_dev,
+                        int64_t ldc, void *stream);
+GLLMK_API int32_t gllmk_dequantize_i32_f32(gllmk_ctx ctx, const int32_t *c_dev, float *out_dev, int64_t m, int64_t n, float scale_a,
+                                 float scale_b, const float *bias_dev, int32_t activation, void *stream);
+GLLMK_API int32_t gllmk_gemm_int8_host(gllmk_ctx ctx, const uint8_t *a, const int8_t *b_kn, int32_t *c, size_t m, size_t n, size_t k);
 
 /* ---- multi-GPU: row-sharded decode with the all-gather fused into the GEMV -------------------------- */
 

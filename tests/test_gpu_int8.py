@@ -1,0 +1,94 @@
+"""W8A8 integer GEMM (tcgen05 kind::i8) and its dequantize epilogue.  The oracle is an exact integer matmul
+(numpy int64), the same reference the project's own tests use (ref_matmul_i32, src/tests_int8.rs:8-20); the
+first four cases are that file's test patterns (:21-108), the epilogue case its :110-136."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def K(gk):
+    k = gk.GpuKernels(0)
+    yield k
+    k.close()
+
+
+def ref_i32(a, b):
+    return (a.astype(np.int64) @ b.astype(np.int64)).astype(np.int32)
+
+
+def pattern(m, n, k, amod, bmod, boff):
+    a = (np.arange(m * k) % amod).astype(np.uint8).reshape(m, k)
+    b = ((np.arange(k * n) % bmod) - boff).astype(np.int8).reshape(k, n)
+    return a, b
+
+
+@pytest.mark.parametrize("m,n,k,amod,bmod,boff", [(2, 4, 8, 128, 64, 32), (14, 32, 64, 200, 100, 50), (17, 37, 13, 250, 120, 60),
+                                                 (64, 128, 512, 255, 127, 63)])
+def test_reference_test_patterns_host_call(gk, K, m, n, k, amod, bmod, boff):
+    a, b = pattern(m, n, k, amod, bmod, boff)
+    c = K.gemm_int8_host(a, b)
+    assert np.array_equal(c, ref_i32(a, b))
+    assert K.status() == 0
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 128, 128), (33, 200, 300), (129, 257, 1000), (300, 130, 4096), (512, 1024, 2048)])
+@pytest.mark.parametrize("layout_kn", [True, False])
+def test_gemm_int8_resident_weight_bit_exact(gk, K, m, n, k, layout_kn):
+    import torch
+    rng = np.random.default_rng(m + n + k)
+    a = rng.integers(0, 256, size=(m, k), dtype=np.uint8)
+    b = rng.integers(-128, 128, size=(k, n), dtype=np.int8)
+    w = K.upload_int8(b if layout_kn else np.ascontiguousarray(b.T), layout_kn=layout_kn)
+    c = K.gemm_int8(w, torch.from_numpy(a).cuda()).cpu().numpy()
+    assert np.array_equal(c, ref_i32(a, b))
+    assert K.status() == 0
+    w.free()
+
+
+def test_gemm_int8_extreme_values_and_strided_views(gk, K):
+    """255 x -128 everywhere (the largest magnitude per product), and A / C that are column slices of wider buffers."""
+    import torch
+    m, n, k = 70, 96, 640
+    a_full = torch.full((m, k + 7), 255, dtype=torch.uint8, device="cuda")
+    b = np.full((k, n), -128, np.int8)
+    w = K.upload_int8(b)
+    c_full = torch.zeros((m, n + 4), dtype=torch.int32, device="cuda")
+    K.gemm_int8(w, a_full[:, 3:3 + k], c=c_full[:, :n])
+    assert (c_full[:, :n] == -128 * 255 * k).all().item() and (c_full[:, n:] == 0).all().item()
+    w.free()
+
+
+def test_dequantize_epilogue(gk, K):
+    import torch
+    n = 35
+    c = (np.arange(n, dtype=np.int32) * 100 - 1700).reshape(1, n)
+    cd = torch.from_numpy(c).cuda()
+    out = K.dequantize_i32(cd, 0.5, 0.25).cpu().numpy()
+    assert np.array_equal(out, (c.astype(np.float32) * np.float32(0.5)) * np.float32(0.25))
+    bias = np.linspace(-1, 1, n, dtype=np.float32)
+    v = (c.astype(np.float32) * np.float32(0.01)) * np.float32(0.1) + bias
+    relu = K.dequantize_i32(cd, 0.01, 0.1, bias=torch.from_numpy(bias).cuda(), activation=1).cpu().numpy()
+    assert np.array_equal(relu, np.where(v < 0, np.float32(0), v))
+    silu = K.dequantize_i32(cd, 0.01, 0.1, bias=torch.from_numpy(bias).cuda(), activation=2).cpu().numpy()
+    assert np.allclose(silu, v / (1.0 + np.exp(-v)), rtol=1e-6, atol=1e-7)
+    gelu = K.dequantize_i32(cd, 0.01, 0.1, bias=torch.from_numpy(bias).cuda(), activation=3).cpu().numpy()
+    inner = np.float32(0.7978845608) * (v + np.float32(0.044715) * v * v * v)
+    assert np.allclose(gelu, 0.5 * v * (1.0 + np.tanh(inner)), rtol=1e-5, atol=1e-6)
+
+
+def test_int8_argument_checks(gk, K, oracle):
+    import torch
+    with pytest.raises(gk.GllmkError) as e:
+        K.dequantize_i32(torch.zeros((1, 4), dtype=torch.int32, device="cuda"), 1.0, 1.0, activation=9)
+    assert e.value.status == gk.Status.UNSUPPORTED
+    w = K.upload_int8(np.zeros((64, 32), np.int8))
+    with pytest.raises(gk.GllmkError) as e:  # an int8 weight is not a block-quantized weight
+        K.gemm(w, torch.zeros((64, 64), device="cuda"))
+    assert e.value.status == gk.Status.UNSUPPORTED
+    with pytest.raises(gk.GllmkError) as e:  # lda smaller than k
+        K.gemm_int8(w, torch.zeros((4, 32), dtype=torch.uint8, device="cuda"))
+    assert e.value.status == gk.Status.INVALID_ARG
+    w.free()
+    assert K.gemm_int8_host(np.zeros((0, 8), np.uint8), np.zeros((8, 4), np.int8)).shape == (0, 4)
