@@ -73,6 +73,7 @@ _SIGS = {
 # Entry points added after the first release of the header are listed here as they land.
 _OPTIONAL_SIGS: dict = {
     "gllmk_gemv_static": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _vp, _i64, _i64, _vp, _i64, _vp]),
+    "gllmk_embedding_gather": (_i32, [_vp, _vp, _vp, _i64, _vp, _vp]),
     "gllmk_int8_weight_upload": (_i32, [_vp, _i64, _i64, _vp, _i32, _i32, C.POINTER(_vp)]),
     "gllmk_gemm_int8": (_i32, [_vp, _vp, _vp, _i64, _i32, _vp, _i64, _vp]),
     "gllmk_dequantize_i32_f32": (_i32, [_vp, _vp, _vp, _i64, _i64, _f32, _f32, _vp, _i32, _vp]),

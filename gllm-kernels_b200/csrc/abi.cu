@@ -345,6 +345,18 @@ int32_t gllmk_dequant(gllmk_ctx ctx, gllmk_weight wh, float *out_dev, void *stre
     return dequant_matrix(c, static_cast<const Weight *>(wh), out_dev, static_cast<cudaStream_t>(stream));
 }
 
+int32_t gllmk_embedding_gather(gllmk_ctx ctx, gllmk_weight wh, const int32_t *ids_dev, int64_t count, float *out_dev, void *stream) {
+    if (!ctx || !wh || !ids_dev || !out_dev) return GLLMK_STATUS_INVALID_ARG;
+    Ctx *c = static_cast<Ctx *>(ctx);
+    const Weight *w = static_cast<const Weight *>(wh);
+    if (count < 0) return fail(c, GLLMK_STATUS_INVALID_ARG, "embedding_gather: negative count");
+    if (((uintptr_t)out_dev & 15) != 0) return fail(c, GLLMK_STATUS_INVALID_ARG, "out_dev must be 16-byte aligned");
+    if (w->qt == GLLMK_QUANT_INT8) return fail(c, GLLMK_STATUS_UNSUPPORTED, "embedding_gather: not a block-quantized weight");
+    if (w->device != c->device) return fail(c, GLLMK_STATUS_INVALID_ARG, "weight lives on another device");
+    DeviceGuard g(c->device);
+    return dequant_matrix(c, w, out_dev, static_cast<cudaStream_t>(stream), ids_dev, count);
+}
+
 int32_t gllmk_gemv(gllmk_ctx ctx, gllmk_weight wh, const float *x_dev, int64_t x_stride_t, int64_t x_stride_k,
                    int32_t m, float *y_dev, int64_t y_stride_t, int64_t y_stride_r, const float *row_scales,
                    int64_t n_row_scales, void *stream) {

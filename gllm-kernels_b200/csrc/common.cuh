@@ -113,7 +113,7 @@ int32_t ensure_dev_io(Ctx *c, size_t bytes);
 // ---- repack.cu ----
 int32_t repack_upload(Ctx *c, Weight *w, const void *blocks_dev, const void *scales_dev, cudaStream_t s);
 int32_t repack_unpack(Ctx *c, const Weight *w, void *blocks_dev, void *scales_dev, cudaStream_t s);
-int32_t dequant_matrix(Ctx *c, const Weight *w, float *out_dev, cudaStream_t s);
+int32_t dequant_matrix(Ctx *c, const Weight *w, float *out_dev, cudaStream_t s, const int32_t *ids = nullptr, int64_t count = 0);
 int32_t dequant_raw(Ctx *c, int32_t qt, const uint8_t *blocks_dev, const uint8_t *scales_dev, float global,
                     float *out_dev, size_t nblocks, size_t block_size, cudaStream_t s);
 // ---- gemv.cu ----

@@ -109,13 +109,24 @@ __global__ void unpack_q4k(const uint8_t *__restrict__ chunks, uint8_t *__restri
     (void)n;
 }
 // out[row][256b + ...] following k_quant.rs:7-56; thread = one 32-bit word of qs (4 low + 4 high outputs)
+// `ids` (optional): output row r decodes weight row ids[r] (embedding gather); rows outside [0, n) decode to zeros
 __global__ void dequant_q4k(const uint8_t *__restrict__ chunks, float *__restrict__ out, int64_t n, int64_t nb,
-                            size_t total) {
+                            size_t total, const int32_t *__restrict__ ids) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // (row*nb + b)*32 + w, w = word 0..31 of qs
     if (idx >= total) return;
     const int wq = (int)(idx & 31);
     const size_t rb = idx >> 5;
-    const int64_t row = (int64_t)(rb / (size_t)nb), b = (int64_t)(rb % (size_t)nb);
+    int64_t row = (int64_t)(rb / (size_t)nb);
+    const int64_t b = (int64_t)(rb % (size_t)nb);
+    if (ids) {
+        row = ids[row];
+        if (row < 0 || row >= n) {
+            float *z = out + rb * 256 + 64 * (wq >> 3) + 4 * (wq & 7);
+            *reinterpret_cast<float4 *>(z) = make_float4(0.f, 0.f, 0.f, 0.f);
+            *reinterpret_cast<float4 *>(z + 32) = make_float4(0.f, 0.f, 0.f, 0.f);
+            return;
+        }
+    }
     const int64_t T = row >> 4;
     const int rr = (int)(row & 15);
     const uint8_t *chunk = chunks + q4k_chunk_index(T, b, nb) * Q4K_CHUNK;
@@ -139,7 +150,7 @@ __global__ void dequant_q4k(const uint8_t *__restrict__ chunks, float *__restric
     hi.y = __fsub_rn(__fmul_rn(d2, (float)((w >> 12) & 15u)), nm2);
     hi.z = __fsub_rn(__fmul_rn(d2, (float)((w >> 20) & 15u)), nm2);
     hi.w = __fsub_rn(__fmul_rn(d2, (float)((w >> 28) & 15u)), nm2);
-    float *o = out + ((size_t)row * nb + b) * 256 + 64 * group + l;
+    float *o = out + rb * 256 + 64 * group + l;
     *reinterpret_cast<float4 *>(o) = lo;
     *reinterpret_cast<float4 *>(o + 32) = hi;
     (void)n;
@@ -205,12 +216,22 @@ __global__ void unpack_q80(const uint8_t *__restrict__ chunks, uint8_t *__restri
 }
 // classic.rs:860-868: out = d * q; thread = 8 elements
 __global__ void dequant_q80(const uint8_t *__restrict__ chunks, float *__restrict__ out, int64_t n, int64_t nb,
-                            int64_t nb8, size_t total) {
+                            int64_t nb8, size_t total, const int32_t *__restrict__ ids) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // (row*nb + b)*4 + t
     if (idx >= total) return;
     const int t = (int)(idx & 3);
     const size_t rb = idx >> 2;
-    const int64_t row = (int64_t)(rb / (size_t)nb), b = (int64_t)(rb % (size_t)nb);
+    int64_t row = (int64_t)(rb / (size_t)nb);
+    const int64_t b = (int64_t)(rb % (size_t)nb);
+    if (ids) {
+        row = ids[row];
+        if (row < 0 || row >= n) {
+            float *z = out + rb * 32 + 8 * t;
+            *reinterpret_cast<float4 *>(z) = make_float4(0.f, 0.f, 0.f, 0.f);
+            *reinterpret_cast<float4 *>(z + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+            return;
+        }
+    }
     const int64_t T = row >> 4;
     const int rr = (int)(row & 15), g = rr & 7, h = rr >> 3;
     const uint8_t *chunk = chunks + q4k_chunk_index(T, b >> 3, nb8) * Q80_CHUNK;
@@ -282,11 +303,22 @@ __global__ void unpack_fp4(const uint8_t *__restrict__ data, const uint8_t *__re
 // thread = 4 data bytes -> 8 f32.  MXFP4: LUT[code] * e8m0 (quant_mxfp4.rs:95-108);
 // NVFP4: (global * e4m3(sub)) * LUT[code] (quant.rs:77-86).
 __global__ void dequant_fp4(const uint32_t *__restrict__ data, const uint8_t *__restrict__ sf, float *__restrict__ out,
-                            int64_t n, int64_t k, int64_t k_pad, int nv, float global, size_t total) {
+                            int64_t n, int64_t k, int64_t k_pad, int nv, float global, size_t total,
+                            const int32_t *__restrict__ ids) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // row * (k/8) + w
     if (idx >= total) return;
     const int64_t wpr = k >> 3;
-    const int64_t row = (int64_t)(idx / (size_t)wpr), w = (int64_t)(idx % (size_t)wpr);
+    const int64_t orow = (int64_t)(idx / (size_t)wpr), w = (int64_t)(idx % (size_t)wpr);
+    int64_t row = orow;
+    if (ids) {
+        row = ids[orow];
+        if (row < 0 || row >= n) {
+            float *z = out + (size_t)orow * k + 8 * w;
+            *reinterpret_cast<float4 *>(z) = make_float4(0.f, 0.f, 0.f, 0.f);
+            *reinterpret_cast<float4 *>(z + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+            return;
+        }
+    }
     const uint32_t v = data[fp4_data_offset(row, 4 * w, k_pad) >> 2];
     float s;
     if (!nv) s = e8m0_to_f32(sf[sf_offset(row, w >> 2, k_pad >> 5)]);
@@ -297,7 +329,7 @@ __global__ void dequant_fp4(const uint32_t *__restrict__ data, const uint8_t *__
         const float c = e2m1_to_f32((v >> (4 * i)) & 15u);
         r[i] = nv ? __fmul_rn(s, c) : __fmul_rn(c, s);
     }
-    float *o = out + (size_t)row * k + 8 * w;
+    float *o = out + (size_t)orow * k + 8 * w;
     *reinterpret_cast<float4 *>(o) = make_float4(r[0], r[1], r[2], r[3]);
     *reinterpret_cast<float4 *>(o + 4) = make_float4(r[4], r[5], r[6], r[7]);
     (void)n;
@@ -383,17 +415,19 @@ int32_t repack_unpack(Ctx *c, const Weight *w, void *blocks, void *scales, cudaS
     return GLLMK_STATUS_OK;
 }
 
-int32_t dequant_matrix(Ctx *c, const Weight *w, float *out, cudaStream_t s) {
+int32_t dequant_matrix(Ctx *c, const Weight *w, float *out, cudaStream_t s, const int32_t *ids, int64_t count) {
+    const size_t rows = ids ? (size_t)count : (size_t)w->n;  // with ids: out [count, k], row r = weight row ids[r]
+    if (rows == 0) return GLLMK_STATUS_OK;
     if (w->qt == GLLMK_QUANT_Q4K) {
-        const size_t t = (size_t)w->n * w->nb * 32;
-        dequant_q4k<<<grid_for(t, 256), 256, 0, s>>>((const uint8_t *)w->qs, out, w->n, w->nb, t);
+        const size_t t = rows * w->nb * 32;
+        dequant_q4k<<<grid_for(t, 256), 256, 0, s>>>((const uint8_t *)w->qs, out, w->n, w->nb, t, ids);
     } else if (w->qt == GLLMK_QUANT_Q8_0) {
-        const size_t t = (size_t)w->n * w->nb * 4;
-        dequant_q80<<<grid_for(t, 256), 256, 0, s>>>((const uint8_t *)w->qs, out, w->n, w->nb, w->nb8, t);
+        const size_t t = rows * w->nb * 4;
+        dequant_q80<<<grid_for(t, 256), 256, 0, s>>>((const uint8_t *)w->qs, out, w->n, w->nb, w->nb8, t, ids);
     } else {
-        const size_t t = (size_t)w->n * (w->k >> 3);
+        const size_t t = rows * (w->k >> 3);
         dequant_fp4<<<grid_for(t, 256), 256, 0, s>>>((const uint32_t *)w->qs, (const uint8_t *)w->aux, out, w->n, w->k,
-                                                     w->k_pad, w->qt == GLLMK_QUANT_NVFP4, w->global_scale, t);
+                                                     w->k_pad, w->qt == GLLMK_QUANT_NVFP4, w->global_scale, t, ids);
     }
     GK_CUDA(c, cudaGetLastError());
     return GLLMK_STATUS_OK;

@@ -181,6 +181,16 @@ class GpuKernels:
         self._check(rc, "gllmk_gemm")
         return y
 
+    def embedding_gather(self, w: Weight, ids, out=None, stream=None):
+        """out[r, :] = decoded weight row ids[r] (int32 CUDA tensor) -> f32 [len(ids), k]; bad ids give zero rows."""
+        import torch
+        count = ids.numel()
+        if out is None:
+            out = torch.empty((count, w.k), dtype=torch.float32, device=ids.device)
+        self._check(lib().gllmk_embedding_gather(self._ctx, w._h, _ptr(ids), count, _ptr(out), _stream(stream)),
+                    "gllmk_embedding_gather")
+        return out
+
     # ---- W8A8 integer path (avx512_int8::gemm_int8 / dequantize_i32_to_f32, src/macros/matmul_x86_int8.rs) ----
     def upload_int8(self, b, layout_kn: bool = True) -> Weight:
         """s8 weight matrix -> resident tiles.  layout_kn=True: b is [k, n] row-major as in the reference's B;

@@ -122,6 +122,13 @@ GLLMK_API int32_t gllmk_dequant(gllmk_ctx ctx, gllmk_weight w, float *out_dev, v
 
 /* ---- decode: fused dequantize + GEMV (M <= 16 tokens) -------------------------------------- */
 
+/* Quantized embedding lookup (the reference emits it inline in its JIT, emit_quant_gather_inline, tested at
+ * src/compiler/codegen/x86_64/jit/quant_gemv_tests.inc.rs:541-828): out[r, :] = decode(weight row ids[r]) for
+ * r < count, f32 [count, k] row-major, bit-exact with gllmk_dequant.  ids are on the device; an id outside
+ * [0, n) yields a row of zeros. */
+GLLMK_API int32_t gllmk_embedding_gather(gllmk_ctx ctx, gllmk_weight w, const int32_t *ids_dev, int64_t count, float *out_dev,
+                               void *stream);
+
 /* Kernels::kquant_matmul / classic_matmul (src/traits.rs:543-563) and gemm_q4
  * (src/traits.rs:511-520) for small batches, on device memory with resident weights.
  *   y[t, r] = sum_k W[r, k] * x[t, k],  t < m <= GLLMK_GEMV_MAX_M, r < n.

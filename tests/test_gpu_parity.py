@@ -388,3 +388,18 @@ def test_swiglu_known_answers_through_ffn_decode(gk, K, oracle, torch):
     assert np.allclose(y[:4], want, rtol=2e-3, atol=1e-6), (y[:4], want)
     w_gu.free()
     w_dn.free()
+
+
+# ---- quantized embedding lookup: decode of selected rows, bit-exact ---------------------------------------
+@pytest.mark.parametrize("fmt,n,k", [("q4k", 300, 512), ("q8_0", 129, 96), ("mxfp4", 200, 320), ("nvfp4", 77, 192)])
+def test_embedding_gather_bit_exact(gk, K, oracle, torch, fmt, n, k):
+    oid, blocks, scales, g = make(oracle, fmt, n, k, 71)
+    qt = {"q4k": gk.QuantType.q4k(), "q8_0": gk.QuantType.q8_0(), "mxfp4": gk.QuantType.mxfp4(32), "nvfp4": gk.QuantType.nvfp4()}[fmt]
+    w = K.upload(qt, n, k, blocks, scales, g if g is not None else 1.0)
+    full = oracle.dequant_matrix(oid, blocks, n, k, scales=scales, global_scale=g if g is not None else 1.0)
+    ids = np.array([0, n - 1, 5, 5, n // 2, -1, n, 17], np.int32)  # repeats, both ends, two ids out of range
+    out = K.embedding_gather(w, torch.from_numpy(ids).cuda()).cpu().numpy()
+    for r, i in enumerate(ids):
+        want = full[i] if 0 <= i < n else np.zeros(k, np.float32)
+        assert np.array_equal(out[r].view(np.uint32), want.view(np.uint32)), (fmt, r, i)
+    w.free()
