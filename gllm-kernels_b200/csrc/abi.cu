@@ -265,6 +265,7 @@ int32_t gllmk_ctx_set(gllmk_ctx ctx, const char *key, int64_t value) {
     Ctx *c = static_cast<Ctx *>(ctx);
     if (!strcmp(key, "gemv_ctas_per_sm")) c->gemv_ctas_per_sm = value;
     else if (!strcmp(key, "gemv_pdl")) c->gemv_pdl = value;
+    else if (!strcmp(key, "gemv_fp4_int")) c->gemv_fp4_int = value;
     else return fail(c, GLLMK_STATUS_INVALID_ARG, "unknown key %s", key);
     return GLLMK_STATUS_OK;
 }

@@ -92,6 +92,7 @@ struct Ctx {
     size_t dev_io_bytes = 0;
     cudaStream_t stream = nullptr;  // the context's own stream for host-pointer entry points
     int64_t gemv_pdl = 1;
+    int64_t gemv_fp4_int = 0;  // 1: FP4 decode on the integer-decode GEMV kernel instead of the tensor-core one
     int64_t gemv_ctas_per_sm = 0;  // 0 = what the occupancy calculator allows
 };
 
@@ -128,6 +129,9 @@ int32_t gemm_grouped_launch(Ctx *c, const Weight *const *ws, int n_groups, const
                             const int64_t *row_offsets, void *y, int y_bf16, int64_t ldy, cudaStream_t s);
 // ---- gemm_fp4.cu ----
 int32_t gemm_fp4_launch(Ctx *c, const Weight *w, const Weight *x, void *y, int y_bf16, int64_t ldy, cudaStream_t s);
+// ---- gemv_fp4.cu ----
+int32_t gemv_fp4_launch(Ctx *c, const Weight *w, const float *x, int64_t xst, int64_t xsk, int m, float *y, int64_t yst, int64_t ysr,
+                        cudaStream_t s);
 // ---- gemm_i8.cu ----
 int32_t i8_weight_fill(Ctx *c, Weight *w, const int8_t *b_dev, int layout, cudaStream_t s);
 int32_t gemm_i8_launch(Ctx *c, const Weight *w, const uint8_t *a, int64_t lda, int m, int32_t *out, int64_t ldc, cudaStream_t s);

@@ -688,6 +688,10 @@ int32_t gemv_launch(Ctx *c, const Weight *w, const float *x, int64_t xst, int64_
                     int n_peers, const float *x_up) {
     if (w->qt != GLLMK_QUANT_Q4K && w->qt != GLLMK_QUANT_Q8_0 && w->qt != GLLMK_QUANT_MXFP4 && w->qt != GLLMK_QUANT_NVFP4)
         return fail(c, GLLMK_STATUS_UNSUPPORTED, "gemv: quant type %d has no decode kernel", w->qt);
+    // FP4 weights: the block-scaled tensor-core kernel (gemv_fp4.cu) unless the call needs what only this kernel
+    // has (row scales, peer outputs, a fused SwiGLU input) or the context asks for the integer-decode kernel
+    if ((w->qt == GLLMK_QUANT_MXFP4 || w->qt == GLLMK_QUANT_NVFP4) && !row_scales && n_peers == 0 && !x_up && !c->gemv_fp4_int)
+        return gemv_fp4_launch(c, w, x, xst, xsk, m, y, yst, ysr, s);
     int32_t rc = ensure_ws(c, gemv_ws_bytes(w, m));
     if (rc) return rc;
     const int nk = (int)((w->k + 255) / 256);

@@ -86,7 +86,8 @@ GLLMK_API const char *gllmk_last_error(gllmk_ctx ctx);
 GLLMK_API int32_t gllmk_ctx_status(gllmk_ctx ctx, int32_t *device_status);
 /* Tuning knobs, for experiments.  key: "gemv_ctas_per_sm" (resident CTAs per SM the decode grid is
  * sized for; 0 = occupancy limit), "gemv_pdl" (1 = overlap the activation staging kernel with the
- * weight stream). */
+ * weight stream), "gemv_fp4_int" (1 = decode MXFP4 / NVFP4 weights on the integer-decode kernel instead of
+ * the block-scaled tensor-core one). */
 GLLMK_API int32_t gllmk_ctx_set(gllmk_ctx ctx, const char *key, int64_t value);
 
 /* ---- weights: upload + repack, the inverse, and the bit-exact decode ----------------------- */
