@@ -118,6 +118,9 @@ __global__ void __launch_bounds__(256) fd_stage_kernel(const float *__restrict__
                                                        float *__restrict__ gtok) {
     __shared__ float red[8];
     __shared__ int bad_s;
+    // the GEMV grid behind this one may start now and stream its first weight tiles; it waits for this grid to
+    // finish before it touches the digit planes
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     const int tok = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const float *xr = x + (int64_t)tok * xst;
     const float inf = __int_as_float(0x7F800000);
@@ -247,28 +250,44 @@ __global__ void __launch_bounds__(FD_THREADS, 1) gemv_fp4_tc_kernel(const __grid
     if (warp == 0) {
         if (lane == 0) {
             // ---------------- copies ----------------
-            int slot = 0, round = 0;
-            bool ok = true;
-            for (int64_t u = u_begin; u < u_end && ok;) {
-                const int tile = (int)(u / p.nks), j0 = (int)(u - (int64_t)tile * p.nks);
-                const int j1 = (int)min((int64_t)p.nks, (int64_t)j0 + (u_end - u));
-                for (int ks = j0; ks < j1; ks++) {
-                    if (round > 0 && !tc::mbar_wait(empty + 8 * slot, (uint32_t)((round - 1) & 1), abort_flag)) {
-                        abort_s = 1;
-                        atomicExch(p.status, 51);
-                        ok = false;
-                        break;
-                    }
-                    const uint32_t st = smem_s + (uint32_t)(slot * p.stage_bytes);
-                    tc::mbar_expect_tx(full + 8 * slot, 16384u + bbytes + 2 * sf_bytes);
-                    const size_t wt = (size_t)tile * p.nks + ks;
-                    fd_bulk(st, p.qw + wt * 16384, 16384u, full + 8 * slot);
-                    fd_bulk(st + sfa_off, p.sfw + wt * sf_bytes, sf_bytes, full + 8 * slot);
-                    fd_bulk(st + b_off, p.qx + (size_t)ks * 16384, bbytes, full + 8 * slot);
-                    fd_bulk(st + sfb_off, p.sfx + (size_t)ks * sf_bytes, sf_bytes, full + 8 * slot);
-                    if (++slot == p.stages) slot = 0, round++;
+            // The weights do not depend on the staging kernel in front of this grid (programmatic dependent
+            // launch): the first ring-full of weight tiles is requested before the dependency wait, the digit
+            // tiles of those stages after it.
+            const int64_t total = u_end - u_begin;
+            const int pre = (int)(total < p.stages ? total : p.stages);
+            for (int i = 0; i < pre; i++) {
+                const int64_t u = u_begin + i;
+                const int tile = (int)(u / p.nks), ks = (int)(u - (int64_t)tile * p.nks);
+                const uint32_t st = smem_s + (uint32_t)(i * p.stage_bytes);
+                tc::mbar_expect_tx(full + 8 * i, 16384u + bbytes + 2 * sf_bytes);
+                const size_t wt = (size_t)tile * p.nks + ks;
+                fd_bulk(st, p.qw + wt * 16384, 16384u, full + 8 * i);
+                fd_bulk(st + sfa_off, p.sfw + wt * sf_bytes, sf_bytes, full + 8 * i);
+            }
+            asm volatile("griddepcontrol.wait;\n" ::: "memory");  // the digit planes and gtok are complete from here on
+            for (int i = 0; i < pre; i++) {
+                const int64_t u = u_begin + i;
+                const int ks = (int)(u % p.nks);
+                const uint32_t st = smem_s + (uint32_t)(i * p.stage_bytes);
+                fd_bulk(st + b_off, p.qx + (size_t)ks * 16384, bbytes, full + 8 * i);
+                fd_bulk(st + sfb_off, p.sfx + (size_t)ks * sf_bytes, sf_bytes, full + 8 * i);
+            }
+            int slot = pre == p.stages ? 0 : pre, round = pre == p.stages ? 1 : 0;
+            for (int64_t u = u_begin + pre; u < u_end; u++) {
+                const int tile = (int)(u / p.nks), ks = (int)(u - (int64_t)tile * p.nks);
+                if (round > 0 && !tc::mbar_wait(empty + 8 * slot, (uint32_t)((round - 1) & 1), abort_flag)) {
+                    abort_s = 1;
+                    atomicExch(p.status, 51);
+                    break;
                 }
-                u += j1 - j0;
+                const uint32_t st = smem_s + (uint32_t)(slot * p.stage_bytes);
+                tc::mbar_expect_tx(full + 8 * slot, 16384u + bbytes + 2 * sf_bytes);
+                const size_t wt = (size_t)tile * p.nks + ks;
+                fd_bulk(st, p.qw + wt * 16384, 16384u, full + 8 * slot);
+                fd_bulk(st + sfa_off, p.sfw + wt * sf_bytes, sf_bytes, full + 8 * slot);
+                fd_bulk(st + b_off, p.qx + (size_t)ks * 16384, bbytes, full + 8 * slot);
+                fd_bulk(st + sfb_off, p.sfx + (size_t)ks * sf_bytes, sf_bytes, full + 8 * slot);
+                if (++slot == p.stages) slot = 0, round++;
             }
         }
     } else if (warp == 1) {
@@ -406,7 +425,7 @@ __global__ void __launch_bounds__(FD_THREADS, 1) gemv_fp4_tc_kernel(const __grid
                 if (row < p.n) {
 #pragma unroll
                     for (int t = 0; t < GLLMK_GEMV_MAX_M; t++)
-                        if (t < p.m) p.y[(int64_t)t * p.yst + row * p.ysr] = o[t] * (p.wscale * p.gtok[t]);
+                        if (t < p.m) p.y[(int64_t)t * p.yst + row * p.ysr] = o[t] * (p.wscale * __ldcg(p.gtok + t));
                 }
             }
             u += j1 - j0;
@@ -468,8 +487,17 @@ int32_t gemv_fp4_launch(Ctx *c, const Weight *w, const float *x, int64_t xst, in
     p.partial = static_cast<float *>(c->red);
     p.counters = static_cast<int *>(c->cnt);
     p.status = c->status_dev;
-    gemv_fp4_tc_kernel<<<grid, FD_THREADS, (size_t)p.stages * p.stage_bytes + 1024, s>>>(p);
-    GK_CUDA(c, cudaGetLastError());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(FD_THREADS);
+    cfg.dynamicSmemBytes = (size_t)p.stages * p.stage_bytes + 1024;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = c->gemv_pdl != 0 ? 1 : 0;
+    GK_CUDA(c, cudaLaunchKernelEx(&cfg, gemv_fp4_tc_kernel, p));
     return GLLMK_STATUS_OK;
 }
 
