@@ -141,8 +141,17 @@ def run_ours(args):
     # --exchange nccl: each rank's GEMV writes its slice of a [world, M, n/world] buffer, then one all-gather.
     gbufs, ex = [], None
     if world > 1 and args.exchange == "peer":
-        ex = gk.PeerExchange(K, world, rank, slots=len(weights), slot_floats=M * 2 * N_FF)
-    elif world > 1:
+        # every rank must take the same path: agree on whether the peer mapping came up everywhere
+        try:
+            ex = gk.PeerExchange(K, world, rank, slots=len(weights), slot_floats=M * 2 * N_FF)
+            ok = torch.ones(1, device=dev)
+        except Exception as e:  # e.g. CUDA IPC not permitted in this container
+            print(f"rank {rank}: peer exchange unavailable ({e}); falling back to NCCL all-gather", file=sys.stderr)
+            ex, ok = None, torch.zeros(1, device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if ok.item() == 0 and ex is not None:
+            ex = None
+    if world > 1 and ex is None:
         gbufs = [torch.empty((world, M, (r1 - r0)), dtype=torch.float32, device=dev) for (_, _, n, _, r0, r1) in weights]
 
     weight_bytes_local = sum(w.ref_bytes for (_, w, *_r) in weights)

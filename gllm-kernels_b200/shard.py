@@ -138,12 +138,28 @@ class PeerExchange:
         import torch.distributed as dist
         self.K, self.world, self.rank, self.slots, self.slot_floats = K, world, rank, slots, slot_floats
         self.nbytes = self.FLAG_BYTES + slots * slot_floats * 4
-        self.local, handle = K.shared_alloc(self.nbytes)
+        # Set-up failures (no device memory, IPC not permitted, ...) must not leave other ranks waiting in a
+        # collective: every step's outcome is shared before the next one, and all ranks raise together.
+        self.local, self.bases, handle, err = None, [], None, None
+        try:
+            self.local, handle = K.shared_alloc(self.nbytes)
+        except Exception as e:
+            err = f"rank {rank}: {e}"
         handles = [None] * world
-        dist.all_gather_object(handles, handle, group=group)
-        self.bases = [self.local if r == rank else K.shared_open(handles[r]) for r in range(world)]
+        dist.all_gather_object(handles, (handle, err), group=group)
+        errs = [e for (_, e) in handles if e]
+        if not errs:
+            try:
+                self.bases = [self.local if r == rank else K.shared_open(handles[r][0]) for r in range(world)]
+            except Exception as e:
+                err = f"rank {rank}: {e}"
+            opened = [None] * world
+            dist.all_gather_object(opened, err, group=group)
+            errs = [e for e in opened if e]
+        if errs:
+            self.close()
+            raise RuntimeError("peer exchange set-up failed: " + "; ".join(errs))
         self.peers = [self.bases[r] for r in range(world) if r != rank]
-        self.seq = 0
         dist.barrier(group=group)  # every rank has mapped every buffer before anyone writes
 
     def slot_ptr(self, rank: int, slot: int, offset_floats: int = 0) -> int:
@@ -177,7 +193,8 @@ class PeerExchange:
 
     def close(self) -> None:
         for r, b in enumerate(self.bases):
-            if r != self.rank:
+            if r != self.rank and b:
                 self.K.shared_close(b)
-        self.K.shared_free(self.local)
-        self.bases = []
+        if self.local:
+            self.K.shared_free(self.local)
+        self.bases, self.local = [], None

@@ -104,3 +104,66 @@ def test_slice_blocks_rejects_wrong_sizes():
         gk.slice_blocks(qt, np.zeros(4 * 2 * 34, np.uint8), 4, 65, 0, 2)
     part = gk.slice_blocks(qt, np.arange(4 * 2 * 34, dtype=np.uint8) % 251, 4, 64, 1, 3)
     assert part.size == 2 * 2 * 34 and part[0] == (2 * 34) % 251
+
+
+class _FakeK:
+    """Stands in for GpuKernels in the set-up protocol of PeerExchange: no GPU, failures injected on the host."""
+
+    def __init__(self, rank, fail_alloc_on=None, fail_open_on=None):
+        self.rank, self.fail_alloc_on, self.fail_open_on, self.device = rank, fail_alloc_on, fail_open_on, 0
+        self.freed, self.closed = [], []
+
+    def shared_alloc(self, nbytes):
+        if self.rank == self.fail_alloc_on:
+            raise RuntimeError("injected: out of device memory")
+        return 0x1000 * (self.rank + 1), bytes([self.rank]) * 64
+
+    def shared_open(self, handle):
+        if self.rank == self.fail_open_on:
+            raise RuntimeError("injected: IPC not permitted")
+        return 0x100000 + handle[0]
+
+    def shared_close(self, ptr):
+        self.closed.append(ptr)
+
+    def shared_free(self, ptr):
+        self.freed.append(ptr)
+
+
+def _setup_worker(rank, world, port, mode, q):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    gk = importlib.import_module("gllm-kernels_b200")
+    try:
+        K = _FakeK(rank, fail_alloc_on=1 if mode == "alloc" else None, fail_open_on=0 if mode == "open" else None)
+        try:
+            ex = gk.PeerExchange(K, world, rank, slots=2, slot_floats=64)
+            q.put((rank, "up", sorted(ex.bases), len(ex.peers)))
+        except RuntimeError as e:
+            # every rank raises together and has released what it had
+            released = (K.freed == [0x1000 * (rank + 1)]) if not (mode == "alloc" and rank == 1) else (K.freed == [])
+            q.put((rank, "raised", "injected" in str(e), released))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(120)
+@pytest.mark.parametrize("mode", ["ok", "alloc", "open"])
+def test_peer_exchange_setup_failures_reach_every_rank(mode):
+    """A rank whose allocation or mapping fails must not leave the others in a collective: all ranks raise."""
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_setup_worker, args=(r, 2, port, mode, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=100) for _ in procs)
+    for p in procs:
+        p.join(timeout=30)
+    if mode == "ok":
+        assert [r[1] for r in res] == ["up", "up"] and all(r[3] == 1 for r in res)
+    else:
+        assert [r[1:] for r in res] == [("raised", True, True)] * 2, res
