@@ -81,8 +81,11 @@ GLLMK_API void gllmk_ctx_free(gllmk_ctx ctx);
 /* Text of the last error raised through this context ("" if none).  Never NULL. */
 GLLMK_API const char *gllmk_last_error(gllmk_ctx ctx);
 /* Waits for the device and reads the context's device-side status word: every wait inside a kernel
- * (on a bulk-copy barrier) is bounded, and a kernel that gives one up records a non-zero code there
- * and returns instead of hanging.  Returns RUNTIME_ERROR (and clears the word) if it was set. */
+ * (on a bulk-copy barrier, a tensor-core completion, another GPU's flag) is bounded, and a kernel that
+ * gives one up records a non-zero code there and returns instead of hanging.  Returns RUNTIME_ERROR (and
+ * clears the word) if it was set.  Codes name the kernel and the wait: 1-2 decode GEMV (consumer, producer),
+ * 10-14 fused-dequant prefill GEMM, 21-23 FP4 x FP4 GEMM, 31 gllmk_peer_barrier, 41-43 W8A8 GEMM, 51-53 FP4
+ * decode GEMV on the tensor core. */
 GLLMK_API int32_t gllmk_ctx_status(gllmk_ctx ctx, int32_t *device_status);
 /* Tuning knobs, for experiments.  key: "gemv_ctas_per_sm" (resident CTAs per SM the decode grid is
  * sized for; 0 = occupancy limit), "gemv_pdl" (1 = overlap the activation staging kernel with the
