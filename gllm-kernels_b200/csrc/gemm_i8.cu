@@ -14,16 +14,24 @@
 
 namespace gllmk {
 
-constexpr int I8_BM = 128, I8_BN = 256, I8_TILE = 16384, I8_STAGES = 4;
-constexpr int I8_STAGE_BYTES = I8_TILE + 2 * I8_TILE;  // weight tile + up to two activation tiles
+constexpr int I8_BM = 128, I8_BN = 256, I8_TILE = 16384;
+constexpr int I8_MAX_STAGES = 4;
+// a stage = MT weight tiles + up to two activation tiles; MT = 2 (two accumulators share one activation stage)
+// needs a third fewer bytes from L2 per MAC, which is what bounds this kernel
+template <int MT>
+__host__ __device__ constexpr int i8_stage_bytes() { return MT * I8_TILE + 2 * I8_TILE; }
+template <int MT>
+__host__ __device__ constexpr int i8_stages() { return MT == 2 ? 3 : 4; }
 constexpr int I8_EPI_WARPS = 8;
 constexpr int I8_THREADS = 64 + 32 * I8_EPI_WARPS;     // warp 0: copies, warp 1: MMA + TMEM, then the epilogue warps
-constexpr size_t I8_SMEM = (size_t)I8_STAGES * I8_STAGE_BYTES + 1024;
+template <int MT>
+__host__ __device__ constexpr size_t i8_smem() { return (size_t)i8_stages<MT>() * i8_stage_bytes<MT>() + 1024; }
 
 struct I8Params {
     const uint8_t *w;   // weight tile images
     const uint8_t *xt;  // activation tile images [token tile of 128][k-step][16384]
     int64_t n;
+    int row_tiles;
     int nks;            // k-steps of 128
     int m;
     int32_t *c;         // [m, n] row-major, leading dimension ldc
@@ -78,16 +86,21 @@ __global__ void __launch_bounds__(256) stage_act_u8_kernel(const uint8_t *__rest
     }
 }
 
-// grid (weight-row tiles, token tiles of 256); ntok = MMA N (multiple of 32, <= 256)
+// grid (groups of MT weight-row tiles, token tiles of 256); ntok = MMA N (multiple of 32, <= 256)
+template <int MT>
 __global__ void __launch_bounds__(I8_THREADS, 1) gemm_i8_kernel(const __grid_constant__ I8Params p, const int ntok) {
+    constexpr int I8_STAGES = i8_stages<MT>(), I8_STAGE_BYTES = i8_stage_bytes<MT>();
+    constexpr uint32_t TMEM_COLS = MT == 2 ? 512 : 256;
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bars[2 * I8_STAGES + 1];
+    __shared__ __align__(8) uint64_t bars[2 * I8_MAX_STAGES + 1];
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s;
     const uint32_t smem_s = (tc::smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t full = tc::smem_u32(&bars[0]), empty = tc::smem_u32(&bars[I8_STAGES]), accum = tc::smem_u32(&bars[2 * I8_STAGES]);
+    const uint32_t full = tc::smem_u32(&bars[0]), empty = tc::smem_u32(&bars[I8_MAX_STAGES]), accum = tc::smem_u32(&bars[2 * I8_MAX_STAGES]);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int64_t row0 = (int64_t)blockIdx.x * I8_BM, tok0 = (int64_t)blockIdx.y * I8_BN;
+    const int tile0 = (int)blockIdx.x * MT;
+    const int mt = min(MT, p.row_tiles - tile0);  // row tiles this CTA really has
+    const int64_t tok0 = (int64_t)blockIdx.y * I8_BN;
     volatile int *abort_flag = &abort_s;
 
     if (threadIdx.x == 0) {
@@ -99,7 +112,7 @@ __global__ void __launch_bounds__(I8_THREADS, 1) gemm_i8_kernel(const __grid_con
         tc::mbar_init(accum, 1);
         tc::mbar_init_fence();
     }
-    if (warp == 1) tc::tmem_alloc(tc::smem_u32(&tmem_base_s), 256);
+    if (warp == 1) tc::tmem_alloc(tc::smem_u32(&tmem_base_s), TMEM_COLS);
     tc::fence_before_sync();
     __syncthreads();
     tc::fence_after_sync();
@@ -118,10 +131,11 @@ __global__ void __launch_bounds__(I8_THREADS, 1) gemm_i8_kernel(const __grid_con
                 break;
             }
             const uint32_t st = smem_s + s * I8_STAGE_BYTES;
-            tc::mbar_expect_tx(full + 8 * s, (uint32_t)I8_TILE + bbytes);
-            i8_bulk(st, p.w + ((size_t)blockIdx.x * p.nks + ks) * I8_TILE, I8_TILE, full + 8 * s);
+            tc::mbar_expect_tx(full + 8 * s, (uint32_t)(mt * I8_TILE) + bbytes);
+            for (int i = 0; i < mt; i++)
+                i8_bulk(st + i * I8_TILE, p.w + ((size_t)(tile0 + i) * p.nks + ks) * I8_TILE, I8_TILE, full + 8 * s);
             for (int h = 0; h < halves; h++)
-                i8_bulk(st + I8_TILE + h * I8_TILE, p.xt + ((size_t)((tok0 >> 7) + h) * p.nks + ks) * I8_TILE, hb[h], full + 8 * s);
+                i8_bulk(st + MT * I8_TILE + h * I8_TILE, p.xt + ((size_t)((tok0 >> 7) + h) * p.nks + ks) * I8_TILE, hb[h], full + 8 * s);
         }
     } else if (warp == 1 && lane == 0) {
         // ---------------- MMA issue: weights signed (operand A), activations unsigned (operand B) ----------------
@@ -137,9 +151,12 @@ __global__ void __launch_bounds__(I8_THREADS, 1) gemm_i8_kernel(const __grid_con
             }
             tc::fence_after_sync();
             const uint32_t st = smem_s + s * I8_STAGE_BYTES;
-            const uint64_t ad = tc::smem_desc_sw128(st), bd = tc::smem_desc_sw128(st + I8_TILE);
+            const uint64_t bd = tc::smem_desc_sw128(st + MT * I8_TILE);
+            for (int i = 0; i < mt; i++) {
+                const uint64_t ad = tc::smem_desc_sw128(st + i * I8_TILE);
 #pragma unroll
-            for (int j = 0; j < 4; j++) tc::mma_i8(tmem, ad + 2 * j, bd + 2 * j, idesc, (uint32_t)((ks | j) != 0));
+                for (int j = 0; j < 4; j++) tc::mma_i8(tmem + 256u * (uint32_t)i, ad + 2 * j, bd + 2 * j, idesc, (uint32_t)((ks | j) != 0));
+            }
             tc::mma_commit(empty + 8 * s);
         }
         if (ok) tc::mma_commit(accum);
@@ -159,20 +176,23 @@ __global__ void __launch_bounds__(I8_THREADS, 1) gemm_i8_kernel(const __grid_con
             tc::fence_after_sync();
             // all MMAs have completed, so the stages are free: each warp stages its blocks in 4 KB of stage 0
             uint8_t *stage = smem_raw + (smem_s - tc::smem_u32(smem_raw)) + (warp - 2) * 4096;
-            for (int c = 32 * ((warp - 2) >> 2); c < ntok; c += 32 * (I8_EPI_WARPS / 4)) {
-                uint32_t v[32];
-                tc::tmem_ld32(tmem + ((uint32_t)(32 * quad) << 16) + (uint32_t)c, v);
-                tc::tmem_ld_wait();
-                float o[32];  // the s32 bit patterns travel through the 32-bit store helper unchanged
+            for (int i = 0; i < mt; i++) {
+                const int64_t row0 = (int64_t)(tile0 + i) * I8_BM;
+                for (int c = 32 * ((warp - 2) >> 2); c < ntok; c += 32 * (I8_EPI_WARPS / 4)) {
+                    uint32_t v[32];
+                    tc::tmem_ld32(tmem + ((uint32_t)(32 * quad) << 16) + 256u * (uint32_t)i + (uint32_t)c, v);
+                    tc::tmem_ld_wait();
+                    float o[32];  // the s32 bit patterns travel through the 32-bit store helper unchanged
 #pragma unroll
-                for (int j = 0; j < 32; j++) o[j] = __uint_as_float(v[j]);
-                tc::store_block_32x32<false>(p.c, p.ldc, row0 + 32 * quad, tok0 + c, p.n, p.m, o, stage, lane, p.vec);
+                    for (int j = 0; j < 32; j++) o[j] = __uint_as_float(v[j]);
+                    tc::store_block_32x32<false>(p.c, p.ldc, row0 + 32 * quad, tok0 + c, p.n, p.m, o, stage, lane, p.vec);
+                }
             }
         }
     }
     tc::fence_before_sync();
     __syncthreads();
-    if (warp == 1) tc::tmem_dealloc(tmem, 256);
+    if (warp == 1) tc::tmem_dealloc(tmem, TMEM_COLS);
 }
 
 // dequantize_i32_to_f32 (src/macros/matmul_x86_int8.rs:414-456, scalar tail semantics): (c as f32) * scale_a * scale_b
@@ -202,19 +222,27 @@ int32_t i8_weight_fill(Ctx *c, Weight *w, const int8_t *b_dev, int layout, cudaS
     return GLLMK_STATUS_OK;
 }
 
-int32_t gemm_i8_launch(Ctx *c, const Weight *w, const uint8_t *a, int64_t lda, int m, int32_t *out, int64_t ldc, cudaStream_t s) {
+template <int MT>
+static int32_t i8_launch_mt(Ctx *c, const I8Params &p, dim3 grid, int ntok, cudaStream_t s) {
     static bool attr_set[64] = {};  // function attributes are per device
     const int dev_slot = c->device & 63;
     if (!attr_set[dev_slot]) {
-        GK_CUDA(c, cudaFuncSetAttribute(gemm_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)I8_SMEM));
+        GK_CUDA(c, cudaFuncSetAttribute(gemm_i8_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)i8_smem<MT>()));
         attr_set[dev_slot] = true;
     }
+    gemm_i8_kernel<MT><<<grid, I8_THREADS, i8_smem<MT>(), s>>>(p, ntok);
+    GK_CUDA(c, cudaGetLastError());
+    return GLLMK_STATUS_OK;
+}
+
+int32_t gemm_i8_launch(Ctx *c, const Weight *w, const uint8_t *a, int64_t lda, int m, int32_t *out, int64_t ldc, cudaStream_t s) {
     const int ntok = m > 128 ? I8_BN : (m + 31) / 32 * 32;
     const int mtiles = (m + I8_BN - 1) / I8_BN;
     const int atiles = ntok > 128 ? 2 * mtiles : 1;
     I8Params p{};
     p.w = static_cast<const uint8_t *>(w->qs);
     p.n = w->n;
+    p.row_tiles = (int)(w->n_pad / I8_BM);
     p.nks = (int)(w->k_pad / 128);
     p.m = m;
     p.c = out;
@@ -226,9 +254,13 @@ int32_t gemm_i8_launch(Ctx *c, const Weight *w, const uint8_t *a, int64_t lda, i
     p.xt = static_cast<const uint8_t *>(c->act);
     stage_act_u8_kernel<<<dim3((unsigned)p.nks, (unsigned)atiles), 256, 0, s>>>(a, lda, m, w->k, static_cast<uint8_t *>(c->act));
     GK_CUDA(c, cudaGetLastError());
-    gemm_i8_kernel<<<dim3((unsigned)(w->n_pad / I8_BM), (unsigned)mtiles), I8_THREADS, I8_SMEM, s>>>(p, ntok);
-    GK_CUDA(c, cudaGetLastError());
-    return GLLMK_STATUS_OK;
+    // two row tiles per CTA when the estimated time (waves x (k-steps per CTA x relative step cost + a fixed
+    // prologue / epilogue worth ~8 steps)) is lower
+    const auto waves = [&](int ctas) { return (double)((ctas + c->sm_count - 1) / c->sm_count); };
+    const int pairs = (p.row_tiles + 1) / 2;
+    const double t1 = waves(mtiles * p.row_tiles) * (p.nks + 8.0), t2 = waves(mtiles * pairs) * (2.0 * p.nks * 0.75 + 8.0);
+    if (ntok > 128 && t2 < t1) return i8_launch_mt<2>(c, p, dim3((unsigned)pairs, (unsigned)mtiles), ntok, s);
+    return i8_launch_mt<1>(c, p, dim3((unsigned)p.row_tiles, (unsigned)mtiles), ntok, s);
 }
 
 int32_t dequant_i32_launch(Ctx *c, const int32_t *ci, float *out, int64_t m, int64_t n, int64_t ldc, int64_t ldo, float scale_a,

@@ -47,6 +47,21 @@ def test_gemm_int8_resident_weight_bit_exact(gk, K, m, n, k, layout_kn):
     w.free()
 
 
+def test_gemm_int8_two_row_tiles_per_cta(gk, K):
+    """299 row tiles and a 256-token tile: a CTA takes two row tiles (two accumulators share the activation stage),
+    the last CTA has one."""
+    import torch
+    m, n, k = 200, 128 * 299 - 50, 256
+    rng = np.random.default_rng(9)
+    a = rng.integers(0, 256, size=(m, k), dtype=np.uint8)
+    b = rng.integers(-128, 128, size=(k, n), dtype=np.int8)
+    w = K.upload_int8(b)
+    c = K.gemm_int8(w, torch.from_numpy(a).cuda()).cpu().numpy()
+    assert np.array_equal(c, ref_i32(a, b))
+    assert K.status() == 0
+    w.free()
+
+
 def test_gemm_int8_extreme_values_and_strided_views(gk, K):
     """255 x -128 everywhere (the largest magnitude per product), and A / C that are column slices of wider buffers."""
     import torch
