@@ -252,3 +252,8 @@ def test_gemm_grouped_rejects_mismatched_weights(gk, K, oracle):
     assert e.value.status == gk.Status.INVALID_ARG
     wa.free()
     wb.free()
+
+
+def test_gemm_more_token_tiles_than_one_launch_holds(gk, K, oracle):
+    # 17000 tokens = 67 tiles of 256: the launcher cuts the token range into launches of at most 64 tiles
+    assert run_case(gk, K, oracle, "q8_0", 128, 64, 17000, seed=31) <= TOL

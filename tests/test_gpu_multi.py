@@ -76,3 +76,34 @@ def test_gemv_allgather_two_gpus():
     for p in procs:
         p.join(timeout=30)
     assert res == {0: "ok", 1: "ok"}, res
+
+
+def test_two_devices_in_one_process():
+    """Contexts on two GPUs of one process: kernels' per-device attributes, buffers and the static scratch are set up
+    for each device separately."""
+    import importlib
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    gk = importlib.import_module("gllm-kernels_b200")
+    from oracle import oracle as O
+    rng = np.random.default_rng(3)
+    n, k = 256, 512
+    W = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    blocks = O.quantize_q4_k(W)
+    wd = O.dequant_matrix(O.Q4K, blocks, n, k)
+    x1 = rng.standard_normal((1, k)).astype(np.float32)
+    xm = rng.standard_normal((96, k)).astype(np.float32)
+    for dev in (1, 0, 1):
+        K = gk.GpuKernels(dev)
+        w = K.upload(gk.QuantType.q4k(), n, k, blocks)
+        with torch.cuda.device(dev):
+            y1 = K.gemv(w, torch.from_numpy(x1).to(f"cuda:{dev}")).cpu().numpy()
+            ym = K.gemm(w, torch.from_numpy(xm).to(f"cuda:{dev}").to(torch.bfloat16)).cpu().numpy()
+            torch.cuda.synchronize(dev)
+        assert O.rel_err(y1, O.quant_matmul(blocks, np.ascontiguousarray(x1.T), O.Q4K, n, 1, k).T) <= 2e-3
+        xb = torch.from_numpy(xm).to(torch.bfloat16).to(torch.float32).numpy()
+        assert O.rel_err(ym, O.gemm_f32_nt(xb, wd)) <= 1e-2
+        assert K.status() == 0
+        w.free()
+        K.close()
