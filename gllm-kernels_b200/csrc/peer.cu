@@ -20,6 +20,10 @@ struct PeerBarrierParams {
 
 // thread q talks to the q-th other rank (rank numbers skip this rank)
 __global__ void peer_barrier_kernel(const __grid_constant__ PeerBarrierParams p) {
+    // Launched with programmatic stream serialization: it may become resident while the product in front of it is
+    // still running and lets the kernel behind it do the same; it orders itself after the product here.
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
     const int q = threadIdx.x;
     // seq == 0: the sequence number lives in this rank's flag area (word 16) and advances by one per barrier,
     // so that a captured graph can be replayed
@@ -61,8 +65,16 @@ int32_t peer_barrier_launch(Ctx *c, uint32_t *mine, uint32_t *const *peers, int 
     p.rank = rank;
     p.seq = seq;
     p.status = c->status_dev;
-    peer_barrier_kernel<<<1, 32, 0, s>>>(p);
-    GK_CUDA(c, cudaGetLastError());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1);
+    cfg.blockDim = dim3(32);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = c->gemv_pdl != 0 ? 1 : 0;
+    GK_CUDA(c, cudaLaunchKernelEx(&cfg, peer_barrier_kernel, p));
     return GLLMK_STATUS_OK;
 }
 
