@@ -118,9 +118,11 @@ __global__ void __launch_bounds__(256) fd_stage_kernel(const float *__restrict__
                                                        float *__restrict__ gtok) {
     __shared__ float red[8];
     __shared__ int bad_s;
-    // the GEMV grid behind this one may start now and stream its first weight tiles; it waits for this grid to
-    // finish before it touches the digit planes
+    // The GEMV grid behind this one may start now and stream its first weight tiles; it waits for this grid to
+    // finish before it touches the digit planes.  This grid is itself launched early: it may read x and overwrite
+    // the planes only once everything in front of it in the stream has completed.
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
     const int tok = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const float *xr = x + (int64_t)tok * xst;
     const float inf = __int_as_float(0x7F800000);
@@ -455,8 +457,18 @@ int32_t gemv_fp4_launch(Ctx *c, const Weight *w, const float *x, int64_t xst, in
     if (rc) return rc;
     uint8_t *qx = static_cast<uint8_t *>(c->act), *sfx = qx + data_bytes;
     float *gtok = reinterpret_cast<float *>(sfx + sf_bytes);
-    fd_stage_kernel<<<dim3((unsigned)((w->k_pad / 32 + 7) / 8), (unsigned)m), 256, 0, s>>>(x, xst, xsk, w->k, w->k_pad, nv, qx, sfx, gtok);
-    GK_CUDA(c, cudaGetLastError());
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    {
+        cudaLaunchConfig_t scfg = {};
+        scfg.gridDim = dim3((unsigned)((w->k_pad / 32 + 7) / 8), (unsigned)m);
+        scfg.blockDim = dim3(256);
+        scfg.stream = s;
+        scfg.attrs = attr;
+        scfg.numAttrs = c->gemv_pdl != 0 ? 1 : 0;
+        GK_CUDA(c, cudaLaunchKernelEx(&scfg, fd_stage_kernel, x, xst, xsk, w->k, w->k_pad, nv, qx, sfx, gtok));
+    }
 
     FdParams p{};
     p.qw = static_cast<const uint8_t *>(w->qs);
@@ -492,9 +504,6 @@ int32_t gemv_fp4_launch(Ctx *c, const Weight *w, const float *x, int64_t xst, in
     cfg.blockDim = dim3(FD_THREADS);
     cfg.dynamicSmemBytes = (size_t)p.stages * p.stage_bytes + 1024;
     cfg.stream = s;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = c->gemv_pdl != 0 ? 1 : 0;
     GK_CUDA(c, cudaLaunchKernelEx(&cfg, gemv_fp4_tc_kernel, p));
