@@ -218,14 +218,16 @@ def run_ours(args):
     value = weight_bytes_total / (ms_step * 1e-3) / 1e9
 
     # ---- end to end through the host-pointer call: pinned x -> device, GEMVs, y -> host, every step ----
-    xh_model = x_model.cpu().numpy()
-    xh_ff = x_ff.cpu().numpy()
+    # host activations and outputs live in page-locked memory, as a serving loop keeps them
+    xh_model = torch.empty(x_model.shape, dtype=torch.float32, pin_memory=True).copy_(x_model).numpy()
+    xh_ff = torch.empty(x_ff.shape, dtype=torch.float32, pin_memory=True).copy_(x_ff).numpy()
+    yh = {n: torch.empty((M, n), dtype=torch.float32, pin_memory=True).numpy() for n in {n for (_, _, n, _, _, _) in weights}}
     e2e = None
     if world == 1:
         def step_host():
             out = None
             for (name, w, n, k, r0, r1) in weights:
-                out = K.matmul_host(w, xh_ff if name == "down" else xh_model)
+                out = K.matmul_host(w, xh_ff if name == "down" else xh_model, out=yh[n])
             return out
         for _ in range(3):
             step_host()
@@ -237,7 +239,8 @@ def run_ours(args):
                "h2d_bytes_per_step": L * sum(M * k * 4 for _, n, k in shapes),
                "d2h_bytes_per_step": L * sum(M * n * 4 for _, n, k in shapes),
                "note": "weights resident (uploaded once, like the reference's weights handle); activations and "
-                       "outputs are host buffers, copied inside the timed region, one synchronous call per GEMV"}
+                       "outputs are page-locked host buffers, transferred inside the timed region (x read by the staging "
+                       "kernel over PCIe, y by a device-to-host copy), one synchronous call per product"}
 
     peak, peak_kind = measured_peaks()
     out = {

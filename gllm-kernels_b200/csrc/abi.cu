@@ -595,14 +595,31 @@ static int32_t matmul_host_impl(Ctx *c, const Weight *w, const float *x_host, in
     if (!rc) rc = ensure_dev_io(c, so + sb + 256);
     if (rc) return rc;
     char *pin = static_cast<char *>(c->pin), *dev = static_cast<char *>(c->dev_io);
-    memcpy(pin + xo, x_host, xb);
+    // Page-locked caller buffers (cudaMallocHost / cudaHostRegister) are used as they are: no staging copy on the
+    // host.  Anything else goes through the context's own pinned buffer.
+    const auto pinned_alias = [](const void *h) -> const void * {
+        cudaPointerAttributes at;
+        if (cudaPointerGetAttributes(&at, h) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return nullptr;
+        }
+        return at.type == cudaMemoryTypeHost ? at.devicePointer : nullptr;
+    };
+    const void *x_alias = pinned_alias(x_host);
+    const bool y_pinned = pinned_alias(y_host) != nullptr;
+    const char *x_src = reinterpret_cast<const char *>(x_host);  // host address copies are issued from
+    if (!x_alias) {
+        memcpy(pin + xo, x_host, xb);
+        x_src = pin + xo;
+        x_alias = pin + xo;  // cudaMallocHost memory: same address on the device
+    }
     if (sb) memcpy(pin + so, scales_host, sb);
-    // Small activation blocks are read by the staging kernel straight from the pinned buffer (mapped into the
-    // device's address space): one copy call and its latency less per product.  Larger ones go through HBM.
+    // Small activation blocks are read by the staging kernel straight from page-locked host memory (mapped into
+    // the device's address space): one copy call and its latency less per product.  Larger ones go through HBM.
     const bool zero_copy_x = xb <= (size_t)256 * 1024;
-    if (!zero_copy_x) GK_CUDA(c, cudaMemcpyAsync(dev + xo, pin + xo, xb, cudaMemcpyHostToDevice, c->stream));
+    if (!zero_copy_x) GK_CUDA(c, cudaMemcpyAsync(dev + xo, x_src, xb, cudaMemcpyHostToDevice, c->stream));
     if (sb) GK_CUDA(c, cudaMemcpyAsync(dev + so, pin + so, sb, cudaMemcpyHostToDevice, c->stream));
-    const float *xd = reinterpret_cast<const float *>(zero_copy_x ? pin + xo : dev + xo);
+    const float *xd = reinterpret_cast<const float *>(zero_copy_x ? static_cast<const char *>(x_alias) : dev + xo);
     float *yd = reinterpret_cast<float *>(dev + yo);
     const float *sd = sb ? reinterpret_cast<const float *>(dev + so) : nullptr;
     if (!ref_layout && !sb && m_t > GLLMK_GEMM_GEMV_MAX_M) {
@@ -619,9 +636,10 @@ static int32_t matmul_host_impl(Ctx *c, const Weight *w, const float *x_host, in
                              c->stream);
         if (rc) return rc;
     }
-    GK_CUDA(c, cudaMemcpyAsync(pin + yo, dev + yo, yb, cudaMemcpyDeviceToHost, c->stream));
+    GK_CUDA(c, cudaMemcpyAsync(y_pinned ? static_cast<void *>(y_host) : static_cast<void *>(pin + yo), dev + yo, yb, cudaMemcpyDeviceToHost,
+                               c->stream));
     GK_CUDA(c, cudaStreamSynchronize(c->stream));
-    memcpy(y_host, pin + yo, yb);
+    if (!y_pinned) memcpy(y_host, pin + yo, yb);
     return GLLMK_STATUS_OK;
 }
 

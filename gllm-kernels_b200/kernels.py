@@ -313,11 +313,15 @@ class GpuKernels:
         self._check(rc, "gllmk_gemv_static")
         return y
 
-    def matmul_host(self, w: Weight, x, ref_layout: bool = False) -> np.ndarray:
-        """Resident weight, HOST activations and outputs (numpy): the call timed end to end."""
+    def matmul_host(self, w: Weight, x, ref_layout: bool = False, out=None) -> np.ndarray:
+        """Resident weight, HOST activations and outputs (numpy): the call timed end to end.  Page-locked arrays
+        (e.g. torch.empty(..., pin_memory=True).numpy()) for `x` and `out` are used without a staging copy."""
         x = _np(x, np.float32)
         m = x.shape[1] if ref_layout else x.shape[0]
-        y = np.empty((w.n, m) if ref_layout else (m, w.n), np.float32)
+        shape = (w.n, m) if ref_layout else (m, w.n)
+        y = np.empty(shape, np.float32) if out is None else _np(out, np.float32, True)
+        if y.shape != shape:
+            raise ValueError(f"out has shape {y.shape}, expected {shape}")
         self._check(lib().gllmk_matmul_host(self._ctx, w._h, _ptr(x), m, _ptr(y), int(ref_layout)), "gllmk_matmul_host")
         return y
 

@@ -403,3 +403,18 @@ def test_embedding_gather_bit_exact(gk, K, oracle, torch, fmt, n, k):
         want = full[i] if 0 <= i < n else np.zeros(k, np.float32)
         assert np.array_equal(out[r].view(np.uint32), want.view(np.uint32)), (fmt, r, i)
     w.free()
+
+
+def test_matmul_host_with_page_locked_buffers(gk, K, oracle, torch):
+    """Pinned x / out are used in place (no staging copy); results equal the pageable-buffer call bit for bit."""
+    oid, blocks, _, _ = make(oracle, "q4k", 512, 1024, 43)
+    w = K.upload(gk.QuantType.q4k(), 512, 1024, blocks)
+    x = np.random.default_rng(43).standard_normal((2, 1024)).astype(np.float32)
+    xp = torch.empty((2, 1024), dtype=torch.float32, pin_memory=True)
+    xp.copy_(torch.from_numpy(x))
+    yp = torch.empty((2, 512), dtype=torch.float32, pin_memory=True)
+    y_pinned = K.matmul_host(w, xp.numpy(), out=yp.numpy())
+    y_plain = K.matmul_host(w, x)
+    assert np.array_equal(y_pinned, y_plain) and np.array_equal(yp.numpy(), y_plain)
+    assert oracle.rel_err(y_plain, oracle.gemm_q4(blocks, x, None, 2, 512, 1024)) <= TOL
+    w.free()
