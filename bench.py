@@ -289,10 +289,33 @@ def extra_configs(K, gk, torch, dev, peak):
     gen = torch.Generator(device=dev).manual_seed(20240)
     torch.cuda.empty_cache()
 
+    def random_gguf_blocks(qt, n, k):
+        """Formats without a device quantizer: random payload bytes, f16 (Q8_K: f32) scale fields of +-0.02."""
+        bs, bb = qt.block_size(), qt.block_bytes()
+        nblk = n * (k // bs)
+        b = torch.randint(0, 256, (nblk, bb), generator=gen, device=dev, dtype=torch.uint8)
+        d = (torch.rand((nblk, 2), generator=gen, device=dev) - 0.5) * 0.04
+        if qt.id == 10:
+            b[:, 0:4] = d[:, :1].contiguous().view(torch.uint8)
+        else:
+            h = d.to(torch.float16).view(torch.uint8)  # [nblk, 4]: two f16
+            if qt.id == 6:
+                b[:, 208:210] = h[:, 0:2]
+            else:
+                b[:, 0:2] = h[:, 0:2]
+            if qt.id == 7:
+                b[:, 2:4] = h[:, 2:4]
+        return b.reshape(-1)
+
     def run(qt, n, k, ms, copies, name):
         bs, bb = qt.block_size(), qt.block_bytes()
         ws = []
         for _ in range(copies):
+            if qt.id >= 6:
+                q = random_gguf_blocks(qt, n, k)
+                ws.append(K.upload(qt, n, k, q))
+                del q
+                continue
             W = torch.randn((n, k), generator=gen, device=dev) * 0.02
             q = K.quantize(qt, W)
             ws.append(K.upload(qt, n, k, q[0], q[1]) if qt.id == 3 else (K.upload(qt, n, k, q[0], None, q[1]) if qt.id == 4
@@ -341,6 +364,12 @@ def extra_configs(K, gk, torch, dev, peak):
     run(gk.QuantType.mxfp4(32), 14336, 4096, [1], 10, "cfg3_mxfp4_expert_decode_14336x4096")
     run(gk.QuantType.nvfp4(), 14336, 4096, [1], 10, "cfg4_nvfp4_decode_14336x4096")
     run(gk.QuantType.q4k(), N_FF, D_MODEL, [16], 3, "cfg5_q4k_28672x8192")
+    # the other GGUF formats (streaming CUDA-core GEMV over reference-layout blocks), down-projection shape of config 5
+    run(gk.QuantType.q6k(), D_MODEL, N_FF, [1, 8], 2, "gguf_q6k_8192x28672")
+    run(gk.QuantType.q5k(), D_MODEL, N_FF, [1], 2, "gguf_q5k_8192x28672")
+    run(gk.QuantType.q8k(), D_MODEL, N_FF, [1], 2, "gguf_q8k_8192x28672")
+    run(gk.QuantType.q4_0(), D_MODEL, N_FF, [1], 3, "gguf_q4_0_8192x28672")
+    run(gk.QuantType.q5_0(), D_MODEL, N_FF, [1], 3, "gguf_q5_0_8192x28672")
     res.update(extra_gemm(K, gk, torch, dev, gen))
     return res
 

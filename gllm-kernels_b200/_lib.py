@@ -72,6 +72,7 @@ _SIGS = {
 }
 # Entry points added after the first release of the header are listed here as they land.
 _OPTIONAL_SIGS: dict = {
+    "gllmk_dequant_gguf": (_i32, [_vp, _i32, _vp, _vp, _sz]),
     "gllmk_gemv_static": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _vp, _i64, _i64, _vp, _i64, _vp]),
     "gllmk_embedding_gather": (_i32, [_vp, _vp, _vp, _i64, _vp, _vp]),
     "gllmk_int8_weight_upload": (_i32, [_vp, _i64, _i64, _vp, _i32, _i32, C.POINTER(_vp)]),

@@ -59,6 +59,8 @@ static int block_size_of(int qt, int mx) {
         case GLLMK_QUANT_Q8_0: return 32;
         case GLLMK_QUANT_MXFP4: return mx;
         case GLLMK_QUANT_NVFP4: return 64;
+        case GLLMK_QUANT_Q6_K: case GLLMK_QUANT_Q5_K: case GLLMK_QUANT_Q8_K: return 256;
+        case GLLMK_QUANT_Q4_0: case GLLMK_QUANT_Q5_0: return 32;
     }
     return 0;
 }
@@ -68,6 +70,11 @@ static int block_bytes_of(int qt, int mx) {
         case GLLMK_QUANT_Q8_0: return 34;
         case GLLMK_QUANT_MXFP4: return 1 + mx / 2;
         case GLLMK_QUANT_NVFP4: return 36;
+        case GLLMK_QUANT_Q6_K: return 210;
+        case GLLMK_QUANT_Q5_K: return 176;
+        case GLLMK_QUANT_Q8_K: return 292;
+        case GLLMK_QUANT_Q4_0: return 18;
+        case GLLMK_QUANT_Q5_0: return 22;
     }
     return 0;
 }
@@ -86,7 +93,7 @@ struct DeviceGuard {
 
 // Creates the handle and its device buffers for an n x k matrix of type qt (no data yet).
 static int32_t weight_alloc(Ctx *c, int32_t qt, int64_t n, int64_t k, int32_t mx_block, float global, Weight **out) {
-    if (qt != GLLMK_QUANT_Q4K && qt != GLLMK_QUANT_Q8_0 && qt != GLLMK_QUANT_MXFP4 && qt != GLLMK_QUANT_NVFP4)
+    if (qt != GLLMK_QUANT_Q4K && qt != GLLMK_QUANT_Q8_0 && qt != GLLMK_QUANT_MXFP4 && qt != GLLMK_QUANT_NVFP4 && !raw_format(qt))
         return fail(c, GLLMK_STATUS_UNSUPPORTED, "unknown quant type %d", qt);
     if (qt == GLLMK_QUANT_MXFP4 && mx_block != 32)
         return fail(c, GLLMK_STATUS_UNSUPPORTED, "MXFP4 weights need block_size 32 (got %d)", mx_block);
@@ -106,7 +113,12 @@ static int32_t weight_alloc(Ctx *c, int32_t qt, int64_t n, int64_t k, int32_t mx
     w->global_scale = global;
     w->device = c->device;
     w->ref_bytes = (uint64_t)n * (uint64_t)w->nb * (uint64_t)block_bytes_of(qt, mx_block);
-    if (qt == GLLMK_QUANT_Q4K) {
+    if (raw_format(qt)) {
+        // reference blocks as they are; 16 spare bytes let the GEMV's 16-byte loads run past the last row
+        w->n_pad = n;
+        w->qs_bytes = (size_t)w->ref_bytes + 16;
+        w->aux_bytes = 0;
+    } else if (qt == GLLMK_QUANT_Q4K) {
         w->n_pad = (n + 127) / 128 * 128;
         w->qs_bytes = (size_t)(w->n_pad / 16) * w->nb * Q4K_CHUNK;
         w->aux_bytes = 0;
@@ -422,6 +434,13 @@ int32_t gllmk_gemm(gllmk_ctx ctx, gllmk_weight wh, const void *a_dev, int32_t a_
     if (lda < w->k || ldy < w->n) return fail(c, GLLMK_STATUS_INVALID_ARG, "gemm: leading dimension smaller than the row");
     if (w->device != c->device) return fail(c, GLLMK_STATUS_INVALID_ARG, "weight lives on another device");
     DeviceGuard g(c->device);
+    if (raw_format(w->qt)) {
+        // no tensor-core prefill kernel for these formats: the streaming GEMV takes any number of tokens
+        if (a_dtype != GLLMK_DTYPE_F32 || y_dtype != GLLMK_DTYPE_F32)
+            return fail(c, GLLMK_STATUS_UNSUPPORTED, "gemm: quant type %d takes f32 activations and outputs only", w->qt);
+        return gemv_launch(c, w, static_cast<const float *>(a_dev), lda, 1, m, static_cast<float *>(y_dev), ldy, 1, nullptr, 0,
+                           static_cast<cudaStream_t>(stream));
+    }
     // A few dozen tokens are still bound by the weight stream, which the decode kernel reads at several times
     // the rate the tensor-core pipeline reaches with a nearly empty N: run them as passes of up to 16 tokens.
     if (m <= GLLMK_GEMM_GEMV_MAX_M && a_dtype == GLLMK_DTYPE_F32 && y_dtype == GLLMK_DTYPE_F32) {
@@ -622,7 +641,7 @@ static int32_t matmul_host_impl(Ctx *c, const Weight *w, const float *x_host, in
     const float *xd = reinterpret_cast<const float *>(zero_copy_x ? static_cast<const char *>(x_alias) : dev + xo);
     float *yd = reinterpret_cast<float *>(dev + yo);
     const float *sd = sb ? reinterpret_cast<const float *>(dev + so) : nullptr;
-    if (!ref_layout && !sb && m_t > GLLMK_GEMM_GEMV_MAX_M) {
+    if (!ref_layout && !sb && m_t > GLLMK_GEMM_GEMV_MAX_M && !raw_format(w->qt)) {
         // prefill-sized batch: one tensor-core GEMM
         rc = gemm_launch(c, w, xd, 0, k, m_t, yd, 0, n_w, c->stream);
         if (rc) return rc;
@@ -655,10 +674,13 @@ int32_t gllmk_matmul_host(gllmk_ctx ctx, gllmk_weight wh, const float *x_host, i
 }
 
 static int32_t family_matmul(gllmk_ctx ctx, const uint8_t *wb, const float *input, float *output, int32_t qt,
-                             int32_t want, size_t m, size_t n, size_t k) {
+                             bool kquant, size_t m, size_t n, size_t k) {
     if (!ctx || !wb || !input || !output) return GLLMK_STATUS_INVALID_ARG;
     Ctx *c = static_cast<Ctx *>(ctx);
-    if (qt != want)
+    // kquant_matmul takes the 256-element K-quants, classic_matmul the 32-element formats (src/cpu_kernels/mod.rs:3226-3394)
+    const bool ok = kquant ? (qt == GLLMK_QUANT_Q4K || qt == GLLMK_QUANT_Q6_K || qt == GLLMK_QUANT_Q5_K || qt == GLLMK_QUANT_Q8_K)
+                           : (qt == GLLMK_QUANT_Q8_0 || qt == GLLMK_QUANT_Q4_0 || qt == GLLMK_QUANT_Q5_0);
+    if (!ok)
         return fail(c, GLLMK_STATUS_UNSUPPORTED, "quant type %d is not handled by this entry point", qt);
     if (m == 0 || n == 0) return GLLMK_STATUS_OK;
     if (n > 0x7fffffffu) return fail(c, GLLMK_STATUS_INVALID_ARG, "n too large");
@@ -674,11 +696,11 @@ static int32_t family_matmul(gllmk_ctx ctx, const uint8_t *wb, const float *inpu
 
 int32_t gllmk_kquant_matmul_f32(gllmk_ctx ctx, const uint8_t *weight_blocks, const float *input, float *output,
                                 int32_t quant_type, size_t m, size_t n, size_t k) {
-    return family_matmul(ctx, weight_blocks, input, output, quant_type, GLLMK_QUANT_Q4K, m, n, k);
+    return family_matmul(ctx, weight_blocks, input, output, quant_type, true, m, n, k);
 }
 int32_t gllmk_classic_matmul_f32(gllmk_ctx ctx, const uint8_t *weight_blocks, const float *input, float *output,
                                  int32_t quant_type, size_t m, size_t n, size_t k) {
-    return family_matmul(ctx, weight_blocks, input, output, quant_type, GLLMK_QUANT_Q8_0, m, n, k);
+    return family_matmul(ctx, weight_blocks, input, output, quant_type, false, m, n, k);
 }
 
 int32_t gllmk_gemm_q4_f32(gllmk_ctx ctx, const uint8_t *weight, const float *input, float *output, const float *scales,
@@ -726,6 +748,12 @@ int32_t gllmk_dequant_q4_k(gllmk_ctx ctx, const uint8_t *blocks, float *out, siz
 }
 int32_t gllmk_dequant_q8_0(gllmk_ctx ctx, const uint8_t *blocks, float *out, size_t nblocks) {
     return dequant_host(ctx, GLLMK_QUANT_Q8_0, blocks, nullptr, 1.0f, out, nblocks, 32);
+}
+int32_t gllmk_dequant_gguf(gllmk_ctx ctx, int32_t quant_type, const uint8_t *blocks, float *out, size_t nblocks) {
+    if (!ctx) return GLLMK_STATUS_INVALID_ARG;
+    if (quant_type != GLLMK_QUANT_Q4K && quant_type != GLLMK_QUANT_Q8_0 && !raw_format(quant_type))
+        return fail(static_cast<Ctx *>(ctx), GLLMK_STATUS_UNSUPPORTED, "dequant_gguf: quant type %d", quant_type);
+    return dequant_host(ctx, quant_type, blocks, nullptr, 1.0f, out, nblocks, (size_t)block_size_of(quant_type, 0));
 }
 int32_t gllmk_dequant_mxfp4(gllmk_ctx ctx, const uint8_t *blocks, const uint8_t *scales, float *out, size_t num_blocks,
                             size_t block_size) {

@@ -686,6 +686,10 @@ static cudaError_t configure_and_launch(Ctx *c, GemvParams &p, int64_t ntg, cuda
 int32_t gemv_launch(Ctx *c, const Weight *w, const float *x, int64_t xst, int64_t xsk, int m, float *y, int64_t yst,
                     int64_t ysr, const float *row_scales, int64_t n_row_scales, cudaStream_t s, void *const *y_peers,
                     int n_peers, const float *x_up) {
+    if (raw_format(w->qt)) {
+        if (n_peers || x_up) return fail(c, GLLMK_STATUS_UNSUPPORTED, "gemv: quant type %d has no fused exchange / SwiGLU input", w->qt);
+        return raw_gemv_launch(c, w, x, xst, xsk, m, y, yst, ysr, row_scales, n_row_scales, s);
+    }
     if (w->qt != GLLMK_QUANT_Q4K && w->qt != GLLMK_QUANT_Q8_0 && w->qt != GLLMK_QUANT_MXFP4 && w->qt != GLLMK_QUANT_NVFP4)
         return fail(c, GLLMK_STATUS_UNSUPPORTED, "gemv: quant type %d has no decode kernel", w->qt);
     // FP4 weights: the block-scaled tensor-core kernel (gemv_fp4.cu) unless the call needs what only this kernel

@@ -1,0 +1,290 @@
+// The other GGUF block formats of the reference's CPU quant path — Q6_K, Q5_K, Q8_K (256 elements per block) and
+// Q4_0, Q5_0 (32 elements per block) — kept on the device exactly as the reference stores them: row after row of
+// blocks, no repacking.  One decode rule per format (an "item" = the elements one data byte, or byte group,
+// yields), used by the matrix decode / embedding gather and by a streaming GEMV: a warp owns a weight row,
+// brings it into shared memory in 16-byte loads, and accumulates in f32 on the CUDA cores.  The decode keeps
+// the reference's operation order (separately rounded products, no fused multiply-add), so decoded values are
+// bit-exact; the dot products add in a different order than the reference's sequential loop.
+//
+// Reference: src/macros/quant_primitive/k_quant.rs:92-101 (Q8_K), :381-436 (Q5_K), :441-472 (Q6_K);
+//            src/macros/quant_primitive/classic.rs:15-29 (Q4_0), :484-504 (Q5_0); block structs src/quant.rs:132-157, 254-275.
+#include "common.cuh"
+
+namespace gllmk {
+
+namespace {
+
+__device__ __forceinline__ float f16_at(const uint8_t *p) {
+    return __half2float(__ushort_as_half((unsigned short)(p[0] | (p[1] << 8))));
+}
+
+// get_scale_min_k4 of the K-quants (k_quant.rs:388-397): sub-block j's 6-bit scale and min
+__device__ __forceinline__ void scale_min_k4(int j, const uint8_t *s, float &sc, float &m) {
+    if (j < 4) {
+        sc = (float)(s[j] & 63);
+        m = (float)(s[j + 4] & 63);
+    } else {
+        sc = (float)((s[j + 4] & 0xF) | ((s[j - 4] >> 6) << 4));
+        m = (float)((s[j + 4] >> 4) | ((s[j] >> 6) << 4));
+    }
+}
+
+// Per format: BS elements and BB bytes per block, ITEMS work items per block, EPI elements per item.
+// item(b, it, v, e): decodes item `it` of the block at b into values v[] of elements e[] (indices in the block).
+template <int QT>
+struct Fmt;
+
+template <>
+struct Fmt<GLLMK_QUANT_Q6_K> {  // ql[128] @0, qh[64] @128, scales[16] i8 @192, d f16 @208
+    static constexpr int BS = 256, BB = 210, ITEMS = 64, EPI = 4;
+    static __device__ __forceinline__ void item(const uint8_t *b, int it, float *v, int *e) {
+        const int g = it >> 5, l = it & 31, is = l >> 4;
+        const uint8_t la = b[g * 64 + l], lb = b[g * 64 + l + 32], h = b[128 + g * 32 + l];
+        const int8_t *sc = reinterpret_cast<const int8_t *>(b + 192 + g * 8);
+        const float d = f16_at(b + 208);
+        const int q1 = (int)((la & 0xF) | (((h >> 0) & 3) << 4)) - 32;
+        const int q2 = (int)((lb & 0xF) | (((h >> 2) & 3) << 4)) - 32;
+        const int q3 = (int)((la >> 4) | (((h >> 4) & 3) << 4)) - 32;
+        const int q4 = (int)((lb >> 4) | (((h >> 6) & 3) << 4)) - 32;
+        v[0] = __fmul_rn(__fmul_rn(d, (float)sc[is]), (float)q1);
+        v[1] = __fmul_rn(__fmul_rn(d, (float)sc[is + 2]), (float)q2);
+        v[2] = __fmul_rn(__fmul_rn(d, (float)sc[is + 4]), (float)q3);
+        v[3] = __fmul_rn(__fmul_rn(d, (float)sc[is + 6]), (float)q4);
+        e[0] = g * 128 + l;
+        e[1] = e[0] + 32;
+        e[2] = e[0] + 64;
+        e[3] = e[0] + 96;
+    }
+};
+
+template <>
+struct Fmt<GLLMK_QUANT_Q5_K> {  // d @0, dmin @2, scales[12] @4, qh[32] @16, qs[128] @48
+    static constexpr int BS = 256, BB = 176, ITEMS = 128, EPI = 2;
+    static __device__ __forceinline__ void item(const uint8_t *b, int it, float *v, int *e) {
+        const int g = it >> 5, l = it & 31;
+        const float d = f16_at(b), mn = f16_at(b + 2);
+        float sc1, m1, sc2, m2;
+        scale_min_k4(2 * g, b + 4, sc1, m1);
+        scale_min_k4(2 * g + 1, b + 4, sc2, m2);
+        const uint8_t q = b[48 + g * 32 + l], h = b[16 + l];
+        const int v1 = (q & 0xF) + (((h >> (2 * g)) & 1) ? 16 : 0);
+        const int v2 = (q >> 4) + (((h >> (2 * g + 1)) & 1) ? 16 : 0);
+        v[0] = __fsub_rn(__fmul_rn(__fmul_rn(d, sc1), (float)v1), __fmul_rn(mn, m1));
+        v[1] = __fsub_rn(__fmul_rn(__fmul_rn(d, sc2), (float)v2), __fmul_rn(mn, m2));
+        e[0] = g * 64 + l;
+        e[1] = e[0] + 32;
+    }
+};
+
+template <>
+struct Fmt<GLLMK_QUANT_Q8_K> {  // d f32 @0, qs[256] i8 @4, bsums[16] i16 @260 (not used by decode)
+    static constexpr int BS = 256, BB = 292, ITEMS = 64, EPI = 4;
+    static __device__ __forceinline__ void item(const uint8_t *b, int it, float *v, int *e) {
+        const float d = __uint_as_float((uint32_t)b[0] | ((uint32_t)b[1] << 8) | ((uint32_t)b[2] << 16) | ((uint32_t)b[3] << 24));
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            // lanes take neighbouring bytes: element it + 64 j
+            e[j] = it + 64 * j;
+            v[j] = __fmul_rn(d, (float)(int8_t)b[4 + e[j]]);
+        }
+    }
+};
+
+template <>
+struct Fmt<GLLMK_QUANT_Q4_0> {  // d @0, qs[16] @2: byte j -> elements j (low nibble) and j + 16 (high nibble)
+    static constexpr int BS = 32, BB = 18, ITEMS = 16, EPI = 2;
+    static __device__ __forceinline__ void item(const uint8_t *b, int it, float *v, int *e) {
+        const float d = f16_at(b);
+        const uint8_t q = b[2 + it];
+        v[0] = __fmul_rn(d, __fsub_rn((float)(q & 0xF), 8.0f));
+        v[1] = __fmul_rn(d, __fsub_rn((float)(q >> 4), 8.0f));
+        e[0] = it;
+        e[1] = it + 16;
+    }
+};
+
+template <>
+struct Fmt<GLLMK_QUANT_Q5_0> {  // d @0, qh[4] @2 (bit j = fifth bit of element j), qs[16] @6
+    static constexpr int BS = 32, BB = 22, ITEMS = 16, EPI = 2;
+    static __device__ __forceinline__ void item(const uint8_t *b, int it, float *v, int *e) {
+        const float d = f16_at(b);
+        const uint32_t qh = (uint32_t)b[2] | ((uint32_t)b[3] << 8) | ((uint32_t)b[4] << 16) | ((uint32_t)b[5] << 24);
+        const uint8_t q = b[6 + it];
+        const uint32_t lo = (q & 0xF) | (((qh >> it) & 1u) << 4), hi = (q >> 4) | (((qh >> (it + 16)) & 1u) << 4);
+        v[0] = __fmul_rn(d, __fsub_rn((float)lo, 16.0f));
+        v[1] = __fmul_rn(d, __fsub_rn((float)hi, 16.0f));
+        e[0] = it;
+        e[1] = it + 16;
+    }
+};
+
+// ---- matrix decode / embedding gather: out[r, :] = decode(row ids ? ids[r] : r); rows outside [0, n) -> zeros ----
+template <int QT>
+__global__ void __launch_bounds__(256) raw_dequant_kernel(const uint8_t *__restrict__ w, int64_t n, int64_t nb,
+                                                          const int32_t *__restrict__ ids, float *__restrict__ out,
+                                                          size_t total) {
+    using F = Fmt<QT>;
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // (out row, block, item)
+    if (idx >= total) return;
+    const int it = (int)(idx % F::ITEMS);
+    const size_t rb = idx / F::ITEMS;
+    const int64_t blk = (int64_t)(rb % (size_t)nb), orow = (int64_t)(rb / (size_t)nb);
+    float *o = out + ((size_t)orow * nb + blk) * F::BS;
+    float v[F::EPI];
+    int e[F::EPI];
+    int64_t row = orow;
+    if (ids) row = ids[orow];
+    if (row < 0 || row >= n) {
+        F::item(w, it, v, e);  // element indices only (block 0 of the matrix always exists)
+#pragma unroll
+        for (int j = 0; j < F::EPI; j++) o[e[j]] = 0.0f;
+        return;
+    }
+    F::item(w + ((size_t)row * nb + blk) * F::BB, it, v, e);
+#pragma unroll
+    for (int j = 0; j < F::EPI; j++) o[e[j]] = v[j];
+}
+
+// ---- streaming GEMV --------------------------------------------------------------------------
+constexpr int RG_WARPS = 8;
+constexpr int RG_CHUNK = 4096;  // block bytes staged per warp and pass
+
+struct RawGemvParams {
+    const uint8_t *w;
+    const float *x;
+    float *y;
+    const float *row_scales;
+    int64_t n, nb, xst, xsk, yst, ysr, n_row_scales;
+    int m;
+};
+
+template <int QT, int MT>
+__global__ void __launch_bounds__(RG_WARPS * 32) raw_gemv_kernel(const RawGemvParams p) {
+    using F = Fmt<QT>;
+    constexpr int CB = RG_CHUNK / F::BB;  // whole blocks per pass
+    __shared__ __align__(16) uint8_t buf[RG_WARPS][RG_CHUNK + 32];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint8_t *mine = buf[warp];
+    for (int64_t row = (int64_t)blockIdx.x * RG_WARPS + warp; row < p.n; row += (int64_t)gridDim.x * RG_WARPS) {
+        const uint8_t *rowp = p.w + (size_t)row * p.nb * F::BB;
+        for (int t0 = 0; t0 < p.m; t0 += MT) {
+            float acc[MT];
+            const float *xt[MT];
+#pragma unroll
+            for (int t = 0; t < MT; t++) {
+                acc[t] = 0.0f;
+                const int tok = t0 + t < p.m ? t0 + t : p.m - 1;  // surplus slots repeat the last token; not stored
+                xt[t] = p.x + (size_t)tok * p.xst;
+            }
+            for (int64_t b0 = 0; b0 < p.nb; b0 += CB) {
+                const int nblk = (int)(p.nb - b0 < CB ? p.nb - b0 : CB);
+                const uint8_t *src = rowp + (size_t)b0 * F::BB;
+                // 16-byte loads from the aligned address below src: up to 15 bytes before the pass and after the
+                // row are read and ignored (the weight buffer starts 256-byte aligned and ends with 16 spare bytes)
+                const uintptr_t a0 = reinterpret_cast<uintptr_t>(src) & ~(uintptr_t)15;
+                const int off = (int)(reinterpret_cast<uintptr_t>(src) - a0);
+                const int n16 = (off + nblk * F::BB + 15) >> 4;
+                __syncwarp();
+                for (int i = lane; i < n16; i += 32)
+                    reinterpret_cast<uint4 *>(mine)[i] = __ldcs(reinterpret_cast<const uint4 *>(a0) + i);
+                __syncwarp();
+                const uint8_t *sb = mine + off;
+                for (int it = lane; it < nblk * F::ITEMS; it += 32) {
+                    const int blk = it / F::ITEMS;
+                    float v[F::EPI];
+                    int e[F::EPI];
+                    F::item(sb + blk * F::BB, it % F::ITEMS, v, e);
+                    const int64_t kb = (b0 + blk) * F::BS;
+#pragma unroll
+                    for (int j = 0; j < F::EPI; j++) {
+                        const size_t xo = (size_t)(kb + e[j]) * p.xsk;
+#pragma unroll
+                        for (int t = 0; t < MT; t++) acc[t] = fmaf(v[j], __ldg(xt[t] + xo), acc[t]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int t = 0; t < MT; t++) {
+                float a = acc[t];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+                if (lane == 0 && t0 + t < p.m) {
+                    if (p.n_row_scales == 1) a *= p.row_scales[0];
+                    else if (p.n_row_scales > 1) a *= p.row_scales[row];
+                    p.y[(size_t)(t0 + t) * p.yst + (size_t)row * p.ysr] = a;
+                }
+            }
+        }
+    }
+}
+
+inline unsigned grid_1d(size_t total, int block) { return (unsigned)((total + block - 1) / block); }
+
+template <int QT>
+int32_t dequant_t(Ctx *c, const uint8_t *w, int64_t n, int64_t nb, const int32_t *ids, size_t rows, float *out, cudaStream_t s) {
+    const size_t total = rows * (size_t)nb * Fmt<QT>::ITEMS;
+    if (total == 0) return GLLMK_STATUS_OK;
+    if (total > (size_t)0x7fffffff * 256) return fail(c, GLLMK_STATUS_INVALID_ARG, "decode: matrix too large for one launch");
+    raw_dequant_kernel<QT><<<grid_1d(total, 256), 256, 0, s>>>(w, n, nb, ids, out, total);
+    GK_CUDA(c, cudaGetLastError());
+    return GLLMK_STATUS_OK;
+}
+
+template <int QT>
+int32_t gemv_t(Ctx *c, const RawGemvParams &p, cudaStream_t s) {
+    // 8 rows per CTA and pass; enough CTAs to fill every SM several times over, never more than the rows need
+    int64_t ctas = (p.n + RG_WARPS - 1) / RG_WARPS;
+    const int64_t cap = (int64_t)c->sm_count * 6;
+    if (ctas > cap) ctas = cap;
+    if (p.m == 1) raw_gemv_kernel<QT, 1><<<(unsigned)ctas, RG_WARPS * 32, 0, s>>>(p);
+    else if (p.m <= 4) raw_gemv_kernel<QT, 4><<<(unsigned)ctas, RG_WARPS * 32, 0, s>>>(p);
+    else raw_gemv_kernel<QT, 8><<<(unsigned)ctas, RG_WARPS * 32, 0, s>>>(p);
+    GK_CUDA(c, cudaGetLastError());
+    return GLLMK_STATUS_OK;
+}
+
+}  // namespace
+
+bool raw_format(int32_t qt) {
+    return qt == GLLMK_QUANT_Q6_K || qt == GLLMK_QUANT_Q5_K || qt == GLLMK_QUANT_Q8_K || qt == GLLMK_QUANT_Q4_0 ||
+           qt == GLLMK_QUANT_Q5_0;
+}
+
+int32_t raw_dequant(Ctx *c, int32_t qt, const uint8_t *w, int64_t n, int64_t nb, const int32_t *ids, size_t rows, float *out,
+                    cudaStream_t s) {
+    switch (qt) {
+        case GLLMK_QUANT_Q6_K: return dequant_t<GLLMK_QUANT_Q6_K>(c, w, n, nb, ids, rows, out, s);
+        case GLLMK_QUANT_Q5_K: return dequant_t<GLLMK_QUANT_Q5_K>(c, w, n, nb, ids, rows, out, s);
+        case GLLMK_QUANT_Q8_K: return dequant_t<GLLMK_QUANT_Q8_K>(c, w, n, nb, ids, rows, out, s);
+        case GLLMK_QUANT_Q4_0: return dequant_t<GLLMK_QUANT_Q4_0>(c, w, n, nb, ids, rows, out, s);
+        case GLLMK_QUANT_Q5_0: return dequant_t<GLLMK_QUANT_Q5_0>(c, w, n, nb, ids, rows, out, s);
+    }
+    return fail(c, GLLMK_STATUS_UNSUPPORTED, "decode: quant type %d", qt);
+}
+
+int32_t raw_gemv_launch(Ctx *c, const Weight *w, const float *x, int64_t xst, int64_t xsk, int m, float *y, int64_t yst,
+                        int64_t ysr, const float *row_scales, int64_t n_row_scales, cudaStream_t s) {
+    RawGemvParams p{};
+    p.w = static_cast<const uint8_t *>(w->qs);
+    p.x = x;
+    p.y = y;
+    p.row_scales = row_scales;
+    p.n_row_scales = row_scales ? n_row_scales : 0;
+    p.n = w->n;
+    p.nb = w->nb;
+    p.xst = xst;
+    p.xsk = xsk;
+    p.yst = yst;
+    p.ysr = ysr;
+    p.m = m;
+    switch (w->qt) {
+        case GLLMK_QUANT_Q6_K: return gemv_t<GLLMK_QUANT_Q6_K>(c, p, s);
+        case GLLMK_QUANT_Q5_K: return gemv_t<GLLMK_QUANT_Q5_K>(c, p, s);
+        case GLLMK_QUANT_Q8_K: return gemv_t<GLLMK_QUANT_Q8_K>(c, p, s);
+        case GLLMK_QUANT_Q4_0: return gemv_t<GLLMK_QUANT_Q4_0>(c, p, s);
+        case GLLMK_QUANT_Q5_0: return gemv_t<GLLMK_QUANT_Q5_0>(c, p, s);
+    }
+    return fail(c, GLLMK_STATUS_UNSUPPORTED, "gemv: quant type %d", w->qt);
+}
+
+}  // namespace gllmk

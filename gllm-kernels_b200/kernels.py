@@ -373,6 +373,28 @@ class GpuKernels:
         self._check(lib().gllmk_dequant_nvfp4(self._ctx, _ptr(blocks), float(global_scale), _ptr(output),
                                               blocks.size // 36), "dequant_nvfp4")
 
+    def dequant_gguf(self, quant_type: QuantType, blocks, out) -> None:
+        """Kernels::dequant_q6_k / dequant_q5_k / dequant_q8_k / dequant_q4_0 / dequant_q5_0 (block, out)
+        (scalar decoders src/macros/quant_primitive/k_quant.rs:92-101,381-472, classic.rs:15-29,484-504)."""
+        blocks, out = _np(blocks, np.uint8), _np(out, np.float32, True)
+        self._check(lib().gllmk_dequant_gguf(self._ctx, quant_type.id, _ptr(blocks), _ptr(out),
+                                             blocks.size // quant_type.block_bytes()), "dequant_gguf")
+
+    def dequant_q6_k(self, block, out) -> None:
+        self.dequant_gguf(QuantType.q6k(), block, out)
+
+    def dequant_q5_k(self, block, out) -> None:
+        self.dequant_gguf(QuantType.q5k(), block, out)
+
+    def dequant_q8_k(self, block, out) -> None:
+        self.dequant_gguf(QuantType.q8k(), block, out)
+
+    def dequant_q4_0(self, block, out) -> None:
+        self.dequant_gguf(QuantType.q4_0(), block, out)
+
+    def dequant_q5_0(self, block, out) -> None:
+        self.dequant_gguf(QuantType.q5_0(), block, out)
+
     def kquant_matmul(self, weight_blocks, input, output, quant_type: QuantType, m: int, n: int, k: int) -> None:
         """Kernels::kquant_matmul (src/traits.rs:543-551): m weight rows, n batch columns, input [k, n],
         output [m, n]."""

@@ -50,7 +50,16 @@ enum {
     GLLMK_QUANT_Q8_0 = 2,  /* QuantType::Q8_0    32 el /  34 B  (src/quant.rs:290-293) */
     GLLMK_QUANT_MXFP4 = 3, /* QuantType::Mxfp4{block_size}      (src/quant.rs:66-76)   */
     GLLMK_QUANT_NVFP4 = 4, /* QuantType::Nvfp4   64 el /  36 B  (src/quant.rs:366-371) */
-    GLLMK_QUANT_INT8 = 5   /* plain s8 matrix of the W8A8 path (gllmk_int8_weight_upload); not a block format */
+    GLLMK_QUANT_INT8 = 5,  /* plain s8 matrix of the W8A8 path (gllmk_int8_weight_upload); not a block format */
+    /* The other GGUF formats of the reference's CPU quant path.  Kept on the device as the reference stores them
+     * and served by a streaming CUDA-core GEMV (f32 activations and outputs, any m) plus decode / gather /
+     * unpack; gllmk_gemm with bf16 operands, gllmk_gemm_grouped, gllmk_gemv_allgather and gllmk_ffn_decode
+     * answer GLLMK_STATUS_UNSUPPORTED for them. */
+    GLLMK_QUANT_Q6_K = 6,  /* QuantType::Q6K    256 el / 210 B  (src/quant.rs:143-148) */
+    GLLMK_QUANT_Q5_K = 7,  /* QuantType::Q5K    256 el / 176 B  (src/quant.rs:132-138) */
+    GLLMK_QUANT_Q4_0 = 8,  /* QuantType::Q4_0    32 el /  18 B  (src/quant.rs:254-257) */
+    GLLMK_QUANT_Q5_0 = 9,  /* QuantType::Q5_0    32 el /  22 B  (src/quant.rs:271-275) */
+    GLLMK_QUANT_Q8_K = 10  /* QuantType::Q8K    256 el / 292 B  (src/quant.rs:153-157) */
 };
 
 /* Element type of an activation / output matrix handed to gllmk_gemm. */
@@ -298,6 +307,11 @@ GLLMK_API int32_t gllmk_dequant_mxfp4(gllmk_ctx ctx, const uint8_t *blocks, cons
                             size_t num_blocks, size_t block_size);
 /* NVFP4 decode of `nblocks` 36-byte blocks, formula of src/quant.rs:77-86 (host pointers). */
 GLLMK_API int32_t gllmk_dequant_nvfp4(gllmk_ctx ctx, const uint8_t *blocks, float global_scale, float *out, size_t nblocks);
+/* Kernels::dequant_q6_k / dequant_q5_k / dequant_q8_k / dequant_q4_0 / dequant_q5_0 (src/traits.rs, the dequant_*
+ * family; scalar decoders src/macros/quant_primitive/k_quant.rs:92-101,381-472, classic.rs:15-29,484-504) behind one
+ * entry point: `quant_type` is one of GLLMK_QUANT_Q6_K .. GLLMK_QUANT_Q8_K (Q4_K and Q8_0 are accepted too);
+ * `nblocks` consecutive blocks -> nblocks*block_size f32, host pointers, bit-exact with the scalar decoders. */
+GLLMK_API int32_t gllmk_dequant_gguf(gllmk_ctx ctx, int32_t quant_type, const uint8_t *blocks, float *out, size_t nblocks);
 
 /* ---- on-device quantizers ------------------------------------------------------------------ */
 

@@ -76,7 +76,8 @@ API uint16_t gko_f32_to_f16(float f) {
  * Format metadata: src/quant.rs:375-456 (block_size / block_bytes) for the four formats of
  * the path.  Type ids are this boundary's own (the reference enum carries no discriminants).
  * ---------------------------------------------------------------------------------------- */
-enum { GKO_Q4K = 1, GKO_Q8_0 = 2, GKO_MXFP4 = 3, GKO_NVFP4 = 4 };
+enum { GKO_Q4K = 1, GKO_Q8_0 = 2, GKO_MXFP4 = 3, GKO_NVFP4 = 4,
+       GKO_Q6K = 6, GKO_Q5K = 7, GKO_Q4_0 = 8, GKO_Q5_0 = 9, GKO_Q8K = 10 };
 
 API int gko_block_size(int qt, int mx_block) {
     switch (qt) {
@@ -84,6 +85,8 @@ API int gko_block_size(int qt, int mx_block) {
         case GKO_Q8_0: return 32;
         case GKO_MXFP4: return mx_block;
         case GKO_NVFP4: return 64;  /* QK_NVFP4, src/quant.rs:92 */
+        case GKO_Q6K: case GKO_Q5K: case GKO_Q8K: return 256;
+        case GKO_Q4_0: case GKO_Q5_0: return 32;
     }
     return 0;
 }
@@ -93,6 +96,11 @@ API int gko_block_bytes(int qt, int mx_block) {
         case GKO_Q8_0: return 34;
         case GKO_MXFP4: return 1 + mx_block / 2; /* src/quant.rs:427 */
         case GKO_NVFP4: return 36;
+        case GKO_Q6K: return 210;   /* BlockQ6K, src/quant.rs:143-148 */
+        case GKO_Q5K: return 176;   /* BlockQ5K, src/quant.rs:132-138 */
+        case GKO_Q4_0: return 18;   /* BlockQ4_0, src/quant.rs:254-257 */
+        case GKO_Q5_0: return 22;   /* BlockQ5_0, src/quant.rs:271-275 */
+        case GKO_Q8K: return 292;   /* BlockQ8K, src/quant.rs:153-157 */
     }
     return 0;
 }
@@ -299,6 +307,185 @@ API void gko_dequant_nvfp4(const uint8_t *blocks, float global_scale, float *out
 }
 
 /* ------------------------------------------------------------------------------------------
+ * The other GGUF formats of the reference's CPU quant path.  Each decode / dot keeps the
+ * reference's operation order (products left to right, no fused multiply-add).
+ *
+ * Q6_K  decode src/macros/quant_primitive/k_quant.rs:441-472, dot :723-755.
+ *       Block: ql[128] @0, qh[64] @128, scales[16] (i8) @192, d f16 @208 (src/quant.rs:143-148).
+ * Q5_K  decode k_quant.rs:381-436, dot :669-721.
+ *       Block: d @0, dmin @2, scales[12] @4, qh[32] @16, qs[128] @48 (src/quant.rs:132-138).
+ * Q8_K  decode k_quant.rs:92-101, dot :549-561.  Block: d f32 @0, qs[256] i8 @4, bsums @260.
+ * Q4_0  decode/dot src/macros/quant_primitive/classic.rs:15-48.  Block: d @0, qs[16] @2.
+ * Q5_0  decode/dot classic.rs:484-526.  Block: d @0, qh[4] @2, qs[16] @6.
+ * ---------------------------------------------------------------------------------------- */
+static inline float rd_f16(const uint8_t *p) {
+    uint16_t h;
+    memcpy(&h, p, 2);
+    return gko_f16_to_f32(h);
+}
+
+API void gko_dequant_q6_k(const uint8_t *b, float *out) {
+    const uint8_t *ql = b, *qh = b + 128;
+    const int8_t *sc = (const int8_t *)(b + 192);
+    const float d = rd_f16(b + 208);
+    for (int g = 0; g < 2; g++) {
+        const int qlo = g * 64, qho = g * 32, so = g * 8, oo = g * 128;
+        for (int l = 0; l < 32; l++) {
+            const int is = l / 16;
+            const int q1 = (int)(int8_t)((ql[qlo + l] & 0xF) | (((qh[qho + l] >> 0) & 3) << 4)) - 32;
+            const int q2 = (int)(int8_t)((ql[qlo + l + 32] & 0xF) | (((qh[qho + l] >> 2) & 3) << 4)) - 32;
+            const int q3 = (int)(int8_t)((ql[qlo + l] >> 4) | (((qh[qho + l] >> 4) & 3) << 4)) - 32;
+            const int q4 = (int)(int8_t)((ql[qlo + l + 32] >> 4) | (((qh[qho + l] >> 6) & 3) << 4)) - 32;
+            out[oo + l] = d * (float)sc[so + is] * (float)q1;
+            out[oo + l + 32] = d * (float)sc[so + is + 2] * (float)q2;
+            out[oo + l + 64] = d * (float)sc[so + is + 4] * (float)q3;
+            out[oo + l + 96] = d * (float)sc[so + is + 6] * (float)q4;
+        }
+    }
+}
+static float dot_q6_k(const uint8_t *b, const float *x) {
+    const uint8_t *ql = b, *qh = b + 128;
+    const int8_t *sc = (const int8_t *)(b + 192);
+    const float d = rd_f16(b + 208);
+    float sum = 0.0f;
+    for (int g = 0; g < 2; g++) {
+        const int qlo = g * 64, qho = g * 32, so = g * 8, oo = g * 128;
+        for (int l = 0; l < 32; l++) {
+            const int is = l / 16;
+            const int q1 = (int)(int8_t)((ql[qlo + l] & 0xF) | (((qh[qho + l] >> 0) & 3) << 4)) - 32;
+            const int q2 = (int)(int8_t)((ql[qlo + l + 32] & 0xF) | (((qh[qho + l] >> 2) & 3) << 4)) - 32;
+            const int q3 = (int)(int8_t)((ql[qlo + l] >> 4) | (((qh[qho + l] >> 4) & 3) << 4)) - 32;
+            const int q4 = (int)(int8_t)((ql[qlo + l + 32] >> 4) | (((qh[qho + l] >> 6) & 3) << 4)) - 32;
+            sum += d * (float)sc[so + is] * (float)q1 * x[oo + l];
+            sum += d * (float)sc[so + is + 2] * (float)q2 * x[oo + l + 32];
+            sum += d * (float)sc[so + is + 4] * (float)q3 * x[oo + l + 64];
+            sum += d * (float)sc[so + is + 6] * (float)q4 * x[oo + l + 96];
+        }
+    }
+    return sum;
+}
+
+API void gko_dequant_q5_k(const uint8_t *b, float *out) {
+    const float d = rd_f16(b), min = rd_f16(b + 2);
+    const uint8_t *scales = b + 4, *qh = b + 16, *ql = b + 48;
+    int is = 0;
+    uint8_t u1 = 1, u2 = 2;
+    for (int g = 0; g < 4; g++) {
+        float sc1, m1, sc2, m2;
+        get_scale_min_k4(is, scales, &sc1, &m1);
+        get_scale_min_k4(is + 1, scales, &sc2, &m2);
+        const float d1 = d * sc1, nm1 = min * m1, d2 = d * sc2, nm2 = min * m2;
+        for (int l = 0; l < 32; l++) {
+            const int v = (ql[g * 32 + l] & 0xF) + ((qh[l] & u1) ? 16 : 0);
+            out[g * 64 + l] = d1 * (float)v - nm1;
+        }
+        for (int l = 0; l < 32; l++) {
+            const int v = (ql[g * 32 + l] >> 4) + ((qh[l] & u2) ? 16 : 0);
+            out[g * 64 + 32 + l] = d2 * (float)v - nm2;
+        }
+        is += 2;
+        u1 <<= 2;
+        u2 <<= 2;
+    }
+}
+static float dot_q5_k(const uint8_t *b, const float *x) {
+    const float d = rd_f16(b), min = rd_f16(b + 2);
+    const uint8_t *scales = b + 4, *qh = b + 16, *ql = b + 48;
+    int is = 0;
+    uint8_t u1 = 1, u2 = 2;
+    float sum = 0.0f;
+    for (int g = 0; g < 4; g++) {
+        float sc1, m1, sc2, m2;
+        get_scale_min_k4(is, scales, &sc1, &m1);
+        get_scale_min_k4(is + 1, scales, &sc2, &m2);
+        const float d1 = d * sc1, nm1 = min * m1, d2 = d * sc2, nm2 = min * m2;
+        for (int l = 0; l < 32; l++) {
+            const int v = (ql[g * 32 + l] & 0xF) + ((qh[l] & u1) ? 16 : 0);
+            sum += (d1 * (float)v - nm1) * x[g * 64 + l];
+        }
+        for (int l = 0; l < 32; l++) {
+            const int v = (ql[g * 32 + l] >> 4) + ((qh[l] & u2) ? 16 : 0);
+            sum += (d2 * (float)v - nm2) * x[g * 64 + 32 + l];
+        }
+        is += 2;
+        u1 <<= 2;
+        u2 <<= 2;
+    }
+    return sum;
+}
+
+API void gko_dequant_q8_k(const uint8_t *b, float *out) {
+    float d;
+    memcpy(&d, b, 4);
+    const int8_t *qs = (const int8_t *)(b + 4);
+    for (int i = 0; i < 256; i++) out[i] = d * (float)qs[i];
+}
+static float dot_q8_k(const uint8_t *b, const float *x) {
+    float d;
+    memcpy(&d, b, 4);
+    const int8_t *qs = (const int8_t *)(b + 4);
+    float sum = 0.0f;
+    for (int i = 0; i < 256; i++) sum += (d * (float)qs[i]) * x[i];
+    return sum;
+}
+
+API void gko_dequant_q4_0(const uint8_t *b, float *out) {
+    const float d = rd_f16(b);
+    for (int j = 0; j < 16; j++) {
+        const float lo = (float)(b[2 + j] & 0x0F), hi = (float)(b[2 + j] >> 4);
+        out[j] = d * (lo - 8.0f);
+        out[j + 16] = d * (hi - 8.0f);
+    }
+}
+static float dot_q4_0(const uint8_t *b, const float *x) {
+    const float d = rd_f16(b);
+    float sum = 0.0f;
+    for (int j = 0; j < 16; j++) {
+        const float lo = (float)(b[2 + j] & 0x0F), hi = (float)(b[2 + j] >> 4);
+        sum += d * (lo - 8.0f) * x[j];
+        sum += d * (hi - 8.0f) * x[j + 16];
+    }
+    return sum;
+}
+
+API void gko_dequant_q5_0(const uint8_t *b, float *out) {
+    const float d = rd_f16(b);
+    const uint32_t qh = (uint32_t)b[2] | ((uint32_t)b[3] << 8) | ((uint32_t)b[4] << 16) | ((uint32_t)b[5] << 24);
+    for (int j = 0; j < 16; j++) {
+        const uint32_t lo = b[6 + j] & 0x0F, hi = b[6 + j] >> 4;
+        const uint32_t bl = ((qh >> j) & 1) << 4, bh = ((qh >> (j + 16)) & 1) << 4;
+        out[j] = d * ((float)(lo | bl) - 16.0f);
+        out[j + 16] = d * ((float)(hi | bh) - 16.0f);
+    }
+}
+static float dot_q5_0(const uint8_t *b, const float *x) {
+    const float d = rd_f16(b);
+    const uint32_t qh = (uint32_t)b[2] | ((uint32_t)b[3] << 8) | ((uint32_t)b[4] << 16) | ((uint32_t)b[5] << 24);
+    float sum = 0.0f;
+    for (int j = 0; j < 16; j++) {
+        const uint32_t lo = b[6 + j] & 0x0F, hi = b[6 + j] >> 4;
+        const uint32_t bl = ((qh >> j) & 1) << 4, bh = ((qh >> (j + 16)) & 1) << 4;
+        sum += d * ((float)(lo | bl) - 16.0f) * x[j];
+        sum += d * ((float)(hi | bh) - 16.0f) * x[j + 16];
+    }
+    return sum;
+}
+
+/* one block of any GGUF format handled above -> block_size floats; 0 on success */
+API int gko_dequant_block(int qt, const uint8_t *b, float *out) {
+    switch (qt) {
+        case GKO_Q4K: gko_dequant_q4_k(b, out); return 0;
+        case GKO_Q8_0: gko_dequant_q8_0(b, out); return 0;
+        case GKO_Q6K: gko_dequant_q6_k(b, out); return 0;
+        case GKO_Q5K: gko_dequant_q5_k(b, out); return 0;
+        case GKO_Q8K: gko_dequant_q8_k(b, out); return 0;
+        case GKO_Q4_0: gko_dequant_q4_0(b, out); return 0;
+        case GKO_Q5_0: gko_dequant_q5_0(b, out); return 0;
+    }
+    return -5;
+}
+
+/* ------------------------------------------------------------------------------------------
  * Matmul drivers.
  *
  * quant_matmul_inner, src/cpu_kernels/mod.rs:443-486: weight rows = m, batch columns = n,
@@ -337,6 +524,11 @@ static int quant_matmul(const uint8_t *w, const float *input, float *out, int qt
     dot_fn dot;
     if (qt == GKO_Q4K) { bb = 144; bs = 256; dot = dot_q4_k; }
     else if (qt == GKO_Q8_0) { bb = 34; bs = 32; dot = dot_q8_0; }
+    else if (qt == GKO_Q6K) { bb = 210; bs = 256; dot = dot_q6_k; }
+    else if (qt == GKO_Q5K) { bb = 176; bs = 256; dot = dot_q5_k; }
+    else if (qt == GKO_Q8K) { bb = 292; bs = 256; dot = dot_q8_k; }
+    else if (qt == GKO_Q4_0) { bb = 18; bs = 32; dot = dot_q4_0; }
+    else if (qt == GKO_Q5_0) { bb = 22; bs = 32; dot = dot_q5_0; }
     else return -5;
     if (k % bs) return -1;
     float *xt = (float *)malloc(sizeof(float) * k * n);
@@ -438,6 +630,10 @@ API int gko_dequant_matrix(int qt, const uint8_t *blocks, const uint8_t *scales,
     } else if (qt == GKO_NVFP4) {
         if (k % 64) return -1;
         gko_dequant_nvfp4(blocks, global, out, n * (k / 64));
+    } else if (qt == GKO_Q6K || qt == GKO_Q5K || qt == GKO_Q8K || qt == GKO_Q4_0 || qt == GKO_Q5_0) {
+        const size_t bs = (size_t)gko_block_size(qt, 0), bb = (size_t)gko_block_bytes(qt, 0);
+        if (k % bs) return -1;
+        for (size_t b = 0; b < n * (k / bs); b++) gko_dequant_block(qt, blocks + b * bb, out + b * bs);
     } else return -5;
     return 0;
 }

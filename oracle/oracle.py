@@ -14,6 +14,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 
 Q4K, Q8_0, MXFP4, NVFP4 = 1, 2, 3, 4
+Q6K, Q5K, Q4_0, Q5_0, Q8K = 6, 7, 8, 9, 10
 
 
 def build(force: bool = False) -> None:
@@ -48,6 +49,7 @@ def _load(name: str) -> C.CDLL:
         "gko_dot_q4_k": (C.c_float, [_u8p, _f32p]),
         "gko_q4k_element": (C.c_float, [_u8p, C.c_int]),
         "gko_dequant_q8_0": (None, [_u8p, _f32p]),
+        "gko_dequant_block": (C.c_int, [C.c_int, _u8p, _f32p]),
         "gko_dot_q8_0": (C.c_float, [_u8p, _f32p]),
         "gko_e2m1": (C.c_float, [C.c_int]),
         "gko_decode_e8m0_scale": (C.c_float, [C.c_uint8]),
@@ -112,6 +114,17 @@ def dequant_q8_0(block) -> np.ndarray:
     assert block.size == 34
     out = np.empty(32, np.float32)
     lib().gko_dequant_q8_0(_p(block, _u8p), _p(out, _f32p))
+    return out
+
+
+def dequant_block(qt: int, block) -> np.ndarray:
+    """One block of a GGUF format (Q4_K, Q8_0, Q6_K, Q5_K, Q8_K, Q4_0, Q5_0) -> block_size floats."""
+    block = _u8(block)
+    assert block.size == lib().gko_block_bytes(qt, 0)
+    out = np.empty(lib().gko_block_size(qt, 0), np.float32)
+    rc = lib().gko_dequant_block(qt, _p(block, _u8p), _p(out, _f32p))
+    if rc:
+        raise ValueError(f"gko_dequant_block: {rc}")
     return out
 
 

@@ -172,6 +172,102 @@ cases["metadata"] = {
     "q4k": [256, 144], "q8_0": [32, 34], "mxfp4_32": [32, 17], "nvfp4": [64, 36],
 }
 
+# ---- the other GGUF formats of the reference's CPU quant path -------------------------------
+# block layouts: src/quant.rs:132-157 (Q5_K, Q6_K, Q8_K), :254-275 (Q4_0, Q5_0)
+
+
+def q4_0_block(d, qs_fill=0x88, qs=None) -> list:
+    b = bytearray(18)
+    b[0:2] = f16(d)
+    b[2:18] = bytes([qs_fill] * 16)
+    for i, v in (qs or {}).items():
+        b[2 + i] = v
+    return list(b)
+
+
+def q5_0_block(d, qh=None, qs=None) -> list:
+    b = bytearray(22)
+    b[0:2] = f16(d)
+    for i, v in (qh or {}).items():
+        b[2 + i] = v
+    for i, v in (qs or {}).items():
+        b[6 + i] = v
+    return list(b)
+
+
+def q8_k_block(d, qs) -> list:
+    b = bytearray(292)
+    b[0:4] = struct.pack("<f", d)
+    for i, v in qs.items():
+        b[4 + i] = v & 0xFF
+    return list(b)
+
+
+# src/tests_quant.rs:46-61  test_dequant_q8_k
+cases["q8_k_decode"] = {"cite": "src/tests_quant.rs:46-61", "qt": "q8_k",
+                        "block": q8_k_block(2.0, {0: 10, 1: -5}), "expect": {"0": 20.0, "1": -10.0}}
+
+# src/tests_quant.rs:122-149  test_dequant_q5_k   (d @0, dmin @2, scales @4, qh @16, qs @48)
+blk = bytearray(176)
+blk[0:2] = f16(1.0)
+blk[4] = 1
+blk[48] = 0x0F
+blk[16] = 0x01
+blk[49] = 0x0F
+blk[17] = 0x01
+cases["q5_k_decode"] = {"cite": "src/tests_quant.rs:122-149", "qt": "q5_k", "block": list(blk),
+                        "expect": {"0": 31.0, "1": 31.0}}
+
+# src/tests_quant.rs:152-174  test_dequant_q6_k   (ql @0, qh @128, scales @192, d @208)
+blk = bytearray(210)
+blk[208:210] = f16(1.0)
+blk[192] = 1
+blk[0] = 0x0F
+blk[128] = 0x03
+cases["q6_k_decode"] = {"cite": "src/tests_quant.rs:152-174", "qt": "q6_k", "block": list(blk), "expect": {"0": 31.0}}
+
+# src/tests_quant.rs:233-246  test_dequant_q4_0_zero
+cases["q4_0_decode_zero"] = {"cite": "src/tests_quant.rs:233-246", "qt": "q4_0", "block": q4_0_block(1.0),
+                             "expect_all": [0.0] * 32}
+# src/tests_quant.rs:249-279  test_dequant_q4_0_known_values
+exp = [0.0] * 32
+exp[0], exp[1], exp[16], exp[17] = -3.0, 1.0, -3.5, 3.5
+cases["q4_0_decode_known"] = {"cite": "src/tests_quant.rs:249-279", "qt": "q4_0",
+                              "block": q4_0_block(0.5, qs={0: 0x12, 1: 0xFA}), "expect_all": exp}
+# src/tests_quant.rs:282-320  test_dequant_q4_0_full_range
+cases["q4_0_decode_full_range"] = {
+    "cite": "src/tests_quant.rs:282-320", "qt": "q4_0",
+    "block": q4_0_block(2.0, 0, {j: j | ((15 - j) << 4) for j in range(16)}),
+    "expect_all": [2.0 * (j - 8.0) for j in range(16)] + [2.0 * ((15 - j) - 8.0) for j in range(16)],
+}
+# src/tests_quant.rs:364-387  test_dequant_q5_0 ; :390-408 test_dequant_q5_0_all_bits
+cases["q5_0_decode"] = {"cite": "src/tests_quant.rs:364-387", "qt": "q5_0",
+                        "block": q5_0_block(1.0, {0: 0x01}, {0: 0x0F}), "expect": {"0": 15.0, "16": -16.0}}
+cases["q5_0_decode_all_bits"] = {"cite": "src/tests_quant.rs:390-408", "qt": "q5_0",
+                                 "block": q5_0_block(0.5, {1: 0x01}, {8: 0x07}), "expect": {"8": 3.5}}
+
+# matmul known answers (reference layout: weight rows m, batch columns n, input [k, n], output [m, n])
+inp = [0.0] * 32
+inp[0], inp[1] = 3.0, 4.0
+# src/tests_quant.rs:508-539  test_dot_q4_0.  The test's comment takes the high nibble of byte 0 as element 1;
+# the decoder puts it at element 16, where the input is 0: the product is 2*3 = 6 and the test's own
+# tolerance check (|out - 10| < 1e-2) would not hold for the scalar decoder.  Recorded with the decoder's value.
+cases["q4_0_dot"] = {"cite": "src/tests_quant.rs:508-539", "qt": "q4_0", "weight": q4_0_block(1.0, qs={0: 0x9A}),
+                     "input": inp, "m": 1, "n": 1, "k": 32, "expect": [6.0], "note": "decoder value; see generator"}
+inp = [0.0] * 32
+inp[0] = 2.0
+# src/tests_quant.rs:577-607  test_dot_q5_0
+cases["q5_0_dot"] = {"cite": "src/tests_quant.rs:577-607", "qt": "q5_0",
+                     "weight": q5_0_block(1.0, {0: 0x01}, {0: 0x05}), "input": inp, "m": 1, "n": 1, "k": 32, "expect": [10.0]}
+# src/tests_fragments/part1.inc.rs:1011-1024  test_kquant_matmul_q8_k
+cases["q8_k_matmul"] = {"cite": "src/tests_fragments/part1.inc.rs:1011-1024", "qt": "q8_k",
+                        "weight": q8_k_block(1.0, {i: 1 for i in range(256)}), "input": [1.0] * 256,
+                        "m": 1, "n": 1, "k": 256, "expect": [256.0]}
+
+# src/quant.rs:375-456 block_size / block_bytes
+cases["metadata_gguf"] = {"cite": "src/quant.rs:375-456",
+                          "q6_k": [256, 210], "q5_k": [256, 176], "q8_k": [256, 292], "q4_0": [32, 18], "q5_0": [32, 22]}
+
 with open(os.path.join(HERE, "reference_known_answers.json"), "w") as f:
     json.dump(cases, f, indent=0)
 print("wrote", len(cases), "groups")

@@ -1,0 +1,199 @@
+"""Parity of the Q6_K / Q5_K / Q8_K / Q4_0 / Q5_0 path (through the C ABI) with the CPU oracle.  Needs a B200.
+
+Bars: decoded values, unpack round trip, gathers — bit-exact.  GEMV / matmul outputs —
+max_i |y_i - ref_i| / max(|ref_i|, rms(ref)) <= 2e-3 against the oracle's sequential f32 sum.
+"""
+import json
+import os
+import struct
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+TOL = 2e-3
+HERE = os.path.dirname(os.path.abspath(__file__))
+with open(os.path.join(HERE, "golden", "reference_known_answers.json")) as f:
+    KA = json.load(f)
+
+FORMATS = ["q6_k", "q5_k", "q8_k", "q4_0", "q5_0"]
+
+
+@pytest.fixture(scope="module")
+def K(gk):
+    k = gk.GpuKernels(0)
+    yield k
+    k.close()
+
+
+@pytest.fixture(scope="module")
+def torch():
+    import torch as t
+    assert t.cuda.is_available()
+    return t
+
+
+def qtype(gk, name):
+    Q = gk.QuantType
+    return {"q6_k": Q.q6k(), "q5_k": Q.q5k(), "q8_k": Q.q8k(), "q4_0": Q.q4_0(), "q5_0": Q.q5_0()}[name]
+
+
+def same_bits(a, b):
+    a = np.ascontiguousarray(a, np.float32).reshape(-1)
+    b = np.ascontiguousarray(b, np.float32).reshape(-1)
+    return bool((a.view(np.uint32) == b.view(np.uint32)).all())
+
+
+def random_blocks(name, qt, n, k, seed):
+    """n rows of k / block_size blocks: random payload bytes, small finite scales (both signs)."""
+    rng = np.random.default_rng(seed)
+    bs, bb = qt.block_size(), qt.block_bytes()
+    nblk = n * (k // bs)
+    v = rng.integers(0, 256, size=(nblk, bb), dtype=np.uint8)
+    if name == "q8_k":
+        v[:, 0:4] = np.frombuffer(rng.uniform(-0.02, 0.02, nblk).astype(np.float32).tobytes(), np.uint8).reshape(-1, 4)
+    else:
+        d = np.frombuffer(rng.uniform(-0.02, 0.02, nblk).astype(np.float16).tobytes(), np.uint8).reshape(-1, 2)
+        if name == "q6_k":
+            v[:, 208:210] = d
+        else:
+            v[:, 0:2] = d
+        if name == "q5_k":
+            v[:, 2:4] = np.frombuffer(rng.uniform(-0.02, 0.02, nblk).astype(np.float16).tobytes(), np.uint8).reshape(-1, 2)
+    return v.reshape(-1)
+
+
+def oracle_matrix(oracle, qt, blocks, n, k):
+    return oracle.dequant_matrix(qt.id, blocks, n, k)
+
+
+@pytest.mark.parametrize("name", FORMATS)
+def test_decode_unpack_gather_bit_exact(K, gk, oracle, torch, name):
+    qt = qtype(gk, name)
+    n, k = 37, 3 * 256  # ragged row count; row byte lengths that are not multiples of 16
+    blocks = random_blocks(name, qt, n, k, 11)
+    ref = oracle_matrix(oracle, qt, blocks, n, k)
+    w = K.upload(qt, n, k, blocks)
+    assert w.ref_bytes() == blocks.size
+    assert same_bits(K.dequant(w).cpu().numpy(), ref)
+    assert np.array_equal(np.asarray(K.unpack(w)).reshape(-1), blocks)
+    ids = torch.tensor([3, 36, -1, 0, 37, 3], dtype=torch.int32, device="cuda")
+    got = K.embedding_gather(w, ids).cpu().numpy()
+    want = np.stack([ref[i] if 0 <= i < n else np.zeros(k, np.float32) for i in ids.cpu().tolist()])
+    assert same_bits(got, want)
+    # host-pointer decode of a run of blocks
+    out = np.empty(n * k, np.float32)
+    K.dequant_gguf(qt, blocks, out)
+    assert same_bits(out, ref)
+    w.free()
+
+
+@pytest.mark.parametrize("name", ["q8_k_decode", "q5_k_decode", "q6_k_decode", "q4_0_decode_zero", "q4_0_decode_known",
+                                  "q4_0_decode_full_range", "q5_0_decode", "q5_0_decode_all_bits"])
+def test_decode_known_answers(K, gk, name):
+    c = KA[name]
+    qt = qtype(gk, c["qt"])
+    out = np.empty(qt.block_size(), np.float32)
+    getattr(K, "dequant_" + c["qt"])(np.array(c["block"], np.uint8), out)
+    if "expect_all" in c:
+        assert out.tolist() == c["expect_all"]
+    for i, v in c.get("expect", {}).items():
+        assert out[int(i)] == v
+
+
+@pytest.mark.parametrize("name", ["q4_0_dot", "q5_0_dot", "q8_k_matmul"])
+def test_matmul_known_answers(K, gk, name):
+    c = KA[name]
+    qt = qtype(gk, c["qt"])
+    out = np.zeros(c["m"] * c["n"], np.float32)
+    fn = K.kquant_matmul if qt.block_size() == 256 else K.classic_matmul
+    fn(np.array(c["weight"], np.uint8), np.array(c["input"], np.float32), out, qt, c["m"], c["n"], c["k"])
+    assert out.tolist() == c["expect"]
+
+
+@pytest.mark.parametrize("name", FORMATS)
+@pytest.mark.parametrize("m", [1, 3, 8, 16])
+def test_gemv_parity(K, gk, oracle, torch, name, m):
+    qt = qtype(gk, name)
+    n, k = 203, 8 * 256  # rows not a multiple of the 8 a CTA takes per pass
+    blocks = random_blocks(name, qt, n, k, 100 + m)
+    rng = np.random.default_rng(7 + m)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    ref = oracle.quant_matmul(blocks, np.ascontiguousarray(x.T), qt.id, n, m, k, threads=4)  # [n, m]
+    w = K.upload(qt, n, k, blocks)
+    y = K.gemv(w, torch.from_numpy(x).cuda()).cpu().numpy()  # [m, n]
+    assert oracle.rel_err(y.T, ref) <= TOL
+    # reference layout (x [k, m] -> y [n, m]) reads the same tensors through strides
+    y2 = K.gemv(w, torch.from_numpy(np.ascontiguousarray(x.T)).cuda(), ref_layout=True).cpu().numpy()
+    assert oracle.rel_err(y2, ref) <= TOL
+    assert K.status() == 0
+    w.free()
+
+
+@pytest.mark.parametrize("name", ["q6_k", "q4_0"])
+def test_gemv_long_rows_and_row_scales(K, gk, oracle, torch, name):
+    """k large enough for several staging passes per row (a pass holds 4 KB of blocks); per-row scales."""
+    qt = qtype(gk, name)
+    n, k = 64, 40 * 256
+    blocks = random_blocks(name, qt, n, k, 5)
+    rng = np.random.default_rng(6)
+    x = rng.standard_normal((1, k)).astype(np.float32)
+    sc = rng.uniform(0.5, 2.0, n).astype(np.float32)
+    ref = oracle.quant_matmul(blocks, np.ascontiguousarray(x.T), qt.id, n, 1, k, threads=4) * sc[:, None]
+    w = K.upload(qt, n, k, blocks)
+    y = K.gemv(w, torch.from_numpy(x).cuda(), row_scales=torch.from_numpy(sc).cuda()).cpu().numpy()
+    assert oracle.rel_err(y.T, ref) <= TOL
+    w.free()
+
+
+@pytest.mark.parametrize("name", ["q6_k", "q5_0"])
+def test_gemm_many_tokens_f32(K, gk, oracle, torch, name):
+    """gllmk_gemm with these formats runs the streaming kernel over token tiles; bf16 operands are refused."""
+    qt = qtype(gk, name)
+    n, k, m = 96, 512, 70
+    blocks = random_blocks(name, qt, n, k, 21)
+    x = np.random.default_rng(22).standard_normal((m, k)).astype(np.float32)
+    ref = oracle.quant_matmul(blocks, np.ascontiguousarray(x.T), qt.id, n, m, k, threads=4)
+    w = K.upload(qt, n, k, blocks)
+    y = K.gemm(w, torch.from_numpy(x).cuda()).cpu().numpy()
+    assert oracle.rel_err(y.T, ref) <= TOL
+    with pytest.raises(gk.GllmkError):
+        K.gemm(w, torch.from_numpy(x).cuda().to(torch.bfloat16))
+    w.free()
+
+
+@pytest.mark.parametrize("name", FORMATS)
+def test_family_matmul_host(K, gk, oracle, name):
+    """kquant_matmul / classic_matmul with host arrays: m weight rows, n batch columns, input [k, n], output [m, n]."""
+    qt = qtype(gk, name)
+    m, n, k = 50, 5, 2 * 256
+    blocks = random_blocks(name, qt, m, k, 31)
+    x = np.random.default_rng(32).standard_normal((k, n)).astype(np.float32)
+    ref = oracle.quant_matmul(blocks, x, qt.id, m, n, k)
+    out = np.empty((m, n), np.float32)
+    fn = K.kquant_matmul if qt.block_size() == 256 else K.classic_matmul
+    fn(blocks, x, out, qt, m, n, k)
+    assert oracle.rel_err(out, ref) <= TOL
+    wrong = K.classic_matmul if qt.block_size() == 256 else K.kquant_matmul
+    with pytest.raises(gk.GllmkError):  # the reference panics for a format of the other family
+        wrong(blocks, x, out, qt, m, n, k)
+
+
+def test_linearity_large(K, gk, torch):
+    """Size-independent property at a decode-sized Q6_K matrix: W(a x1 + b x2) = a W x1 + b W x2 to rounding."""
+    qt = qtype(gk, "q6_k")
+    n, k = 4096, 4096
+    blocks = random_blocks("q6_k", qt, n, k, 41)
+    w = K.upload(qt, n, k, blocks)
+    g = torch.Generator(device="cuda").manual_seed(1)
+    x1 = torch.randn(1, k, device="cuda", generator=g)
+    x2 = torch.randn(1, k, device="cuda", generator=g)
+    y = K.gemv(w, 0.5 * x1 - 2.0 * x2)
+    y12 = 0.5 * K.gemv(w, x1) - 2.0 * K.gemv(w, x2)
+    den = max(float(y12.abs().max()), 1e-6)
+    assert float((y - y12).abs().max()) / den <= 1e-4
+    # and against the f64 product with the decoded matrix
+    ref = (K.dequant(w).double() @ x1.double().T).T
+    assert float((K.gemv(w, x1).double() - ref).abs().max()) / float(ref.abs().max()) <= 1e-4
+    w.free()

@@ -125,3 +125,61 @@ def test_e4m3_codec_against_torch(oracle):
                 assert L.gko_f32_to_e4m3(float(ref[b])) == b
     assert L.gko_f32_to_e4m3(1000.0) == 0x7E  # saturates to 448
     assert L.gko_e4m3_to_f32(0x7E) == 448.0
+
+
+# ---- the other GGUF formats (Q6_K, Q5_K, Q8_K, Q4_0, Q5_0) ------------------------------------
+def _qt(oracle, name):
+    return {"q6_k": oracle.Q6K, "q5_k": oracle.Q5K, "q8_k": oracle.Q8K, "q4_0": oracle.Q4_0, "q5_0": oracle.Q5_0}[name]
+
+
+GGUF_DECODE_CASES = ["q8_k_decode", "q5_k_decode", "q6_k_decode", "q4_0_decode_zero", "q4_0_decode_known",
+                     "q4_0_decode_full_range", "q5_0_decode", "q5_0_decode_all_bits"]
+
+
+@pytest.mark.parametrize("name", GGUF_DECODE_CASES)
+def test_gguf_decode_known_answers(oracle, name):
+    c = KA[name]
+    out = oracle.dequant_block(_qt(oracle, c["qt"]), c["block"])
+    if "expect_all" in c:
+        assert out.tolist() == c["expect_all"]
+    for i, v in c.get("expect", {}).items():
+        assert out[int(i)] == v
+
+
+@pytest.mark.parametrize("name", ["q4_0_dot", "q5_0_dot", "q8_k_matmul"])
+def test_gguf_matmul_known_answers(oracle, name):
+    c = KA[name]
+    out = oracle.quant_matmul(c["weight"], c["input"], _qt(oracle, c["qt"]), c["m"], c["n"], c["k"])
+    assert out.reshape(-1).tolist() == c["expect"]
+
+
+def test_gguf_metadata(oracle):
+    c = KA["metadata_gguf"]
+    for name in ("q6_k", "q5_k", "q8_k", "q4_0", "q5_0"):
+        qt = _qt(oracle, name)
+        assert [oracle.lib().gko_block_size(qt, 0), oracle.lib().gko_block_bytes(qt, 0)] == c[name]
+
+
+@pytest.mark.parametrize("name", ["q6_k", "q5_k", "q8_k", "q4_0", "q5_0"])
+def test_gguf_dot_is_decode_then_dot(oracle, name):
+    """The block dot of each format equals the f32 dot with its own decode, term by term in element order
+    (Q6_K and Q5_K visit elements in the order of their decode loops), so both agree to rounding."""
+    qt = _qt(oracle, name)
+    bs, bb = oracle.lib().gko_block_size(qt, 0), oracle.lib().gko_block_bytes(qt, 0)
+    rng = np.random.default_rng(5)
+    nb = 4
+    w = rng.integers(0, 256, size=(nb, bb), dtype=np.uint8)
+    for b in range(nb):  # finite scales
+        if name == "q8_k":
+            w[b, 0:4] = np.frombuffer(struct.pack("<f", 0.01 * (b + 1)), np.uint8)
+        elif name == "q6_k":
+            w[b, 208:210] = np.frombuffer(struct.pack("<e", 0.01 * (b + 1)), np.uint8)
+        else:
+            w[b, 0:2] = np.frombuffer(struct.pack("<e", 0.01 * (b + 1)), np.uint8)
+            if name == "q5_k":
+                w[b, 2:4] = np.frombuffer(struct.pack("<e", 0.02), np.uint8)
+    x = rng.standard_normal(nb * bs).astype(np.float32)
+    y = oracle.quant_matmul(w.reshape(-1), x, qt, 1, 1, nb * bs)
+    dec = np.concatenate([oracle.dequant_block(qt, w[b]) for b in range(nb)])
+    ref = float(np.dot(dec.astype(np.float64), x.astype(np.float64)))
+    assert abs(float(y[0, 0]) - ref) <= 1e-4 * max(1.0, abs(ref))
