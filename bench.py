@@ -644,6 +644,8 @@ def run_prefill_case(args):
     K = gk.GpuKernels(0)
     gen = torch.Generator(device=dev).manual_seed(20245)
     QT = gk.QuantType
+    if args.case == "decode_q6k":
+        return run_gguf_case(args, K, gk, torch, dev, gen)
     if args.case == "prefill_q4k":
         n, k, m = N_FF, D_MODEL, 512
         W = torch.randn((n, k), generator=gen, device=dev) * 0.02
@@ -690,6 +692,42 @@ def run_prefill_case(args):
                       "gpu_launches": args.steps * launches, "status": K.status()}), flush=True)
 
 
+def run_gguf_case(args, K, gk, torch, dev, gen):
+    """Q6_K decode product on its own: W[8192, 28672] (the down projection of config 5), M = 1, two weight
+    copies in rotation (2 x 193 MB > L2)."""
+    qt = gk.QuantType.q6k()
+    n, k = D_MODEL, N_FF
+    nblk = n * (k // 256)
+    ws = []
+    for _ in range(2):
+        b = torch.randint(0, 256, (nblk, 210), generator=gen, device=dev, dtype=torch.uint8)
+        d = ((torch.rand((nblk, 1), generator=gen, device=dev) - 0.5) * 0.04).to(torch.float16)
+        b[:, 208:210] = d.view(torch.uint8)
+        ws.append(K.upload(qt, n, k, b.reshape(-1)))
+        del b, d
+    x = torch.randn((1, k), generator=gen, device=dev)
+    y = torch.empty((1, n), dtype=torch.float32, device=dev)
+    for i in range(max(args.warmup, 3)):
+        K.gemv(ws[i % 2], x, y=y)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        K.gemv(ws[i % 2], x, y=y)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    wbytes = nblk * 210
+    gbs = wbytes / (ms * 1e-3) / 1e9
+    peak, kind = measured_peaks()
+    print(json.dumps({"metric": "Q6_K decode weight GB/s", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+                      "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "data": "synthetic",
+                      "config": {"workload": args.case, "n": n, "k": k, "m": 1, "l2": "two weight copies in rotation"},
+                      "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
+                                   "traffic": None, "peak_kind": kind, "kernel": "raw_gemv_kernel<Q6_K, 1> (+ act_quant_kernel)"},
+                      "gpu_launches": args.steps * 2, "status": K.status()}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -705,7 +743,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying a CUDA graph")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="N > 1: how the bands of y reach every rank (peer stores fused into the GEMV, or NCCL all-gather)")
-    ap.add_argument("--case", default="decode", choices=["decode", "prefill_q4k", "prefill_nvfp4"],
+    ap.add_argument("--case", default="decode", choices=["decode", "prefill_q4k", "prefill_nvfp4", "decode_q6k"],
                     help="decode = the headline workload; prefill_* = one prefill kernel on its own (1 GPU)")
     args = ap.parse_args()
     if args.case != "decode":

@@ -2,9 +2,9 @@
 // Q4_0, Q5_0 (32 elements per block) — kept on the device exactly as the reference stores them: row after row of
 // blocks, no repacking.  One decode rule per format (an "item" = the elements one data byte, or byte group,
 // yields), used by the matrix decode / embedding gather and by a streaming GEMV: a warp owns a weight row,
-// brings it into shared memory in 16-byte loads, and accumulates integer dot products (dp4a) against s8-quantized activations.  The decode keeps
+// brings it into shared memory in 16-byte loads, and accumulates integer dot products (dp2a) against s16 fixed-point activations.  The decode keeps
 // the reference's operation order (separately rounded products, no fused multiply-add), so decoded values are
-// bit-exact; the GEMV rounds the activations to 16 bits per 32-element group (error ~2e-5, far inside the 2e-3 bar).
+// bit-exact; the GEMV rounds the activations to 16 bits per 32-element group (error ~1.5e-5, far inside the 2e-3 bar).
 //
 // Reference: src/macros/quant_primitive/k_quant.rs:92-101 (Q8_K), :381-436 (Q5_K), :441-472 (Q6_K);
 //            src/macros/quant_primitive/classic.rs:15-29 (Q4_0), :484-504 (Q5_0); block structs src/quant.rs:132-157, 254-275.
@@ -146,20 +146,17 @@ __global__ void __launch_bounds__(256) raw_dequant_kernel(const uint8_t *__restr
 }
 
 // ---- streaming GEMV on integer dot products ------------------------------------------------------
-// The activations are quantized once per call to two s8 planes (16 bits in all) with one f32 scale per 32 elements
-// (act_quant_kernel); a weight
+// The activations are quantized once per call to s16 with one f32 scale per 32 elements (act_quant_kernel); a weight
 // "unit" is a few 32-bit words of four s8 (or u8 below 128) weight values each, assembled from the block's bit
 // fields with word-wide logic, with the f32 factor (and, for Q5_K, the min term) of the sub-block each word lies
-// in.  Two dp4a per word and token, then acc += x_scale * (w_scale * dot + w_min * sum(x)).
+// in.  Two dp2a (s16 x s8) per word and token, then acc += x_scale * (w_scale * dot + w_min * sum(x)).
 constexpr int RG_WARPS = 8;
 constexpr int RG_CHUNK = 4096;  // block bytes staged per warp and pass
 
-// x [m tokens, k] (any strides) -> two s8 planes xq1, xq2 [m, k] and xs f32 [m, k / 32] with
-// x ~= xs * (254 * q1 + q2): q1 rounds x to 8 bits per 32-element group, q2 rounds what is left to 8 more
-// (relative error ~2e-5 of the group's largest value).  One warp per 32 elements.
+// x [m tokens, k] (any strides) -> xq s16 [m, k] and xs f32 [m, k / 32] with x ~= xs * xq: 16-bit fixed point per
+// 32-element group (relative error ~1.5e-5 of the group's largest value).  One warp per 32 elements.
 __global__ void __launch_bounds__(256) act_quant_kernel(const float *__restrict__ x, int64_t xst, int64_t xsk, int m, int64_t k,
-                                                        int8_t *__restrict__ xq1, int8_t *__restrict__ xq2,
-                                                        float *__restrict__ xs) {
+                                                        int16_t *__restrict__ xq, float *__restrict__ xs) {
     const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     const int64_t per_tok = k >> 5;
@@ -169,18 +166,16 @@ __global__ void __launch_bounds__(256) act_quant_kernel(const float *__restrict_
     float a = fabsf(v);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
-    const float sc = a * (1.0f / 127.0f);
-    float q1 = 0.0f, q2 = 0.0f;
-    if (a > 0.0f) {
-        q1 = fminf(fmaxf(rintf(v / sc), -127.0f), 127.0f);
-        q2 = fminf(fmaxf(rintf((v - q1 * sc) * (254.0f / sc)), -127.0f), 127.0f);
-    }
-    const size_t o = (size_t)t * k + b * 32 + lane;
-    xq1[o] = (int8_t)(int)q1;
-    xq2[o] = (int8_t)(int)q2;
-    if (lane == 0) xs[(size_t)t * per_tok + b] = sc * (1.0f / 254.0f);
+    const float sc = a * (1.0f / 32767.0f);
+    const float q = a > 0.0f ? fminf(fmaxf(rintf(v / sc), -32767.0f), 32767.0f) : 0.0f;
+    xq[(size_t)t * k + b * 32 + lane] = (int16_t)(int)q;
+    if (lane == 0) xs[(size_t)t * per_tok + b] = sc;
 }
 
+// f16 field at a 2-byte aligned address
+__device__ __forceinline__ float f16_even(const uint8_t *p) {
+    return __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(p)));
+}
 // 32-bit word at a 2-byte aligned shared-memory address (block sizes and field offsets are all even)
 __device__ __forceinline__ uint32_t ld32(const uint8_t *p) {
     const unsigned short *h = reinterpret_cast<const unsigned short *>(p);
@@ -202,12 +197,13 @@ struct Dp<GLLMK_QUANT_Q6_K> {
     static __device__ __forceinline__ void unit(const uint8_t *b, int u, uint32_t *q, int *ko, float *ws, float *) {
         const int g = u >> 3, lw = u & 7, is = lw >> 2;
         const uint32_t A = ld32(b + g * 64 + 4 * lw), B = ld32(b + g * 64 + 32 + 4 * lw), H = ld32(b + 128 + g * 32 + 4 * lw);
-        q[0] = __vsub4((A & 0x0F0F0F0Fu) | ((H << 4) & 0x30303030u), 0x20202020u);
-        q[1] = __vsub4((B & 0x0F0F0F0Fu) | ((H << 2) & 0x30303030u), 0x20202020u);
-        q[2] = __vsub4(((A >> 4) & 0x0F0F0F0Fu) | (H & 0x30303030u), 0x20202020u);
-        q[3] = __vsub4(((B >> 4) & 0x0F0F0F0Fu) | ((H >> 2) & 0x30303030u), 0x20202020u);
+        // a 6-bit value with bit 5 flipped is q - 32 in 6-bit two's complement; two places up it is the s8 4 (q - 32)
+        q[0] = ((((A & 0x0F0F0F0Fu) | ((H << 4) & 0x30303030u)) ^ 0x20202020u) << 2) & 0xFCFCFCFCu;
+        q[1] = ((((B & 0x0F0F0F0Fu) | ((H << 2) & 0x30303030u)) ^ 0x20202020u) << 2) & 0xFCFCFCFCu;
+        q[2] = (((((A >> 4) & 0x0F0F0F0Fu) | (H & 0x30303030u)) ^ 0x20202020u) << 2) & 0xFCFCFCFCu;
+        q[3] = (((((B >> 4) & 0x0F0F0F0Fu) | ((H >> 2) & 0x30303030u)) ^ 0x20202020u) << 2) & 0xFCFCFCFCu;
         const int8_t *sc = reinterpret_cast<const int8_t *>(b + 192 + g * 8 + is);
-        const float d = f16_at(b + 208);
+        const float d = 0.25f * f16_even(b + 208);
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             ko[j] = g * 128 + 32 * j + 4 * lw;
@@ -225,7 +221,7 @@ struct Dp<GLLMK_QUANT_Q5_K> {
         const uint32_t A = ld32(b + 48 + g * 32 + 4 * lw), H = ld32(b + 16 + 4 * lw);
         q[0] = (A & 0x0F0F0F0Fu) | (((H >> (2 * g)) & 0x01010101u) << 4);
         q[1] = ((A >> 4) & 0x0F0F0F0Fu) | (((H >> (2 * g + 1)) & 0x01010101u) << 4);
-        const float d = f16_at(b), mn = f16_at(b + 2);
+        const float d = f16_even(b), mn = f16_even(b + 2);
         float sc1, m1, sc2, m2;
         scale_min_k4(2 * g, b + 4, sc1, m1);
         scale_min_k4(2 * g + 1, b + 4, sc2, m2);
@@ -259,11 +255,12 @@ struct Dp<GLLMK_QUANT_Q4_0> {
     static constexpr bool MIN = false;
     static __device__ __forceinline__ void unit(const uint8_t *b, int u, uint32_t *q, int *ko, float *ws, float *) {
         const uint32_t W = ld32(b + 2 + 4 * u);
-        q[0] = __vsub4(W & 0x0F0F0F0Fu, 0x08080808u);
-        q[1] = __vsub4((W >> 4) & 0x0F0F0F0Fu, 0x08080808u);
+        // a nibble with bit 3 flipped is q - 8 in 4-bit two's complement; in the high half of a byte it is the s8 16 (q - 8)
+        q[0] = ((W ^ 0x08080808u) << 4) & 0xF0F0F0F0u;
+        q[1] = (W ^ 0x80808080u) & 0xF0F0F0F0u;
         ko[0] = 4 * u;
         ko[1] = 16 + 4 * u;
-        ws[0] = ws[1] = f16_at(b);
+        ws[0] = ws[1] = 0.0625f * f16_even(b);
     }
 };
 
@@ -273,17 +270,18 @@ struct Dp<GLLMK_QUANT_Q5_0> {
     static constexpr bool MIN = false;
     static __device__ __forceinline__ void unit(const uint8_t *b, int u, uint32_t *q, int *ko, float *ws, float *) {
         const uint32_t W = ld32(b + 6 + 4 * u), qh = ld32(b + 2);
-        q[0] = __vsub4((W & 0x0F0F0F0Fu) | (spread4(qh >> (4 * u)) << 4), 0x10101010u);
-        q[1] = __vsub4(((W >> 4) & 0x0F0F0F0Fu) | (spread4(qh >> (16 + 4 * u)) << 4), 0x10101010u);
+        // a 5-bit value with bit 4 flipped is q - 16 in 5-bit two's complement; three places up it is the s8 8 (q - 16)
+        q[0] = ((((W & 0x0F0F0F0Fu) | (spread4(qh >> (4 * u)) << 4)) ^ 0x10101010u) << 3) & 0xF8F8F8F8u;
+        q[1] = (((((W >> 4) & 0x0F0F0F0Fu) | (spread4(qh >> (16 + 4 * u)) << 4)) ^ 0x10101010u) << 3) & 0xF8F8F8F8u;
         ko[0] = 4 * u;
         ko[1] = 16 + 4 * u;
-        ws[0] = ws[1] = f16_at(b);
+        ws[0] = ws[1] = 0.125f * f16_even(b);
     }
 };
 
 struct RawGemvParams {
     const uint8_t *w;
-    const int8_t *xq;   // [2 planes][m, k]
+    const int16_t *xq;  // [m, k]
     const float *xs;    // [m, k / 32]
     float *y;
     const float *row_scales;
@@ -304,14 +302,13 @@ __global__ void __launch_bounds__(RG_WARPS * 32) raw_gemv_kernel(const RawGemvPa
         const uint8_t *rowp = p.w + (size_t)row * p.nb * F::BB;
         for (int t0 = 0; t0 < p.m; t0 += MT) {
             float acc[MT];
-            const int *xq[MT];
+            const int2 *xq[MT];  // four s16 activations per entry
             const float *xs[MT];
-            const size_t plane = ((size_t)p.m * p.k) >> 2;  // second activation plane, in words
 #pragma unroll
             for (int t = 0; t < MT; t++) {
                 acc[t] = 0.0f;
                 const int tok = t0 + t < p.m ? t0 + t : p.m - 1;  // surplus slots repeat the last token; not stored
-                xq[t] = reinterpret_cast<const int *>(p.xq + (size_t)tok * p.k);
+                xq[t] = reinterpret_cast<const int2 *>(p.xq + (size_t)tok * p.k);
                 xs[t] = p.xs + (size_t)tok * k32;
             }
             for (int64_t b0 = 0; b0 < p.nb; b0 += CB) {
@@ -333,17 +330,18 @@ __global__ void __launch_bounds__(RG_WARPS * 32) raw_gemv_kernel(const RawGemvPa
                     int ko[D::NW];
                     float ws[D::NW], wm[D::NW];
                     D::unit(sb + blk * F::BB, u % D::UNITS, q, ko, ws, wm);
-                    const int64_t kb = (b0 + blk) * F::BS;
+                    const int kb = ((int)b0 + blk) * F::BS;
 #pragma unroll
                     for (int j = 0; j < D::NW; j++) {
-                        const int64_t kk = kb + ko[j];
+                        const int kk = kb + ko[j];
 #pragma unroll
                         for (int t = 0; t < MT; t++) {
-                            const int xw = __ldg(xq[t] + (kk >> 2)), xw2 = __ldg(xq[t] + plane + (kk >> 2));
+                            const int2 xw = __ldg(xq[t] + (kk >> 2));
                             const float s = __ldg(xs[t] + (kk >> 5));
-                            const float dot = (float)__dp4a((int)q[j], xw2, __dp4a((int)q[j], xw, 0) * 254);
+                            // s16 x s8 products: elements 0, 1 of the word against xw.x, elements 2, 3 against xw.y
+                            const float dot = (float)__dp2a_hi(xw.y, (int)q[j], __dp2a_lo(xw.x, (int)q[j], 0));
                             if (D::MIN) {
-                                const float sx = (float)__dp4a(0x01010101, xw2, __dp4a(0x01010101, xw, 0) * 254);
+                                const float sx = (float)__dp2a_hi(xw.y, 0x01010101, __dp2a_lo(xw.x, 0x01010101, 0));
                                 acc[t] = fmaf(s, fmaf(ws[j], dot, wm[j] * sx), acc[t]);
                             } else {
                                 acc[t] = fmaf(s * ws[j], dot, acc[t]);
@@ -413,14 +411,14 @@ int32_t raw_dequant(Ctx *c, int32_t qt, const uint8_t *w, int64_t n, int64_t nb,
 
 int32_t raw_gemv_launch(Ctx *c, const Weight *w, const float *x, int64_t xst, int64_t xsk, int m, float *y, int64_t yst,
                         int64_t ysr, const float *row_scales, int64_t n_row_scales, cudaStream_t s) {
-    // activations -> two s8 planes + one f32 scale per 32 elements, in the context's activation scratch
+    // activations -> s16 + one f32 scale per 32 elements, in the context's activation scratch
     const size_t qb = (2 * (size_t)m * w->k + 255) & ~(size_t)255;
     int32_t rc = ensure_act(c, qb + (size_t)m * (w->k / 32) * sizeof(float));
     if (rc) return rc;
-    int8_t *xq = static_cast<int8_t *>(c->act);
+    int16_t *xq = static_cast<int16_t *>(c->act);
     float *xs = reinterpret_cast<float *>(static_cast<char *>(c->act) + qb);
     const size_t qthreads = (size_t)m * (w->k / 32) * 32;
-    act_quant_kernel<<<grid_1d(qthreads, 256), 256, 0, s>>>(x, xst, xsk, m, w->k, xq, xq + (size_t)m * w->k, xs);
+    act_quant_kernel<<<grid_1d(qthreads, 256), 256, 0, s>>>(x, xst, xsk, m, w->k, xq, xs);
     GK_CUDA(c, cudaGetLastError());
     RawGemvParams p{};
     p.w = static_cast<const uint8_t *>(w->qs);
