@@ -116,7 +116,7 @@ static int32_t weight_alloc(Ctx *c, int32_t qt, int64_t n, int64_t k, int32_t mx
     if (raw_format(qt)) {
         // reference blocks as they are; 16 spare bytes let the GEMV's 16-byte loads run past the last row
         w->n_pad = n;
-        w->qs_bytes = (size_t)w->ref_bytes + 16;
+        w->qs_bytes = (size_t)n * w->nb * raw_dev_block_bytes(qt) + 16;
         w->aux_bytes = 0;
     } else if (qt == GLLMK_QUANT_Q4K) {
         w->n_pad = (n + 127) / 128 * 128;

@@ -137,10 +137,13 @@ int32_t i8_weight_fill(Ctx *c, Weight *w, const int8_t *b_dev, int layout, cudaS
 int32_t gemm_i8_launch(Ctx *c, const Weight *w, const uint8_t *a, int64_t lda, int m, int32_t *out, int64_t ldc, cudaStream_t s);
 int32_t dequant_i32_launch(Ctx *c, const int32_t *ci, float *out, int64_t m, int64_t n, int64_t ldc, int64_t ldo, float scale_a,
                            float scale_b, const float *bias, int act, cudaStream_t s);
-// ---- gguf_raw.cu: Q6_K, Q5_K, Q8_K, Q4_0, Q5_0 kept as reference blocks (w->qs = n rows of nb blocks + 16 spare bytes) ----
+// ---- gguf_raw.cu: Q6_K, Q5_K, Q8_K, Q4_0, Q5_0 kept as reference blocks (w->qs = n rows of nb block slots + 16 spare bytes) ----
 bool raw_format(int32_t qt);
+int raw_dev_block_bytes(int32_t qt);  // Q6_K: 224-byte slots; the others: the reference block size
+int32_t raw_fill(Ctx *c, const Weight *w, const void *blocks_dev, cudaStream_t s);
+int32_t raw_unfill(Ctx *c, const Weight *w, void *blocks_dev, cudaStream_t s);
 int32_t raw_dequant(Ctx *c, int32_t qt, const uint8_t *w, int64_t n, int64_t nb, const int32_t *ids, size_t rows, float *out,
-                    cudaStream_t s);
+                    cudaStream_t s, bool dev_layout);
 int32_t raw_gemv_launch(Ctx *c, const Weight *w, const float *x, int64_t xst, int64_t xsk, int m, float *y, int64_t yst,
                         int64_t ysr, const float *row_scales, int64_t n_row_scales, cudaStream_t s);
 // ---- quantize.cu ----

@@ -1,8 +1,9 @@
 // The other GGUF block formats of the reference's CPU quant path — Q6_K, Q5_K, Q8_K (256 elements per block) and
-// Q4_0, Q5_0 (32 elements per block) — kept on the device exactly as the reference stores them: row after row of
-// blocks, no repacking.  One decode rule per format (an "item" = the elements one data byte, or byte group,
-// yields), used by the matrix decode / embedding gather and by a streaming GEMV: a warp owns a weight row,
-// brings it into shared memory in 16-byte loads, and accumulates integer dot products (dp2a) against s16 fixed-point activations.  The decode keeps
+// Q4_0, Q5_0 (32 elements per block) — kept on the device as the reference stores them, row after row of blocks
+// (Q6_K blocks, 210 bytes, sit in 224-byte slots so that every field starts on a 4-byte boundary of a 16-byte
+// aligned block).  One decode rule per format (an "item" = the elements one data byte, or byte group,
+// yields), used by the matrix decode / embedding gather and by a streaming GEMV: a warp owns two weight rows,
+// brings them into shared memory in 16-byte loads, and accumulates integer dot products (dp2a) against s16 fixed-point activations.  The decode keeps
 // the reference's operation order (separately rounded products, no fused multiply-add), so decoded values are
 // bit-exact; the GEMV rounds the activations to 16 bits per 32-element group (error ~1.5e-5, far inside the 2e-3 bar).
 //
@@ -36,7 +37,7 @@ struct Fmt;
 
 template <>
 struct Fmt<GLLMK_QUANT_Q6_K> {  // ql[128] @0, qh[64] @128, scales[16] i8 @192, d f16 @208
-    static constexpr int BS = 256, BB = 210, ITEMS = 64, EPI = 4;
+    static constexpr int BS = 256, BB = 210, DB = 224, ITEMS = 64, EPI = 4;  // DB: bytes per block slot on the device
     static __device__ __forceinline__ void item(const uint8_t *b, int it, float *v, int *e) {
         const int g = it >> 5, l = it & 31, is = l >> 4;
         const uint8_t la = b[g * 64 + l], lb = b[g * 64 + l + 32], h = b[128 + g * 32 + l];
@@ -59,7 +60,7 @@ struct Fmt<GLLMK_QUANT_Q6_K> {  // ql[128] @0, qh[64] @128, scales[16] i8 @192, 
 
 template <>
 struct Fmt<GLLMK_QUANT_Q5_K> {  // d @0, dmin @2, scales[12] @4, qh[32] @16, qs[128] @48
-    static constexpr int BS = 256, BB = 176, ITEMS = 128, EPI = 2;
+    static constexpr int BS = 256, BB = 176, DB = 176, ITEMS = 128, EPI = 2;
     static __device__ __forceinline__ void item(const uint8_t *b, int it, float *v, int *e) {
         const int g = it >> 5, l = it & 31;
         const float d = f16_at(b), mn = f16_at(b + 2);
@@ -78,7 +79,7 @@ struct Fmt<GLLMK_QUANT_Q5_K> {  // d @0, dmin @2, scales[12] @4, qh[32] @16, qs[
 
 template <>
 struct Fmt<GLLMK_QUANT_Q8_K> {  // d f32 @0, qs[256] i8 @4, bsums[16] i16 @260 (not used by decode)
-    static constexpr int BS = 256, BB = 292, ITEMS = 64, EPI = 4;
+    static constexpr int BS = 256, BB = 292, DB = 292, ITEMS = 64, EPI = 4;
     static __device__ __forceinline__ void item(const uint8_t *b, int it, float *v, int *e) {
         const float d = __uint_as_float((uint32_t)b[0] | ((uint32_t)b[1] << 8) | ((uint32_t)b[2] << 16) | ((uint32_t)b[3] << 24));
 #pragma unroll
@@ -92,7 +93,7 @@ struct Fmt<GLLMK_QUANT_Q8_K> {  // d f32 @0, qs[256] i8 @4, bsums[16] i16 @260 (
 
 template <>
 struct Fmt<GLLMK_QUANT_Q4_0> {  // d @0, qs[16] @2: byte j -> elements j (low nibble) and j + 16 (high nibble)
-    static constexpr int BS = 32, BB = 18, ITEMS = 16, EPI = 2;
+    static constexpr int BS = 32, BB = 18, DB = 18, ITEMS = 16, EPI = 2;
     static __device__ __forceinline__ void item(const uint8_t *b, int it, float *v, int *e) {
         const float d = f16_at(b);
         const uint8_t q = b[2 + it];
@@ -105,7 +106,7 @@ struct Fmt<GLLMK_QUANT_Q4_0> {  // d @0, qs[16] @2: byte j -> elements j (low ni
 
 template <>
 struct Fmt<GLLMK_QUANT_Q5_0> {  // d @0, qh[4] @2 (bit j = fifth bit of element j), qs[16] @6
-    static constexpr int BS = 32, BB = 22, ITEMS = 16, EPI = 2;
+    static constexpr int BS = 32, BB = 22, DB = 22, ITEMS = 16, EPI = 2;
     static __device__ __forceinline__ void item(const uint8_t *b, int it, float *v, int *e) {
         const float d = f16_at(b);
         const uint32_t qh = (uint32_t)b[2] | ((uint32_t)b[3] << 8) | ((uint32_t)b[4] << 16) | ((uint32_t)b[5] << 24);
@@ -122,7 +123,7 @@ struct Fmt<GLLMK_QUANT_Q5_0> {  // d @0, qh[4] @2 (bit j = fifth bit of element 
 template <int QT>
 __global__ void __launch_bounds__(256) raw_dequant_kernel(const uint8_t *__restrict__ w, int64_t n, int64_t nb,
                                                           const int32_t *__restrict__ ids, float *__restrict__ out,
-                                                          size_t total) {
+                                                          size_t total, int stride) {
     using F = Fmt<QT>;
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // (out row, block, item)
     if (idx >= total) return;
@@ -140,7 +141,7 @@ __global__ void __launch_bounds__(256) raw_dequant_kernel(const uint8_t *__restr
         for (int j = 0; j < F::EPI; j++) o[e[j]] = 0.0f;
         return;
     }
-    F::item(w + ((size_t)row * nb + blk) * F::BB, it, v, e);
+    F::item(w + ((size_t)row * nb + blk) * (size_t)stride, it, v, e);
 #pragma unroll
     for (int j = 0; j < F::EPI; j++) o[e[j]] = v[j];
 }
@@ -151,7 +152,7 @@ __global__ void __launch_bounds__(256) raw_dequant_kernel(const uint8_t *__restr
 // fields with word-wide logic, with the f32 factor (and, for Q5_K, the min term) of the sub-block each word lies
 // in.  Two dp2a (s16 x s8) per word and token, then acc += x_scale * (w_scale * dot + w_min * sum(x)).
 constexpr int RG_WARPS = 8;
-constexpr int RG_CHUNK = 4096;  // block bytes staged per warp and pass
+constexpr int RG_CHUNK = 2048;  // block bytes staged per warp and pass (two stages of this size per warp)
 
 // x [m tokens, k] (any strides) -> xq s16 [m, k] and xs f32 [m, k / 32] with x ~= xs * xq: 16-bit fixed point per
 // 32-element group (relative error ~1.5e-5 of the group's largest value).  One warp per 32 elements.
@@ -177,7 +178,14 @@ __device__ __forceinline__ float f16_even(const uint8_t *p) {
     return __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(p)));
 }
 // 32-bit word at a 2-byte aligned shared-memory address (block sizes and field offsets are all even)
+// 16 bytes global -> shared without passing registers (both addresses 16-byte aligned)
+__device__ __forceinline__ void cp_async16(void *smem, const void *gmem) {
+    const unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(gmem) : "memory");
+}
+template <bool A4>
 __device__ __forceinline__ uint32_t ld32(const uint8_t *p) {
+    if (A4) return *reinterpret_cast<const uint32_t *>(p);
     const unsigned short *h = reinterpret_cast<const unsigned short *>(p);
     return (uint32_t)h[0] | ((uint32_t)h[1] << 16);
 }
@@ -196,19 +204,22 @@ struct Dp<GLLMK_QUANT_Q6_K> {
     static constexpr bool MIN = false;
     static __device__ __forceinline__ void unit(const uint8_t *b, int u, uint32_t *q, int *ko, float *ws, float *) {
         const int g = u >> 3, lw = u & 7, is = lw >> 2;
-        const uint32_t A = ld32(b + g * 64 + 4 * lw), B = ld32(b + g * 64 + 32 + 4 * lw), H = ld32(b + 128 + g * 32 + 4 * lw);
+        const uint32_t A = ld32<true>(b + g * 64 + 4 * lw), B = ld32<true>(b + g * 64 + 32 + 4 * lw), H = ld32<true>(b + 128 + g * 32 + 4 * lw);
         // a 6-bit value with bit 5 flipped is q - 32 in 6-bit two's complement; two places up it is the s8 4 (q - 32)
         q[0] = ((((A & 0x0F0F0F0Fu) | ((H << 4) & 0x30303030u)) ^ 0x20202020u) << 2) & 0xFCFCFCFCu;
         q[1] = ((((B & 0x0F0F0F0Fu) | ((H << 2) & 0x30303030u)) ^ 0x20202020u) << 2) & 0xFCFCFCFCu;
         q[2] = (((((A >> 4) & 0x0F0F0F0Fu) | (H & 0x30303030u)) ^ 0x20202020u) << 2) & 0xFCFCFCFCu;
         q[3] = (((((B >> 4) & 0x0F0F0F0Fu) | ((H >> 2) & 0x30303030u)) ^ 0x20202020u) << 2) & 0xFCFCFCFCu;
-        const int8_t *sc = reinterpret_cast<const int8_t *>(b + 192 + g * 8 + is);
+        // the eight scale bytes of this half in one load; run j uses byte is + 2 j
+        const uint2 S = *reinterpret_cast<const uint2 *>(b + 192 + g * 8);
+        const uint32_t s01 = S.x >> (8 * is), s23 = S.y >> (8 * is);
         const float d = 0.25f * f16_even(b + 208);
+        ws[0] = d * (float)(int8_t)(s01 & 0xFF);
+        ws[1] = d * (float)(int8_t)((s01 >> 16) & 0xFF);
+        ws[2] = d * (float)(int8_t)(s23 & 0xFF);
+        ws[3] = d * (float)(int8_t)((s23 >> 16) & 0xFF);
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            ko[j] = g * 128 + 32 * j + 4 * lw;
-            ws[j] = d * (float)sc[2 * j];
-        }
+        for (int j = 0; j < 4; j++) ko[j] = g * 128 + 32 * j + 4 * lw;
     }
 };
 
@@ -218,7 +229,7 @@ struct Dp<GLLMK_QUANT_Q5_K> {
     static constexpr bool MIN = true;
     static __device__ __forceinline__ void unit(const uint8_t *b, int u, uint32_t *q, int *ko, float *ws, float *wm) {
         const int g = u >> 3, lw = u & 7;
-        const uint32_t A = ld32(b + 48 + g * 32 + 4 * lw), H = ld32(b + 16 + 4 * lw);
+        const uint32_t A = ld32<true>(b + 48 + g * 32 + 4 * lw), H = ld32<true>(b + 16 + 4 * lw);
         q[0] = (A & 0x0F0F0F0Fu) | (((H >> (2 * g)) & 0x01010101u) << 4);
         q[1] = ((A >> 4) & 0x0F0F0F0Fu) | (((H >> (2 * g + 1)) & 0x01010101u) << 4);
         const float d = f16_even(b), mn = f16_even(b + 2);
@@ -239,11 +250,11 @@ struct Dp<GLLMK_QUANT_Q8_K> {
     static constexpr int UNITS = 16, NW = 4;
     static constexpr bool MIN = false;
     static __device__ __forceinline__ void unit(const uint8_t *b, int u, uint32_t *q, int *ko, float *ws, float *) {
-        const float d = __uint_as_float(ld32(b));
+        const float d = __uint_as_float(ld32<true>(b));
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             ko[j] = 4 * (u + 16 * j);
-            q[j] = ld32(b + 4 + ko[j]);
+            q[j] = ld32<true>(b + 4 + ko[j]);
             ws[j] = d;
         }
     }
@@ -254,7 +265,7 @@ struct Dp<GLLMK_QUANT_Q4_0> {
     static constexpr int UNITS = 4, NW = 2;
     static constexpr bool MIN = false;
     static __device__ __forceinline__ void unit(const uint8_t *b, int u, uint32_t *q, int *ko, float *ws, float *) {
-        const uint32_t W = ld32(b + 2 + 4 * u);
+        const uint32_t W = ld32<false>(b + 2 + 4 * u);
         // a nibble with bit 3 flipped is q - 8 in 4-bit two's complement; in the high half of a byte it is the s8 16 (q - 8)
         q[0] = ((W ^ 0x08080808u) << 4) & 0xF0F0F0F0u;
         q[1] = (W ^ 0x80808080u) & 0xF0F0F0F0u;
@@ -269,7 +280,7 @@ struct Dp<GLLMK_QUANT_Q5_0> {
     static constexpr int UNITS = 4, NW = 2;
     static constexpr bool MIN = false;
     static __device__ __forceinline__ void unit(const uint8_t *b, int u, uint32_t *q, int *ko, float *ws, float *) {
-        const uint32_t W = ld32(b + 6 + 4 * u), qh = ld32(b + 2);
+        const uint32_t W = ld32<false>(b + 6 + 4 * u), qh = ld32<false>(b + 2);
         // a 5-bit value with bit 4 flipped is q - 16 in 5-bit two's complement; three places up it is the s8 8 (q - 16)
         q[0] = ((((W & 0x0F0F0F0Fu) | (spread4(qh >> (4 * u)) << 4)) ^ 0x10101010u) << 3) & 0xF8F8F8F8u;
         q[1] = (((((W >> 4) & 0x0F0F0F0Fu) | (spread4(qh >> (16 + 4 * u)) << 4)) ^ 0x10101010u) << 3) & 0xF8F8F8F8u;
@@ -289,48 +300,76 @@ struct RawGemvParams {
     int m;
 };
 
+constexpr int RG_ROWS = 2;  // rows per warp: their words meet the same activations, loaded once
+
 template <int QT, int MT>
 __global__ void __launch_bounds__(RG_WARPS * 32) raw_gemv_kernel(const RawGemvParams p) {
     using F = Fmt<QT>;
     using D = Dp<QT>;
-    constexpr int CB = RG_CHUNK / F::BB;  // whole blocks per pass
-    __shared__ __align__(16) uint8_t buf[RG_WARPS][RG_CHUNK + 32];
+    constexpr int R = RG_ROWS, CH = RG_CHUNK / R;
+    constexpr int LPB = D::UNITS < 32 ? 32 / D::UNITS : 1;   // blocks one warp pass over the units covers
+    constexpr int CB = (CH / F::DB) / LPB * LPB;             // whole blocks per row and pass, no idle lanes inside a pass
+    __shared__ __align__(16) uint8_t buf[RG_WARPS][2][R][CH + 32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    uint8_t *mine = buf[warp];
-    const int64_t k32 = p.k >> 5;
-    for (int64_t row = (int64_t)blockIdx.x * RG_WARPS + warp; row < p.n; row += (int64_t)gridDim.x * RG_WARPS) {
-        const uint8_t *rowp = p.w + (size_t)row * p.nb * F::BB;
+    const int k32 = (int)(p.k >> 5);
+    const int64_t groups = (p.n + R - 1) / R;
+    for (int64_t grp = (int64_t)blockIdx.x * RG_WARPS + warp; grp < groups; grp += (int64_t)gridDim.x * RG_WARPS) {
+        const uint8_t *rowp[R];
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+            const int64_t row = grp * R + r < p.n ? grp * R + r : p.n - 1;  // a surplus row repeats the last one; not stored
+            rowp[r] = p.w + (size_t)row * p.nb * F::DB;
+        }
         for (int t0 = 0; t0 < p.m; t0 += MT) {
-            float acc[MT];
+            float acc[R][MT];
             const int2 *xq[MT];  // four s16 activations per entry
             const float *xs[MT];
 #pragma unroll
             for (int t = 0; t < MT; t++) {
-                acc[t] = 0.0f;
                 const int tok = t0 + t < p.m ? t0 + t : p.m - 1;  // surplus slots repeat the last token; not stored
                 xq[t] = reinterpret_cast<const int2 *>(p.xq + (size_t)tok * p.k);
                 xs[t] = p.xs + (size_t)tok * k32;
+#pragma unroll
+                for (int r = 0; r < R; r++) acc[r][t] = 0.0f;
             }
-            for (int64_t b0 = 0; b0 < p.nb; b0 += CB) {
-                const int nblk = (int)(p.nb - b0 < CB ? p.nb - b0 : CB);
-                const uint8_t *src = rowp + (size_t)b0 * F::BB;
-                // 16-byte loads from the aligned address below src: up to 15 bytes before the pass and after the
-                // row are read and ignored (the weight buffer starts 256-byte aligned and ends with 16 spare bytes)
-                const uintptr_t a0 = reinterpret_cast<uintptr_t>(src) & ~(uintptr_t)15;
-                const int off = (int)(reinterpret_cast<uintptr_t>(src) - a0);
-                const int n16 = (off + nblk * F::BB + 15) >> 4;
+            // two shared-memory stages per warp: the copies of pass i + 1 (cp.async, 16 bytes each) run while pass i
+            // is computed.  Copies start at the aligned address below the pass: up to 15 bytes before it and after the
+            // row are copied and ignored (the weight buffer starts 256-byte aligned and ends with 16 spare bytes).
+            const auto issue = [&](int b0, int st) {
+                const int nblk = (int)p.nb - b0 < CB ? (int)p.nb - b0 : CB;
+#pragma unroll
+                for (int r = 0; r < R; r++) {
+                    const uint8_t *src = rowp[r] + (size_t)b0 * F::DB;
+                    const uintptr_t a0 = reinterpret_cast<uintptr_t>(src) & ~(uintptr_t)15;
+                    const int n16 = ((int)(reinterpret_cast<uintptr_t>(src) - a0) + nblk * F::DB + 15) >> 4;
+                    for (int i = lane; i < n16; i += 32) cp_async16(buf[warp][st][r] + 16 * i, reinterpret_cast<const uint8_t *>(a0) + 16 * i);
+                }
+                asm volatile("cp.async.commit_group;" ::: "memory");
+            };
+            __syncwarp();
+            issue(0, 0);
+            int st = 0;
+            for (int b0 = 0; b0 < (int)p.nb; b0 += CB, st ^= 1) {
+                const int nblk = (int)p.nb - b0 < CB ? (int)p.nb - b0 : CB;
+                if (b0 + CB < (int)p.nb) {
+                    issue(b0 + CB, st ^ 1);
+                    asm volatile("cp.async.wait_group 1;" ::: "memory");
+                } else {
+                    asm volatile("cp.async.wait_group 0;" ::: "memory");
+                }
                 __syncwarp();
-                for (int i = lane; i < n16; i += 32)
-                    reinterpret_cast<uint4 *>(mine)[i] = __ldcs(reinterpret_cast<const uint4 *>(a0) + i);
-                __syncwarp();
-                const uint8_t *sb = mine + off;
+                const uint8_t *sb[R];
+#pragma unroll
+                for (int r = 0; r < R; r++)
+                    sb[r] = buf[warp][st][r] + (int)(reinterpret_cast<uintptr_t>(rowp[r] + (size_t)b0 * F::DB) & 15);
                 for (int u = lane; u < nblk * D::UNITS; u += 32) {
                     const int blk = u / D::UNITS;
-                    uint32_t q[D::NW];
+                    uint32_t q[R][D::NW];
                     int ko[D::NW];
-                    float ws[D::NW], wm[D::NW];
-                    D::unit(sb + blk * F::BB, u % D::UNITS, q, ko, ws, wm);
-                    const int kb = ((int)b0 + blk) * F::BS;
+                    float ws[R][D::NW], wm[R][D::NW];
+#pragma unroll
+                    for (int r = 0; r < R; r++) D::unit(sb[r] + blk * F::DB, u % D::UNITS, q[r], ko, ws[r], wm[r]);
+                    const int kb = (b0 + blk) * F::BS;
 #pragma unroll
                     for (int j = 0; j < D::NW; j++) {
                         const int kk = kb + ko[j];
@@ -338,49 +377,64 @@ __global__ void __launch_bounds__(RG_WARPS * 32) raw_gemv_kernel(const RawGemvPa
                         for (int t = 0; t < MT; t++) {
                             const int2 xw = __ldg(xq[t] + (kk >> 2));
                             const float s = __ldg(xs[t] + (kk >> 5));
-                            // s16 x s8 products: elements 0, 1 of the word against xw.x, elements 2, 3 against xw.y
-                            const float dot = (float)__dp2a_hi(xw.y, (int)q[j], __dp2a_lo(xw.x, (int)q[j], 0));
-                            if (D::MIN) {
-                                const float sx = (float)__dp2a_hi(xw.y, 0x01010101, __dp2a_lo(xw.x, 0x01010101, 0));
-                                acc[t] = fmaf(s, fmaf(ws[j], dot, wm[j] * sx), acc[t]);
-                            } else {
-                                acc[t] = fmaf(s * ws[j], dot, acc[t]);
+                            float sx = 0.0f;
+                            if (D::MIN) sx = (float)__dp2a_hi(xw.y, 0x01010101, __dp2a_lo(xw.x, 0x01010101, 0));
+#pragma unroll
+                            for (int r = 0; r < R; r++) {
+                                // s16 x s8 products: elements 0, 1 of the word against xw.x, elements 2, 3 against xw.y
+                                const float dot = (float)__dp2a_hi(xw.y, (int)q[r][j], __dp2a_lo(xw.x, (int)q[r][j], 0));
+                                if (D::MIN) acc[r][t] = fmaf(s, fmaf(ws[r][j], dot, wm[r][j] * sx), acc[r][t]);
+                                else acc[r][t] = fmaf(s * ws[r][j], dot, acc[r][t]);
                             }
                         }
                     }
                 }
+                __syncwarp();  // every lane is done with this stage before the next pass's copies overwrite it
             }
 #pragma unroll
-            for (int t = 0; t < MT; t++) {
-                float a = acc[t];
+            for (int r = 0; r < R; r++)
 #pragma unroll
-                for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
-                if (lane == 0 && t0 + t < p.m) {
-                    if (p.n_row_scales == 1) a *= p.row_scales[0];
-                    else if (p.n_row_scales > 1) a *= p.row_scales[row];
-                    p.y[(size_t)(t0 + t) * p.yst + (size_t)row * p.ysr] = a;
+                for (int t = 0; t < MT; t++) {
+                    float a = acc[r][t];
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+                    const int64_t row = grp * R + r;
+                    if (lane == 0 && t0 + t < p.m && row < p.n) {
+                        if (p.n_row_scales == 1) a *= p.row_scales[0];
+                        else if (p.n_row_scales > 1) a *= p.row_scales[row];
+                        p.y[(size_t)(t0 + t) * p.yst + (size_t)row * p.ysr] = a;
+                    }
                 }
-            }
         }
     }
+}
+
+// Q6_K: reference blocks (210 bytes) <-> device slots (224 bytes); one thread per 2 bytes
+__global__ void q6k_pad_kernel(const unsigned short *__restrict__ src, unsigned short *__restrict__ dst, size_t total, int to_device) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const size_t blk = idx / 105, o = idx % 105;
+    if (to_device) dst[blk * 112 + o] = src[blk * 105 + o];
+    else dst[blk * 105 + o] = src[blk * 112 + o];
 }
 
 inline unsigned grid_1d(size_t total, int block) { return (unsigned)((total + block - 1) / block); }
 
 template <int QT>
-int32_t dequant_t(Ctx *c, const uint8_t *w, int64_t n, int64_t nb, const int32_t *ids, size_t rows, float *out, cudaStream_t s) {
+int32_t dequant_t(Ctx *c, const uint8_t *w, int64_t n, int64_t nb, const int32_t *ids, size_t rows, float *out, cudaStream_t s,
+                  bool dev_layout) {
     const size_t total = rows * (size_t)nb * Fmt<QT>::ITEMS;
     if (total == 0) return GLLMK_STATUS_OK;
     if (total > (size_t)0x7fffffff * 256) return fail(c, GLLMK_STATUS_INVALID_ARG, "decode: matrix too large for one launch");
-    raw_dequant_kernel<QT><<<grid_1d(total, 256), 256, 0, s>>>(w, n, nb, ids, out, total);
+    raw_dequant_kernel<QT><<<grid_1d(total, 256), 256, 0, s>>>(w, n, nb, ids, out, total, dev_layout ? Fmt<QT>::DB : Fmt<QT>::BB);
     GK_CUDA(c, cudaGetLastError());
     return GLLMK_STATUS_OK;
 }
 
 template <int QT>
 int32_t gemv_t(Ctx *c, const RawGemvParams &p, cudaStream_t s) {
-    // 8 rows per CTA and pass; enough CTAs to fill every SM several times over, never more than the rows need
-    int64_t ctas = (p.n + RG_WARPS - 1) / RG_WARPS;
+    // 16 rows per CTA and pass; enough CTAs to fill every SM several times over, never more than the rows need
+    int64_t ctas = (p.n + RG_WARPS * RG_ROWS - 1) / (RG_WARPS * RG_ROWS);
     const int64_t cap = (int64_t)c->sm_count * 6;
     if (ctas > cap) ctas = cap;
     if (p.m == 1) raw_gemv_kernel<QT, 1><<<(unsigned)ctas, RG_WARPS * 32, 0, s>>>(p);
@@ -397,14 +451,51 @@ bool raw_format(int32_t qt) {
            qt == GLLMK_QUANT_Q5_0;
 }
 
-int32_t raw_dequant(Ctx *c, int32_t qt, const uint8_t *w, int64_t n, int64_t nb, const int32_t *ids, size_t rows, float *out,
-                    cudaStream_t s) {
+int raw_dev_block_bytes(int32_t qt) {
     switch (qt) {
-        case GLLMK_QUANT_Q6_K: return dequant_t<GLLMK_QUANT_Q6_K>(c, w, n, nb, ids, rows, out, s);
-        case GLLMK_QUANT_Q5_K: return dequant_t<GLLMK_QUANT_Q5_K>(c, w, n, nb, ids, rows, out, s);
-        case GLLMK_QUANT_Q8_K: return dequant_t<GLLMK_QUANT_Q8_K>(c, w, n, nb, ids, rows, out, s);
-        case GLLMK_QUANT_Q4_0: return dequant_t<GLLMK_QUANT_Q4_0>(c, w, n, nb, ids, rows, out, s);
-        case GLLMK_QUANT_Q5_0: return dequant_t<GLLMK_QUANT_Q5_0>(c, w, n, nb, ids, rows, out, s);
+        case GLLMK_QUANT_Q6_K: return Fmt<GLLMK_QUANT_Q6_K>::DB;
+        case GLLMK_QUANT_Q5_K: return Fmt<GLLMK_QUANT_Q5_K>::DB;
+        case GLLMK_QUANT_Q8_K: return Fmt<GLLMK_QUANT_Q8_K>::DB;
+        case GLLMK_QUANT_Q4_0: return Fmt<GLLMK_QUANT_Q4_0>::DB;
+        case GLLMK_QUANT_Q5_0: return Fmt<GLLMK_QUANT_Q5_0>::DB;
+    }
+    return 0;
+}
+
+// reference-layout blocks (device memory) -> the weight's device buffer, and back
+int32_t raw_fill(Ctx *c, const Weight *w, const void *blocks, cudaStream_t s) {
+    GK_CUDA(c, cudaMemsetAsync(w->qs, 0, w->qs_bytes, s));
+    if (w->qt == GLLMK_QUANT_Q6_K) {
+        const size_t total = (size_t)w->n * w->nb * 105;
+        q6k_pad_kernel<<<grid_1d(total, 256), 256, 0, s>>>(static_cast<const unsigned short *>(blocks),
+                                                           static_cast<unsigned short *>(w->qs), total, 1);
+        GK_CUDA(c, cudaGetLastError());
+    } else {
+        GK_CUDA(c, cudaMemcpyAsync(w->qs, blocks, w->ref_bytes, cudaMemcpyDeviceToDevice, s));
+    }
+    return GLLMK_STATUS_OK;
+}
+int32_t raw_unfill(Ctx *c, const Weight *w, void *blocks, cudaStream_t s) {
+    if (w->qt == GLLMK_QUANT_Q6_K) {
+        const size_t total = (size_t)w->n * w->nb * 105;
+        q6k_pad_kernel<<<grid_1d(total, 256), 256, 0, s>>>(static_cast<const unsigned short *>(w->qs),
+                                                           static_cast<unsigned short *>(blocks), total, 0);
+        GK_CUDA(c, cudaGetLastError());
+    } else {
+        GK_CUDA(c, cudaMemcpyAsync(blocks, w->qs, w->ref_bytes, cudaMemcpyDeviceToDevice, s));
+    }
+    return GLLMK_STATUS_OK;
+}
+
+// dev_layout: blocks at the device stride (a weight's buffer); otherwise consecutive reference blocks
+int32_t raw_dequant(Ctx *c, int32_t qt, const uint8_t *w, int64_t n, int64_t nb, const int32_t *ids, size_t rows, float *out,
+                    cudaStream_t s, bool dev_layout) {
+    switch (qt) {
+        case GLLMK_QUANT_Q6_K: return dequant_t<GLLMK_QUANT_Q6_K>(c, w, n, nb, ids, rows, out, s, dev_layout);
+        case GLLMK_QUANT_Q5_K: return dequant_t<GLLMK_QUANT_Q5_K>(c, w, n, nb, ids, rows, out, s, dev_layout);
+        case GLLMK_QUANT_Q8_K: return dequant_t<GLLMK_QUANT_Q8_K>(c, w, n, nb, ids, rows, out, s, dev_layout);
+        case GLLMK_QUANT_Q4_0: return dequant_t<GLLMK_QUANT_Q4_0>(c, w, n, nb, ids, rows, out, s, dev_layout);
+        case GLLMK_QUANT_Q5_0: return dequant_t<GLLMK_QUANT_Q5_0>(c, w, n, nb, ids, rows, out, s, dev_layout);
     }
     return fail(c, GLLMK_STATUS_UNSUPPORTED, "decode: quant type %d", qt);
 }

@@ -377,11 +377,7 @@ __global__ void dequant_raw_kernel(int qt, const uint8_t *__restrict__ blocks, c
 // ================================ host side ================================================
 int32_t repack_upload(Ctx *c, Weight *w, const void *blocks, const void *scales, cudaStream_t s) {
     const uint8_t *src = static_cast<const uint8_t *>(blocks);
-    if (raw_format(w->qt)) {  // stored as the reference stores it; the spare bytes after the last row stay zero
-        GK_CUDA(c, cudaMemsetAsync(static_cast<uint8_t *>(w->qs) + w->ref_bytes, 0, w->qs_bytes - w->ref_bytes, s));
-        GK_CUDA(c, cudaMemcpyAsync(w->qs, src, w->ref_bytes, cudaMemcpyDeviceToDevice, s));
-        return GLLMK_STATUS_OK;
-    }
+    if (raw_format(w->qt)) return raw_fill(c, w, src, s);  // stored as the reference stores it
     if (w->qt == GLLMK_QUANT_Q4K) {
         // n_pad is a multiple of 128: tiles beyond n are written as zero chunks
         const size_t tq = (size_t)(w->n_pad / 16) * w->nb * 128, th = (size_t)(w->n_pad / 16) * w->nb * 16;
@@ -405,10 +401,7 @@ int32_t repack_upload(Ctx *c, Weight *w, const void *blocks, const void *scales,
 
 int32_t repack_unpack(Ctx *c, const Weight *w, void *blocks, void *scales, cudaStream_t s) {
     uint8_t *dst = static_cast<uint8_t *>(blocks);
-    if (raw_format(w->qt)) {
-        GK_CUDA(c, cudaMemcpyAsync(dst, w->qs, w->ref_bytes, cudaMemcpyDeviceToDevice, s));
-        return GLLMK_STATUS_OK;
-    }
+    if (raw_format(w->qt)) return raw_unfill(c, w, dst, s);
     if (w->qt == GLLMK_QUANT_Q4K) {
         const size_t t = (size_t)w->n * w->nb * 9;
         unpack_q4k<<<grid_for(t, 256), 256, 0, s>>>((const uint8_t *)w->qs, dst, w->n, w->nb, t);
@@ -427,7 +420,7 @@ int32_t repack_unpack(Ctx *c, const Weight *w, void *blocks, void *scales, cudaS
 int32_t dequant_matrix(Ctx *c, const Weight *w, float *out, cudaStream_t s, const int32_t *ids, int64_t count) {
     const size_t rows = ids ? (size_t)count : (size_t)w->n;  // with ids: out [count, k], row r = weight row ids[r]
     if (rows == 0) return GLLMK_STATUS_OK;
-    if (raw_format(w->qt)) return raw_dequant(c, w->qt, static_cast<const uint8_t *>(w->qs), w->n, w->nb, ids, rows, out, s);
+    if (raw_format(w->qt)) return raw_dequant(c, w->qt, static_cast<const uint8_t *>(w->qs), w->n, w->nb, ids, rows, out, s, true);
     if (w->qt == GLLMK_QUANT_Q4K) {
         const size_t t = rows * w->nb * 32;
         dequant_q4k<<<grid_for(t, 256), 256, 0, s>>>((const uint8_t *)w->qs, out, w->n, w->nb, t, ids);
@@ -447,7 +440,7 @@ int32_t dequant_raw(Ctx *c, int32_t qt, const uint8_t *blocks, const uint8_t *sc
                     size_t nblocks, size_t block_size, cudaStream_t s) {
     const size_t total = nblocks * block_size;
     if (total == 0) return GLLMK_STATUS_OK;
-    if (raw_format(qt)) return raw_dequant(c, qt, blocks, (int64_t)nblocks, 1, nullptr, nblocks, out, s);
+    if (raw_format(qt)) return raw_dequant(c, qt, blocks, (int64_t)nblocks, 1, nullptr, nblocks, out, s, false);
     dequant_raw_kernel<<<grid_for(total, 256), 256, 0, s>>>(qt, blocks, scales, global, out, block_size, total);
     GK_CUDA(c, cudaGetLastError());
     return GLLMK_STATUS_OK;
