@@ -225,23 +225,34 @@ struct Dp<GLLMK_QUANT_Q6_K> {
 
 template <>
 struct Dp<GLLMK_QUANT_Q5_K> {
-    static constexpr int UNITS = 32, NW = 2;
+    static constexpr int UNITS = 16, NW = 4;
     static constexpr bool MIN = true;
     static __device__ __forceinline__ void unit(const uint8_t *b, int u, uint32_t *q, int *ko, float *ws, float *wm) {
-        const int g = u >> 3, lw = u & 7;
-        const uint32_t A = ld32<true>(b + 48 + g * 32 + 4 * lw), H = ld32<true>(b + 16 + 4 * lw);
-        q[0] = (A & 0x0F0F0F0Fu) | (((H >> (2 * g)) & 0x01010101u) << 4);
-        q[1] = ((A >> 4) & 0x0F0F0F0Fu) | (((H >> (2 * g + 1)) & 0x01010101u) << 4);
-        const float d = f16_even(b), mn = f16_even(b + 2);
-        float sc1, m1, sc2, m2;
-        scale_min_k4(2 * g, b + 4, sc1, m1);
-        scale_min_k4(2 * g + 1, b + 4, sc2, m2);
+        const int g = u >> 2, lw = u & 3;  // words lw and lw + 4 of the 32-byte group g: two sub-blocks, two words each
+        const uint32_t A0 = ld32<true>(b + 48 + g * 32 + 4 * lw), A1 = ld32<true>(b + 48 + g * 32 + 16 + 4 * lw);
+        const uint32_t H0 = ld32<true>(b + 16 + 4 * lw), H1 = ld32<true>(b + 32 + 4 * lw);
+        q[0] = (A0 & 0x0F0F0F0Fu) | (((H0 >> (2 * g)) & 0x01010101u) << 4);
+        q[1] = ((A0 >> 4) & 0x0F0F0F0Fu) | (((H0 >> (2 * g + 1)) & 0x01010101u) << 4);
+        q[2] = (A1 & 0x0F0F0F0Fu) | (((H1 >> (2 * g)) & 0x01010101u) << 4);
+        q[3] = ((A1 >> 4) & 0x0F0F0F0Fu) | (((H1 >> (2 * g + 1)) & 0x01010101u) << 4);
+        // d and dmin in one word; the twelve scale bytes as three words.  Sub-blocks 2g and 2g + 1 (get_scale_min_k4,
+        // k_quant.rs:388-397) without a branch: both forms from bytes jj = j & 3 of the words, chosen by j < 4.
+        const uint32_t dm = ld32<true>(b), w0 = ld32<true>(b + 4), w1 = ld32<true>(b + 8), w2 = ld32<true>(b + 12);
+        const float d = __half2float(__ushort_as_half((unsigned short)(dm & 0xFFFF)));
+        const float mn = __half2float(__ushort_as_half((unsigned short)(dm >> 16)));
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const int j = 2 * g + i, sh = 8 * (j & 3);
+            const uint32_t a = (w0 >> sh) & 0xFF, bb = (w1 >> sh) & 0xFF, c = (w2 >> sh) & 0xFF;
+            const uint32_t s_lo = a & 63, m_lo = bb & 63;
+            const uint32_t s_hi = (c & 0xF) | ((a >> 6) << 4), m_hi = (c >> 4) | ((bb >> 6) << 4);
+            ws[i] = ws[i + 2] = d * (float)(j < 4 ? s_lo : s_hi);
+            wm[i] = wm[i + 2] = -(mn * (float)(j < 4 ? m_lo : m_hi));
+        }
         ko[0] = g * 64 + 4 * lw;
         ko[1] = ko[0] + 32;
-        ws[0] = d * sc1;
-        ws[1] = d * sc2;
-        wm[0] = -(mn * m1);
-        wm[1] = -(mn * m2);
+        ko[2] = ko[0] + 16;
+        ko[3] = ko[0] + 48;
     }
 };
 
@@ -262,31 +273,39 @@ struct Dp<GLLMK_QUANT_Q8_K> {
 
 template <>
 struct Dp<GLLMK_QUANT_Q4_0> {
-    static constexpr int UNITS = 4, NW = 2;
+    static constexpr int UNITS = 2, NW = 4;
     static constexpr bool MIN = false;
     static __device__ __forceinline__ void unit(const uint8_t *b, int u, uint32_t *q, int *ko, float *ws, float *) {
-        const uint32_t W = ld32<false>(b + 2 + 4 * u);
+        const uint32_t W0 = ld32<false>(b + 2 + 8 * u), W1 = ld32<false>(b + 6 + 8 * u);
         // a nibble with bit 3 flipped is q - 8 in 4-bit two's complement; in the high half of a byte it is the s8 16 (q - 8)
-        q[0] = ((W ^ 0x08080808u) << 4) & 0xF0F0F0F0u;
-        q[1] = (W ^ 0x80808080u) & 0xF0F0F0F0u;
-        ko[0] = 4 * u;
-        ko[1] = 16 + 4 * u;
-        ws[0] = ws[1] = 0.0625f * f16_even(b);
+        q[0] = ((W0 ^ 0x08080808u) << 4) & 0xF0F0F0F0u;
+        q[1] = (W0 ^ 0x80808080u) & 0xF0F0F0F0u;
+        q[2] = ((W1 ^ 0x08080808u) << 4) & 0xF0F0F0F0u;
+        q[3] = (W1 ^ 0x80808080u) & 0xF0F0F0F0u;
+        ko[0] = 8 * u;
+        ko[1] = 16 + 8 * u;
+        ko[2] = 8 * u + 4;
+        ko[3] = 20 + 8 * u;
+        ws[0] = ws[1] = ws[2] = ws[3] = 0.0625f * f16_even(b);
     }
 };
 
 template <>
 struct Dp<GLLMK_QUANT_Q5_0> {
-    static constexpr int UNITS = 4, NW = 2;
+    static constexpr int UNITS = 2, NW = 4;
     static constexpr bool MIN = false;
     static __device__ __forceinline__ void unit(const uint8_t *b, int u, uint32_t *q, int *ko, float *ws, float *) {
-        const uint32_t W = ld32<false>(b + 6 + 4 * u), qh = ld32<false>(b + 2);
+        const uint32_t W0 = ld32<false>(b + 6 + 8 * u), W1 = ld32<false>(b + 10 + 8 * u), qh = ld32<false>(b + 2);
         // a 5-bit value with bit 4 flipped is q - 16 in 5-bit two's complement; three places up it is the s8 8 (q - 16)
-        q[0] = ((((W & 0x0F0F0F0Fu) | (spread4(qh >> (4 * u)) << 4)) ^ 0x10101010u) << 3) & 0xF8F8F8F8u;
-        q[1] = (((((W >> 4) & 0x0F0F0F0Fu) | (spread4(qh >> (16 + 4 * u)) << 4)) ^ 0x10101010u) << 3) & 0xF8F8F8F8u;
-        ko[0] = 4 * u;
-        ko[1] = 16 + 4 * u;
-        ws[0] = ws[1] = 0.125f * f16_even(b);
+        q[0] = ((((W0 & 0x0F0F0F0Fu) | (spread4(qh >> (8 * u)) << 4)) ^ 0x10101010u) << 3) & 0xF8F8F8F8u;
+        q[1] = (((((W0 >> 4) & 0x0F0F0F0Fu) | (spread4(qh >> (16 + 8 * u)) << 4)) ^ 0x10101010u) << 3) & 0xF8F8F8F8u;
+        q[2] = ((((W1 & 0x0F0F0F0Fu) | (spread4(qh >> (8 * u + 4)) << 4)) ^ 0x10101010u) << 3) & 0xF8F8F8F8u;
+        q[3] = (((((W1 >> 4) & 0x0F0F0F0Fu) | (spread4(qh >> (20 + 8 * u)) << 4)) ^ 0x10101010u) << 3) & 0xF8F8F8F8u;
+        ko[0] = 8 * u;
+        ko[1] = 16 + 8 * u;
+        ko[2] = 8 * u + 4;
+        ko[3] = 20 + 8 * u;
+        ws[0] = ws[1] = ws[2] = ws[3] = 0.125f * f16_even(b);
     }
 };
 
