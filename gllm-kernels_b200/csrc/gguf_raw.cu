@@ -192,24 +192,35 @@ __device__ __forceinline__ uint32_t ld32(const uint8_t *p) {
 // bits 0..3 of v -> bit 0 of bytes 0..3
 __device__ __forceinline__ uint32_t spread4(uint32_t v) { return ((v & 0xFu) * 0x00204081u) & 0x01010101u; }
 
-// Per format: UNITS per block, NW words per unit, MIN = has a min term.
-// unit(b, u, q, ko, ws, wm): words q[] (four values each, as s8), their element offsets ko[] in the block
-// (multiples of 4, inside one 32-element group), weight factors ws[] and min terms wm[].
+// Per format: UNITS per block, NW words per unit (NP = NW / 2 pairs), MIN = has a min term.
+// unit(b, u, q, ko, ws, wm): words q[] (four values each, as s8); words 2i and 2i + 1 are neighbours in k and lie
+// in one scale group: pair i starts at element ko[i] of the block (a multiple of 8) and has the weight factor
+// ws[i] and the min term wm[i].
 template <int QT>
 struct Dp;
 
+// 6-bit fields -> s8 4 (q - 32): bit 5 flipped (q - 32 in 6-bit two's complement), two places up
+__device__ __forceinline__ uint32_t q6_word(uint32_t lo4, uint32_t hi2_at_4) {
+    return ((((lo4 & 0x0F0F0F0Fu) | (hi2_at_4 & 0x30303030u)) ^ 0x20202020u) << 2) & 0xFCFCFCFCu;
+}
+
 template <>
 struct Dp<GLLMK_QUANT_Q6_K> {
-    static constexpr int UNITS = 16, NW = 4;
+    static constexpr int UNITS = 8, NW = 8;
     static constexpr bool MIN = false;
     static __device__ __forceinline__ void unit(const uint8_t *b, int u, uint32_t *q, int *ko, float *ws, float *) {
-        const int g = u >> 3, lw = u & 7, is = lw >> 2;
-        const uint32_t A = ld32<true>(b + g * 64 + 4 * lw), B = ld32<true>(b + g * 64 + 32 + 4 * lw), H = ld32<true>(b + 128 + g * 32 + 4 * lw);
-        // a 6-bit value with bit 5 flipped is q - 32 in 6-bit two's complement; two places up it is the s8 4 (q - 32)
-        q[0] = ((((A & 0x0F0F0F0Fu) | ((H << 4) & 0x30303030u)) ^ 0x20202020u) << 2) & 0xFCFCFCFCu;
-        q[1] = ((((B & 0x0F0F0F0Fu) | ((H << 2) & 0x30303030u)) ^ 0x20202020u) << 2) & 0xFCFCFCFCu;
-        q[2] = (((((A >> 4) & 0x0F0F0F0Fu) | (H & 0x30303030u)) ^ 0x20202020u) << 2) & 0xFCFCFCFCu;
-        q[3] = (((((B >> 4) & 0x0F0F0F0Fu) | ((H >> 2) & 0x30303030u)) ^ 0x20202020u) << 2) & 0xFCFCFCFCu;
+        const int g = u >> 2, p = u & 3, is = p >> 1;  // bytes 8p .. 8p + 7 of the half-block's ql / qh runs
+        const uint2 A = *reinterpret_cast<const uint2 *>(b + g * 64 + 8 * p);
+        const uint2 B = *reinterpret_cast<const uint2 *>(b + g * 64 + 32 + 8 * p);
+        const uint2 H = *reinterpret_cast<const uint2 *>(b + 128 + g * 32 + 8 * p);
+        q[0] = q6_word(A.x, H.x << 4);
+        q[1] = q6_word(A.y, H.y << 4);
+        q[2] = q6_word(B.x, H.x << 2);
+        q[3] = q6_word(B.y, H.y << 2);
+        q[4] = q6_word(A.x >> 4, H.x);
+        q[5] = q6_word(A.y >> 4, H.y);
+        q[6] = q6_word(B.x >> 4, H.x >> 2);
+        q[7] = q6_word(B.y >> 4, H.y >> 2);
         // the eight scale bytes of this half in one load; run j uses byte is + 2 j
         const uint2 S = *reinterpret_cast<const uint2 *>(b + 192 + g * 8);
         const uint32_t s01 = S.x >> (8 * is), s23 = S.y >> (8 * is);
@@ -219,7 +230,7 @@ struct Dp<GLLMK_QUANT_Q6_K> {
         ws[2] = d * (float)(int8_t)(s23 & 0xFF);
         ws[3] = d * (float)(int8_t)((s23 >> 16) & 0xFF);
 #pragma unroll
-        for (int j = 0; j < 4; j++) ko[j] = g * 128 + 32 * j + 4 * lw;
+        for (int j = 0; j < 4; j++) ko[j] = g * 128 + 32 * j + 8 * p;
     }
 };
 
@@ -228,13 +239,13 @@ struct Dp<GLLMK_QUANT_Q5_K> {
     static constexpr int UNITS = 16, NW = 4;
     static constexpr bool MIN = true;
     static __device__ __forceinline__ void unit(const uint8_t *b, int u, uint32_t *q, int *ko, float *ws, float *wm) {
-        const int g = u >> 2, lw = u & 3;  // words lw and lw + 4 of the 32-byte group g: two sub-blocks, two words each
-        const uint32_t A0 = ld32<true>(b + 48 + g * 32 + 4 * lw), A1 = ld32<true>(b + 48 + g * 32 + 16 + 4 * lw);
-        const uint32_t H0 = ld32<true>(b + 16 + 4 * lw), H1 = ld32<true>(b + 32 + 4 * lw);
-        q[0] = (A0 & 0x0F0F0F0Fu) | (((H0 >> (2 * g)) & 0x01010101u) << 4);
-        q[1] = ((A0 >> 4) & 0x0F0F0F0Fu) | (((H0 >> (2 * g + 1)) & 0x01010101u) << 4);
-        q[2] = (A1 & 0x0F0F0F0Fu) | (((H1 >> (2 * g)) & 0x01010101u) << 4);
-        q[3] = ((A1 >> 4) & 0x0F0F0F0Fu) | (((H1 >> (2 * g + 1)) & 0x01010101u) << 4);
+        const int g = u >> 2, p = u & 3;  // bytes 8p .. 8p + 7 of the 32-byte group g: two sub-blocks, a pair each
+        const uint2 A = *reinterpret_cast<const uint2 *>(b + 48 + g * 32 + 8 * p);
+        const uint2 H = *reinterpret_cast<const uint2 *>(b + 16 + 8 * p);
+        q[0] = (A.x & 0x0F0F0F0Fu) | (((H.x >> (2 * g)) & 0x01010101u) << 4);
+        q[1] = (A.y & 0x0F0F0F0Fu) | (((H.y >> (2 * g)) & 0x01010101u) << 4);
+        q[2] = ((A.x >> 4) & 0x0F0F0F0Fu) | (((H.x >> (2 * g + 1)) & 0x01010101u) << 4);
+        q[3] = ((A.y >> 4) & 0x0F0F0F0Fu) | (((H.y >> (2 * g + 1)) & 0x01010101u) << 4);
         // d and dmin in one word; the twelve scale bytes as three words.  Sub-blocks 2g and 2g + 1 (get_scale_min_k4,
         // k_quant.rs:388-397) without a branch: both forms from bytes jj = j & 3 of the words, chosen by j < 4.
         const uint32_t dm = ld32<true>(b), w0 = ld32<true>(b + 4), w1 = ld32<true>(b + 8), w2 = ld32<true>(b + 12);
@@ -246,13 +257,11 @@ struct Dp<GLLMK_QUANT_Q5_K> {
             const uint32_t a = (w0 >> sh) & 0xFF, bb = (w1 >> sh) & 0xFF, c = (w2 >> sh) & 0xFF;
             const uint32_t s_lo = a & 63, m_lo = bb & 63;
             const uint32_t s_hi = (c & 0xF) | ((a >> 6) << 4), m_hi = (c >> 4) | ((bb >> 6) << 4);
-            ws[i] = ws[i + 2] = d * (float)(j < 4 ? s_lo : s_hi);
-            wm[i] = wm[i + 2] = -(mn * (float)(j < 4 ? m_lo : m_hi));
+            ws[i] = d * (float)(j < 4 ? s_lo : s_hi);
+            wm[i] = -(mn * (float)(j < 4 ? m_lo : m_hi));
         }
-        ko[0] = g * 64 + 4 * lw;
+        ko[0] = g * 64 + 8 * p;
         ko[1] = ko[0] + 32;
-        ko[2] = ko[0] + 16;
-        ko[3] = ko[0] + 48;
     }
 };
 
@@ -261,13 +270,13 @@ struct Dp<GLLMK_QUANT_Q8_K> {
     static constexpr int UNITS = 16, NW = 4;
     static constexpr bool MIN = false;
     static __device__ __forceinline__ void unit(const uint8_t *b, int u, uint32_t *q, int *ko, float *ws, float *) {
-        const float d = __uint_as_float(ld32<true>(b));
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-            ko[j] = 4 * (u + 16 * j);
-            q[j] = ld32<true>(b + 4 + ko[j]);
-            ws[j] = d;
-        }
+        ws[0] = ws[1] = __uint_as_float(ld32<true>(b));
+        ko[0] = 8 * u;
+        ko[1] = 128 + 8 * u;
+        q[0] = ld32<true>(b + 4 + 8 * u);
+        q[1] = ld32<true>(b + 8 + 8 * u);
+        q[2] = ld32<true>(b + 132 + 8 * u);
+        q[3] = ld32<true>(b + 136 + 8 * u);
     }
 };
 
@@ -279,14 +288,12 @@ struct Dp<GLLMK_QUANT_Q4_0> {
         const uint32_t W0 = ld32<false>(b + 2 + 8 * u), W1 = ld32<false>(b + 6 + 8 * u);
         // a nibble with bit 3 flipped is q - 8 in 4-bit two's complement; in the high half of a byte it is the s8 16 (q - 8)
         q[0] = ((W0 ^ 0x08080808u) << 4) & 0xF0F0F0F0u;
-        q[1] = (W0 ^ 0x80808080u) & 0xF0F0F0F0u;
-        q[2] = ((W1 ^ 0x08080808u) << 4) & 0xF0F0F0F0u;
+        q[1] = ((W1 ^ 0x08080808u) << 4) & 0xF0F0F0F0u;
+        q[2] = (W0 ^ 0x80808080u) & 0xF0F0F0F0u;
         q[3] = (W1 ^ 0x80808080u) & 0xF0F0F0F0u;
         ko[0] = 8 * u;
         ko[1] = 16 + 8 * u;
-        ko[2] = 8 * u + 4;
-        ko[3] = 20 + 8 * u;
-        ws[0] = ws[1] = ws[2] = ws[3] = 0.0625f * f16_even(b);
+        ws[0] = ws[1] = 0.0625f * f16_even(b);
     }
 };
 
@@ -298,14 +305,12 @@ struct Dp<GLLMK_QUANT_Q5_0> {
         const uint32_t W0 = ld32<false>(b + 6 + 8 * u), W1 = ld32<false>(b + 10 + 8 * u), qh = ld32<false>(b + 2);
         // a 5-bit value with bit 4 flipped is q - 16 in 5-bit two's complement; three places up it is the s8 8 (q - 16)
         q[0] = ((((W0 & 0x0F0F0F0Fu) | (spread4(qh >> (8 * u)) << 4)) ^ 0x10101010u) << 3) & 0xF8F8F8F8u;
-        q[1] = (((((W0 >> 4) & 0x0F0F0F0Fu) | (spread4(qh >> (16 + 8 * u)) << 4)) ^ 0x10101010u) << 3) & 0xF8F8F8F8u;
-        q[2] = ((((W1 & 0x0F0F0F0Fu) | (spread4(qh >> (8 * u + 4)) << 4)) ^ 0x10101010u) << 3) & 0xF8F8F8F8u;
+        q[1] = ((((W1 & 0x0F0F0F0Fu) | (spread4(qh >> (8 * u + 4)) << 4)) ^ 0x10101010u) << 3) & 0xF8F8F8F8u;
+        q[2] = (((((W0 >> 4) & 0x0F0F0F0Fu) | (spread4(qh >> (16 + 8 * u)) << 4)) ^ 0x10101010u) << 3) & 0xF8F8F8F8u;
         q[3] = (((((W1 >> 4) & 0x0F0F0F0Fu) | (spread4(qh >> (20 + 8 * u)) << 4)) ^ 0x10101010u) << 3) & 0xF8F8F8F8u;
         ko[0] = 8 * u;
         ko[1] = 16 + 8 * u;
-        ko[2] = 8 * u + 4;
-        ko[3] = 20 + 8 * u;
-        ws[0] = ws[1] = ws[2] = ws[3] = 0.125f * f16_even(b);
+        ws[0] = ws[1] = 0.125f * f16_even(b);
     }
 };
 
@@ -341,12 +346,12 @@ __global__ void __launch_bounds__(RG_WARPS * 32) raw_gemv_kernel(const RawGemvPa
         }
         for (int t0 = 0; t0 < p.m; t0 += MT) {
             float acc[R][MT];
-            const int2 *xq[MT];  // four s16 activations per entry
+            const int16_t *xq[MT];
             const float *xs[MT];
 #pragma unroll
             for (int t = 0; t < MT; t++) {
                 const int tok = t0 + t < p.m ? t0 + t : p.m - 1;  // surplus slots repeat the last token; not stored
-                xq[t] = reinterpret_cast<const int2 *>(p.xq + (size_t)tok * p.k);
+                xq[t] = p.xq + (size_t)tok * p.k;
                 xs[t] = p.xs + (size_t)tok * k32;
 #pragma unroll
                 for (int r = 0; r < R; r++) acc[r][t] = 0.0f;
@@ -384,24 +389,28 @@ __global__ void __launch_bounds__(RG_WARPS * 32) raw_gemv_kernel(const RawGemvPa
                 for (int u = lane; u < nblk * D::UNITS; u += 32) {
                     const int blk = u / D::UNITS;
                     uint32_t q[R][D::NW];
-                    int ko[D::NW];
-                    float ws[R][D::NW], wm[R][D::NW];
+                    int ko[D::NW / 2];
+                    float ws[R][D::NW / 2], wm[R][D::NW / 2];
 #pragma unroll
                     for (int r = 0; r < R; r++) D::unit(sb[r] + blk * F::DB, u % D::UNITS, q[r], ko, ws[r], wm[r]);
                     const int kb = (b0 + blk) * F::BS;
 #pragma unroll
-                    for (int j = 0; j < D::NW; j++) {
+                    for (int j = 0; j < D::NW / 2; j++) {
                         const int kk = kb + ko[j];
 #pragma unroll
                         for (int t = 0; t < MT; t++) {
-                            const int2 xw = __ldg(xq[t] + (kk >> 2));
+                            const int4 xw = __ldg(reinterpret_cast<const int4 *>(xq[t] + kk));  // eight s16 activations
                             const float s = __ldg(xs[t] + (kk >> 5));
                             float sx = 0.0f;
-                            if (D::MIN) sx = (float)__dp2a_hi(xw.y, 0x01010101, __dp2a_lo(xw.x, 0x01010101, 0));
+                            if (D::MIN)
+                                sx = (float)__dp2a_hi(xw.w, 0x01010101, __dp2a_lo(xw.z, 0x01010101,
+                                            __dp2a_hi(xw.y, 0x01010101, __dp2a_lo(xw.x, 0x01010101, 0))));
 #pragma unroll
                             for (int r = 0; r < R; r++) {
-                                // s16 x s8 products: elements 0, 1 of the word against xw.x, elements 2, 3 against xw.y
-                                const float dot = (float)__dp2a_hi(xw.y, (int)q[r][j], __dp2a_lo(xw.x, (int)q[r][j], 0));
+                                // s16 x s8 products: a word's elements 0, 1 against one register, 2, 3 against the next
+                                const int q0 = (int)q[r][2 * j], q1 = (int)q[r][2 * j + 1];
+                                const float dot =
+                                    (float)__dp2a_hi(xw.w, q1, __dp2a_lo(xw.z, q1, __dp2a_hi(xw.y, q0, __dp2a_lo(xw.x, q0, 0))));
                                 if (D::MIN) acc[r][t] = fmaf(s, fmaf(ws[r][j], dot, wm[r][j] * sx), acc[r][t]);
                                 else acc[r][t] = fmaf(s * ws[r][j], dot, acc[r][t]);
                             }
