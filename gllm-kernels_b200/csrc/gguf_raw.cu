@@ -236,19 +236,22 @@ struct Dp<GLLMK_QUANT_Q6_K> {
 
 template <>
 struct Dp<GLLMK_QUANT_Q5_K> {
-    static constexpr int UNITS = 16, NW = 4;
+    static constexpr int UNITS = 8, NW = 8;
     static constexpr bool MIN = true;
     static __device__ __forceinline__ void unit(const uint8_t *b, int u, uint32_t *q, int *ko, float *ws, float *wm) {
-        const int g = u >> 2, p = u & 3;  // bytes 8p .. 8p + 7 of the 32-byte group g: two sub-blocks, a pair each
-        const uint2 A = *reinterpret_cast<const uint2 *>(b + 48 + g * 32 + 8 * p);
-        const uint2 H = *reinterpret_cast<const uint2 *>(b + 16 + 8 * p);
-        q[0] = (A.x & 0x0F0F0F0Fu) | (((H.x >> (2 * g)) & 0x01010101u) << 4);
-        q[1] = (A.y & 0x0F0F0F0Fu) | (((H.y >> (2 * g)) & 0x01010101u) << 4);
-        q[2] = ((A.x >> 4) & 0x0F0F0F0Fu) | (((H.x >> (2 * g + 1)) & 0x01010101u) << 4);
-        q[3] = ((A.y >> 4) & 0x0F0F0F0Fu) | (((H.y >> (2 * g + 1)) & 0x01010101u) << 4);
+        const int g = u >> 1, p = u & 1;  // bytes 16p .. 16p + 15 of the 32-byte group g: two sub-blocks, two pairs each
+        const uint4 A = *reinterpret_cast<const uint4 *>(b + 48 + g * 32 + 16 * p);
+        const uint4 H = *reinterpret_cast<const uint4 *>(b + 16 + 16 * p);
+        const uint32_t aw[4] = {A.x, A.y, A.z, A.w}, hw[4] = {H.x, H.y, H.z, H.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            q[i] = (aw[i] & 0x0F0F0F0Fu) | (((hw[i] >> (2 * g)) & 0x01010101u) << 4);
+            q[4 + i] = ((aw[i] >> 4) & 0x0F0F0F0Fu) | (((hw[i] >> (2 * g + 1)) & 0x01010101u) << 4);
+        }
         // d and dmin in one word; the twelve scale bytes as three words.  Sub-blocks 2g and 2g + 1 (get_scale_min_k4,
         // k_quant.rs:388-397) without a branch: both forms from bytes jj = j & 3 of the words, chosen by j < 4.
-        const uint32_t dm = ld32<true>(b), w0 = ld32<true>(b + 4), w1 = ld32<true>(b + 8), w2 = ld32<true>(b + 12);
+        const uint4 hd = *reinterpret_cast<const uint4 *>(b);
+        const uint32_t dm = hd.x, w0 = hd.y, w1 = hd.z, w2 = hd.w;
         const float d = __half2float(__ushort_as_half((unsigned short)(dm & 0xFFFF)));
         const float mn = __half2float(__ushort_as_half((unsigned short)(dm >> 16)));
 #pragma unroll
@@ -257,11 +260,13 @@ struct Dp<GLLMK_QUANT_Q5_K> {
             const uint32_t a = (w0 >> sh) & 0xFF, bb = (w1 >> sh) & 0xFF, c = (w2 >> sh) & 0xFF;
             const uint32_t s_lo = a & 63, m_lo = bb & 63;
             const uint32_t s_hi = (c & 0xF) | ((a >> 6) << 4), m_hi = (c >> 4) | ((bb >> 6) << 4);
-            ws[i] = d * (float)(j < 4 ? s_lo : s_hi);
-            wm[i] = -(mn * (float)(j < 4 ? m_lo : m_hi));
+            ws[2 * i] = ws[2 * i + 1] = d * (float)(j < 4 ? s_lo : s_hi);
+            wm[2 * i] = wm[2 * i + 1] = -(mn * (float)(j < 4 ? m_lo : m_hi));
         }
-        ko[0] = g * 64 + 8 * p;
-        ko[1] = ko[0] + 32;
+        ko[0] = g * 64 + 16 * p;
+        ko[1] = ko[0] + 8;
+        ko[2] = ko[0] + 32;
+        ko[3] = ko[0] + 40;
     }
 };
 
