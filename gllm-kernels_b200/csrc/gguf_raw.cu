@@ -1,11 +1,14 @@
 // The other GGUF block formats of the reference's CPU quant path — Q6_K, Q5_K, Q8_K (256 elements per block) and
 // Q4_0, Q5_0 (32 elements per block) — kept on the device as the reference stores them, row after row of blocks
-// (Q6_K blocks, 210 bytes, sit in 224-byte slots so that every field starts on a 4-byte boundary of a 16-byte
-// aligned block).  One decode rule per format (an "item" = the elements one data byte, or byte group,
-// yields), used by the matrix decode / embedding gather and by a streaming GEMV: a warp owns two weight rows,
-// brings them into shared memory in 16-byte loads, and accumulates integer dot products (dp2a) against s16 fixed-point activations.  The decode keeps
-// the reference's operation order (separately rounded products, no fused multiply-add), so decoded values are
-// bit-exact; the GEMV rounds the activations to 16 bits per 32-element group (error ~1.5e-5, far inside the 2e-3 bar).
+// (Q6_K blocks, 210 bytes, sit in 224-byte slots so that every block starts on a 16-byte boundary).
+//
+// Decode: one rule per format (an "item" = the elements one data byte, or byte group, yields) with the reference's
+// operation order (separately rounded products, no fused multiply-add): matrix decode, embedding gather and the
+// host drop-ins are bit-exact.
+//
+// GEMV: a warp owns two weight rows, streams them through two shared-memory stages with cp.async and accumulates
+// integer dot products (dp2a) against s16 fixed-point activations (16 bits per 32-element group, error ~1.5e-5
+// of the group maximum, far inside the 2e-3 bar of the decode path).
 //
 // Reference: src/macros/quant_primitive/k_quant.rs:92-101 (Q8_K), :381-436 (Q5_K), :441-472 (Q6_K);
 //            src/macros/quant_primitive/classic.rs:15-29 (Q4_0), :484-504 (Q5_0); block structs src/quant.rs:132-157, 254-275.

@@ -52,8 +52,8 @@ enum {
     GLLMK_QUANT_NVFP4 = 4, /* QuantType::Nvfp4   64 el /  36 B  (src/quant.rs:366-371) */
     GLLMK_QUANT_INT8 = 5,  /* plain s8 matrix of the W8A8 path (gllmk_int8_weight_upload); not a block format */
     /* The other GGUF formats of the reference's CPU quant path.  Kept on the device as the reference stores them
-     * and served by a streaming CUDA-core GEMV (f32 activations and outputs, any m) plus decode / gather /
-     * unpack; gllmk_gemm with bf16 operands, gllmk_gemm_grouped, gllmk_gemv_allgather and gllmk_ffn_decode
+     * (Q6_K in 224-byte slots) and served by a streaming CUDA-core integer-dot GEMV (f32 activations and outputs,
+     * any m) plus decode / gather / unpack; gllmk_gemm with bf16 operands, gllmk_gemm_grouped, gllmk_gemv_allgather and gllmk_ffn_decode
      * answer GLLMK_STATUS_UNSUPPORTED for them. */
     GLLMK_QUANT_Q6_K = 6,  /* QuantType::Q6K    256 el / 210 B  (src/quant.rs:143-148) */
     GLLMK_QUANT_Q5_K = 7,  /* QuantType::Q5K    256 el / 176 B  (src/quant.rs:132-138) */
