@@ -9,6 +9,7 @@ from .quant import QuantType, E2M1_LUT_F32, decode_e8m0_scale  # noqa: F401
 from ._lib import GllmkError, Status, lib, lib_path, build_library  # noqa: F401
 from .kernels import GpuKernels, Weight  # noqa: F401
 from .shard import PeerExchange, ShardedLinear, gpu_sharded_linear, shard_rows, slice_blocks  # noqa: F401
+from .gguf import GgufFile, GgufError, TensorInfo, write_gguf  # noqa: F401
 
-__all__ = ["QuantType", "E2M1_LUT_F32", "decode_e8m0_scale", "GllmkError", "Status", "lib", "lib_path",
+__all__ = ["GgufFile", "GgufError", "TensorInfo", "write_gguf", "QuantType", "E2M1_LUT_F32", "decode_e8m0_scale", "GllmkError", "Status", "lib", "lib_path",
            "build_library", "GpuKernels", "Weight", "PeerExchange", "ShardedLinear", "gpu_sharded_linear", "shard_rows", "slice_blocks"]
