@@ -163,7 +163,10 @@ class GgufFile:
 
     def close(self) -> None:
         if getattr(self, "_mm", None) is not None:
-            self._mm.close()
+            try:
+                self._mm.close()
+            except BufferError:  # a caller still holds a view from raw(): the mapping goes when the view does
+                pass
             self._mm = None
         if getattr(self, "_f", None) is not None:
             self._f.close()
@@ -186,12 +189,12 @@ class GgufFile:
         return np.frombuffer(self._mm, dtype=np.uint8, count=t.nbytes, offset=self.data_start + t.offset)
 
     def load(self, K, name: str):
-        """Quantized tensor -> `Weight` in HBM (repacked once by `K.upload`); F32 / F16 -> numpy array [n, k]."""
+        """Quantized tensor -> `Weight` in HBM (repacked once by `K.upload`); F32 / F16 -> numpy array [n, k] (a copy)."""
         t = self._tensors[name]
         if t.ggml_type == GGML_F32:
-            return self.raw(name).view(np.float32).reshape(t.n, t.k)
+            return self.raw(name).view(np.float32).reshape(t.n, t.k).copy()
         if t.ggml_type == GGML_F16:
-            return self.raw(name).view(np.float16).reshape(t.n, t.k)
+            return self.raw(name).view(np.float16).reshape(t.n, t.k).copy()
         qt = t.quant_type
         if qt is None:
             raise GgufError(f"tensor {name}: ggml type {t.ggml_type} is not served")
