@@ -30,6 +30,11 @@ if ROOT not in sys.path:
 N_FF, D_MODEL = 28672, 8192
 Q4K_BLOCK_BYTES, Q4K_BLOCK = 144, 256
 METRIC = "quant GEMV weight-GB/s (Q4_K decode, 70B-shaped FFN)"
+# what the decode kernel computes in: packed u4 weights as they are x activations re-expressed per 256-block as two
+# s8 digits with one f32 scale (x = amax/127 * (d1 + d2/254)), exact s32 dot products (mma.sync u8 x s8), sub-block
+# scales applied as integers, one f32 multiply-add per block for d, dmin and the activation scale, f32 sums over blocks
+DTYPE = "u4 x (2 x s8 digit-split f32 activations), s32 dot products then f32 accumulate"
+DTYPE_REF = "u4 decoded to f32 x f32 activations, sequential f32 accumulate (CPU port of the reference)"
 GEMV_DRAM_TRAFFIC_PER_LAUNCH = 276.03e6
 
 
@@ -91,6 +96,59 @@ class ClockSampler(threading.Thread):
 def shard_rows(n: int, world: int, rank: int):
     """N-wise split in multiples of 16 rows (the row tile of the device layout); the package's rule."""
     return importlib.import_module("gllm-kernels_b200").shard_rows(n, world, rank)
+
+
+# ------------------------------------------------------------------------------------------------
+# Parity of a full-size product on a SAMPLE of its weight rows (the oracle is scalar C: whole matrices of the
+# benchmark shapes would take minutes, 256 rows x every token take seconds).  Used by the bench's `parity` records
+# and by tests/test_gpu_shapes.py, so both check the same thing.
+PARITY_METRIC = "max_i |y_i - ref_i| / max(|ref_i|, rms(ref))"
+
+
+def sample_rows(n: int, count: int = 256, seed: int = 0):
+    """`count` weight rows: the first and the last 32 (edge tiles) and a random draw of the rest, sorted."""
+    import numpy as np
+    if n <= count:
+        return np.arange(n)
+    rng = np.random.default_rng(seed)
+    mid = rng.choice(np.arange(32, n - 32), size=count - 64, replace=False)
+    return np.sort(np.concatenate([np.arange(32), mid, np.arange(n - 32, n)]))
+
+
+def sampled_parity(O, oid, blocks, n, k, rows, x_host, y, bar, scales=None, global_scale=1.0, sequential=False, threads=8):
+    """Compares columns `rows` of y [m, n] (torch, any float dtype) with the oracle's product of x_host [m, k] and
+    the sampled rows of the quantized weight.  blocks / scales: the whole matrix in the reference's block format
+    (torch uint8 on the device, or numpy).  sequential=True: the reference's own quantized matmul (block-ordered
+    f32 sum, Q4_K / Q8_0 / GGUF formats); False: its decode followed by its f32 GEMM loop (scalar_gemm order)."""
+    import numpy as np
+    import torch
+
+    def take(buf, per_row):
+        if isinstance(buf, np.ndarray):
+            return np.ascontiguousarray(buf.reshape(n, per_row)[rows]).reshape(-1)
+        idx = torch.from_numpy(np.asarray(rows)).to(buf.device)
+        return buf.reshape(n, per_row)[idx].cpu().numpy().reshape(-1)
+    m = x_host.shape[0]
+    hb = take(blocks, blocks.numel() // n if hasattr(blocks, "numel") else blocks.size // n)
+    hs = None if scales is None else take(scales, scales.numel() // n if hasattr(scales, "numel") else scales.size // n)
+    if sequential:
+        ref = O.quant_matmul(hb, np.ascontiguousarray(x_host.T), oid, len(rows), m, k, threads=threads).T
+    else:
+        ref = O.gemm_f32_nt(x_host, O.dequant_matrix(oid, hb, len(rows), k, scales=hs, global_scale=global_scale))
+    got = y[:, torch.from_numpy(np.asarray(rows)).to(y.device)].to(torch.float32).cpu().numpy()
+    err = O.rel_err(got, ref)
+    return {"metric": PARITY_METRIC, "rows_sampled": int(len(rows)), "tokens": int(m), "rel_err": err, "bar": bar,
+            "ok": bool(err <= bar),
+            "oracle": "reference quantized matmul (sequential f32)" if sequential else "reference decode + f32 GEMM loop order"}
+
+
+def workload_config(L, M, fused):
+    """The workload, named identically by both arms (the GPU arm adds how it ran under `run`)."""
+    return {"workload": f"70B-shaped FFN decode (W gate/up [28672, 8192], W down [8192, 28672], Q4_K), {L} layers, M={M}; " +
+                        ("gate and up stored as one 57344-row weight (2 products per layer)" if fused
+                         else "one product per matrix (3 per layer)"),
+            "layers": L, "M": M, "N_ff": N_FF, "d_model": D_MODEL,
+            "weight_bytes_per_step": L * 3 * N_FF * (D_MODEL // Q4K_BLOCK) * Q4K_BLOCK_BYTES}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -164,10 +222,9 @@ def run_ours(args):
             if world == 1:
                 K.gemv(w, x, y=ys[i])
             elif ex is not None:
-                # gate and up read the same x and nothing reads them before down: one barrier covers both
-                ex.gemv(w, x, i, r0, n)
-                if name != "gate":
-                    ex.barrier()
+                # every product waits (in its staging kernel) for all ranks' bands of the product before it, as a
+                # real decode step must, and signals its own completion from the GEMV's last block
+                ex.gemv_chained(w, x, i, r0, n)
             else:
                 K.gemv(w, x, y=gbufs[i][rank])
                 dist.all_gather_into_tensor(gbufs[i].view(-1), gbufs[i][rank].view(-1))
@@ -204,6 +261,8 @@ def run_ours(args):
     ev0.record()
     for _ in range(args.steps):
         step()
+    if ex is not None:
+        ex.wait()  # the last product's bands have landed on this rank
     ev1.record()
     torch.cuda.synchronize()
     if world > 1:
@@ -242,19 +301,53 @@ def run_ours(args):
                        "outputs are page-locked host buffers, transferred inside the timed region (x read by the staging "
                        "kernel over PCIe, y by a device-to-host copy), one synchronous call per product"}
 
+    elif ex is not None:
+        # sharded: every rank copies the step's activations from page-locked host memory, runs its band of every
+        # product (bands exchanged over NVLink as above) and reads the last product's gathered y back to the host
+        xd = {"model": torch.empty_like(x_model), "ff": torch.empty_like(x_ff)}
+        xp = {"model": torch.from_numpy(xh_model), "ff": torch.from_numpy(xh_ff)}
+        last = len(weights) - 1
+        y_last = ex.local_tensor(last, (M, weights[last][2]))
+        y_host = torch.empty((M, weights[last][2]), dtype=torch.float32, pin_memory=True)
+
+        def step_host():
+            for i, (name, w, n, k, r0, r1) in enumerate(weights):
+                key = "ff" if name == "down" else "model"
+                xd[key].copy_(xp[key], non_blocking=True)
+                ex.gemv_chained(w, xd[key], i, r0, n)
+            ex.wait()
+            y_host.copy_(y_last, non_blocking=True)
+            torch.cuda.synchronize()
+        for _ in range(3):
+            step_host()
+        dist.barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            step_host()
+        dt_t = torch.tensor([(time.perf_counter() - t0) / args.steps], device=dev)
+        dist.all_reduce(dt_t, op=dist.ReduceOp.MAX)
+        e2e = {"value": weight_bytes_total / dt_t.item() / 1e9, "unit": "GB/s",
+               "h2d_bytes_per_step": world * L * sum(M * k * 4 for _, n, k in shapes),
+               "d2h_bytes_per_step": world * M * weights[last][2] * 4,
+               "note": "per step every rank copies each product's activations from page-locked host memory, the bands "
+                       "are exchanged over NVLink, and every rank reads the last product's gathered y back; host "
+                       "launches (no graph), wall clock, max over ranks"}
+
+    parity_multi = None
+    if world > 1:
+        parity_multi = multi_gpu_parity(args, K, gk, torch, dev, weights, ex, gbufs, x_model, M, world, rank)
+
     peak, peak_kind = measured_peaks()
     out = {
         "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": "u4 weights x f32 activations, f32 accumulate", "data": "synthetic",
-        "config": {"workload": f"config 5: 70B-shaped FFN decode, {L} layers x (gate, up, down) Q4_K, M={M}; " +
-                               ("gate and up stored as one 57344-row weight (2 products per layer)" if fused
-                                else "one product per matrix (3 per layer)"),
-                   "layers": L, "M": M, "N_ff": N_FF, "d_model": D_MODEL, "weight_bytes_per_step": weight_bytes_total,
-                   "l2": "per-GPU weight set larger than L2, no flush", "cuda_graph": graphed,
-                   "parallelism": "single GPU" if world == 1 else (
-                       f"N-wise row shards x{world}, GEMV stores its band into every rank's y over NVLink peer pointers + flag barrier"
-                       if ex is not None else f"N-wise row shards x{world} + NCCL all-gather")},
+        "vs_baseline": None, "dtype": DTYPE, "data": "synthetic",
+        "config": workload_config(L, M, fused),
+        "run": {"l2": "per-GPU weight set larger than L2, no flush", "cuda_graph": graphed,
+                "parallelism": "single GPU" if world == 1 else (
+                    f"N-wise row shards x{world}, GEMV stores its band into every rank's y over NVLink peer pointers, "
+                    f"flags signalled by the GEMV's last block and awaited by the next product's staging kernel"
+                    if ex is not None else f"N-wise row shards x{world} + NCCL all-gather")},
         "roofline": {"bound": "hbm", "achieved": algo_bytes_step / (ms_step * 1e-3) / 1e9 / world, "peak": peak,
                      "unit": "GB/s", "frac": algo_bytes_step / (ms_step * 1e-3) / 1e9 / world / peak,
                      # dram__bytes_read + dram__bytes_write of one gemv_kernel launch on the 264.2 MB gate||up weight,
@@ -263,13 +356,15 @@ def run_ours(args):
                      "traffic_note": "bytes per gemv_kernel launch on the 57344x8192 gate||up weight (algorithmic 264.50e6), ncu",
                      "peak_kind": peak_kind,
                      "kernel": "gemv_kernel<Q4_K, 1 n-tile> (+ stage_x_kernel), per-GPU average"},
-        "gpu_launches": args.steps * len(weights) * 2 if ex is None else args.steps * (len(weights) * 2 + 2 * L),
+        "gpu_launches": args.steps * len(weights) * 2 + (1 if ex is not None else 0),
         "device_status": K.status(),
         "clocks": clocks,
         "e2e": e2e,
     }
     if world == 1 and rank == 0 and not args.no_extra:
         out["extra"] = extra_configs(K, gk, torch, dev, peak)
+    if parity_multi is not None:
+        out["parity"] = parity_multi
     if keep_host:
         out["cpu_baseline"] = cpu_baseline(host_blocks, xh_model, xh_ff, M, threads=1)
         out["parity"] = parity_record(K, weights[0][1], host_blocks[0], x_model, xh_model, M)
@@ -281,6 +376,38 @@ def run_ours(args):
         if ex is not None:
             ex.close()
         dist.destroy_process_group()
+
+
+def multi_gpu_parity(args, K, gk, torch, dev, weights, ex, gbufs, x_model, M, world, rank):
+    """Sharded run: the gathered y of the step's first product, as it sits in rank 0's buffer after the timed
+    region, against the CPU oracle on sampled rows of EVERY rank's band.  Rank 0 regenerates the first matrix from
+    the seed (every rank drew the same stream and kept its band) and quantizes the sampled rows again: the
+    quantizer works row by row, so these are the bytes the owning rank uploaded."""
+    import numpy as np
+    name, w, n, k, r0, r1 = weights[0]
+    torch.cuda.synchronize()
+    if rank != 0:
+        return None
+    from oracle import oracle as O
+    gen = torch.Generator(device=dev).manual_seed(20244)
+    W = torch.randn((n, k), generator=gen, device=dev) * 0.02
+    rows = []
+    for r in range(world):
+        b0, b1 = shard_rows(n, world, r)
+        rows.append(b0 + sample_rows(b1 - b0, max(64, 256 // world), seed=r))
+    rows = np.concatenate(rows)
+    sub = W[torch.from_numpy(rows).to(dev)].contiguous()
+    del W
+    blocks = K.quantize(gk.QuantType.q4k(), sub)
+    if ex is not None:
+        y = ex.local_tensor(0, (M, n))
+    else:
+        parts = [gbufs[0][r, :, : shard_rows(n, world, r)[1] - shard_rows(n, world, r)[0]] for r in range(world)]
+        y = torch.cat(parts, dim=1)
+    rec = sampled_parity(O, O.Q4K, blocks, len(rows), k, np.arange(len(rows)), x_model.cpu().numpy(),
+                         y[:, torch.from_numpy(rows).to(dev)], bar=2e-3, sequential=True)
+    rec["matrix"] = f"{name} [{n}, {k}]: rows sampled from each of the {world} ranks' bands, read from rank 0's gathered y"
+    return rec
 
 
 def extra_configs(K, gk, torch, dev, peak):
@@ -307,25 +434,33 @@ def extra_configs(K, gk, torch, dev, peak):
                 b[:, 2:4] = h[:, 2:4]
         return b.reshape(-1)
 
+    from oracle import oracle as O  # checker and CPU-baseline legs only, outside every timed region
+
     def run(qt, n, k, ms, copies, name):
         bs, bb = qt.block_size(), qt.block_bytes()
-        ws = []
+        ws, first = [], None
         for _ in range(copies):
             if qt.id >= 6:
                 q = random_gguf_blocks(qt, n, k)
                 ws.append(K.upload(qt, n, k, q))
+                first = first or (q, None, 1.0)
                 del q
                 continue
             W = torch.randn((n, k), generator=gen, device=dev) * 0.02
             q = K.quantize(qt, W)
             ws.append(K.upload(qt, n, k, q[0], q[1]) if qt.id == 3 else (K.upload(qt, n, k, q[0], None, q[1]) if qt.id == 4
                                                                            else K.upload(qt, n, k, q)))
+            first = first or ((q[0], q[1], 1.0) if qt.id == 3 else ((q[0], None, q[1]) if qt.id == 4 else (q, None, 1.0)))
             del W, q
         wbytes = n * (k // bs) * bb
+        rows = sample_rows(n, 256, seed=n)
         for m in ms:
             x = torch.randn((m, k), generator=gen, device=dev)
             y = torch.empty((m, n), dtype=torch.float32, device=dev)
             reps = 20
+            K.gemv(ws[0], x, y=y)
+            par = sampled_parity(O, qt.id, first[0], n, k, rows, x.cpu().numpy(), y, bar=2e-3, scales=first[1], global_scale=first[2],
+                                 sequential=qt.id not in (3, 4))
 
             def sweep():
                 for w in ws:
@@ -353,7 +488,9 @@ def extra_configs(K, gk, torch, dev, peak):
             torch.cuda.synchronize()
             us = e0.elapsed_time(e1) * 1e3 / (reps * copies)
             res[f"{name}_M{m}"] = {"us_per_gemv": us, "weight_GBps": wbytes / us / 1e3, "frac_hbm": wbytes / us / 1e3 / peak,
-                                   "tflops": 2.0 * m * n * k / us / 1e6, "copies_rotated": copies}
+                                   "tflops": 2.0 * m * n * k / us / 1e6, "copies_rotated": copies, "parity": par}
+            if name.startswith("cfg"):
+                res[f"{name}_M{m}"]["cpu_baseline"] = cpu_baseline_rows(O, qt.id, first, n, k, rows, x.cpu().numpy(), wbytes)
         for w in ws:
             w.free()
 
@@ -371,6 +508,62 @@ def extra_configs(K, gk, torch, dev, peak):
     run(gk.QuantType.q4_0(), D_MODEL, N_FF, [1], 3, "gguf_q4_0_8192x28672")
     run(gk.QuantType.q5_0(), D_MODEL, N_FF, [1], 3, "gguf_q5_0_8192x28672")
     res.update(extra_gemm(K, gk, torch, dev, gen))
+    res["cpu_bench_quant_kernels"] = bench_quant_cpu_all()
+    return res
+
+
+def cpu_baseline_rows(O, oid, packed, n, k, rows, x_host, wbytes, flops=None):
+    """The CPU port of the reference on a row subset of one configuration, scaled to the whole matrix (its cost is
+    proportional to the rows): 1 thread (as the reference runs it) and all host threads (rows in parallel).
+    Q4_K / Q8_0 / GGUF formats: the reference's quantized matmul.  MXFP4 / NVFP4: the reference has no matmul for
+    them; its decode followed by its scalar f32 GEMM is timed, 1 thread."""
+    import numpy as np
+    blocks, scales, g = packed
+    idx = None
+
+    def take(buf):
+        nonlocal idx
+        if isinstance(buf, np.ndarray):
+            return np.ascontiguousarray(buf.reshape(n, -1)[rows]).reshape(-1)
+        import torch
+        idx = torch.from_numpy(np.asarray(rows)).to(buf.device) if idx is None else idx
+        return buf.reshape(n, -1)[idx].cpu().numpy().reshape(-1)
+    hb = take(blocks)
+    hs = None if scales is None else take(scales)
+    m = x_host.shape[0]
+    xt = np.ascontiguousarray(x_host.T)
+    out = {"rows_timed": int(len(rows)), "of_rows": int(n), "kind": "port", "scaled": "time x n / rows_timed"}
+    threads = os.cpu_count() or 1
+    for label, th in (("1_thread", 1), ("all_threads", threads)):
+        if oid in (3, 4) and th > 1:
+            continue
+        t0 = time.perf_counter()
+        if oid in (3, 4):
+            O.gemm_f32_nt(x_host, O.dequant_matrix(oid, hb, len(rows), k, scales=hs, global_scale=g))
+        else:
+            O.quant_matmul(hb, xt, oid, len(rows), m, k, threads=th)
+        dt = (time.perf_counter() - t0) * n / len(rows)
+        out[label] = {"cores": th, "ms": dt * 1e3, "weight_GBps": wbytes / dt / 1e9, "gflops": 2.0 * m * n * k / dt / 1e9}
+    return out
+
+
+def bench_quant_cpu_all():
+    """Every group of the reference's benches/bench_quant.rs (:21-25, :67, :150, :191, :272-279) on this box's host:
+    the five scalar-ops kernels restated in C and built -O1 -fno-tree-vectorize like the reference's bench
+    profile, one thread, at bench_quant's own shapes.  GEMM groups time 8 of the M rows and scale."""
+    from oracle import oracle as O
+    res = {}
+    groups = [("gemv_q8", [(1, 4096, 4096), (1, 11008, 4096), (1, 16384, 4096)]),
+              ("gemv_q4", [(1, 4096, 4096), (1, 11008, 4096)]),
+              ("gemm_q8", [(32, 4096, 4096), (64, 4096, 4096), (128, 4096, 4096)]),
+              ("gemm_q4", [(32, 4096, 4096), (64, 4096, 4096), (128, 4096, 4096)]),
+              ("kquant_matmul", [(1, 4096, 4096), (32, 4096, 4096)])]
+    for kind, shapes in groups:
+        for m, n, k in shapes:
+            dt, mi = O.bench_quant_kernel(kind, m, n, k)
+            dt_full = dt * m / mi
+            res[f"{kind}_{m}x{n}x{k}"] = {"ms": dt_full * 1e3, "gflops": 2.0 * m * n * k / dt_full / 1e9, "rows_of_x_timed": mi,
+                                         "cores": 1, "build": "-O1 -fno-tree-vectorize"}
     return res
 
 
@@ -433,15 +626,18 @@ def extra_gemm(K, gk, torch, dev, gen):
     res = {}
     QT = gk.QuantType
 
+    from oracle import oracle as O  # checker and CPU-baseline legs only, outside every timed region
+
     def upload(qt, n, k):
+        """-> (weight handle, (blocks, scales, global scale) as the reference stores them, on the device)"""
         W = torch.randn((n, k), generator=gen, device=dev) * 0.02
         q = K.quantize(qt, W)
         del W
         if qt.id == 3:
-            return K.upload(qt, n, k, q[0], q[1])
+            return K.upload(qt, n, k, q[0], q[1]), (q[0], q[1], 1.0)
         if qt.id == 4:
-            return K.upload(qt, n, k, q[0], None, q[1])
-        return K.upload(qt, n, k, q)
+            return K.upload(qt, n, k, q[0], None, q[1]), (q[0], None, q[1])
+        return K.upload(qt, n, k, q), (q, None, 1.0)
 
     def timeit(fn, reps):
         for _ in range(3):
@@ -457,23 +653,34 @@ def extra_gemm(K, gk, torch, dev, gen):
 
     # config 5 prefill: gate/up-shaped and down-shaped Q4_K, f32 activations
     for n, k in ((28672, 8192), (8192, 28672)):
-        w = upload(QT.q4k(), n, k)
+        w, packed = upload(QT.q4k(), n, k)
+        rows = sample_rows(n, 256, seed=k)
         for m in (32, 512):
             a = torch.randn((m, k), generator=gen, device=dev)
             y = torch.empty((m, n), dtype=torch.float32, device=dev)
             us = timeit(lambda: K.gemm(w, a, y=y), 5)
+            tc = m > K.GEMM_GEMV_MAX_M
             res[f"cfg5_q4k_{n}x{k}_M{m}"] = {"us": us, "tflops": 2.0 * m * n * k / us / 1e6, "weight_GBps": w.ref_bytes / us / 1e3,
-                                            "staging": "fp16 x fp16 -> f32 (kind::f16)"}
+                                            "staging": "fp16 x fp16 -> f32 (kind::f16)" if tc else "passes of the decode kernel",
+                                            "parity": sampled_parity(O, O.Q4K, packed[0], n, k, rows, a.cpu().numpy(), y,
+                                                                     bar=1e-2 if tc else 2e-3, sequential=not tc)}
+            if k == 8192:
+                res[f"cfg5_q4k_{n}x{k}_M{m}"]["cpu_baseline"] = cpu_baseline_rows(O, O.Q4K, packed, n, k, rows[:64 if m > 32 else 256],
+                                                                                   a.cpu().numpy(), w.ref_bytes)
         w.free()
-    # config 3: 8 experts MXFP4 [14336, 4096], 512 tokens top-2 -> 1024 rows grouped per expert, bf16 activations
-    experts = [upload(QT.mxfp4(32), 14336, 4096) for _ in range(8)]
-    ids = torch.stack([torch.randperm(8, generator=gen, device=dev)[:2] for _ in range(512)]).reshape(-1)
-    counts = torch.bincount(ids, minlength=8).cpu().tolist()
-    a = torch.randn((1024, 4096), generator=gen, device=dev).to(torch.bfloat16)
+        del packed
+    # config 3: 8 experts MXFP4 [14336, 4096], 512 tokens, top-2 routing by the reference's conventions (scalar_topk: the
+    # two largest of 8 uniform draws = two distinct experts, uniform), rows grouped per expert, bf16 activations
+    ups = [upload(QT.mxfp4(32), 14336, 4096) for _ in range(8)]
+    experts = [u[0] for u in ups]
+    x_tok = torch.randn((512, 4096), generator=gen, device=dev).to(torch.bfloat16)
+    probs = torch.rand((512, 8), generator=gen, device=dev)
+    probs = probs / probs.sum(dim=1, keepdim=True)
+    routing = K.moe_topk(probs, 2)
+    offs, perm, inv = K.moe_route(routing, 512, 8, 2)
+    counts = [offs[e + 1] - offs[e] for e in range(8)]
+    a = K.moe_gather(x_tok, perm, 2)
     y = torch.empty((1024, 14336), dtype=torch.bfloat16, device=dev)
-    offs = [0]
-    for cnt in counts:
-        offs.append(offs[-1] + cnt)
 
     def moe_loop():
         for e, w in enumerate(experts):
@@ -486,8 +693,19 @@ def extra_gemm(K, gk, torch, dev, gen):
                                                      "rows_per_expert": counts, "staging": "fp16 x fp16 -> f32 (kind::f16)",
                                                      "launch": "one grouped launch over the 8 experts",
                                                      "us_one_call_per_expert": us_loop}
+    a_host, worst = a.to(torch.float32).cpu().numpy(), None
+    for e in range(8):
+        rec = sampled_parity(O, O.MXFP4, ups[e][1][0], 14336, 4096, sample_rows(14336, 256, seed=e), a_host[offs[e]:offs[e + 1]],
+                             y[offs[e]:offs[e + 1]], bar=1e-2, scales=ups[e][1][1])
+        worst = rec if worst is None or rec["rel_err"] > worst["rel_err"] else worst
+    worst["note"] = "worst of the 8 experts; 256 sampled rows x the expert's tokens each; bf16 output"
+    res["cfg3_mxfp4_moe_8x14336x4096_M512_top2"]["parity"] = worst
+    res["cfg3_mxfp4_moe_8x14336x4096_M512_top2"]["cpu_baseline"] = cpu_baseline_rows(
+        O, O.MXFP4, ups[0][1], 14336, 4096, sample_rows(14336, 64, seed=0), a_host[offs[0]:offs[1]],
+        ups[0][0].ref_bytes, None)
     for w in experts:
         w.free()
+    del ups
     # W8A8: s8 weights x u8 activations -> s32 (exact), tcgen05 kind::i8, at config 2's matrix and a 70B-shaped one
     for n, k, m in ((11008, 4096, 2048), (28672, 8192, 2048)):
         b = torch.randint(-128, 128, (n, k), generator=gen, device=dev, dtype=torch.int8)
@@ -502,14 +720,19 @@ def extra_gemm(K, gk, torch, dev, gen):
         del a8, c32
     # config 4: NVFP4 weights x NVFP4 activations, bf16 out, native block-scaled MMA
     n, k, m = 14336, 4096, 2048
-    w = upload(QT.nvfp4(), n, k)
+    w, packed = upload(QT.nvfp4(), n, k)
     X = torch.randn((m, k), generator=gen, device=dev)
     xb, gx = K.quantize(QT.nvfp4(), X)
     x = K.upload(QT.nvfp4(), m, k, xb, None, gx)
     y = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
     us = timeit(lambda: K.gemm_fp4(w, x, y=y), 20)
+    a_host = O.dequant_matrix(O.NVFP4, xb.cpu().numpy(), m, k, global_scale=gx)
+    rows = sample_rows(n, 256, seed=4)
     res["cfg4_nvfp4_14336x4096_M2048"] = {"us": us, "tflops": 2.0 * m * n * k / us / 1e6, "frac_of_nominal_fp4_9000": 2.0 * m * n * k / us / 1e6 / 9000.0,
-                                          "mma": "tcgen05 kind::mxf4nvf4 block_scale"}
+                                          "mma": "tcgen05 kind::mxf4nvf4 block_scale",
+                                          "parity": sampled_parity(O, O.NVFP4, packed[0], n, k, rows, a_host, y, bar=2e-3 + 2.0 ** -9,
+                                                                   global_scale=packed[2]),
+                                          "cpu_baseline": cpu_baseline_rows(O, O.NVFP4, packed, n, k, rows[:32], a_host, w.ref_bytes)}
     w.free()
     x.free()
     return res
@@ -620,11 +843,8 @@ def run_reference(args):
     out = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 1), "ms_per_step": dt * 1e3 * L, "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": "u4 weights x f32 activations, f32 accumulate", "data": "synthetic",
-        "config": {"workload": f"config 5: 70B-shaped FFN decode, {L} layers x (gate, up, down) Q4_K, M={M}; " +
-                               ("gate and up stored as one 57344-row weight (2 products per layer)" if fused
-                                else "one product per matrix (3 per layer)"),
-                   "layers": L, "M": M, "N_ff": N_FF, "d_model": D_MODEL},
+        "vs_baseline": None, "dtype": DTYPE_REF, "data": "synthetic",
+        "config": workload_config(L, M, fused),
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port",
                          "sample": f"each step = one layer (gate, up, down, {layer_bytes} weight bytes) of the "
                                    f"{L}-layer step; ms_per_step is scaled x{L}"},

@@ -87,6 +87,19 @@ _OPTIONAL_SIGS: dict = {
     "gllmk_shared_free": (_i32, [_vp, _vp]),
     "gllmk_gemv_allgather": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _vp, _i64, _i64, C.POINTER(_vp), _i32, _vp]),
     "gllmk_peer_barrier": (_i32, [_vp, _vp, C.POINTER(_vp), _i32, _i32, C.c_uint32, _vp]),
+    "gllmk_quantize_act_int8": (_i32, [_vp, _vp, _i64, _i64, _i64, _vp, _i64, _i32, _vp, _vp]),
+    "gllmk_w8a8_linear_f32": (_i32, [_vp, _vp, _vp, _i64, _i32, _vp, _i64, _f32, _vp, _i32, _vp]),
+    "gllmk_gemm_q8_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz]),
+    "gllmk_gemv_q4_f32": (_i32, [_vp, _vp, _vp, _f32, _sz, _vp]),
+    "gllmk_gemv_q8_f32": (_i32, [_vp, _vp, _vp, _f32, _sz, _vp]),
+    "gllmk_quant_format_descriptor_for_type": (_i32, [_i32, _i32, _vp]),
+    "gllmk_quant_format_registry": (_i32, [_vp, _i32]),
+    "gllmk_gemv_exchange": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _vp, _i64, _i64, C.POINTER(_vp), _vp, C.POINTER(_vp), _i32, _i32, _vp]),
+    "gllmk_exchange_wait": (_i32, [_vp, _vp, _i32, _i32, _vp]),
+    "gllmk_moe_topk": (_i32, [_vp, _vp, _vp, _i64, _i32, _i32, _vp]),
+    "gllmk_moe_route": (_i32, [_vp, _vp, _i64, _i32, _i32, C.POINTER(_i64), _vp, _vp, _vp]),
+    "gllmk_moe_gather": (_i32, [_vp, _vp, _i32, _i64, _vp, _i64, _i32, _i64, _vp, _i64, _vp]),
+    "gllmk_moe_weighted_sum": (_i32, [_vp, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _vp]),
 }
 
 _lib = None

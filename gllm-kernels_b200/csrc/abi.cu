@@ -53,43 +53,9 @@ int32_t ensure_cnt(Ctx *c, size_t bytes) {
 int32_t ensure_pin(Ctx *c, size_t bytes) { return grow(c, &c->pin, &c->pin_bytes, bytes, true); }
 int32_t ensure_dev_io(Ctx *c, size_t bytes) { return grow(c, &c->dev_io, &c->dev_io_bytes, bytes, false); }
 
-static int block_size_of(int qt, int mx) {
-    switch (qt) {
-        case GLLMK_QUANT_Q4K: return 256;
-        case GLLMK_QUANT_Q8_0: return 32;
-        case GLLMK_QUANT_MXFP4: return mx;
-        case GLLMK_QUANT_NVFP4: return 64;
-        case GLLMK_QUANT_Q6_K: case GLLMK_QUANT_Q5_K: case GLLMK_QUANT_Q8_K: return 256;
-        case GLLMK_QUANT_Q4_0: case GLLMK_QUANT_Q5_0: return 32;
-    }
-    return 0;
-}
-static int block_bytes_of(int qt, int mx) {
-    switch (qt) {
-        case GLLMK_QUANT_Q4K: return 144;
-        case GLLMK_QUANT_Q8_0: return 34;
-        case GLLMK_QUANT_MXFP4: return 1 + mx / 2;
-        case GLLMK_QUANT_NVFP4: return 36;
-        case GLLMK_QUANT_Q6_K: return 210;
-        case GLLMK_QUANT_Q5_K: return 176;
-        case GLLMK_QUANT_Q8_K: return 292;
-        case GLLMK_QUANT_Q4_0: return 18;
-        case GLLMK_QUANT_Q5_0: return 22;
-    }
-    return 0;
-}
-
-struct DeviceGuard {
-    int prev = -1;
-    bool ok = true;
-    explicit DeviceGuard(int dev) {
-        if (cudaGetDevice(&prev) != cudaSuccess) { ok = false; (void)cudaGetLastError(); return; }
-        if (prev != dev && cudaSetDevice(dev) != cudaSuccess) { ok = false; (void)cudaGetLastError(); }
-    }
-    ~DeviceGuard() {
-        if (ok && prev >= 0) cudaSetDevice(prev);
-    }
-};
+// QuantType::block_size / block_bytes: read from the format descriptor table (quant_format.cuh)
+static int block_size_of(int qt, int mx) { return quant_format(qt, mx).block_size; }
+static int block_bytes_of(int qt, int mx) { return quant_format(qt, mx).block_bytes; }
 
 // Creates the handle and its device buffers for an n x k matrix of type qt (no data yet).
 static int32_t weight_alloc(Ctx *c, int32_t qt, int64_t n, int64_t k, int32_t mx_block, float global, Weight **out) {
@@ -203,6 +169,23 @@ int32_t gllmk_hw_info(char *buf, size_t len) {
     return (int32_t)((size_t)n < len ? (size_t)n : len - 1);
 }
 
+int32_t gllmk_quant_format_descriptor_for_type(int32_t quant_type, int32_t mx_block, gllmk_quant_format_descriptor *out) {
+    if (!out) return GLLMK_STATUS_INVALID_ARG;
+    const gllmk_quant_format_descriptor d = quant_format(quant_type, mx_block);
+    if (d.quant_type == 0) return GLLMK_STATUS_UNSUPPORTED;
+    if (quant_type == GLLMK_QUANT_MXFP4 && (mx_block <= 0 || (mx_block & 1))) return GLLMK_STATUS_INVALID_ARG;
+    *out = d;
+    return GLLMK_STATUS_OK;
+}
+
+int32_t gllmk_quant_format_registry(int32_t *quant_types, int32_t cap) {
+    static const int32_t ids[] = {GLLMK_QUANT_Q4_0, GLLMK_QUANT_Q5_0, GLLMK_QUANT_Q8_0, GLLMK_QUANT_Q4K, GLLMK_QUANT_Q5_K,
+                                  GLLMK_QUANT_Q6_K, GLLMK_QUANT_Q8_K, GLLMK_QUANT_MXFP4, GLLMK_QUANT_NVFP4};
+    const int32_t n = (int32_t)(sizeof(ids) / sizeof(ids[0]));
+    for (int32_t i = 0; quant_types && i < n && i < cap; i++) quant_types[i] = ids[i];
+    return n;
+}
+
 int32_t gllmk_quant_block_size(int32_t qt, int32_t mx_block) { return block_size_of(qt, mx_block); }
 int32_t gllmk_quant_block_bytes(int32_t qt, int32_t mx_block) { return block_bytes_of(qt, mx_block); }
 
@@ -267,6 +250,9 @@ int32_t gllmk_ctx_status(gllmk_ctx ctx, int32_t *device_status) {
     *device_status = v;
     if (v) {
         GK_CUDA(c, cudaMemset(c->status_dev, 0, sizeof(int)));
+        // A kernel that gave up left without arriving at its row tiles' counters: the "zero between launches"
+        // rule of the split-k arrival counters (decode GEMV and FP4 decode GEMV share them) no longer holds.
+        if (c->cnt) GK_CUDA(c, cudaMemset(c->cnt, 0, c->cnt_bytes));
         return fail(c, GLLMK_STATUS_RUNTIME_ERROR, "a kernel gave up a bounded wait (status word %d)", v);
     }
     return GLLMK_STATUS_OK;
@@ -278,6 +264,19 @@ int32_t gllmk_ctx_set(gllmk_ctx ctx, const char *key, int64_t value) {
     if (!strcmp(key, "gemv_ctas_per_sm")) c->gemv_ctas_per_sm = value;
     else if (!strcmp(key, "gemv_pdl")) c->gemv_pdl = value;
     else if (!strcmp(key, "gemv_fp4_int")) c->gemv_fp4_int = value;
+    else if (!strcmp(key, "peer_wait_spins")) {
+        if (value < 1 || value > ((int64_t)1 << 30)) return fail(c, GLLMK_STATUS_INVALID_ARG, "peer_wait_spins outside 1..2^30");
+        c->peer_wait_spins = value;
+    } else if (!strcmp(key, "inject_give_up")) {
+        // Host-side fault injection for tests of the failure path: leaves the context exactly as a kernel that gave
+        // up a bounded wait would (status word = value, arrival counters non-zero) without making any kernel wait.
+        if (value < 1 || value > 255) return fail(c, GLLMK_STATUS_INVALID_ARG, "inject_give_up takes a status code 1..255");
+        DeviceGuard g(c->device);
+        GK_CUDA(c, cudaDeviceSynchronize());
+        const int v = (int)value;
+        GK_CUDA(c, cudaMemcpy(c->status_dev, &v, sizeof(int), cudaMemcpyHostToDevice));
+        if (c->cnt) GK_CUDA(c, cudaMemset(c->cnt, 1, c->cnt_bytes));
+    }
     else return fail(c, GLLMK_STATUS_INVALID_ARG, "unknown key %s", key);
     return GLLMK_STATUS_OK;
 }
@@ -378,7 +377,8 @@ int32_t gllmk_gemv(gllmk_ctx ctx, gllmk_weight wh, const float *x_dev, int64_t x
     const Weight *w = static_cast<const Weight *>(wh);
     if (m < 1 || m > GLLMK_GEMV_MAX_M)
         return fail(c, GLLMK_STATUS_INVALID_ARG, "gemv: m=%d outside 1..%d", m, GLLMK_GEMV_MAX_M);
-    if (row_scales && n_row_scales != 1 && n_row_scales != w->n) { row_scales = nullptr; n_row_scales = 0; }
+    if (row_scales && n_row_scales != 1 && n_row_scales != w->n)
+        return fail(c, GLLMK_STATUS_INVALID_ARG, "gemv: n_row_scales=%lld must be 1 or n=%lld", (long long)n_row_scales, (long long)w->n);
     if (w->device != c->device) return fail(c, GLLMK_STATUS_INVALID_ARG, "weight lives on another device");
     DeviceGuard g(c->device);
     return gemv_launch(c, w, x_dev, x_stride_t, x_stride_k, m, y_dev, y_stride_t, y_stride_r, row_scales, n_row_scales,
@@ -497,8 +497,11 @@ static int32_t int8_weight_create(Ctx *c, int64_t n, int64_t k, const int8_t *b,
     w->device = c->device;
     w->ref_bytes = (uint64_t)n * (uint64_t)k;
     w->qs_bytes = (size_t)w->n_pad * (size_t)w->k_pad;
+    w->aux_bytes = (size_t)n * sizeof(int32_t);  // column sums of B (zero-point correction of the f32 activation path)
     cudaError_t e = cudaMalloc(&w->qs, w->qs_bytes);
+    if (e == cudaSuccess) e = cudaMalloc(&w->aux, w->aux_bytes);
     if (e != cudaSuccess) {
+        if (w->qs) cudaFree(w->qs);
         delete w;
         return cuda_fail(c, e, "cudaMalloc(int8 weight)");
     }
@@ -559,6 +562,42 @@ int32_t gllmk_dequantize_i32_f32(gllmk_ctx ctx, const int32_t *c_dev, float *out
     if (activation < 0 || activation > 4) return fail(c, GLLMK_STATUS_UNSUPPORTED, "dequantize: activation %d", activation);
     DeviceGuard g(c->device);
     return dequant_i32_launch(c, c_dev, out_dev, m, n, n, n, scale_a, scale_b, bias_dev, activation, static_cast<cudaStream_t>(stream));
+}
+
+int32_t gllmk_quantize_act_int8(gllmk_ctx ctx, const float *x_dev, int64_t rows, int64_t k, int64_t ldx, void *q_dev, int64_t ldq,
+                                int32_t as_unsigned, float *scale_dev, void *stream) {
+    if (!ctx || !x_dev || !q_dev || !scale_dev) return GLLMK_STATUS_INVALID_ARG;
+    Ctx *c = static_cast<Ctx *>(ctx);
+    if (rows < 1 || k < 1 || ldx < k || ldq < k) return fail(c, GLLMK_STATUS_INVALID_ARG, "quantize_act_int8: bad shape");
+    DeviceGuard g(c->device);
+    return act_quant_i8_launch(c, x_dev, rows, k, ldx, static_cast<uint8_t *>(q_dev), ldq, as_unsigned ? 128 : 0, scale_dev,
+                               static_cast<cudaStream_t>(stream));
+}
+
+int32_t gllmk_w8a8_linear_f32(gllmk_ctx ctx, gllmk_weight wh, const float *x_dev, int64_t ldx, int32_t m, float *y_dev, int64_t ldy,
+                              float scale_b, const float *bias_dev, int32_t activation, void *stream) {
+    if (!ctx || !wh || !x_dev || !y_dev) return GLLMK_STATUS_INVALID_ARG;
+    Ctx *c = static_cast<Ctx *>(ctx);
+    const Weight *w = static_cast<const Weight *>(wh);
+    if (w->qt != GLLMK_QUANT_INT8) return fail(c, GLLMK_STATUS_INVALID_ARG, "w8a8_linear: the weight was not uploaded with gllmk_int8_weight_upload");
+    if (m < 1 || ldx < w->k || ldy < w->n) return fail(c, GLLMK_STATUS_INVALID_ARG, "w8a8_linear: bad shape");
+    if (activation < 0 || activation > 4) return fail(c, GLLMK_STATUS_UNSUPPORTED, "w8a8_linear: activation %d", activation);
+    if (w->device != c->device) return fail(c, GLLMK_STATUS_INVALID_ARG, "weight lives on another device");
+    DeviceGuard g(c->device);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // context scratch: [scale f32, amax u32 | pad to 256] [u8 activations m x k] [s32 products m x n]
+    const size_t ab = ((size_t)m * (size_t)w->k + 255) & ~(size_t)255, cb = (size_t)m * (size_t)w->n * sizeof(int32_t);
+    int32_t rc = ensure_act(c, 256 + ab + cb);
+    if (rc) return rc;
+    char *base = static_cast<char *>(c->act);
+    float *scale = reinterpret_cast<float *>(base);
+    uint8_t *q = reinterpret_cast<uint8_t *>(base + 256);
+    int32_t *ci = reinterpret_cast<int32_t *>(base + 256 + ab);
+    rc = act_quant_i8_launch(c, x_dev, m, w->k, ldx, q, w->k, 128, scale, s);
+    if (!rc) rc = gemm_i8_launch(c, w, q, w->k, m, ci, w->n, s);
+    if (!rc) rc = dequant_i32_launch(c, ci, y_dev, m, w->n, w->n, ldy, 0.0f, scale_b, bias_dev, activation, s, scale,
+                                     static_cast<const int32_t *>(w->aux));
+    return rc;
 }
 
 int32_t gllmk_gemm_int8_host(gllmk_ctx ctx, const uint8_t *a, const int8_t *b_kn, int32_t *c_out, size_t m, size_t n, size_t k) {
@@ -703,22 +742,40 @@ int32_t gllmk_classic_matmul_f32(gllmk_ctx ctx, const uint8_t *weight_blocks, co
     return family_matmul(ctx, weight_blocks, input, output, quant_type, false, m, n, k);
 }
 
-int32_t gllmk_gemm_q4_f32(gllmk_ctx ctx, const uint8_t *weight, const float *input, float *output, const float *scales,
-                          size_t n_scales, size_t m, size_t n, size_t k) {
+// gemm_q4 / gemm_q8 share everything but the block format (Q4_K / Q8_K rows of k / 256 blocks).
+static int32_t gemm_kq_host(gllmk_ctx ctx, int32_t qt, const char *what, const void *weight, const float *input, float *output,
+                            const float *scales, size_t n_scales, size_t m, size_t n, size_t k) {
     if (!ctx || !weight || !input || !output) return GLLMK_STATUS_INVALID_ARG;
     Ctx *c = static_cast<Ctx *>(ctx);
     if (n_scales && !scales) return GLLMK_STATUS_INVALID_ARG;
-    if (k % 256) return fail(c, GLLMK_STATUS_INVALID_ARG, "gemm_q4: k %% 256 != 0");
+    if (k % 256) return fail(c, GLLMK_STATUS_INVALID_ARG, "%s: k %% 256 != 0", what);
     if (m == 0 || n == 0) return GLLMK_STATUS_OK;
     if (m > 0x7fffffffu) return fail(c, GLLMK_STATUS_INVALID_ARG, "m too large");
     DeviceGuard g(c->device);
     Weight *w = nullptr;
-    int32_t rc = weight_alloc(c, GLLMK_QUANT_Q4K, (int64_t)n, (int64_t)k, 0, 1.0f, &w);
+    int32_t rc = weight_alloc(c, qt, (int64_t)n, (int64_t)k, 0, 1.0f, &w);
     if (rc) return rc;
     rc = weight_fill(c, w, weight, nullptr, false);
     if (!rc) rc = matmul_host_impl(c, w, input, (int)m, output, false, scales, n_scales);
     weight_destroy(w);
     return rc;
+}
+
+int32_t gllmk_gemm_q4_f32(gllmk_ctx ctx, const uint8_t *weight, const float *input, float *output, const float *scales,
+                          size_t n_scales, size_t m, size_t n, size_t k) {
+    return gemm_kq_host(ctx, GLLMK_QUANT_Q4K, "gemm_q4", weight, input, output, scales, n_scales, m, n, k);
+}
+int32_t gllmk_gemm_q8_f32(gllmk_ctx ctx, const int8_t *weight, const float *input, float *output, const float *scales,
+                          size_t n_scales, size_t m, size_t n, size_t k) {
+    return gemm_kq_host(ctx, GLLMK_QUANT_Q8_K, "gemm_q8", weight, input, output, scales, n_scales, m, n, k);
+}
+int32_t gllmk_gemv_q4_f32(gllmk_ctx ctx, const uint8_t *weight, const float *input, float scale, size_t n, float *out) {
+    if (!out) return GLLMK_STATUS_INVALID_ARG;
+    return gemm_kq_host(ctx, GLLMK_QUANT_Q4K, "gemv_q4", weight, input, out, &scale, 1, 1, 1, n);
+}
+int32_t gllmk_gemv_q8_f32(gllmk_ctx ctx, const int8_t *weight, const float *input, float scale, size_t n, float *out) {
+    if (!out) return GLLMK_STATUS_INVALID_ARG;
+    return gemm_kq_host(ctx, GLLMK_QUANT_Q8_K, "gemv_q8", weight, input, out, &scale, 1, 1, 1, n);
 }
 
 static int32_t dequant_host(gllmk_ctx ctx, int32_t qt, const uint8_t *blocks, const uint8_t *scales, float global,

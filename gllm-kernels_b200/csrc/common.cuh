@@ -11,6 +11,7 @@
 #include <string>
 
 #include "../../include/gllmk.h"
+#include "quant_format.cuh"
 
 namespace gllmk {
 
@@ -94,6 +95,7 @@ struct Ctx {
     int64_t gemv_pdl = 1;
     int64_t gemv_fp4_int = 0;  // 1: FP4 decode on the integer-decode GEMV kernel instead of the tensor-core one
     int64_t gemv_ctas_per_sm = 0;  // 0 = what the occupancy calculator allows
+    int64_t peer_wait_spins = (int64_t)1 << 22;  // probes of another rank's flag before a wait gives up (status 31 / 32)
 };
 
 int32_t fail(Ctx *c, int32_t code, const char *fmt, ...);
@@ -104,6 +106,19 @@ int32_t ensure_act(Ctx *c, size_t bytes);
 int32_t ensure_cnt(Ctx *c, size_t bytes);
 int32_t ensure_pin(Ctx *c, size_t bytes);
 int32_t ensure_dev_io(Ctx *c, size_t bytes);
+
+// Makes the context's device current for the duration of an entry point and restores the caller's.
+struct DeviceGuard {
+    int prev = -1;
+    bool ok = true;
+    explicit DeviceGuard(int dev) {
+        if (cudaGetDevice(&prev) != cudaSuccess) { ok = false; (void)cudaGetLastError(); return; }
+        if (prev != dev && cudaSetDevice(dev) != cudaSuccess) { ok = false; (void)cudaGetLastError(); }
+    }
+    ~DeviceGuard() {
+        if (ok && prev >= 0) cudaSetDevice(prev);
+    }
+};
 
 #define GK_CUDA(c, call)                                             \
     do {                                                             \
@@ -118,9 +133,20 @@ int32_t dequant_matrix(Ctx *c, const Weight *w, float *out_dev, cudaStream_t s, 
 int32_t dequant_raw(Ctx *c, int32_t qt, const uint8_t *blocks_dev, const uint8_t *scales_dev, float global,
                     float *out_dev, size_t nblocks, size_t block_size, cudaStream_t s);
 // ---- gemv.cu ----
+// Flag words of a row-sharded decode product that signals its own completion (gllmk_gemv_exchange): the first
+// GLLMK_PEER_FLAG_BYTES of every rank's exchange buffer, viewed as uint32_t[64].
+//   [0, 8)   gllmk_peer_barrier: last sequence number signalled by each source rank      [16] its replay counter
+//   [32, 40) exchange products:  epoch (= products completed) last signalled by each source rank
+//   [48]     this rank's own epoch, advanced by the last block of each exchange product
+constexpr int XF_FLAGS = 32, XF_EPOCH = 48;
+struct Exchange {
+    uint32_t *flags_local = nullptr;               // this rank's flag words; nullptr: no signalling
+    uint32_t *flags_peer[GLLMK_MAX_PEERS] = {};    // the other ranks' flag words (peer-mapped), rank order
+    int n_peers = 0, rank = 0;
+};
 int32_t gemv_launch(Ctx *c, const Weight *w, const float *x, int64_t xst, int64_t xsk, int m, float *y, int64_t yst,
                     int64_t ysr, const float *row_scales, int64_t n_row_scales, cudaStream_t s, void *const *y_peers = nullptr,
-                    int n_peers = 0, const float *x_up = nullptr);
+                    int n_peers = 0, const float *x_up = nullptr, const Exchange *xch = nullptr);
 size_t gemv_ws_bytes(const Weight *w, int m);
 // ---- gemm.cu ----
 int32_t gemm_launch(Ctx *c, const Weight *w, const void *a, int a_bf16, int64_t lda, int m, void *y, int y_bf16, int64_t ldy,
@@ -136,7 +162,11 @@ int32_t gemv_fp4_launch(Ctx *c, const Weight *w, const float *x, int64_t xst, in
 int32_t i8_weight_fill(Ctx *c, Weight *w, const int8_t *b_dev, int layout, cudaStream_t s);
 int32_t gemm_i8_launch(Ctx *c, const Weight *w, const uint8_t *a, int64_t lda, int m, int32_t *out, int64_t ldc, cudaStream_t s);
 int32_t dequant_i32_launch(Ctx *c, const int32_t *ci, float *out, int64_t m, int64_t n, int64_t ldc, int64_t ldo, float scale_a,
-                           float scale_b, const float *bias, int act, cudaStream_t s);
+                           float scale_b, const float *bias, int act, cudaStream_t s, const float *scale_a_dev = nullptr,
+                           const int32_t *colsum = nullptr);
+// f32 activations -> per-tensor int8 (stored as q + offset); scale_dev: two words of device memory, [0] receives the scale
+int32_t act_quant_i8_launch(Ctx *c, const float *x, int64_t rows, int64_t k, int64_t ld, uint8_t *q, int64_t ldq, int offset,
+                            float *scale_dev, cudaStream_t s);
 // ---- gguf_raw.cu: Q6_K, Q5_K, Q8_K, Q4_0, Q5_0 kept as reference blocks (w->qs = n rows of nb block slots + 16 spare bytes) ----
 bool raw_format(int32_t qt);
 int raw_dev_block_bytes(int32_t qt);  // Q6_K: 224-byte slots; the others: the reference block size

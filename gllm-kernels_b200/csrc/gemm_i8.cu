@@ -197,13 +197,20 @@ __global__ void __launch_bounds__(I8_THREADS, 1) gemm_i8_kernel(const __grid_con
 
 // dequantize_i32_to_f32 (src/macros/matmul_x86_int8.rs:414-456, scalar tail semantics): (c as f32) * scale_a * scale_b
 // (+ bias[j]), then the activation of src/macros/gemm_epilogue.rs:131-152
+// scale_a_dev != nullptr: the activation scale is read from device memory (written by the activation quantizer of the
+// same stream).  colsum != nullptr: the activations were stored as q + 128 (unsigned), so 128 * sum_k B[k, j] is
+// taken off the integer result first — exact, the s32 range holds both terms for k < 66000.
 __global__ void __launch_bounds__(256) dequant_i32_kernel(const int32_t *__restrict__ c, float *__restrict__ out, int64_t n, int64_t ldc,
                                                           int64_t ldo, float scale_a, float scale_b, const float *__restrict__ bias,
-                                                          int act, size_t total) {
+                                                          int act, size_t total, const float *__restrict__ scale_a_dev,
+                                                          const int32_t *__restrict__ colsum) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     const int64_t i = (int64_t)(idx / (size_t)n), j = (int64_t)(idx % (size_t)n);
-    float v = __fmul_rn(__fmul_rn((float)c[i * ldc + j], scale_a), scale_b);
+    if (scale_a_dev) scale_a = *scale_a_dev;
+    int32_t ci = c[i * ldc + j];
+    if (colsum) ci -= 128 * colsum[j];
+    float v = __fmul_rn(__fmul_rn((float)ci, scale_a), scale_b);
     if (bias) v = __fadd_rn(v, bias[j]);
     if (act == 1) v = v < 0.0f ? 0.0f : v;
     else if (act == 2) v = v / (1.0f + expf(-v));
@@ -215,9 +222,65 @@ __global__ void __launch_bounds__(256) dequant_i32_kernel(const int32_t *__restr
 }
 
 // ---------------------------------------------------------------------------------------------
+// one warp per weight row j: colsum[j] = sum_k B[k, j]
+__global__ void __launch_bounds__(256) i8_colsum_kernel(const int8_t *__restrict__ b, int64_t n, int64_t k, int layout, int32_t *__restrict__ colsum) {
+    const int64_t j = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (j >= n) return;
+    int32_t acc = 0;
+    for (int64_t kk = lane; kk < k; kk += 32) acc += layout == 0 ? (int32_t)b[kk * n + j] : (int32_t)b[j * k + kk];
+#pragma unroll
+    for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) colsum[j] = acc;
+}
+
 int32_t i8_weight_fill(Ctx *c, Weight *w, const int8_t *b_dev, int layout, cudaStream_t s) {
     const size_t total = (size_t)w->n_pad * (size_t)(w->k_pad / 16);
     repack_i8_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(b_dev, static_cast<uint8_t *>(w->qs), w->n, w->k, w->k_pad, layout, total);
+    GK_CUDA(c, cudaGetLastError());
+    if (w->aux) {  // per-column sums of B: the zero-point correction of the f32 -> u8 activation path
+        i8_colsum_kernel<<<(unsigned)((w->n * 32 + 255) / 256), 256, 0, s>>>(b_dev, w->n, w->k, layout, static_cast<int32_t *>(w->aux));
+        GK_CUDA(c, cudaGetLastError());
+    }
+    return GLLMK_STATUS_OK;
+}
+
+// quantize_from_fp32 / QuantFormat::Int8PerTensor (src/compiler/quant_convert.rs:17-20,165-177): scale = max|x| / 127,
+// q = (x / scale).round().clamp(-128, 127) as i8 (round half away from zero; NaN, i.e. 0 / 0 for an all-zero tensor, -> 0).
+__global__ void __launch_bounds__(256) act_amax_kernel(const float *__restrict__ x, int64_t rows, int64_t k, int64_t ld, uint32_t *amax_bits) {
+    float a = 0.0f;
+    const int64_t total = rows * k;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const float v = fabsf(x[(i / k) * ld + i % k]);
+        if (v > a) a = v;  // f32::max semantics: a NaN operand is ignored
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+    if ((threadIdx.x & 31) == 0) atomicMax(amax_bits, __float_as_uint(a));  // non-negative floats order like their bits
+}
+__global__ void __launch_bounds__(256) act_quant_i8_kernel(const float *__restrict__ x, int64_t rows, int64_t k, int64_t ld, uint8_t *__restrict__ q,
+                                                           int64_t ldq, int offset, const uint32_t *amax_bits, float *scale_out) {
+    const float scale = __fdiv_rn(__uint_as_float(*amax_bits), 127.0f);
+    const int64_t total = rows * k;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / k, cidx = i % k;
+        float v = roundf(__fdiv_rn(x[r * ld + cidx], scale));
+        if (v != v) v = 0.0f;
+        v = fminf(fmaxf(v, -128.0f), 127.0f);
+        q[r * ldq + cidx] = (uint8_t)((int)v + offset);
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0) *scale_out = scale;
+}
+
+int32_t act_quant_i8_launch(Ctx *c, const float *x, int64_t rows, int64_t k, int64_t ld, uint8_t *q, int64_t ldq, int offset,
+                            float *scale_dev, cudaStream_t s) {
+    // the running maximum lives next to the caller's scale word: [scale f32][amax bits u32]
+    uint32_t *amax = reinterpret_cast<uint32_t *>(scale_dev) + 1;
+    GK_CUDA(c, cudaMemsetAsync(amax, 0, sizeof(uint32_t), s));
+    const int64_t total = rows * k;
+    const unsigned grid = (unsigned)((total + 1023) / 1024 > 1184 ? 1184 : (total + 1023) / 1024);
+    act_amax_kernel<<<grid, 256, 0, s>>>(x, rows, k, ld, amax);
+    act_quant_i8_kernel<<<grid, 256, 0, s>>>(x, rows, k, ld, q, ldq, offset, amax, scale_dev);
     GK_CUDA(c, cudaGetLastError());
     return GLLMK_STATUS_OK;
 }
@@ -264,10 +327,11 @@ int32_t gemm_i8_launch(Ctx *c, const Weight *w, const uint8_t *a, int64_t lda, i
 }
 
 int32_t dequant_i32_launch(Ctx *c, const int32_t *ci, float *out, int64_t m, int64_t n, int64_t ldc, int64_t ldo, float scale_a,
-                           float scale_b, const float *bias, int act, cudaStream_t s) {
+                           float scale_b, const float *bias, int act, cudaStream_t s, const float *scale_a_dev, const int32_t *colsum) {
     const size_t total = (size_t)m * (size_t)n;
     if (total == 0) return GLLMK_STATUS_OK;
-    dequant_i32_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(ci, out, n, ldc, ldo, scale_a, scale_b, bias, act, total);
+    dequant_i32_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(ci, out, n, ldc, ldo, scale_a, scale_b, bias, act, total, scale_a_dev,
+                                                                      colsum);
     GK_CUDA(c, cudaGetLastError());
     return GLLMK_STATUS_OK;
 }

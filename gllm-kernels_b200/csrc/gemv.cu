@@ -39,6 +39,12 @@ struct StageParams {
     int m;
     int64_t K;
     uint8_t *img;
+    // exchange products: before x is read, wait (bounded) until every other rank has completed as many exchange
+    // products as this rank has (its bands of the previous product have then landed in this rank's buffers)
+    const uint32_t *xflags;  // this rank's flag words, or nullptr
+    int nranks, rank;
+    uint32_t spins;
+    int *status;
 };
 
 __global__ void __launch_bounds__(256) stage_x_kernel(StageParams p) {
@@ -49,6 +55,23 @@ __global__ void __launch_bounds__(256) stage_x_kernel(StageParams p) {
     // only read x and overwrite the image once everything before it in the stream has completed.
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    if (p.xflags) {
+        // Everything before this grid in the stream is complete, so this rank's own epoch is final: thread q waits
+        // for the q-th other rank to reach it.  A rank that never arrives costs `spins` probes, then status 32.
+        if ((int)threadIdx.x < p.nranks - 1) {
+            const int src = (int)threadIdx.x < p.rank ? (int)threadIdx.x : (int)threadIdx.x + 1;
+            const uint32_t want = p.xflags[XF_EPOCH];
+            bool seen = false;
+            for (uint32_t it = 0; it < p.spins && !seen; it++) {
+                uint32_t v;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p.xflags + XF_FLAGS + src) : "memory");
+                seen = (int32_t)(v - want) >= 0;
+                if (!seen && it > 64) __nanosleep(100);
+            }
+            if (!seen) atomicExch(p.status, 32);
+        }
+        __syncthreads();
+    }
     const int tok = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t k0 = ((int64_t)blockIdx.x * 256 + threadIdx.x) * 4;
     const float *xr = p.x + (int64_t)tok * p.xst;
@@ -194,6 +217,12 @@ struct GemvParams {
     int64_t yst, ysr;
     float *ypeer[GLLMK_MAX_PEERS];  // the same element positions in other GPUs' buffers (peer-mapped), npeer of them
     int npeer;
+    // exchange products: the block that completes the launch's last row tile advances this rank's epoch and
+    // signals it to every rank
+    uint32_t *xflags;                        // this rank's flag words, or nullptr
+    uint32_t *xflags_peer[GLLMK_MAX_PEERS];
+    int xrank;
+    int ntiles;                              // row tiles of the launch (counters[ntiles] counts the completed ones)
     const float *row_scales;
     int64_t n_row_scales;
     int64_t n;
@@ -365,6 +394,23 @@ __device__ __noinline__ void gemv_flush(const GemvParams &p, int tile, int slot,
                     // fused all-gather: the band also goes straight into the peers' copies of y over NVLink
                     for (int q = 0; q < p.npeer; q++) p.ypeer[q][at] = o;
                 }
+            }
+        }
+    }
+    if (p.xflags) {
+        // This warp's stores (local and peer) are ordered, at system scope, before its arrival; the warp that
+        // makes the count complete therefore follows every band store of this GPU, and tells all ranks.
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) {
+            const int done = atomicAdd(p.counters + p.ntiles, 1);
+            if (done == p.ntiles - 1) {
+                p.counters[p.ntiles] = 0;  // ready for the next launch
+                __threadfence_system();
+                const uint32_t e = p.xflags[XF_EPOCH] + 1u;
+                p.xflags[XF_EPOCH] = e;
+                for (int q = 0; q < p.npeer; q++)
+                    asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(p.xflags_peer[q] + XF_FLAGS + p.xrank), "r"(e) : "memory");
             }
         }
     }
@@ -676,25 +722,26 @@ static cudaError_t configure_and_launch(Ctx *c, GemvParams &p, int64_t ntg, cuda
     const int64_t tiles = ntg * 8;
     const size_t part_bytes = align_up((size_t)tiles * p.maxslot * 256 * sizeof(float), 256);
     *rc_out = ensure_red(c, part_bytes);
-    if (!*rc_out) *rc_out = ensure_cnt(c, (size_t)tiles * sizeof(int));
+    if (!*rc_out) *rc_out = ensure_cnt(c, (size_t)(tiles + 1) * sizeof(int));
     if (*rc_out) return cudaSuccess;
     p.partial = static_cast<float *>(c->red);
     p.counters = static_cast<int *>(c->cnt);
+    p.ntiles = (int)tiles;
     return launch_pdl(gemv_kernel<FMT, NT>, grid, 256, smem, s, c->gemv_pdl != 0, p);
 }
 
 int32_t gemv_launch(Ctx *c, const Weight *w, const float *x, int64_t xst, int64_t xsk, int m, float *y, int64_t yst,
                     int64_t ysr, const float *row_scales, int64_t n_row_scales, cudaStream_t s, void *const *y_peers,
-                    int n_peers, const float *x_up) {
+                    int n_peers, const float *x_up, const Exchange *xch) {
     if (raw_format(w->qt)) {
-        if (n_peers || x_up) return fail(c, GLLMK_STATUS_UNSUPPORTED, "gemv: quant type %d has no fused exchange / SwiGLU input", w->qt);
+        if (n_peers || x_up || xch) return fail(c, GLLMK_STATUS_UNSUPPORTED, "gemv: quant type %d has no fused exchange / SwiGLU input", w->qt);
         return raw_gemv_launch(c, w, x, xst, xsk, m, y, yst, ysr, row_scales, n_row_scales, s);
     }
     if (w->qt != GLLMK_QUANT_Q4K && w->qt != GLLMK_QUANT_Q8_0 && w->qt != GLLMK_QUANT_MXFP4 && w->qt != GLLMK_QUANT_NVFP4)
         return fail(c, GLLMK_STATUS_UNSUPPORTED, "gemv: quant type %d has no decode kernel", w->qt);
     // FP4 weights: the block-scaled tensor-core kernel (gemv_fp4.cu) unless the call needs what only this kernel
     // has (row scales, peer outputs, a fused SwiGLU input) or the context asks for the integer-decode kernel
-    if ((w->qt == GLLMK_QUANT_MXFP4 || w->qt == GLLMK_QUANT_NVFP4) && !row_scales && n_peers == 0 && !x_up && !c->gemv_fp4_int)
+    if ((w->qt == GLLMK_QUANT_MXFP4 || w->qt == GLLMK_QUANT_NVFP4) && !row_scales && n_peers == 0 && !x_up && !xch && !c->gemv_fp4_int)
         return gemv_fp4_launch(c, w, x, xst, xsk, m, y, yst, ysr, s);
     int32_t rc = ensure_ws(c, gemv_ws_bytes(w, m));
     if (rc) return rc;
@@ -716,8 +763,20 @@ int32_t gemv_launch(Ctx *c, const Weight *w, const float *x, int64_t xst, int64_
     p.nk = nk;
     p.m = m;
     p.status = c->status_dev;
+    if (xch && xch->flags_local) {
+        p.xflags = xch->flags_local;
+        for (int q = 0; q < xch->n_peers; q++) p.xflags_peer[q] = xch->flags_peer[q];
+        p.xrank = xch->rank;
+    }
 
     StageParams sp{x, x_up, xst, xsk, m, w->k, static_cast<uint8_t *>(c->ws)};
+    if (p.xflags) {
+        sp.xflags = xch->flags_local;
+        sp.nranks = xch->n_peers + 1;
+        sp.rank = xch->rank;
+        sp.spins = (uint32_t)c->peer_wait_spins;
+        sp.status = c->status_dev;
+    }
     dim3 sgrid((unsigned)(((size_t)nk * 256 + 1023) / 1024), (unsigned)m);
     static bool stage_carveout_set = false;
     if (!stage_carveout_set) {
@@ -773,7 +832,7 @@ int32_t gemv_launch(Ctx *c, const Weight *w, const float *x, int64_t xst, int64_
 // latency-critical serving loop that has pre-reserved all of HBM for weights and KV pages, under an
 // allocator that owns the whole device, or in a callback where cudaMalloc's implicit synchronisation
 // is not acceptable.  gllmk_gemv grows context-owned buffers on demand; this variant never does.  All of
-// the kernel's scratch (activation image, split-k partial sums, arrival counters, status word) lives in
+// the kernel's scratch (activation image, split-k partial sums, arrival counters) lives in
 // one fixed array inside the library image, so every GPU that loads the library holds these 8 MiB until
 // the process exits.
 // ---------------------------------------------------------------------------------------------
@@ -811,7 +870,9 @@ static cudaError_t launch_static(Ctx *c, GemvParams &p, int64_t ntg, unsigned ch
     p.rem = (int)(p.nsuper % ctas);
     p.maxslot = (p.nk - 1) / p.per_cta + 2;
     const size_t tiles = (size_t)ntg * 8;
-    // layout: status word [256] | counters [GEMV_STATIC_MAX_TILES ints] | activation image | partial sums
+    // layout: reserved [256] | counters [GEMV_STATIC_MAX_TILES ints] | activation image | partial sums.  The status
+    // word is NOT in the array: a give-up is reported through the context's own word (allocated when the context
+    // was created), so gllmk_ctx_status sees it like any other kernel's.
     const size_t cnt_off = 256, img_off = cnt_off + GEMV_STATIC_MAX_TILES * sizeof(int);
     const size_t part_off = align_up(img_off + img_bytes, 256);
     const size_t part_bytes = tiles * (size_t)p.maxslot * 256 * sizeof(float);
@@ -822,7 +883,7 @@ static cudaError_t launch_static(Ctx *c, GemvParams &p, int64_t ntg, unsigned ch
                        part_off + part_bytes, tiles, GEMV_STATIC_BYTES, GEMV_STATIC_MAX_TILES);
         return cudaSuccess;
     }
-    p.status = reinterpret_cast<int *>(base);
+    p.status = c->status_dev;
     p.counters = reinterpret_cast<int *>(base + cnt_off);
     p.img = base + img_off;
     p.partial = reinterpret_cast<float *>(base + part_off);
@@ -848,7 +909,9 @@ extern "C" int32_t gllmk_gemv_static(gllmk_ctx ctx, gllmk_weight wh, const float
     if (w->qt != GLLMK_QUANT_Q4K && w->qt != GLLMK_QUANT_Q8_0)
         return fail(c, GLLMK_STATUS_UNSUPPORTED, "gemv_static: quant type %d has no decode kernel", w->qt);
     if (w->device != c->device) return fail(c, GLLMK_STATUS_INVALID_ARG, "weight lives on another device");
-    if (row_scales && n_row_scales != 1 && n_row_scales != w->n) { row_scales = nullptr; n_row_scales = 0; }
+    if (row_scales && n_row_scales != 1 && n_row_scales != w->n)
+        return fail(c, GLLMK_STATUS_INVALID_ARG, "gemv_static: n_row_scales=%lld must be 1 or n=%lld", (long long)n_row_scales,
+                    (long long)w->n);
     int prev = -1;
     GK_CUDA(c, cudaGetDevice(&prev));
     if (prev != c->device) GK_CUDA(c, cudaSetDevice(c->device));
@@ -874,7 +937,7 @@ extern "C" int32_t gllmk_gemv_static(gllmk_ctx ctx, gllmk_weight wh, const float
             rc = fail(c, GLLMK_STATUS_INVALID_ARG, "gemv_static: k=%lld with m=%d needs a %zu-byte activation image, "
                       "more than the built-in %zu-byte area; use gllmk_gemv", (long long)w->k, m, img_bytes, GEMV_STATIC_BYTES);
         } else {
-            StageParams sp{x_dev, nullptr, x_stride_t, x_stride_k, m, w->k, base + img_off};
+            StageParams sp{x_dev, nullptr, x_stride_t, x_stride_k, m, w->k, base + img_off};  // no exchange: the other fields stay zero
             dim3 sgrid((unsigned)(((size_t)nk * 256 + 1023) / 1024), (unsigned)m);
             e = launch_pdl(stage_x_kernel, sgrid, 256, 0, s, false, sp);
             const int64_t ntg = w->n_pad / 128;

@@ -40,16 +40,16 @@ struct Fmt;
 
 template <>
 struct Fmt<GLLMK_QUANT_Q6_K> {  // ql[128] @0, qh[64] @128, scales[16] i8 @192, d f16 @208
-    static constexpr int BS = 256, BB = 210, DB = 224, ITEMS = 64, EPI = 4;  // DB: bytes per block slot on the device
+    static constexpr int BS = FD_Q6K.block_size, BB = FD_Q6K.block_bytes, DB = 224, ITEMS = 64, EPI = 4;  // DB: bytes per block slot on the device
     static __device__ __forceinline__ void item(const uint8_t *b, int it, float *v, int *e) {
         const int g = it >> 5, l = it & 31, is = l >> 4;
-        const uint8_t la = b[g * 64 + l], lb = b[g * 64 + l + 32], h = b[128 + g * 32 + l];
-        const int8_t *sc = reinterpret_cast<const int8_t *>(b + 192 + g * 8);
-        const float d = f16_at(b + 208);
-        const int q1 = (int)((la & 0xF) | (((h >> 0) & 3) << 4)) - 32;
-        const int q2 = (int)((lb & 0xF) | (((h >> 2) & 3) << 4)) - 32;
-        const int q3 = (int)((la >> 4) | (((h >> 4) & 3) << 4)) - 32;
-        const int q4 = (int)((lb >> 4) | (((h >> 6) & 3) << 4)) - 32;
+        const uint8_t la = b[FD_Q6K.data_offset + g * 64 + l], lb = b[FD_Q6K.data_offset + g * 64 + l + 32], h = b[FD_Q6K.data_high_offset + g * 32 + l];
+        const int8_t *sc = reinterpret_cast<const int8_t *>(b + FD_Q6K.sub_scales_offset + g * 8);
+        const float d = f16_at(b + FD_Q6K.scale_offset);
+        const int q1 = (int)((la & 0xF) | (((h >> 0) & 3) << 4)) - FD_Q6K.static_bias;
+        const int q2 = (int)((lb & 0xF) | (((h >> 2) & 3) << 4)) - FD_Q6K.static_bias;
+        const int q3 = (int)((la >> 4) | (((h >> 4) & 3) << 4)) - FD_Q6K.static_bias;
+        const int q4 = (int)((lb >> 4) | (((h >> 6) & 3) << 4)) - FD_Q6K.static_bias;
         v[0] = __fmul_rn(__fmul_rn(d, (float)sc[is]), (float)q1);
         v[1] = __fmul_rn(__fmul_rn(d, (float)sc[is + 2]), (float)q2);
         v[2] = __fmul_rn(__fmul_rn(d, (float)sc[is + 4]), (float)q3);
@@ -63,14 +63,14 @@ struct Fmt<GLLMK_QUANT_Q6_K> {  // ql[128] @0, qh[64] @128, scales[16] i8 @192, 
 
 template <>
 struct Fmt<GLLMK_QUANT_Q5_K> {  // d @0, dmin @2, scales[12] @4, qh[32] @16, qs[128] @48
-    static constexpr int BS = 256, BB = 176, DB = 176, ITEMS = 128, EPI = 2;
+    static constexpr int BS = FD_Q5K.block_size, BB = FD_Q5K.block_bytes, DB = 176, ITEMS = 128, EPI = 2;
     static __device__ __forceinline__ void item(const uint8_t *b, int it, float *v, int *e) {
         const int g = it >> 5, l = it & 31;
-        const float d = f16_at(b), mn = f16_at(b + 2);
+        const float d = f16_at(b + FD_Q5K.scale_offset), mn = f16_at(b + FD_Q5K.scale_min_offset);
         float sc1, m1, sc2, m2;
-        scale_min_k4(2 * g, b + 4, sc1, m1);
-        scale_min_k4(2 * g + 1, b + 4, sc2, m2);
-        const uint8_t q = b[48 + g * 32 + l], h = b[16 + l];
+        scale_min_k4(2 * g, b + FD_Q5K.sub_scales_offset, sc1, m1);
+        scale_min_k4(2 * g + 1, b + FD_Q5K.sub_scales_offset, sc2, m2);
+        const uint8_t q = b[FD_Q5K.data_offset + g * 32 + l], h = b[FD_Q5K.data_high_offset + l];
         const int v1 = (q & 0xF) + (((h >> (2 * g)) & 1) ? 16 : 0);
         const int v2 = (q >> 4) + (((h >> (2 * g + 1)) & 1) ? 16 : 0);
         v[0] = __fsub_rn(__fmul_rn(__fmul_rn(d, sc1), (float)v1), __fmul_rn(mn, m1));
@@ -82,26 +82,26 @@ struct Fmt<GLLMK_QUANT_Q5_K> {  // d @0, dmin @2, scales[12] @4, qh[32] @16, qs[
 
 template <>
 struct Fmt<GLLMK_QUANT_Q8_K> {  // d f32 @0, qs[256] i8 @4, bsums[16] i16 @260 (not used by decode)
-    static constexpr int BS = 256, BB = 292, DB = 292, ITEMS = 64, EPI = 4;
+    static constexpr int BS = FD_Q8K.block_size, BB = FD_Q8K.block_bytes, DB = 292, ITEMS = 64, EPI = 4;
     static __device__ __forceinline__ void item(const uint8_t *b, int it, float *v, int *e) {
         const float d = __uint_as_float((uint32_t)b[0] | ((uint32_t)b[1] << 8) | ((uint32_t)b[2] << 16) | ((uint32_t)b[3] << 24));
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             // lanes take neighbouring bytes: element it + 64 j
             e[j] = it + 64 * j;
-            v[j] = __fmul_rn(d, (float)(int8_t)b[4 + e[j]]);
+            v[j] = __fmul_rn(d, (float)(int8_t)b[FD_Q8K.data_offset + e[j]]);
         }
     }
 };
 
 template <>
 struct Fmt<GLLMK_QUANT_Q4_0> {  // d @0, qs[16] @2: byte j -> elements j (low nibble) and j + 16 (high nibble)
-    static constexpr int BS = 32, BB = 18, DB = 18, ITEMS = 16, EPI = 2;
+    static constexpr int BS = FD_Q4_0.block_size, BB = FD_Q4_0.block_bytes, DB = 18, ITEMS = 16, EPI = 2;
     static __device__ __forceinline__ void item(const uint8_t *b, int it, float *v, int *e) {
         const float d = f16_at(b);
-        const uint8_t q = b[2 + it];
-        v[0] = __fmul_rn(d, __fsub_rn((float)(q & 0xF), 8.0f));
-        v[1] = __fmul_rn(d, __fsub_rn((float)(q >> 4), 8.0f));
+        const uint8_t q = b[FD_Q4_0.data_offset + it];
+        v[0] = __fmul_rn(d, __fsub_rn((float)(q & 0xF), (float)FD_Q4_0.static_bias));
+        v[1] = __fmul_rn(d, __fsub_rn((float)(q >> 4), (float)FD_Q4_0.static_bias));
         e[0] = it;
         e[1] = it + 16;
     }
@@ -109,14 +109,14 @@ struct Fmt<GLLMK_QUANT_Q4_0> {  // d @0, qs[16] @2: byte j -> elements j (low ni
 
 template <>
 struct Fmt<GLLMK_QUANT_Q5_0> {  // d @0, qh[4] @2 (bit j = fifth bit of element j), qs[16] @6
-    static constexpr int BS = 32, BB = 22, DB = 22, ITEMS = 16, EPI = 2;
+    static constexpr int BS = FD_Q5_0.block_size, BB = FD_Q5_0.block_bytes, DB = 22, ITEMS = 16, EPI = 2;
     static __device__ __forceinline__ void item(const uint8_t *b, int it, float *v, int *e) {
         const float d = f16_at(b);
         const uint32_t qh = (uint32_t)b[2] | ((uint32_t)b[3] << 8) | ((uint32_t)b[4] << 16) | ((uint32_t)b[5] << 24);
-        const uint8_t q = b[6 + it];
+        const uint8_t q = b[FD_Q5_0.data_offset + it];
         const uint32_t lo = (q & 0xF) | (((qh >> it) & 1u) << 4), hi = (q >> 4) | (((qh >> (it + 16)) & 1u) << 4);
-        v[0] = __fmul_rn(d, __fsub_rn((float)lo, 16.0f));
-        v[1] = __fmul_rn(d, __fsub_rn((float)hi, 16.0f));
+        v[0] = __fmul_rn(d, __fsub_rn((float)lo, (float)FD_Q5_0.static_bias));
+        v[1] = __fmul_rn(d, __fsub_rn((float)hi, (float)FD_Q5_0.static_bias));
         e[0] = it;
         e[1] = it + 16;
     }
@@ -213,9 +213,9 @@ struct Dp<GLLMK_QUANT_Q6_K> {
     static constexpr bool MIN = false;
     static __device__ __forceinline__ void unit(const uint8_t *b, int u, uint32_t *q, int *ko, float *ws, float *) {
         const int g = u >> 2, p = u & 3, is = p >> 1;  // bytes 8p .. 8p + 7 of the half-block's ql / qh runs
-        const uint2 A = *reinterpret_cast<const uint2 *>(b + g * 64 + 8 * p);
-        const uint2 B = *reinterpret_cast<const uint2 *>(b + g * 64 + 32 + 8 * p);
-        const uint2 H = *reinterpret_cast<const uint2 *>(b + 128 + g * 32 + 8 * p);
+        const uint2 A = *reinterpret_cast<const uint2 *>(b + FD_Q6K.data_offset + g * 64 + 8 * p);
+        const uint2 B = *reinterpret_cast<const uint2 *>(b + FD_Q6K.data_offset + g * 64 + 32 + 8 * p);
+        const uint2 H = *reinterpret_cast<const uint2 *>(b + FD_Q6K.data_high_offset + g * 32 + 8 * p);
         q[0] = q6_word(A.x, H.x << 4);
         q[1] = q6_word(A.y, H.y << 4);
         q[2] = q6_word(B.x, H.x << 2);
@@ -225,9 +225,9 @@ struct Dp<GLLMK_QUANT_Q6_K> {
         q[6] = q6_word(B.x >> 4, H.x >> 2);
         q[7] = q6_word(B.y >> 4, H.y >> 2);
         // the eight scale bytes of this half in one load; run j uses byte is + 2 j
-        const uint2 S = *reinterpret_cast<const uint2 *>(b + 192 + g * 8);
+        const uint2 S = *reinterpret_cast<const uint2 *>(b + FD_Q6K.sub_scales_offset + g * 8);
         const uint32_t s01 = S.x >> (8 * is), s23 = S.y >> (8 * is);
-        const float d = 0.25f * f16_even(b + 208);
+        const float d = 0.25f * f16_even(b + FD_Q6K.scale_offset);
         ws[0] = d * (float)(int8_t)(s01 & 0xFF);
         ws[1] = d * (float)(int8_t)((s01 >> 16) & 0xFF);
         ws[2] = d * (float)(int8_t)(s23 & 0xFF);
@@ -243,8 +243,8 @@ struct Dp<GLLMK_QUANT_Q5_K> {
     static constexpr bool MIN = true;
     static __device__ __forceinline__ void unit(const uint8_t *b, int u, uint32_t *q, int *ko, float *ws, float *wm) {
         const int g = u >> 1, p = u & 1;  // bytes 16p .. 16p + 15 of the 32-byte group g: two sub-blocks, two pairs each
-        const uint4 A = *reinterpret_cast<const uint4 *>(b + 48 + g * 32 + 16 * p);
-        const uint4 H = *reinterpret_cast<const uint4 *>(b + 16 + 16 * p);
+        const uint4 A = *reinterpret_cast<const uint4 *>(b + FD_Q5K.data_offset + g * 32 + 16 * p);
+        const uint4 H = *reinterpret_cast<const uint4 *>(b + FD_Q5K.data_high_offset + 16 * p);
         const uint32_t aw[4] = {A.x, A.y, A.z, A.w}, hw[4] = {H.x, H.y, H.z, H.w};
 #pragma unroll
         for (int i = 0; i < 4; i++) {
@@ -253,6 +253,8 @@ struct Dp<GLLMK_QUANT_Q5_K> {
         }
         // d and dmin in one word; the twelve scale bytes as three words.  Sub-blocks 2g and 2g + 1 (get_scale_min_k4,
         // k_quant.rs:388-397) without a branch: both forms from bytes jj = j & 3 of the words, chosen by j < 4.
+        static_assert(FD_Q5K.scale_offset == 0 && FD_Q5K.scale_min_offset == 2 && FD_Q5K.sub_scales_offset == 4 && FD_Q5K.data_high_offset == 16,
+                      "Q5_K header is the block's first 16 bytes");
         const uint4 hd = *reinterpret_cast<const uint4 *>(b);
         const uint32_t dm = hd.x, w0 = hd.y, w1 = hd.z, w2 = hd.w;
         const float d = __half2float(__ushort_as_half((unsigned short)(dm & 0xFFFF)));
@@ -278,13 +280,13 @@ struct Dp<GLLMK_QUANT_Q8_K> {
     static constexpr int UNITS = 16, NW = 4;
     static constexpr bool MIN = false;
     static __device__ __forceinline__ void unit(const uint8_t *b, int u, uint32_t *q, int *ko, float *ws, float *) {
-        ws[0] = ws[1] = __uint_as_float(ld32<true>(b));
+        ws[0] = ws[1] = __uint_as_float(ld32<true>(b + FD_Q8K.scale_offset));
         ko[0] = 8 * u;
         ko[1] = 128 + 8 * u;
-        q[0] = ld32<true>(b + 4 + 8 * u);
-        q[1] = ld32<true>(b + 8 + 8 * u);
-        q[2] = ld32<true>(b + 132 + 8 * u);
-        q[3] = ld32<true>(b + 136 + 8 * u);
+        q[0] = ld32<true>(b + FD_Q8K.data_offset + 8 * u);
+        q[1] = ld32<true>(b + FD_Q8K.data_offset + 4 + 8 * u);
+        q[2] = ld32<true>(b + FD_Q8K.data_offset + 128 + 8 * u);
+        q[3] = ld32<true>(b + FD_Q8K.data_offset + 132 + 8 * u);
     }
 };
 
@@ -293,7 +295,7 @@ struct Dp<GLLMK_QUANT_Q4_0> {
     static constexpr int UNITS = 2, NW = 4;
     static constexpr bool MIN = false;
     static __device__ __forceinline__ void unit(const uint8_t *b, int u, uint32_t *q, int *ko, float *ws, float *) {
-        const uint32_t W0 = ld32<false>(b + 2 + 8 * u), W1 = ld32<false>(b + 6 + 8 * u);
+        const uint32_t W0 = ld32<false>(b + FD_Q4_0.data_offset + 8 * u), W1 = ld32<false>(b + FD_Q4_0.data_offset + 4 + 8 * u);
         // a nibble with bit 3 flipped is q - 8 in 4-bit two's complement; in the high half of a byte it is the s8 16 (q - 8)
         q[0] = ((W0 ^ 0x08080808u) << 4) & 0xF0F0F0F0u;
         q[1] = ((W1 ^ 0x08080808u) << 4) & 0xF0F0F0F0u;
@@ -301,7 +303,7 @@ struct Dp<GLLMK_QUANT_Q4_0> {
         q[3] = (W1 ^ 0x80808080u) & 0xF0F0F0F0u;
         ko[0] = 8 * u;
         ko[1] = 16 + 8 * u;
-        ws[0] = ws[1] = 0.0625f * f16_even(b);
+        ws[0] = ws[1] = 0.0625f * f16_even(b + FD_Q4_0.scale_offset);
     }
 };
 
@@ -310,7 +312,8 @@ struct Dp<GLLMK_QUANT_Q5_0> {
     static constexpr int UNITS = 2, NW = 4;
     static constexpr bool MIN = false;
     static __device__ __forceinline__ void unit(const uint8_t *b, int u, uint32_t *q, int *ko, float *ws, float *) {
-        const uint32_t W0 = ld32<false>(b + 6 + 8 * u), W1 = ld32<false>(b + 10 + 8 * u), qh = ld32<false>(b + 2);
+        const uint32_t W0 = ld32<false>(b + FD_Q5_0.data_offset + 8 * u), W1 = ld32<false>(b + FD_Q5_0.data_offset + 4 + 8 * u),
+                       qh = ld32<false>(b + FD_Q5_0.data_high_offset);
         // a 5-bit value with bit 4 flipped is q - 16 in 5-bit two's complement; three places up it is the s8 8 (q - 16)
         q[0] = ((((W0 & 0x0F0F0F0Fu) | (spread4(qh >> (8 * u)) << 4)) ^ 0x10101010u) << 3) & 0xF8F8F8F8u;
         q[1] = ((((W1 & 0x0F0F0F0Fu) | (spread4(qh >> (8 * u + 4)) << 4)) ^ 0x10101010u) << 3) & 0xF8F8F8F8u;

@@ -15,6 +15,7 @@ struct PeerBarrierParams {
     uint32_t *peer[GLLMK_MAX_PEERS];     // the other ranks' flag words (peer-mapped)
     int npeer, rank;
     uint32_t seq;
+    uint32_t spins;                      // probes before the wait gives up
     int *status;
 };
 
@@ -48,13 +49,32 @@ __global__ void peer_barrier_kernel(const __grid_constant__ PeerBarrierParams p)
     // bounded wait for the same sequence number from that rank (it can be at most one barrier ahead)
     const uint32_t *flag = p.mine + src;
     bool seen = false;
-    for (uint32_t it = 0; it < (1u << 22) && !seen; it++) {
+    for (uint32_t it = 0; it < p.spins && !seen; it++) {
         uint32_t v;
         asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(flag) : "memory");
         seen = (int32_t)(v - seq) >= 0;
         if (!seen && it > 64) __nanosleep(200);
     }
     if (!seen) atomicExch(p.status, 31);  // the host reads it with gllmk_ctx_status; the kernel just returns
+}
+
+// End of a chain of exchange products (gllmk_gemv_exchange): thread q waits until the q-th other rank has
+// completed as many of them as this rank.  Inside a chain the next product's staging kernel does this wait itself.
+__global__ void exchange_wait_kernel(const uint32_t *flags, int nranks, int rank, uint32_t spins, int *status) {
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    const int q = threadIdx.x;
+    if (q >= nranks - 1) return;
+    const int src = q < rank ? q : q + 1;
+    const uint32_t want = flags[XF_EPOCH];
+    bool seen = false;
+    for (uint32_t it = 0; it < spins && !seen; it++) {
+        uint32_t v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(flags + XF_FLAGS + src) : "memory");
+        seen = (int32_t)(v - want) >= 0;
+        if (!seen && it > 64) __nanosleep(100);
+    }
+    if (!seen) atomicExch(status, 32);
 }
 
 int32_t peer_barrier_launch(Ctx *c, uint32_t *mine, uint32_t *const *peers, int n_peers, int rank, uint32_t seq, cudaStream_t s) {
@@ -64,6 +84,7 @@ int32_t peer_barrier_launch(Ctx *c, uint32_t *mine, uint32_t *const *peers, int 
     p.npeer = n_peers;
     p.rank = rank;
     p.seq = seq;
+    p.spins = (uint32_t)c->peer_wait_spins;
     p.status = c->status_dev;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(1);
@@ -149,4 +170,48 @@ extern "C" int32_t gllmk_peer_barrier(gllmk_ctx ctx, void *flags_local, void *co
     if (n_peers == 0) return GLLMK_STATUS_OK;
     return peer_barrier_launch(c, static_cast<uint32_t *>(flags_local), reinterpret_cast<uint32_t *const *>(flags_peers), n_peers, rank,
                                seq, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int32_t gllmk_gemv_exchange(gllmk_ctx ctx, gllmk_weight wh, const float *x_dev, int64_t x_stride_t, int64_t x_stride_k,
+                                       int32_t m, float *y_local, int64_t y_stride_t, int64_t y_stride_r, void *const *y_peers,
+                                       void *flags_local, void *const *flags_peers, int32_t n_peers, int32_t rank, void *stream) {
+    if (!ctx || !wh || !x_dev || !y_local || !flags_local || (n_peers > 0 && (!y_peers || !flags_peers))) return GLLMK_STATUS_INVALID_ARG;
+    Ctx *c = static_cast<Ctx *>(ctx);
+    const Weight *w = static_cast<const Weight *>(wh);
+    if (m < 1 || m > GLLMK_GEMV_MAX_M) return fail(c, GLLMK_STATUS_INVALID_ARG, "gemv_exchange: m=%d outside 1..%d", m, GLLMK_GEMV_MAX_M);
+    if (n_peers < 0 || n_peers > GLLMK_MAX_PEERS || rank < 0 || rank > n_peers)
+        return fail(c, GLLMK_STATUS_INVALID_ARG, "gemv_exchange: %d peers / rank %d out of range", n_peers, rank);
+    Exchange x{};
+    x.flags_local = static_cast<uint32_t *>(flags_local);
+    x.n_peers = n_peers;
+    x.rank = rank;
+    for (int q = 0; q < n_peers; q++) {
+        if (!y_peers[q] || !flags_peers[q]) return fail(c, GLLMK_STATUS_INVALID_ARG, "gemv_exchange: null peer pointer");
+        x.flags_peer[q] = static_cast<uint32_t *>(flags_peers[q]);
+    }
+    if (w->device != c->device) return fail(c, GLLMK_STATUS_INVALID_ARG, "weight lives on another device");
+    DeviceGuard g(c->device);
+    return gemv_launch(c, w, x_dev, x_stride_t, x_stride_k, m, y_local, y_stride_t, y_stride_r, nullptr, 0,
+                       static_cast<cudaStream_t>(stream), y_peers, n_peers, nullptr, &x);
+}
+
+extern "C" int32_t gllmk_exchange_wait(gllmk_ctx ctx, void *flags_local, int32_t n_peers, int32_t rank, void *stream) {
+    if (!ctx || !flags_local) return GLLMK_STATUS_INVALID_ARG;
+    Ctx *c = static_cast<Ctx *>(ctx);
+    if (n_peers < 0 || n_peers > GLLMK_MAX_PEERS || rank < 0 || rank > n_peers)
+        return fail(c, GLLMK_STATUS_INVALID_ARG, "exchange_wait: %d peers / rank %d out of range", n_peers, rank);
+    if (n_peers == 0) return GLLMK_STATUS_OK;
+    DeviceGuard g(c->device);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1);
+    cfg.blockDim = dim3(32);
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = c->gemv_pdl != 0 ? 1 : 0;
+    GK_CUDA(c, cudaLaunchKernelEx(&cfg, exchange_wait_kernel, static_cast<const uint32_t *>(flags_local), n_peers + 1, (int)rank,
+                                  (uint32_t)c->peer_wait_spins, c->status_dev));
+    return GLLMK_STATUS_OK;
 }

@@ -4,6 +4,17 @@
 
 namespace gllmk {
 
+// The repack kernels move a Q4_K block's header (d, dmin, the 12 scale bytes) as its first 16-byte word and the
+// block as nine such words, Q8_0's scale as the two bytes in front of its data, the FP4 scale bytes in front of
+// theirs: what the format descriptors must say for those loads to be right.
+static_assert(FD_Q4K.scale_offset == 0 && FD_Q4K.scale_min_offset == 2 && FD_Q4K.sub_scales_offset == 4 && FD_Q4K.data_offset == 16 &&
+                  FD_Q4K.block_bytes == 144 && FD_Q4K.sub_scales_bits == 6 && FD_Q4K.data_low_first == 1,
+              "Q4_K block layout");
+static_assert(FD_Q8_0.scale_offset == 0 && FD_Q8_0.data_offset == 2 && FD_Q8_0.block_bytes == 34 && FD_Q8_0.data_signed == 1, "Q8_0 block layout");
+static_assert(FD_MXFP4.scale_offset == 0 && FD_MXFP4.data_offset == 1 && FD_MXFP4.block_bytes == 17, "MXFP4 inline block layout");
+static_assert(FD_NVFP4.sub_scales_offset == 0 && FD_NVFP4.sub_scales_count == 4 && FD_NVFP4.data_offset == 4 && FD_NVFP4.block_bytes == 36,
+              "NVFP4 block layout");
+
 static inline unsigned grid_for(size_t n, unsigned block) { return (unsigned)((n + block - 1) / block); }
 
 // ================================ Q4_K =====================================================
@@ -33,7 +44,7 @@ __global__ void repack_q4k_qs(const uint8_t *__restrict__ src, uint8_t *__restri
     for (int h = 0; h < 2; h++) {
         const int64_t row = 16 * T + g + 8 * h;
         if (row < n) {
-            const uint2 w = *reinterpret_cast<const uint2 *>(src + ((size_t)row * nb + b) * 144 + 16 + 32 * pgrp + 8 * t);
+            const uint2 w = *reinterpret_cast<const uint2 *>(src + ((size_t)row * nb + b) * FD_Q4K.block_bytes + FD_Q4K.data_offset + 32 * pgrp + 8 * t);
             v[2 * h] = w.x;
             v[2 * h + 1] = w.y;
         }
@@ -50,7 +61,7 @@ __global__ void repack_q4k_hdr(const uint8_t *__restrict__ src, uint8_t *__restr
     const int64_t T = (int64_t)(tb / (size_t)nb), b = (int64_t)(tb % (size_t)nb);
     const int64_t row = 16 * T + rr;
     uint4 v = make_uint4(0, 0, 0, 0);
-    if (row < n) v = reinterpret_cast<const uint4 *>(src + ((size_t)row * nb + b) * 144)[0];
+    if (row < n) v = reinterpret_cast<const uint4 *>(src + ((size_t)row * nb + b) * FD_Q4K.block_bytes)[0];
     uint8_t s[12];
     *reinterpret_cast<uint32_t *>(s) = v.y;
     *reinterpret_cast<uint32_t *>(s + 4) = v.z;
@@ -105,7 +116,7 @@ __global__ void unpack_q4k(const uint8_t *__restrict__ chunks, uint8_t *__restri
         v = make_uint4(q4k_word(chunk, rr, w0), q4k_word(chunk, rr, w0 + 1), q4k_word(chunk, rr, w0 + 2),
                        q4k_word(chunk, rr, w0 + 3));
     }
-    reinterpret_cast<uint4 *>(dst + rb * 144)[u9] = v;
+    reinterpret_cast<uint4 *>(dst + rb * FD_Q4K.block_bytes)[u9] = v;
     (void)n;
 }
 // out[row][256b + ...] following k_quant.rs:7-56; thread = one 32-bit word of qs (4 low + 4 high outputs)
@@ -174,7 +185,7 @@ __global__ void repack_q80_qs(const uint8_t *__restrict__ src, uint8_t *__restri
         const int64_t row = 16 * T + g + 8 * h;
         if (row < n && b < nb) {
             const unsigned short *p =
-                reinterpret_cast<const unsigned short *>(src + ((size_t)row * nb + b) * 34 + 2 + 8 * t);
+                reinterpret_cast<const unsigned short *>(src + ((size_t)row * nb + b) * FD_Q8_0.block_bytes + FD_Q8_0.data_offset + 8 * t);
             v[2 * h] = (uint32_t)p[0] | ((uint32_t)p[1] << 16);
             v[2 * h + 1] = (uint32_t)p[2] | ((uint32_t)p[3] << 16);
         }
@@ -191,7 +202,7 @@ __global__ void repack_q80_d(const uint8_t *__restrict__ src, uint8_t *__restric
     const int64_t T = (int64_t)(tb / (size_t)nb8), b8 = (int64_t)(tb % (size_t)nb8);
     const int64_t row = 16 * T + rr, b = 8 * b8 + bb;
     unsigned short v = 0;
-    if (row < n && b < nb) v = *reinterpret_cast<const unsigned short *>(src + ((size_t)row * nb + b) * 34);
+    if (row < n && b < nb) v = *reinterpret_cast<const unsigned short *>(src + ((size_t)row * nb + b) * FD_Q8_0.block_bytes + FD_Q8_0.scale_offset);
     reinterpret_cast<unsigned short *>(chunks + q4k_chunk_index(T, b8, nb8) * Q80_CHUNK + 4096)[rr * 8 + bb] = v;
 }
 __global__ void unpack_q80(const uint8_t *__restrict__ chunks, uint8_t *__restrict__ dst, int64_t n, int64_t nb,
@@ -206,11 +217,11 @@ __global__ void unpack_q80(const uint8_t *__restrict__ chunks, uint8_t *__restri
     const uint8_t *chunk = chunks + q4k_chunk_index(T, b >> 3, nb8) * Q80_CHUNK;
     const uint4 q = reinterpret_cast<const uint4 *>(chunk)[(b & 7) * 32 + 4 * g + t];
     const uint32_t w0 = h ? q.z : q.x, w1 = h ? q.w : q.y;
-    unsigned short *p = reinterpret_cast<unsigned short *>(dst + rb * 34 + 2 + 8 * t);
+    unsigned short *p = reinterpret_cast<unsigned short *>(dst + rb * FD_Q8_0.block_bytes + FD_Q8_0.data_offset + 8 * t);
     p[0] = (unsigned short)(w0 & 0xFFFF); p[1] = (unsigned short)(w0 >> 16);
     p[2] = (unsigned short)(w1 & 0xFFFF); p[3] = (unsigned short)(w1 >> 16);
     if (t == 0)
-        *reinterpret_cast<unsigned short *>(dst + rb * 34) =
+        *reinterpret_cast<unsigned short *>(dst + rb * FD_Q8_0.block_bytes + FD_Q8_0.scale_offset) =
             reinterpret_cast<const unsigned short *>(chunk + 4096)[rr * 8 + (b & 7)];
     (void)n;
 }
@@ -263,8 +274,8 @@ __global__ void repack_fp4_data(const uint8_t *__restrict__ blocks, uint32_t *__
     if (row < n && w < (k >> 3)) {
         const uint8_t *p;
         if (mode == 0) p = blocks + (size_t)row * (k >> 1) + 4 * w;
-        else if (mode == 1) p = blocks + ((size_t)row * (k >> 5) + (w >> 2)) * 17 + 1 + 4 * (w & 3);
-        else p = blocks + ((size_t)row * (k >> 6) + (w >> 3)) * 36 + 4 + 4 * (w & 7);
+        else if (mode == 1) p = blocks + ((size_t)row * (k >> 5) + (w >> 2)) * FD_MXFP4.block_bytes + FD_MXFP4.data_offset + 4 * (w & 3);
+        else p = blocks + ((size_t)row * (k >> 6) + (w >> 3)) * FD_NVFP4.block_bytes + FD_NVFP4.data_offset + 4 * (w & 7);
         v = (uint32_t)p[0] | ((uint32_t)p[1] << 8) | ((uint32_t)p[2] << 16) | ((uint32_t)p[3] << 24);
     }
     data[fp4_data_offset(row, 4 * w, k_pad) >> 2] = v;
@@ -278,8 +289,8 @@ __global__ void repack_fp4_sf(const uint8_t *__restrict__ blocks, const uint8_t 
     uint8_t v = 0;
     if (row < n && s < spr) {
         if (mode == 0) v = scales[(size_t)row * spr + s];
-        else if (mode == 1) v = blocks[((size_t)row * spr + s) * 17];
-        else v = blocks[((size_t)row * (k >> 6) + (s >> 2)) * 36 + (s & 3)];
+        else if (mode == 1) v = blocks[((size_t)row * spr + s) * FD_MXFP4.block_bytes + FD_MXFP4.scale_offset];
+        else v = blocks[((size_t)row * (k >> 6) + (s >> 2)) * FD_NVFP4.block_bytes + FD_NVFP4.sub_scales_offset + (s & 3)];
     }
     sf[sf_offset(row, s, spr_pad)] = v;
 }
@@ -294,7 +305,7 @@ __global__ void unpack_fp4(const uint8_t *__restrict__ data, const uint8_t *__re
         blocks[idx] = v;
         if ((by & 15) == 0) scales[(size_t)row * (k >> 5) + (by >> 4)] = sf[sf_offset(row, by >> 4, k_pad >> 5)];
     } else {
-        uint8_t *blk = blocks + ((size_t)row * (k >> 6) + (by >> 5)) * 36;
+        uint8_t *blk = blocks + ((size_t)row * (k >> 6) + (by >> 5)) * FD_NVFP4.block_bytes;
         blk[4 + (by & 31)] = v;
         if ((by & 7) == 0) blk[(by & 31) >> 3] = sf[sf_offset(row, by >> 3, k_pad >> 4)];
     }
@@ -344,12 +355,12 @@ __global__ void dequant_raw_kernel(int qt, const uint8_t *__restrict__ blocks, c
     const int e = (int)(idx % bs);
     float r;
     if (qt == GLLMK_QUANT_Q4K) {
-        const uint8_t *b = blocks + blk * 144;
+        const uint8_t *b = blocks + blk * FD_Q4K.block_bytes;
         const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(b)));
-        const float dmin = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(b + 2)));
-        const uint8_t *s = b + 4;
+        const float dmin = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(b + FD_Q4K.scale_min_offset)));
+        const uint8_t *s = b + FD_Q4K.sub_scales_offset;
         const int mini = e >> 5, l = e & 31, g = mini >> 1;
-        const uint8_t byte = b[16 + 32 * g + l];
+        const uint8_t byte = b[FD_Q4K.data_offset + 32 * g + l];
         const float q = (float)((mini & 1) ? (byte >> 4) : (byte & 15));
         float sc, m;
         if (mini < 4) { sc = (float)(s[mini] & 63); m = (float)(s[mini + 4] & 63); }
@@ -359,15 +370,15 @@ __global__ void dequant_raw_kernel(int qt, const uint8_t *__restrict__ blocks, c
         }
         r = __fsub_rn(__fmul_rn(__fmul_rn(d, sc), q), __fmul_rn(dmin, m));
     } else if (qt == GLLMK_QUANT_Q8_0) {
-        const uint8_t *b = blocks + blk * 34;
+        const uint8_t *b = blocks + blk * FD_Q8_0.block_bytes;
         const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(b)));
-        r = __fmul_rn(d, (float)(int8_t)b[2 + e]);
+        r = __fmul_rn(d, (float)(int8_t)b[FD_Q8_0.data_offset + e]);
     } else if (qt == GLLMK_QUANT_MXFP4) {
         const uint8_t byte = blocks[blk * (bs / 2) + (e >> 1)];
         r = __fmul_rn(e2m1_to_f32((e & 1) ? (byte >> 4) : (byte & 15)), e8m0_to_f32(scales[blk]));
     } else {
-        const uint8_t *b = blocks + blk * 36;
-        const uint8_t byte = b[4 + (e >> 1)];
+        const uint8_t *b = blocks + blk * FD_NVFP4.block_bytes;
+        const uint8_t byte = b[FD_NVFP4.data_offset + (e >> 1)];
         const float s = __fmul_rn(global, e4m3_to_f32(b[e >> 4]));
         r = __fmul_rn(s, e2m1_to_f32((e & 1) ? (byte >> 4) : (byte & 15)));
     }

@@ -78,6 +78,7 @@ class GpuKernels:
     """B200 implementation of the reference's quantized operators (one context = one device)."""
 
     GEMV_MAX_M = 16
+    GEMM_GEMV_MAX_M = 48  # f32 products up to this many tokens run as passes of the decode kernel
 
     def __init__(self, device: int = 0):
         h = C.c_void_p()
@@ -225,6 +226,28 @@ class GpuKernels:
         self._check(rc, "gllmk_dequantize_i32_f32")
         return out
 
+    def quantize_act_int8(self, x, as_unsigned: bool = False, stream=None):
+        """quantize_from_fp32 / Int8PerTensor on a CUDA f32 tensor [rows, k]: (int8 tensor — or uint8 = q + 128 —, scale
+        as a 1-element CUDA tensor: no host synchronisation)."""
+        import torch
+        rows, k = x.shape
+        q = torch.empty((rows, k), dtype=torch.uint8 if as_unsigned else torch.int8, device=x.device)
+        sc = torch.zeros(2, dtype=torch.float32, device=x.device)
+        self._check(lib().gllmk_quantize_act_int8(self._ctx, _ptr(x), rows, k, x.stride(0), _ptr(q), k, int(as_unsigned), _ptr(sc),
+                                                  _stream(stream)), "gllmk_quantize_act_int8")
+        return q, sc[:1]
+
+    def w8a8_linear(self, w: Weight, x, scale_b: float, bias=None, activation: int = 0, y=None, stream=None):
+        """y = act((quantize(x) . W) * scale_x * scale_b + bias): f32 in, f32 out, int8 tensor-core product."""
+        import torch
+        m = x.shape[0]
+        if y is None:
+            y = torch.empty((m, w.n), dtype=torch.float32, device=x.device)
+        rc = lib().gllmk_w8a8_linear_f32(self._ctx, w._h, _ptr(x), x.stride(0), m, _ptr(y), y.stride(0), float(scale_b), _ptr(bias),
+                                         int(activation), _stream(stream))
+        self._check(rc, "gllmk_w8a8_linear_f32")
+        return y
+
     def gemm_int8_host(self, a, b_kn) -> np.ndarray:
         """The reference call with host arrays: a uint8 [m, k], b int8 [k, n] -> int32 [m, n]."""
         a, b = _np(a, np.uint8), _np(b_kn, np.int8)
@@ -259,6 +282,54 @@ class GpuKernels:
                                       y.stride(0), _stream(stream))
         self._check(rc, "gllmk_gemm_grouped")
         return y
+
+    # ---- mixture-of-experts routing conventions (scalar-ops/src/moe.rs:59-157) ----
+    def moe_topk(self, gate_probs, top_k: int, stream=None):
+        """scalar_topk: gate_probs [seq, experts] f32 CUDA -> [2, seq * top_k] f32: row 0 the expert indices as u32
+        bit patterns, row 1 the renormalised weights (the reference's output buffer, viewed as two rows)."""
+        import torch
+        seq, ne = gate_probs.shape
+        out = torch.empty((2, seq * top_k), dtype=torch.float32, device=gate_probs.device)
+        self._check(lib().gllmk_moe_topk(self._ctx, _ptr(gate_probs.contiguous()), _ptr(out), seq, ne, top_k, _stream(stream)),
+                    "gllmk_moe_topk")
+        return out
+
+    def moe_route(self, routing, seq_len: int, num_experts: int, top_k: int, stream=None):
+        """Groups the slots of a scalar_topk result per expert: (row_offsets list, perm int32 [seq * top_k],
+        inv int32 [seq * top_k])."""
+        import torch
+        slots = seq_len * top_k
+        perm = torch.empty(slots, dtype=torch.int32, device=routing.device)
+        inv = torch.empty(slots, dtype=torch.int32, device=routing.device)
+        offs = (C.c_int64 * (num_experts + 1))()
+        self._check(lib().gllmk_moe_route(self._ctx, _ptr(routing), seq_len, num_experts, top_k, offs, _ptr(perm), _ptr(inv),
+                                          _stream(stream)), "gllmk_moe_route")
+        return list(offs), perm, inv
+
+    def moe_gather(self, x, perm, top_k: int, rows: int = None, stream=None):
+        """x [seq, k] (f32 or bf16) -> [rows, k] in grouped order."""
+        import torch
+        rows = perm.numel() if rows is None else rows
+        out = torch.empty((rows, x.shape[1]), dtype=x.dtype, device=x.device)
+        dt = {torch.float32: 0, torch.bfloat16: 1}
+        self._check(lib().gllmk_moe_gather(self._ctx, _ptr(x), dt[x.dtype], x.stride(0), _ptr(perm), rows, top_k, x.shape[1],
+                                           _ptr(out), out.stride(0), _stream(stream)), "gllmk_moe_gather")
+        return out
+
+    def moe_weighted_sum(self, expert_outputs, routing, inv, seq_len: int, top_k: int, num_experts: int = 1 << 30, stream=None):
+        """scalar_weighted_sum.  inv=None: expert_outputs is the reference's [experts, seq, hidden] buffer; else the
+        grouped rows [seq * top_k, hidden] and `inv` from moe_route."""
+        import torch
+        hidden = expert_outputs.shape[-1]
+        if inv is None:
+            num_experts = expert_outputs.shape[0]
+        out = torch.empty((seq_len, hidden), dtype=torch.float32, device=expert_outputs.device)
+        slots = seq_len * top_k
+        flat = routing.reshape(-1)
+        self._check(lib().gllmk_moe_weighted_sum(self._ctx, _ptr(expert_outputs), expert_outputs.stride(-2), _ptr(flat),
+                                                 flat.data_ptr() + 4 * slots, _ptr(inv), _ptr(out), seq_len, hidden, top_k,
+                                                 min(num_experts, (1 << 31) - 1), _stream(stream)), "gllmk_moe_weighted_sum")
+        return out
 
     def gemm_fp4(self, w: Weight, x: Weight, y=None, out_dtype=None, stream=None):
         """Native FP4 x FP4 product: `x` is the activation matrix [m, k] quantized and uploaded like a weight."""
@@ -295,6 +366,19 @@ class GpuKernels:
         rc = lib().gllmk_gemv_allgather(self._ctx, w._h, _ptr(x), x.stride(0), x.stride(1), m, y_local, y_stride_t, 1,
                                         arr, len(y_peers), _stream(stream))
         self._check(rc, "gllmk_gemv_allgather")
+
+    def gemv_exchange(self, w: Weight, x, y_local: int, y_peers, y_stride_t: int, m: int, flags_local: int, flags_peers,
+                      rank: int, stream=None) -> None:
+        """gemv_allgather with the hand-shake built in: waits for every rank's previous exchange product before x
+        is read, signals this one's completion from the GEMV's last block."""
+        ya = (C.c_void_p * max(len(y_peers), 1))(*y_peers)
+        fa = (C.c_void_p * max(len(flags_peers), 1))(*flags_peers)
+        rc = lib().gllmk_gemv_exchange(self._ctx, w._h, _ptr(x), x.stride(0), x.stride(1), m, y_local, y_stride_t, 1, ya,
+                                       flags_local, fa, len(y_peers), rank, _stream(stream))
+        self._check(rc, "gllmk_gemv_exchange")
+
+    def exchange_wait(self, flags_local: int, n_peers: int, rank: int, stream=None) -> None:
+        self._check(lib().gllmk_exchange_wait(self._ctx, flags_local, n_peers, rank, _stream(stream)), "gllmk_exchange_wait")
 
     def peer_barrier(self, flags_local: int, flags_peers, rank: int, seq: int, stream=None) -> None:
         arr = (C.c_void_p * max(len(flags_peers), 1))(*flags_peers)
@@ -415,8 +499,24 @@ class GpuKernels:
         self._check(lib().gllmk_gemm_q4_f32(self._ctx, _ptr(w), _ptr(x), _ptr(y), _ptr(s), 0 if s is None else s.size,
                                             m, n, k), "gemm_q4")
 
+    def gemm_q8(self, weight, input, output, scales, m: int, n: int, k: int) -> None:
+        """Kernels::gemm_q8 (src/traits.rs:502-510): Q8_K rows; `weight` is the reference's i8 (or u8) view of the blocks."""
+        w = np.ascontiguousarray(weight).view(np.uint8)
+        x, y = _np(input, np.float32), _np(output, np.float32, True)
+        s = _np(scales, np.float32) if scales is not None and len(scales) else None
+        self._check(lib().gllmk_gemm_q8_f32(self._ctx, _ptr(w), _ptr(x), _ptr(y), _ptr(s), 0 if s is None else s.size,
+                                            m, n, k), "gemm_q8")
+
     def gemv_q4(self, weight, input, scale: float, n: int) -> float:
         """Kernels::gemv_q4 (src/traits.rs:501): one Q4_K row of n elements, result * scale."""
         out = np.empty(1, np.float32)
-        self.gemm_q4(weight, input, out, [scale], 1, 1, n)
+        w, x = _np(weight, np.uint8), _np(input, np.float32)
+        self._check(lib().gllmk_gemv_q4_f32(self._ctx, _ptr(w), _ptr(x), float(scale), n, _ptr(out)), "gemv_q4")
+        return float(out[0])
+
+    def gemv_q8(self, weight, input, scale: float, n: int) -> float:
+        """Kernels::gemv_q8 (src/traits.rs:500): one Q8_K row of n elements, result * scale."""
+        out = np.empty(1, np.float32)
+        w, x = np.ascontiguousarray(weight).view(np.uint8), _np(input, np.float32)
+        self._check(lib().gllmk_gemv_q8_f32(self._ctx, _ptr(w), _ptr(x), float(scale), n, _ptr(out)), "gemv_q8")
         return float(out[0])

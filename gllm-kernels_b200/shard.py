@@ -186,6 +186,19 @@ class PeerExchange:
         others = [d for r, d in enumerate(dst) if r != self.rank]
         self.K.gemv_allgather(w, x, mine, others, n_total, m, stream)
 
+    def gemv_chained(self, w, x, slot: int, r0: int, n_total: int, stream=None) -> None:
+        """The same product as `gemv` for chains of sharded products: it first waits until every rank has completed
+        the previous chained product (so an x that is a gathered y is complete) and signals its own completion from
+        the GEMV's last block — no barrier launch in between.  Finish a chain with `wait`."""
+        m = x.shape[0]
+        dst = [self.slot_ptr(r, slot, r0) for r in range(self.world)]
+        others = [d for r, d in enumerate(dst) if r != self.rank]
+        self.K.gemv_exchange(w, x, dst[self.rank], others, n_total, m, self.bases[self.rank], self.peers, self.rank, stream)
+
+    def wait(self, stream=None) -> None:
+        """After the last `gemv_chained` of a chain: returns (on the stream) when its bands have landed here."""
+        self.K.exchange_wait(self.bases[self.rank], self.world - 1, self.rank, stream)
+
     def barrier(self, stream=None) -> None:
         """After this rank's products: returns (on the stream) when every rank's bands have landed here."""
         # sequence number 0 = the counter in the flag area: the launch can be captured in a graph and replayed

@@ -80,6 +80,58 @@ GLLMK_API int32_t gllmk_hw_info(char *buf, size_t len);
 GLLMK_API int32_t gllmk_quant_block_size(int32_t quant_type, int32_t mx_block);
 GLLMK_API int32_t gllmk_quant_block_bytes(int32_t quant_type, int32_t mx_block);
 
+/* ---- format descriptors ------------------------------------------------------------------------------- */
+
+/* QuantFormatDescriptor (src/quant_format.rs:129-157), flattened for C: where a block of a format keeps its
+ * scale(s), its zero point / min and its quantized data.  The enums mirror ScaleLayout (:159-199), ZeroLayout
+ * (:202-225), DataLayout (:228-252), ScaleDType (:255-266), QuantDataKind (:94-121), StorageLayout (:19-30) and
+ * NativeIsa (:53-91; only the variants these formats use).  Offsets are bytes from the start of the block, -1 =
+ * the format has no such field.  The library's own kernels read their offsets from the same table. */
+enum { GLLMK_SCALE_NONE = 0, GLLMK_SCALE_BLOCK_SCALAR, GLLMK_SCALE_BLOCK_SCALAR_WITH_MIN, GLLMK_SCALE_HIERARCHICAL,
+       GLLMK_SCALE_Q6K_SCALES, GLLMK_SCALE_EXTERNAL_ARRAY, GLLMK_SCALE_SUB_BLOCK_SCALARS };
+enum { GLLMK_ZERO_NONE = 0, GLLMK_ZERO_BLOCK_SCALAR, GLLMK_ZERO_HIERARCHICAL, GLLMK_ZERO_STATIC_BIAS, GLLMK_ZERO_BLOCK_MIN };
+enum { GLLMK_DATA_PACKED_NIBBLES = 0, GLLMK_DATA_NIBBLE_WITH_HIGH_BITS, GLLMK_DATA_BYTES };
+enum { GLLMK_SDT_F16 = 0, GLLMK_SDT_F32, GLLMK_SDT_BF16, GLLMK_SDT_U8RANGE, GLLMK_SDT_I8RANGE, GLLMK_SDT_F8E4M3, GLLMK_SDT_F8E5M2,
+       GLLMK_SDT_E8M0 };
+enum { GLLMK_KIND_INT8 = 0, GLLMK_KIND_PACKED_INT4, GLLMK_KIND_SIGNED_PACKED_INT4, GLLMK_KIND_PACKED_INT5, GLLMK_KIND_PACKED_INT6,
+       GLLMK_KIND_FLOAT4, GLLMK_KIND_NVFP4 };
+enum { GLLMK_STORAGE_ROW_MAJOR = 0, GLLMK_STORAGE_COL_INTERLEAVED, GLLMK_STORAGE_PACKED };
+enum { GLLMK_ISA_NONE = 0, GLLMK_ISA_VPDPBUSD, GLLMK_ISA_TCGEN05_FP4 };
+typedef struct gllmk_quant_format_descriptor {
+    int32_t quant_type;          /* GLLMK_QUANT_*                                                              */
+    int32_t block_size;          /* elements per block                                                          */
+    int32_t block_bytes;         /* bytes per block                                                             */
+    int32_t bits_per_element;
+    int32_t scale_kind;          /* GLLMK_SCALE_*                                                               */
+    int32_t scale_dtype;         /* GLLMK_SDT_* of the block / sub-block scale                                  */
+    int32_t scale_offset;        /* BlockScalar.offset_bytes, Hierarchical.block_d_offset, Q6KScales.block_d_offset,
+                                    SubBlockScalars.offset_bytes                                               */
+    int32_t scale_min_offset;    /* Hierarchical.block_dmin_offset                                             */
+    int32_t sub_scales_offset;   /* Hierarchical / Q6KScales sub_scales_offset; SubBlockScalars.offset_bytes   */
+    int32_t sub_scales_bits;     /* 6 = KQuant6Bit packing (12 bytes -> 8 (scale, min) pairs); 8 = one byte each */
+    int32_t sub_scales_count;
+    int32_t sub_block_elements;
+    int32_t zero_kind;           /* GLLMK_ZERO_*                                                               */
+    int32_t zero_offset;         /* Hierarchical.dmin_offset                                                   */
+    int32_t zero_sub_offset;     /* Hierarchical.sub_m_offset                                                  */
+    int32_t static_bias;         /* StaticBias.value (subtracted from the code)                                */
+    int32_t data_layout;         /* GLLMK_DATA_*                                                               */
+    int32_t data_offset;         /* PackedNibbles.offset, NibbleWithHighBits.low_offset, Bytes.offset          */
+    int32_t data_high_offset;    /* NibbleWithHighBits.high_offset                                             */
+    int32_t data_high_bits;      /* NibbleWithHighBits.high_bits_per_elem                                      */
+    int32_t data_low_first;      /* PackedNibbles.low_first                                                    */
+    int32_t data_signed;         /* Bytes.signed                                                               */
+    int32_t data_kind;           /* GLLMK_KIND_*                                                               */
+    int32_t storage_layout;      /* GLLMK_STORAGE_*                                                            */
+    int32_t native_isa;          /* GLLMK_ISA_* (Nvfp4: Tcgen05Fp4, src/quant_format.rs:1026)                  */
+} gllmk_quant_format_descriptor;
+/* QuantFormatDescriptor::for_type (src/quant_format.rs:36-44).  UNSUPPORTED for a type this library does not serve
+ * (the reference panics for an unregistered type).  `mx_block` as in gllmk_quant_block_size.  Needs no device. */
+GLLMK_API int32_t gllmk_quant_format_descriptor_for_type(int32_t quant_type, int32_t mx_block, gllmk_quant_format_descriptor *out);
+/* registry() (src/quant_format.rs:1189-1193), restricted to the served formats: writes up to `cap` GLLMK_QUANT_* ids
+ * and returns how many formats are registered. */
+GLLMK_API int32_t gllmk_quant_format_registry(int32_t *quant_types, int32_t cap);
+
 /* ---- context ---------------------------------------------------------------------------- */
 
 /* gllm_backend_create / gllm_backend_free (src/ffi/mod.rs:25-57).  Binds to CUDA device
@@ -91,15 +143,21 @@ GLLMK_API void gllmk_ctx_free(gllmk_ctx ctx);
 GLLMK_API const char *gllmk_last_error(gllmk_ctx ctx);
 /* Waits for the device and reads the context's device-side status word: every wait inside a kernel
  * (on a bulk-copy barrier, a tensor-core completion, another GPU's flag) is bounded, and a kernel that
- * gives one up records a non-zero code there and returns instead of hanging.  Returns RUNTIME_ERROR (and
- * clears the word) if it was set.  Codes name the kernel and the wait: 1-2 decode GEMV (consumer, producer),
- * 10-14 fused-dequant prefill GEMM, 21-23 FP4 x FP4 GEMM, 31 gllmk_peer_barrier, 41-43 W8A8 GEMM, 51-53 FP4
+ * gives one up records a non-zero code there and returns instead of hanging.  Returns RUNTIME_ERROR if it
+ * was set, and puts the context back into a usable state: the word and the decode kernels' split-k arrival
+ * counters (which a kernel that gave up leaves non-zero) are cleared, so the next call on the context is
+ * correct again.  Results of the call that gave up are incomplete.  Codes name the kernel and the wait: 1-2 decode GEMV (consumer, producer),
+ * 10-14 fused-dequant prefill GEMM, 21-23 FP4 x FP4 GEMM, 31 gllmk_peer_barrier, 32 gllmk_gemv_exchange /
+ * gllmk_exchange_wait (another rank's products), 41-43 W8A8 GEMM, 51-53 FP4
  * decode GEMV on the tensor core. */
 GLLMK_API int32_t gllmk_ctx_status(gllmk_ctx ctx, int32_t *device_status);
 /* Tuning knobs, for experiments.  key: "gemv_ctas_per_sm" (resident CTAs per SM the decode grid is
  * sized for; 0 = occupancy limit), "gemv_pdl" (1 = overlap the activation staging kernel with the
  * weight stream), "gemv_fp4_int" (1 = decode MXFP4 / NVFP4 weights on the integer-decode kernel instead of
- * the block-scaled tensor-core one). */
+ * the block-scaled tensor-core one), "peer_wait_spins" (how many times a wait on another GPU's flag probes it
+ * before it gives up with status 31; default 2^22, about a second), "inject_give_up" (testing aid, host side
+ * only: leaves the context as a kernel that gave up a wait with that status code would — word set, arrival
+ * counters dirty — without making any kernel wait). */
 GLLMK_API int32_t gllmk_ctx_set(gllmk_ctx ctx, const char *key, int64_t value);
 
 /* ---- weights: upload + repack, the inverse, and the bit-exact decode ----------------------- */
@@ -148,8 +206,8 @@ GLLMK_API int32_t gllmk_embedding_gather(gllmk_ctx ctx, gllmk_weight w, const in
  * Element (t, k) of x is x_dev[t*x_stride_t + k*x_stride_k]; element (t, r) of y is
  * y_dev[t*y_stride_t + r*y_stride_r] — so the reference's [k, n]-input / [m, n]-output convention
  * is strides (1, n_ref) / (1, n_ref) and gemm_q4's [m, k] / [m, n] is (k, 1) / (n, 1).
- * `row_scales` (NULL, 1 or n entries on the device) multiplies row r's result like gemm_q4's
- * `scales`.  f32 accumulation; result within 2e-3 of the reference's sequential f32 sum.  All four
+ * `row_scales` (NULL, or 1 or n entries on the device; any other count is INVALID_ARG) multiplies row r's
+ * result like gemm_q4's `scales`.  f32 accumulation; result within 2e-3 of the reference's sequential f32 sum.  All four
  * weight types (for MXFP4 / NVFP4 the reference has no matmul; the oracle is its dequant followed by the
  * same f32 sum). */
 #define GLLMK_GEMV_MAX_M 16
@@ -188,6 +246,19 @@ GLLMK_API int32_t gllmk_gemm_int8(gllmk_ctx ctx, gllmk_weight w, const uint8_t *
 GLLMK_API int32_t gllmk_dequantize_i32_f32(gllmk_ctx ctx, const int32_t *c_dev, float *out_dev, int64_t m, int64_t n, float scale_a,
                                  float scale_b, const float *bias_dev, int32_t activation, void *stream);
 GLLMK_API int32_t gllmk_gemm_int8_host(gllmk_ctx ctx, const uint8_t *a, const int8_t *b_kn, int32_t *c, size_t m, size_t n, size_t k);
+/* The activation half of W8A8: quantize_from_fp32 with QuantFormat::Int8PerTensor (src/compiler/quant_convert.rs:17-20,
+ * 165-177) on device memory: scale = max|x| / 127 over the whole [rows, k] tensor (leading dimension ldx),
+ * q = (x / scale).round().clamp(-128, 127), round half away from zero, bit-exact with the reference's loop.
+ * q_dev receives one byte per element (leading dimension ldq): the reference's signed values, or, with
+ * as_unsigned != 0, q + 128 — the unsigned operand gllmk_gemm_int8 takes.  scale_dev: TWO 32-bit words of device
+ * memory; word 0 receives the f32 scale (word 1 is the routine's running maximum). */
+GLLMK_API int32_t gllmk_quantize_act_int8(gllmk_ctx ctx, const float *x_dev, int64_t rows, int64_t k, int64_t ldx, void *q_dev, int64_t ldq,
+                                int32_t as_unsigned, float *scale_dev, void *stream);
+/* A whole W8A8 linear layer on device memory: y = act((q_x . W) * scale_x * scale_b + bias), x f32 [m, k] quantized per
+ * tensor as above, products on the tensor core (u8 = q_x + 128 against s8 weights), the 128 * sum_k W[k, j] the offset
+ * adds taken off the exact s32 result with column sums computed at upload, then dequantize_i32_to_f32's epilogue. */
+GLLMK_API int32_t gllmk_w8a8_linear_f32(gllmk_ctx ctx, gllmk_weight w, const float *x_dev, int64_t ldx, int32_t m, float *y_dev, int64_t ldy,
+                              float scale_b, const float *bias_dev, int32_t activation, void *stream);
 
 /* ---- multi-GPU: row-sharded decode with the all-gather fused into the GEMV -------------------------- */
 
@@ -209,6 +280,16 @@ GLLMK_API int32_t gllmk_gemm_int8_host(gllmk_ctx ctx, const uint8_t *a, const in
  *   order, `rank` this rank's number.  `seq` must grow by one per barrier, starting at 1; seq = 0 means
  *   "use and advance the counter kept in this rank's flag area", which is what a captured CUDA graph
  *   needs (every rank must then use 0 for every barrier).  After the barrier, y is complete on this rank.  A buffer may be rewritten by peers one barrier after its last reader finished. */
+/* gllmk_gemv_exchange: the same product with the hand-shake built in, for chains of sharded products (a decode
+ *   step): before it reads x it waits (bounded: "peer_wait_spins" probes per rank, then status 32) until every
+ *   rank has completed as many exchange products as this rank — so an x that is the previous product's gathered y
+ *   is complete — and the block that finishes the launch's last row tile signals the new count to every rank.  No
+ *   barrier kernel between products: one staging + one GEMV launch per product, whose weight prefetch overlaps
+ *   the wait.  Every rank must issue the same sequence of exchange products; flags_local / flags_peers are the
+ *   flag words at the start of each rank's gllmk_shared_alloc buffer (this call uses words 32..48, the barrier
+ *   words 0..16).  A buffer may be rewritten by peers one product after its last reader finished.
+ * gllmk_exchange_wait: after the last product of a chain, on `stream`: returns once every rank's bands of that
+ *   product have landed here (what the next product's staging would otherwise wait for). */
 #define GLLMK_MAX_PEERS 7
 #define GLLMK_IPC_HANDLE_BYTES 64
 #define GLLMK_PEER_FLAG_BYTES 256
@@ -221,6 +302,10 @@ GLLMK_API int32_t gllmk_gemv_allgather(gllmk_ctx ctx, gllmk_weight w, const floa
                              int32_t n_peers, void *stream);
 GLLMK_API int32_t gllmk_peer_barrier(gllmk_ctx ctx, void *flags_local, void *const *flags_peers, int32_t n_peers, int32_t rank,
                            uint32_t seq, void *stream);
+GLLMK_API int32_t gllmk_gemv_exchange(gllmk_ctx ctx, gllmk_weight w, const float *x_dev, int64_t x_stride_t, int64_t x_stride_k,
+                                      int32_t m, float *y_local, int64_t y_stride_t, int64_t y_stride_r, void *const *y_peers,
+                                      void *flags_local, void *const *flags_peers, int32_t n_peers, int32_t rank, void *stream);
+GLLMK_API int32_t gllmk_exchange_wait(gllmk_ctx ctx, void *flags_local, int32_t n_peers, int32_t rank, void *stream);
 
 /* ---- prefill: fused dequantize + GEMM on tcgen05 tensor cores (any M) --------------------------- */
 
@@ -244,6 +329,36 @@ GLLMK_API int32_t gllmk_gemm(gllmk_ctx ctx, gllmk_weight w, const void *a_dev, i
 GLLMK_API int32_t gllmk_gemm_grouped(gllmk_ctx ctx, int32_t n_groups, const gllmk_weight *weights, const void *a_dev, int32_t a_dtype,
                            int64_t lda, const int64_t *row_offsets, void *y_dev, int32_t y_dtype, int64_t ldy, void *stream);
 
+/* ---- mixture-of-experts routing conventions around gllmk_gemm_grouped -------------------------------- */
+
+/* scalar_topk (scalar-ops/src/moe.rs:59-115) on device memory: for every row of gate_probs [seq_len,
+ * num_experts] the top_k largest values (strict '>' insertion: the earlier expert wins a tie) and their
+ * indices.  out holds 2 * seq_len * top_k floats: first the indices [seq_len * top_k] as u32 BIT PATTERNS in
+ * f32 slots, then the weights [seq_len * top_k] renormalised to sum 1 (value * (1 / sum), 0 if sum <= 0).
+ * Bit-exact with the reference's routine.  top_k <= 16. */
+GLLMK_API int32_t gllmk_moe_topk(gllmk_ctx ctx, const float *gate_probs_dev, float *out_dev, int64_t seq_len, int32_t num_experts,
+                                 int32_t top_k, void *stream);
+/* Groups the (token, k) slots of a scalar_topk index section per expert — "rows grouped per expert", the order
+ * gllmk_gemm_grouped takes its activation rows in.  Within an expert the slots keep their order.
+ *   row_offsets_host [num_experts + 1]: rows of expert e are [row_offsets[e], row_offsets[e + 1])  (HOST, out)
+ *   perm_dev [seq_len * top_k]: grouped row -> slot s * top_k + ki                                   (device, out)
+ *   inv_dev  [seq_len * top_k]: slot -> grouped row, -1 for an index >= num_experts, which no expert serves
+ *                               (scalar_moe_dispatch_packed skips it, scalar-ops/src/moe_dispatch_packed.rs:113-116)
+ * Synchronises `stream` (the offsets come back to the host).  num_experts <= 1024. */
+GLLMK_API int32_t gllmk_moe_route(gllmk_ctx ctx, const float *indices_dev, int64_t seq_len, int32_t num_experts, int32_t top_k,
+                                  int64_t *row_offsets_host, int32_t *perm_dev, int32_t *inv_dev, void *stream);
+/* out[g, :] = x[perm[g] / top_k, :] for g < rows: the activation rows in grouped order (f32 or bf16). */
+GLLMK_API int32_t gllmk_moe_gather(gllmk_ctx ctx, const void *x_dev, int32_t dtype, int64_t ldx, const int32_t *perm_dev, int64_t rows,
+                                   int32_t top_k, int64_t k, void *out_dev, int64_t ldo, void *stream);
+/* scalar_weighted_sum (scalar-ops/src/moe.rs:127-157): out[s, d] = sum_ki weights[s, ki] * row(s, ki)[d], terms
+ * added in ki order onto 0 with a separate multiply and add each (bit-exact with the reference's loop).
+ *   inv_dev == NULL: expert_outputs is the reference's buffer [expert][seq_len][hidden] (ld = hidden);
+ *   inv_dev != NULL: expert_outputs holds the grouped rows gllmk_gemm_grouped wrote (leading dimension ld) and
+ *                    row(s, ki) = expert_outputs[inv[s * top_k + ki]]; slots with inv < 0 add nothing. */
+GLLMK_API int32_t gllmk_moe_weighted_sum(gllmk_ctx ctx, const float *expert_outputs_dev, int64_t ld, const float *indices_dev,
+                                         const float *weights_dev, const int32_t *inv_dev, float *out_dev, int64_t seq_len,
+                                         int64_t hidden, int32_t top_k, int32_t num_experts, void *stream);
+
 /* Both operands in FP4 (config "NVFP4 prefill GEMM": weights and activations quantized the same way;
  * the reference declares the format, src/quant.rs:357-371, and a native-FP4 capability,
  * DotProductCap::NativeFp4 / Tcgen05Fp4 in src/quant_format.rs:1007-1027, but ships no kernel).
@@ -259,9 +374,10 @@ GLLMK_API int32_t gllmk_gemm_fp4(gllmk_ctx ctx, gllmk_weight w, gllmk_weight x, 
  * under a pool allocator that owns the device, or a latency-critical section where cudaMalloc's implicit
  * device synchronisation is unacceptable.  This entry point has no counterpart in the reference (its CPU
  * path keeps scratch in a thread_local Vec).  It calls no cudaMalloc / cudaFree and no allocating library
- * routine: the activation image, the split-k partial sums, the arrival counters and the status word all
- * live in one 8 MiB array compiled into the library, which every GPU that loads the library holds until the
- * process exits.
+ * routine: the activation image, the split-k partial sums and the arrival counters all live in one 8 MiB
+ * array compiled into the library, which every GPU that loads the library holds until the process exits.
+ * A bounded wait that gives up is reported through the context's own status word (allocated with the
+ * context), i.e. by gllmk_ctx_status exactly as for gllmk_gemv.
  *   - Shapes whose scratch does not fit (more than 8192 row tiles = 131072 rows, or image + partial sums
  *     over 8 MiB; the message gives the byte count) are rejected with INVALID_ARG: use gllmk_gemv there.
  *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress); make that
@@ -293,6 +409,15 @@ GLLMK_API int32_t gllmk_classic_matmul_f32(gllmk_ctx ctx, const uint8_t *weight_
  * (the reference asserts). */
 GLLMK_API int32_t gllmk_gemm_q4_f32(gllmk_ctx ctx, const uint8_t *weight, const float *input, float *output,
                           const float *scales, size_t n_scales, size_t m, size_t n, size_t k);
+/* Kernels::gemm_q8 with E = f32 (src/traits.rs:502-510; src/cpu_kernels/mod.rs:2983-3031): the same call over
+ * Q8_K rows (`weight` is the reference's &[i8] view of 292-byte BlockQ8K blocks, k / 256 per row). */
+GLLMK_API int32_t gllmk_gemm_q8_f32(gllmk_ctx ctx, const int8_t *weight, const float *input, float *output,
+                          const float *scales, size_t n_scales, size_t m, size_t n, size_t k);
+/* Kernels::gemv_q4 / gemv_q8 (src/traits.rs:500-501; src/cpu_kernels/mod.rs:2888-2932): ONE weight row of n
+ * elements (n / 256 Q4_K or Q8_K blocks) dotted with input [n], times `scale`, into *out.  INVALID_ARG if
+ * n % 256 != 0 (the reference asserts). */
+GLLMK_API int32_t gllmk_gemv_q4_f32(gllmk_ctx ctx, const uint8_t *weight, const float *input, float scale, size_t n, float *out);
+GLLMK_API int32_t gllmk_gemv_q8_f32(gllmk_ctx ctx, const int8_t *weight, const float *input, float scale, size_t n, float *out);
 /* The same two conventions against a resident weight; x / y are HOST memory.
  * `ref_layout` != 0: kquant_matmul's input [k, m] / output [n, m]; 0: gemm_q4's [m, k] / [m, n]. */
 GLLMK_API int32_t gllmk_matmul_host(gllmk_ctx ctx, gllmk_weight w, const float *x_host, int32_t m, float *y_host,

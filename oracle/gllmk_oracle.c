@@ -590,6 +590,48 @@ API float gko_gemv_q4(const uint8_t *w, const float *input, float scale, size_t 
     return sum * scale;
 }
 
+/* Kernels::gemm_q8 / gemv_q8, src/cpu_kernels/mod.rs:2983-3031, 2910-2932: the same two loops over Q8_K blocks. */
+API int gko_gemm_q8(const uint8_t *w, const float *input, float *out, const float *scales, size_t n_scales,
+                    size_t m, size_t n, size_t k) {
+    if (k % 256) return -1;
+    const size_t bpr = k / 256;
+    for (size_t i = 0; i < m; i++) {
+        const float *in_row = input + i * k;
+        for (size_t j = 0; j < n; j++) {
+            float sum = 0.0f;
+            for (size_t b = 0; b < bpr; b++) sum += dot_q8_k(w + (j * bpr + b) * 292, in_row + b * 256);
+            const float s = (n_scales == n) ? scales[j] : (n_scales == 1 ? scales[0] : 1.0f);
+            out[i * n + j] = sum * s;
+        }
+    }
+    return 0;
+}
+API float gko_gemv_q8(const uint8_t *w, const float *input, float scale, size_t n) {
+    float sum = 0.0f;
+    for (size_t b = 0; b < n / 256; b++) sum += dot_q8_k(w + b * 292, input + b * 256);
+    return sum * scale;
+}
+
+/* quantize_from_fp32, QuantFormat::Int8PerTensor (src/compiler/quant_convert.rs:17-20,165-177): scale = max|x| / 127,
+ * q = (x / scale).round().clamp(-128, 127) as i8 — Rust's round() is half away from zero and `as i8` turns NaN
+ * (an all-zero input: 0 / 0) into 0.  Returns the scale. */
+API float gko_quantize_int8_per_tensor(const float *x, int8_t *q, size_t count) {
+    float max_abs = 0.0f;
+    for (size_t i = 0; i < count; i++) {
+        const float a = fabsf(x[i]);
+        if (a > max_abs) max_abs = a;  /* f32::max ignores NaN operands */
+    }
+    const float scale = max_abs / 127.0f;
+    for (size_t i = 0; i < count; i++) {
+        float v = roundf(x[i] / scale);
+        if (v != v) v = 0.0f;
+        if (v < -128.0f) v = -128.0f;
+        if (v > 127.0f) v = 127.0f;
+        q[i] = (int8_t)v;
+    }
+    return scale;
+}
+
 /* scalar_gemm loop order, scalar-ops/src/blas.rs:116-135: for i, for j, acc = sum_p a[i,p]*b[p,j].
  * Here b is the dequantised weight held row-major as [n, k] (b[p,j] = wd[j*k+p]) so the
  * accumulation over p is the same sequence of products. */
@@ -611,6 +653,62 @@ API void gko_gemm_f64_nt(const float *a, const float *wd, double *c, size_t m, s
             const float *ar = a + i * k, *wr = wd + j * k;
             for (size_t p = 0; p < k; p++) acc += (double)ar[p] * (double)wr[p];
             c[i * n + j] = acc;
+        }
+}
+
+/* ---- mixture-of-experts conventions --------------------------------------------------------- */
+
+/* scalar_topk, scalar-ops/src/moe.rs:59-115.  output: indices [seq*top_k] (u32 bit patterns in f32 slots), then
+ * weights [seq*top_k].  Insertion with a strict '>' into a list that starts at -inf / index 0; weights are
+ * value * (1 / sum), inv_sum = 0 when sum <= 0. */
+API void gko_scalar_topk(const float *gate_probs, float *output, size_t seq_len, size_t num_experts, size_t top_k) {
+    float *idx_base = output, *wt_base = output + seq_len * top_k;
+    for (size_t s = 0; s < seq_len; s++) {
+        const float *row = gate_probs + s * num_experts;
+        uint32_t ti[64];
+        float tv[64];
+        for (size_t i = 0; i < top_k; i++) { ti[i] = 0; tv[i] = -INFINITY; }
+        for (size_t e = 0; e < num_experts; e++) {
+            const float val = row[e];
+            size_t pos = top_k;
+            for (size_t ki = 0; ki < top_k; ki++)
+                if (val > tv[ki]) { pos = ki; break; }
+            if (pos < top_k) {
+                for (size_t ki = top_k - 1; ki > pos; ki--) { ti[ki] = ti[ki - 1]; tv[ki] = tv[ki - 1]; }
+                ti[pos] = (uint32_t)e;
+                tv[pos] = val;
+            }
+        }
+        float sum = 0.0f;
+        for (size_t ki = 0; ki < top_k; ki++) sum += tv[ki];
+        const float inv_sum = sum > 0.0f ? 1.0f / sum : 0.0f;
+        for (size_t ki = 0; ki < top_k; ki++) {
+            memcpy(idx_base + s * top_k + ki, &ti[ki], 4);
+            wt_base[s * top_k + ki] = tv[ki] * inv_sum;
+        }
+    }
+}
+
+/* scalar_weighted_sum, scalar-ops/src/moe.rs:127-157: output zeroed, then for s, for ki: output[s, :] += w * row,
+ * row = expert_outputs[expert][s].  rows == NULL: the reference's [expert][seq][hidden] buffer.  rows != NULL: the
+ * same sum over a buffer of grouped rows, rows[s*top_k+ki] naming the row (negative = skipped) — the layout
+ * gllmk_gemm_grouped writes. */
+API void gko_scalar_weighted_sum(const float *expert_outputs, const float *indices, const float *weights, const int64_t *rows,
+                                 float *output, size_t seq_len, size_t hidden, size_t top_k) {
+    for (size_t i = 0; i < seq_len * hidden; i++) output[i] = 0.0f;
+    for (size_t s = 0; s < seq_len; s++)
+        for (size_t ki = 0; ki < top_k; ki++) {
+            const float w = weights[s * top_k + ki];
+            const float *row;
+            if (rows) {
+                if (rows[s * top_k + ki] < 0) continue;
+                row = expert_outputs + (size_t)rows[s * top_k + ki] * hidden;
+            } else {
+                uint32_t e;
+                memcpy(&e, indices + s * top_k + ki, 4);
+                row = expert_outputs + ((size_t)e * seq_len + s) * hidden;
+            }
+            for (size_t d = 0; d < hidden; d++) output[s * hidden + d] += w * row[d];
         }
 }
 
@@ -660,6 +758,10 @@ API float gko_scalar_gemv_q4(const uint8_t *w, const float *x, float scale, size
 /* The row loop benches/bench_quant.rs:84-96 times: one scalar_gemv_q4 call per output row. */
 API void gko_bench_gemv_q4_rows(const uint8_t *w, const float *x, const float *scales, float *out, size_t n, size_t k) {
     for (size_t j = 0; j < n; j++) out[j] = gko_scalar_gemv_q4(w + j * (k / 2), x, scales[j], k);
+}
+/* benches/bench_quant.rs:40-58: one scalar_gemv_q8 call per output row. */
+API void gko_bench_gemv_q8_rows(const int8_t *w, const float *x, const float *scales, float *out, size_t n, size_t k) {
+    for (size_t j = 0; j < n; j++) out[j] = gko_scalar_gemv_q8(w + j * k, x, scales[j], k);
 }
 API void gko_scalar_gemm_q8(const int8_t *w, const float *x, float *out, const float *scales, size_t m,
                             size_t n, size_t k) {

@@ -61,6 +61,9 @@ def _load(name: str) -> C.CDLL:
         "gko_quant_matmul_mt": (C.c_int, [_u8p, _f32p, _f32p, C.c_int, z, z, z, C.c_int]),
         "gko_gemm_q4": (C.c_int, [_u8p, _f32p, _f32p, _f32p, z, z, z, z]),
         "gko_gemv_q4": (C.c_float, [_u8p, _f32p, C.c_float, z]),
+        "gko_gemm_q8": (C.c_int, [_u8p, _f32p, _f32p, _f32p, z, z, z, z]),
+        "gko_gemv_q8": (C.c_float, [_u8p, _f32p, C.c_float, z]),
+        "gko_quantize_int8_per_tensor": (C.c_float, [_f32p, C.POINTER(C.c_int8), z]),
         "gko_gemm_f32_nt": (None, [_f32p, _f32p, _f32p, z, z, z]),
         "gko_gemm_f64_nt": (None, [_f32p, _f32p, _f64p, z, z, z]),
         "gko_dequant_matrix": (C.c_int, [C.c_int, _u8p, _u8p, C.c_float, z, z, C.c_int, _f32p]),
@@ -75,6 +78,10 @@ def _load(name: str) -> C.CDLL:
         "gko_nvfp4_global": (C.c_float, [_f32p, z]),
         "gko_quantize_nvfp4": (None, [_f32p, C.c_float, _u8p, z]),
         "gko_mxfp4_split": (None, [_u8p, _u8p, _u8p, z, z]),
+        "gko_bench_gemv_q4_rows": (None, [_u8p, _f32p, _f32p, _f32p, z, z]),
+        "gko_bench_gemv_q8_rows": (None, [C.POINTER(C.c_int8), _f32p, _f32p, _f32p, z, z]),
+        "gko_scalar_topk": (None, [_f32p, _f32p, z, z, z]),
+        "gko_scalar_weighted_sum": (None, [_f32p, _f32p, _f32p, C.POINTER(C.c_int64), _f32p, z, z, z]),
     }
     for k, (res, args) in sig.items():
         f = getattr(lib, k)
@@ -186,6 +193,36 @@ def gemm_q4(weight, inp, scales, m, n, k) -> np.ndarray:
     return out
 
 
+def gemm_q8(weight, inp, scales, m, n, k) -> np.ndarray:
+    """Kernels::gemm_q8: Q8_K rows, input [m,k], output [m,n]."""
+    w, x = _u8(np.ascontiguousarray(weight).view(np.uint8)), _f32(inp)
+    s = _f32(scales) if scales is not None and len(scales) else np.zeros(0, np.float32)
+    out = np.empty((m, n), np.float32)
+    sp = _p(s, _f32p) if s.size else C.cast(None, _f32p)
+    rc = lib().gko_gemm_q8(_p(w, _u8p), _p(x, _f32p), _p(out, _f32p), sp, s.size, m, n, k)
+    if rc:
+        raise ValueError(f"gko_gemm_q8 rc={rc}")
+    return out
+
+
+def gemv_q8(weight, inp, scale: float, n: int) -> float:
+    w, x = _u8(np.ascontiguousarray(weight).view(np.uint8)), _f32(inp)
+    return float(lib().gko_gemv_q8(_p(w, _u8p), _p(x, _f32p), scale, n))
+
+
+def gemv_q4(weight, inp, scale: float, n: int) -> float:
+    w, x = _u8(weight), _f32(inp)
+    return float(lib().gko_gemv_q4(_p(w, _u8p), _p(x, _f32p), scale, n))
+
+
+def quantize_int8_per_tensor(x):
+    """quantize_from_fp32 / Int8PerTensor (src/compiler/quant_convert.rs:165-177): (int8 array, scale)."""
+    x = _f32(x)
+    q = np.empty(x.shape, np.int8)
+    scale = lib().gko_quantize_int8_per_tensor(_p(x, _f32p), _p(q, C.POINTER(C.c_int8)), x.size)
+    return q, float(scale)
+
+
 def gemm_f32_nt(a, wd) -> np.ndarray:
     """C[m,n] = sum_p a[m,p]*wd[n,p], sequential f32 (scalar_gemm order)."""
     a, wd = _f32(a), _f32(wd)
@@ -202,6 +239,38 @@ def gemm_f64_nt(a, wd) -> np.ndarray:
     n = wd.shape[0]
     out = np.empty((m, n), np.float64)
     lib().gko_gemm_f64_nt(_p(a, _f32p), _p(wd, _f32p), _p(out, _f64p), m, n, k)
+    return out
+
+
+# ---- mixture-of-experts conventions (scalar-ops/src/moe.rs) ----------------------------------
+def scalar_topk(gate_probs, top_k: int) -> np.ndarray:
+    """scalar_topk: [seq, experts] -> [2, seq*top_k] f32 (row 0: index bit patterns, row 1: weights)."""
+    p = _f32(gate_probs)
+    seq, ne = p.shape
+    assert top_k <= 64
+    out = np.empty((2, seq * top_k), np.float32)
+    lib().gko_scalar_topk(_p(p, _f32p), _p(out, _f32p), seq, ne, top_k)
+    return out
+
+
+def scalar_weighted_sum(expert_outputs, routing, seq_len: int, top_k: int) -> np.ndarray:
+    """scalar_weighted_sum over the reference's [experts, seq, hidden] buffer."""
+    eo, r = _f32(expert_outputs), _f32(routing).reshape(2, -1)
+    hidden = eo.shape[-1]
+    out = np.empty((seq_len, hidden), np.float32)
+    lib().gko_scalar_weighted_sum(_p(eo, _f32p), _p(r[0].copy(), _f32p), _p(r[1].copy(), _f32p), None, _p(out, _f32p), seq_len,
+                                  hidden, top_k)
+    return out
+
+
+def scalar_weighted_sum_grouped(rows_buf, routing, inv, seq_len: int, top_k: int) -> np.ndarray:
+    """The same sum over grouped rows [seq*top_k, hidden]; inv[slot] = row (negative: skipped)."""
+    eo, r = _f32(rows_buf), _f32(routing).reshape(2, -1)
+    inv = np.ascontiguousarray(inv, np.int64)
+    hidden = eo.shape[-1]
+    out = np.empty((seq_len, hidden), np.float32)
+    lib().gko_scalar_weighted_sum(_p(eo, _f32p), _p(r[0].copy(), _f32p), _p(r[1].copy(), _f32p), _p(inv, C.POINTER(C.c_int64)),
+                                  _p(out, _f32p), seq_len, hidden, top_k)
     return out
 
 
@@ -249,12 +318,44 @@ def bench_gemv_q4_rows(w, x, scales, n: int, k: int, o1: bool = True) -> np.ndar
     """The loop benches/bench_quant.rs times for quant/gemv_q4 (simplified nibble-8 format, per-row scale),
     by default from the -O1 build that mirrors the reference's bench profile."""
     out = np.empty(n, np.float32)
-    L = lib(o1)
-    L.gko_bench_gemv_q4_rows.restype = None
-    L.gko_bench_gemv_q4_rows.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t]
     w, x, scales = _u8(w), _f32(x), _f32(scales)
-    L.gko_bench_gemv_q4_rows(w.ctypes.data, x.ctypes.data, scales.ctypes.data, out.ctypes.data, n, k)
+    lib(o1).gko_bench_gemv_q4_rows(_p(w, _u8p), _p(x, _f32p), _p(scales, _f32p), _p(out, _f32p), n, k)
     return out
+
+
+def bench_quant_kernel(kind: str, m: int, n: int, k: int, seed: int = 0, o1: bool = True):
+    """One call of a benches/bench_quant.rs kernel on random data of its shape (the restated scalar-ops loops,
+    built -O1 like the reference's bench profile).  Returns (seconds, rows of x actually run): GEMM kinds run
+    min(m, 8) rows of x — the loops are `for i in 0..m` outermost, so the time per row does not depend on m."""
+    import time
+    rng = np.random.default_rng(seed)
+    L = lib(o1)
+    mi = min(m, 8)
+    x = rng.standard_normal((mi, k), dtype=np.float32)
+    sc = rng.random(n, dtype=np.float32)
+    out = np.empty((mi, n), np.float32)
+    i8p = C.POINTER(C.c_int8)
+    if kind == "gemv_q8":
+        w = rng.integers(-128, 128, size=n * k, dtype=np.int8)
+        fn = lambda: L.gko_bench_gemv_q8_rows(_p(w, i8p), _p(x, _f32p), _p(sc, _f32p), _p(out, _f32p), n, k)
+    elif kind == "gemv_q4":
+        w = rng.integers(0, 256, size=n * k // 2, dtype=np.uint8)
+        fn = lambda: L.gko_bench_gemv_q4_rows(_p(w, _u8p), _p(x, _f32p), _p(sc, _f32p), _p(out, _f32p), n, k)
+    elif kind == "gemm_q8":
+        w = rng.integers(-128, 128, size=n * k, dtype=np.int8)
+        fn = lambda: L.gko_scalar_gemm_q8(_p(w, i8p), _p(x, _f32p), _p(out, _f32p), _p(sc, _f32p), mi, n, k)
+    elif kind == "gemm_q4":
+        w = rng.integers(0, 256, size=n * k // 2, dtype=np.uint8)
+        fn = lambda: L.gko_scalar_gemm_q4(_p(w, _u8p), _p(x, _f32p), _p(out, _f32p), _p(sc, _f32p), mi, n, k)
+    elif kind == "kquant_matmul":
+        w = rng.integers(0, 256, size=n * (k // 256) * 144, dtype=np.uint8)
+        w.reshape(-1, 144)[:, 0:4] = np.frombuffer(np.float32(0.01).tobytes(), np.uint8)
+        fn = lambda: L.gko_scalar_kquant_matmul(_p(w, _u8p), _p(x, _f32p), _p(out, _f32p), 144, 256, mi, n, k)
+    else:
+        raise ValueError(kind)
+    t0 = time.perf_counter()
+    fn()
+    return time.perf_counter() - t0, mi
 
 
 def rel_err(y, ref) -> float:

@@ -268,6 +268,23 @@ cases["q8_k_matmul"] = {"cite": "src/tests_fragments/part1.inc.rs:1011-1024", "q
 cases["metadata_gguf"] = {"cite": "src/quant.rs:375-456",
                           "q6_k": [256, 210], "q5_k": [256, 176], "q8_k": [256, 292], "q4_0": [32, 18], "q5_0": [32, 22]}
 
+# src/tests_fragments/part2.inc.rs:161-176 test_gemv_q8 and :214-232 test_gemm_q8: one Q8_K block d = 0.5, qs = 1, input = 1
+# -> 128 (tolerance 1.0 in the reference)
+cases["gemv_q8"] = {"cite": "src/tests_fragments/part2.inc.rs:161-176", "weight": q8_k_block(0.5, {i: 1 for i in range(256)}),
+                    "input": [1.0] * 256, "scale": 1.0, "n": 256, "expect": 128.0, "tol": 1.0}
+cases["gemm_q8"] = {"cite": "src/tests_fragments/part2.inc.rs:214-232", "weight": q8_k_block(0.5, {i: 1 for i in range(256)}),
+                    "input": [1.0] * 512, "scales": [1.0], "m": 2, "n": 1, "k": 256, "expect": [128.0, 128.0], "tol": 1.0}
+# src/tests_fragments/part2.inc.rs:178-188 test_gemv_q4: an all-zero Q4_K block -> |result| < 1
+cases["gemv_q4_zero"] = {"cite": "src/tests_fragments/part2.inc.rs:178-188", "weight": [0] * 144, "input": [1.0] * 256, "scale": 1.0,
+                         "n": 256, "expect": 0.0, "tol": 1.0}
+
+# scalar-ops/src/moe.rs:178-192  test_topk_selects_largest: 1 row, 4 experts, top_k = 2 -> experts 1 then 2, weights sum 1
+cases["moe_topk"] = {"cite": "scalar-ops/src/moe.rs:178-192", "probs": [0.1, 0.5, 0.3, 0.1], "seq_len": 1, "num_experts": 4,
+                     "top_k": 2, "expect_indices": [1, 2], "weights_sum": 1.0, "weights_sum_tol": 1e-5}
+# scalar-ops/src/moe.rs:194-217  test_weighted_sum_identity: one expert, weight 1 -> the expert's row
+cases["moe_weighted_sum"] = {"cite": "scalar-ops/src/moe.rs:194-217", "expert_outputs": [1.0, 2.0, 3.0], "indices": [0],
+                             "weights": [1.0], "seq_len": 1, "hidden": 3, "top_k": 1, "expect": [1.0, 2.0, 3.0]}
+
 with open(os.path.join(HERE, "reference_known_answers.json"), "w") as f:
     json.dump(cases, f, indent=0)
 print("wrote", len(cases), "groups")

@@ -198,3 +198,40 @@ def test_linearity_large(K, gk, torch):
     ref = (K.dequant(w).double() @ x1.double().T).T
     assert float((K.gemv(w, x1).double() - ref).abs().max()) / float(ref.abs().max()) <= 1e-4
     w.free()
+
+
+# ---- Kernels::gemv_q8 / gemm_q8 / gemv_q4 (src/traits.rs:500-510): Q8_K / Q4_K rows with optional scales -------------
+def test_gemv_q8_gemm_q8_gemv_q4_reference_known_answers(gk, K):
+    import json
+    import os
+    with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_known_answers.json")) as f:
+        KA = json.load(f)
+    c = KA["gemv_q8"]
+    w_i8 = np.array(c["weight"], np.uint8).view(np.int8)  # the reference hands the blocks over as &[i8]
+    assert abs(K.gemv_q8(w_i8, np.array(c["input"], np.float32), c["scale"], c["n"]) - c["expect"]) < c["tol"]
+    c = KA["gemm_q8"]
+    out = np.zeros(c["m"] * c["n"], np.float32)
+    K.gemm_q8(np.array(c["weight"], np.uint8).view(np.int8), np.array(c["input"], np.float32), out, c["scales"], c["m"], c["n"], c["k"])
+    assert np.abs(out - np.array(c["expect"], np.float32)).max() < c["tol"]
+    c = KA["gemv_q4_zero"]
+    assert abs(K.gemv_q4(np.array(c["weight"], np.uint8), np.array(c["input"], np.float32), c["scale"], c["n"]) - c["expect"]) < c["tol"]
+
+
+@pytest.mark.parametrize("m,n,k,nscales", [(1, 64, 512, 0), (3, 100, 1024, 1), (20, 37, 768, 37), (5, 16, 256, 2)])
+def test_gemm_q8_against_the_oracle(gk, K, oracle, m, n, k, nscales):
+    """per-channel (n scales), per-tensor (1) and 'anything else = none' (src/cpu_kernels/mod.rs:2998-3026)."""
+    rng = np.random.default_rng(m + n + k)
+    nblk = n * (k // 256)
+    b = rng.integers(0, 256, size=(nblk, 292), dtype=np.uint8)
+    b[:, 0:4] = np.frombuffer(rng.uniform(-0.02, 0.02, nblk).astype(np.float32).tobytes(), np.uint8).reshape(nblk, 4)
+    b = b.reshape(-1)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    scales = rng.uniform(0.5, 2.0, nscales).astype(np.float32) if nscales else None
+    out = np.zeros((m, n), np.float32)
+    K.gemm_q8(b.view(np.int8), x, out, scales, m, n, k)
+    ref = oracle.gemm_q8(b, x, scales, m, n, k)
+    assert oracle.rel_err(out, ref) <= 2e-3
+    assert K.gemv_q8(b[: (k // 256) * 292].view(np.int8), x[0], 1.5, k) == pytest.approx(oracle.gemv_q8(b[: (k // 256) * 292], x[0], 1.5, k), rel=2e-3, abs=1e-5)
+    with pytest.raises(gk.GllmkError) as e:  # k % 256 != 0: the reference asserts
+        K.gemm_q8(b.view(np.int8), x, out, None, m, n, 100)
+    assert e.value.status == gk.Status.INVALID_ARG

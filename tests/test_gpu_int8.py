@@ -107,3 +107,57 @@ def test_int8_argument_checks(gk, K, oracle):
     assert e.value.status == gk.Status.INVALID_ARG
     w.free()
     assert K.gemm_int8_host(np.zeros((0, 8), np.uint8), np.zeros((8, 4), np.int8)).shape == (0, 4)
+
+
+# ---- the activation half of W8A8: per-tensor f32 -> int8 (src/compiler/quant_convert.rs:165-177) -------------------------
+@pytest.mark.parametrize("rows,k", [(1, 7), (5, 64), (33, 1000), (257, 4096)])
+def test_activation_quantizer_bit_exact(gk, K, oracle, rows, k):
+    import torch
+    rng = np.random.default_rng(rows + k)
+    x = rng.standard_normal((rows, k)).astype(np.float32) * 3.0
+    x[0, 0] = 0.0
+    if k > 8:
+        x[-1, 3] = -x.__abs__().max() * 1.5   # the maximum is negative: -127 after rounding
+        x[0, 5] = np.float32(0.5) * np.float32(np.abs(x).max() / 127.0)  # a tie: rounds away from zero
+    q_ref, s_ref = oracle.quantize_int8_per_tensor(x)
+    xd = torch.from_numpy(x).cuda()
+    q, s = K.quantize_act_int8(xd)
+    assert s.item() == s_ref
+    assert np.array_equal(q.cpu().numpy(), q_ref)
+    qu, s2 = K.quantize_act_int8(xd, as_unsigned=True)
+    assert s2.item() == s_ref
+    assert np.array_equal(qu.cpu().numpy().astype(np.int16) - 128, q_ref.astype(np.int16))
+    # a strided view (leading dimension larger than k) and an all-zero tensor
+    wide = torch.zeros((rows, k + 9), device="cuda")
+    wide[:, :k] = xd
+    q3, _ = K.quantize_act_int8(wide[:, :k])
+    assert np.array_equal(q3.cpu().numpy(), q_ref)
+    qz, sz = K.quantize_act_int8(torch.zeros((rows, k), device="cuda"))
+    assert sz.item() == 0.0 and not qz.cpu().numpy().any()
+
+
+@pytest.mark.parametrize("m,n,k,act", [(1, 128, 256, 0), (37, 300, 1000, 0), (200, 513, 2048, 1), (64, 1024, 4096, 2)])
+def test_w8a8_linear_against_the_reference_pipeline(gk, K, oracle, m, n, k, act):
+    """quantize_from_fp32 -> gemm_int8 (exact s32) -> dequantize_i32_to_f32, as the reference chains them, evaluated with
+    the oracle's quantizer, an int64 matmul and f32 arithmetic in the epilogue's order: bit-exact without an activation
+    function, 1e-6 relative with one (expf / tanhf differ in the last bit between libm and the device)."""
+    import torch
+    rng = np.random.default_rng(m * n + k)
+    x = (rng.standard_normal((m, k)) * 2.0).astype(np.float32)
+    b = rng.integers(-128, 128, size=(k, n), dtype=np.int8)
+    bias = rng.standard_normal(n).astype(np.float32)
+    scale_b = np.float32(0.013)
+    w = K.upload_int8(b, layout_kn=True)
+    y = K.w8a8_linear(w, torch.from_numpy(x).cuda(), float(scale_b), bias=torch.from_numpy(bias).cuda(), activation=act).cpu().numpy()
+    q, s = oracle.quantize_int8_per_tensor(x)
+    c = (q.astype(np.int64) @ b.astype(np.int64)).astype(np.float32)
+    ref = (c * np.float32(s)) * scale_b + bias
+    if act == 1:
+        ref = np.maximum(ref, 0)
+    elif act == 2:
+        ref = ref / (np.float32(1) + np.exp(-ref, dtype=np.float32))
+    if act == 0:
+        assert np.array_equal(y.view(np.uint32), ref.astype(np.float32).view(np.uint32))
+    else:
+        assert np.allclose(y, ref, rtol=2e-6, atol=1e-7)
+    w.free()

@@ -31,7 +31,7 @@ def _worker(rank, world, port, q):
         from oracle import oracle as O
         K = gk.GpuKernels(rank)
         cases = [("q4k", 256, 512, 1), ("q4k", 200, 256, 3), ("q8_0", 176, 96, 16)]
-        ex = gk.PeerExchange(K, world, rank, slots=len(cases), slot_floats=16 * 256)
+        ex = gk.PeerExchange(K, world, rank, slots=len(cases), slot_floats=16 * 512)
         for rep in range(3):  # the same slots are rewritten: sequence numbers and flag reuse
             for slot, (fmt, n, k, m) in enumerate(cases):
                 rng = np.random.default_rng(n + k + m + rep)
@@ -51,6 +51,58 @@ def _worker(rank, world, port, q):
                 assert err <= 2e-3, f"rank {rank} {fmt} n={n} m={m} rep={rep}: {err}"
                 w.free()
                 dist.barrier()  # nobody rewrites a slot another rank is still reading back to the host
+        # chained products without a barrier launch: y1 = W1 x is gathered into slot 0 of every rank, y2 = W2 y1
+        # reads it there (its staging kernel waits for every rank's bands of y1), and the chain ends with wait().
+        # Eager launches first, then the same chain captured once and replayed (the epochs live in device memory).
+        n1, k1, n2, m = 512, 256, 208, 2
+        rng = np.random.default_rng(99)
+        W1 = (rng.standard_normal((n1, k1)) * 0.05).astype(np.float32)
+        W2 = (rng.standard_normal((n2, n1)) * 0.05).astype(np.float32)
+        b1, b2 = O.quantize_q4_k(W1), O.quantize_q4_k(W2)
+        qt = gk.QuantType.q4k()
+        ra, rb = gk.shard_rows(n1, world, rank), gk.shard_rows(n2, world, rank)
+        w1 = K.upload(qt, ra[1] - ra[0], k1, gk.slice_blocks(qt, b1, n1, k1, *ra))
+        w2 = K.upload(qt, rb[1] - rb[0], n1, gk.slice_blocks(qt, b2, n2, n1, *rb))
+        y1_t, y2_t = ex.local_tensor(0, (m, n1)), ex.local_tensor(1, (m, n2))
+        xs = torch.empty((m, k1), device="cuda")
+
+        def chain():
+            ex.gemv_chained(w1, xs, 0, ra[0], n1)
+            ex.gemv_chained(w2, y1_t, 1, rb[0], n2)
+            ex.wait()
+
+        def check(tag):
+            torch.cuda.synchronize()
+            assert K.status() == 0
+            x = xs.cpu().numpy()
+            y1 = O.quant_matmul(b1, np.ascontiguousarray(x.T), O.Q4K, n1, m, k1).T
+            y2 = O.quant_matmul(b2, np.ascontiguousarray(y1.T), O.Q4K, n2, m, n1).T
+            e1, e2 = O.rel_err(y1_t.cpu().numpy(), y1), O.rel_err(y2_t.cpu().numpy(), y2)
+            assert e1 <= 2e-3 and e2 <= 4e-3, f"rank {rank} {tag}: {e1} {e2}"
+            dist.barrier()
+
+        for rep in range(3):
+            xs.copy_(torch.from_numpy(np.random.default_rng(200 + rep).standard_normal((m, k1)).astype(np.float32)))
+            chain()
+            check(f"eager {rep}")
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            chain()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        dist.barrier()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            chain()
+        for rep in range(4):
+            xs.copy_(torch.from_numpy(np.random.default_rng(300 + rep).standard_normal((m, k1)).astype(np.float32)))
+            graph.replay()
+            if rep % 2:
+                graph.replay()  # back-to-back replays: slot reuse one chain later
+            check(f"graph {rep}")
+        w1.free()
+        w2.free()
         ex.close()
         K.close()
         q.put((rank, "ok"))
@@ -100,7 +152,10 @@ def test_two_devices_in_one_process():
         with torch.cuda.device(dev):
             y1 = K.gemv(w, torch.from_numpy(x1).to(f"cuda:{dev}")).cpu().numpy()
             ym = K.gemm(w, torch.from_numpy(xm).to(f"cuda:{dev}").to(torch.bfloat16)).cpu().numpy()
+            ys = torch.full((1, n), float("nan"), device=f"cuda:{dev}")
+            K.gemv_static(w, torch.from_numpy(x1).to(f"cuda:{dev}"), ys)  # its scratch array exists once per device
             torch.cuda.synchronize(dev)
+            assert np.array_equal(ys.cpu().numpy(), y1)
         assert O.rel_err(y1, O.quant_matmul(blocks, np.ascontiguousarray(x1.T), O.Q4K, n, 1, k).T) <= 2e-3
         xb = torch.from_numpy(xm).to(torch.bfloat16).to(torch.float32).numpy()
         assert O.rel_err(ym, O.gemm_f32_nt(xb, wd)) <= 1e-2

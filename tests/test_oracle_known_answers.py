@@ -183,3 +183,56 @@ def test_gguf_dot_is_decode_then_dot(oracle, name):
     dec = np.concatenate([oracle.dequant_block(qt, w[b]) for b in range(nb)])
     ref = float(np.dot(dec.astype(np.float64), x.astype(np.float64)))
     assert abs(float(y[0, 0]) - ref) <= 1e-4 * max(1.0, abs(ref))
+
+
+def test_moe_topk_and_weighted_sum_known_answers(oracle):
+    """scalar-ops/src/moe.rs:178-217 (the reference's own tests), plus the conventions the restatement must keep."""
+    c = KA["moe_topk"]
+    out = oracle.scalar_topk(np.array(c["probs"], np.float32).reshape(c["seq_len"], c["num_experts"]), c["top_k"])
+    assert out[0].view(np.uint32).tolist() == c["expect_indices"]  # indices are u32 bit patterns in f32 slots
+    assert abs(out[1].sum() - c["weights_sum"]) < c["weights_sum_tol"]
+    assert out[1].tolist() == [np.float32(0.5) * (np.float32(1.0) / (np.float32(0.5) + np.float32(0.3))),
+                               np.float32(0.3) * (np.float32(1.0) / (np.float32(0.5) + np.float32(0.3)))]
+    c = KA["moe_weighted_sum"]
+    routing = np.concatenate([np.array(c["indices"], np.uint32).view(np.float32), np.array(c["weights"], np.float32)])
+    got = oracle.scalar_weighted_sum(np.array(c["expert_outputs"], np.float32).reshape(1, c["seq_len"], c["hidden"]), routing,
+                                     c["seq_len"], c["top_k"])
+    assert got.reshape(-1).tolist() == c["expect"]
+    # ties go to the earlier expert; a NaN probability is never selected; all-zero rows give zero weights
+    out = oracle.scalar_topk(np.array([[0.25, 0.25, 0.25, 0.25], [np.nan, 0.2, 0.7, 0.1], [0, 0, 0, 0]], np.float32), 2)
+    assert out[0].view(np.uint32).reshape(3, 2).tolist() == [[0, 1], [2, 1], [0, 1]]
+    assert out[1].reshape(3, 2)[2].tolist() == [0.0, 0.0]
+    # the grouped-row form of the recombination is the same sum as the reference's [expert][seq][hidden] form
+    rng = np.random.default_rng(5)
+    E, T, H, top_k = 4, 9, 7, 2
+    routing = oracle.scalar_topk(rng.random((T, E), dtype=np.float32), top_k)
+    eo = rng.standard_normal((E, T, H)).astype(np.float32)
+    idx = routing[0].view(np.uint32).reshape(T, top_k)
+    rows = np.stack([eo[idx[t, ki], t] for t in range(T) for ki in range(top_k)])
+    a = oracle.scalar_weighted_sum(eo, routing, T, top_k)
+    b = oracle.scalar_weighted_sum_grouped(rows, routing, np.arange(T * top_k), T, top_k)
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
+def test_gemv_q8_gemm_q8_gemv_q4_known_answers(oracle):
+    """src/tests_fragments/part2.inc.rs:161-232."""
+    c = KA["gemv_q8"]
+    assert abs(oracle.gemv_q8(np.array(c["weight"], np.uint8), c["input"], c["scale"], c["n"]) - c["expect"]) < c["tol"]
+    c = KA["gemm_q8"]
+    out = oracle.gemm_q8(np.array(c["weight"], np.uint8), np.array(c["input"], np.float32).reshape(c["m"], c["k"]), c["scales"],
+                         c["m"], c["n"], c["k"])
+    assert np.abs(out.reshape(-1) - np.array(c["expect"])).max() < c["tol"]
+    c = KA["gemv_q4_zero"]
+    assert abs(oracle.gemv_q4(np.array(c["weight"], np.uint8), c["input"], c["scale"], c["n"]) - c["expect"]) < c["tol"]
+
+
+def test_int8_per_tensor_quantizer_rule(oracle):
+    """src/compiler/quant_convert.rs:17-20,165-177: scale = max|x| / 127, round half away from zero, clamp to
+    [-128, 127]; an all-zero tensor gives scale 0 and zeros."""
+    x = np.array([0.0, 1.27, -1.27, 0.005, -0.005, 0.015, 0.635, -0.645], np.float32)
+    q, s = oracle.quantize_int8_per_tensor(x)
+    assert s == np.float32(1.27) / np.float32(127.0)
+    want = np.clip(np.sign(x / np.float32(s)) * np.floor(np.abs(x / np.float32(s)) + np.float32(0.5)), -128, 127).astype(np.int8)
+    assert q.tolist() == want.tolist() and q[1] == 127 and q[2] == -127
+    q, s = oracle.quantize_int8_per_tensor(np.zeros(5, np.float32))
+    assert s == 0.0 and not q.any()
