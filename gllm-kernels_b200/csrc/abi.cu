@@ -264,6 +264,8 @@ int32_t gllmk_ctx_set(gllmk_ctx ctx, const char *key, int64_t value) {
     if (!strcmp(key, "gemv_ctas_per_sm")) c->gemv_ctas_per_sm = value;
     else if (!strcmp(key, "gemv_pdl")) c->gemv_pdl = value;
     else if (!strcmp(key, "gemv_fp4_int")) c->gemv_fp4_int = value;
+    else if (!strcmp(key, "gemm_fp4_pair")) c->gemm_fp4_pair = value;
+    else if (!strcmp(key, "gemv_fuse")) c->gemv_fuse = value;
     else if (!strcmp(key, "peer_wait_spins")) {
         if (value < 1 || value > ((int64_t)1 << 30)) return fail(c, GLLMK_STATUS_INVALID_ARG, "peer_wait_spins outside 1..2^30");
         c->peer_wait_spins = value;
@@ -587,9 +589,10 @@ int32_t gllmk_w8a8_linear_f32(gllmk_ctx ctx, gllmk_weight wh, const float *x_dev
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     // context scratch: [scale f32, amax u32 | pad to 256] [u8 activations m x k] [s32 products m x n]
     const size_t ab = ((size_t)m * (size_t)w->k + 255) & ~(size_t)255, cb = (size_t)m * (size_t)w->n * sizeof(int32_t);
-    int32_t rc = ensure_act(c, 256 + ab + cb);
+    // (the context's device I/O buffer: the integer GEMM stages its tile images in the activation workspace itself)
+    int32_t rc = ensure_dev_io(c, 256 + ab + cb);
     if (rc) return rc;
-    char *base = static_cast<char *>(c->act);
+    char *base = static_cast<char *>(c->dev_io);
     float *scale = reinterpret_cast<float *>(base);
     uint8_t *q = reinterpret_cast<uint8_t *>(base + 256);
     int32_t *ci = reinterpret_cast<int32_t *>(base + 256 + ab);

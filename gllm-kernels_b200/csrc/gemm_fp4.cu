@@ -196,6 +196,222 @@ gemm_fp4_kernel(const __grid_constant__ Fp4Params p, const int ntok) {
     if (warp == 1) tc::tmem_dealloc(tmem, F4_TMEM_COLS);
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// CTA-pair version (m > 128): persistent, two CTAs of a cluster on two SMs work on one 256-row x 256-token tile.
+//
+// The one-CTA kernel above is bound by what an SM can pull from L2: 54 KB per k-step for 8.4 M multiply-adds.  As
+// a pair (tcgen05 cta_group::2, MMA M = 256) each CTA brings in its own 128 weight rows, HALF of the activation
+// tile (the tensor core reads the other half from the partner's shared memory) and the scale atoms: 38 KB per
+// k-step for the same multiply-adds per SM.  The kernel is persistent (grid = resident pairs, tiles dealt round
+// robin), so the copy threads run ahead into the next tile while the accumulator of the finished one is stored.
+//
+// Per CTA: warp 0 lane 0 copies; warp 1 lane 0 issues the MMAs (leader = cluster rank 0) or forwards "my stage is
+// full" to the leader (rank 1), because a wait on an mbarrier can only be done by its own CTA; warps 2..9 store the
+// CTA's 128 rows x 256 tokens of the accumulator.  Loads are plain bulk copies: nothing is multicast.
+// ---------------------------------------------------------------------------------------------
+constexpr int P4_STAGES = 5;
+constexpr int P4_A_BYTES = 16384, P4_B_BYTES = 16384, P4_SFA_BYTES = 2048, P4_SFB_BYTES = 4096;
+constexpr int P4_STAGE_BYTES = P4_A_BYTES + P4_B_BYTES + P4_SFA_BYTES + P4_SFB_BYTES;
+constexpr int P4_EPI_WARPS = 8;
+constexpr int P4_THREADS = 64 + 32 * P4_EPI_WARPS;
+constexpr size_t P4_SMEM = (size_t)P4_STAGES * P4_STAGE_BYTES + (size_t)P4_EPI_WARPS * 4096 + 1024;
+constexpr uint32_t P4_TMEM_COLS = 512;                      // 256 accumulator + 16 SFA + 32 SFB, power of two
+constexpr uint32_t P4_TMEM_SFA = 256, P4_TMEM_SFB = 272;    // one set: scale copies and MMAs execute in issue order
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P4_THREADS, 1)
+gemm_fp4_pair_kernel(const __grid_constant__ Fp4Params p, const int row_tiles, const int tok_tiles) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bars[3 * P4_STAGES + 2];
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int abort_s;
+    const uint32_t smem_s = (tc::smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t full = tc::smem_u32(&bars[0]), empty = tc::smem_u32(&bars[P4_STAGES]), full2 = tc::smem_u32(&bars[2 * P4_STAGES]);
+    const uint32_t accum_full = tc::smem_u32(&bars[3 * P4_STAGES]), accum_empty = tc::smem_u32(&bars[3 * P4_STAGES + 1]);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = tc::cluster_ctarank();
+    const int pair = (int)(blockIdx.x >> 1), npairs = (int)(gridDim.x >> 1);
+    const int row_pairs = (row_tiles + 1) >> 1;
+    const int ntiles = row_pairs * tok_tiles;
+    const int nks = (int)(p.k / 256);
+    const int64_t atoms_per_row_tile = p.nv ? (p.k >> 6) : (p.k >> 7);
+    const int atoms_per_stage = p.nv ? 4 : 2;
+    volatile int *abort_flag = &abort_s;
+
+    if (threadIdx.x == 0) {
+        abort_s = 0;
+        for (int s = 0; s < P4_STAGES; s++) {
+            tc::mbar_init(full + 8 * s, 1);
+            tc::mbar_init(empty + 8 * s, 1);
+            tc::mbar_init(full2 + 8 * s, 1);
+        }
+        tc::mbar_init(accum_full, 1);
+        tc::mbar_init(accum_empty, 2 * P4_EPI_WARPS);
+        tc::mbar_init_fence();
+    }
+    if (warp == 1) tc::tmem_alloc_pair(tc::smem_u32(&tmem_base_s), P4_TMEM_COLS);
+    tc::fence_before_sync();
+    __syncthreads();
+    // both CTAs' barriers exist before either CTA arrives on the other's
+    tc::cluster_arrive();
+    tc::cluster_wait();
+    tc::fence_after_sync();
+    const uint32_t tmem = tmem_base_s;
+
+    if (warp == 0 && lane == 0) {
+        // ---------------- copies: own weight rows, own half of the activation tile, scale atoms ----------------
+        const uint32_t sf_bytes = (uint32_t)atoms_per_stage * 512u;
+        const size_t ktiles = (size_t)nks;
+        uint32_t g = 0;
+        for (int t = pair; t < ntiles && !*abort_flag; t += npairs) {
+            const int rp = t / tok_tiles, tt = t % tok_tiles;
+            const int64_t my_row_tile = 2 * (int64_t)rp + rank;
+            const bool a_ok = my_row_tile < row_tiles;
+            const int64_t b_tile0 = 2 * (int64_t)tt;  // 128-token groups of this tile: b_tile0 (leader's half), + 1 (partner's)
+            const bool b_ok = b_tile0 + rank < p.x_row_tiles;
+            const bool sfb_ok[2] = {b_tile0 < p.x_row_tiles, b_tile0 + 1 < p.x_row_tiles};
+            // rows / tokens that do not exist are not copied: whatever the stage holds there only reaches accumulator
+            // rows / columns that are never stored
+            const uint32_t tx = (a_ok ? 16384u + sf_bytes : 0u) + (b_ok ? 16384u : 0u) + ((uint32_t)sfb_ok[0] + (uint32_t)sfb_ok[1]) * sf_bytes;
+            for (int ks = 0; ks < nks; ks++, g++) {
+                const uint32_t s = g % P4_STAGES;
+                if (g >= P4_STAGES && !tc::mbar_wait_cluster(empty + 8 * s, (g / P4_STAGES - 1) & 1u, abort_flag)) {
+                    abort_s = 1;
+                    atomicExch(p.status, 24);
+                    break;
+                }
+                const uint32_t st = smem_s + s * P4_STAGE_BYTES;
+                tc::mbar_expect_tx(full + 8 * s, tx);
+                if (a_ok) {
+                    bulk_load(st, p.qw + ((size_t)my_row_tile * ktiles + ks) * 16384, 16384u, full + 8 * s);
+                    bulk_load(st + P4_A_BYTES + P4_B_BYTES, p.sfw + ((size_t)my_row_tile * atoms_per_row_tile + (size_t)ks * atoms_per_stage) * 512,
+                              sf_bytes, full + 8 * s);
+                }
+                if (b_ok) bulk_load(st + P4_A_BYTES, p.qx + ((size_t)(b_tile0 + rank) * ktiles + ks) * 16384, 16384u, full + 8 * s);
+                for (int h = 0; h < 2; h++)
+                    if (sfb_ok[h])
+                        bulk_load(st + P4_A_BYTES + P4_B_BYTES + P4_SFA_BYTES + h * 2048,
+                                  p.sfx + ((size_t)(b_tile0 + h) * atoms_per_row_tile + (size_t)ks * atoms_per_stage) * 512, sf_bytes, full + 8 * s);
+            }
+        }
+    } else if (warp == 1 && lane == 0 && rank != 0) {
+        // ---------------- partner CTA: tell the leader when this CTA's stage has landed ----------------
+        uint32_t g = 0;
+        for (int t = pair; t < ntiles && !*abort_flag; t += npairs)
+            for (int ks = 0; ks < nks; ks++, g++) {
+                const uint32_t s = g % P4_STAGES;
+                if (!tc::mbar_wait(full + 8 * s, (g / P4_STAGES) & 1u, abort_flag)) {
+                    abort_s = 1;
+                    atomicExch(p.status, 25);
+                    t = ntiles;
+                    break;
+                }
+                tc::mbar_arrive_cluster(tc::map_to_cta(full2 + 8 * s, 0));
+            }
+    } else if (warp == 1 && lane == 0) {
+        // ---------------- leader CTA: scale copies + MMA issue for the pair ----------------
+        const uint32_t idesc_nv = tc::idesc_fp4(256, 256, 0, 0, 0);
+        uint32_t g = 0, it = 0;
+        for (int t = pair; t < ntiles && !*abort_flag; t += npairs, it++) {
+            // the accumulator of the previous tile has been read out by all sixteen epilogue warps of the pair
+            if (it > 0 && !tc::mbar_wait_cluster(accum_empty, (it - 1) & 1u, abort_flag)) {
+                abort_s = 1;
+                atomicExch(p.status, 26);
+                break;
+            }
+            tc::fence_after_sync();
+            bool ok = true;
+            for (int ks = 0; ks < nks; ks++, g++) {
+                const uint32_t s = g % P4_STAGES, ph = (g / P4_STAGES) & 1u;
+                if (!tc::mbar_wait(full + 8 * s, ph, abort_flag) || !tc::mbar_wait_cluster(full2 + 8 * s, ph, abort_flag)) {
+                    abort_s = 1;
+                    atomicExch(p.status, 22);
+                    ok = false;
+                    break;
+                }
+                tc::fence_after_sync();
+                const uint32_t st = smem_s + s * P4_STAGE_BYTES;
+                const uint32_t sfa = st + P4_A_BYTES + P4_B_BYTES, sfb = sfa + P4_SFA_BYTES;
+                const uint64_t ad = tc::smem_desc_sw128(st), bd = tc::smem_desc_sw128(st + P4_A_BYTES);
+                if (p.nv) {
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        tc::tmem_cp_sf_pair(tmem + P4_TMEM_SFA + 4 * j, sf_desc(sfa + 512 * j));
+                        tc::tmem_cp_sf_pair(tmem + P4_TMEM_SFB + 8 * j, sf_desc(sfb + 512 * j));
+                        tc::tmem_cp_sf_pair(tmem + P4_TMEM_SFB + 8 * j + 4, sf_desc(sfb + 2048 + 512 * j));
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; j++)
+                        tc::mma_nvf4_pair(tmem, ad + 2 * j, bd + 2 * j, idesc_nv, (uint32_t)((ks | j) != 0), tmem + P4_TMEM_SFA + 4 * j,
+                                          tmem + P4_TMEM_SFB + 8 * j);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 2; j++) {
+                        tc::tmem_cp_sf_pair(tmem + P4_TMEM_SFA + 4 * j, sf_desc(sfa + 512 * j));
+                        tc::tmem_cp_sf_pair(tmem + P4_TMEM_SFB + 8 * j, sf_desc(sfb + 512 * j));
+                        tc::tmem_cp_sf_pair(tmem + P4_TMEM_SFB + 8 * j + 4, sf_desc(sfb + 2048 + 512 * j));
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const int id = (j & 1) * 2;
+                        tc::mma_mxf4_pair(tmem, ad + 2 * j, bd + 2 * j, tc::idesc_fp4(256, 256, 1, id, id), (uint32_t)((ks | j) != 0),
+                                          tmem + P4_TMEM_SFA + 4 * (j >> 1), tmem + P4_TMEM_SFB + 8 * (j >> 1));
+                    }
+                }
+                // stage s is free in BOTH CTAs once these MMAs have read it
+                tc::mma_commit_pair(empty + 8 * s);
+                tc::mma_commit_pair(tc::map_to_cta(empty + 8 * s, 1));
+            }
+            if (!ok) break;
+            tc::mma_commit_pair(accum_full);
+            tc::mma_commit_pair(tc::map_to_cta(accum_full, 1));
+        }
+    }
+    __syncwarp();
+
+    if (warp >= 2) {
+        // ---------------- epilogue: this CTA's 128 rows x 256 tokens; warp w reads TMEM lane quadrant w % 4 ----------------
+        const int quad = warp & 3, half = (warp - 2) >> 2;
+        uint8_t *stage = smem_raw + (smem_s - tc::smem_u32(smem_raw)) + (size_t)P4_STAGES * P4_STAGE_BYTES + (size_t)(warp - 2) * 4096;
+        const uint32_t accum_empty_leader = tc::map_to_cta(accum_empty, 0);
+        uint32_t it = 0;
+        for (int t = pair; t < ntiles; t += npairs, it++) {
+            bool ok = !abort_s && tc::mbar_wait_cluster(accum_full, it & 1u, abort_flag);
+            if (!ok && !abort_s) {
+                abort_s = 1;
+                atomicExch(p.status, 23);
+            }
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc::fence_after_sync();
+            const int rp = t / tok_tiles, tt = t % tok_tiles;
+            const int64_t row0 = (2 * (int64_t)rp + rank) * 128 + 32 * quad, tok0 = (int64_t)tt * 256;
+            for (int c = 128 * half; c < 128 * half + 128; c += 32) {
+                uint32_t v[32];
+                tc::tmem_ld32(tmem + ((uint32_t)(32 * quad) << 16) + (uint32_t)c, v);
+                tc::tmem_ld_wait();
+                if (row0 < p.n && tok0 + c < p.m) {
+                    float o[32];
+#pragma unroll
+                    for (int j = 0; j < 32; j++) o[j] = __uint_as_float(v[j]) * p.scale;
+                    if (p.y_bf16) tc::store_block_32x32<true>(p.y, p.ldy, row0, tok0 + c, p.n, p.m, o, stage, lane, p.vec);
+                    else tc::store_block_32x32<false>(p.y, p.ldy, row0, tok0 + c, p.n, p.m, o, stage, lane, p.vec);
+                }
+            }
+            // this warp's reads of the accumulator are complete: the leader may start the next tile
+            tc::fence_before_sync();
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive_cluster(accum_empty_leader);
+        }
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    // neither CTA may leave (or give TMEM back) while the pair's MMAs can still read its shared memory
+    tc::cluster_arrive();
+    tc::cluster_wait();
+    if (warp == 1) tc::tmem_dealloc_pair(tmem, P4_TMEM_COLS);
+}
+
 // ---------------------------------------------------------------------------------------------
 // w: weights [n, k]; x: activations [m, k] in the same FP4 format, uploaded like a weight.
 int32_t gemm_fp4_launch(Ctx *c, const Weight *w, const Weight *x, void *y, int y_bf16, int64_t ldy, cudaStream_t s) {
@@ -226,6 +442,35 @@ int32_t gemm_fp4_launch(Ctx *c, const Weight *w, const Weight *x, void *y, int y
     p.ldy = ldy;
     p.vec = (((uintptr_t)y & 15) == 0 && (ldy * (y_bf16 ? 2 : 4)) % 16 == 0) ? 1 : 0;
     p.status = c->status_dev;
+    if (m > 128 && c->gemm_fp4_pair) {
+        static int pairs_resident[64] = {};  // per device: CTA pairs that can be resident at once (0 = not yet asked)
+        if (!pairs_resident[dev_slot]) {
+            GK_CUDA(c, cudaFuncSetAttribute(gemm_fp4_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P4_SMEM));
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3((unsigned)c->sm_count & ~1u);
+            cfg.blockDim = dim3(P4_THREADS);
+            cfg.dynamicSmemBytes = P4_SMEM;
+            int nclusters = 0;
+            cudaLaunchAttribute at[1];
+            at[0].id = cudaLaunchAttributeClusterDimension;
+            at[0].val.clusterDim.x = 2;
+            at[0].val.clusterDim.y = 1;
+            at[0].val.clusterDim.z = 1;
+            cfg.attrs = at;
+            cfg.numAttrs = 1;
+            if (cudaOccupancyMaxActiveClusters(&nclusters, gemm_fp4_pair_kernel, &cfg) != cudaSuccess || nclusters < 1) {
+                (void)cudaGetLastError();
+                nclusters = c->sm_count / 2;
+            }
+            pairs_resident[dev_slot] = nclusters < c->sm_count / 2 ? nclusters : c->sm_count / 2;
+        }
+        const int row_tiles = (int)(w->n_pad / 128), tok_tiles = (m + 255) / 256;
+        const int ntiles = ((row_tiles + 1) / 2) * tok_tiles;
+        const int npairs = ntiles < pairs_resident[dev_slot] ? ntiles : pairs_resident[dev_slot];
+        gemm_fp4_pair_kernel<<<dim3(2u * (unsigned)npairs), P4_THREADS, P4_SMEM, s>>>(p, row_tiles, tok_tiles);
+        GK_CUDA(c, cudaGetLastError());
+        return GLLMK_STATUS_OK;
+    }
     dim3 grid((unsigned)(w->n_pad / F4_BM), (unsigned)((m + F4_BN - 1) / F4_BN));
     gemm_fp4_kernel<<<grid, F4_THREADS, F4_SMEM, s>>>(p, ntok);
     GK_CUDA(c, cudaGetLastError());

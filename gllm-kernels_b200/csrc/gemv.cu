@@ -223,6 +223,13 @@ struct GemvParams {
     uint32_t *xflags_peer[GLLMK_MAX_PEERS];
     int xrank;
     int ntiles;                              // row tiles of the launch (counters[ntiles] counts the completed ones)
+    // fused staging (small shares): every CTA converts the activation slices of ITS k-steps itself, straight into shared
+    // memory, instead of copying them from an image a staging kernel wrote — one launch less per product
+    const float *x, *x_up;
+    int64_t xst, xsk, K;
+    int fuse_slices;                         // slices a CTA keeps (0: the image path)
+    int xnranks;                             // exchange products: ranks to wait for before x is read
+    uint32_t spins;
     const float *row_scales;
     int64_t n_row_scales;
     int64_t n;
@@ -249,6 +256,61 @@ __host__ __device__ constexpr int sf_bytes() { return FMT == FMT_MXFP4 ? 1024 : 
 template <int FMT>
 static inline size_t gemv_smem_bytes(int m) {
     return (size_t)GEMV_STAGES * (GEMV_WARPS * chunk_bytes<FMT>() + sf_bytes<FMT>() + slice_bytes(m)) + GEMV_ZERO + 2 * GEMV_STAGES * 8;
+}
+
+template <int FMT>
+static inline size_t gemv_smem_bytes_fused(int m, int nslices) {
+    return (size_t)GEMV_STAGES * (GEMV_WARPS * chunk_bytes<FMT>() + sf_bytes<FMT>()) + (size_t)nslices * slice_bytes(m) + GEMV_ZERO +
+           2 * GEMV_STAGES * 8;
+}
+
+// One activation slice (256 elements of k-block kb, all tokens) written by the whole CTA (thread = element, warp =
+// 32-element sub-block) in the layout of the image above: the arithmetic of stage_x_kernel, element for element.
+__device__ __forceinline__ void stage_slice_in_cta(const float *__restrict__ x, const float *__restrict__ x_up, int64_t xst, int64_t xsk,
+                                                   int64_t K, int m, int kb, uint8_t *slice, float (*wmax)[8], int (*wbad)[8], int &par) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int64_t k = (int64_t)kb * 256 + tid;
+    for (int tok = 0; tok < m; tok++, par ^= 1) {
+        float v = 0.f;
+        if (k < K) {
+            v = __ldcg(x + (int64_t)tok * xst + k * xsk);
+            if (x_up) v = (v / (1.0f + expf(-v))) * __ldcg(x_up + (int64_t)tok * xst + k * xsk);
+        }
+        float amax = fabsf(v);
+        const float inf = __int_as_float(0x7F800000);
+        int bad = !(fabsf(v) < inf);
+#pragma unroll
+        for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        bad = __any_sync(0xffffffffu, bad);
+        if (lane == 0) { wmax[par][warp] = amax; wbad[par][warp] = bad; }
+        __syncthreads();  // the other parity's slots are rewritten only after the next barrier: one barrier per token
+        amax = 0.f;
+        bad = 0;
+#pragma unroll
+        for (int w = 0; w < 8; w++) { amax = fmaxf(amax, wmax[par][w]); bad |= wbad[par][w]; }
+        const float pre = amax < 1e-20f ? 18446744073709551616.0f : 1.0f;
+        const float inv = (amax > 0.0f && !bad) ? 127.0f / (amax * pre) : 0.0f;
+        const float sc = (v * pre) * inv;
+        const float r1 = fminf(fmaxf(rintf(sc), -127.0f), 127.0f);
+        const float r2 = fminf(fmaxf(rintf((sc - r1) * 254.0f), -127.0f), 127.0f);
+        const int d1 = (int)r1, d2 = (int)r2;
+        slice[(2 * tok) * 288 + tid] = (uint8_t)(int8_t)d1;
+        slice[(2 * tok + 1) * 288 + tid] = (uint8_t)(int8_t)d2;
+        int s1 = d1, s2 = d2;
+#pragma unroll
+        for (int o = 16; o; o >>= 1) {
+            s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+            s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+        }
+        if (lane == 0) {
+            uint8_t *sp = slice + (2 * m) * 288;
+            sp[(2 * tok) * 16 + warp] = (uint8_t)(int8_t)(s1 >> 6);
+            sp[(2 * tok) * 16 + 8 + warp] = (uint8_t)(s1 & 63);
+            sp[(2 * tok + 1) * 16 + warp] = (uint8_t)(int8_t)(s2 >> 6);
+            sp[(2 * tok + 1) * 16 + 8 + warp] = (uint8_t)(s2 & 63);
+        }
+        if (tid == 0) reinterpret_cast<float *>(slice + (2 * m) * 304)[tok] = bad ? __int_as_float(0x7FC00000) : amax / 127.0f;
+    }
 }
 
 // ---- one 16-row x 256-k chunk of Q4_K -------------------------------------------------------
@@ -520,9 +582,11 @@ __device__ __forceinline__ int cta_of(const GemvParams &p, int64_t sc) {
 // contiguous in memory): CTA c owns super-chunks [c*per_cta, (c+1)*per_cta), one contiguous byte range.
 // Thread 0 is the producer: per step it issues two bulk copies (the super-chunk and the activation slice
 // of its k-step) into a ring stage; the 8 warps, each working on row tile 8*TG + warp, consume it.
-template <int FMT, int NT>
+template <int FMT, int NT, bool FUSE = false>
 __global__ void __launch_bounds__(256) gemv_kernel(const __grid_constant__ GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ float wmax_s[2][8];
+    __shared__ int wbad_s[2][8];
     constexpr int CHUNK = chunk_bytes<FMT>();
     constexpr int SFB = sf_bytes<FMT>();           // FP4 scale atoms of a super-chunk (own plane, own copy)
     constexpr int WDATA = GEMV_WARPS * CHUNK;      // weight bytes of a super-chunk in the main plane
@@ -530,9 +594,10 @@ __global__ void __launch_bounds__(256) gemv_kernel(const __grid_constant__ GemvP
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const uint32_t xbytes = slice_bytes(p.m);
-    const uint32_t stage_bytes = SUPER + xbytes;
+    const uint32_t stage_bytes = SUPER + (FUSE ? 0u : xbytes);
     const uint32_t smem_s = smem_u32(smem);
-    const uint32_t zero_s = smem_s + GEMV_STAGES * stage_bytes;
+    const uint32_t slices_s = smem_s + GEMV_STAGES * stage_bytes;  // FUSE: this CTA's activation slices, in step order
+    const uint32_t zero_s = slices_s + (FUSE ? (uint32_t)p.fuse_slices * xbytes : 0u);
     const uint32_t full = zero_s + GEMV_ZERO, empty = full + GEMV_STAGES * 8;
 
     // Whatever follows in the stream (the next call's staging kernel, then its GEMV grid) may be
@@ -562,8 +627,32 @@ __global__ void __launch_bounds__(256) gemv_kernel(const __grid_constant__ GemvP
             }
     }
     if (threadIdx.x < GEMV_ZERO / 4) reinterpret_cast<uint32_t *>(smem + (zero_s - smem_s))[threadIdx.x] = 0u;
-    asm volatile("griddepcontrol.wait;\n" ::: "memory");  // the activation image is complete from here on
-    if (threadIdx.x == 0) {
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");  // everything before this grid in the stream is complete from here on
+    if constexpr (FUSE) {
+        if (p.xflags) {
+            // exchange products: x may be the previous product's gathered y — wait (bounded) until every other rank
+            // has completed as many exchange products as this rank; the weight copies above are already in flight
+            if ((int)threadIdx.x < p.xnranks - 1) {
+                const int src = (int)threadIdx.x < p.xrank ? (int)threadIdx.x : (int)threadIdx.x + 1;
+                const uint32_t want = *reinterpret_cast<volatile const uint32_t *>(p.xflags + XF_EPOCH);
+                bool seen = false;
+                for (uint32_t it = 0; it < p.spins && !seen; it++) {
+                    uint32_t v;
+                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p.xflags + XF_FLAGS + src) : "memory");
+                    seen = (int32_t)(v - want) >= 0;
+                    if (!seen && it > 64) __nanosleep(100);
+                }
+                if (!seen) atomicExch(p.status, 32);
+            }
+            __syncthreads();
+        }
+        const int nsl = min(n, p.fuse_slices);
+        int kb = b, par = 0;
+        for (int i = 0; i < nsl; i++) {
+            stage_slice_in_cta(p.x, p.x_up, p.xst, p.xsk, p.K, p.m, kb, smem + (slices_s - smem_s) + (size_t)i * xbytes, wmax_s, wbad_s, par);
+            if (++kb == nk) kb = 0;
+        }
+    } else if (threadIdx.x == 0) {
         int bb = b;
 #pragma unroll
         for (int s = 0; s < GEMV_STAGES; s++) {
@@ -579,12 +668,15 @@ __global__ void __launch_bounds__(256) gemv_kernel(const __grid_constant__ GemvP
     for (int nt = 0; nt < NT; nt++) {
         const int col = nt * 8 + g, tok = nt * 4 + t;
         const bool act = col < 2 * p.m;
-        xstride[nt] = act ? stage_bytes : 0u;
-        xb0[nt] = act ? smem_s + SUPER + col * 288 + 8 * t : zero_s;
-        sb0[nt] = act ? smem_s + SUPER + (2 * p.m) * 288 + col * 16 : zero_s;
-        xsstride[nt] = (tok < p.m) ? stage_bytes : 0u;
-        xs0[nt] = (tok < p.m) ? smem_s + SUPER + (2 * p.m) * 304 + tok * 4 : zero_s;
+        // image path: the slice travels with its stage; fused path: slice i of the CTA's own area belongs to step i
+        const uint32_t xbase = FUSE ? slices_s : smem_s + SUPER, xstep = FUSE ? xbytes : stage_bytes;
+        xstride[nt] = act ? xstep : 0u;
+        xb0[nt] = act ? xbase + col * 288 + 8 * t : zero_s;
+        sb0[nt] = act ? xbase + (2 * p.m) * 288 + col * 16 : zero_s;
+        xsstride[nt] = (tok < p.m) ? xstep : 0u;
+        xs0[nt] = (tok < p.m) ? xbase + (2 * p.m) * 304 + tok * 4 : zero_s;
     }
+    int sl = 0;  // FUSE: slice of step i
     int st = 0;                // stage of step i
     uint32_t ph = 0;           // its parity
     int bx = b + GEMV_STAGES;  // k-step of the next activation slice to request
@@ -611,7 +703,7 @@ __global__ void __launch_bounds__(256) gemv_kernel(const __grid_constant__ GemvP
                     bulk_g2s(smem_s + ps * stage_bytes, wsrc + (size_t)(i - 1 + GEMV_STAGES) * WDATA, WDATA, full + 8 * ps);
                     if constexpr (SFB != 0)
                         bulk_g2s(smem_s + ps * stage_bytes + WDATA, sfsrc + (size_t)(i - 1 + GEMV_STAGES) * SFB, SFB, full + 8 * ps);
-                    bulk_g2s(smem_s + ps * stage_bytes + SUPER, p.img + (size_t)bx * xbytes, xbytes, full + 8 * ps);
+                    if constexpr (!FUSE) bulk_g2s(smem_s + ps * stage_bytes + SUPER, p.img + (size_t)bx * xbytes, xbytes, full + 8 * ps);
                 }
                 if (++bx == nk) bx = 0;
             }
@@ -622,11 +714,13 @@ __global__ void __launch_bounds__(256) gemv_kernel(const __grid_constant__ GemvP
             uint32_t xb[NT], sb[NT];
             float xs[NT];
 #pragma unroll
+            const int xi = FUSE ? sl : st;
             for (int nt = 0; nt < NT; nt++) {
-                xb[nt] = xb0[nt] + st * xstride[nt];
-                sb[nt] = sb0[nt] + st * xstride[nt];
-                xs[nt] = __uint_as_float(lds32(xs0[nt] + st * xsstride[nt]));
+                xb[nt] = xb0[nt] + xi * xstride[nt];
+                sb[nt] = sb0[nt] + xi * xstride[nt];
+                xs[nt] = __uint_as_float(lds32(xs0[nt] + xi * xsstride[nt]));
             }
+            if (FUSE && ++sl == p.fuse_slices) sl = 0;
             const uint32_t ch = smem_s + st * stage_bytes + warp * CHUNK;
             if constexpr (FMT == FMT_Q4K) q4k_chunk<NT>(ch, lane, xb, sb, xs, tot);
             else if constexpr (FMT == FMT_Q80) q80_chunk<NT>(ch, lane, xb, xs, tot);
@@ -705,19 +799,65 @@ static cudaError_t gemv_occupancy(int device, int m, size_t smem, int *per_sm) {
     return cudaSuccess;
 }
 
+// Fused staging pays when a CTA's share is a handful of k-steps (small matrices, row shards of a few thousand
+// rows): the staging kernel's launch and the hand-over between the two grids then cost more than converting
+// fuse_slices x m slices of 256 activations in every CTA.
+constexpr int GEMV_FUSE_MAX_WORK = 20;  // slices x tokens a CTA converts itself at most
+
+// Grid of a decode launch: resident CTAs, each with a contiguous share of the super-chunk sequence.
+struct GemvGrid {
+    int per_sm;
+    int64_t ctas;
+    int per_cta, rem;
+};
 template <int FMT, int NT>
-static cudaError_t configure_and_launch(Ctx *c, GemvParams &p, int64_t ntg, cudaStream_t s, int32_t *rc_out) {
-    const size_t smem = gemv_smem_bytes<FMT>(p.m);
-    int per_sm = 0;
-    cudaError_t e = gemv_occupancy<FMT, NT>(c->device, p.m, smem, &per_sm);
+static cudaError_t gemv_grid(Ctx *c, int m, int64_t nsuper, GemvGrid *g) {
+    cudaError_t e = gemv_occupancy<FMT, NT>(c->device, m, gemv_smem_bytes<FMT>(m), &g->per_sm);
     if (e != cudaSuccess) return e;
-    if (c->gemv_ctas_per_sm > 0 && c->gemv_ctas_per_sm < per_sm) per_sm = (int)c->gemv_ctas_per_sm;
+    if (c->gemv_ctas_per_sm > 0 && c->gemv_ctas_per_sm < g->per_sm) g->per_sm = (int)c->gemv_ctas_per_sm;
+    g->ctas = (int64_t)c->sm_count * g->per_sm;
+    if (g->ctas > nsuper) g->ctas = nsuper;
+    g->per_cta = (int)(nsuper / g->ctas);
+    g->rem = (int)(nsuper % g->ctas);
+    return cudaSuccess;
+}
+
+// Slices a CTA would stage itself (0 = use the staging kernel and its image): few enough, and the fused variant
+// must keep as many CTAs resident as the image variant.
+template <int FMT>
+static cudaError_t gemv_fuse_plan(Ctx *c, int m, int64_t ntg, int nk, int *slices) {
+    *slices = 0;
+    if (!c->gemv_fuse || m > 4) return cudaSuccess;
+    GemvGrid g;
+    cudaError_t e = gemv_grid<FMT, 1>(c, m, ntg * nk, &g);
+    if (e != cudaSuccess) return e;
+    const int share = g.per_cta + (g.rem ? 1 : 0);
+    const int nsl = share < nk ? share : nk;
+    if (nsl * m > GEMV_FUSE_MAX_WORK) return cudaSuccess;
+    static int occ[16][5][GEMV_FUSE_MAX_WORK + 1];  // [device][m][slices], 0 = not yet asked
+    const int dv = c->device & 15;
+    if (!occ[dv][m][nsl]) {
+        e = cudaFuncSetAttribute(gemv_kernel<FMT, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)gemv_smem_bytes_fused<FMT>(4, GEMV_FUSE_MAX_WORK));
+        if (e != cudaSuccess) return e;
+        int nb = 0;
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, gemv_kernel<FMT, 1, true>, 256, gemv_smem_bytes_fused<FMT>(m, nsl));
+        if (e != cudaSuccess) return e;
+        occ[dv][m][nsl] = nb < 1 ? -1 : nb;
+    }
+    if (occ[dv][m][nsl] >= g.per_sm) *slices = nsl;
+    return cudaSuccess;
+}
+
+template <int FMT, int NT>
+static cudaError_t configure_and_launch(Ctx *c, GemvParams &p, int64_t ntg, cudaStream_t s, int32_t *rc_out, int fuse_slices) {
     p.nsuper = ntg * p.nk;
-    int64_t ctas = (int64_t)c->sm_count * per_sm;
-    if (ctas > p.nsuper) ctas = p.nsuper;
-    p.per_cta = (int)(p.nsuper / ctas);
-    p.rem = (int)(p.nsuper % ctas);
-    const unsigned grid = (unsigned)ctas;
+    GemvGrid g;
+    cudaError_t e = gemv_grid<FMT, NT>(c, p.m, p.nsuper, &g);
+    if (e != cudaSuccess) return e;
+    p.per_cta = g.per_cta;
+    p.rem = g.rem;
+    const unsigned grid = (unsigned)g.ctas;
     p.maxslot = (p.nk - 1) / p.per_cta + 2;
     const int64_t tiles = ntg * 8;
     const size_t part_bytes = align_up((size_t)tiles * p.maxslot * 256 * sizeof(float), 256);
@@ -727,7 +867,13 @@ static cudaError_t configure_and_launch(Ctx *c, GemvParams &p, int64_t ntg, cuda
     p.partial = static_cast<float *>(c->red);
     p.counters = static_cast<int *>(c->cnt);
     p.ntiles = (int)tiles;
-    return launch_pdl(gemv_kernel<FMT, NT>, grid, 256, smem, s, c->gemv_pdl != 0, p);
+    if constexpr (NT == 1 && (FMT == FMT_Q4K || FMT == FMT_Q80)) {
+        if (fuse_slices > 0) {
+            p.fuse_slices = fuse_slices;
+            return launch_pdl(gemv_kernel<FMT, NT, true>, grid, 256, gemv_smem_bytes_fused<FMT>(p.m, fuse_slices), s, c->gemv_pdl != 0, p);
+        }
+    }
+    return launch_pdl(gemv_kernel<FMT, NT>, grid, 256, gemv_smem_bytes<FMT>(p.m), s, c->gemv_pdl != 0, p);
 }
 
 int32_t gemv_launch(Ctx *c, const Weight *w, const float *x, int64_t xst, int64_t xsk, int m, float *y, int64_t yst,
@@ -769,6 +915,14 @@ int32_t gemv_launch(Ctx *c, const Weight *w, const float *x, int64_t xst, int64_
         p.xrank = xch->rank;
     }
 
+    p.x = x;
+    p.x_up = x_up;
+    p.xst = xst;
+    p.xsk = xsk;
+    p.K = w->k;
+    p.spins = (uint32_t)c->peer_wait_spins;
+    p.xnranks = xch ? xch->n_peers + 1 : 1;
+
     StageParams sp{x, x_up, xst, xsk, m, w->k, static_cast<uint8_t *>(c->ws)};
     if (p.xflags) {
         sp.xflags = xch->flags_local;
@@ -785,39 +939,43 @@ int32_t gemv_launch(Ctx *c, const Weight *w, const float *x, int64_t xst, int64_
         (void)cudaGetLastError();
         stage_carveout_set = true;
     }
-    GK_CUDA(c, launch_pdl(stage_x_kernel, sgrid, 256, 0, s, c->gemv_pdl != 0, sp));
-
     const int64_t ntg = w->n_pad / 128;
     const int NT = (2 * m + 7) / 8;
+    // Small shares: the GEMV converts its activation slices itself and the staging kernel is not launched at all.
+    int fuse = 0;
+    if (NT == 1 && w->qt == GLLMK_QUANT_Q4K) GK_CUDA(c, gemv_fuse_plan<FMT_Q4K>(c, m, ntg, nk, &fuse));
+    else if (NT == 1 && w->qt == GLLMK_QUANT_Q8_0) GK_CUDA(c, gemv_fuse_plan<FMT_Q80>(c, m, ntg, nk, &fuse));
+    if (!fuse) GK_CUDA(c, launch_pdl(stage_x_kernel, sgrid, 256, 0, s, c->gemv_pdl != 0, sp));
+
     cudaError_t e;
     rc = 0;
     if (w->qt == GLLMK_QUANT_Q4K) {
         switch (NT) {
-            case 1: e = configure_and_launch<FMT_Q4K, 1>(c, p, ntg, s, &rc); break;
-            case 2: e = configure_and_launch<FMT_Q4K, 2>(c, p, ntg, s, &rc); break;
-            case 3: e = configure_and_launch<FMT_Q4K, 3>(c, p, ntg, s, &rc); break;
-            default: e = configure_and_launch<FMT_Q4K, 4>(c, p, ntg, s, &rc); break;
+            case 1: e = configure_and_launch<FMT_Q4K, 1>(c, p, ntg, s, &rc, fuse); break;
+            case 2: e = configure_and_launch<FMT_Q4K, 2>(c, p, ntg, s, &rc, 0); break;
+            case 3: e = configure_and_launch<FMT_Q4K, 3>(c, p, ntg, s, &rc, 0); break;
+            default: e = configure_and_launch<FMT_Q4K, 4>(c, p, ntg, s, &rc, 0); break;
         }
     } else if (w->qt == GLLMK_QUANT_Q8_0) {
         switch (NT) {
-            case 1: e = configure_and_launch<FMT_Q80, 1>(c, p, ntg, s, &rc); break;
-            case 2: e = configure_and_launch<FMT_Q80, 2>(c, p, ntg, s, &rc); break;
-            case 3: e = configure_and_launch<FMT_Q80, 3>(c, p, ntg, s, &rc); break;
-            default: e = configure_and_launch<FMT_Q80, 4>(c, p, ntg, s, &rc); break;
+            case 1: e = configure_and_launch<FMT_Q80, 1>(c, p, ntg, s, &rc, fuse); break;
+            case 2: e = configure_and_launch<FMT_Q80, 2>(c, p, ntg, s, &rc, 0); break;
+            case 3: e = configure_and_launch<FMT_Q80, 3>(c, p, ntg, s, &rc, 0); break;
+            default: e = configure_and_launch<FMT_Q80, 4>(c, p, ntg, s, &rc, 0); break;
         }
     } else if (w->qt == GLLMK_QUANT_MXFP4) {
         switch (NT) {
-            case 1: e = configure_and_launch<FMT_MXFP4, 1>(c, p, ntg, s, &rc); break;
-            case 2: e = configure_and_launch<FMT_MXFP4, 2>(c, p, ntg, s, &rc); break;
-            case 3: e = configure_and_launch<FMT_MXFP4, 3>(c, p, ntg, s, &rc); break;
-            default: e = configure_and_launch<FMT_MXFP4, 4>(c, p, ntg, s, &rc); break;
+            case 1: e = configure_and_launch<FMT_MXFP4, 1>(c, p, ntg, s, &rc, 0); break;
+            case 2: e = configure_and_launch<FMT_MXFP4, 2>(c, p, ntg, s, &rc, 0); break;
+            case 3: e = configure_and_launch<FMT_MXFP4, 3>(c, p, ntg, s, &rc, 0); break;
+            default: e = configure_and_launch<FMT_MXFP4, 4>(c, p, ntg, s, &rc, 0); break;
         }
     } else {
         switch (NT) {
-            case 1: e = configure_and_launch<FMT_NVFP4, 1>(c, p, ntg, s, &rc); break;
-            case 2: e = configure_and_launch<FMT_NVFP4, 2>(c, p, ntg, s, &rc); break;
-            case 3: e = configure_and_launch<FMT_NVFP4, 3>(c, p, ntg, s, &rc); break;
-            default: e = configure_and_launch<FMT_NVFP4, 4>(c, p, ntg, s, &rc); break;
+            case 1: e = configure_and_launch<FMT_NVFP4, 1>(c, p, ntg, s, &rc, 0); break;
+            case 2: e = configure_and_launch<FMT_NVFP4, 2>(c, p, ntg, s, &rc, 0); break;
+            case 3: e = configure_and_launch<FMT_NVFP4, 3>(c, p, ntg, s, &rc, 0); break;
+            default: e = configure_and_launch<FMT_NVFP4, 4>(c, p, ntg, s, &rc, 0); break;
         }
     }
     if (rc) return rc;

@@ -162,6 +162,63 @@ def test_gemm_fp4_mxfp4(gk, K, oracle, n, k, m):
     assert run_fp4_case(gk, K, oracle, "mxfp4", n, k, m, seed=n + m) <= 2e-3
 
 
+@pytest.mark.parametrize("fmt,n,k,m", [("nvfp4", 256, 256, 256), ("nvfp4", 128, 512, 300), ("nvfp4", 384, 1024, 129), ("nvfp4", 640, 768, 513),
+                                       ("nvfp4", 1100, 2560, 777), ("mxfp4", 256, 512, 256), ("mxfp4", 900, 1280, 600)])
+def test_gemm_fp4_cta_pair_kernel(gk, K, oracle, fmt, n, k, m):
+    """m > 128 runs on the persistent CTA-pair kernel: an odd number of 128-row groups (the pair's second CTA has no rows),
+    token counts that leave the second half of a tile empty or ragged, more k-steps than pipeline stages, several
+    tiles per pair — against the oracle, and bit-identical with the one-CTA kernel (the same products, accumulated in
+    the same k order)."""
+    K.set("gemm_fp4_pair", 1)
+    assert run_fp4_case(gk, K, oracle, fmt, n, k, m, seed=n + m) <= 2e-3
+    import torch
+    rng = np.random.default_rng(n * m)
+    W = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    X = rng.standard_normal((m, k)).astype(np.float32)
+    if fmt == "nvfp4":
+        qt = gk.QuantType.nvfp4()
+        (wb, gw), (xb, gx) = oracle.quantize_nvfp4(W), oracle.quantize_nvfp4(X)
+        w, x = K.upload(qt, n, k, wb, None, gw), K.upload(qt, m, k, xb, None, gx)
+    else:
+        qt = gk.QuantType.mxfp4(32)
+        (wb, ws), (xb, xs) = oracle.quantize_mxfp4(W), oracle.quantize_mxfp4(X)
+        w, x = K.upload(qt, n, k, wb, ws), K.upload(qt, m, k, xb, xs)
+    y_pair = K.gemm_fp4(w, x, out_dtype=torch.bfloat16).clone()
+    K.set("gemm_fp4_pair", 0)
+    try:
+        y_one = K.gemm_fp4(w, x, out_dtype=torch.bfloat16)
+    finally:
+        K.set("gemm_fp4_pair", 1)
+    torch.cuda.synchronize()
+    assert K.status() == 0
+    assert torch.equal(y_pair, y_one)
+    w.free()
+    x.free()
+
+
+def test_gemm_fp4_cta_pair_kernel_many_tiles(gk, K, oracle):
+    """More tiles than resident pairs: every pair walks several tiles, the accumulator hand-over between the MMA
+    thread and the sixteen epilogue warps of a pair is exercised over many rounds."""
+    import torch
+    n, k, m = 6144, 512, 2048  # 24 row pairs x 8 token tiles = 192 tiles on 74 pairs
+    qt = gk.QuantType.nvfp4()
+    g = torch.Generator(device="cuda").manual_seed(5)
+    W = torch.randn((n, k), generator=g, device="cuda") * 0.02
+    X = torch.randn((m, k), generator=g, device="cuda")
+    wb, gw = K.quantize(qt, W)
+    xb, gx = K.quantize(qt, X)
+    w, x = K.upload(qt, n, k, wb, None, gw), K.upload(qt, m, k, xb, None, gx)
+    y = K.gemm_fp4(w, x)
+    torch.cuda.synchronize()
+    assert K.status() == 0
+    wd = oracle.dequant_matrix(oracle.NVFP4, wb.cpu().numpy(), n, k, global_scale=gw)
+    xd = oracle.dequant_matrix(oracle.NVFP4, xb.cpu().numpy(), m, k, global_scale=gx)
+    rows = np.r_[0:64, 3000:3064, n - 64:n]
+    assert oracle.rel_err(y.cpu().numpy()[:, rows], oracle.gemm_f32_nt(xd, wd[rows])) <= 2e-3
+    w.free()
+    x.free()
+
+
 # ---- FP4 weights on the decode kernel, and host batches that land on the tensor-core kernel -------------
 @pytest.mark.parametrize("fmt", ["mxfp4", "nvfp4"])
 @pytest.mark.parametrize("n,k", [(200, 384), (128, 256), (1000, 2048)])

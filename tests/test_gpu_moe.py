@@ -46,7 +46,10 @@ def test_topk_route_gather_weighted_sum_bit_exact(gk, K, oracle, T, E, top_k):
     routing = K.moe_topk(probs_d, top_k)
     ref = oracle.scalar_topk(probs, top_k)
     got = routing.cpu().numpy()
-    assert np.array_equal(got.view(np.uint32), ref.view(np.uint32))
+    # (a row with fewer selectable experts than top_k has -inf entries left: its weights are NaN on both sides, whose
+    # bit patterns differ between the CPU and the GPU)
+    same = (got.view(np.uint32) == ref.view(np.uint32)) | (np.isnan(got) & np.isnan(ref))
+    assert same.all()
     offs, perm, inv = K.moe_route(routing, T, E, top_k)
     idx = ref[0].view(np.uint32)
     counts = np.bincount(idx, minlength=E)

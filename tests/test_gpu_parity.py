@@ -418,3 +418,28 @@ def test_matmul_host_with_page_locked_buffers(gk, K, oracle, torch):
     assert np.array_equal(y_pinned, y_plain) and np.array_equal(yp.numpy(), y_plain)
     assert oracle.rel_err(y_plain, oracle.gemm_q4(blocks, x, None, 2, 512, 1024)) <= TOL
     w.free()
+
+
+# ---- small shares: the GEMV stages its activation slices itself (no staging launch) ---------------------------
+@pytest.mark.parametrize("fmt,n,k,m", [("q4k", 4096, 4096, 1), ("q4k", 1024, 28672, 1), ("q4k", 7168, 8192, 1), ("q4k", 300, 1280, 3),
+                                       ("q4k", 16, 256, 4), ("q8_0", 11008, 4096, 1), ("q8_0", 129, 4000, 2)])
+def test_gemv_fused_staging_equals_the_staging_kernel(gk, K, oracle, torch, fmt, n, k, m):
+    """Both variants do the same arithmetic on the same partition of the work: bit-identical outputs; and the
+    oracle bar on top."""
+    oid, blocks, _, _ = make(oracle, fmt, n, k, seed=n + k)
+    w = K.upload(qt_of(gk, fmt), n, k, blocks)
+    x = torch.from_numpy(np.random.default_rng(n).standard_normal((m, k)).astype(np.float32)).cuda()
+    K.set("gemv_fuse", 0)
+    try:
+        y_img = K.gemv(w, x).clone()
+    finally:
+        K.set("gemv_fuse", 1)
+    y_fused = K.gemv(w, x)
+    assert K.status() == 0
+    assert torch.equal(y_img, y_fused)
+    ref = oracle.quant_matmul(blocks, np.ascontiguousarray(x.cpu().numpy().T), oid, n, m, k, threads=8).T
+    assert oracle.rel_err(y_fused.cpu().numpy(), ref) <= TOL
+    # strided x (the reference's [k, m] layout) goes through the same fused path
+    y_ref_layout = K.gemv(w, x.t().contiguous(), ref_layout=True)
+    assert torch.equal(y_ref_layout.t().contiguous(), y_fused)
+    w.free()
