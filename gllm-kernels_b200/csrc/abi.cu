@@ -266,6 +266,7 @@ int32_t gllmk_ctx_set(gllmk_ctx ctx, const char *key, int64_t value) {
     else if (!strcmp(key, "gemv_fp4_int")) c->gemv_fp4_int = value;
     else if (!strcmp(key, "gemm_fp4_pair")) c->gemm_fp4_pair = value;
     else if (!strcmp(key, "gemv_fuse")) c->gemv_fuse = value;
+    else if (!strcmp(key, "gemm_tail_split")) c->gemm_tail_split = value;
     else if (!strcmp(key, "peer_wait_spins")) {
         if (value < 1 || value > ((int64_t)1 << 30)) return fail(c, GLLMK_STATUS_INVALID_ARG, "peer_wait_spins outside 1..2^30");
         c->peer_wait_spins = value;

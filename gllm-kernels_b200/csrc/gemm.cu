@@ -73,6 +73,12 @@ struct GemmParams {
     int row_tiles;       // 128-row tiles of the weight matrix
     int sb, r;           // ring depths: B stages, raw super-chunks
     int *status;
+    // Tail split (split_s > 1; the grid is then one-dimensional): units [0, split_f) are whole tiles, in the order
+    // tile = token tile + ntt * row group; every later tile is cut along k into split_s units whose f32 partial
+    // accumulators meet in `partial`, added up in unit order by whichever unit of the tile finishes last.
+    int split_f, split_s, ntt;
+    float *partial;      // [tail tile][split][row tile of the CTA][token][128 rows]
+    int *tail_cnt;       // [tail tile] arrivals, zero between launches
 };
 
 // ---- activations -> fp16 tile images ------------------------------------------------------------
@@ -295,11 +301,27 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
                    emptyB = fullB + 8 * WQ_MAX_SB, rawfull = emptyB + 8 * WQ_MAX_SB, rawempty = rawfull + 8 * WQ_MAX_R,
                    accum = rawempty + 8 * WQ_MAX_R;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile0 = blockIdx.y * MT;
+    // which tile, and which part of its k range
+    int bx = blockIdx.x, by = blockIdx.y, jb0 = 0, njb = p.nsc, split = 0, nsplit = 1, tail_tile = 0;
+    if (p.split_s > 1) {
+        const int u = (int)blockIdx.x;
+        int t = u;
+        if (u >= p.split_f) {
+            tail_tile = (u - p.split_f) / p.split_s;
+            split = (u - p.split_f) % p.split_s;
+            nsplit = p.split_s;
+            t = p.split_f + tail_tile;
+            jb0 = (int)((int64_t)p.nsc * split / nsplit);
+            njb = (int)((int64_t)p.nsc * (split + 1) / nsplit) - jb0;
+        }
+        bx = t % p.ntt;
+        by = t / p.ntt;
+    }
+    const int tile0 = by * MT;
     const int mt = min(MT, p.row_tiles - tile0);  // row tiles this CTA really has
-    const int grp_id = G.tile_group[blockIdx.x];
-    const int64_t tok0 = G.tile_tok0[blockIdx.x], tok_end = tok0 + G.tile_cnt[blockIdx.x];
-    const int nks = 4 * p.nsc;
+    const int grp_id = G.tile_group[bx];
+    const int64_t tok0 = G.tile_tok0[bx], tok_end = tok0 + G.tile_cnt[bx];
+    const int nks = 4 * njb, nks_row = 4 * p.nsc;  // k-steps of this unit / of a whole row
     volatile int *abort_flag = &abort_s;
 
     if (threadIdx.x == 0) {
@@ -329,12 +351,13 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
         // ---------------- raw weight super-chunks: one thread, bulk copies ----------------
         if (lane == 0) {
             int slot = 0, round = 0;
-            for (int jb = 0; jb < p.nsc; jb++) {
+            for (int jl = 0; jl < njb; jl++) {
+                const int jb = jb0 + jl;
                 for (int ti = 0; ti < mt; ti++) {
                     if (round > 0 && !tc::mbar_wait(rawempty + 8 * slot, (uint32_t)((round - 1) & 1), abort_flag)) {
                         abort_s = 1;
                         atomicExch(p.status, 10);
-                        jb = p.nsc;
+                        jl = njb;
                         break;
                     }
                     const int tile = tile0 + ti;
@@ -356,7 +379,7 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
         // ---------------- activation tiles: one thread, bulk copies ----------------
         if (lane == 0) {
             // a tile of more than 128 tokens is two activation images: a whole one and the first ntok - 128 rows
-            const int halves = (p.ntok + 127) / 128, img0 = G.tile_img[blockIdx.x];
+            const int halves = (p.ntok + 127) / 128, img0 = G.tile_img[bx];
             const uint32_t hbytes[2] = {(uint32_t)(p.ntok > 128 ? WQ_TILE : bstage), (uint32_t)(bstage - WQ_TILE)};
             int slot = 0, round = 0;
             for (int ks = 0; ks < nks; ks++) {
@@ -368,7 +391,7 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
                 const uint32_t dst = smem_s + b_off + (uint32_t)(slot * bstage);
                 tc::mbar_expect_tx(fullB + 8 * slot, (uint32_t)bstage);
                 for (int h = 0; h < halves; h++)
-                    bulk_g2s(dst + h * WQ_TILE, p.xt + ((size_t)(img0 + h) * nks + ks) * WQ_TILE, hbytes[h], fullB + 8 * slot);
+                    bulk_g2s(dst + h * WQ_TILE, p.xt + ((size_t)(img0 + h) * nks_row + 4 * jb0 + ks) * WQ_TILE, hbytes[h], fullB + 8 * slot);
                 if (++slot == p.sb) slot = 0, round++;
             }
         }
@@ -453,17 +476,61 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
             const int quad = warp & 3;
             // all MMAs have completed, so the rings are free: each warp stages its blocks in 4 KB of the A ring
             uint8_t *stage = smem + a_off + dw * 4096;
-            for (int i = 0; i < mt; i++) {
-                const int64_t row_base = (int64_t)(tile0 + i) * WQ_BM + 32 * quad;
-                for (int c = 32 * (dw >> 2); c < p.ntok; c += 32 * (WQ_DW / 4)) {
-                    uint32_t v[32];
-                    tc::tmem_ld32(tmem_d + ((uint32_t)(32 * quad) << 16) + 256u * (uint32_t)i + (uint32_t)c, v);
-                    tc::tmem_ld_wait();
-                    float o[32];
+            if (nsplit == 1) {
+                for (int i = 0; i < mt; i++) {
+                    const int64_t row_base = (int64_t)(tile0 + i) * WQ_BM + 32 * quad;
+                    for (int c = 32 * (dw >> 2); c < p.ntok; c += 32 * (WQ_DW / 4)) {
+                        uint32_t v[32];
+                        tc::tmem_ld32(tmem_d + ((uint32_t)(32 * quad) << 16) + 256u * (uint32_t)i + (uint32_t)c, v);
+                        tc::tmem_ld_wait();
+                        float o[32];
 #pragma unroll
-                    for (int jj = 0; jj < 32; jj++) o[jj] = __uint_as_float(v[jj]);
-                    if (p.y_bf16) tc::store_block_32x32<true>(p.y, p.ldy, row_base, tok0 + c, p.n, tok_end, o, stage, lane, p.vec);
-                    else tc::store_block_32x32<false>(p.y, p.ldy, row_base, tok0 + c, p.n, tok_end, o, stage, lane, p.vec);
+                        for (int jj = 0; jj < 32; jj++) o[jj] = __uint_as_float(v[jj]);
+                        if (p.y_bf16) tc::store_block_32x32<true>(p.y, p.ldy, row_base, tok0 + c, p.n, tok_end, o, stage, lane, p.vec);
+                        else tc::store_block_32x32<false>(p.y, p.ldy, row_base, tok0 + c, p.n, tok_end, o, stage, lane, p.vec);
+                    }
+                }
+            } else {
+                // A unit of a split tile: the accumulator goes to this unit's partial area ([row tile][token][128 rows]
+                // f32), and the unit that arrives last at the tile's counter adds the partials in unit order — the
+                // result does not depend on which one that is — and stores y.
+                const size_t unit_floats = (size_t)MT * p.ntok * WQ_BM;
+                float *tile_part = p.partial + (size_t)tail_tile * nsplit * unit_floats, *mine = tile_part + (size_t)split * unit_floats;
+                for (int i = 0; i < mt; i++)
+                    for (int c = 32 * (dw >> 2); c < p.ntok; c += 32 * (WQ_DW / 4)) {
+                        uint32_t v[32];
+                        tc::tmem_ld32(tmem_d + ((uint32_t)(32 * quad) << 16) + 256u * (uint32_t)i + (uint32_t)c, v);
+                        tc::tmem_ld_wait();
+                        float *dst = mine + ((size_t)i * p.ntok + c) * WQ_BM + 32 * quad + lane;
+#pragma unroll
+                        for (int jj = 0; jj < 32; jj++) __stcg(dst + (size_t)jj * WQ_BM, __uint_as_float(v[jj]));  // lanes: 32 consecutive rows
+                    }
+                __threadfence();
+                tc::named_bar_sync(6, 32 * WQ_DW);  // every dequant / epilogue warp has written and fenced
+                __shared__ int last_s;
+                if (dw == 0 && lane == 0) {
+                    const int old = atomicAdd(p.tail_cnt + tail_tile, 1);
+                    last_s = (old == nsplit - 1);
+                    if (last_s) p.tail_cnt[tail_tile] = 0;  // ready for the next launch
+                    __threadfence();
+                }
+                tc::named_bar_sync(6, 32 * WQ_DW);
+                if (last_s) {
+                    for (int i = 0; i < mt; i++) {
+                        const int64_t row_base = (int64_t)(tile0 + i) * WQ_BM + 32 * quad;
+                        for (int c = 32 * (dw >> 2); c < p.ntok; c += 32 * (WQ_DW / 4)) {
+                            float o[32];
+#pragma unroll
+                            for (int jj = 0; jj < 32; jj++) o[jj] = 0.0f;
+                            for (int sp = 0; sp < nsplit; sp++) {
+                                const float *src = tile_part + (size_t)sp * unit_floats + ((size_t)i * p.ntok + c) * WQ_BM + 32 * quad + lane;
+#pragma unroll
+                                for (int jj = 0; jj < 32; jj++) o[jj] += __ldcg(src + (size_t)jj * WQ_BM);
+                            }
+                            if (p.y_bf16) tc::store_block_32x32<true>(p.y, p.ldy, row_base, tok0 + c, p.n, tok_end, o, stage, lane, p.vec);
+                            else tc::store_block_32x32<false>(p.y, p.ldy, row_base, tok0 + c, p.n, tok_end, o, stage, lane, p.vec);
+                        }
+                    }
                 }
             }
         } else if (!abort_s) {
@@ -571,6 +638,36 @@ static int32_t gemm_groups_chunk(Ctx *c, const Weight *const *ws, int ng, const 
     stage_act_kernel<<<dim3((unsigned)nks, (unsigned)nimg), 256, 0, s>>>(a, a_bf16, lda, w->k, static_cast<uint8_t *>(c->act), imgs);
     GK_CUDA(c, cudaGetLastError());
     dim3 grid((unsigned)ntiles, (unsigned)((row_tiles + mt - 1) / mt));
+    // Tail split: with more tiles than SMs the last, partly filled wave of tiles is cut along k so that its work
+    // spreads over all SMs (224 tiles on 148 SMs: 148 whole tiles, then 76 tiles in thirds = 228 units in two short
+    // waves — 1.67 tile times instead of 2).  Only when the weights are one group (a plain GEMM) and a unit keeps at
+    // least four k-blocks.
+    p.split_s = 1;
+    if (ng == 1 && c->gemm_tail_split != 1) {
+        const int tiles = (int)(grid.x * grid.y), sms = c->sm_count;
+        const int full = tiles / sms * sms, tail = tiles - full;
+        if (full > 0 && tail > 0) {
+            int best_s = 1;
+            double best = 1.0;  // tail time in tile times, unsplit
+            for (int sp = 2; sp <= 8 && p.nsc / sp >= 4; sp++) {
+                const double t = (double)((tail * sp + sms - 1) / sms) / sp + 0.05 * sp;  // + fill / drain and the partial traffic
+                if (t < best) best = t, best_s = sp;
+            }
+            if (c->gemm_tail_split > 1 && p.nsc / (int)c->gemm_tail_split >= 1) best_s = (int)c->gemm_tail_split;
+            if (best_s > 1) {
+                const size_t unit_floats = (size_t)mt * ntok * WQ_BM;
+                rc = ensure_red(c, (size_t)tail * best_s * unit_floats * sizeof(float));
+                if (!rc) rc = ensure_cnt(c, (size_t)(tail + 1) * sizeof(int));
+                if (rc) return rc;
+                p.split_s = best_s;
+                p.split_f = full;
+                p.ntt = (int)grid.x;
+                p.partial = static_cast<float *>(c->red);
+                p.tail_cnt = static_cast<int *>(c->cnt);
+                grid = dim3((unsigned)(full + tail * best_s), 1u);
+            }
+        }
+    }
     switch (fmt) {
         case FMT_Q4K: return launch_wq_mt<FMT_Q4K>(c, p, G, mt, grid, smem, s);
         case FMT_Q80: return launch_wq_mt<FMT_Q80>(c, p, G, mt, grid, smem, s);

@@ -713,8 +713,8 @@ __global__ void __launch_bounds__(256) gemv_kernel(const __grid_constant__ GemvP
             }
             uint32_t xb[NT], sb[NT];
             float xs[NT];
-#pragma unroll
             const int xi = FUSE ? sl : st;
+#pragma unroll
             for (int nt = 0; nt < NT; nt++) {
                 xb[nt] = xb0[nt] + xi * xstride[nt];
                 sb[nt] = sb0[nt] + xi * xstride[nt];

@@ -82,3 +82,24 @@ def test_e8m0_and_lut_mirror(gk, oracle):
         a, r = gk.decode_e8m0_scale(b), oracle.lib().gko_decode_e8m0_scale(b)
         assert (np.isnan(a) and np.isnan(r)) or a == r
     assert [oracle.lib().gko_e2m1(i) for i in range(16)] == list(gk.E2M1_LUT_F32)
+
+
+def test_rust_shim_declares_every_entry_point(gk):
+    """gllm-kernels_b200/rust/gpu_b200.rs is shipped uncompiled (no Rust toolchain here): at least its extern block must
+    name exactly the functions include/gllmk.h declares, and the header must declare what the binding binds."""
+    import os
+    import re
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    rs = open(os.path.join(root, "gllm-kernels_b200", "rust", "gpu_b200.rs")).read()
+    ext = rs[rs.index('extern "C" {'):]
+    ext = ext[:ext.index("\n}\n")]
+    rust_syms = set(re.findall(r"fn (gllmk_\w+)\(", ext))
+    header = open(os.path.join(root, "include", "gllmk.h")).read()
+    header_syms = set(re.findall(r"GLLMK_API [\w \*]+?\b(gllmk_\w+)\(", header))
+    assert header_syms == set(_lib_syms(gk)), (header_syms ^ set(_lib_syms(gk)))
+    assert rust_syms == header_syms, (rust_syms ^ header_syms)
+
+
+def _lib_syms(gk):
+    import importlib
+    return importlib.import_module("gllm-kernels_b200._lib").exported_symbols()

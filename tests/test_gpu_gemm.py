@@ -114,6 +114,35 @@ def test_gemm_fp4_weights_ragged_k(gk, K, oracle):
     assert run_case(gk, K, oracle, "nvfp4", 128, 192, 64, seed=17, a_bf16=True) <= 1e-2
 
 
+@pytest.mark.parametrize("fmt,n,k,m,split", [("q8_0", 19072, 2048, 64, 3), ("q4k", 38400, 1024, 300, 2), ("q4k", 19072, 2048, 200, 0),
+                                             ("nvfp4", 19072, 1280, 96, 5)])
+def test_gemm_tail_tiles_split_along_k(gk, K, oracle, fmt, n, k, m, split):
+    """More tiles than SMs: the tiles of the last, partly filled wave are cut along k into units whose partial
+    accumulators are added by the last unit to finish.  Forced split counts and the automatic choice, against the
+    oracle and against the unsplit launch (same products, another summation order: f32 rounding apart)."""
+    import torch
+    qt, blocks, scales, g, wd = quantized(oracle, gk, fmt, n, k, seed=n % 977 + m)
+    w = K.upload(qt, n, k, blocks, scales, g)
+    x = torch.from_numpy(np.random.default_rng(m).standard_normal((m, k)).astype(np.float32)).cuda().to(torch.bfloat16)
+    K.set("gemm_tail_split", 1)
+    try:
+        y_whole = K.gemm(w, x).clone()
+        K.set("gemm_tail_split", split)
+        y_split = K.gemm(w, x).clone()
+        y_again = K.gemm(w, x)  # the arrival counters reset themselves; and the sum order is fixed: bit-identical
+    finally:
+        K.set("gemm_tail_split", 0)
+    torch.cuda.synchronize()
+    assert K.status() == 0
+    assert torch.equal(y_split, y_again)
+    scale = y_whole.abs().max().item()
+    assert (y_split - y_whole).abs().max().item() <= 1e-5 * scale
+    rows = np.r_[0:64, n // 2:n // 2 + 64, n - 64:n]  # the split tiles are the last ones
+    ref = oracle.gemm_f32_nt(x.to(torch.float32).cpu().numpy(), wd[rows])
+    assert oracle.rel_err(y_split.cpu().numpy()[:, rows], ref) <= TOL
+    w.free()
+
+
 # ---- both operands FP4: native block-scaled MMA ---------------------------------------------------
 def run_fp4_case(gk, K, oracle, fmt, n, k, m, seed):
     import torch
