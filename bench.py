@@ -728,8 +728,10 @@ def extra_gemm(K, gk, torch, dev, gen):
     us = timeit(lambda: K.gemm_fp4(w, x, y=y), 20)
     a_host = O.dequant_matrix(O.NVFP4, xb.cpu().numpy(), m, k, global_scale=gx)
     rows = sample_rows(n, 256, seed=4)
+    ceil_tf = K.probe_fp4_mma(True, True)
     res["cfg4_nvfp4_14336x4096_M2048"] = {"us": us, "tflops": 2.0 * m * n * k / us / 1e6, "frac_of_nominal_fp4_9000": 2.0 * m * n * k / us / 1e6 / 9000.0,
-                                          "mma": "tcgen05 kind::mxf4nvf4 block_scale",
+                                          "measured_mma_ceiling_tflops": ceil_tf, "frac_of_measured_mma_ceiling": 2.0 * m * n * k / us / 1e6 / ceil_tf,
+                                          "mma": "tcgen05 kind::mxf4nvf4 block_scale, cta_group::2",
                                           "parity": sampled_parity(O, O.NVFP4, packed[0], n, k, rows, a_host, y, bar=2e-3 + 2.0 ** -9,
                                                                    global_scale=packed[2]),
                                           "cpu_baseline": cpu_baseline_rows(O, O.NVFP4, packed, n, k, rows[:32], a_host, w.ref_bytes)}
@@ -884,7 +886,7 @@ def run_prefill_case(args):
         w, x = K.upload(QT.nvfp4(), n, k, wb, None, gw), K.upload(QT.nvfp4(), m, k, xb, None, gx)
         y = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
         fn = lambda: K.gemm_fp4(w, x, y=y)
-        kernel, peak_key, launches = "gemm_fp4_kernel", None, 1
+        kernel, peak_key, launches = "gemm_fp4_pair_kernel", None, 1
     for _ in range(max(args.warmup, 3)):
         fn()
     torch.cuda.synchronize()
@@ -897,6 +899,13 @@ def run_prefill_case(args):
     ms = e0.elapsed_time(e1) / args.steps
     tflops = 2.0 * m * n * k / (ms * 1e-3) / 1e12
     peak, kind = 9000.0, "nominal dense FP4"
+    ceiling = None
+    if not peak_key:
+        # what the same MMA reaches on operands parked in shared memory (no copies, no epilogue), with and without the
+        # per-k-step scale-factor copies: the practical ceiling of this kernel on this device
+        ceiling = {"mma_and_scale_copies_cta_pair": K.probe_fp4_mma(True, True), "mma_only_cta_pair": K.probe_fp4_mma(True, False),
+                   "mma_and_scale_copies_one_cta": K.probe_fp4_mma(False, True), "mma_only_one_cta": K.probe_fp4_mma(False, False),
+                   "unit": "TFLOP/s", "how": "gllmk_probe_fp4_mma: 4096 k-steps of 4 block-scaled MMAs per CTA, best of 3 launches"}
     if peak_key:
         pth = os.path.join(ROOT, "MEASURED_PEAKS.json")
         if os.path.exists(pth):
@@ -908,7 +917,8 @@ def run_prefill_case(args):
                       "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
                       "data": "synthetic", "config": {"workload": args.case, "n": n, "k": k, "m": m},
                       "roofline": {"bound": "tensor", "achieved": tflops, "peak": peak, "unit": "TFLOP/s", "frac": tflops / peak,
-                                   "traffic": None, "peak_kind": kind, "kernel": kernel},
+                                   "traffic": None, "peak_kind": kind, "kernel": kernel, "measured_mma_ceiling": ceiling,
+                                   "frac_of_measured_ceiling": (tflops / ceiling["mma_and_scale_copies_cta_pair"]) if ceiling else None},
                       "gpu_launches": args.steps * launches, "status": K.status()}), flush=True)
 
 

@@ -87,6 +87,7 @@ _OPTIONAL_SIGS: dict = {
     "gllmk_shared_free": (_i32, [_vp, _vp]),
     "gllmk_gemv_allgather": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _vp, _i64, _i64, C.POINTER(_vp), _i32, _vp]),
     "gllmk_peer_barrier": (_i32, [_vp, _vp, C.POINTER(_vp), _i32, _i32, C.c_uint32, _vp]),
+    "gllmk_probe_fp4_mma": (_i32, [_vp, _i32, _i32, _i32, _i32, C.POINTER(_f32)]),
     "gllmk_quantize_act_int8": (_i32, [_vp, _vp, _i64, _i64, _i64, _vp, _i64, _i32, _vp, _vp]),
     "gllmk_w8a8_linear_f32": (_i32, [_vp, _vp, _vp, _i64, _i32, _vp, _i64, _f32, _vp, _i32, _vp]),
     "gllmk_gemm_q8_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz]),

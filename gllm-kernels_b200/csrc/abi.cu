@@ -645,6 +645,14 @@ int32_t gllmk_gemm_fp4(gllmk_ctx ctx, gllmk_weight wh, gllmk_weight xh, void *y_
     return gemm_fp4_launch(c, w, x, y_dev, y_dtype == GLLMK_DTYPE_BF16, ldy, static_cast<cudaStream_t>(stream));
 }
 
+int32_t gllmk_probe_fp4_mma(gllmk_ctx ctx, int32_t cta_pair, int32_t with_scale_copies, int32_t nvfp4, int32_t ksteps, float *tflops) {
+    if (!ctx || !tflops) return GLLMK_STATUS_INVALID_ARG;
+    Ctx *c = static_cast<Ctx *>(ctx);
+    if (ksteps < 1 || ksteps > (1 << 20)) return fail(c, GLLMK_STATUS_INVALID_ARG, "probe_fp4_mma: ksteps outside 1..2^20");
+    DeviceGuard g(c->device);
+    return probe_fp4_mma(c, cta_pair != 0, with_scale_copies != 0, nvfp4 != 0, ksteps, tflops);
+}
+
 // Shared body of the host-pointer matmuls: weight rows n_w, tokens m_t, reduction k.
 //   ref_layout: input [k, m_t], output [n_w, m_t]; else input [m_t, k], output [m_t, n_w].
 static int32_t matmul_host_impl(Ctx *c, const Weight *w, const float *x_host, int m_t, float *y_host, bool ref_layout,

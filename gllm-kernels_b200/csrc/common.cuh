@@ -158,6 +158,7 @@ int32_t gemm_grouped_launch(Ctx *c, const Weight *const *ws, int n_groups, const
                             const int64_t *row_offsets, void *y, int y_bf16, int64_t ldy, cudaStream_t s);
 // ---- gemm_fp4.cu ----
 int32_t gemm_fp4_launch(Ctx *c, const Weight *w, const Weight *x, void *y, int y_bf16, int64_t ldy, cudaStream_t s);
+int32_t probe_fp4_mma(Ctx *c, int pair, int with_cp, int nv, int ksteps, float *tflops);
 // ---- gemv_fp4.cu ----
 int32_t gemv_fp4_launch(Ctx *c, const Weight *w, const float *x, int64_t xst, int64_t xsk, int m, float *y, int64_t yst, int64_t ysr,
                         cudaStream_t s);

@@ -413,6 +413,137 @@ gemm_fp4_pair_kernel(const __grid_constant__ Fp4Params p, const int row_tiles, c
 }
 
 // ---------------------------------------------------------------------------------------------
+// Ceiling probe: the block-scaled FP4 MMA of the kernels above issued back to back on operands that never leave
+// shared memory (no copies from L2, no epilogue), one CTA (or CTA pair) per SM, k-steps of four MMAs committed to a
+// ring of four barriers like the real pipelines.  What this reaches is the most the GEMM kernels can: it is the
+// denominator bench.py reports beside the nominal 9 PFLOP/s.
+// ---------------------------------------------------------------------------------------------
+template <bool PAIR>
+__device__ __forceinline__ void probe_body(int nv, int with_cp, int ksteps, int *status) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bars[4];
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int abort_s;
+    const uint32_t smem_s = (tc::smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *smem = smem_raw + (smem_s - tc::smem_u32(smem_raw));
+    const int warp = threadIdx.x >> 5;
+    const uint32_t bar0 = tc::smem_u32(&bars[0]);
+    const uint32_t rank = PAIR ? tc::cluster_ctarank() : 0u;
+    constexpr int A = 16384, B = PAIR ? 16384 : 32768, SFA = 2048, SFB = 4096;
+    // operands: every E2M1 code, scale bytes 0x38 (UE4M3 1.0; as UE8M0 2^-71: still finite)
+    for (int i = threadIdx.x; i < (A + B) / 4; i += blockDim.x) reinterpret_cast<uint32_t *>(smem)[i] = 0x76543210u * (uint32_t)(i | 1);
+    for (int i = threadIdx.x; i < (SFA + SFB) / 4; i += blockDim.x) reinterpret_cast<uint32_t *>(smem + A + B)[i] = 0x38383838u;
+    if (threadIdx.x == 0) {
+        abort_s = 0;
+        for (int s = 0; s < 4; s++) tc::mbar_init(bar0 + 8 * s, 1);
+        tc::mbar_init_fence();
+    }
+    tc::fence_proxy_async();
+    if (warp == 1) {
+        if (PAIR) tc::tmem_alloc_pair(tc::smem_u32(&tmem_base_s), 512);
+        else tc::tmem_alloc(tc::smem_u32(&tmem_base_s), 512);
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    if (PAIR) { tc::cluster_arrive(); tc::cluster_wait(); }
+    tc::fence_after_sync();
+    const uint32_t tmem = tmem_base_s;
+    volatile int *abort_flag = &abort_s;
+    if (threadIdx.x == 32 && rank == 0) {
+        const uint64_t ad = tc::smem_desc_sw128(smem_s), bd = tc::smem_desc_sw128(smem_s + A);
+        const uint32_t sfa = smem_s + A + B, sfb = sfa + SFA;
+        const uint32_t idesc_nv = tc::idesc_fp4(PAIR ? 256 : 128, 256, 0, 0, 0);
+        for (int ks = 0; ks < ksteps; ks++) {
+            const int s = ks & 3;
+            if (ks >= 4 && !tc::mbar_wait(bar0 + 8 * s, (uint32_t)((ks / 4 - 1) & 1), abort_flag)) {
+                atomicExch(status, 27);
+                break;
+            }
+            const int atoms = nv ? 4 : 2;
+            if (with_cp)
+                for (int j = 0; j < atoms; j++) {
+                    if (PAIR) {
+                        tc::tmem_cp_sf_pair(tmem + 256 + 4 * j, sf_desc(sfa + 512 * j));
+                        tc::tmem_cp_sf_pair(tmem + 272 + 8 * j, sf_desc(sfb + 512 * j));
+                        tc::tmem_cp_sf_pair(tmem + 272 + 8 * j + 4, sf_desc(sfb + 2048 + 512 * j));
+                    } else {
+                        tc::tmem_cp_sf(tmem + 256 + 4 * j, sf_desc(sfa + 512 * j));
+                        tc::tmem_cp_sf(tmem + 272 + 8 * j, sf_desc(sfb + 512 * j));
+                        tc::tmem_cp_sf(tmem + 272 + 8 * j + 4, sf_desc(sfb + 2048 + 512 * j));
+                    }
+                }
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                if (nv) {
+                    if (PAIR) tc::mma_nvf4_pair(tmem, ad + 2 * j, bd + 2 * j, idesc_nv, (uint32_t)((ks | j) != 0), tmem + 256 + 4 * j, tmem + 272 + 8 * j);
+                    else tc::mma_nvf4(tmem, ad + 2 * j, bd + 2 * j, idesc_nv, (uint32_t)((ks | j) != 0), tmem + 256 + 4 * j, tmem + 272 + 8 * j);
+                } else {
+                    const int id = (j & 1) * 2;
+                    const uint32_t idm = tc::idesc_fp4(PAIR ? 256 : 128, 256, 1, id, id);
+                    if (PAIR) tc::mma_mxf4_pair(tmem, ad + 2 * j, bd + 2 * j, idm, (uint32_t)((ks | j) != 0), tmem + 256 + 4 * (j >> 1), tmem + 272 + 8 * (j >> 1));
+                    else tc::mma_mxf4(tmem, ad + 2 * j, bd + 2 * j, idm, (uint32_t)((ks | j) != 0), tmem + 256 + 4 * (j >> 1), tmem + 272 + 8 * (j >> 1));
+                }
+            }
+            if (PAIR) tc::mma_commit_pair(bar0 + 8 * s);
+            else tc::mma_commit(bar0 + 8 * s);
+        }
+        // drain: the last commits
+        for (int ks = max(ksteps - 4, 0); ks < ksteps; ks++)
+            if (!tc::mbar_wait(bar0 + 8 * (ks & 3), (uint32_t)((ks / 4) & 1), abort_flag)) {
+                atomicExch(status, 27);
+                break;
+            }
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    if (PAIR) { tc::cluster_arrive(); tc::cluster_wait(); }
+    if (warp == 1) {
+        if (PAIR) tc::tmem_dealloc_pair(tmem, 512);
+        else tc::tmem_dealloc(tmem, 512);
+    }
+}
+__global__ void __launch_bounds__(128, 1) probe_fp4_single_kernel(int nv, int with_cp, int ksteps, int *status) { probe_body<false>(nv, with_cp, ksteps, status); }
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(128, 1) probe_fp4_pair_kernel(int nv, int with_cp, int ksteps, int *status) {
+    probe_body<true>(nv, with_cp, ksteps, status);
+}
+
+int32_t probe_fp4_mma(Ctx *c, int pair, int with_cp, int nv, int ksteps, float *tflops) {
+    const size_t smem = 16384 + 32768 + 2048 + 4096 + 1024;
+    // more shared memory than half an SM has: one CTA per SM, as in the GEMM kernels
+    const size_t smem_req = smem < 120 * 1024 ? 120 * 1024 : smem;
+    if (pair) GK_CUDA(c, cudaFuncSetAttribute(probe_fp4_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_req));
+    else GK_CUDA(c, cudaFuncSetAttribute(probe_fp4_single_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_req));
+    const unsigned grid = (unsigned)c->sm_count & ~1u;
+    cudaEvent_t e0, e1;
+    GK_CUDA(c, cudaEventCreate(&e0));
+    GK_CUDA(c, cudaEventCreate(&e1));
+    float best = 0.f;
+    for (int rep = 0; rep < 4; rep++) {
+        cudaEventRecord(e0, c->stream);
+        if (pair) probe_fp4_pair_kernel<<<grid, 128, smem_req, c->stream>>>(nv, with_cp, ksteps, c->status_dev);
+        else probe_fp4_single_kernel<<<grid, 128, smem_req, c->stream>>>(nv, with_cp, ksteps, c->status_dev);
+        cudaEventRecord(e1, c->stream);
+        cudaError_t e = cudaStreamSynchronize(c->stream);
+        if (e == cudaSuccess) e = cudaGetLastError();
+        if (e != cudaSuccess) {
+            cudaEventDestroy(e0);
+            cudaEventDestroy(e1);
+            return cuda_fail(c, e, "probe_fp4_mma");
+        }
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, e0, e1);
+        // per k-step and CTA: four MMAs of 128 x 256 x 64 (a pair: 256 x 256 x 64 over two CTAs = the same per CTA)
+        const double flops = (double)grid * ksteps * 4.0 * 2.0 * 128.0 * 256.0 * 64.0;
+        const float tf = (float)(flops / (ms * 1e-3) / 1e12);
+        if (rep > 0 && tf > best) best = tf;  // the first launch warms up
+    }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    *tflops = best;
+    return GLLMK_STATUS_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
 // w: weights [n, k]; x: activations [m, k] in the same FP4 format, uploaded like a weight.
 int32_t gemm_fp4_launch(Ctx *c, const Weight *w, const Weight *x, void *y, int y_bf16, int64_t ldy, cudaStream_t s) {
     if (w->qt != x->qt || (w->qt != GLLMK_QUANT_NVFP4 && w->qt != GLLMK_QUANT_MXFP4))

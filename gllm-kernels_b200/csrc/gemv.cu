@@ -244,6 +244,10 @@ struct GemvParams {
     int *status;       // device status word
 };
 
+// Fused staging pays when a CTA's share is a handful of k-steps (small matrices, row shards of a few thousand
+// rows): the staging kernel's launch and the hand-over between the two grids then cost more than converting
+// fuse_slices x m slices of 256 activations in every CTA.
+constexpr int GEMV_FUSE_MAX_WORK = 10;  // slices x tokens a CTA converts itself at most
 constexpr int GEMV_STAGES = 3;  // pipeline depth (stages of one super-chunk + its activation slice)
 constexpr int GEMV_WARPS = 8;
 constexpr int GEMV_ZERO = 512;  // zero region read by the lanes of unused MMA columns
@@ -264,53 +268,45 @@ static inline size_t gemv_smem_bytes_fused(int m, int nslices) {
            2 * GEMV_STAGES * 8;
 }
 
-// One activation slice (256 elements of k-block kb, all tokens) written by the whole CTA (thread = element, warp =
-// 32-element sub-block) in the layout of the image above: the arithmetic of stage_x_kernel, element for element.
-__device__ __forceinline__ void stage_slice_in_cta(const float *__restrict__ x, const float *__restrict__ x_up, int64_t xst, int64_t xsk,
-                                                   int64_t K, int m, int kb, uint8_t *slice, float (*wmax)[8], int (*wbad)[8], int &par) {
+// One value of an activation slice turned into its two digits by the whole CTA (thread = element of the 256-block,
+// warp = 32-element sub-block), in the layout of the image above: the arithmetic of stage_x_kernel, element for element.
+__device__ __forceinline__ void stage_value_in_cta(float v, int m, int tok, uint8_t *slice, float (*wmax)[8], int (*wbad)[8], int &par) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int64_t k = (int64_t)kb * 256 + tid;
-    for (int tok = 0; tok < m; tok++, par ^= 1) {
-        float v = 0.f;
-        if (k < K) {
-            v = __ldcg(x + (int64_t)tok * xst + k * xsk);
-            if (x_up) v = (v / (1.0f + expf(-v))) * __ldcg(x_up + (int64_t)tok * xst + k * xsk);
-        }
-        float amax = fabsf(v);
-        const float inf = __int_as_float(0x7F800000);
-        int bad = !(fabsf(v) < inf);
+    float amax = fabsf(v);
+    const float inf = __int_as_float(0x7F800000);
+    int bad = !(fabsf(v) < inf);
 #pragma unroll
-        for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-        bad = __any_sync(0xffffffffu, bad);
-        if (lane == 0) { wmax[par][warp] = amax; wbad[par][warp] = bad; }
-        __syncthreads();  // the other parity's slots are rewritten only after the next barrier: one barrier per token
-        amax = 0.f;
-        bad = 0;
+    for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    bad = __any_sync(0xffffffffu, bad);
+    if (lane == 0) { wmax[par][warp] = amax; wbad[par][warp] = bad; }
+    __syncthreads();  // the other parity's slots are rewritten only after the next barrier: one barrier per value
+    amax = 0.f;
+    bad = 0;
 #pragma unroll
-        for (int w = 0; w < 8; w++) { amax = fmaxf(amax, wmax[par][w]); bad |= wbad[par][w]; }
-        const float pre = amax < 1e-20f ? 18446744073709551616.0f : 1.0f;
-        const float inv = (amax > 0.0f && !bad) ? 127.0f / (amax * pre) : 0.0f;
-        const float sc = (v * pre) * inv;
-        const float r1 = fminf(fmaxf(rintf(sc), -127.0f), 127.0f);
-        const float r2 = fminf(fmaxf(rintf((sc - r1) * 254.0f), -127.0f), 127.0f);
-        const int d1 = (int)r1, d2 = (int)r2;
-        slice[(2 * tok) * 288 + tid] = (uint8_t)(int8_t)d1;
-        slice[(2 * tok + 1) * 288 + tid] = (uint8_t)(int8_t)d2;
-        int s1 = d1, s2 = d2;
+    for (int w = 0; w < 8; w++) { amax = fmaxf(amax, wmax[par][w]); bad |= wbad[par][w]; }
+    par ^= 1;
+    const float pre = amax < 1e-20f ? 18446744073709551616.0f : 1.0f;
+    const float inv = (amax > 0.0f && !bad) ? 127.0f / (amax * pre) : 0.0f;
+    const float sc = (v * pre) * inv;
+    const float r1 = fminf(fmaxf(rintf(sc), -127.0f), 127.0f);
+    const float r2 = fminf(fmaxf(rintf((sc - r1) * 254.0f), -127.0f), 127.0f);
+    const int d1 = (int)r1, d2 = (int)r2;
+    slice[(2 * tok) * 288 + tid] = (uint8_t)(int8_t)d1;
+    slice[(2 * tok + 1) * 288 + tid] = (uint8_t)(int8_t)d2;
+    int s1 = d1, s2 = d2;
 #pragma unroll
-        for (int o = 16; o; o >>= 1) {
-            s1 += __shfl_xor_sync(0xffffffffu, s1, o);
-            s2 += __shfl_xor_sync(0xffffffffu, s2, o);
-        }
-        if (lane == 0) {
-            uint8_t *sp = slice + (2 * m) * 288;
-            sp[(2 * tok) * 16 + warp] = (uint8_t)(int8_t)(s1 >> 6);
-            sp[(2 * tok) * 16 + 8 + warp] = (uint8_t)(s1 & 63);
-            sp[(2 * tok + 1) * 16 + warp] = (uint8_t)(int8_t)(s2 >> 6);
-            sp[(2 * tok + 1) * 16 + 8 + warp] = (uint8_t)(s2 & 63);
-        }
-        if (tid == 0) reinterpret_cast<float *>(slice + (2 * m) * 304)[tok] = bad ? __int_as_float(0x7FC00000) : amax / 127.0f;
+    for (int o = 16; o; o >>= 1) {
+        s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+        s2 += __shfl_xor_sync(0xffffffffu, s2, o);
     }
+    if (lane == 0) {
+        uint8_t *sp = slice + (2 * m) * 288;
+        sp[(2 * tok) * 16 + warp] = (uint8_t)(int8_t)(s1 >> 6);
+        sp[(2 * tok) * 16 + 8 + warp] = (uint8_t)(s1 & 63);
+        sp[(2 * tok + 1) * 16 + warp] = (uint8_t)(int8_t)(s2 >> 6);
+        sp[(2 * tok + 1) * 16 + 8 + warp] = (uint8_t)(s2 & 63);
+    }
+    if (tid == 0) reinterpret_cast<float *>(slice + (2 * m) * 304)[tok] = bad ? __int_as_float(0x7FC00000) : amax / 127.0f;
 }
 
 // ---- one 16-row x 256-k chunk of Q4_K -------------------------------------------------------
@@ -646,11 +642,28 @@ __global__ void __launch_bounds__(256) gemv_kernel(const __grid_constant__ GemvP
             }
             __syncthreads();
         }
+        // this CTA's slices: all loads first (one L2 round trip for the lot), then the conversions
         const int nsl = min(n, p.fuse_slices);
-        int kb = b, par = 0;
-        for (int i = 0; i < nsl; i++) {
-            stage_slice_in_cta(p.x, p.x_up, p.xst, p.xsk, p.K, p.m, kb, smem + (slices_s - smem_s) + (size_t)i * xbytes, wmax_s, wbad_s, par);
-            if (++kb == nk) kb = 0;
+        float xv[GEMV_FUSE_MAX_WORK];
+#pragma unroll
+        for (int j = 0; j < GEMV_FUSE_MAX_WORK; j++) {
+            const int i = j / p.m, tok = j - i * p.m;  // slice, token
+            xv[j] = 0.f;
+            if (i < nsl) {
+                int kb = b + i;
+                if (kb >= nk) kb -= nk;
+                const int64_t k = (int64_t)kb * 256 + threadIdx.x;
+                if (k < p.K) {
+                    xv[j] = __ldcg(p.x + (int64_t)tok * p.xst + k * p.xsk);
+                    if (p.x_up) xv[j] = (xv[j] / (1.0f + expf(-xv[j]))) * __ldcg(p.x_up + (int64_t)tok * p.xst + k * p.xsk);
+                }
+            }
+        }
+        int par = 0;
+#pragma unroll
+        for (int j = 0; j < GEMV_FUSE_MAX_WORK; j++) {
+            const int i = j / p.m, tok = j - i * p.m;
+            if (i < nsl) stage_value_in_cta(xv[j], p.m, tok, smem + (slices_s - smem_s) + (size_t)i * xbytes, wmax_s, wbad_s, par);
         }
     } else if (threadIdx.x == 0) {
         int bb = b;
@@ -799,10 +812,6 @@ static cudaError_t gemv_occupancy(int device, int m, size_t smem, int *per_sm) {
     return cudaSuccess;
 }
 
-// Fused staging pays when a CTA's share is a handful of k-steps (small matrices, row shards of a few thousand
-// rows): the staging kernel's launch and the hand-over between the two grids then cost more than converting
-// fuse_slices x m slices of 256 activations in every CTA.
-constexpr int GEMV_FUSE_MAX_WORK = 20;  // slices x tokens a CTA converts itself at most
 
 // Grid of a decode launch: resident CTAs, each with a contiguous share of the super-chunk sequence.
 struct GemvGrid {

@@ -92,6 +92,7 @@ extern "C" {
     fn gllmk_gemm_grouped(ctx: *mut c_void, n_groups: i32, weights: *const *mut c_void, a_dev: *const c_void, a_dtype: i32, lda: i64,
                           row_offsets: *const i64, y_dev: *mut c_void, y_dtype: i32, ldy: i64, stream: *mut c_void) -> i32;
     fn gllmk_gemm_fp4(ctx: *mut c_void, w: *mut c_void, x: *mut c_void, y_dev: *mut c_void, y_dtype: i32, ldy: i64, stream: *mut c_void) -> i32;
+    fn gllmk_probe_fp4_mma(ctx: *mut c_void, cta_pair: i32, with_scale_copies: i32, nvfp4: i32, ksteps: i32, tflops: *mut f32) -> i32;
     fn gllmk_quantize(ctx: *mut c_void, quant_type: i32, x_dev: *const f32, rows: i64, k: i64, mx_block: i32, blocks_dev: *mut c_void,
                       scales_dev: *mut c_void, global_scale: *mut f32, stream: *mut c_void) -> i32;
 
@@ -414,7 +415,7 @@ fn _declared_but_unwrapped() {
     let _ = (
         gllmk_quant_block_size as usize, gllmk_quant_block_bytes as usize, gllmk_ctx_set as usize, gllmk_weight_unpack as usize,
         gllmk_dequant as usize, gllmk_embedding_gather as usize, gllmk_gemv_static as usize, gllmk_ffn_decode as usize,
-        gllmk_gemm_grouped as usize, gllmk_gemm_fp4 as usize, gllmk_quantize as usize, gllmk_moe_topk as usize, gllmk_moe_route as usize,
+        gllmk_gemm_grouped as usize, gllmk_gemm_fp4 as usize, gllmk_probe_fp4_mma as usize, gllmk_quantize as usize, gllmk_moe_topk as usize, gllmk_moe_route as usize,
         gllmk_moe_gather as usize, gllmk_moe_weighted_sum as usize, gllmk_int8_weight_upload as usize, gllmk_gemm_int8 as usize,
         gllmk_dequantize_i32_f32 as usize, gllmk_quantize_act_int8 as usize, gllmk_w8a8_linear_f32 as usize, gllmk_shared_alloc as usize,
         gllmk_shared_open as usize, gllmk_shared_close as usize, gllmk_shared_free as usize, gllmk_gemv_allgather as usize,

@@ -369,6 +369,14 @@ GLLMK_API int32_t gllmk_moe_weighted_sum(gllmk_ctx ctx, const float *expert_outp
 GLLMK_API int32_t gllmk_gemm_fp4(gllmk_ctx ctx, gllmk_weight w, gllmk_weight x, void *y_dev, int32_t y_dtype, int64_t ldy,
                                  void *stream);
 
+/* Measurement aid, no counterpart in the reference: the block-scaled FP4 MMA of gllmk_gemm_fp4 (kind::mxf4nvf4 scale_vec::4X
+ * for nvfp4 != 0, kind::mxf4 scale_vec::2X otherwise; one CTA per SM, or CTA pairs with cta_pair != 0) issued back to
+ * back on operands parked in shared memory, with or without the per-k-step scale-factor copies to tensor memory.
+ * Writes the TFLOP/s reached (best of three timed launches of `ksteps` k-steps of 256 per CTA): the practical ceiling
+ * of the FP4 x FP4 GEMM on this device, which bench.py reports as the denominator beside the nominal peak.
+ * Synchronous on the context's own stream. */
+GLLMK_API int32_t gllmk_probe_fp4_mma(gllmk_ctx ctx, int32_t cta_pair, int32_t with_scale_copies, int32_t nvfp4, int32_t ksteps, float *tflops);
+
 /* Same product as gllmk_gemv for callers that are not allowed to allocate device memory while they run:
  * a serving loop whose allocator has already claimed all of HBM for weights and KV pages, code running
  * under a pool allocator that owns the device, or a latency-critical section where cudaMalloc's implicit
