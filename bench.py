@@ -363,6 +363,10 @@ def run_ours(args):
     }
     if world == 1 and rank == 0 and not args.no_extra:
         out["extra"] = extra_configs(K, gk, torch, dev, peak)
+    if world > 1 and not args.no_extra:
+        sharded = sharded_prefill_extra(K, gk, torch, dist, dev, world, rank)
+        if rank == 0:
+            out["extra"] = sharded
     if parity_multi is not None:
         out["parity"] = parity_multi
     if keep_host:
@@ -408,6 +412,60 @@ def multi_gpu_parity(args, K, gk, torch, dev, weights, ex, gbufs, x_model, M, wo
                          y[:, torch.from_numpy(rows).to(dev)], bar=2e-3, sequential=True)
     rec["matrix"] = f"{name} [{n}, {k}]: rows sampled from each of the {world} ranks' bands, read from rank 0's gathered y"
     return rec
+
+
+def sharded_prefill_extra(K, gk, torch, dist, dev, world, rank):
+    """The sharded gate matrix W[28672, 8192] (Q4_K) at M = 32 and M = 512: every rank multiplies its band of rows
+    (decode passes for 32 f32 tokens, the tensor-core kernel with bf16 output for 512) and ONE NCCL all-gather puts the
+    bands side by side.  Device time (CUDA events), max over ranks; parity on rank 0 against the oracle on rows sampled
+    from every rank's band of the gathered result."""
+    import numpy as np
+    qt = gk.QuantType.q4k()
+    n, k = N_FF, D_MODEL
+    gen = torch.Generator(device=dev).manual_seed(20246)
+    W = torch.randn((n, k), generator=gen, device=dev) * 0.02
+    r0, r1 = shard_rows(n, world, rank)
+    band = r1 - r0
+    w = K.upload(qt, band, k, K.quantize(qt, W[r0:r1].contiguous()))
+    rows = np.concatenate([shard_rows(n, world, r)[0] + sample_rows(shard_rows(n, world, r)[1] - shard_rows(n, world, r)[0],
+                                                                     max(64, 256 // world), seed=r) for r in range(world)])
+    sub_blocks = K.quantize(qt, W[torch.from_numpy(rows).to(dev)].contiguous()) if rank == 0 else None
+    del W
+    res = {}
+    for m in (32, 512):
+        x = torch.randn((m, k), generator=gen, device=dev)
+        dt = torch.float32 if m <= K.GEMM_GEMV_MAX_M else torch.bfloat16
+        buf = torch.empty((world, m, band), dtype=dt, device=dev)
+
+        def step():
+            K.gemm(w, x, y=buf[rank])
+            dist.all_gather_into_tensor(buf.view(-1), buf[rank].view(-1))
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 10
+        e0.record()
+        for _ in range(reps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / reps], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        us = t.item() * 1e3
+        entry = {"us": us, "tflops": 2.0 * m * n * k / us / 1e6, "weight_GBps": n * (k // Q4K_BLOCK) * Q4K_BLOCK_BYTES / us / 1e3,
+                 "gather": f"one NCCL all_gather_into_tensor of [{m}, {band}] {str(dt).split('.')[-1]} bands",
+                 "all_gather_bytes_per_rank": m * band * (4 if dt == torch.float32 else 2)}
+        if rank == 0:
+            from oracle import oracle as O
+            y = torch.cat([buf[r] for r in range(world)], dim=1)
+            tc = m > K.GEMM_GEMV_MAX_M
+            entry["parity"] = sampled_parity(O, O.Q4K, sub_blocks, len(rows), k, np.arange(len(rows)), x.cpu().numpy(),
+                                             y[:, torch.from_numpy(rows).to(dev)], bar=1e-2 if tc else 2e-3, sequential=not tc)
+        res[f"sharded_q4k_{n}x{k}_M{m}"] = entry
+    w.free()
+    return res
 
 
 def extra_configs(K, gk, torch, dev, peak):
@@ -728,7 +786,7 @@ def extra_gemm(K, gk, torch, dev, gen):
     us = timeit(lambda: K.gemm_fp4(w, x, y=y), 20)
     a_host = O.dequant_matrix(O.NVFP4, xb.cpu().numpy(), m, k, global_scale=gx)
     rows = sample_rows(n, 256, seed=4)
-    ceil_tf = K.probe_fp4_mma(True, True)
+    ceil_tf = K.probe_fp4_mma(True, 2)
     res["cfg4_nvfp4_14336x4096_M2048"] = {"us": us, "tflops": 2.0 * m * n * k / us / 1e6, "frac_of_nominal_fp4_9000": 2.0 * m * n * k / us / 1e6 / 9000.0,
                                           "measured_mma_ceiling_tflops": ceil_tf, "frac_of_measured_mma_ceiling": 2.0 * m * n * k / us / 1e6 / ceil_tf,
                                           "mma": "tcgen05 kind::mxf4nvf4 block_scale, cta_group::2",
@@ -903,8 +961,9 @@ def run_prefill_case(args):
     if not peak_key:
         # what the same MMA reaches on operands parked in shared memory (no copies, no epilogue), with and without the
         # per-k-step scale-factor copies: the practical ceiling of this kernel on this device
-        ceiling = {"mma_and_scale_copies_cta_pair": K.probe_fp4_mma(True, True), "mma_only_cta_pair": K.probe_fp4_mma(True, False),
-                   "mma_and_scale_copies_one_cta": K.probe_fp4_mma(False, True), "mma_only_one_cta": K.probe_fp4_mma(False, False),
+        ceiling = {"mma_and_scale_warps_cta_pair": K.probe_fp4_mma(True, 2), "mma_and_scale_copies_cta_pair": K.probe_fp4_mma(True, 1),
+                   "mma_only_cta_pair": K.probe_fp4_mma(True, 0), "mma_and_scale_warps_one_cta": K.probe_fp4_mma(False, 2),
+                   "mma_and_scale_copies_one_cta": K.probe_fp4_mma(False, 1), "mma_only_one_cta": K.probe_fp4_mma(False, 0),
                    "unit": "TFLOP/s", "how": "gllmk_probe_fp4_mma: 4096 k-steps of 4 block-scaled MMAs per CTA, best of 3 launches"}
     if peak_key:
         pth = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -918,7 +977,7 @@ def run_prefill_case(args):
                       "data": "synthetic", "config": {"workload": args.case, "n": n, "k": k, "m": m},
                       "roofline": {"bound": "tensor", "achieved": tflops, "peak": peak, "unit": "TFLOP/s", "frac": tflops / peak,
                                    "traffic": None, "peak_kind": kind, "kernel": kernel, "measured_mma_ceiling": ceiling,
-                                   "frac_of_measured_ceiling": (tflops / ceiling["mma_and_scale_copies_cta_pair"]) if ceiling else None},
+                                   "frac_of_measured_ceiling": (tflops / ceiling["mma_and_scale_warps_cta_pair"]) if ceiling else None},
                       "gpu_launches": args.steps * launches, "status": K.status()}), flush=True)
 
 

@@ -650,7 +650,8 @@ int32_t gllmk_probe_fp4_mma(gllmk_ctx ctx, int32_t cta_pair, int32_t with_scale_
     Ctx *c = static_cast<Ctx *>(ctx);
     if (ksteps < 1 || ksteps > (1 << 20)) return fail(c, GLLMK_STATUS_INVALID_ARG, "probe_fp4_mma: ksteps outside 1..2^20");
     DeviceGuard g(c->device);
-    return probe_fp4_mma(c, cta_pair != 0, with_scale_copies != 0, nvfp4 != 0, ksteps, tflops);
+    if (with_scale_copies < 0 || with_scale_copies > 2) return fail(c, GLLMK_STATUS_INVALID_ARG, "probe_fp4_mma: scale-factor mode outside 0..2");
+    return probe_fp4_mma(c, cta_pair != 0, with_scale_copies, nvfp4 != 0, ksteps, tflops);
 }
 
 // Shared body of the host-pointer matmuls: weight rows n_w, tokens m_t, reduction k.

@@ -96,7 +96,8 @@ struct Ctx {
     int64_t gemv_fp4_int = 0;  // 1: FP4 decode on the integer-decode GEMV kernel instead of the tensor-core one
     int64_t gemv_ctas_per_sm = 0;  // 0 = what the occupancy calculator allows
     int64_t gemm_tail_split = 0;  // prefill GEMM: 0 = cut the last partial wave of tiles along k when that pays, 1 = never, n = into n
-    int64_t gemv_fuse = 1;      // decode GEMV: small shares convert their activation slices inside the GEMV (no staging launch)
+    int64_t gemv_fuse = 1;      // decode GEMV, small shares convert their activation slices inside the GEMV (no staging launch):
+                                // 0 never, 1 exchange products only, 2 every product
     int64_t gemm_fp4_pair = 1;  // FP4 x FP4 GEMM with m > 128: the CTA-pair (cta_group::2) persistent kernel
     int64_t peer_wait_spins = (int64_t)1 << 22;  // probes of another rank's flag before a wait gives up (status 31 / 32)
 };

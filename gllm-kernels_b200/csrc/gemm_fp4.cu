@@ -200,34 +200,44 @@ gemm_fp4_kernel(const __grid_constant__ Fp4Params p, const int ntok) {
 // ---------------------------------------------------------------------------------------------
 // CTA-pair version (m > 128): persistent, two CTAs of a cluster on two SMs work on one 256-row x 256-token tile.
 //
-// The one-CTA kernel above is bound by what an SM can pull from L2: 54 KB per k-step for 8.4 M multiply-adds.  As
-// a pair (tcgen05 cta_group::2, MMA M = 256) each CTA brings in its own 128 weight rows, HALF of the activation
-// tile (the tensor core reads the other half from the partner's shared memory) and the scale atoms: 38 KB per
-// k-step for the same multiply-adds per SM.  The kernel is persistent (grid = resident pairs, tiles dealt round
-// robin), so the copy threads run ahead into the next tile while the accumulator of the finished one is stored.
+// Two things bound the one-CTA kernel above.  (1) What an SM can pull from L2: 54 KB per k-step for 8.4 M
+// multiply-adds.  As a pair (tcgen05 cta_group::2, MMA M = 256) each CTA brings in its own 128 weight rows, HALF of
+// the activation tile (the tensor core reads the other half from the partner's shared memory) and the scale atoms:
+// 38 KB per k-step for the same multiply-adds per SM.  (2) The scale-factor copies: twelve tcgen05.cp per k-step run
+// on the tensor pipe itself and take as long as the four MMAs they feed (measured with the MMA issued back to back
+// on resident operands: 6.0 PFLOP/s without the copies, 3.1 with them).  Here the scale factors never touch that
+// pipe: four "scale warps" per CTA (one per tensor-memory lane quadrant) read the atoms from the stage with 16-byte
+// shared-memory loads and write them to tensor memory with tcgen05.st — the layout tcgen05.cp.32x128b.warpx4 would
+// produce: lane = row % 32, one column per group of 32 rows, every quadrant a copy — three sets of columns in rotation.
+//
+// The kernel is persistent (grid = resident pairs, tiles dealt round robin), so the copy threads and the scale
+// warps run ahead into the next tile while the accumulator of the finished one is stored.
 //
 // Per CTA: warp 0 lane 0 copies; warp 1 lane 0 issues the MMAs (leader = cluster rank 0) or forwards "my stage is
 // full" to the leader (rank 1), because a wait on an mbarrier can only be done by its own CTA; warps 2..9 store the
-// CTA's 128 rows x 256 tokens of the accumulator.  Loads are plain bulk copies: nothing is multicast.
+// CTA's 128 rows x 256 tokens of the accumulator; warps 10..13 are the scale warps.  Loads are plain bulk copies:
+// nothing is multicast.
 // ---------------------------------------------------------------------------------------------
 constexpr int P4_STAGES = 5;
 constexpr int P4_A_BYTES = 16384, P4_B_BYTES = 16384, P4_SFA_BYTES = 2048, P4_SFB_BYTES = 4096;
 constexpr int P4_STAGE_BYTES = P4_A_BYTES + P4_B_BYTES + P4_SFA_BYTES + P4_SFB_BYTES;
-constexpr int P4_EPI_WARPS = 8;
-constexpr int P4_THREADS = 64 + 32 * P4_EPI_WARPS;
+constexpr int P4_EPI_WARPS = 8, P4_SF_WARPS = 4;
+constexpr int P4_THREADS = 64 + 32 * (P4_EPI_WARPS + P4_SF_WARPS);
 constexpr size_t P4_SMEM = (size_t)P4_STAGES * P4_STAGE_BYTES + (size_t)P4_EPI_WARPS * 4096 + 1024;
-constexpr uint32_t P4_TMEM_COLS = 512;                      // 256 accumulator + 16 SFA + 32 SFB, power of two
-constexpr uint32_t P4_TMEM_SFA = 256, P4_TMEM_SFB = 272;    // one set: scale copies and MMAs execute in issue order
+constexpr uint32_t P4_TMEM_COLS = 512;                     // 256 accumulator + 3 x 48 scale-factor columns, power of two
+constexpr int P4_SF_SETS = 3;                              // scale-factor column sets in rotation
+constexpr uint32_t P4_TMEM_SF = 256, P4_SF_SET_COLS = 48;  // per set: SFA 16 columns, then SFB 32
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P4_THREADS, 1)
 gemm_fp4_pair_kernel(const __grid_constant__ Fp4Params p, const int row_tiles, const int tok_tiles) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bars[3 * P4_STAGES + 2];
+    __shared__ __align__(8) uint64_t bars[3 * P4_STAGES + 2 * P4_SF_SETS + 2];
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s;
     const uint32_t smem_s = (tc::smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t full = tc::smem_u32(&bars[0]), empty = tc::smem_u32(&bars[P4_STAGES]), full2 = tc::smem_u32(&bars[2 * P4_STAGES]);
-    const uint32_t accum_full = tc::smem_u32(&bars[3 * P4_STAGES]), accum_empty = tc::smem_u32(&bars[3 * P4_STAGES + 1]);
+    const uint32_t sf_full = tc::smem_u32(&bars[3 * P4_STAGES]), sf_empty = tc::smem_u32(&bars[3 * P4_STAGES + P4_SF_SETS]);
+    const uint32_t accum_full = tc::smem_u32(&bars[3 * P4_STAGES + 2 * P4_SF_SETS]), accum_empty = accum_full + 8;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = tc::cluster_ctarank();
     const int pair = (int)(blockIdx.x >> 1), npairs = (int)(gridDim.x >> 1);
@@ -244,6 +254,10 @@ gemm_fp4_pair_kernel(const __grid_constant__ Fp4Params p, const int row_tiles, c
             tc::mbar_init(full + 8 * s, 1);
             tc::mbar_init(empty + 8 * s, 1);
             tc::mbar_init(full2 + 8 * s, 1);
+        }
+        for (int s = 0; s < P4_SF_SETS; s++) {
+            tc::mbar_init(sf_full + 8 * s, 2 * P4_SF_WARPS);  // the scale warps of both CTAs (used in the leader only)
+            tc::mbar_init(sf_empty + 8 * s, 1);
         }
         tc::mbar_init(accum_full, 1);
         tc::mbar_init(accum_empty, 2 * P4_EPI_WARPS);
@@ -309,7 +323,7 @@ gemm_fp4_pair_kernel(const __grid_constant__ Fp4Params p, const int row_tiles, c
                 tc::mbar_arrive_cluster(tc::map_to_cta(full2 + 8 * s, 0));
             }
     } else if (warp == 1 && lane == 0) {
-        // ---------------- leader CTA: scale copies + MMA issue for the pair ----------------
+        // ---------------- leader CTA: MMA issue for the pair ----------------
         const uint32_t idesc_nv = tc::idesc_fp4(256, 256, 0, 0, 0);
         uint32_t g = 0, it = 0;
         for (int t = pair; t < ntiles && !*abort_flag; t += npairs, it++) {
@@ -323,7 +337,10 @@ gemm_fp4_pair_kernel(const __grid_constant__ Fp4Params p, const int row_tiles, c
             bool ok = true;
             for (int ks = 0; ks < nks; ks++, g++) {
                 const uint32_t s = g % P4_STAGES, ph = (g / P4_STAGES) & 1u;
-                if (!tc::mbar_wait(full + 8 * s, ph, abort_flag) || !tc::mbar_wait_cluster(full2 + 8 * s, ph, abort_flag)) {
+                const uint32_t b = g % P4_SF_SETS, bph = (g / P4_SF_SETS) & 1u;
+                // both CTAs' operand tiles have landed, and both CTAs' scale warps have filled column set b
+                if (!tc::mbar_wait(full + 8 * s, ph, abort_flag) || !tc::mbar_wait_cluster(full2 + 8 * s, ph, abort_flag) ||
+                    !tc::mbar_wait_cluster(sf_full + 8 * b, bph, abort_flag)) {
                     abort_s = 1;
                     atomicExch(p.status, 22);
                     ok = false;
@@ -331,45 +348,74 @@ gemm_fp4_pair_kernel(const __grid_constant__ Fp4Params p, const int row_tiles, c
                 }
                 tc::fence_after_sync();
                 const uint32_t st = smem_s + s * P4_STAGE_BYTES;
-                const uint32_t sfa = st + P4_A_BYTES + P4_B_BYTES, sfb = sfa + P4_SFA_BYTES;
                 const uint64_t ad = tc::smem_desc_sw128(st), bd = tc::smem_desc_sw128(st + P4_A_BYTES);
+                const uint32_t tsfa = tmem + P4_TMEM_SF + P4_SF_SET_COLS * b, tsfb = tsfa + 16;
                 if (p.nv) {
 #pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        tc::tmem_cp_sf_pair(tmem + P4_TMEM_SFA + 4 * j, sf_desc(sfa + 512 * j));
-                        tc::tmem_cp_sf_pair(tmem + P4_TMEM_SFB + 8 * j, sf_desc(sfb + 512 * j));
-                        tc::tmem_cp_sf_pair(tmem + P4_TMEM_SFB + 8 * j + 4, sf_desc(sfb + 2048 + 512 * j));
-                    }
-#pragma unroll
                     for (int j = 0; j < 4; j++)
-                        tc::mma_nvf4_pair(tmem, ad + 2 * j, bd + 2 * j, idesc_nv, (uint32_t)((ks | j) != 0), tmem + P4_TMEM_SFA + 4 * j,
-                                          tmem + P4_TMEM_SFB + 8 * j);
+                        tc::mma_nvf4_pair(tmem, ad + 2 * j, bd + 2 * j, idesc_nv, (uint32_t)((ks | j) != 0), tsfa + 4 * j, tsfb + 8 * j);
                 } else {
-#pragma unroll
-                    for (int j = 0; j < 2; j++) {
-                        tc::tmem_cp_sf_pair(tmem + P4_TMEM_SFA + 4 * j, sf_desc(sfa + 512 * j));
-                        tc::tmem_cp_sf_pair(tmem + P4_TMEM_SFB + 8 * j, sf_desc(sfb + 512 * j));
-                        tc::tmem_cp_sf_pair(tmem + P4_TMEM_SFB + 8 * j + 4, sf_desc(sfb + 2048 + 512 * j));
-                    }
 #pragma unroll
                     for (int j = 0; j < 4; j++) {
                         const int id = (j & 1) * 2;
                         tc::mma_mxf4_pair(tmem, ad + 2 * j, bd + 2 * j, tc::idesc_fp4(256, 256, 1, id, id), (uint32_t)((ks | j) != 0),
-                                          tmem + P4_TMEM_SFA + 4 * (j >> 1), tmem + P4_TMEM_SFB + 8 * (j >> 1));
+                                          tsfa + 4 * (j >> 1), tsfb + 8 * (j >> 1));
                     }
                 }
-                // stage s is free in BOTH CTAs once these MMAs have read it
+                // once these MMAs have completed, stage s and column set b are free in BOTH CTAs
                 tc::mma_commit_pair(empty + 8 * s);
                 tc::mma_commit_pair(tc::map_to_cta(empty + 8 * s, 1));
+                tc::mma_commit_pair(sf_empty + 8 * b);
+                tc::mma_commit_pair(tc::map_to_cta(sf_empty + 8 * b, 1));
             }
             if (!ok) break;
             tc::mma_commit_pair(accum_full);
             tc::mma_commit_pair(tc::map_to_cta(accum_full, 1));
         }
+    } else if (warp >= 2 + P4_EPI_WARPS) {
+        // ---------------- scale warps: stage -> tensor memory, lane quadrant warp % 4 ----------------
+        // Atom = 128 rows x 4 scales as 512 bytes: row r's four bytes at (r % 32) * 16 + (r / 32) * 4.  Lane l reads
+        // its 16 bytes (the scales of rows l, l + 32, l + 64, l + 96) and writes them to four columns of its own lane:
+        // SFA atom j -> columns 4j; SFB atom j of token half h -> columns 16 + 8j + 4h.
+        const uint32_t quad_lane = (uint32_t)(32 * (warp & 3)) << 16;
+        const uint32_t sf_full_leader = tc::map_to_cta(sf_full, 0);
+        uint32_t g = 0;
+        bool ok = true;
+        for (int t = pair; t < ntiles && ok; t += npairs)
+            for (int ks = 0; ks < nks; ks++, g++) {
+                const uint32_t s = g % P4_STAGES, b = g % P4_SF_SETS;
+                ok = tc::mbar_wait(full + 8 * s, (g / P4_STAGES) & 1u, abort_flag) &&
+                     (g < P4_SF_SETS || tc::mbar_wait_cluster(sf_empty + 8 * b, (g / P4_SF_SETS - 1) & 1u, abort_flag));
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) {
+                    if (lane == 0 && !abort_s) {
+                        abort_s = 1;
+                        atomicExch(p.status, 28);
+                    }
+                    break;
+                }
+                tc::fence_after_sync();
+                const uint32_t sfa = smem_s + s * P4_STAGE_BYTES + P4_A_BYTES + P4_B_BYTES + 16u * (uint32_t)lane, sfb = sfa + P4_SFA_BYTES;
+                const uint32_t tsfa = tmem + quad_lane + P4_TMEM_SF + P4_SF_SET_COLS * b, tsfb = tsfa + 16;
+                for (int j = 0; j < atoms_per_stage; j++) {
+                    uint4 v;
+                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(sfa + 512u * j));
+                    tc::tmem_st4(tsfa + 4 * j, v.x, v.y, v.z, v.w);
+#pragma unroll
+                    for (int h = 0; h < 2; h++) {
+                        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(sfb + 2048u * h + 512u * j));
+                        tc::tmem_st4(tsfb + 8 * j + 4 * h, v.x, v.y, v.z, v.w);
+                    }
+                }
+                tc::tmem_st_wait();
+                tc::fence_before_sync();
+                __syncwarp();
+                if (lane == 0) tc::mbar_arrive_cluster(sf_full_leader + 8 * b);
+            }
     }
     __syncwarp();
 
-    if (warp >= 2) {
+    if (warp >= 2 && warp < 2 + P4_EPI_WARPS) {
         // ---------------- epilogue: this CTA's 128 rows x 256 tokens; warp w reads TMEM lane quadrant w % 4 ----------------
         const int quad = warp & 3, half = (warp - 2) >> 2;
         uint8_t *stage = smem_raw + (smem_s - tc::smem_u32(smem_raw)) + (size_t)P4_STAGES * P4_STAGE_BYTES + (size_t)(warp - 2) * 4096;
@@ -418,16 +464,19 @@ gemm_fp4_pair_kernel(const __grid_constant__ Fp4Params p, const int row_tiles, c
 // ring of four barriers like the real pipelines.  What this reaches is the most the GEMM kernels can: it is the
 // denominator bench.py reports beside the nominal 9 PFLOP/s.
 // ---------------------------------------------------------------------------------------------
+// sf_mode: 0 = no scale-factor traffic, 1 = twelve (six for MXFP4) tcgen05.cp per k-step issued by the MMA thread,
+// 2 = the scale factors written by four scale warps with tcgen05.st into three column sets in rotation, as in
+// gemm_fp4_pair_kernel.
 template <bool PAIR>
-__device__ __forceinline__ void probe_body(int nv, int with_cp, int ksteps, int *status) {
+__device__ __forceinline__ void probe_body(int nv, int sf_mode, int ksteps, int *status) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bars[4];
+    __shared__ __align__(8) uint64_t bars[4 + 6];
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s;
     const uint32_t smem_s = (tc::smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *smem = smem_raw + (smem_s - tc::smem_u32(smem_raw));
-    const int warp = threadIdx.x >> 5;
-    const uint32_t bar0 = tc::smem_u32(&bars[0]);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t bar0 = tc::smem_u32(&bars[0]), sf_full = tc::smem_u32(&bars[4]), sf_empty = tc::smem_u32(&bars[7]);
     const uint32_t rank = PAIR ? tc::cluster_ctarank() : 0u;
     constexpr int A = 16384, B = PAIR ? 16384 : 32768, SFA = 2048, SFB = 4096;
     // operands: every E2M1 code, scale bytes 0x38 (UE4M3 1.0; as UE8M0 2^-71: still finite)
@@ -436,6 +485,10 @@ __device__ __forceinline__ void probe_body(int nv, int with_cp, int ksteps, int 
     if (threadIdx.x == 0) {
         abort_s = 0;
         for (int s = 0; s < 4; s++) tc::mbar_init(bar0 + 8 * s, 1);
+        for (int s = 0; s < 3; s++) {
+            tc::mbar_init(sf_full + 8 * s, PAIR ? 8 : 4);
+            tc::mbar_init(sf_empty + 8 * s, 1);
+        }
         tc::mbar_init_fence();
     }
     tc::fence_proxy_async();
@@ -449,50 +502,94 @@ __device__ __forceinline__ void probe_body(int nv, int with_cp, int ksteps, int 
     tc::fence_after_sync();
     const uint32_t tmem = tmem_base_s;
     volatile int *abort_flag = &abort_s;
+    const int atoms = nv ? 4 : 2;
+    const uint32_t sfa = smem_s + A + B, sfb = sfa + SFA;
     if (threadIdx.x == 32 && rank == 0) {
         const uint64_t ad = tc::smem_desc_sw128(smem_s), bd = tc::smem_desc_sw128(smem_s + A);
-        const uint32_t sfa = smem_s + A + B, sfb = sfa + SFA;
         const uint32_t idesc_nv = tc::idesc_fp4(PAIR ? 256 : 128, 256, 0, 0, 0);
         for (int ks = 0; ks < ksteps; ks++) {
             const int s = ks & 3;
-            if (ks >= 4 && !tc::mbar_wait(bar0 + 8 * s, (uint32_t)((ks / 4 - 1) & 1), abort_flag)) {
+            const uint32_t b = sf_mode == 2 ? (uint32_t)(ks % 3) : 0u;
+            if ((ks >= 4 && !tc::mbar_wait(bar0 + 8 * s, (uint32_t)((ks / 4 - 1) & 1), abort_flag)) ||
+                (sf_mode == 2 && !tc::mbar_wait_cluster(sf_full + 8 * b, (uint32_t)((ks / 3) & 1), abort_flag))) {
+                abort_s = 1;
                 atomicExch(status, 27);
                 break;
             }
-            const int atoms = nv ? 4 : 2;
-            if (with_cp)
+            tc::fence_after_sync();
+            const uint32_t tsfa = tmem + 256 + 48 * b, tsfb = tsfa + 16;
+            if (sf_mode == 1)
                 for (int j = 0; j < atoms; j++) {
                     if (PAIR) {
-                        tc::tmem_cp_sf_pair(tmem + 256 + 4 * j, sf_desc(sfa + 512 * j));
-                        tc::tmem_cp_sf_pair(tmem + 272 + 8 * j, sf_desc(sfb + 512 * j));
-                        tc::tmem_cp_sf_pair(tmem + 272 + 8 * j + 4, sf_desc(sfb + 2048 + 512 * j));
+                        tc::tmem_cp_sf_pair(tsfa + 4 * j, sf_desc(sfa + 512 * j));
+                        tc::tmem_cp_sf_pair(tsfb + 8 * j, sf_desc(sfb + 512 * j));
+                        tc::tmem_cp_sf_pair(tsfb + 8 * j + 4, sf_desc(sfb + 2048 + 512 * j));
                     } else {
-                        tc::tmem_cp_sf(tmem + 256 + 4 * j, sf_desc(sfa + 512 * j));
-                        tc::tmem_cp_sf(tmem + 272 + 8 * j, sf_desc(sfb + 512 * j));
-                        tc::tmem_cp_sf(tmem + 272 + 8 * j + 4, sf_desc(sfb + 2048 + 512 * j));
+                        tc::tmem_cp_sf(tsfa + 4 * j, sf_desc(sfa + 512 * j));
+                        tc::tmem_cp_sf(tsfb + 8 * j, sf_desc(sfb + 512 * j));
+                        tc::tmem_cp_sf(tsfb + 8 * j + 4, sf_desc(sfb + 2048 + 512 * j));
                     }
                 }
 #pragma unroll
             for (int j = 0; j < 4; j++) {
                 if (nv) {
-                    if (PAIR) tc::mma_nvf4_pair(tmem, ad + 2 * j, bd + 2 * j, idesc_nv, (uint32_t)((ks | j) != 0), tmem + 256 + 4 * j, tmem + 272 + 8 * j);
-                    else tc::mma_nvf4(tmem, ad + 2 * j, bd + 2 * j, idesc_nv, (uint32_t)((ks | j) != 0), tmem + 256 + 4 * j, tmem + 272 + 8 * j);
+                    if (PAIR) tc::mma_nvf4_pair(tmem, ad + 2 * j, bd + 2 * j, idesc_nv, (uint32_t)((ks | j) != 0), tsfa + 4 * j, tsfb + 8 * j);
+                    else tc::mma_nvf4(tmem, ad + 2 * j, bd + 2 * j, idesc_nv, (uint32_t)((ks | j) != 0), tsfa + 4 * j, tsfb + 8 * j);
                 } else {
                     const int id = (j & 1) * 2;
                     const uint32_t idm = tc::idesc_fp4(PAIR ? 256 : 128, 256, 1, id, id);
-                    if (PAIR) tc::mma_mxf4_pair(tmem, ad + 2 * j, bd + 2 * j, idm, (uint32_t)((ks | j) != 0), tmem + 256 + 4 * (j >> 1), tmem + 272 + 8 * (j >> 1));
-                    else tc::mma_mxf4(tmem, ad + 2 * j, bd + 2 * j, idm, (uint32_t)((ks | j) != 0), tmem + 256 + 4 * (j >> 1), tmem + 272 + 8 * (j >> 1));
+                    if (PAIR) tc::mma_mxf4_pair(tmem, ad + 2 * j, bd + 2 * j, idm, (uint32_t)((ks | j) != 0), tsfa + 4 * (j >> 1), tsfb + 8 * (j >> 1));
+                    else tc::mma_mxf4(tmem, ad + 2 * j, bd + 2 * j, idm, (uint32_t)((ks | j) != 0), tsfa + 4 * (j >> 1), tsfb + 8 * (j >> 1));
                 }
             }
-            if (PAIR) tc::mma_commit_pair(bar0 + 8 * s);
-            else tc::mma_commit(bar0 + 8 * s);
+            if (PAIR) {
+                tc::mma_commit_pair(bar0 + 8 * s);
+                if (sf_mode == 2) {
+                    tc::mma_commit_pair(sf_empty + 8 * b);
+                    tc::mma_commit_pair(tc::map_to_cta(sf_empty + 8 * b, 1));
+                }
+            } else {
+                tc::mma_commit(bar0 + 8 * s);
+                if (sf_mode == 2) tc::mma_commit(sf_empty + 8 * b);
+            }
         }
         // drain: the last commits
-        for (int ks = max(ksteps - 4, 0); ks < ksteps; ks++)
+        for (int ks = max(ksteps - 4, 0); ks < ksteps && !abort_s; ks++)
             if (!tc::mbar_wait(bar0 + 8 * (ks & 3), (uint32_t)((ks / 4) & 1), abort_flag)) {
+                abort_s = 1;
                 atomicExch(status, 27);
+            }
+    } else if (warp >= 2 && sf_mode == 2) {
+        const uint32_t quad_lane = (uint32_t)(32 * (warp & 3)) << 16;
+        const uint32_t sf_full_leader = PAIR ? tc::map_to_cta(sf_full, 0) : sf_full;
+        for (int ks = 0; ks < ksteps; ks++) {
+            const uint32_t b = (uint32_t)(ks % 3);
+            bool ok = ks < 3 || tc::mbar_wait_cluster(sf_empty + 8 * b, (uint32_t)((ks / 3 - 1) & 1), abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) {
+                if (lane == 0) atomicExch(status, 27);
                 break;
             }
+            tc::fence_after_sync();
+            const uint32_t tsfa = tmem + quad_lane + 256 + 48 * b, tsfb = tsfa + 16;
+            for (int j = 0; j < atoms; j++) {
+                uint4 v;
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(sfa + 16u * lane + 512u * j));
+                tc::tmem_st4(tsfa + 4 * j, v.x, v.y, v.z, v.w);
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(sfb + 16u * lane + 2048u * h + 512u * j));
+                    tc::tmem_st4(tsfb + 8 * j + 4 * h, v.x, v.y, v.z, v.w);
+                }
+            }
+            tc::tmem_st_wait();
+            tc::fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+                if (PAIR) tc::mbar_arrive_cluster(sf_full_leader + 8 * b);
+                else tc::mbar_arrive(sf_full + 8 * b);
+            }
+        }
     }
     tc::fence_before_sync();
     __syncthreads();
@@ -502,9 +599,9 @@ __device__ __forceinline__ void probe_body(int nv, int with_cp, int ksteps, int 
         else tc::tmem_dealloc(tmem, 512);
     }
 }
-__global__ void __launch_bounds__(128, 1) probe_fp4_single_kernel(int nv, int with_cp, int ksteps, int *status) { probe_body<false>(nv, with_cp, ksteps, status); }
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(128, 1) probe_fp4_pair_kernel(int nv, int with_cp, int ksteps, int *status) {
-    probe_body<true>(nv, with_cp, ksteps, status);
+__global__ void __launch_bounds__(192, 1) probe_fp4_single_kernel(int nv, int sf_mode, int ksteps, int *status) { probe_body<false>(nv, sf_mode, ksteps, status); }
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1) probe_fp4_pair_kernel(int nv, int sf_mode, int ksteps, int *status) {
+    probe_body<true>(nv, sf_mode, ksteps, status);
 }
 
 int32_t probe_fp4_mma(Ctx *c, int pair, int with_cp, int nv, int ksteps, float *tflops) {
@@ -520,8 +617,8 @@ int32_t probe_fp4_mma(Ctx *c, int pair, int with_cp, int nv, int ksteps, float *
     float best = 0.f;
     for (int rep = 0; rep < 4; rep++) {
         cudaEventRecord(e0, c->stream);
-        if (pair) probe_fp4_pair_kernel<<<grid, 128, smem_req, c->stream>>>(nv, with_cp, ksteps, c->status_dev);
-        else probe_fp4_single_kernel<<<grid, 128, smem_req, c->stream>>>(nv, with_cp, ksteps, c->status_dev);
+        if (pair) probe_fp4_pair_kernel<<<grid, 192, smem_req, c->stream>>>(nv, with_cp, ksteps, c->status_dev);
+        else probe_fp4_single_kernel<<<grid, 192, smem_req, c->stream>>>(nv, with_cp, ksteps, c->status_dev);
         cudaEventRecord(e1, c->stream);
         cudaError_t e = cudaStreamSynchronize(c->stream);
         if (e == cudaSuccess) e = cudaGetLastError();

@@ -951,9 +951,13 @@ int32_t gemv_launch(Ctx *c, const Weight *w, const float *x, int64_t xst, int64_
     const int64_t ntg = w->n_pad / 128;
     const int NT = (2 * m + 7) / 8;
     // Small shares: the GEMV converts its activation slices itself and the staging kernel is not launched at all.
+    // (Measured on one GPU the two-kernel form is as fast or faster even for small matrices — its staging kernel runs
+    // under the previous product's tail — so by default only exchange products fuse: there the staging kernel would
+    // also have to carry the wait for the other ranks.)
     int fuse = 0;
-    if (NT == 1 && w->qt == GLLMK_QUANT_Q4K) GK_CUDA(c, gemv_fuse_plan<FMT_Q4K>(c, m, ntg, nk, &fuse));
-    else if (NT == 1 && w->qt == GLLMK_QUANT_Q8_0) GK_CUDA(c, gemv_fuse_plan<FMT_Q80>(c, m, ntg, nk, &fuse));
+    const bool want_fuse = c->gemv_fuse == 2 || (c->gemv_fuse == 1 && xch != nullptr);
+    if (want_fuse && NT == 1 && w->qt == GLLMK_QUANT_Q4K) GK_CUDA(c, gemv_fuse_plan<FMT_Q4K>(c, m, ntg, nk, &fuse));
+    else if (want_fuse && NT == 1 && w->qt == GLLMK_QUANT_Q8_0) GK_CUDA(c, gemv_fuse_plan<FMT_Q80>(c, m, ntg, nk, &fuse));
     if (!fuse) GK_CUDA(c, launch_pdl(stage_x_kernel, sgrid, 256, 0, s, c->gemv_pdl != 0, sp));
 
     cudaError_t e;

@@ -331,9 +331,9 @@ class GpuKernels:
                                                  min(num_experts, (1 << 31) - 1), _stream(stream)), "gllmk_moe_weighted_sum")
         return out
 
-    def probe_fp4_mma(self, cta_pair: bool = True, with_scale_copies: bool = True, nvfp4: bool = True, ksteps: int = 4096) -> float:
+    def probe_fp4_mma(self, cta_pair: bool = True, with_scale_copies: int = 2, nvfp4: bool = True, ksteps: int = 4096) -> float:
         """TFLOP/s of the block-scaled FP4 MMA issued back to back on shared-memory operands (the practical ceiling of
-        gemm_fp4 on this device)."""
+        gemm_fp4 on this device).  with_scale_copies: 0 none, 1 tcgen05.cp per k-step, 2 tcgen05.st by scale warps."""
         v = C.c_float()
         self._check(lib().gllmk_probe_fp4_mma(self._ctx, int(cta_pair), int(with_scale_copies), int(nvfp4), ksteps, C.byref(v)),
                     "gllmk_probe_fp4_mma")

@@ -154,7 +154,10 @@ GLLMK_API int32_t gllmk_ctx_status(gllmk_ctx ctx, int32_t *device_status);
 /* Tuning knobs, for experiments.  key: "gemv_ctas_per_sm" (resident CTAs per SM the decode grid is
  * sized for; 0 = occupancy limit), "gemv_pdl" (1 = overlap the activation staging kernel with the
  * weight stream), "gemv_fp4_int" (1 = decode MXFP4 / NVFP4 weights on the integer-decode kernel instead of
- * the block-scaled tensor-core one), "peer_wait_spins" (how many times a wait on another GPU's flag probes it
+ * the block-scaled tensor-core one), "gemv_fuse" (decode GEMV converting its own activation slices instead of a staging launch when a
+ * block's share is small: 0 never, 1 products of an exchange chain only, 2 every product), "gemm_fp4_pair" (0: the one-CTA
+ * FP4 x FP4 kernel instead of the CTA-pair one), "gemm_tail_split" (prefill GEMM, last partial wave of tiles cut along k:
+ * 0 automatic, 1 never, n into n), "peer_wait_spins" (how many times a wait on another GPU's flag probes it
  * before it gives up with status 31; default 2^22, about a second), "inject_give_up" (testing aid, host side
  * only: leaves the context as a kernel that gave up a wait with that status code would — word set, arrival
  * counters dirty — without making any kernel wait). */
@@ -371,8 +374,9 @@ GLLMK_API int32_t gllmk_gemm_fp4(gllmk_ctx ctx, gllmk_weight w, gllmk_weight x, 
 
 /* Measurement aid, no counterpart in the reference: the block-scaled FP4 MMA of gllmk_gemm_fp4 (kind::mxf4nvf4 scale_vec::4X
  * for nvfp4 != 0, kind::mxf4 scale_vec::2X otherwise; one CTA per SM, or CTA pairs with cta_pair != 0) issued back to
- * back on operands parked in shared memory, with or without the per-k-step scale-factor copies to tensor memory.
- * Writes the TFLOP/s reached (best of three timed launches of `ksteps` k-steps of 256 per CTA): the practical ceiling
+ * back on operands parked in shared memory.  with_scale_copies: 0 = no scale-factor traffic, 1 = the scale atoms copied to
+ * tensor memory by tcgen05.cp from the MMA thread every k-step (what the one-CTA kernel does), 2 = written by four scale
+ * warps with tcgen05.st into rotating column sets (what the CTA-pair kernel does).  Writes the TFLOP/s reached (best of three timed launches of `ksteps` k-steps of 256 per CTA): the practical ceiling
  * of the FP4 x FP4 GEMM on this device, which bench.py reports as the denominator beside the nominal peak.
  * Synchronous on the context's own stream. */
 GLLMK_API int32_t gllmk_probe_fp4_mma(gllmk_ctx ctx, int32_t cta_pair, int32_t with_scale_copies, int32_t nvfp4, int32_t ksteps, float *tflops);

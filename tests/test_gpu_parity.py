@@ -432,14 +432,15 @@ def test_gemv_fused_staging_equals_the_staging_kernel(gk, K, oracle, torch, fmt,
     K.set("gemv_fuse", 0)
     try:
         y_img = K.gemv(w, x).clone()
+        K.set("gemv_fuse", 2)  # every product (the default fuses only the products of a multi-GPU exchange chain)
+        y_fused = K.gemv(w, x).clone()
+        y_ref_layout = K.gemv(w, x.t().contiguous(), ref_layout=True)
     finally:
         K.set("gemv_fuse", 1)
-    y_fused = K.gemv(w, x)
     assert K.status() == 0
     assert torch.equal(y_img, y_fused)
     ref = oracle.quant_matmul(blocks, np.ascontiguousarray(x.cpu().numpy().T), oid, n, m, k, threads=8).T
     assert oracle.rel_err(y_fused.cpu().numpy(), ref) <= TOL
-    # strided x (the reference's [k, m] layout) goes through the same fused path
-    y_ref_layout = K.gemv(w, x.t().contiguous(), ref_layout=True)
+    # strided x (the reference's [k, m] layout) went through the same fused path
     assert torch.equal(y_ref_layout.t().contiguous(), y_fused)
     w.free()
