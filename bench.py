@@ -168,6 +168,8 @@ def run_ours(args):
     K = gk.GpuKernels(local)
     if args.gemv_ctas_per_sm:
         K.set("gemv_ctas_per_sm", args.gemv_ctas_per_sm)
+    if args.gemv_fuse >= 0:
+        K.set("gemv_fuse", args.gemv_fuse)
     qt = gk.QuantType.q4k()
     M, L = args.m, args.layers
 
@@ -1029,6 +1031,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--separate-gate-up", action="store_true", help="keep gate and up as two weights (3 products per layer)")
     ap.add_argument("--gemv-ctas-per-sm", type=int, default=0, help="tuning knob: resident GEMV CTAs per SM (0 = occupancy limit)")
+    ap.add_argument("--gemv-fuse", type=int, default=-1,
+                    help="tuning knob: decode GEMV converting its own activation slices (0 never, 1 exchange products, 2 always; -1 = library default)")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying a CUDA graph")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="N > 1: how the bands of y reach every rank (peer stores fused into the GEMV, or NCCL all-gather)")

@@ -1,5 +1,7 @@
 // extern "C" boundary of libgllmk.so (declared in include/gllmk.h).  Argument validation happens
 // here, before any launch; nothing below throws.
+#include <cuda_bf16.h>
+
 #include <vector>
 
 #include "common.cuh"
@@ -406,6 +408,33 @@ int32_t gllmk_ffn_decode(gllmk_ctx ctx, gllmk_weight w_gate_up, gllmk_weight w_d
     if (rc) return rc;
     // y = W_down (silu(gate) * up): the activation staging of the second product applies SwiGLU while it reads h
     return gemv_launch(c, wd, h_dev, 2 * f, 1, m, y_dev, wd->n, 1, nullptr, 0, s, nullptr, 0, h_dev + f);
+}
+
+int32_t gllmk_ffn_prefill(gllmk_ctx ctx, gllmk_weight w_gate_up, gllmk_weight w_down, const void *x_dev, int32_t x_dtype, int64_t ldx,
+                          int32_t m, void *h_dev, void *y_dev, int32_t y_dtype, int64_t ldy, void *stream) {
+    if (!ctx || !w_gate_up || !w_down || !x_dev || !h_dev || !y_dev) return GLLMK_STATUS_INVALID_ARG;
+    Ctx *c = static_cast<Ctx *>(ctx);
+    const Weight *wg = static_cast<const Weight *>(w_gate_up), *wd = static_cast<const Weight *>(w_down);
+    if (m < 1) return fail(c, GLLMK_STATUS_INVALID_ARG, "ffn_prefill: m must be positive");
+    if ((x_dtype != GLLMK_DTYPE_F32 && x_dtype != GLLMK_DTYPE_BF16) || (y_dtype != GLLMK_DTYPE_F32 && y_dtype != GLLMK_DTYPE_BF16))
+        return fail(c, GLLMK_STATUS_UNSUPPORTED, "ffn_prefill: dtype must be f32 or bf16");
+    if (wg->n % 2 || wg->n / 2 != wd->k || wd->n != wg->k)
+        return fail(c, GLLMK_STATUS_INVALID_ARG, "ffn_prefill: shapes do not chain: gate||up [%lld, %lld], down [%lld, %lld]", (long long)wg->n,
+                    (long long)wg->k, (long long)wd->n, (long long)wd->k);
+    if (raw_format(wg->qt) || raw_format(wd->qt) || wg->qt == GLLMK_QUANT_INT8 || wd->qt == GLLMK_QUANT_INT8)
+        return fail(c, GLLMK_STATUS_UNSUPPORTED, "ffn_prefill: weight type has no tensor-core prefill kernel");
+    const int64_t f = wd->k;
+    if (f % 8) return fail(c, GLLMK_STATUS_INVALID_ARG, "ffn_prefill: the intermediate width must be a multiple of 8");
+    if (ldx < wg->k || ldy < wd->n) return fail(c, GLLMK_STATUS_INVALID_ARG, "ffn_prefill: leading dimension smaller than the row");
+    if (wg->device != c->device || wd->device != c->device) return fail(c, GLLMK_STATUS_INVALID_ARG, "weight lives on another device");
+    DeviceGuard g(c->device);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // h = [gate | up] = W_gate_up x, kept in bf16: [m, 2f]
+    int32_t rc = gemm_launch(c, wg, x_dev, x_dtype == GLLMK_DTYPE_BF16, ldx, m, h_dev, 1, 2 * f, s);
+    if (rc) return rc;
+    // y = W_down (silu(gate) * up): SwiGLU is applied by the second product's activation staging while it reads h
+    return gemm_launch(c, wd, h_dev, 1, 2 * f, m, y_dev, y_dtype == GLLMK_DTYPE_BF16, ldy, s,
+                       static_cast<const __nv_bfloat16 *>(h_dev) + f);
 }
 
 int32_t gllmk_gemv_allgather(gllmk_ctx ctx, gllmk_weight wh, const float *x_dev, int64_t x_stride_t, int64_t x_stride_k, int32_t m,

@@ -153,10 +153,11 @@ int32_t gemv_launch(Ctx *c, const Weight *w, const float *x, int64_t xst, int64_
                     int n_peers = 0, const float *x_up = nullptr, const Exchange *xch = nullptr);
 size_t gemv_ws_bytes(const Weight *w, int m);
 // ---- gemm.cu ----
+// a_up != nullptr: the activation matrix is silu(a) * a_up (same dtype / leading dimension), applied while staging
 int32_t gemm_launch(Ctx *c, const Weight *w, const void *a, int a_bf16, int64_t lda, int m, void *y, int y_bf16, int64_t ldy,
-                    cudaStream_t s);
+                    cudaStream_t s, const void *a_up = nullptr);
 int32_t gemm_grouped_launch(Ctx *c, const Weight *const *ws, int n_groups, const void *a, int a_bf16, int64_t lda,
-                            const int64_t *row_offsets, void *y, int y_bf16, int64_t ldy, cudaStream_t s);
+                            const int64_t *row_offsets, void *y, int y_bf16, int64_t ldy, cudaStream_t s, const void *a_up = nullptr);
 // ---- gemm_fp4.cu ----
 int32_t gemm_fp4_launch(Ctx *c, const Weight *w, const Weight *x, void *y, int y_bf16, int64_t ldy, cudaStream_t s);
 int32_t probe_fp4_mma(Ctx *c, int pair, int with_cp, int nv, int ksteps, float *tflops);

@@ -83,8 +83,12 @@ struct GemmParams {
 
 // ---- activations -> fp16 tile images ------------------------------------------------------------
 // grid (k-steps, images of 128 rows); rows past an image's count and k >= k_valid are zero
+// a_up != nullptr: the activation is silu(a) * a_up (SwiGLU of the two halves of a gate || up product, same dtype and
+// leading dimension), evaluated in f32 as scalar_swiglu does (scalar-ops/src/activations.rs:57-66) before the fp16 rounding
+__device__ __forceinline__ float swiglu_f32(float g, float u) { return (g / (1.0f + expf(-g))) * u; }
 __global__ void __launch_bounds__(256) stage_act_kernel(const void *__restrict__ a, int a_bf16, int64_t lda, int64_t k_valid,
-                                                        uint8_t *__restrict__ xt, const __grid_constant__ ImgTiles imgs) {
+                                                        uint8_t *__restrict__ xt, const __grid_constant__ ImgTiles imgs,
+                                                        const void *__restrict__ a_up) {
     const int ks = blockIdx.x, tile = blockIdx.y;
     const int64_t img_tok0 = imgs.tok0[tile];
     const int img_cnt = imgs.cnt[tile];
@@ -100,13 +104,30 @@ __global__ void __launch_bounds__(256) stage_act_kernel(const void *__restrict__
                 const uint4 v = __ldg(reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(a) + tok * lda + k0));
                 const uint32_t w[4] = {v.x, v.y, v.z, v.w};
                 uint32_t r[4];
+                if (a_up) {
+                    const uint4 vu = __ldg(reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(a_up) + tok * lda + k0));
+                    const uint32_t wu[4] = {vu.x, vu.y, vu.z, vu.w};
 #pragma unroll
-                for (int q = 0; q < 4; q++)
-                    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;\n" : "=r"(r[q]) : "f"(__uint_as_float(w[q] & 0xFFFF0000u)), "f"(__uint_as_float(w[q] << 16)));
+                    for (int q = 0; q < 4; q++) {
+                        const float lo = swiglu_f32(__uint_as_float(w[q] << 16), __uint_as_float(wu[q] << 16));
+                        const float hi = swiglu_f32(__uint_as_float(w[q] & 0xFFFF0000u), __uint_as_float(wu[q] & 0xFFFF0000u));
+                        asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;\n" : "=r"(r[q]) : "f"(hi), "f"(lo));
+                    }
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 4; q++)
+                        asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;\n" : "=r"(r[q]) : "f"(__uint_as_float(w[q] & 0xFFFF0000u)), "f"(__uint_as_float(w[q] << 16)));
+                }
                 o = make_uint4(r[0], r[1], r[2], r[3]);
             } else {
                 const float4 *src = reinterpret_cast<const float4 *>(static_cast<const float *>(a) + tok * lda + k0);
-                const float4 x0 = __ldg(src), x1 = __ldg(src + 1);
+                float4 x0 = __ldg(src), x1 = __ldg(src + 1);
+                if (a_up) {
+                    const float4 *su = reinterpret_cast<const float4 *>(static_cast<const float *>(a_up) + tok * lda + k0);
+                    const float4 u0 = __ldg(su), u1 = __ldg(su + 1);
+                    x0 = make_float4(swiglu_f32(x0.x, u0.x), swiglu_f32(x0.y, u0.y), swiglu_f32(x0.z, u0.z), swiglu_f32(x0.w, u0.w));
+                    x1 = make_float4(swiglu_f32(x1.x, u1.x), swiglu_f32(x1.y, u1.y), swiglu_f32(x1.z, u1.z), swiglu_f32(x1.w, u1.w));
+                }
                 uint32_t r[4];
                 asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;\n" : "=r"(r[0]) : "f"(x0.y), "f"(x0.x));
                 asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;\n" : "=r"(r[1]) : "f"(x0.w), "f"(x0.z));
@@ -564,7 +585,7 @@ static int32_t launch_wq_mt(Ctx *c, const GemmParams &p, const GemmGroups &G, in
 // One launch: groups [g0, g1) with their token ranges cut into tiles of `ntok` tokens.
 static int32_t gemm_groups_chunk(Ctx *c, const Weight *const *ws, int ng, const void *a, int a_bf16, int64_t lda,
                                  const int64_t *tok_begin, const int64_t *tok_count, int ntok, void *y, int y_bf16, int64_t ldy,
-                                 cudaStream_t s) {
+                                 cudaStream_t s, const void *a_up) {
     const Weight *w = ws[0];
     const int fmt = w->qt == GLLMK_QUANT_Q4K ? FMT_Q4K : (w->qt == GLLMK_QUANT_Q8_0 ? FMT_Q80 : (w->qt == GLLMK_QUANT_NVFP4 ? FMT_NVFP4 : FMT_MXFP4));
     const int raw = wq_raw_bytes(fmt);
@@ -635,7 +656,7 @@ static int32_t gemm_groups_chunk(Ctx *c, const Weight *const *ws, int ng, const 
     int32_t rc = ensure_act(c, (size_t)nimg * nks * WQ_TILE);
     if (rc) return rc;
     p.xt = static_cast<const uint8_t *>(c->act);
-    stage_act_kernel<<<dim3((unsigned)nks, (unsigned)nimg), 256, 0, s>>>(a, a_bf16, lda, w->k, static_cast<uint8_t *>(c->act), imgs);
+    stage_act_kernel<<<dim3((unsigned)nks, (unsigned)nimg), 256, 0, s>>>(a, a_bf16, lda, w->k, static_cast<uint8_t *>(c->act), imgs, a_up);
     GK_CUDA(c, cudaGetLastError());
     dim3 grid((unsigned)ntiles, (unsigned)((row_tiles + mt - 1) / mt));
     // Tail split: with more tiles than SMs the last, partly filled wave of tiles is cut along k so that its work
@@ -678,7 +699,7 @@ static int32_t gemm_groups_chunk(Ctx *c, const Weight *const *ws, int ng, const 
 
 // Groups g use rows [row_offsets[g], row_offsets[g + 1]) of a and y with weight ws[g] (all of one shape and type).
 int32_t gemm_grouped_launch(Ctx *c, const Weight *const *ws, int n_groups, const void *a, int a_bf16, int64_t lda,
-                            const int64_t *row_offsets, void *y, int y_bf16, int64_t ldy, cudaStream_t s) {
+                            const int64_t *row_offsets, void *y, int y_bf16, int64_t ldy, cudaStream_t s, const void *a_up) {
     const int align = a_bf16 ? 8 : 4;
     if (ws[0]->qt < GLLMK_QUANT_Q4K || ws[0]->qt > GLLMK_QUANT_NVFP4)
         return fail(c, GLLMK_STATUS_UNSUPPORTED, "gemm: weight type %d is not block-quantized (use gllmk_gemm_int8)", ws[0]->qt);
@@ -696,7 +717,7 @@ int32_t gemm_grouped_launch(Ctx *c, const Weight *const *ws, int n_groups, const
     int ng = 0, tiles = 0;
     const auto flush = [&]() -> int32_t {
         if (ng == 0) return GLLMK_STATUS_OK;
-        const int32_t rc = gemm_groups_chunk(c, cw, ng, a, a_bf16, lda, cb, cc, ntok, y, y_bf16, ldy, s);
+        const int32_t rc = gemm_groups_chunk(c, cw, ng, a, a_bf16, lda, cb, cc, ntok, y, y_bf16, ldy, s, a_up);
         ng = 0;
         tiles = 0;
         return rc;
@@ -724,9 +745,9 @@ int32_t gemm_grouped_launch(Ctx *c, const Weight *const *ws, int n_groups, const
 }
 
 int32_t gemm_launch(Ctx *c, const Weight *w, const void *a, int a_bf16, int64_t lda, int m, void *y, int y_bf16, int64_t ldy,
-                    cudaStream_t s) {
+                    cudaStream_t s, const void *a_up) {
     const int64_t offs[2] = {0, m};
-    return gemm_grouped_launch(c, &w, 1, a, a_bf16, lda, offs, y, y_bf16, ldy, s);
+    return gemm_grouped_launch(c, &w, 1, a, a_bf16, lda, offs, y, y_bf16, ldy, s, a_up);
 }
 
 }  // namespace gllmk

@@ -269,6 +269,20 @@ class GpuKernels:
         self._check(rc, "gllmk_ffn_decode")
         return y
 
+    def ffn_prefill(self, w_gate_up: Weight, w_down: Weight, x, h=None, y=None, out_dtype=None, stream=None):
+        """The gated block for any number of tokens: x [m, k] f32 / bf16 CUDA -> y [m, k]; h [m, 2f] bf16 scratch."""
+        import torch
+        m = x.shape[0]
+        if h is None:
+            h = torch.empty((m, w_gate_up.n), dtype=torch.bfloat16, device=x.device)
+        if y is None:
+            y = torch.empty((m, w_down.n), dtype=out_dtype or torch.float32, device=x.device)
+        dt = {torch.float32: 0, torch.bfloat16: 1}
+        rc = lib().gllmk_ffn_prefill(self._ctx, w_gate_up._h, w_down._h, _ptr(x), dt[x.dtype], x.stride(0), m, _ptr(h), _ptr(y),
+                                     dt[y.dtype], y.stride(0), _stream(stream))
+        self._check(rc, "gllmk_ffn_prefill")
+        return y
+
     def gemm_grouped(self, weights, a, row_offsets, y=None, out_dtype=None, stream=None):
         """Mixture-of-experts product in one launch: rows [row_offsets[g], row_offsets[g+1]) of `a` times weights[g]."""
         import torch

@@ -87,6 +87,8 @@ extern "C" {
                          y_stride_t: i64, y_stride_r: i64, row_scales: *const f32, n_row_scales: i64, stream: *mut c_void) -> i32;
     fn gllmk_ffn_decode(ctx: *mut c_void, w_gate_up: *mut c_void, w_down: *mut c_void, x_dev: *const f32, m: i32, h_dev: *mut f32,
                         y_dev: *mut f32, stream: *mut c_void) -> i32;
+    fn gllmk_ffn_prefill(ctx: *mut c_void, w_gate_up: *mut c_void, w_down: *mut c_void, x_dev: *const c_void, x_dtype: i32, ldx: i64, m: i32,
+                         h_dev: *mut c_void, y_dev: *mut c_void, y_dtype: i32, ldy: i64, stream: *mut c_void) -> i32;
     fn gllmk_gemm(ctx: *mut c_void, w: *mut c_void, a_dev: *const c_void, a_dtype: i32, lda: i64, m: i32, y_dev: *mut c_void,
                   y_dtype: i32, ldy: i64, stream: *mut c_void) -> i32;
     fn gllmk_gemm_grouped(ctx: *mut c_void, n_groups: i32, weights: *const *mut c_void, a_dev: *const c_void, a_dtype: i32, lda: i64,
@@ -414,7 +416,7 @@ impl GpuKernels {
 fn _declared_but_unwrapped() {
     let _ = (
         gllmk_quant_block_size as usize, gllmk_quant_block_bytes as usize, gllmk_ctx_set as usize, gllmk_weight_unpack as usize,
-        gllmk_dequant as usize, gllmk_embedding_gather as usize, gllmk_gemv_static as usize, gllmk_ffn_decode as usize,
+        gllmk_dequant as usize, gllmk_embedding_gather as usize, gllmk_gemv_static as usize, gllmk_ffn_decode as usize, gllmk_ffn_prefill as usize,
         gllmk_gemm_grouped as usize, gllmk_gemm_fp4 as usize, gllmk_probe_fp4_mma as usize, gllmk_quantize as usize, gllmk_moe_topk as usize, gllmk_moe_route as usize,
         gllmk_moe_gather as usize, gllmk_moe_weighted_sum as usize, gllmk_int8_weight_upload as usize, gllmk_gemm_int8 as usize,
         gllmk_dequantize_i32_f32 as usize, gllmk_quantize_act_int8 as usize, gllmk_w8a8_linear_f32 as usize, gllmk_shared_alloc as usize,

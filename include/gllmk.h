@@ -229,6 +229,15 @@ GLLMK_API int32_t gllmk_gemv(gllmk_ctx ctx, gllmk_weight w, const float *x_dev, 
 GLLMK_API int32_t gllmk_ffn_decode(gllmk_ctx ctx, gllmk_weight w_gate_up, gllmk_weight w_down, const float *x_dev, int32_t m,
                          float *h_dev, float *y_dev, void *stream);
 
+/* The same block for any number of tokens (prefill): two tensor-core products with the intermediate kept in bf16,
+ *   h = W_gate_up x   (bf16 [m, 2f], caller-provided scratch; it holds gate || up afterwards)
+ *   y = W_down (silu(gate) * up)
+ * SwiGLU (f32 arithmetic on the bf16 values of h) is applied by the second product's activation staging, so no
+ * activation kernel runs and no third buffer exists.  x [m, k] f32 or bf16 (ldx), y [m, k] f32 or bf16 (ldy); the
+ * Q4_K / Q8_0 / MXFP4 / NVFP4 weights of gllmk_gemm.  Each product is within 1e-2 of the reference's f32 evaluation. */
+GLLMK_API int32_t gllmk_ffn_prefill(gllmk_ctx ctx, gllmk_weight w_gate_up, gllmk_weight w_down, const void *x_dev, int32_t x_dtype,
+                                    int64_t ldx, int32_t m, void *h_dev, void *y_dev, int32_t y_dtype, int64_t ldy, void *stream);
+
 /* ---- W8A8 integer path ------------------------------------------------------------------------------ */
 
 /* avx512_int8::gemm_int8 and dequantize_i32_to_f32 (src/macros/matmul_x86_int8.rs:307-456; tests

@@ -344,3 +344,40 @@ def test_gemm_grouped_rejects_mismatched_weights(gk, K, oracle):
 def test_gemm_more_token_tiles_than_one_launch_holds(gk, K, oracle):
     # 17000 tokens = 67 tiles of 256: the launcher cuts the token range into launches of at most 64 tiles
     assert run_case(gk, K, oracle, "q8_0", 128, 64, 17000, seed=31) <= TOL
+
+
+# ---- the gated feed-forward block for prefill batches: two tensor-core products, bf16 intermediate -------------------
+@pytest.mark.parametrize("fmt,d,f,m,x_bf16", [("q4k", 512, 768, 96, False), ("q4k", 1024, 2048, 300, True), ("q8_0", 256, 384, 40, True),
+                                              ("mxfp4", 512, 1024, 130, True)])
+def test_ffn_prefill_swiglu(gk, K, oracle, fmt, d, f, m, x_bf16):
+    """y = W_down (silu(gate) * up), [gate | up] = W_gate_up x, against the oracle's chain: the reference's f32 GEMM,
+    scalar_swiglu, the reference's f32 GEMM.  The intermediate lives in bf16 and both products stage fp16 operands:
+    each product holds the 1e-2 bar given the same inputs; the two-product chain against the all-f32 chain 2e-2."""
+    import torch
+    qt, b_gu, s_gu, g_gu, wd_gu = quantized(oracle, gk, fmt, 2 * f, d, 71)
+    _, b_dn, s_dn, g_dn, wd_dn = quantized(oracle, gk, fmt, d, f, 72)
+    w_gu, w_dn = K.upload(qt, 2 * f, d, b_gu, s_gu, g_gu), K.upload(qt, d, f, b_dn, s_dn, g_dn)
+    # weights ~N(0, 0.02): scale x so that gate and up are of order one and SwiGLU is not linear
+    x = (np.random.default_rng(73).standard_normal((m, d)) * 2.5).astype(np.float32)
+    xd = torch.from_numpy(x).cuda()
+    if x_bf16:
+        xd = xd.to(torch.bfloat16)
+        x = xd.to(torch.float32).cpu().numpy()
+    h = torch.empty((m, 2 * f), dtype=torch.bfloat16, device="cuda")
+    y = K.ffn_prefill(w_gu, w_dn, xd, h=h).cpu().numpy()
+    torch.cuda.synchronize()
+    assert K.status() == 0
+    silu_mul = lambda gu: ((gu[:, :f] / (np.float32(1.0) + np.exp(-gu[:, :f], dtype=np.float32))) * gu[:, f:]).astype(np.float32)
+    h_ref = oracle.gemm_f32_nt(x, wd_gu)
+    assert oracle.rel_err(h.to(torch.float32).cpu().numpy(), h_ref) <= 1e-2
+    # second product alone: from the h the device produced
+    y_from_h = oracle.gemm_f32_nt(silu_mul(h.to(torch.float32).cpu().numpy()), wd_dn)
+    assert oracle.rel_err(y, y_from_h) <= 1e-2
+    # the whole chain in f32
+    y_ref = oracle.gemm_f32_nt(silu_mul(h_ref), wd_dn)
+    assert oracle.rel_err(y, y_ref) <= 2e-2
+    with pytest.raises(gk.GllmkError) as e:  # shapes that do not chain
+        K.ffn_prefill(w_dn, w_dn, xd)
+    assert e.value.status == gk.Status.INVALID_ARG
+    w_gu.free()
+    w_dn.free()
