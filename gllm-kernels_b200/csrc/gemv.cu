@@ -60,7 +60,7 @@ __global__ void __launch_bounds__(256) stage_x_kernel(StageParams p) {
         // for the q-th other rank to reach it.  A rank that never arrives costs `spins` probes, then status 32.
         if ((int)threadIdx.x < p.nranks - 1) {
             const int src = (int)threadIdx.x < p.rank ? (int)threadIdx.x : (int)threadIdx.x + 1;
-            const uint32_t want = p.xflags[XF_EPOCH];
+            const uint32_t want = *reinterpret_cast<const volatile uint32_t *>(p.xflags + XF_EPOCH);  // L2, never a stale L1 line
             bool seen = false;
             for (uint32_t it = 0; it < p.spins && !seen; it++) {
                 uint32_t v;
@@ -465,8 +465,9 @@ __device__ __noinline__ void gemv_flush(const GemvParams &p, int tile, int slot,
             if (done == p.ntiles - 1) {
                 p.counters[p.ntiles] = 0;  // ready for the next launch
                 __threadfence_system();
-                const uint32_t e = p.xflags[XF_EPOCH] + 1u;
-                p.xflags[XF_EPOCH] = e;
+                volatile uint32_t *epoch = p.xflags + XF_EPOCH;  // read and written through L2 only
+                const uint32_t e = *epoch + 1u;
+                *epoch = e;
                 for (int q = 0; q < p.npeer; q++)
                     asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(p.xflags_peer[q] + XF_FLAGS + p.xrank), "r"(e) : "memory");
             }

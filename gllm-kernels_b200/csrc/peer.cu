@@ -66,7 +66,7 @@ __global__ void exchange_wait_kernel(const uint32_t *flags, int nranks, int rank
     const int q = threadIdx.x;
     if (q >= nranks - 1) return;
     const int src = q < rank ? q : q + 1;
-    const uint32_t want = flags[XF_EPOCH];
+    const uint32_t want = *reinterpret_cast<const volatile uint32_t *>(flags + XF_EPOCH);
     bool seen = false;
     for (uint32_t it = 0; it < spins && !seen; it++) {
         uint32_t v;
