@@ -278,6 +278,40 @@ def run_ours(args):
     ms_step = ms / args.steps
     value = weight_bytes_total / (ms_step * 1e-3) / 1e9
 
+    # Sharded runs: where does the step go?  The same shards multiplied WITHOUT the exchange (no peer stores, no waits
+    # for other ranks; y stays local), replayed as a graph like the step itself: the difference is what the exchange
+    # costs; the remainder, against the HBM time of a rank's bytes, is the per-product launch / ramp / tail cost.
+    breakdown = None
+    if world > 1 and ex is not None and graphed:
+        def local_step():
+            for i, (name, w, n, k, r0, r1) in enumerate(weights):
+                K.gemv(w, x_ff if name == "down" else x_model, y=ys[i][:, r0:r1])
+        for _ in range(3):
+            local_step()
+        torch.cuda.synchronize()
+        g2 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g2):
+            local_step()
+        for _ in range(3):
+            g2.replay()
+        torch.cuda.synchronize()
+        dist.barrier()
+        l0, l1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0.record()
+        for _ in range(args.steps):
+            g2.replay()
+        l1.record()
+        torch.cuda.synchronize()
+        tl = torch.tensor([l0.elapsed_time(l1) / args.steps], device=dev)
+        dist.all_reduce(tl, op=dist.ReduceOp.MAX)
+        peak_gbs = measured_peaks()[0]
+        hbm_us = weight_bytes_local / peak_gbs / 1e3
+        breakdown = {"step_us": ms_step * 1e3, "same_shards_without_exchange_us": tl.item() * 1e3,
+                     "exchange_us": ms_step * 1e3 - tl.item() * 1e3, "hbm_time_of_a_rank_s_bytes_us": hbm_us,
+                     "products_per_step": len(weights),
+                     "fixed_cost_per_product_us": (tl.item() * 1e3 - hbm_us) / len(weights),
+                     "exchange_per_product_us": (ms_step * 1e3 - tl.item() * 1e3) / len(weights)}
+
     # ---- end to end through the host-pointer call: pinned x -> device, GEMVs, y -> host, every step ----
     # host activations and outputs live in page-locked memory, as a serving loop keeps them
     xh_model = torch.empty(x_model.shape, dtype=torch.float32, pin_memory=True).copy_(x_model).numpy()
@@ -371,6 +405,8 @@ def run_ours(args):
             out["extra"] = sharded
     if parity_multi is not None:
         out["parity"] = parity_multi
+    if breakdown is not None:
+        out["breakdown"] = breakdown
     if keep_host:
         out["cpu_baseline"] = cpu_baseline(host_blocks, xh_model, xh_ff, M, threads=1)
         out["parity"] = parity_record(K, weights[0][1], host_blocks[0], x_model, xh_model, M)
