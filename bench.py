@@ -323,11 +323,23 @@ def run_ours(args):
     yh = {n: torch.empty((M, n), dtype=torch.float32, pin_memory=True).numpy() for n in {n for (_, _, n, _, _, _) in weights}}
     e2e = None
     if world == 1:
+        # one output buffer per product (a step's products do not share results), all enqueued by one call that waits
+        # once: gllmk_matmul_host_batch
+        yh_all = [torch.empty((M, n), dtype=torch.float32, pin_memory=True).numpy() for (_, _, n, _, _, _) in weights]
+        ws_all = [w for (_, w, *_r) in weights]
+        xs_all = [xh_ff if name == "down" else xh_model for (name, *_r) in weights]
+
         def step_host():
-            out = None
-            for (name, w, n, k, r0, r1) in weights:
-                out = K.matmul_host(w, xh_ff if name == "down" else xh_model, out=yh[n])
-            return out
+            return K.matmul_host_batch(ws_all, xs_all, yh_all)
+        def step_host_each():
+            for (name, w, n, k, r0, r1), y in zip(weights, yh_all):
+                K.matmul_host(w, xh_ff if name == "down" else xh_model, out=y)
+        for _ in range(3):
+            step_host_each()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            step_host_each()
+        e2e_per_product = weight_bytes_total / ((time.perf_counter() - t0) / args.steps) / 1e9
         for _ in range(3):
             step_host()
         t0 = time.perf_counter()
@@ -339,7 +351,9 @@ def run_ours(args):
                "d2h_bytes_per_step": L * sum(M * n * 4 for _, n, k in shapes),
                "note": "weights resident (uploaded once, like the reference's weights handle); activations and "
                        "outputs are page-locked host buffers, transferred inside the timed region (x read by the staging "
-                       "kernel over PCIe, y by a device-to-host copy), one synchronous call per product"}
+                       "kernel over PCIe, every product's y by a device-to-host copy); the step's products go through ONE "
+                       "gllmk_matmul_host_batch call, which waits once at the end",
+               "one_synchronous_call_per_product": e2e_per_product}
 
     elif ex is not None:
         # sharded: every rank copies the step's activations from page-locked host memory, runs its band of every

@@ -80,6 +80,7 @@ _OPTIONAL_SIGS: dict = {
     "gllmk_dequantize_i32_f32": (_i32, [_vp, _vp, _vp, _i64, _i64, _f32, _f32, _vp, _i32, _vp]),
     "gllmk_gemm_int8_host": (_i32, [_vp, _vp, _vp, _vp, _sz, _sz, _sz]),
     "gllmk_ffn_decode": (_i32, [_vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp]),
+    "gllmk_matmul_host_batch": (_i32, [_vp, _i32, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_i32), C.POINTER(_vp), _i32]),
     "gllmk_ffn_prefill": (_i32, [_vp, _vp, _vp, _vp, _i32, _i64, _i32, _vp, _vp, _i32, _i64, _vp]),
     "gllmk_gemm_grouped": (_i32, [_vp, _i32, C.POINTER(_vp), _vp, _i32, _i64, C.POINTER(_i64), _vp, _i32, _i64, _vp]),
     "gllmk_shared_alloc": (_i32, [_vp, _sz, C.POINTER(_vp), _vp]),

@@ -743,6 +743,92 @@ static int32_t matmul_host_impl(Ctx *c, const Weight *w, const float *x_host, in
     return GLLMK_STATUS_OK;
 }
 
+// Several products with host activations / outputs, enqueued back to back on the context's stream and awaited ONCE:
+// what a decode step is (a handful of products whose host-side inputs are all known when the step starts).
+static int32_t matmul_host_batch_impl(Ctx *c, int count, const gllmk_weight *ws, const float *const *xs, const int32_t *ms,
+                                      float *const *ys, bool ref_layout) {
+    const auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
+    size_t total = 256;
+    for (int i = 0; i < count; i++) {
+        const Weight *w = static_cast<const Weight *>(ws[i]);
+        total += up((size_t)ms[i] * w->k * sizeof(float)) + up((size_t)ms[i] * w->n * sizeof(float));
+    }
+    int32_t rc = ensure_pin(c, total);
+    if (!rc) rc = ensure_dev_io(c, total);
+    if (rc) return rc;
+    char *pin = static_cast<char *>(c->pin), *dev = static_cast<char *>(c->dev_io);
+    const auto pinned_alias = [](const void *h) -> const void * {
+        cudaPointerAttributes at;
+        if (cudaPointerGetAttributes(&at, h) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return nullptr;
+        }
+        return at.type == cudaMemoryTypeHost ? at.devicePointer : nullptr;
+    };
+    std::vector<size_t> y_off((size_t)count, 0);
+    std::vector<char> y_staged((size_t)count, 0);
+    size_t off = 0;
+    for (int i = 0; i < count; i++) {
+        const Weight *w = static_cast<const Weight *>(ws[i]);
+        const int m_t = ms[i];
+        const int64_t n_w = w->n, k = w->k;
+        const size_t xb = (size_t)m_t * k * sizeof(float), yb = (size_t)m_t * n_w * sizeof(float);
+        const size_t xo = off, yo = off + up(xb);
+        off = yo + up(yb);
+        const void *x_alias = pinned_alias(xs[i]);
+        const char *x_src = reinterpret_cast<const char *>(xs[i]);
+        if (!x_alias) {
+            memcpy(pin + xo, xs[i], xb);
+            x_src = pin + xo;
+            x_alias = pin + xo;
+        }
+        const bool zero_copy_x = xb <= (size_t)256 * 1024;
+        if (!zero_copy_x) GK_CUDA(c, cudaMemcpyAsync(dev + xo, x_src, xb, cudaMemcpyHostToDevice, c->stream));
+        const float *xd = reinterpret_cast<const float *>(zero_copy_x ? static_cast<const char *>(x_alias) : dev + xo);
+        float *yd = reinterpret_cast<float *>(dev + yo);
+        if (!ref_layout && m_t > GLLMK_GEMM_GEMV_MAX_M && !raw_format(w->qt)) {
+            rc = gemm_launch(c, w, xd, 0, k, m_t, yd, 0, n_w, c->stream);
+            if (rc) return rc;
+        } else {
+            for (int t0 = 0; t0 < m_t; t0 += GLLMK_GEMV_MAX_M) {
+                const int mt = (m_t - t0 < GLLMK_GEMV_MAX_M) ? m_t - t0 : GLLMK_GEMV_MAX_M;
+                if (ref_layout) rc = gemv_launch(c, w, xd + t0, 1, m_t, mt, yd + t0, 1, m_t, nullptr, 0, c->stream);
+                else rc = gemv_launch(c, w, xd + (size_t)t0 * k, k, 1, mt, yd + (size_t)t0 * n_w, n_w, 1, nullptr, 0, c->stream);
+                if (rc) return rc;
+            }
+        }
+        const bool y_pinned = pinned_alias(ys[i]) != nullptr;
+        y_off[(size_t)i] = yo;
+        y_staged[(size_t)i] = y_pinned ? 0 : 1;
+        GK_CUDA(c, cudaMemcpyAsync(y_pinned ? static_cast<void *>(ys[i]) : static_cast<void *>(pin + yo), dev + yo, yb, cudaMemcpyDeviceToHost,
+                                   c->stream));
+    }
+    GK_CUDA(c, cudaStreamSynchronize(c->stream));
+    for (int i = 0; i < count; i++)
+        if (y_staged[(size_t)i]) {
+            const Weight *w = static_cast<const Weight *>(ws[i]);
+            memcpy(ys[i], pin + y_off[(size_t)i], (size_t)ms[i] * w->n * sizeof(float));
+        }
+    return GLLMK_STATUS_OK;
+}
+
+int32_t gllmk_matmul_host_batch(gllmk_ctx ctx, int32_t count, const gllmk_weight *weights, const float *const *x_host, const int32_t *m,
+                                float *const *y_host, int32_t ref_layout) {
+    if (!ctx || !weights || !x_host || !m || !y_host) return GLLMK_STATUS_INVALID_ARG;
+    Ctx *c = static_cast<Ctx *>(ctx);
+    if (count < 0 || count > 4096) return fail(c, GLLMK_STATUS_INVALID_ARG, "matmul_host_batch: count=%d", count);
+    for (int i = 0; i < count; i++) {
+        if (!weights[i] || !x_host[i] || !y_host[i]) return fail(c, GLLMK_STATUS_INVALID_ARG, "matmul_host_batch: null pointer in product %d", i);
+        if (m[i] < 1) return fail(c, GLLMK_STATUS_INVALID_ARG, "matmul_host_batch: m must be positive");
+        const Weight *w = static_cast<const Weight *>(weights[i]);
+        if (w->qt == GLLMK_QUANT_INT8) return fail(c, GLLMK_STATUS_UNSUPPORTED, "matmul_host_batch: not a block-quantized weight");
+        if (w->device != c->device) return fail(c, GLLMK_STATUS_INVALID_ARG, "weight lives on another device");
+    }
+    if (count == 0) return GLLMK_STATUS_OK;
+    DeviceGuard g(c->device);
+    return matmul_host_batch_impl(c, count, weights, x_host, m, y_host, ref_layout != 0);
+}
+
 int32_t gllmk_matmul_host(gllmk_ctx ctx, gllmk_weight wh, const float *x_host, int32_t m, float *y_host,
                           int32_t ref_layout) {
     if (!ctx || !wh || !x_host || !y_host) return GLLMK_STATUS_INVALID_ARG;

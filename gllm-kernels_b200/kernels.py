@@ -431,6 +431,17 @@ class GpuKernels:
         self._check(lib().gllmk_matmul_host(self._ctx, w._h, _ptr(x), m, _ptr(y), int(ref_layout)), "gllmk_matmul_host")
         return y
 
+    def matmul_host_batch(self, weights, xs, outs, ref_layout: bool = False):
+        """The products of one decode step in one call: outs[i] = product of weights[i] and xs[i] (numpy f32, [m, k] ->
+        [m, n]; page-locked arrays are used in place), enqueued back to back and awaited once."""
+        n = len(weights)
+        ms = (C.c_int32 * n)(*[(x.shape[1] if ref_layout else x.shape[0]) for x in xs])
+        wh = (C.c_void_p * n)(*[w._h for w in weights])
+        xp = (C.c_void_p * n)(*[_ptr(_np(x, np.float32)) for x in xs])
+        yp = (C.c_void_p * n)(*[_ptr(_np(y, np.float32, True)) for y in outs])
+        self._check(lib().gllmk_matmul_host_batch(self._ctx, n, wh, xp, ms, yp, int(ref_layout)), "gllmk_matmul_host_batch")
+        return outs
+
     def quantize(self, quant_type: QuantType, x, global_scale: float = 0.0, stream=None):
         """f32 [rows, k] CUDA tensor -> reference-format blocks (CUDA uint8 tensors).
         Returns blocks for Q4K/Q8_0, (blocks, scales) for MXFP4, (blocks, global_scale) for NVFP4."""

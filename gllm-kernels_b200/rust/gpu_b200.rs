@@ -141,6 +141,8 @@ extern "C" {
                          m: usize, n: usize, k: usize) -> i32;
     fn gllmk_gemv_q4_f32(ctx: *mut c_void, weight: *const u8, input: *const f32, scale: f32, n: usize, out: *mut f32) -> i32;
     fn gllmk_gemv_q8_f32(ctx: *mut c_void, weight: *const i8, input: *const f32, scale: f32, n: usize, out: *mut f32) -> i32;
+    fn gllmk_matmul_host_batch(ctx: *mut c_void, count: i32, weights: *const *mut c_void, x_host: *const *const f32, m: *const i32,
+                               y_host: *const *mut f32, ref_layout: i32) -> i32;
     fn gllmk_matmul_host(ctx: *mut c_void, w: *mut c_void, x_host: *const f32, m: i32, y_host: *mut f32, ref_layout: i32) -> i32;
     fn gllmk_dequant_q4_k(ctx: *mut c_void, blocks: *const u8, out: *mut f32, nblocks: usize) -> i32;
     fn gllmk_dequant_q8_0(ctx: *mut c_void, blocks: *const u8, out: *mut f32, nblocks: usize) -> i32;
@@ -286,6 +288,16 @@ impl GpuKernels {
         assert!(x.len() >= m * w.k && y.len() >= m * w.n);
         let rc = unsafe { gllmk_matmul_host(self.ctx, w.h, x.as_ptr(), m as i32, y.as_mut_ptr(), ref_layout as i32) };
         self.check(rc, "gllmk_matmul_host");
+    }
+
+    /// The products of one decode step in one call (enqueued back to back, one wait): `jobs[i] = (weight, x [m, k], m, y [m, n])`.
+    pub fn matmul_batch(&self, jobs: &mut [(&GpuWeight, &[f32], usize, &mut [f32])]) {
+        let ws: Vec<*mut c_void> = jobs.iter().map(|j| j.0.h).collect();
+        let xs: Vec<*const f32> = jobs.iter().map(|j| j.1.as_ptr()).collect();
+        let ms: Vec<i32> = jobs.iter().map(|j| j.2 as i32).collect();
+        let ys: Vec<*mut f32> = jobs.iter_mut().map(|j| j.3.as_mut_ptr()).collect();
+        let rc = unsafe { gllmk_matmul_host_batch(self.ctx, jobs.len() as i32, ws.as_ptr(), xs.as_ptr(), ms.as_ptr(), ys.as_ptr(), 0) };
+        self.check(rc, "gllmk_matmul_host_batch");
     }
 
     /// Decode product on device memory (m <= 16): x [m, k] and y [m, n] row-major device pointers.

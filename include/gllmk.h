@@ -443,6 +443,12 @@ GLLMK_API int32_t gllmk_gemv_q8_f32(gllmk_ctx ctx, const int8_t *weight, const f
  * `ref_layout` != 0: kquant_matmul's input [k, m] / output [n, m]; 0: gemm_q4's [m, k] / [m, n]. */
 GLLMK_API int32_t gllmk_matmul_host(gllmk_ctx ctx, gllmk_weight w, const float *x_host, int32_t m, float *y_host,
                           int32_t ref_layout);
+/* The products of one decode step in ONE call: product i is gllmk_matmul_host(weights[i], x_host[i], m[i], y_host[i]).  All
+ * of them are enqueued back to back on the context's stream (activations read from / results copied to the host
+ * buffers, page-locked ones in place) and the call waits once, at the end, instead of once per product.  Outputs must
+ * not alias inputs of the same call.  No counterpart in the reference (its products are synchronous CPU calls). */
+GLLMK_API int32_t gllmk_matmul_host_batch(gllmk_ctx ctx, int32_t count, const gllmk_weight *weights, const float *const *x_host,
+                                          const int32_t *m, float *const *y_host, int32_t ref_layout);
 /* Kernels::dequant_q4_k(block, out) / dequant_q8_0 (src/traits.rs:476,488): `nblocks` consecutive
  * blocks -> nblocks*block_size f32, host pointers. */
 GLLMK_API int32_t gllmk_dequant_q4_k(gllmk_ctx ctx, const uint8_t *blocks, float *out, size_t nblocks);

@@ -444,3 +444,33 @@ def test_gemv_fused_staging_equals_the_staging_kernel(gk, K, oracle, torch, fmt,
     # strided x (the reference's [k, m] layout) went through the same fused path
     assert torch.equal(y_ref_layout.t().contiguous(), y_fused)
     w.free()
+
+
+def test_matmul_host_batch_equals_one_call_per_product(gk, K, oracle, torch):
+    """The products of a step through one call (enqueued back to back, one wait): bit-identical with one synchronous call
+    per product, with pageable and with page-locked host buffers, decode- and prefill-sized batches mixed."""
+    rng = np.random.default_rng(81)
+    specs = [("q4k", 512, 1024, 1), ("q8_0", 300, 416, 5), ("q4k", 256, 512, 70), ("q4k", 512, 1024, 2)]
+    ws, xs, want = [], [], []
+    for fmt, n, k, m in specs:
+        oid, blocks, _, _ = make(oracle, fmt, n, k, seed=n + m)
+        w = K.upload(qt_of(gk, fmt), n, k, blocks)
+        x = rng.standard_normal((m, k)).astype(np.float32)
+        ws.append(w), xs.append(x), want.append(K.matmul_host(w, x))
+    outs = [np.full((x.shape[0], w.n), np.nan, np.float32) for w, x in zip(ws, xs)]
+    K.matmul_host_batch(ws, xs, outs)
+    for got, ref in zip(outs, want):
+        assert np.array_equal(got, ref)
+    xp = [torch.empty(x.shape, dtype=torch.float32, pin_memory=True) for x in xs]
+    for t, x in zip(xp, xs):
+        t.copy_(torch.from_numpy(x))
+    yp = [torch.full(o.shape, float("nan"), dtype=torch.float32, pin_memory=True) for o in outs]
+    K.matmul_host_batch(ws, [t.numpy() for t in xp], [t.numpy() for t in yp])
+    for got, ref in zip(yp, want):
+        assert np.array_equal(got.numpy(), ref)
+    assert K.status() == 0
+    with pytest.raises(gk.GllmkError) as e:
+        K.matmul_host_batch(ws[:1], [np.zeros((0, 1024), np.float32)], [np.zeros((0, 512), np.float32)])
+    assert e.value.status == gk.Status.INVALID_ARG
+    for w in ws:
+        w.free()
