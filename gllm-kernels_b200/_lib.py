@@ -97,7 +97,7 @@ _OPTIONAL_SIGS: dict = {
     "gllmk_gemv_q8_f32": (_i32, [_vp, _vp, _vp, _f32, _sz, _vp]),
     "gllmk_quant_format_descriptor_for_type": (_i32, [_i32, _i32, _vp]),
     "gllmk_quant_format_registry": (_i32, [_vp, _i32]),
-    "gllmk_gemv_exchange": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _vp, _i64, _i64, C.POINTER(_vp), _vp, C.POINTER(_vp), _i32, _i32, _vp]),
+    "gllmk_gemv_exchange": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i32, _vp, _i64, _i64, C.POINTER(_vp), _vp, C.POINTER(_vp), _i32, _i32, _vp]),
     "gllmk_exchange_wait": (_i32, [_vp, _vp, _i32, _i32, _vp]),
     "gllmk_moe_topk": (_i32, [_vp, _vp, _vp, _i64, _i32, _i32, _vp]),
     "gllmk_moe_route": (_i32, [_vp, _vp, _i64, _i32, _i32, C.POINTER(_i64), _vp, _vp, _vp]),

@@ -172,9 +172,10 @@ extern "C" int32_t gllmk_peer_barrier(gllmk_ctx ctx, void *flags_local, void *co
                                seq, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int32_t gllmk_gemv_exchange(gllmk_ctx ctx, gllmk_weight wh, const float *x_dev, int64_t x_stride_t, int64_t x_stride_k,
-                                       int32_t m, float *y_local, int64_t y_stride_t, int64_t y_stride_r, void *const *y_peers,
-                                       void *flags_local, void *const *flags_peers, int32_t n_peers, int32_t rank, void *stream) {
+extern "C" int32_t gllmk_gemv_exchange(gllmk_ctx ctx, gllmk_weight wh, const float *x_dev, const float *x_up_dev, int64_t x_stride_t,
+                                       int64_t x_stride_k, int32_t m, float *y_local, int64_t y_stride_t, int64_t y_stride_r,
+                                       void *const *y_peers, void *flags_local, void *const *flags_peers, int32_t n_peers, int32_t rank,
+                                       void *stream) {
     if (!ctx || !wh || !x_dev || !y_local || !flags_local || (n_peers > 0 && (!y_peers || !flags_peers))) return GLLMK_STATUS_INVALID_ARG;
     Ctx *c = static_cast<Ctx *>(ctx);
     const Weight *w = static_cast<const Weight *>(wh);
@@ -192,7 +193,7 @@ extern "C" int32_t gllmk_gemv_exchange(gllmk_ctx ctx, gllmk_weight wh, const flo
     if (w->device != c->device) return fail(c, GLLMK_STATUS_INVALID_ARG, "weight lives on another device");
     DeviceGuard g(c->device);
     return gemv_launch(c, w, x_dev, x_stride_t, x_stride_k, m, y_local, y_stride_t, y_stride_r, nullptr, 0,
-                       static_cast<cudaStream_t>(stream), y_peers, n_peers, nullptr, &x);
+                       static_cast<cudaStream_t>(stream), y_peers, n_peers, x_up_dev, &x);
 }
 
 extern "C" int32_t gllmk_exchange_wait(gllmk_ctx ctx, void *flags_local, int32_t n_peers, int32_t rank, void *stream) {

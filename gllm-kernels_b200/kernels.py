@@ -390,12 +390,12 @@ class GpuKernels:
         self._check(rc, "gllmk_gemv_allgather")
 
     def gemv_exchange(self, w: Weight, x, y_local: int, y_peers, y_stride_t: int, m: int, flags_local: int, flags_peers,
-                      rank: int, stream=None) -> None:
+                      rank: int, stream=None, x_up=None) -> None:
         """gemv_allgather with the hand-shake built in: waits for every rank's previous exchange product before x
-        is read, signals this one's completion from the GEMV's last block."""
+        is read, signals this one's completion from the GEMV's last block.  x_up: the activation is silu(x) * x_up."""
         ya = (C.c_void_p * max(len(y_peers), 1))(*y_peers)
         fa = (C.c_void_p * max(len(flags_peers), 1))(*flags_peers)
-        rc = lib().gllmk_gemv_exchange(self._ctx, w._h, _ptr(x), x.stride(0), x.stride(1), m, y_local, y_stride_t, 1, ya,
+        rc = lib().gllmk_gemv_exchange(self._ctx, w._h, _ptr(x), _ptr(x_up), x.stride(0), x.stride(1), m, y_local, y_stride_t, 1, ya,
                                        flags_local, fa, len(y_peers), rank, _stream(stream))
         self._check(rc, "gllmk_gemv_exchange")
 

@@ -126,7 +126,7 @@ extern "C" {
                             y_stride_t: i64, y_stride_r: i64, y_peers: *const *mut c_void, n_peers: i32, stream: *mut c_void) -> i32;
     fn gllmk_peer_barrier(ctx: *mut c_void, flags_local: *mut c_void, flags_peers: *const *mut c_void, n_peers: i32, rank: i32, seq: u32,
                           stream: *mut c_void) -> i32;
-    fn gllmk_gemv_exchange(ctx: *mut c_void, w: *mut c_void, x_dev: *const f32, x_stride_t: i64, x_stride_k: i64, m: i32, y_local: *mut f32,
+    fn gllmk_gemv_exchange(ctx: *mut c_void, w: *mut c_void, x_dev: *const f32, x_up_dev: *const f32, x_stride_t: i64, x_stride_k: i64, m: i32, y_local: *mut f32,
                            y_stride_t: i64, y_stride_r: i64, y_peers: *const *mut c_void, flags_local: *mut c_void,
                            flags_peers: *const *mut c_void, n_peers: i32, rank: i32, stream: *mut c_void) -> i32;
     fn gllmk_exchange_wait(ctx: *mut c_void, flags_local: *mut c_void, n_peers: i32, rank: i32, stream: *mut c_void) -> i32;

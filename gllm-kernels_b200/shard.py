@@ -186,6 +186,22 @@ class PeerExchange:
         others = [d for r, d in enumerate(dst) if r != self.rank]
         self.K.gemv_allgather(w, x, mine, others, n_total, m, stream)
 
+    def ffn_decode_sharded(self, w_gate_up, w_down, x, slot_h: int, slot_y: int, r0_h: int, r0_y: int, stream=None):
+        """The gated feed-forward block with row-sharded weights, two chained exchange products: this rank's band of
+        [gate | up] = W_gate_up x is stored into every rank's h [m, 2f] (slot_h), then y = W_down (silu(gate) * up) reads the
+        gathered h with SwiGLU applied while staging, and its band goes into every rank's y [m, d] (slot_y).  `w_gate_up` /
+        `w_down` are this rank's row bands, r0_h / r0_y their first rows.  Returns (h, y) views of this rank's copies;
+        y is complete after `wait()` (or inside the next chained product)."""
+        m = x.shape[0]
+        two_f, d = 2 * w_down.k, w_gate_up.k
+        self.gemv_chained(w_gate_up, x, slot_h, r0_h, two_f, stream)
+        h = self.local_tensor(slot_h, (m, two_f))
+        dst = [self.slot_ptr(r, slot_y, r0_y) for r in range(self.world)]
+        others = [p for r, p in enumerate(dst) if r != self.rank]
+        self.K.gemv_exchange(w_down, h, dst[self.rank], others, d, m, self.bases[self.rank], self.peers, self.rank, stream,
+                             x_up=h[:, two_f // 2:])
+        return h, self.local_tensor(slot_y, (m, d))
+
     def gemv_chained(self, w, x, slot: int, r0: int, n_total: int, stream=None) -> None:
         """The same product as `gemv` for chains of sharded products: it first waits until every rank has completed
         the previous chained product (so an x that is a gathered y is complete) and signals its own completion from

@@ -300,6 +300,8 @@ GLLMK_API int32_t gllmk_w8a8_linear_f32(gllmk_ctx ctx, gllmk_weight w, const flo
  *   the wait.  Every rank must issue the same sequence of exchange products; flags_local / flags_peers are the
  *   flag words at the start of each rank's gllmk_shared_alloc buffer (this call uses words 32..48, the barrier
  *   words 0..16).  A buffer may be rewritten by peers one product after its last reader finished.
+ *   x_up_dev != NULL: the activation is silu(x) * x_up (same strides) — the sharded form of gllmk_ffn_decode: a
+ *   gate || up product gathered into h [m, 2f], then the down product with x = h, x_up = h + f.
  * gllmk_exchange_wait: after the last product of a chain, on `stream`: returns once every rank's bands of that
  *   product have landed here (what the next product's staging would otherwise wait for). */
 #define GLLMK_MAX_PEERS 7
@@ -314,9 +316,10 @@ GLLMK_API int32_t gllmk_gemv_allgather(gllmk_ctx ctx, gllmk_weight w, const floa
                              int32_t n_peers, void *stream);
 GLLMK_API int32_t gllmk_peer_barrier(gllmk_ctx ctx, void *flags_local, void *const *flags_peers, int32_t n_peers, int32_t rank,
                            uint32_t seq, void *stream);
-GLLMK_API int32_t gllmk_gemv_exchange(gllmk_ctx ctx, gllmk_weight w, const float *x_dev, int64_t x_stride_t, int64_t x_stride_k,
-                                      int32_t m, float *y_local, int64_t y_stride_t, int64_t y_stride_r, void *const *y_peers,
-                                      void *flags_local, void *const *flags_peers, int32_t n_peers, int32_t rank, void *stream);
+GLLMK_API int32_t gllmk_gemv_exchange(gllmk_ctx ctx, gllmk_weight w, const float *x_dev, const float *x_up_dev, int64_t x_stride_t,
+                                      int64_t x_stride_k, int32_t m, float *y_local, int64_t y_stride_t, int64_t y_stride_r,
+                                      void *const *y_peers, void *flags_local, void *const *flags_peers, int32_t n_peers, int32_t rank,
+                                      void *stream);
 GLLMK_API int32_t gllmk_exchange_wait(gllmk_ctx ctx, void *flags_local, int32_t n_peers, int32_t rank, void *stream);
 
 /* ---- prefill: fused dequantize + GEMM on tcgen05 tensor cores (any M) --------------------------- */

@@ -103,6 +103,28 @@ def _worker(rank, world, port, q):
             check(f"graph {rep}")
         w1.free()
         w2.free()
+        # the gated feed-forward block with row-sharded weights: gate || up gathered into h, the down product reads it with
+        # SwiGLU applied while staging (two chained exchange products), against the oracle's chain
+        d_model, f, m = 256, 256, 2
+        b_gu = O.quantize_q4_k((np.random.default_rng(401).standard_normal((2 * f, d_model)) * 0.05).astype(np.float32))
+        b_dn = O.quantize_q4_k((np.random.default_rng(402).standard_normal((d_model, f)) * 0.05).astype(np.float32))
+        rg, rd = gk.shard_rows(2 * f, world, rank), gk.shard_rows(d_model, world, rank)
+        w_gu = K.upload(qt, rg[1] - rg[0], d_model, gk.slice_blocks(qt, b_gu, 2 * f, d_model, *rg))
+        w_dn = K.upload(qt, rd[1] - rd[0], f, gk.slice_blocks(qt, b_dn, d_model, f, *rd))
+        for rep in range(2):
+            xf = (np.random.default_rng(410 + rep).standard_normal((m, d_model)) * 4.0).astype(np.float32)
+            h_t, y_t = ex.ffn_decode_sharded(w_gu, w_dn, torch.from_numpy(xf).cuda(), 0, 1, rg[0], rd[0])
+            ex.wait()
+            torch.cuda.synchronize()
+            assert K.status() == 0
+            h_ref = O.quant_matmul(b_gu, np.ascontiguousarray(xf.T), O.Q4K, 2 * f, m, d_model).T
+            act = ((h_ref[:, :f] / (np.float32(1.0) + np.exp(-h_ref[:, :f], dtype=np.float32))) * h_ref[:, f:]).astype(np.float32)
+            y_ref = O.quant_matmul(b_dn, np.ascontiguousarray(act.T), O.Q4K, d_model, m, f).T
+            e1, e2 = O.rel_err(h_t.cpu().numpy(), h_ref), O.rel_err(y_t.cpu().numpy(), y_ref)
+            assert e1 <= 2e-3 and e2 <= 4e-3, f"rank {rank} sharded ffn {rep}: {e1} {e2}"
+            dist.barrier()
+        w_gu.free()
+        w_dn.free()
         ex.close()
         K.close()
         q.put((rank, "ok"))
