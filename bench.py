@@ -1000,7 +1000,7 @@ def run_prefill_case(args):
         w, x = K.upload(QT.nvfp4(), n, k, wb, None, gw), K.upload(QT.nvfp4(), m, k, xb, None, gx)
         y = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
         fn = lambda: K.gemm_fp4(w, x, y=y)
-        kernel, peak_key, launches = "gemm_fp4_pair_kernel", None, 1
+        kernel, peak_key, launches = "gemm_fp4_pair2_kernel<192>", None, 1
     for _ in range(max(args.warmup, 3)):
         fn()
     torch.cuda.synchronize()
@@ -1014,7 +1014,23 @@ def run_prefill_case(args):
     tflops = 2.0 * m * n * k / (ms * 1e-3) / 1e12
     peak, kind = 9000.0, "nominal dense FP4"
     ceiling = None
+    variants = None
     if not peak_key:
+        # the same product on the other FP4 x FP4 kernels the "gemm_fp4_pair" knob selects (the headline is the default, 2)
+        variants = {}
+        for v, name in ((0, "one_cta_128x128"), (1, "cta_pair_256x256_one_accumulator"), (2, "cta_pair_256x192_two_accumulators"),
+                        (3, "cta_pair_256x128_two_accumulators")):
+            K.set("gemm_fp4_pair", v)
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(args.steps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            variants[name] = {"us": e0.elapsed_time(e1) / args.steps * 1e3, "status": K.status()}
+        K.set("gemm_fp4_pair", 2)
         # what the same MMA reaches on operands parked in shared memory (no copies, no epilogue), with and without the
         # per-k-step scale-factor copies: the practical ceiling of this kernel on this device
         ceiling = {"mma_and_scale_warps_cta_pair": K.probe_fp4_mma(True, 2), "mma_and_scale_copies_cta_pair": K.probe_fp4_mma(True, 1),
@@ -1032,7 +1048,7 @@ def run_prefill_case(args):
                       "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
                       "data": "synthetic", "config": {"workload": args.case, "n": n, "k": k, "m": m},
                       "roofline": {"bound": "tensor", "achieved": tflops, "peak": peak, "unit": "TFLOP/s", "frac": tflops / peak,
-                                   "traffic": None, "peak_kind": kind, "kernel": kernel, "measured_mma_ceiling": ceiling,
+                                   "traffic": None, "peak_kind": kind, "kernel": kernel, "measured_mma_ceiling": ceiling, "kernel_variants": variants,
                                    "frac_of_measured_ceiling": (tflops / ceiling["mma_and_scale_warps_cta_pair"]) if ceiling else None},
                       "gpu_launches": args.steps * launches, "status": K.status()}), flush=True)
 

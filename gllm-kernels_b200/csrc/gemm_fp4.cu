@@ -459,6 +459,290 @@ gemm_fp4_pair_kernel(const __grid_constant__ Fp4Params p, const int row_tiles, c
 }
 
 // ---------------------------------------------------------------------------------------------
+// CTA-pair version with TWO accumulators (the default for m > 128): tiles of 256 rows x NT tokens, NT = 192 or 128.
+//
+// With one 256-column accumulator the epilogue of a tile (tensor memory -> bf16 -> global, ~10 k cycles) cannot
+// overlap the next tile's MMAs: measured, it was 40 % of the launch.  Tensor memory has 512 columns: two accumulators of
+// 192 columns and three 40-column scale-factor sets fit (2 x 192 + 3 x 40 = 504), so the epilogue warps drain
+// accumulator (tile & 1) while the MMA thread fills the other one.  Everything else is the kernel above: own weight
+// rows and own half of the activation tile per CTA, scale warps, relay of "stage full" to the leader.
+//
+// A 192-token tile does not line up with the 128-token groups the activation planes are stored in: a CTA's 96
+// activation rows start at a multiple of 32 inside a group and may run into the next one (two bulk copies; the
+// 128-byte swizzle only depends on row % 8, which a shift by a multiple of 8 rows keeps), and the scale warps pick the
+// tile's 32-token column groups out of the (at most two) groups of scale atoms the tile touches.
+// ---------------------------------------------------------------------------------------------
+template <int NT>
+struct P2 {
+    static constexpr int STAGES = 5;
+    static constexpr int A_BYTES = 16384, B_BYTES = NT / 2 * 128, SFA_BYTES = 2048, SFB_BYTES = 4096;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
+    static constexpr int EPI_WARPS = 8, SF_WARPS = 4, SF_SETS = 3;
+    static constexpr int THREADS = 64 + 32 * (EPI_WARPS + SF_WARPS);
+    static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + (size_t)EPI_WARPS * 4096 + 1024;
+    static constexpr uint32_t TMEM_COLS = 512, ACC1 = NT, SF0 = 2 * NT, SFB_PER_MMA = NT / 32, SET_COLS = 16 + NT / 8;
+    static_assert(SF0 + SF_SETS * SET_COLS <= TMEM_COLS, "tensor memory budget");
+    static constexpr int CHUNKS = NT / 32;  // 32-token column groups of a tile
+};
+
+template <int NT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P2<NT>::THREADS, 1)
+gemm_fp4_pair2_kernel(const __grid_constant__ Fp4Params p, const int row_tiles, const int tok_tiles) {
+    using C = P2<NT>;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bars[3 * C::STAGES + 2 * C::SF_SETS + 4];
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int abort_s;
+    const uint32_t smem_s = (tc::smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t full = tc::smem_u32(&bars[0]), empty = tc::smem_u32(&bars[C::STAGES]), full2 = tc::smem_u32(&bars[2 * C::STAGES]);
+    const uint32_t sf_full = tc::smem_u32(&bars[3 * C::STAGES]), sf_empty = sf_full + 8 * C::SF_SETS;
+    const uint32_t accum_full = sf_empty + 8 * C::SF_SETS, accum_empty = accum_full + 16;  // two each
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = tc::cluster_ctarank();
+    const int pair = (int)(blockIdx.x >> 1), npairs = (int)(gridDim.x >> 1);
+    const int row_pairs = (row_tiles + 1) >> 1;
+    const int ntiles = row_pairs * tok_tiles;
+    const int nks = (int)(p.k / 256);
+    const int64_t atoms_per_row_tile = p.nv ? (p.k >> 6) : (p.k >> 7);
+    const int atoms_per_stage = p.nv ? 4 : 2;
+    volatile int *abort_flag = &abort_s;
+
+    if (threadIdx.x == 0) {
+        abort_s = 0;
+        for (int s = 0; s < C::STAGES; s++) {
+            tc::mbar_init(full + 8 * s, 1);
+            tc::mbar_init(empty + 8 * s, 1);
+            tc::mbar_init(full2 + 8 * s, 1);
+        }
+        for (int s = 0; s < C::SF_SETS; s++) {
+            tc::mbar_init(sf_full + 8 * s, 2 * C::SF_WARPS);  // the scale warps of both CTAs (used in the leader only)
+            tc::mbar_init(sf_empty + 8 * s, 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            tc::mbar_init(accum_full + 8 * a, 1);
+            tc::mbar_init(accum_empty + 8 * a, 2 * C::EPI_WARPS);  // the epilogue warps of both CTAs (used in the leader only)
+        }
+        tc::mbar_init_fence();
+    }
+    if (warp == 1) tc::tmem_alloc_pair(tc::smem_u32(&tmem_base_s), C::TMEM_COLS);
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::cluster_arrive();
+    tc::cluster_wait();
+    tc::fence_after_sync();
+    const uint32_t tmem = tmem_base_s;
+
+    if (warp == 0 && lane == 0) {
+        // ---------------- copies ----------------
+        const uint32_t sf_bytes = (uint32_t)atoms_per_stage * 512u;
+        const size_t ktiles = (size_t)nks;
+        uint32_t g = 0;
+        for (int t = pair; t < ntiles && !*abort_flag; t += npairs) {
+            const int rp = t / tok_tiles, tt = t % tok_tiles;
+            const int64_t my_row_tile = 2 * (int64_t)rp + rank;
+            const bool a_ok = my_row_tile < row_tiles;
+            // this CTA's NT / 2 activation rows: tokens [s0, s0 + NT / 2), in 128-token groups g0 (from row r0) and g0 + 1
+            const int64_t tok_s = (int64_t)NT * tt, s0 = tok_s + (NT / 2) * (int64_t)rank;
+            const int64_t g0 = s0 >> 7;
+            const int r0 = (int)(s0 & 127);
+            const int n1 = min(NT / 2, 128 - r0), n2 = NT / 2 - n1;
+            const bool b1_ok = g0 < p.x_row_tiles, b2_ok = n2 > 0 && g0 + 1 < p.x_row_tiles;
+            // the tile's scale atoms: groups G0 and (if the tile reaches into it) G0 + 1
+            const int64_t G0 = tok_s >> 7, G1 = (tok_s + NT - 1) >> 7;
+            const bool s1_ok = G0 < p.x_row_tiles, s2_ok = G1 != G0 && G1 < p.x_row_tiles;
+            const uint32_t tx = (a_ok ? 16384u + sf_bytes : 0u) + (b1_ok ? (uint32_t)n1 * 128u : 0u) + (b2_ok ? (uint32_t)n2 * 128u : 0u) +
+                                ((uint32_t)s1_ok + (uint32_t)s2_ok) * sf_bytes;
+            for (int ks = 0; ks < nks; ks++, g++) {
+                const uint32_t s = g % C::STAGES;
+                if (g >= (uint32_t)C::STAGES && !tc::mbar_wait_cluster(empty + 8 * s, (g / C::STAGES - 1) & 1u, abort_flag)) {
+                    abort_s = 1;
+                    atomicExch(p.status, 24);
+                    break;
+                }
+                const uint32_t st = smem_s + s * C::STAGE_BYTES, stb = st + C::A_BYTES, stsfa = stb + C::B_BYTES, stsfb = stsfa + C::SFA_BYTES;
+                tc::mbar_expect_tx(full + 8 * s, tx);
+                if (a_ok) {
+                    bulk_load(st, p.qw + ((size_t)my_row_tile * ktiles + ks) * 16384, 16384u, full + 8 * s);
+                    bulk_load(stsfa, p.sfw + ((size_t)my_row_tile * atoms_per_row_tile + (size_t)ks * atoms_per_stage) * 512, sf_bytes, full + 8 * s);
+                }
+                if (b1_ok) bulk_load(stb, p.qx + ((size_t)g0 * ktiles + ks) * 16384 + (size_t)r0 * 128, (uint32_t)n1 * 128u, full + 8 * s);
+                if (b2_ok) bulk_load(stb + (uint32_t)n1 * 128u, p.qx + ((size_t)(g0 + 1) * ktiles + ks) * 16384, (uint32_t)n2 * 128u, full + 8 * s);
+                if (s1_ok) bulk_load(stsfb, p.sfx + ((size_t)G0 * atoms_per_row_tile + (size_t)ks * atoms_per_stage) * 512, sf_bytes, full + 8 * s);
+                if (s2_ok) bulk_load(stsfb + 2048, p.sfx + ((size_t)G1 * atoms_per_row_tile + (size_t)ks * atoms_per_stage) * 512, sf_bytes, full + 8 * s);
+            }
+        }
+    } else if (warp == 1 && lane == 0 && rank != 0) {
+        // ---------------- partner CTA: tell the leader when this CTA's stage has landed ----------------
+        uint32_t g = 0;
+        for (int t = pair; t < ntiles && !*abort_flag; t += npairs)
+            for (int ks = 0; ks < nks; ks++, g++) {
+                const uint32_t s = g % C::STAGES;
+                if (!tc::mbar_wait(full + 8 * s, (g / C::STAGES) & 1u, abort_flag)) {
+                    abort_s = 1;
+                    atomicExch(p.status, 25);
+                    t = ntiles;
+                    break;
+                }
+                tc::mbar_arrive_cluster(tc::map_to_cta(full2 + 8 * s, 0));
+            }
+    } else if (warp == 1 && lane == 0) {
+        // ---------------- leader CTA: MMA issue for the pair, accumulator (tile & 1) ----------------
+        const uint32_t idesc_nv = tc::idesc_fp4(256, NT, 0, 0, 0);
+        uint32_t g = 0, it = 0;
+        for (int t = pair; t < ntiles && !*abort_flag; t += npairs, it++) {
+            const uint32_t acc = it & 1u;
+            // the tile before last used this accumulator: all sixteen epilogue warps of the pair have read it out
+            if (it >= 2 && !tc::mbar_wait_cluster(accum_empty + 8 * acc, ((it >> 1) - 1) & 1u, abort_flag)) {
+                abort_s = 1;
+                atomicExch(p.status, 26);
+                break;
+            }
+            tc::fence_after_sync();
+            const uint32_t td = tmem + acc * C::ACC1;
+            bool ok = true;
+            for (int ks = 0; ks < nks; ks++, g++) {
+                const uint32_t s = g % C::STAGES, ph = (g / C::STAGES) & 1u;
+                const uint32_t b = g % C::SF_SETS, bph = (g / C::SF_SETS) & 1u;
+                if (!tc::mbar_wait(full + 8 * s, ph, abort_flag) || !tc::mbar_wait_cluster(full2 + 8 * s, ph, abort_flag) ||
+                    !tc::mbar_wait_cluster(sf_full + 8 * b, bph, abort_flag)) {
+                    abort_s = 1;
+                    atomicExch(p.status, 22);
+                    ok = false;
+                    break;
+                }
+                tc::fence_after_sync();
+                const uint32_t st = smem_s + s * C::STAGE_BYTES;
+                const uint64_t ad = tc::smem_desc_sw128(st), bd = tc::smem_desc_sw128(st + C::A_BYTES);
+                const uint32_t tsfa = tmem + C::SF0 + C::SET_COLS * b, tsfb = tsfa + 16;
+                if (p.nv) {
+#pragma unroll
+                    for (int j = 0; j < 4; j++)
+                        tc::mma_nvf4_pair(td, ad + 2 * j, bd + 2 * j, idesc_nv, (uint32_t)((ks | j) != 0), tsfa + 4 * j, tsfb + C::SFB_PER_MMA * j);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const int id = (j & 1) * 2;
+                        tc::mma_mxf4_pair(td, ad + 2 * j, bd + 2 * j, tc::idesc_fp4(256, NT, 1, id, id), (uint32_t)((ks | j) != 0),
+                                          tsfa + 4 * (j >> 1), tsfb + C::SFB_PER_MMA * (j >> 1));
+                    }
+                }
+                tc::mma_commit_pair(empty + 8 * s);
+                tc::mma_commit_pair(tc::map_to_cta(empty + 8 * s, 1));
+                tc::mma_commit_pair(sf_empty + 8 * b);
+                tc::mma_commit_pair(tc::map_to_cta(sf_empty + 8 * b, 1));
+            }
+            if (!ok) break;
+            tc::mma_commit_pair(accum_full + 8 * acc);
+            tc::mma_commit_pair(tc::map_to_cta(accum_full + 8 * acc, 1));
+        }
+    } else if (warp >= 2 + C::EPI_WARPS) {
+        // ---------------- scale warps: stage -> tensor memory, lane quadrant warp % 4 ----------------
+        // An atom holds 128 rows x 4 scales: row r's four bytes at (r % 32) * 16 + (r / 32) * 4.  SFA atom j -> columns 4j.. of
+        // the set; SFB: the tile's 32-token group c is word (gt % 4) of group (gt / 4), gt = first token / 32 + c, and goes
+        // to column 16 + (NT / 32) * j + c.
+        const uint32_t quad_lane = (uint32_t)(32 * (warp & 3)) << 16;
+        const uint32_t sf_full_leader = tc::map_to_cta(sf_full, 0);
+        uint32_t g = 0;
+        bool ok = true;
+        for (int t = pair; t < ntiles && ok; t += npairs) {
+            const int tt = t % tok_tiles;
+            const int gt0 = (NT / 32) * tt, G0 = gt0 >> 2;
+            for (int ks = 0; ks < nks; ks++, g++) {
+                const uint32_t s = g % C::STAGES, b = g % C::SF_SETS;
+                ok = tc::mbar_wait(full + 8 * s, (g / C::STAGES) & 1u, abort_flag) &&
+                     (g < (uint32_t)C::SF_SETS || tc::mbar_wait_cluster(sf_empty + 8 * b, (g / C::SF_SETS - 1) & 1u, abort_flag));
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) {
+                    if (lane == 0 && !abort_s) {
+                        abort_s = 1;
+                        atomicExch(p.status, 28);
+                    }
+                    break;
+                }
+                tc::fence_after_sync();
+                const uint32_t sfa = smem_s + s * C::STAGE_BYTES + C::A_BYTES + C::B_BYTES + 16u * (uint32_t)lane, sfb = sfa + C::SFA_BYTES;
+                const uint32_t tsfa = tmem + quad_lane + C::SF0 + C::SET_COLS * b, tsfb = tsfa + 16;
+                for (int j = 0; j < atoms_per_stage; j++) {
+                    uint4 v;
+                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(sfa + 512u * j));
+                    tc::tmem_st4(tsfa + 4 * j, v.x, v.y, v.z, v.w);
+#pragma unroll
+                    for (int c = 0; c < C::CHUNKS; c += 2) {
+                        uint32_t w[2];
+#pragma unroll
+                        for (int e = 0; e < 2; e++) {
+                            const int gt = gt0 + c + e;
+                            asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(w[e]) : "r"(sfb + 2048u * (uint32_t)((gt >> 2) - G0) + 512u * j + 4u * (uint32_t)(gt & 3)));
+                        }
+                        tc::tmem_st2(tsfb + C::SFB_PER_MMA * j + c, w[0], w[1]);
+                    }
+                }
+                tc::tmem_st_wait();
+                tc::fence_before_sync();
+                __syncwarp();
+                if (lane == 0) tc::mbar_arrive_cluster(sf_full_leader + 8 * b);
+            }
+        }
+    }
+    __syncwarp();
+
+    if (warp >= 2 && warp < 2 + C::EPI_WARPS) {
+        // ---------------- epilogue: this CTA's 128 rows x NT tokens of accumulator (tile & 1) ----------------
+        // warp w reads TMEM lane quadrant w % 4; the two warps of a quadrant split the tile's 32-token column groups; two
+        // tensor-memory loads are in flight per warp
+        const int quad = warp & 3, half = (warp - 2) >> 2;
+        constexpr int PER = C::CHUNKS / 2;  // column groups per warp: 3 (NT = 192) or 2 (128)
+        uint8_t *stage = smem_raw + (smem_s - tc::smem_u32(smem_raw)) + (size_t)C::STAGES * C::STAGE_BYTES + (size_t)(warp - 2) * 4096;
+        const uint32_t accum_empty_leader = tc::map_to_cta(accum_empty, 0);
+        uint32_t it = 0;
+        for (int t = pair; t < ntiles; t += npairs, it++) {
+            const uint32_t acc = it & 1u;
+            bool ok = !abort_s && tc::mbar_wait_cluster(accum_full + 8 * acc, (it >> 1) & 1u, abort_flag);
+            if (!ok && !abort_s) {
+                abort_s = 1;
+                atomicExch(p.status, 23);
+            }
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc::fence_after_sync();
+            const int rp = t / tok_tiles, tt = t % tok_tiles;
+            const int64_t row0 = (2 * (int64_t)rp + rank) * 128 + 32 * quad, tok0 = (int64_t)NT * tt;
+            const uint32_t tbase = tmem + ((uint32_t)(32 * quad) << 16) + acc * C::ACC1 + (uint32_t)(32 * PER * half);
+            const auto emit = [&](const uint32_t (&v)[32], int ci) {
+                const int64_t tok = tok0 + 32 * (PER * half + ci);
+                if (row0 < p.n && tok < p.m) {
+                    float o[32];
+#pragma unroll
+                    for (int j = 0; j < 32; j++) o[j] = __uint_as_float(v[j]) * p.scale;
+                    if (p.y_bf16) tc::store_block_32x32<true>(p.y, p.ldy, row0, tok, p.n, p.m, o, stage, lane, p.vec);
+                    else tc::store_block_32x32<false>(p.y, p.ldy, row0, tok, p.n, p.m, o, stage, lane, p.vec);
+                }
+            };
+            uint32_t va[32], vb[32];
+            tc::tmem_ld32(tbase, va);
+            tc::tmem_ld32(tbase + 32, vb);
+            tc::tmem_ld_wait();
+            emit(va, 0);
+            if (PER > 2) tc::tmem_ld32(tbase + 64, va);
+            emit(vb, 1);
+            if (PER > 2) {
+                tc::tmem_ld_wait();
+                emit(va, 2);
+            }
+            // this warp's reads of the accumulator are complete: the leader may reuse it for the tile after next
+            tc::fence_before_sync();
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive_cluster(accum_empty_leader + 8 * acc);
+        }
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::cluster_arrive();
+    tc::cluster_wait();
+    if (warp == 1) tc::tmem_dealloc_pair(tmem, C::TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------------------------
 // Ceiling probe: the block-scaled FP4 MMA of the kernels above issued back to back on operands that never leave
 // shared memory (no copies from L2, no epilogue), one CTA (or CTA pair) per SM, k-steps of four MMAs committed to a
 // ring of four barriers like the real pipelines.  What this reaches is the most the GEMM kernels can: it is the
@@ -671,13 +955,20 @@ int32_t gemm_fp4_launch(Ctx *c, const Weight *w, const Weight *x, void *y, int y
     p.vec = (((uintptr_t)y & 15) == 0 && (ldy * (y_bf16 ? 2 : 4)) % 16 == 0) ? 1 : 0;
     p.status = c->status_dev;
     if (m > 128 && c->gemm_fp4_pair) {
-        static int pairs_resident[64] = {};  // per device: CTA pairs that can be resident at once (0 = not yet asked)
-        if (!pairs_resident[dev_slot]) {
-            GK_CUDA(c, cudaFuncSetAttribute(gemm_fp4_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P4_SMEM));
+        // 1: one 256-token accumulator; 2 (default): two 192-token accumulators; 3: two 128-token accumulators
+        const int variant = (int)c->gemm_fp4_pair;
+        const int tile_tok = variant == 1 ? 256 : (variant == 3 ? 128 : 192);
+        const size_t smem_bytes = variant == 1 ? P4_SMEM : (variant == 3 ? P2<128>::SMEM : P2<192>::SMEM);
+        const int threads = variant == 1 ? P4_THREADS : P2<192>::THREADS;
+        const void *fn = variant == 1 ? (const void *)gemm_fp4_pair_kernel
+                                      : (variant == 3 ? (const void *)gemm_fp4_pair2_kernel<128> : (const void *)gemm_fp4_pair2_kernel<192>);
+        static int pairs_resident[64][4] = {};  // per device and variant: CTA pairs resident at once (0 = not yet asked)
+        if (!pairs_resident[dev_slot][variant & 3]) {
+            GK_CUDA(c, cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3((unsigned)c->sm_count & ~1u);
-            cfg.blockDim = dim3(P4_THREADS);
-            cfg.dynamicSmemBytes = P4_SMEM;
+            cfg.blockDim = dim3((unsigned)threads);
+            cfg.dynamicSmemBytes = smem_bytes;
             int nclusters = 0;
             cudaLaunchAttribute at[1];
             at[0].id = cudaLaunchAttributeClusterDimension;
@@ -686,16 +977,19 @@ int32_t gemm_fp4_launch(Ctx *c, const Weight *w, const Weight *x, void *y, int y
             at[0].val.clusterDim.z = 1;
             cfg.attrs = at;
             cfg.numAttrs = 1;
-            if (cudaOccupancyMaxActiveClusters(&nclusters, gemm_fp4_pair_kernel, &cfg) != cudaSuccess || nclusters < 1) {
+            if (cudaOccupancyMaxActiveClusters(&nclusters, fn, &cfg) != cudaSuccess || nclusters < 1) {
                 (void)cudaGetLastError();
                 nclusters = c->sm_count / 2;
             }
-            pairs_resident[dev_slot] = nclusters < c->sm_count / 2 ? nclusters : c->sm_count / 2;
+            pairs_resident[dev_slot][variant & 3] = nclusters < c->sm_count / 2 ? nclusters : c->sm_count / 2;
         }
-        const int row_tiles = (int)(w->n_pad / 128), tok_tiles = (m + 255) / 256;
+        const int row_tiles = (int)(w->n_pad / 128), tok_tiles = (m + tile_tok - 1) / tile_tok;
         const int ntiles = ((row_tiles + 1) / 2) * tok_tiles;
-        const int npairs = ntiles < pairs_resident[dev_slot] ? ntiles : pairs_resident[dev_slot];
-        gemm_fp4_pair_kernel<<<dim3(2u * (unsigned)npairs), P4_THREADS, P4_SMEM, s>>>(p, row_tiles, tok_tiles);
+        const int resident = pairs_resident[dev_slot][variant & 3];
+        const int npairs = ntiles < resident ? ntiles : resident;
+        if (variant == 1) gemm_fp4_pair_kernel<<<dim3(2u * (unsigned)npairs), P4_THREADS, P4_SMEM, s>>>(p, row_tiles, tok_tiles);
+        else if (variant == 3) gemm_fp4_pair2_kernel<128><<<dim3(2u * (unsigned)npairs), P2<128>::THREADS, P2<128>::SMEM, s>>>(p, row_tiles, tok_tiles);
+        else gemm_fp4_pair2_kernel<192><<<dim3(2u * (unsigned)npairs), P2<192>::THREADS, P2<192>::SMEM, s>>>(p, row_tiles, tok_tiles);
         GK_CUDA(c, cudaGetLastError());
         return GLLMK_STATUS_OK;
     }

@@ -192,13 +192,20 @@ def test_gemm_fp4_mxfp4(gk, K, oracle, n, k, m):
 
 
 @pytest.mark.parametrize("fmt,n,k,m", [("nvfp4", 256, 256, 256), ("nvfp4", 128, 512, 300), ("nvfp4", 384, 1024, 129), ("nvfp4", 640, 768, 513),
-                                       ("nvfp4", 1100, 2560, 777), ("mxfp4", 256, 512, 256), ("mxfp4", 900, 1280, 600)])
-def test_gemm_fp4_cta_pair_kernel(gk, K, oracle, fmt, n, k, m):
-    """m > 128 runs on the persistent CTA-pair kernel: an odd number of 128-row groups (the pair's second CTA has no rows),
-    token counts that leave the second half of a tile empty or ragged, more k-steps than pipeline stages, several
-    tiles per pair — against the oracle, and against the one-CTA kernel."""
-    K.set("gemm_fp4_pair", 1)
-    assert run_fp4_case(gk, K, oracle, fmt, n, k, m, seed=n + m) <= 2e-3
+                                       ("nvfp4", 1100, 2560, 777), ("mxfp4", 256, 512, 256), ("mxfp4", 900, 1280, 600),
+                                       ("nvfp4", 512, 512, 193), ("nvfp4", 260, 1536, 1000)])
+@pytest.mark.parametrize("variant", [1, 2, 3])
+def test_gemm_fp4_cta_pair_kernel(gk, K, oracle, fmt, n, k, m, variant):
+    """m > 128 runs on a persistent CTA-pair kernel (variant 1: one 256-token accumulator; 2: two of 192 tokens, whose tiles
+    straddle the 128-token groups of the activation planes; 3: two of 128): an odd number of 128-row groups (the pair's
+    second CTA has no rows), token counts that leave part of a tile empty or ragged, more k-steps than pipeline stages,
+    several tiles per pair — against the oracle, and against the one-CTA kernel."""
+    K.set("gemm_fp4_pair", variant)
+    try:
+        assert run_fp4_case(gk, K, oracle, fmt, n, k, m, seed=n + m) <= 2e-3
+    finally:
+        K.set("gemm_fp4_pair", 2)
+    K.set("gemm_fp4_pair", variant)
     import torch
     rng = np.random.default_rng(n * m)
     W = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
@@ -216,7 +223,7 @@ def test_gemm_fp4_cta_pair_kernel(gk, K, oracle, fmt, n, k, m):
     try:
         y_one = K.gemm_fp4(w, x, out_dtype=torch.bfloat16)
     finally:
-        K.set("gemm_fp4_pair", 1)
+        K.set("gemm_fp4_pair", 2)
     torch.cuda.synchronize()
     assert K.status() == 0
     # the same products in the same k order: equal up to the last bf16 bit of the output
@@ -226,11 +233,12 @@ def test_gemm_fp4_cta_pair_kernel(gk, K, oracle, fmt, n, k, m):
     x.free()
 
 
-def test_gemm_fp4_cta_pair_kernel_many_tiles(gk, K, oracle):
+@pytest.mark.parametrize("variant", [1, 2, 3])
+def test_gemm_fp4_cta_pair_kernel_many_tiles(gk, K, oracle, variant):
     """More tiles than resident pairs: every pair walks several tiles, the accumulator hand-over between the MMA
     thread and the sixteen epilogue warps of a pair is exercised over many rounds."""
     import torch
-    n, k, m = 6144, 512, 2048  # 24 row pairs x 8 token tiles = 192 tiles on 74 pairs
+    n, k, m = 6144, 512, 2048  # 24 row pairs x 8 / 11 / 16 token tiles on 74 pairs
     qt = gk.QuantType.nvfp4()
     g = torch.Generator(device="cuda").manual_seed(5)
     W = torch.randn((n, k), generator=g, device="cuda") * 0.02
@@ -238,7 +246,11 @@ def test_gemm_fp4_cta_pair_kernel_many_tiles(gk, K, oracle):
     wb, gw = K.quantize(qt, W)
     xb, gx = K.quantize(qt, X)
     w, x = K.upload(qt, n, k, wb, None, gw), K.upload(qt, m, k, xb, None, gx)
-    y = K.gemm_fp4(w, x)
+    K.set("gemm_fp4_pair", variant)
+    try:
+        y = K.gemm_fp4(w, x)
+    finally:
+        K.set("gemm_fp4_pair", 2)
     torch.cuda.synchronize()
     assert K.status() == 0
     wd = oracle.dequant_matrix(oracle.NVFP4, wb.cpu().numpy(), n, k, global_scale=gw)
