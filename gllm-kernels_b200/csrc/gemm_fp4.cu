@@ -231,13 +231,13 @@ constexpr uint32_t P4_TMEM_SF = 256, P4_SF_SET_COLS = 48;  // per set: SFA 16 co
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P4_THREADS, 1)
 gemm_fp4_pair_kernel(const __grid_constant__ Fp4Params p, const int row_tiles, const int tok_tiles) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bars[3 * P4_STAGES + 2 * P4_SF_SETS + 2];
+    __shared__ __align__(8) uint64_t bars[3 * P4_STAGES + P4_SF_SETS + 2];
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s;
     const uint32_t smem_s = (tc::smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t full = tc::smem_u32(&bars[0]), empty = tc::smem_u32(&bars[P4_STAGES]), full2 = tc::smem_u32(&bars[2 * P4_STAGES]);
-    const uint32_t sf_full = tc::smem_u32(&bars[3 * P4_STAGES]), sf_empty = tc::smem_u32(&bars[3 * P4_STAGES + P4_SF_SETS]);
-    const uint32_t accum_full = tc::smem_u32(&bars[3 * P4_STAGES + 2 * P4_SF_SETS]), accum_empty = accum_full + 8;
+    const uint32_t sf_full = tc::smem_u32(&bars[3 * P4_STAGES]);
+    const uint32_t accum_full = tc::smem_u32(&bars[3 * P4_STAGES + P4_SF_SETS]), accum_empty = accum_full + 8;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = tc::cluster_ctarank();
     const int pair = (int)(blockIdx.x >> 1), npairs = (int)(gridDim.x >> 1);
@@ -255,10 +255,7 @@ gemm_fp4_pair_kernel(const __grid_constant__ Fp4Params p, const int row_tiles, c
             tc::mbar_init(empty + 8 * s, 1);
             tc::mbar_init(full2 + 8 * s, 1);
         }
-        for (int s = 0; s < P4_SF_SETS; s++) {
-            tc::mbar_init(sf_full + 8 * s, 2 * P4_SF_WARPS);  // the scale warps of both CTAs (used in the leader only)
-            tc::mbar_init(sf_empty + 8 * s, 1);
-        }
+        for (int s = 0; s < P4_SF_SETS; s++) tc::mbar_init(sf_full + 8 * s, 2 * P4_SF_WARPS);  // the scale warps of both CTAs (leader only)
         tc::mbar_init(accum_full, 1);
         tc::mbar_init(accum_empty, 2 * P4_EPI_WARPS);
         tc::mbar_init_fence();
@@ -320,7 +317,7 @@ gemm_fp4_pair_kernel(const __grid_constant__ Fp4Params p, const int row_tiles, c
                     t = ntiles;
                     break;
                 }
-                tc::mbar_arrive_cluster(tc::map_to_cta(full2 + 8 * s, 0));
+                tc::mbar_arrive_cluster_relaxed(tc::map_to_cta(full2 + 8 * s, 0));
             }
     } else if (warp == 1 && lane == 0) {
         // ---------------- leader CTA: MMA issue for the pair ----------------
@@ -365,8 +362,6 @@ gemm_fp4_pair_kernel(const __grid_constant__ Fp4Params p, const int row_tiles, c
                 // once these MMAs have completed, stage s and column set b are free in BOTH CTAs
                 tc::mma_commit_pair(empty + 8 * s);
                 tc::mma_commit_pair(tc::map_to_cta(empty + 8 * s, 1));
-                tc::mma_commit_pair(sf_empty + 8 * b);
-                tc::mma_commit_pair(tc::map_to_cta(sf_empty + 8 * b, 1));
             }
             if (!ok) break;
             tc::mma_commit_pair(accum_full);
@@ -385,7 +380,8 @@ gemm_fp4_pair_kernel(const __grid_constant__ Fp4Params p, const int row_tiles, c
             for (int ks = 0; ks < nks; ks++, g++) {
                 const uint32_t s = g % P4_STAGES, b = g % P4_SF_SETS;
                 ok = tc::mbar_wait(full + 8 * s, (g / P4_STAGES) & 1u, abort_flag) &&
-                     (g < P4_SF_SETS || tc::mbar_wait_cluster(sf_empty + 8 * b, (g / P4_SF_SETS - 1) & 1u, abort_flag));
+                     // set b was last read by the MMAs of k-step g - 3, whose completion also released that k-step's stage
+                     (g < P4_SF_SETS || tc::mbar_wait_cluster(empty + 8 * ((g - P4_SF_SETS) % P4_STAGES), ((g - P4_SF_SETS) / P4_STAGES) & 1u, abort_flag));
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) {
                     if (lane == 0 && !abort_s) {
@@ -396,21 +392,24 @@ gemm_fp4_pair_kernel(const __grid_constant__ Fp4Params p, const int row_tiles, c
                 }
                 tc::fence_after_sync();
                 const uint32_t sfa = smem_s + s * P4_STAGE_BYTES + P4_A_BYTES + P4_B_BYTES + 16u * (uint32_t)lane, sfb = sfa + P4_SFA_BYTES;
-                const uint32_t tsfa = tmem + quad_lane + P4_TMEM_SF + P4_SF_SET_COLS * b, tsfb = tsfa + 16;
-                for (int j = 0; j < atoms_per_stage; j++) {
-                    uint4 v;
-                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(sfa + 512u * j));
-                    tc::tmem_st4(tsfa + 4 * j, v.x, v.y, v.z, v.w);
+                const uint32_t tsfa = tmem + quad_lane + P4_TMEM_SF + P4_SF_SET_COLS * b;
+                // the set's 48 columns built in registers, two wide stores (with two atoms per stage the rest is never read)
+                uint32_t w[48];
 #pragma unroll
-                    for (int h = 0; h < 2; h++) {
-                        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(sfb + 2048u * h + 512u * j));
-                        tc::tmem_st4(tsfb + 8 * j + 4 * h, v.x, v.y, v.z, v.w);
-                    }
+                for (int j = 0; j < 4; j++) {
+                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(w[4 * j]), "=r"(w[4 * j + 1]), "=r"(w[4 * j + 2]), "=r"(w[4 * j + 3]) : "r"(sfa + 512u * j));
+#pragma unroll
+                    for (int h = 0; h < 2; h++)
+                        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                                     : "=r"(w[16 + 8 * j + 4 * h]), "=r"(w[17 + 8 * j + 4 * h]), "=r"(w[18 + 8 * j + 4 * h]), "=r"(w[19 + 8 * j + 4 * h])
+                                     : "r"(sfb + 2048u * h + 512u * j));
                 }
+                tc::tmem_st32(tsfa, w);
+                tc::tmem_st16(tsfa + 32, w + 32);
                 tc::tmem_st_wait();
                 tc::fence_before_sync();
                 __syncwarp();
-                if (lane == 0) tc::mbar_arrive_cluster(sf_full_leader + 8 * b);
+                if (lane == 0) tc::mbar_arrive_cluster_relaxed(sf_full_leader + 8 * b);
             }
     }
     __syncwarp();
@@ -432,22 +431,57 @@ gemm_fp4_pair_kernel(const __grid_constant__ Fp4Params p, const int row_tiles, c
             tc::fence_after_sync();
             const int rp = t / tok_tiles, tt = t % tok_tiles;
             const int64_t row0 = (2 * (int64_t)rp + rank) * 128 + 32 * quad, tok0 = (int64_t)tt * 256;
-            for (int c = 128 * half; c < 128 * half + 128; c += 32) {
-                uint32_t v[32];
-                tc::tmem_ld32(tmem + ((uint32_t)(32 * quad) << 16) + (uint32_t)c, v);
-                tc::tmem_ld_wait();
-                if (row0 < p.n && tok0 + c < p.m) {
-                    float o[32];
+            const uint32_t tbase = tmem + ((uint32_t)(32 * quad) << 16) + (uint32_t)(128 * half);
+            if (p.y_bf16) {
+                // bf16 output: the warp's 32 rows x 128 tokens fit in registers as packed pairs (64 per thread), so the
+                // accumulator is handed back to the MMA thread after four tensor-memory loads and the stores run under the
+                // next tile's MMAs (with the stores in front of the hand-over the epilogue was ~23 % of a tile's time)
+                uint32_t pk[4][16], v[2][32];
+                tc::tmem_ld32(tbase, v[0]);
 #pragma unroll
-                    for (int j = 0; j < 32; j++) o[j] = __uint_as_float(v[j]) * p.scale;
-                    if (p.y_bf16) tc::store_block_32x32<true>(p.y, p.ldy, row0, tok0 + c, p.n, p.m, o, stage, lane, p.vec);
-                    else tc::store_block_32x32<false>(p.y, p.ldy, row0, tok0 + c, p.n, p.m, o, stage, lane, p.vec);
+                for (int ci = 0; ci < 4; ci++) {
+                    tc::tmem_ld_wait();
+                    if (ci < 3) tc::tmem_ld32(tbase + 32 * (ci + 1), v[(ci + 1) & 1]);
+#pragma unroll
+                    for (int j = 0; j < 16; j++) {
+                        const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[ci & 1][2 * j]) * p.scale, __uint_as_float(v[ci & 1][2 * j + 1]) * p.scale);
+                        pk[ci][j] = *reinterpret_cast<const uint32_t *>(&h);
+                    }
                 }
+                tc::fence_before_sync();
+                __syncwarp();
+                if (lane == 0) tc::mbar_arrive_cluster_relaxed(accum_empty_leader);  // the loads above have completed (wait::ld)
+#pragma unroll
+                for (int ci = 0; ci < 4; ci++) {
+                    const int64_t tok = tok0 + 128 * half + 32 * ci;
+                    if (row0 < p.n && tok < p.m) {
+                        float o[32];
+#pragma unroll
+                        for (int j = 0; j < 16; j++) {
+                            o[2 * j] = __uint_as_float(pk[ci][j] << 16);
+                            o[2 * j + 1] = __uint_as_float(pk[ci][j] & 0xffff0000u);
+                        }
+                        tc::store_block_32x32<true>(p.y, p.ldy, row0, tok, p.n, p.m, o, stage, lane, p.vec);
+                    }
+                }
+            } else {
+                for (int c = 0; c < 128; c += 32) {
+                    uint32_t v[32];
+                    tc::tmem_ld32(tbase + (uint32_t)c, v);
+                    tc::tmem_ld_wait();
+                    const int64_t tok = tok0 + 128 * half + c;
+                    if (row0 < p.n && tok < p.m) {
+                        float o[32];
+#pragma unroll
+                        for (int j = 0; j < 32; j++) o[j] = __uint_as_float(v[j]) * p.scale;
+                        tc::store_block_32x32<false>(p.y, p.ldy, row0, tok, p.n, p.m, o, stage, lane, p.vec);
+                    }
+                }
+                // this warp's reads of the accumulator are complete: the leader may start the next tile
+                tc::fence_before_sync();
+                __syncwarp();
+                if (lane == 0) tc::mbar_arrive_cluster(accum_empty_leader);
             }
-            // this warp's reads of the accumulator are complete: the leader may start the next tile
-            tc::fence_before_sync();
-            __syncwarp();
-            if (lane == 0) tc::mbar_arrive_cluster(accum_empty_leader);
         }
     }
     tc::fence_before_sync();
@@ -472,12 +506,32 @@ gemm_fp4_pair_kernel(const __grid_constant__ Fp4Params p, const int row_tiles, c
 // 128-byte swizzle only depends on row % 8, which a shift by a multiple of 8 rows keeps), and the scale warps pick the
 // tile's 32-token column groups out of the (at most two) groups of scale atoms the tile touches.
 // ---------------------------------------------------------------------------------------------
+#ifdef GLLMK_FP4_PROF
+// Development aid (not built by default): cycles each role of gemm_fp4_pair2_kernel spends in its waits.
+__device__ unsigned long long g_fp4_prof[296 * 16];
+#define PROF_DECL unsigned long long prof_t = 0, prof_a[4] = {0, 0, 0, 0}, prof_start = clock64()
+#define PROF_T0() prof_t = clock64()
+#define PROF_ACC(i) prof_a[i] += clock64() - prof_t
+#define PROF_OUT(slot, i) g_fp4_prof[blockIdx.x * 16 + (slot)] = prof_a[i]
+#define PROF_TOTAL(slot) g_fp4_prof[blockIdx.x * 16 + (slot)] = clock64() - prof_start
+// timeline of the first 256 k-steps of CTA 0 (the leader of pair 0): row r, k-step g
+__device__ unsigned long long g_fp4_tl[8 * 256];
+#define PROF_TL(r, g) do { if (blockIdx.x == 0 && (g) < 256u) g_fp4_tl[(r) * 256 + (g)] = clock64(); } while (0)
+#else
+#define PROF_TL(r, g)
+#define PROF_DECL
+#define PROF_T0()
+#define PROF_ACC(i)
+#define PROF_OUT(slot, i)
+#define PROF_TOTAL(slot)
+#endif
+
 template <int NT>
 struct P2 {
-    static constexpr int STAGES = 5;
+    static constexpr int STAGES = 6;
     static constexpr int A_BYTES = 16384, B_BYTES = NT / 2 * 128, SFA_BYTES = 2048, SFB_BYTES = 4096;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
-    static constexpr int EPI_WARPS = 8, SF_WARPS = 4, SF_SETS = 3;
+    static constexpr int EPI_WARPS = 4, SF_WARPS = 4, SF_SETS = 3;
     static constexpr int THREADS = 64 + 32 * (EPI_WARPS + SF_WARPS);
     static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + (size_t)EPI_WARPS * 4096 + 1024;
     static constexpr uint32_t TMEM_COLS = 512, ACC1 = NT, SF0 = 2 * NT, SFB_PER_MMA = NT / 32, SET_COLS = 16 + NT / 8;
@@ -490,13 +544,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P2<NT>::THREADS, 1)
 gemm_fp4_pair2_kernel(const __grid_constant__ Fp4Params p, const int row_tiles, const int tok_tiles) {
     using C = P2<NT>;
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bars[3 * C::STAGES + 2 * C::SF_SETS + 4];
+    __shared__ __align__(8) uint64_t bars[3 * C::STAGES + C::SF_SETS + 4];
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s;
     const uint32_t smem_s = (tc::smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t full = tc::smem_u32(&bars[0]), empty = tc::smem_u32(&bars[C::STAGES]), full2 = tc::smem_u32(&bars[2 * C::STAGES]);
-    const uint32_t sf_full = tc::smem_u32(&bars[3 * C::STAGES]), sf_empty = sf_full + 8 * C::SF_SETS;
-    const uint32_t accum_full = sf_empty + 8 * C::SF_SETS, accum_empty = accum_full + 16;  // two each
+    const uint32_t sf_full = tc::smem_u32(&bars[3 * C::STAGES]);
+    const uint32_t accum_full = sf_full + 8 * C::SF_SETS, accum_empty = accum_full + 16;  // two each
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = tc::cluster_ctarank();
     const int pair = (int)(blockIdx.x >> 1), npairs = (int)(gridDim.x >> 1);
@@ -514,10 +568,7 @@ gemm_fp4_pair2_kernel(const __grid_constant__ Fp4Params p, const int row_tiles, 
             tc::mbar_init(empty + 8 * s, 1);
             tc::mbar_init(full2 + 8 * s, 1);
         }
-        for (int s = 0; s < C::SF_SETS; s++) {
-            tc::mbar_init(sf_full + 8 * s, 2 * C::SF_WARPS);  // the scale warps of both CTAs (used in the leader only)
-            tc::mbar_init(sf_empty + 8 * s, 1);
-        }
+        for (int s = 0; s < C::SF_SETS; s++) tc::mbar_init(sf_full + 8 * s, 2 * C::SF_WARPS);  // the scale warps of both CTAs (leader only)
         for (int a = 0; a < 2; a++) {
             tc::mbar_init(accum_full + 8 * a, 1);
             tc::mbar_init(accum_empty + 8 * a, 2 * C::EPI_WARPS);  // the epilogue warps of both CTAs (used in the leader only)
@@ -537,6 +588,7 @@ gemm_fp4_pair2_kernel(const __grid_constant__ Fp4Params p, const int row_tiles, 
         const uint32_t sf_bytes = (uint32_t)atoms_per_stage * 512u;
         const size_t ktiles = (size_t)nks;
         uint32_t g = 0;
+        PROF_DECL;
         for (int t = pair; t < ntiles && !*abort_flag; t += npairs) {
             const int rp = t / tok_tiles, tt = t % tok_tiles;
             const int64_t my_row_tile = 2 * (int64_t)rp + rank;
@@ -554,11 +606,14 @@ gemm_fp4_pair2_kernel(const __grid_constant__ Fp4Params p, const int row_tiles, 
                                 ((uint32_t)s1_ok + (uint32_t)s2_ok) * sf_bytes;
             for (int ks = 0; ks < nks; ks++, g++) {
                 const uint32_t s = g % C::STAGES;
+                PROF_T0();
                 if (g >= (uint32_t)C::STAGES && !tc::mbar_wait_cluster(empty + 8 * s, (g / C::STAGES - 1) & 1u, abort_flag)) {
                     abort_s = 1;
                     atomicExch(p.status, 24);
                     break;
                 }
+                PROF_ACC(0);
+                PROF_TL(0, g);
                 const uint32_t st = smem_s + s * C::STAGE_BYTES, stb = st + C::A_BYTES, stsfa = stb + C::B_BYTES, stsfb = stsfa + C::SFA_BYTES;
                 tc::mbar_expect_tx(full + 8 * s, tx);
                 if (a_ok) {
@@ -571,6 +626,8 @@ gemm_fp4_pair2_kernel(const __grid_constant__ Fp4Params p, const int row_tiles, 
                 if (s2_ok) bulk_load(stsfb + 2048, p.sfx + ((size_t)G1 * atoms_per_row_tile + (size_t)ks * atoms_per_stage) * 512, sf_bytes, full + 8 * s);
             }
         }
+        PROF_OUT(0, 0);
+        PROF_TOTAL(13);
     } else if (warp == 1 && lane == 0 && rank != 0) {
         // ---------------- partner CTA: tell the leader when this CTA's stage has landed ----------------
         uint32_t g = 0;
@@ -583,28 +640,46 @@ gemm_fp4_pair2_kernel(const __grid_constant__ Fp4Params p, const int row_tiles, 
                     t = ntiles;
                     break;
                 }
-                tc::mbar_arrive_cluster(tc::map_to_cta(full2 + 8 * s, 0));
+                tc::mbar_arrive_cluster_relaxed(tc::map_to_cta(full2 + 8 * s, 0));
             }
     } else if (warp == 1 && lane == 0) {
         // ---------------- leader CTA: MMA issue for the pair, accumulator (tile & 1) ----------------
         const uint32_t idesc_nv = tc::idesc_fp4(256, NT, 0, 0, 0);
         uint32_t g = 0, it = 0;
+        PROF_DECL;
         for (int t = pair; t < ntiles && !*abort_flag; t += npairs, it++) {
             const uint32_t acc = it & 1u;
+            PROF_T0();
             // the tile before last used this accumulator: all sixteen epilogue warps of the pair have read it out
             if (it >= 2 && !tc::mbar_wait_cluster(accum_empty + 8 * acc, ((it >> 1) - 1) & 1u, abort_flag)) {
                 abort_s = 1;
                 atomicExch(p.status, 26);
                 break;
             }
+            PROF_ACC(3);
             tc::fence_after_sync();
             const uint32_t td = tmem + acc * C::ACC1;
             bool ok = true;
             for (int ks = 0; ks < nks; ks++, g++) {
                 const uint32_t s = g % C::STAGES, ph = (g / C::STAGES) & 1u;
                 const uint32_t b = g % C::SF_SETS, bph = (g / C::SF_SETS) & 1u;
+#ifdef GLLMK_FP4_PROF
+                PROF_T0();
+                bool w_ok = tc::mbar_wait(full + 8 * s, ph, abort_flag);
+                PROF_ACC(0);
+                PROF_T0();
+                w_ok = w_ok && tc::mbar_wait_cluster(full2 + 8 * s, ph, abort_flag);
+                PROF_ACC(1);
+                PROF_TL(1, g);
+                PROF_T0();
+                w_ok = w_ok && tc::mbar_wait_cluster(sf_full + 8 * b, bph, abort_flag);
+                PROF_ACC(2);
+                PROF_TL(2, g);
+                if (!w_ok) {
+#else
                 if (!tc::mbar_wait(full + 8 * s, ph, abort_flag) || !tc::mbar_wait_cluster(full2 + 8 * s, ph, abort_flag) ||
                     !tc::mbar_wait_cluster(sf_full + 8 * b, bph, abort_flag)) {
+#endif
                     abort_s = 1;
                     atomicExch(p.status, 22);
                     ok = false;
@@ -628,30 +703,42 @@ gemm_fp4_pair2_kernel(const __grid_constant__ Fp4Params p, const int row_tiles, 
                 }
                 tc::mma_commit_pair(empty + 8 * s);
                 tc::mma_commit_pair(tc::map_to_cta(empty + 8 * s, 1));
-                tc::mma_commit_pair(sf_empty + 8 * b);
-                tc::mma_commit_pair(tc::map_to_cta(sf_empty + 8 * b, 1));
+                PROF_TL(3, g);
             }
             if (!ok) break;
             tc::mma_commit_pair(accum_full + 8 * acc);
             tc::mma_commit_pair(tc::map_to_cta(accum_full + 8 * acc, 1));
         }
+        PROF_OUT(1, 0);
+        PROF_OUT(2, 1);
+        PROF_OUT(3, 2);
+        PROF_OUT(4, 3);
+        PROF_TOTAL(5);
     } else if (warp >= 2 + C::EPI_WARPS) {
         // ---------------- scale warps: stage -> tensor memory, lane quadrant warp % 4 ----------------
         // An atom holds 128 rows x 4 scales: row r's four bytes at (r % 32) * 16 + (r / 32) * 4.  SFA atom j -> columns 4j.. of
-        // the set; SFB: the tile's 32-token group c is word (gt % 4) of group (gt / 4), gt = first token / 32 + c, and goes
-        // to column 16 + (NT / 32) * j + c.
+        // the set; SFB: the tile's 32-token group c is word (gt % 4) of 128-token group (gt / 4), gt = first token / 32 + c,
+        // and goes to column 16 + (NT / 32) * j + c.
         const uint32_t quad_lane = (uint32_t)(32 * (warp & 3)) << 16;
         const uint32_t sf_full_leader = tc::map_to_cta(sf_full, 0);
         uint32_t g = 0;
         bool ok = true;
+        PROF_DECL;
         for (int t = pair; t < ntiles && ok; t += npairs) {
-            const int tt = t % tok_tiles;
-            const int gt0 = (NT / 32) * tt, G0 = gt0 >> 2;
+            const bool tile_odd = NT == 192 && ((t % tok_tiles) & 1);
             for (int ks = 0; ks < nks; ks++, g++) {
                 const uint32_t s = g % C::STAGES, b = g % C::SF_SETS;
-                ok = tc::mbar_wait(full + 8 * s, (g / C::STAGES) & 1u, abort_flag) &&
-                     (g < (uint32_t)C::SF_SETS || tc::mbar_wait_cluster(sf_empty + 8 * b, (g / C::SF_SETS - 1) & 1u, abort_flag));
+                PROF_T0();
+                ok = tc::mbar_wait(full + 8 * s, (g / C::STAGES) & 1u, abort_flag);
+                PROF_ACC(0);
+                PROF_T0();
+                // set b was last read by the MMAs of k-step g - 3, whose completion also released that k-step's stage
+                ok = ok && (g < (uint32_t)C::SF_SETS ||
+                            tc::mbar_wait_cluster(empty + 8 * ((g - C::SF_SETS) % C::STAGES), ((g - C::SF_SETS) / C::STAGES) & 1u, abort_flag));
+                PROF_ACC(1);
                 ok = __all_sync(0xffffffffu, ok);
+                PROF_T0();
+                if (warp == 2 + C::EPI_WARPS && lane == 0) PROF_TL(4, g);
                 if (!ok) {
                     if (lane == 0 && !abort_s) {
                         abort_s = 1;
@@ -661,55 +748,81 @@ gemm_fp4_pair2_kernel(const __grid_constant__ Fp4Params p, const int row_tiles, 
                 }
                 tc::fence_after_sync();
                 const uint32_t sfa = smem_s + s * C::STAGE_BYTES + C::A_BYTES + C::B_BYTES + 16u * (uint32_t)lane, sfb = sfa + C::SFA_BYTES;
-                const uint32_t tsfa = tmem + quad_lane + C::SF0 + C::SET_COLS * b, tsfb = tsfa + 16;
-                for (int j = 0; j < atoms_per_stage; j++) {
-                    uint4 v;
-                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(sfa + 512u * j));
-                    tc::tmem_st4(tsfa + 4 * j, v.x, v.y, v.z, v.w);
+                const uint32_t tsfa = tmem + quad_lane + C::SF0 + C::SET_COLS * b;
+                // the whole set is built in registers and stored with one (NT = 128) or two (192) wide tcgen05.st: per-atom
+                // stores made this role the slowest of the kernel (1500 cycles per k-step, the MMA thread waiting on it half
+                // of the time).  With two atoms per stage (MXFP4) the upper columns carry stale bytes nobody reads.
+                uint32_t w[C::SET_COLS];
 #pragma unroll
-                    for (int c = 0; c < C::CHUNKS; c += 2) {
-                        uint32_t w[2];
-#pragma unroll
-                        for (int e = 0; e < 2; e++) {
-                            const int gt = gt0 + c + e;
-                            asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(w[e]) : "r"(sfb + 2048u * (uint32_t)((gt >> 2) - G0) + 512u * j + 4u * (uint32_t)(gt & 3)));
-                        }
-                        tc::tmem_st2(tsfb + C::SFB_PER_MMA * j + c, w[0], w[1]);
+                for (int j = 0; j < 4; j++) {
+                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(w[4 * j]), "=r"(w[4 * j + 1]), "=r"(w[4 * j + 2]), "=r"(w[4 * j + 3]) : "r"(sfa + 512u * j));
+                    if (NT == 128) {
+                        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                                     : "=r"(w[16 + 4 * j]), "=r"(w[17 + 4 * j]), "=r"(w[18 + 4 * j]), "=r"(w[19 + 4 * j]) : "r"(sfb + 512u * j));
+                    } else if (tile_odd) {  // the tile starts at token 64 of group G0: words 2, 3 of G0, then words 0..3 of G0 + 1
+                        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];\n" : "=r"(w[16 + 6 * j]), "=r"(w[17 + 6 * j]) : "r"(sfb + 512u * j + 8u));
+                        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                                     : "=r"(w[18 + 6 * j]), "=r"(w[19 + 6 * j]), "=r"(w[20 + 6 * j]), "=r"(w[21 + 6 * j]) : "r"(sfb + 2048u + 512u * j));
+                    } else {  // the tile starts at token 0 of group G0: words 0..3 of G0, then words 0, 1 of G0 + 1
+                        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                                     : "=r"(w[16 + 6 * j]), "=r"(w[17 + 6 * j]), "=r"(w[18 + 6 * j]), "=r"(w[19 + 6 * j]) : "r"(sfb + 512u * j));
+                        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];\n" : "=r"(w[20 + 6 * j]), "=r"(w[21 + 6 * j]) : "r"(sfb + 2048u + 512u * j));
                     }
                 }
+#ifdef GLLMK_FP4_PROF
+                {
+                    uint32_t dep;
+                    asm volatile("add.u32 %0, %1, %2;\n" : "=r"(dep) : "r"(w[C::SET_COLS - 1]), "r"(w[0]));
+                    if (warp == 2 + C::EPI_WARPS && lane == 0) PROF_TL(5, g);
+                }
+#endif
+                tc::tmem_st32(tsfa, w);
+                if (NT == 192) tc::tmem_st8(tsfa + 32, w + 32);
                 tc::tmem_st_wait();
+                if (warp == 2 + C::EPI_WARPS && lane == 0) PROF_TL(6, g);
                 tc::fence_before_sync();
                 __syncwarp();
-                if (lane == 0) tc::mbar_arrive_cluster(sf_full_leader + 8 * b);
+                if (lane == 0) tc::mbar_arrive_cluster_relaxed(sf_full_leader + 8 * b);
+                PROF_ACC(2);
+                if (warp == 2 + C::EPI_WARPS && lane == 0) PROF_TL(7, g);
             }
+        }
+        if (warp == 2 + C::EPI_WARPS && lane == 0) {
+            PROF_OUT(6, 0);
+            PROF_OUT(7, 1);
+            PROF_OUT(8, 2);
+            PROF_TOTAL(9);
         }
     }
     __syncwarp();
 
     if (warp >= 2 && warp < 2 + C::EPI_WARPS) {
         // ---------------- epilogue: this CTA's 128 rows x NT tokens of accumulator (tile & 1) ----------------
-        // warp w reads TMEM lane quadrant w % 4; the two warps of a quadrant split the tile's 32-token column groups; two
-        // tensor-memory loads are in flight per warp
-        const int quad = warp & 3, half = (warp - 2) >> 2;
-        constexpr int PER = C::CHUNKS / 2;  // column groups per warp: 3 (NT = 192) or 2 (128)
+        // warp w reads TMEM lane quadrant w % 4 and walks the tile's 32-token column groups with one tensor-memory load in
+        // flight under the stores of the group before (the whole epilogue runs under the next tile's MMAs)
+        const int quad = warp & 3;
         uint8_t *stage = smem_raw + (smem_s - tc::smem_u32(smem_raw)) + (size_t)C::STAGES * C::STAGE_BYTES + (size_t)(warp - 2) * 4096;
         const uint32_t accum_empty_leader = tc::map_to_cta(accum_empty, 0);
         uint32_t it = 0;
+        PROF_DECL;
         for (int t = pair; t < ntiles; t += npairs, it++) {
             const uint32_t acc = it & 1u;
+            PROF_T0();
             bool ok = !abort_s && tc::mbar_wait_cluster(accum_full + 8 * acc, (it >> 1) & 1u, abort_flag);
+            PROF_ACC(0);
             if (!ok && !abort_s) {
                 abort_s = 1;
                 atomicExch(p.status, 23);
             }
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
+            PROF_T0();
             tc::fence_after_sync();
             const int rp = t / tok_tiles, tt = t % tok_tiles;
             const int64_t row0 = (2 * (int64_t)rp + rank) * 128 + 32 * quad, tok0 = (int64_t)NT * tt;
-            const uint32_t tbase = tmem + ((uint32_t)(32 * quad) << 16) + acc * C::ACC1 + (uint32_t)(32 * PER * half);
+            const uint32_t tbase = tmem + ((uint32_t)(32 * quad) << 16) + acc * C::ACC1;
             const auto emit = [&](const uint32_t (&v)[32], int ci) {
-                const int64_t tok = tok0 + 32 * (PER * half + ci);
+                const int64_t tok = tok0 + 32 * ci;
                 if (row0 < p.n && tok < p.m) {
                     float o[32];
 #pragma unroll
@@ -720,19 +833,25 @@ gemm_fp4_pair2_kernel(const __grid_constant__ Fp4Params p, const int row_tiles, 
             };
             uint32_t va[32], vb[32];
             tc::tmem_ld32(tbase, va);
-            tc::tmem_ld32(tbase + 32, vb);
-            tc::tmem_ld_wait();
-            emit(va, 0);
-            if (PER > 2) tc::tmem_ld32(tbase + 64, va);
-            emit(vb, 1);
-            if (PER > 2) {
+#pragma unroll
+            for (int ci = 0; ci < C::CHUNKS; ci += 2) {
                 tc::tmem_ld_wait();
-                emit(va, 2);
+                tc::tmem_ld32(tbase + 32 * (ci + 1), vb);
+                emit(va, ci);
+                tc::tmem_ld_wait();
+                if (ci + 2 < C::CHUNKS) tc::tmem_ld32(tbase + 32 * (ci + 2), va);
+                emit(vb, ci + 1);
             }
             // this warp's reads of the accumulator are complete: the leader may reuse it for the tile after next
             tc::fence_before_sync();
             __syncwarp();
             if (lane == 0) tc::mbar_arrive_cluster(accum_empty_leader + 8 * acc);
+            PROF_ACC(1);
+        }
+        if (warp == 2 && lane == 0) {
+            PROF_OUT(10, 0);
+            PROF_OUT(11, 1);
+            PROF_TOTAL(12);
         }
     }
     tc::fence_before_sync();
@@ -855,22 +974,24 @@ __device__ __forceinline__ void probe_body(int nv, int sf_mode, int ksteps, int 
                 break;
             }
             tc::fence_after_sync();
-            const uint32_t tsfa = tmem + quad_lane + 256 + 48 * b, tsfb = tsfa + 16;
-            for (int j = 0; j < atoms; j++) {
-                uint4 v;
-                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(sfa + 16u * lane + 512u * j));
-                tc::tmem_st4(tsfa + 4 * j, v.x, v.y, v.z, v.w);
+            const uint32_t tsfa = tmem + quad_lane + 256 + 48 * b;
+            uint32_t w[48];
 #pragma unroll
-                for (int h = 0; h < 2; h++) {
-                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(sfb + 16u * lane + 2048u * h + 512u * j));
-                    tc::tmem_st4(tsfb + 8 * j + 4 * h, v.x, v.y, v.z, v.w);
-                }
+            for (int j = 0; j < 4; j++) {
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(w[4 * j]), "=r"(w[4 * j + 1]), "=r"(w[4 * j + 2]), "=r"(w[4 * j + 3]) : "r"(sfa + 16u * lane + 512u * j));
+#pragma unroll
+                for (int h = 0; h < 2; h++)
+                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                                 : "=r"(w[16 + 8 * j + 4 * h]), "=r"(w[17 + 8 * j + 4 * h]), "=r"(w[18 + 8 * j + 4 * h]), "=r"(w[19 + 8 * j + 4 * h])
+                                 : "r"(sfb + 16u * lane + 2048u * h + 512u * j));
             }
+            tc::tmem_st32(tsfa, w);
+            tc::tmem_st16(tsfa + 32, w + 32);
             tc::tmem_st_wait();
             tc::fence_before_sync();
             __syncwarp();
             if (lane == 0) {
-                if (PAIR) tc::mbar_arrive_cluster(sf_full_leader + 8 * b);
+                if (PAIR) tc::mbar_arrive_cluster_relaxed(sf_full_leader + 8 * b);
                 else tc::mbar_arrive(sf_full + 8 * b);
             }
         }
@@ -955,9 +1076,9 @@ int32_t gemm_fp4_launch(Ctx *c, const Weight *w, const Weight *x, void *y, int y
     p.vec = (((uintptr_t)y & 15) == 0 && (ldy * (y_bf16 ? 2 : 4)) % 16 == 0) ? 1 : 0;
     p.status = c->status_dev;
     if (m > 128 && c->gemm_fp4_pair) {
-        // 1: one 256-token accumulator; 2 (default): two 192-token accumulators; 3: two 128-token accumulators
-        const int variant = (int)c->gemm_fp4_pair;
-        const int tile_tok = variant == 1 ? 256 : (variant == 3 ? 128 : 192);
+        // 1 (default): one 256-token accumulator; 2: two 192-token accumulators; 3: two 128-token accumulators
+        const int variant = (c->gemm_fp4_pair == 2 || c->gemm_fp4_pair == 3) ? (int)c->gemm_fp4_pair : 1;
+        const int tile_tok = variant == 3 ? 128 : (variant == 2 ? 192 : 256);
         const size_t smem_bytes = variant == 1 ? P4_SMEM : (variant == 3 ? P2<128>::SMEM : P2<192>::SMEM);
         const int threads = variant == 1 ? P4_THREADS : P2<192>::THREADS;
         const void *fn = variant == 1 ? (const void *)gemm_fp4_pair_kernel
@@ -1000,3 +1121,12 @@ int32_t gemm_fp4_launch(Ctx *c, const Weight *w, const Weight *x, void *y, int y
 }
 
 }  // namespace gllmk
+
+#ifdef GLLMK_FP4_PROF
+extern "C" __attribute__((visibility("default"))) int gllmk_debug_fp4_prof(unsigned long long *out) {
+    return (int)cudaMemcpyFromSymbol(out, gllmk::g_fp4_prof, sizeof(gllmk::g_fp4_prof));
+}
+extern "C" __attribute__((visibility("default"))) int gllmk_debug_fp4_timeline(unsigned long long *out) {
+    return (int)cudaMemcpyFromSymbol(out, gllmk::g_fp4_tl, sizeof(gllmk::g_fp4_tl));
+}
+#endif
