@@ -286,16 +286,12 @@ def run_ours(args):
         def local_step():
             for i, (name, w, n, k, r0, r1) in enumerate(weights):
                 K.gemv(w, x_ff if name == "down" else x_model, y=ys[i][:, r0:r1])
-        if args.gemv_fuse < 0:
-            K.set("gemv_fuse", 2)  # the same kernels as the exchange products (they stage their own activations)
         for _ in range(3):
             local_step()
         torch.cuda.synchronize()
         g2 = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g2):
             local_step()
-        if args.gemv_fuse < 0:
-            K.set("gemv_fuse", 1)
         for _ in range(3):
             g2.replay()
         torch.cuda.synchronize()

@@ -96,8 +96,9 @@ struct Ctx {
     int64_t gemv_fp4_int = 0;  // 1: FP4 decode on the integer-decode GEMV kernel instead of the tensor-core one
     int64_t gemv_ctas_per_sm = 0;  // 0 = what the occupancy calculator allows
     int64_t gemm_tail_split = 0;  // prefill GEMM: 0 = cut the last partial wave of tiles along k when that pays, 1 = never, n = into n
-    int64_t gemv_fuse = 1;      // decode GEMV, small shares convert their activation slices inside the GEMV (no staging launch):
-                                // 0 never, 1 exchange products only, 2 every product
+    int64_t gemv_fuse = 0;      // decode GEMV, small shares convert their activation slices inside the GEMV (no staging launch):
+                                // 0 never (default: the staging launch overlaps the weight stream and measured faster on one
+                                // and two GPUs), 1 exchange products only, 2 every product
     int64_t gemm_fp4_pair = 1;  // FP4 x FP4 GEMM with m > 128 on CTA pairs (cta_group::2, persistent): 0 off, 1 one 256-token
                                 // accumulator (fastest measured), 2 two 192-token accumulators, 3 two 128-token accumulators
     int64_t peer_wait_spins = (int64_t)1 << 22;  // probes of another rank's flag before a wait gives up (status 31 / 32)

@@ -155,7 +155,7 @@ GLLMK_API int32_t gllmk_ctx_status(gllmk_ctx ctx, int32_t *device_status);
  * sized for; 0 = occupancy limit), "gemv_pdl" (1 = overlap the activation staging kernel with the
  * weight stream), "gemv_fp4_int" (1 = decode MXFP4 / NVFP4 weights on the integer-decode kernel instead of
  * the block-scaled tensor-core one), "gemv_fuse" (decode GEMV converting its own activation slices instead of a staging launch when a
- * block's share is small: 0 never, 1 products of an exchange chain only, 2 every product), "gemm_fp4_pair" (FP4 x FP4 GEMM with
+ * block's share is small: 0 never (default), 1 products of an exchange chain only, 2 every product), "gemm_fp4_pair" (FP4 x FP4 GEMM with
  * m > 128: 0 the one-CTA kernel, 1 (default) CTA pairs with one 256-token accumulator, 2 CTA pairs with two 192-token
  * accumulators, 3 CTA pairs with two 128-token accumulators), "gemm_tail_split" (prefill GEMM, last partial wave of tiles cut along k:
  * 0 automatic, 1 never, n into n), "peer_wait_spins" (how many times a wait on another GPU's flag probes it

@@ -85,6 +85,11 @@ def _worker(rank, world, port, q):
             xs.copy_(torch.from_numpy(np.random.default_rng(200 + rep).standard_normal((m, k1)).astype(np.float32)))
             chain()
             check(f"eager {rep}")
+        for fuse in (1, 0):  # the exchange products staging their own activations inside the GEMV, then the default again
+            K.set("gemv_fuse", fuse)
+            xs.copy_(torch.from_numpy(np.random.default_rng(250 + fuse).standard_normal((m, k1)).astype(np.float32)))
+            chain()
+            check(f"gemv_fuse {fuse}")
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):

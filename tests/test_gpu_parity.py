@@ -432,11 +432,11 @@ def test_gemv_fused_staging_equals_the_staging_kernel(gk, K, oracle, torch, fmt,
     K.set("gemv_fuse", 0)
     try:
         y_img = K.gemv(w, x).clone()
-        K.set("gemv_fuse", 2)  # every product (the default fuses only the products of a multi-GPU exchange chain)
+        K.set("gemv_fuse", 2)  # every product (off by default)
         y_fused = K.gemv(w, x).clone()
         y_ref_layout = K.gemv(w, x.t().contiguous(), ref_layout=True)
     finally:
-        K.set("gemv_fuse", 1)
+        K.set("gemv_fuse", 0)
     assert K.status() == 0
     assert torch.equal(y_img, y_fused)
     ref = oracle.quant_matmul(blocks, np.ascontiguousarray(x.cpu().numpy().T), oid, n, m, k, threads=8).T
