@@ -138,7 +138,7 @@ def sampled_parity(O, oid, blocks, n, k, rows, x_host, y, bar, scales=None, glob
     got = y[:, torch.from_numpy(np.asarray(rows)).to(y.device)].to(torch.float32).cpu().numpy()
     err = O.rel_err(got, ref)
     return {"metric": PARITY_METRIC, "rows_sampled": int(len(rows)), "tokens": int(m), "rel_err": err, "bar": bar,
-            "ok": bool(err <= bar),
+            "ok": bool(err <= bar), "non_finite": {"y": int((~np.isfinite(got)).sum()), "oracle": int((~np.isfinite(ref)).sum())},
             "oracle": "reference quantized matmul (sequential f32)" if sequential else "reference decode + f32 GEMM loop order"}
 
 
@@ -488,10 +488,11 @@ def sharded_prefill_extra(K, gk, torch, dist, dev, world, rank):
         x = torch.randn((m, k), generator=gen, device=dev)
         dt = torch.float32 if m <= K.GEMM_GEMV_MAX_M else torch.bfloat16
         buf = torch.empty((world, m, band), dtype=dt, device=dev)
+        mine = torch.empty((m, band), dtype=dt, device=dev)
 
         def step():
-            K.gemm(w, x, y=buf[rank])
-            dist.all_gather_into_tensor(buf.view(-1), buf[rank].view(-1))
+            K.gemm(w, x, y=mine)
+            dist.all_gather_into_tensor(buf.view(-1), mine.view(-1))
         for _ in range(3):
             step()
         torch.cuda.synchronize()
@@ -515,6 +516,7 @@ def sharded_prefill_extra(K, gk, torch, dist, dev, world, rank):
             tc = m > K.GEMM_GEMV_MAX_M
             entry["parity"] = sampled_parity(O, O.Q4K, sub_blocks, len(rows), k, np.arange(len(rows)), x.cpu().numpy(),
                                              y[:, torch.from_numpy(rows).to(dev)], bar=1e-2 if tc else 2e-3, sequential=not tc)
+            entry["parity"]["non_finite"]["y_per_band"] = [int((~torch.isfinite(buf[r].float())).sum().item()) for r in range(world)]
         res[f"sharded_q4k_{n}x{k}_M{m}"] = entry
     w.free()
     return res
