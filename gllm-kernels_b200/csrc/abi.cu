@@ -136,8 +136,11 @@ static int32_t weight_fill(Ctx *c, Weight *w, const void *blocks, const void *sc
         if (e != cudaSuccess) { cudaFree(stage); return cuda_fail(c, e, "cudaMemcpyAsync(weight blocks)"); }
         bdev = stage;
         sdev = sraw ? static_cast<char *>(stage) + off : nullptr;
-    } else if (((uintptr_t)blocks & 15) != 0) {
-        return fail(c, GLLMK_STATUS_INVALID_ARG, "device block pointer must be 16-byte aligned");
+    } else {
+        if (((uintptr_t)blocks & 15) != 0) return fail(c, GLLMK_STATUS_INVALID_ARG, "device block pointer must be 16-byte aligned");
+        // The caller's kernels that produce the blocks run on streams this library does not know: the repack (on the
+        // context's own non-blocking stream) must not start before they have finished.  Load-time call: wait for the device.
+        GK_CUDA(c, cudaDeviceSynchronize());
     }
     int32_t rc = repack_upload(c, w, bdev, sdev, c->stream);
     cudaError_t e = cudaStreamSynchronize(c->stream);
@@ -548,6 +551,8 @@ static int32_t int8_weight_create(Ctx *c, int64_t n, int64_t k, const int8_t *b,
             return cuda_fail(c, e, "upload(int8 weight)");
         }
         bdev = static_cast<const int8_t *>(stage);
+    } else {
+        (void)cudaDeviceSynchronize();  // the kernels that produced b ran on the caller's streams (see weight_fill)
     }
     int32_t rc = i8_weight_fill(c, w, bdev, layout, c->stream);
     e = cudaStreamSynchronize(c->stream);

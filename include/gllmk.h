@@ -175,7 +175,8 @@ GLLMK_API int32_t gllmk_ctx_set(gllmk_ctx ctx, const char *key, int64_t value);
  *          bytes and `scales` n*k/mx_block E8M0 bytes; or, with scales == NULL, the GGUF inline
  *          form (17-byte blocks, scale first; src/quant.rs:427).  mx_block must be 32.
  *   `global_scale` is NVFP4's out-of-band per-tensor f32 (src/quant.rs:77-86); pass 1 otherwise.
- *   `src_on_device` != 0 means `blocks`/`scales` are device pointers (16-byte aligned).
+ *   `src_on_device` != 0 means `blocks`/`scales` are device pointers (16-byte aligned); the call then waits
+ *   for all work already queued on the device (whatever stream produced the blocks) before it repacks.
  * Errors: INVALID_ARG (null, n<=0, k not a multiple of the block size, or of 128 for MXFP4),
  * UNSUPPORTED (unknown type, mx_block != 32), OUT_OF_MEMORY, RUNTIME_ERROR. */
 GLLMK_API int32_t gllmk_weight_upload(gllmk_ctx ctx, int32_t quant_type, int64_t n, int64_t k, int32_t mx_block,
