@@ -844,7 +844,7 @@ def extra_gemm(K, gk, torch, dev, gen):
     res["cfg4_nvfp4_14336x4096_M2048"] = {"us": us, "tflops": 2.0 * m * n * k / us / 1e6, "frac_of_nominal_fp4_9000": 2.0 * m * n * k / us / 1e6 / 9000.0,
                                           "measured_mma_ceiling_tflops": ceil_tf, "frac_of_measured_mma_ceiling": 2.0 * m * n * k / us / 1e6 / ceil_tf,
                                           "mma": "tcgen05 kind::mxf4nvf4 block_scale, cta_group::2",
-                                          "parity": sampled_parity(O, O.NVFP4, packed[0], n, k, rows, a_host, y, bar=2e-3 + 2.0 ** -9,
+                                          "parity": sampled_parity(O, O.NVFP4, packed[0], n, k, rows, a_host, y, bar=2e-3 + 2.0 ** -8,
                                                                    global_scale=packed[2]),
                                           "cpu_baseline": cpu_baseline_rows(O, O.NVFP4, packed, n, k, rows[:32], a_host, w.ref_bytes)}
     w.free()

@@ -53,7 +53,8 @@ def test_q4k_70b_ffn_matrices_at_every_batch(gk, K, oracle, n, k, m):
 
 def test_nvfp4_prefill_14336x4096_m2048(gk, K, oracle):
     """W[14336, 4096] NVFP4 x A[2048, 4096] NVFP4 (quantized the same way from N(0, 1)), bf16 out, block-scaled MMA.
-    Codes and scales are consumed exactly: the f32 bar applies, plus the bf16 rounding of the output (2^-9)."""
+    Codes and scales are consumed exactly: the f32 bar applies, plus the bf16 rounding of the output (half an ulp of an
+    8-bit significand: up to 2^-8 of the value)."""
     import torch
     n, k, m = 14336, 4096, 2048
     qt = gk.QuantType.nvfp4()
@@ -62,7 +63,7 @@ def test_nvfp4_prefill_14336x4096_m2048(gk, K, oracle):
     xb, gx = K.quantize(qt, X)
     x = K.upload(qt, m, k, xb, None, gx)
     a_host = oracle.dequant_matrix(oracle.NVFP4, xb.cpu().numpy(), m, k, global_scale=gx)
-    for dtype, bar in ((torch.float32, 2e-3), (torch.bfloat16, 2e-3 + 2.0 ** -9)):
+    for dtype, bar in ((torch.float32, 2e-3), (torch.bfloat16, 2e-3 + 2.0 ** -8)):
         y = K.gemm_fp4(w, x, out_dtype=dtype)
         torch.cuda.synchronize()
         assert K.status() == 0
