@@ -7,9 +7,9 @@ CPU fallback and importing the compute classes fails loudly if the library is mi
 """
 from .quant import QuantType, QuantFormatDescriptor, registry, E2M1_LUT_F32, decode_e8m0_scale  # noqa: F401
 from ._lib import GllmkError, Status, lib, lib_path, build_library  # noqa: F401
-from .kernels import GpuKernels, Weight  # noqa: F401
+from .kernels import GpuKernels, HostBatch, Weight  # noqa: F401
 from .shard import PeerExchange, ShardedLinear, gpu_sharded_linear, shard_rows, slice_blocks  # noqa: F401
 from .gguf import GgufFile, GgufError, TensorInfo, write_gguf  # noqa: F401
 
 __all__ = ["GgufFile", "GgufError", "TensorInfo", "write_gguf", "QuantType", "QuantFormatDescriptor", "registry", "E2M1_LUT_F32", "decode_e8m0_scale", "GllmkError", "Status", "lib", "lib_path",
-           "build_library", "GpuKernels", "Weight", "PeerExchange", "ShardedLinear", "gpu_sharded_linear", "shard_rows", "slice_blocks"]
+           "build_library", "GpuKernels", "HostBatch", "Weight", "PeerExchange", "ShardedLinear", "gpu_sharded_linear", "shard_rows", "slice_blocks"]

@@ -236,6 +236,9 @@ void gllmk_ctx_free(gllmk_ctx ctx) {
     if (c->status_dev) cudaFree(c->status_dev);
     if (c->dev_io) cudaFree(c->dev_io);
     if (c->pin) cudaFreeHost(c->pin);
+    if (c->batch_exec) cudaGraphExecDestroy(c->batch_exec);
+    for (cudaEvent_t e : c->events) cudaEventDestroy(e);
+    if (c->copy_stream) cudaStreamDestroy(c->copy_stream);
     if (c->stream) cudaStreamDestroy(c->stream);
     delete c;
 }
@@ -272,6 +275,7 @@ int32_t gllmk_ctx_set(gllmk_ctx ctx, const char *key, int64_t value) {
     else if (!strcmp(key, "gemm_fp4_pair")) c->gemm_fp4_pair = value;
     else if (!strcmp(key, "gemv_fuse")) c->gemv_fuse = value;
     else if (!strcmp(key, "gemm_tail_split")) c->gemm_tail_split = value;
+    else if (!strcmp(key, "host_batch_graph")) c->host_batch_graph = value;
     else if (!strcmp(key, "peer_wait_spins")) {
         if (value < 1 || value > ((int64_t)1 << 30)) return fail(c, GLLMK_STATUS_INVALID_ARG, "peer_wait_spins outside 1..2^30");
         c->peer_wait_spins = value;
@@ -748,49 +752,48 @@ static int32_t matmul_host_impl(Ctx *c, const Weight *w, const float *x_host, in
     return GLLMK_STATUS_OK;
 }
 
-// Several products with host activations / outputs, enqueued back to back on the context's stream and awaited ONCE:
-// what a decode step is (a handful of products whose host-side inputs are all known when the step starts).
-static int32_t matmul_host_batch_impl(Ctx *c, int count, const gllmk_weight *ws, const float *const *xs, const int32_t *ms,
-                                      float *const *ys, bool ref_layout) {
-    const auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
-    size_t total = 256;
-    for (int i = 0; i < count; i++) {
-        const Weight *w = static_cast<const Weight *>(ws[i]);
-        total += up((size_t)ms[i] * w->k * sizeof(float)) + up((size_t)ms[i] * w->n * sizeof(float));
+// Several products with host activations / outputs, enqueued back to back and awaited ONCE: what a decode step is (a
+// handful of products whose host-side inputs are all known when the step starts).  The products run on the context's
+// stream; every x goes up and every y comes back on a second stream, so the copies of product i + 1 and i - 1 run beside
+// product i.  An argument list seen twice in a row is captured as a CUDA graph (same pointers, same shapes, same scratch
+// buffers) and replayed from then on: one launch instead of ~3 per product.
+struct BatchItem {
+    const Weight *w;
+    int m;
+    size_t xo, yo, xb, yb;
+    const char *x_src;  // page-locked source of the upload (the caller's buffer or the staging area)
+    void *y_dst;        // page-locked destination of the download
+    bool x_staged, y_staged;
+};
+
+static int32_t batch_enqueue(Ctx *c, const std::vector<BatchItem> &items, bool ref_layout) {
+    char *dev = static_cast<char *>(c->dev_io);
+    const size_t count = items.size();
+    while (c->events.size() < 2 * count + 2) {
+        cudaEvent_t e;
+        GK_CUDA(c, cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        c->events.push_back(e);
     }
-    int32_t rc = ensure_pin(c, total);
-    if (!rc) rc = ensure_dev_io(c, total);
-    if (rc) return rc;
-    char *pin = static_cast<char *>(c->pin), *dev = static_cast<char *>(c->dev_io);
-    const auto pinned_alias = [](const void *h) -> const void * {
-        cudaPointerAttributes at;
-        if (cudaPointerGetAttributes(&at, h) != cudaSuccess) {
-            (void)cudaGetLastError();
-            return nullptr;
-        }
-        return at.type == cudaMemoryTypeHost ? at.devicePointer : nullptr;
-    };
-    std::vector<size_t> y_off((size_t)count, 0);
-    std::vector<char> y_staged((size_t)count, 0);
-    size_t off = 0;
-    for (int i = 0; i < count; i++) {
-        const Weight *w = static_cast<const Weight *>(ws[i]);
-        const int m_t = ms[i];
+    cudaEvent_t *ev_x = c->events.data() + 2, *ev_y = ev_x + count;
+    GK_CUDA(c, cudaEventRecord(c->events[0], c->stream));
+    GK_CUDA(c, cudaStreamWaitEvent(c->copy_stream, c->events[0], 0));
+    for (size_t i = 0; i < count; i++) {
+        GK_CUDA(c, cudaMemcpyAsync(dev + items[i].xo, items[i].x_src, items[i].xb, cudaMemcpyHostToDevice, c->copy_stream));
+        GK_CUDA(c, cudaEventRecord(ev_x[i], c->copy_stream));
+    }
+    for (size_t i = 0; i < count; i++) {
+        const BatchItem &it = items[i];
+        const Weight *w = it.w;
+        const int m_t = it.m;
         const int64_t n_w = w->n, k = w->k;
-        const size_t xb = (size_t)m_t * k * sizeof(float), yb = (size_t)m_t * n_w * sizeof(float);
-        const size_t xo = off, yo = off + up(xb);
-        off = yo + up(yb);
-        const void *x_alias = pinned_alias(xs[i]);
-        const char *x_src = reinterpret_cast<const char *>(xs[i]);
-        if (!x_alias) {
-            memcpy(pin + xo, xs[i], xb);
-            x_src = pin + xo;
-            x_alias = pin + xo;
-        }
-        const bool zero_copy_x = xb <= (size_t)256 * 1024;
-        if (!zero_copy_x) GK_CUDA(c, cudaMemcpyAsync(dev + xo, x_src, xb, cudaMemcpyHostToDevice, c->stream));
-        const float *xd = reinterpret_cast<const float *>(zero_copy_x ? static_cast<const char *>(x_alias) : dev + xo);
-        float *yd = reinterpret_cast<float *>(dev + yo);
+        const float *xd = reinterpret_cast<const float *>(dev + it.xo);
+        float *yd = reinterpret_cast<float *>(dev + it.yo);
+        // The upload of product i + 1 is awaited BEFORE product i is enqueued (all uploads were issued up front and take
+        // a few us each): the staging kernel of product i + 1 then depends on nothing but the GEMV in front of it, which
+        // keeps the programmatic (early) launch between the two.
+        if (i == 0) GK_CUDA(c, cudaStreamWaitEvent(c->stream, ev_x[0], 0));
+        if (i + 1 < count) GK_CUDA(c, cudaStreamWaitEvent(c->stream, ev_x[i + 1], 0));
+        int32_t rc = 0;
         if (!ref_layout && m_t > GLLMK_GEMM_GEMV_MAX_M && !raw_format(w->qt)) {
             rc = gemm_launch(c, w, xd, 0, k, m_t, yd, 0, n_w, c->stream);
             if (rc) return rc;
@@ -802,18 +805,119 @@ static int32_t matmul_host_batch_impl(Ctx *c, int count, const gllmk_weight *ws,
                 if (rc) return rc;
             }
         }
-        const bool y_pinned = pinned_alias(ys[i]) != nullptr;
-        y_off[(size_t)i] = yo;
-        y_staged[(size_t)i] = y_pinned ? 0 : 1;
-        GK_CUDA(c, cudaMemcpyAsync(y_pinned ? static_cast<void *>(ys[i]) : static_cast<void *>(pin + yo), dev + yo, yb, cudaMemcpyDeviceToHost,
-                                   c->stream));
+        GK_CUDA(c, cudaEventRecord(ev_y[i], c->stream));
+        GK_CUDA(c, cudaStreamWaitEvent(c->copy_stream, ev_y[i], 0));
+        GK_CUDA(c, cudaMemcpyAsync(it.y_dst, dev + it.yo, it.yb, cudaMemcpyDeviceToHost, c->copy_stream));
     }
-    GK_CUDA(c, cudaStreamSynchronize(c->stream));
-    for (int i = 0; i < count; i++)
-        if (y_staged[(size_t)i]) {
-            const Weight *w = static_cast<const Weight *>(ws[i]);
-            memcpy(ys[i], pin + y_off[(size_t)i], (size_t)ms[i] * w->n * sizeof(float));
+    GK_CUDA(c, cudaEventRecord(c->events[1], c->copy_stream));
+    GK_CUDA(c, cudaStreamWaitEvent(c->stream, c->events[1], 0));
+    return GLLMK_STATUS_OK;
+}
+
+static int32_t matmul_host_batch_impl(Ctx *c, int count, const gllmk_weight *ws, const float *const *xs, const int32_t *ms,
+                                      float *const *ys, bool ref_layout) {
+    const auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
+    size_t total = 256;
+    for (int i = 0; i < count; i++) {
+        const Weight *w = static_cast<const Weight *>(ws[i]);
+        total += up((size_t)ms[i] * w->k * sizeof(float)) + up((size_t)ms[i] * w->n * sizeof(float));
+    }
+    int32_t rc = ensure_pin(c, total);
+    if (!rc) rc = ensure_dev_io(c, total);
+    if (rc) return rc;
+    if (!c->copy_stream) GK_CUDA(c, cudaStreamCreateWithFlags(&c->copy_stream, cudaStreamNonBlocking));
+    char *pin = static_cast<char *>(c->pin);
+    const auto page_locked = [](const void *h) {
+        cudaPointerAttributes at;
+        if (cudaPointerGetAttributes(&at, h) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return false;
         }
+        return at.type == cudaMemoryTypeHost;
+    };
+    // what a captured graph depends on: the argument list and every scratch buffer a launch may take its pointers from
+    const auto make_key = [&]() {
+        std::vector<uint64_t> key;
+        key.reserve(8 + 6 * (size_t)count);
+        for (const void *q : {static_cast<const void *>(c->pin), static_cast<const void *>(c->dev_io), static_cast<const void *>(c->ws),
+                              static_cast<const void *>(c->red), static_cast<const void *>(c->cnt), static_cast<const void *>(c->act)})
+            key.push_back((uint64_t)(uintptr_t)q);
+        key.push_back((uint64_t)count);
+        key.push_back(ref_layout ? 1u : 0u);
+        for (int i = 0; i < count; i++) {
+            const Weight *w = static_cast<const Weight *>(ws[i]);
+            key.push_back((uint64_t)(uintptr_t)ws[i]);
+            key.push_back((uint64_t)(uintptr_t)w->qs);
+            key.push_back(((uint64_t)w->n << 32) ^ (uint64_t)w->k ^ ((uint64_t)w->qt << 60));
+            key.push_back((uint64_t)(uintptr_t)xs[i]);
+            key.push_back((uint64_t)(uintptr_t)ys[i]);
+            key.push_back((uint64_t)(uint32_t)ms[i]);
+        }
+        return key;
+    };
+    const bool replay = c->host_batch_graph && c->batch_exec && make_key() == c->batch_key;
+    std::vector<BatchItem> items((size_t)count);
+    size_t off = 0;
+    for (int i = 0; i < count; i++) {
+        BatchItem &it = items[(size_t)i];
+        it.w = static_cast<const Weight *>(ws[i]);
+        it.m = ms[i];
+        it.xb = (size_t)it.m * it.w->k * sizeof(float);
+        it.yb = (size_t)it.m * it.w->n * sizeof(float);
+        it.xo = off;
+        it.yo = off + up(it.xb);
+        off = it.yo + up(it.yb);
+        // which host buffers are page-locked was found out when the list was captured (same pointers since)
+        it.x_staged = replay ? (c->batch_staged[(size_t)i] & 1) != 0 : !page_locked(xs[i]);
+        it.y_staged = replay ? (c->batch_staged[(size_t)i] & 2) != 0 : !page_locked(ys[i]);
+        it.x_src = it.x_staged ? pin + it.xo : reinterpret_cast<const char *>(xs[i]);
+        it.y_dst = it.y_staged ? static_cast<void *>(pin + it.yo) : static_cast<void *>(ys[i]);
+        if (it.x_staged) memcpy(pin + it.xo, xs[i], it.xb);
+    }
+    const auto finish = [&]() -> int32_t {
+        GK_CUDA(c, cudaStreamSynchronize(c->stream));
+        for (int i = 0; i < count; i++)
+            if (items[(size_t)i].y_staged) memcpy(ys[i], pin + items[(size_t)i].yo, items[(size_t)i].yb);
+        return GLLMK_STATUS_OK;
+    };
+    if (replay) {
+        GK_CUDA(c, cudaGraphLaunch(c->batch_exec, c->stream));
+        return finish();
+    }
+    rc = batch_enqueue(c, items, ref_layout);
+    if (rc) return rc;
+    rc = finish();
+    if (rc || !c->host_batch_graph) return rc;
+    // The scratch buffers have their final sizes now.  Second sighting of this list in a row: capture it for next time.
+    std::vector<uint64_t> key = make_key();
+    if (key != c->batch_candidate) {
+        c->batch_candidate.swap(key);
+        return GLLMK_STATUS_OK;
+    }
+    if (c->batch_exec) {
+        cudaGraphExecDestroy(c->batch_exec);
+        c->batch_exec = nullptr;
+        c->batch_key.clear();
+    }
+    if (cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeRelaxed) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return GLLMK_STATUS_OK;  // no graph: the next call enqueues again
+    }
+    const int32_t crc = batch_enqueue(c, items, ref_layout);
+    cudaGraph_t graph = nullptr;
+    const cudaError_t ce = cudaStreamEndCapture(c->stream, &graph);
+    if (crc == GLLMK_STATUS_OK && ce == cudaSuccess && graph && make_key() == key &&
+        cudaGraphInstantiate(&c->batch_exec, graph, 0) == cudaSuccess) {
+        c->batch_key.swap(key);
+        c->batch_staged.assign((size_t)count, 0);
+        for (int i = 0; i < count; i++)
+            c->batch_staged[(size_t)i] = (uint8_t)((items[(size_t)i].x_staged ? 1 : 0) | (items[(size_t)i].y_staged ? 2 : 0));
+    } else {
+        (void)cudaGetLastError();
+        c->batch_exec = nullptr;
+        c->err.clear();
+    }
+    if (graph) cudaGraphDestroy(graph);
     return GLLMK_STATUS_OK;
 }
 

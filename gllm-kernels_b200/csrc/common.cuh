@@ -9,6 +9,7 @@
 #include <cstdio>
 #include <cstring>
 #include <string>
+#include <vector>
 
 #include "../../include/gllmk.h"
 #include "quant_format.cuh"
@@ -92,6 +93,14 @@ struct Ctx {
     void *dev_io = nullptr;
     size_t dev_io_bytes = 0;
     cudaStream_t stream = nullptr;  // the context's own stream for host-pointer entry points
+    // gllmk_matmul_host_batch: a second stream for the host <-> device copies (they run beside the products), events
+    // for the hand-overs, and the instantiated graph of the last argument list that was seen twice
+    cudaStream_t copy_stream = nullptr;
+    std::vector<cudaEvent_t> events;
+    std::vector<uint64_t> batch_key, batch_candidate;
+    std::vector<uint8_t> batch_staged;  // of the captured list: per product, bit 0 = x goes through the staging area, bit 1 = y
+    cudaGraphExec_t batch_exec = nullptr;
+    int64_t host_batch_graph = 1;  // 0: never replay a graph in gllmk_matmul_host_batch
     int64_t gemv_pdl = 1;
     int64_t gemv_fp4_int = 0;  // 1: FP4 decode on the integer-decode GEMV kernel instead of the tensor-core one
     int64_t gemv_ctas_per_sm = 0;  // 0 = what the occupancy calculator allows

@@ -442,6 +442,11 @@ class GpuKernels:
         self._check(lib().gllmk_matmul_host_batch(self._ctx, n, wh, xp, ms, yp, int(ref_layout)), "gllmk_matmul_host_batch")
         return outs
 
+    def host_batch(self, weights, xs, outs, ref_layout: bool = False) -> "HostBatch":
+        """The argument arrays of `matmul_host_batch` built once, for a step that is run many times on the same host
+        buffers (a decode loop): `HostBatch.run()` is then one C call with nothing to convert."""
+        return HostBatch(self, weights, xs, outs, ref_layout)
+
     def quantize(self, quant_type: QuantType, x, global_scale: float = 0.0, stream=None):
         """f32 [rows, k] CUDA tensor -> reference-format blocks (CUDA uint8 tensors).
         Returns blocks for Q4K/Q8_0, (blocks, scales) for MXFP4, (blocks, global_scale) for NVFP4."""
@@ -553,3 +558,25 @@ class GpuKernels:
         w, x = np.ascontiguousarray(weight).view(np.uint8), _np(input, np.float32)
         self._check(lib().gllmk_gemv_q8_f32(self._ctx, _ptr(w), _ptr(x), float(scale), n, _ptr(out)), "gemv_q8")
         return float(out[0])
+
+
+class HostBatch:
+    """Prebuilt argument arrays of one `gllmk_matmul_host_batch` step (see GpuKernels.host_batch).  Keeps the weights and
+    the host arrays alive; the arrays' contents may change between runs, their addresses may not."""
+
+    def __init__(self, K: "GpuKernels", weights, xs, outs, ref_layout: bool = False):
+        self.K, self.weights, self.ref_layout = K, list(weights), bool(ref_layout)
+        self.xs = [_np(x, np.float32) for x in xs]
+        self.outs = [_np(y, np.float32, True) for y in outs]
+        n = self.n = len(self.weights)
+        self._ms = (C.c_int32 * n)(*[(x.shape[1] if ref_layout else x.shape[0]) for x in self.xs])
+        self._wh = (C.c_void_p * n)(*[w._h for w in self.weights])
+        self._xp = (C.c_void_p * n)(*[_ptr(x) for x in self.xs])
+        self._yp = (C.c_void_p * n)(*[_ptr(y) for y in self.outs])
+        self._fn = lib().gllmk_matmul_host_batch
+
+    def run(self):
+        rc = self._fn(self.K._ctx, self.n, self._wh, self._xp, self._ms, self._yp, int(self.ref_layout))
+        if rc:
+            self.K._check(rc, "gllmk_matmul_host_batch")
+        return self.outs

@@ -157,7 +157,8 @@ GLLMK_API int32_t gllmk_ctx_status(gllmk_ctx ctx, int32_t *device_status);
  * the block-scaled tensor-core one), "gemv_fuse" (decode GEMV converting its own activation slices instead of a staging launch when a
  * block's share is small: 0 never (default), 1 products of an exchange chain only, 2 every product), "gemm_fp4_pair" (FP4 x FP4 GEMM with
  * m > 128: 0 the one-CTA kernel, 1 (default) CTA pairs with one 256-token accumulator, 2 CTA pairs with two 192-token
- * accumulators, 3 CTA pairs with two 128-token accumulators), "gemm_tail_split" (prefill GEMM, last partial wave of tiles cut along k:
+ * accumulators, 3 CTA pairs with two 128-token accumulators), "host_batch_graph" (gllmk_matmul_host_batch replays a captured graph for a repeated
+ * argument list: 1 default, 0 never), "gemm_tail_split" (prefill GEMM, last partial wave of tiles cut along k:
  * 0 automatic, 1 never, n into n), "peer_wait_spins" (how many times a wait on another GPU's flag probes it
  * before it gives up with status 31; default 2^22, about a second), "inject_give_up" (testing aid, host side
  * only: leaves the context as a kernel that gave up a wait with that status code would — word set, arrival
@@ -449,9 +450,12 @@ GLLMK_API int32_t gllmk_gemv_q8_f32(gllmk_ctx ctx, const int8_t *weight, const f
 GLLMK_API int32_t gllmk_matmul_host(gllmk_ctx ctx, gllmk_weight w, const float *x_host, int32_t m, float *y_host,
                           int32_t ref_layout);
 /* The products of one decode step in ONE call: product i is gllmk_matmul_host(weights[i], x_host[i], m[i], y_host[i]).  All
- * of them are enqueued back to back on the context's stream (activations read from / results copied to the host
- * buffers, page-locked ones in place) and the call waits once, at the end, instead of once per product.  Outputs must
- * not alias inputs of the same call.  No counterpart in the reference (its products are synchronous CPU calls). */
+ * of them are enqueued back to back on the context's stream, every activation is uploaded and every result downloaded on
+ * a second stream beside the products (page-locked host buffers in place, pageable ones through the context's
+ * page-locked staging area), and the call waits once, at the end.  An argument list (handles, host pointers, m) that is
+ * passed twice in a row is captured as a CUDA graph and replayed on later calls with the same list: one launch per step
+ * (gllmk_ctx_set "host_batch_graph" = 0 switches the replay off).  Outputs must not alias inputs of the same call.
+ * No counterpart in the reference (its products are synchronous CPU calls). */
 GLLMK_API int32_t gllmk_matmul_host_batch(gllmk_ctx ctx, int32_t count, const gllmk_weight *weights, const float *const *x_host,
                                           const int32_t *m, float *const *y_host, int32_t ref_layout);
 /* Kernels::dequant_q4_k(block, out) / dequant_q8_0 (src/traits.rs:476,488): `nblocks` consecutive

@@ -469,6 +469,53 @@ def test_matmul_host_batch_equals_one_call_per_product(gk, K, oracle, torch):
     for got, ref in zip(yp, want):
         assert np.array_equal(got.numpy(), ref)
     assert K.status() == 0
+    # The same argument list again and again: from the third call on the step is replayed as a captured graph.  New
+    # activations in the same buffers every time, page-locked and pageable buffers; then a different list (fresh
+    # enqueue), the first list again, and the graph switched off.
+    xn, yn = [t.numpy() for t in xp], [t.numpy() for t in yp]
+    for rep in range(5):
+        fresh = [rng.standard_normal(x.shape).astype(np.float32) for x in xs]
+        ref = [K.matmul_host(w, x) for w, x in zip(ws, fresh)]
+        for dst, x in zip(xn, fresh):
+            dst[...] = x
+        for y in yn:
+            y[...] = np.nan
+        K.matmul_host_batch(ws, xn, yn)
+        for got, want_i in zip(yn, ref):
+            assert np.array_equal(got, want_i), rep
+    pageable_x = [x.copy() for x in xs]
+    for rep in range(4):
+        fresh = [rng.standard_normal(x.shape).astype(np.float32) for x in xs]
+        ref = [K.matmul_host(w, x) for w, x in zip(ws, fresh)]
+        for dst, x in zip(pageable_x, fresh):
+            dst[...] = x
+        for o in outs:
+            o[...] = np.nan
+        K.matmul_host_batch(ws, pageable_x, outs)
+        for got, want_i in zip(outs, ref):
+            assert np.array_equal(got, want_i), rep
+    K.matmul_host_batch(ws[1:3], xn[1:3], yn[1:3])
+    assert np.array_equal(yn[1], K.matmul_host(ws[1], xn[1])) and np.array_equal(yn[2], K.matmul_host(ws[2], xn[2]))
+    plan = K.host_batch(ws, xn, yn)  # the argument arrays built once
+    for rep in range(4):
+        for dst in xn:
+            dst[...] = rng.standard_normal(dst.shape).astype(np.float32)
+        ref = [K.matmul_host(w, x) for w, x in zip(ws, xn)]
+        for y in yn:
+            y[...] = np.nan
+        plan.run()
+        for got, want_i in zip(yn, ref):
+            assert np.array_equal(got, want_i), rep
+    K.set("host_batch_graph", 0)
+    try:
+        for y in yn:
+            y[...] = np.nan
+        K.matmul_host_batch(ws, xn, yn)
+        for got, w, x in zip(yn, ws, xn):
+            assert np.array_equal(got, K.matmul_host(w, x))
+    finally:
+        K.set("host_batch_graph", 1)
+    assert K.status() == 0
     with pytest.raises(gk.GllmkError) as e:
         K.matmul_host_batch(ws[:1], [np.zeros((0, 1024), np.float32)], [np.zeros((0, 512), np.float32)])
     assert e.value.status == gk.Status.INVALID_ARG
