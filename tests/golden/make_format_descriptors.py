@@ -60,7 +60,9 @@ def parse_value(v: str):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_format_descriptors.py <checkout of gllm-kernels>")
+    ref = sys.argv[1]
     path = os.path.join(ref, "src", "quant_format.rs")
     raw = open(path).read()
     text = strip_comments(raw)
