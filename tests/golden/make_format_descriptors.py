@@ -5,7 +5,7 @@ registry behind QuantFormatDescriptor::for_type) and records, for the nine forma
 field as the reference wrote it: enum variants by name, their payload fields as integers.  Nothing is computed by
 this project's code.  Needs the reference checkout; the JSON it writes is what travels.
 
-Run:  python tests/golden/make_format_descriptors.py [path/to/gllm-kernels]
+Run:  python tests/golden/make_format_descriptors.py path/to/gllm-kernels
 """
 import json
 import os
