@@ -231,13 +231,15 @@ constexpr uint32_t P4_TMEM_SF = 256, P4_SF_SET_COLS = 48;  // per set: SFA 16 co
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P4_THREADS, 1)
 gemm_fp4_pair_kernel(const __grid_constant__ Fp4Params p, const int row_tiles, const int tok_tiles) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bars[3 * P4_STAGES + P4_SF_SETS + 2];
+    __shared__ __align__(8) uint64_t bars[4 * P4_STAGES + P4_SF_SETS + 2];
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s;
     const uint32_t smem_s = (tc::smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t full = tc::smem_u32(&bars[0]), empty = tc::smem_u32(&bars[P4_STAGES]), full2 = tc::smem_u32(&bars[2 * P4_STAGES]);
-    const uint32_t sf_full = tc::smem_u32(&bars[3 * P4_STAGES]);
-    const uint32_t accum_full = tc::smem_u32(&bars[3 * P4_STAGES + P4_SF_SETS]), accum_empty = accum_full + 8;
+    const uint32_t sf_landed = tc::smem_u32(&bars[3 * P4_STAGES]);  // per stage: its scale atoms have landed (they are
+                                                                     // requested first and are a sixth of the stage's bytes)
+    const uint32_t sf_full = tc::smem_u32(&bars[4 * P4_STAGES]);
+    const uint32_t accum_full = tc::smem_u32(&bars[4 * P4_STAGES + P4_SF_SETS]), accum_empty = accum_full + 8;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = tc::cluster_ctarank();
     const int pair = (int)(blockIdx.x >> 1), npairs = (int)(gridDim.x >> 1);
@@ -254,6 +256,7 @@ gemm_fp4_pair_kernel(const __grid_constant__ Fp4Params p, const int row_tiles, c
             tc::mbar_init(full + 8 * s, 1);
             tc::mbar_init(empty + 8 * s, 1);
             tc::mbar_init(full2 + 8 * s, 1);
+            tc::mbar_init(sf_landed + 8 * s, 1);
         }
         for (int s = 0; s < P4_SF_SETS; s++) tc::mbar_init(sf_full + 8 * s, 2 * P4_SF_WARPS);  // the scale warps of both CTAs (leader only)
         tc::mbar_init(accum_full, 1);
@@ -283,7 +286,11 @@ gemm_fp4_pair_kernel(const __grid_constant__ Fp4Params p, const int row_tiles, c
             const bool sfb_ok[2] = {b_tile0 < p.x_row_tiles, b_tile0 + 1 < p.x_row_tiles};
             // rows / tokens that do not exist are not copied: whatever the stage holds there only reaches accumulator
             // rows / columns that are never stored
-            const uint32_t tx = (a_ok ? 16384u + sf_bytes : 0u) + (b_ok ? 16384u : 0u) + ((uint32_t)sfb_ok[0] + (uint32_t)sfb_ok[1]) * sf_bytes;
+            // The scale atoms go first and signal a barrier of their own: the scale warps turn them into tensor-memory
+            // columns while the operand tiles of the same stage are still in flight (with one barrier for the whole
+            // stage the MMA thread waited ~190 cycles per k-step for the scale sets after the operands had landed).
+            const uint32_t tx_sf = (a_ok ? sf_bytes : 0u) + ((uint32_t)sfb_ok[0] + (uint32_t)sfb_ok[1]) * sf_bytes;
+            const uint32_t tx = (a_ok ? 16384u : 0u) + (b_ok ? 16384u : 0u);
             for (int ks = 0; ks < nks; ks++, g++) {
                 const uint32_t s = g % P4_STAGES;
                 if (g >= P4_STAGES && !tc::mbar_wait_cluster(empty + 8 * s, (g / P4_STAGES - 1) & 1u, abort_flag)) {
@@ -292,17 +299,18 @@ gemm_fp4_pair_kernel(const __grid_constant__ Fp4Params p, const int row_tiles, c
                     break;
                 }
                 const uint32_t st = smem_s + s * P4_STAGE_BYTES;
-                tc::mbar_expect_tx(full + 8 * s, tx);
-                if (a_ok) {
-                    bulk_load(st, p.qw + ((size_t)my_row_tile * ktiles + ks) * 16384, 16384u, full + 8 * s);
+                tc::mbar_expect_tx(sf_landed + 8 * s, tx_sf);
+                if (a_ok)
                     bulk_load(st + P4_A_BYTES + P4_B_BYTES, p.sfw + ((size_t)my_row_tile * atoms_per_row_tile + (size_t)ks * atoms_per_stage) * 512,
-                              sf_bytes, full + 8 * s);
-                }
-                if (b_ok) bulk_load(st + P4_A_BYTES, p.qx + ((size_t)(b_tile0 + rank) * ktiles + ks) * 16384, 16384u, full + 8 * s);
+                              sf_bytes, sf_landed + 8 * s);
                 for (int h = 0; h < 2; h++)
                     if (sfb_ok[h])
                         bulk_load(st + P4_A_BYTES + P4_B_BYTES + P4_SFA_BYTES + h * 2048,
-                                  p.sfx + ((size_t)(b_tile0 + h) * atoms_per_row_tile + (size_t)ks * atoms_per_stage) * 512, sf_bytes, full + 8 * s);
+                                  p.sfx + ((size_t)(b_tile0 + h) * atoms_per_row_tile + (size_t)ks * atoms_per_stage) * 512, sf_bytes,
+                                  sf_landed + 8 * s);
+                tc::mbar_expect_tx(full + 8 * s, tx);
+                if (a_ok) bulk_load(st, p.qw + ((size_t)my_row_tile * ktiles + ks) * 16384, 16384u, full + 8 * s);
+                if (b_ok) bulk_load(st + P4_A_BYTES, p.qx + ((size_t)(b_tile0 + rank) * ktiles + ks) * 16384, 16384u, full + 8 * s);
             }
         }
     } else if (warp == 1 && lane == 0 && rank != 0) {
@@ -379,7 +387,7 @@ gemm_fp4_pair_kernel(const __grid_constant__ Fp4Params p, const int row_tiles, c
         for (int t = pair; t < ntiles && ok; t += npairs)
             for (int ks = 0; ks < nks; ks++, g++) {
                 const uint32_t s = g % P4_STAGES, b = g % P4_SF_SETS;
-                ok = tc::mbar_wait(full + 8 * s, (g / P4_STAGES) & 1u, abort_flag) &&
+                ok = tc::mbar_wait(sf_landed + 8 * s, (g / P4_STAGES) & 1u, abort_flag) &&
                      // set b was last read by the MMAs of k-step g - 3, whose completion also released that k-step's stage
                      (g < P4_SF_SETS || tc::mbar_wait_cluster(empty + 8 * ((g - P4_SF_SETS) % P4_STAGES), ((g - P4_SF_SETS) / P4_STAGES) & 1u, abort_flag));
                 ok = __all_sync(0xffffffffu, ok);
