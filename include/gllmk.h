@@ -298,7 +298,7 @@ GLLMK_API int32_t gllmk_w8a8_linear_f32(gllmk_ctx ctx, gllmk_weight w, const flo
 /* gllmk_gemv_exchange: the same product with the hand-shake built in, for chains of sharded products (a decode
  *   step): before it reads x it waits (bounded: "peer_wait_spins" probes per rank, then status 32) until every
  *   rank has completed as many exchange products as this rank — so an x that is the previous product's gathered y
- *   is complete — and the block that finishes the launch's last row tile signals the new count to every rank.  No
+ *   is complete — and the block that finishes last signals the new count to every rank (one system-scope fence per launch).  No
  *   barrier kernel between products: one staging + one GEMV launch per product, whose weight prefetch overlaps
  *   the wait.  Every rank must issue the same sequence of exchange products; flags_local / flags_peers are the
  *   flag words at the start of each rank's gllmk_shared_alloc buffer (this call uses words 32..48, the barrier
