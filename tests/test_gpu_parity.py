@@ -506,6 +506,24 @@ def test_matmul_host_batch_equals_one_call_per_product(gk, K, oracle, torch):
         plan.run()
         for got, want_i in zip(yn, ref):
             assert np.array_equal(got, want_i), rep
+    # a larger product in between makes the context grow its scratch buffers: the captured step must not be replayed
+    # with the old ones (the cached graph is keyed on them), and the list is captured again later
+    oid_big, blocks_big, _, _ = make(oracle, "q4k", 2048, 4096, seed=5)
+    w_big = K.upload(qt_of(gk, "q4k"), 2048, 4096, blocks_big)
+    x_big = rng.standard_normal((9, 4096)).astype(np.float32)
+    y_big = K.matmul_host(w_big, x_big)
+    ref_big = oracle.quant_matmul(blocks_big, np.ascontiguousarray(x_big.T), oid_big, 2048, 9, 4096, threads=8).T
+    assert oracle.rel_err(y_big, ref_big) <= 2e-3
+    for rep in range(4):
+        for dst in xn:
+            dst[...] = rng.standard_normal(dst.shape).astype(np.float32)
+        ref = [K.matmul_host(w, x) for w, x in zip(ws, xn)]
+        for y in yn:
+            y[...] = np.nan
+        plan.run()
+        for got, want_i in zip(yn, ref):
+            assert np.array_equal(got, want_i), rep
+    w_big.free()
     K.set("host_batch_graph", 0)
     try:
         for y in yn:
