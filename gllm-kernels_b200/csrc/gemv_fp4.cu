@@ -24,8 +24,9 @@ constexpr int FD_DIGITS = 8;
 constexpr int FD_MAX_STAGES = 12;     // a stage = weight tile (16 KB) + digit tile (128 B x MMA N) + both scale atoms, 1 KB aligned;
                                       // as many as fit: bytes in flight per SM are what hides the HBM latency
 constexpr int FD_SMEM_BUDGET = 232448 - 2048;
-constexpr int FD_THREADS = 192;       // warp 0: copies, warp 1: MMA + TMEM, warps 2-5: epilogue
-constexpr uint32_t FD_TMEM_COLS = 256;                        // 128 accumulator + 2 x (16 SFA + 16 SFB)
+constexpr int FD_THREADS = 320;       // warp 0: copies, warp 1: MMA + TMEM, warps 2-5: epilogue, warps 6-9: scale factors
+constexpr int FD_SF_SETS = 4;         // scale-factor column sets in rotation
+constexpr uint32_t FD_TMEM_COLS = 256;                        // 128 accumulator + 4 x (16 SFA + 16 SFB)
 
 struct FdParams {
     const uint8_t *qw, *sfw;  // weight data / scale planes
@@ -133,10 +134,23 @@ __global__ void __launch_bounds__(256) fd_stage_kernel(const float *__restrict__
         // tens of KB out of L2): cheaper than a reduction kernel of its own in front of this one.
         float a = 0.0f;
         int bad = 0;
-        for (int64_t k = threadIdx.x; k < K; k += 256) {
-            const float v = fabsf(xr[k * xsk]);
-            bad |= !(v < inf);
-            a = fmaxf(a, v);
+        if (xsk == 1 && (K & 3) == 0 && (reinterpret_cast<uintptr_t>(xr) & 15) == 0) {
+            // contiguous row: 16-byte loads, four in flight per thread (a 28672-element row is 7 rounds instead of 112)
+            const float4 *x4 = reinterpret_cast<const float4 *>(xr);
+            const int64_t n4 = K >> 2;
+#pragma unroll 4
+            for (int64_t k = threadIdx.x; k < n4; k += 256) {
+                const float4 q = __ldg(x4 + k);
+                const float v0 = fabsf(q.x), v1 = fabsf(q.y), v2 = fabsf(q.z), v3 = fabsf(q.w);
+                bad |= !(v0 < inf) | !(v1 < inf) | !(v2 < inf) | !(v3 < inf);
+                a = fmaxf(fmaxf(a, fmaxf(v0, v1)), fmaxf(v2, v3));
+            }
+        } else {
+            for (int64_t k = threadIdx.x; k < K; k += 256) {
+                const float v = fabsf(xr[k * xsk]);
+                bad |= !(v < inf);
+                a = fmaxf(a, v);
+            }
         }
 #pragma unroll
         for (int o = 16; o; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
@@ -221,11 +235,12 @@ __global__ void __launch_bounds__(256) fd_stage_kernel(const float *__restrict__
 // ---- the kernel -------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(FD_THREADS, 1) gemv_fp4_tc_kernel(const __grid_constant__ FdParams p) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bars[2 * FD_MAX_STAGES + 2];
+    __shared__ __align__(8) uint64_t bars[2 * FD_MAX_STAGES + 2 + 2 * FD_SF_SETS];
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s, last_s;
     const uint32_t smem_s = (tc::smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t full = tc::smem_u32(&bars[0]), empty = full + 8 * FD_MAX_STAGES, accum = empty + 8 * FD_MAX_STAGES, tmem_free = accum + 8;
+    const uint32_t sf_full = tmem_free + 8, sf_empty = sf_full + 8 * FD_SF_SETS;  // per scale set: written by the four scale warps / read by its MMAs
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int aps = p.nv ? 4 : 2;  // 512-byte scale atoms per k-step
     const uint32_t sf_bytes = (uint32_t)aps * 512u, bbytes = (uint32_t)p.ncol * 128u;
@@ -241,6 +256,10 @@ __global__ void __launch_bounds__(FD_THREADS, 1) gemv_fp4_tc_kernel(const __grid
         }
         tc::mbar_init(accum, 1);
         tc::mbar_init(tmem_free, 4);
+        for (int s = 0; s < FD_SF_SETS; s++) {
+            tc::mbar_init(sf_full + 8 * s, 4);
+            tc::mbar_init(sf_empty + 8 * s, 1);
+        }
         tc::mbar_init_fence();
     }
     if (warp == 1) tc::tmem_alloc(tc::smem_u32(&tmem_base_s), FD_TMEM_COLS);
@@ -294,8 +313,12 @@ __global__ void __launch_bounds__(FD_THREADS, 1) gemv_fp4_tc_kernel(const __grid
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            // ---------------- scale copies + MMA issue ----------------
+            // ---------------- MMA issue ----------------
+            // The scale factors are put into tensor memory by the scale warps (below), not by tcgen05.cp from this thread:
+            // a copy occupies the tensor pipe for ~120 cycles here, eight of them per k-step (NVFP4) were more than half of
+            // the k-step and held the kernel at 0.46 of the HBM bandwidth (MXFP4, four copies: 0.62).
             int slot = 0, round = 0, seg = 0;
+            uint32_t g = 0;  // k-steps issued by this CTA so far
             bool ok = true;
             for (int64_t u = u_begin; u < u_end && ok; seg++) {
                 const int tile = (int)(u / p.nks), j0 = (int)(u - (int64_t)tile * p.nks);
@@ -303,33 +326,24 @@ __global__ void __launch_bounds__(FD_THREADS, 1) gemv_fp4_tc_kernel(const __grid
                 // the accumulator is rewritten from the segment's first MMA on: the previous epilogue must be done
                 if (seg > 0 && !tc::mbar_wait(tmem_free, (uint32_t)((seg - 1) & 1), abort_flag)) ok = false;
                 tc::fence_after_sync();
-                for (int ks = j0; ks < j1 && ok; ks++) {
-                    if (!tc::mbar_wait(full + 8 * slot, (uint32_t)(round & 1), abort_flag)) {
+                for (int ks = j0; ks < j1 && ok; ks++, g++) {
+                    const uint32_t b = g % FD_SF_SETS;
+                    if (!tc::mbar_wait(full + 8 * slot, (uint32_t)(round & 1), abort_flag) ||
+                        !tc::mbar_wait(sf_full + 8 * b, (g / FD_SF_SETS) & 1u, abort_flag)) {
                         ok = false;
                         break;
                     }
                     tc::fence_after_sync();
                     const uint32_t st = smem_s + (uint32_t)(slot * p.stage_bytes);
-                    const uint32_t sfa = st + sfa_off, sfb = st + sfb_off;
                     const uint64_t ad = tc::smem_desc_sw128(st), bd = tc::smem_desc_sw128(st + b_off);
-                    const uint32_t tsfa = tmem + 128u + 32u * (uint32_t)(ks & 1), tsfb = tsfa + 16u;
+                    const uint32_t tsfa = tmem + 128u + 32u * b, tsfb = tsfa + 16u;
                     const uint32_t first = (uint32_t)(ks != j0);
                     if (p.nv) {
-#pragma unroll
-                        for (int j = 0; j < 4; j++) {
-                            tc::tmem_cp_sf(tsfa + 4 * j, fd_sf_desc(sfa + 512 * j));
-                            tc::tmem_cp_sf(tsfb + 4 * j, fd_sf_desc(sfb + 512 * j));
-                        }
                         const uint32_t idesc = tc::idesc_fp4(128, p.ncol, 0, 0, 0);
 #pragma unroll
                         for (int j = 0; j < 4; j++)
                             tc::mma_nvf4(tmem, ad + 2 * j, bd + 2 * j, idesc, first | (uint32_t)(j != 0), tsfa + 4 * j, tsfb + 4 * j);
                     } else {
-#pragma unroll
-                        for (int j = 0; j < 2; j++) {
-                            tc::tmem_cp_sf(tsfa + 4 * j, fd_sf_desc(sfa + 512 * j));
-                            tc::tmem_cp_sf(tsfb + 4 * j, fd_sf_desc(sfb + 512 * j));
-                        }
 #pragma unroll
                         for (int j = 0; j < 4; j++) {
                             const int id = (j & 1) * 2;
@@ -338,6 +352,7 @@ __global__ void __launch_bounds__(FD_THREADS, 1) gemv_fp4_tc_kernel(const __grid
                         }
                     }
                     tc::mma_commit(empty + 8 * slot);
+                    tc::mma_commit(sf_empty + 8 * b);
                     if (++slot == p.stages) slot = 0, round++;
                 }
                 if (!ok) {
@@ -348,6 +363,46 @@ __global__ void __launch_bounds__(FD_THREADS, 1) gemv_fp4_tc_kernel(const __grid
                 tc::mma_commit(accum);
                 u += j1 - j0;
             }
+        }
+    } else if (warp >= 6) {
+        // ---------------- scale warps: stage -> tensor memory, lane quadrant warp % 4 ----------------
+        // An atom is 128 rows x 4 scale bytes: row r's bytes at (r % 32) * 16 + (r / 32) * 4.  Lane l reads its 16 bytes of
+        // every atom (weight atoms -> columns 4j of the set, digit atoms -> columns 16 + 4j) and writes all 32 columns of
+        // its own lane with ONE tcgen05.st: what tcgen05.cp.32x128b.warpx4 would leave there, every quadrant a copy.
+        const uint32_t quad_lane = (uint32_t)(32 * (warp & 3)) << 16;
+        int slot = 0, round = 0;
+        uint32_t g = 0;
+        bool ok = true;
+        for (int64_t u = u_begin; u < u_end && ok; u++, g++) {
+            const uint32_t b = g % FD_SF_SETS;
+            ok = tc::mbar_wait(full + 8 * slot, (uint32_t)(round & 1), abort_flag) &&
+                 (g < (uint32_t)FD_SF_SETS || tc::mbar_wait(sf_empty + 8 * b, (g / FD_SF_SETS - 1) & 1u, abort_flag));
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) {
+                if (lane == 0 && !abort_s) {
+                    abort_s = 1;
+                    atomicExch(p.status, 54);
+                }
+                break;
+            }
+            tc::fence_after_sync();
+            const uint32_t st = smem_s + (uint32_t)(slot * p.stage_bytes) + 16u * (uint32_t)lane;
+            uint32_t w[32];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                // with two atoms per k-step (MXFP4) the upper columns take stale bytes that no MMA reads
+                const uint32_t ja = (uint32_t)(j < aps ? j : 0);
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                             : "=r"(w[4 * j]), "=r"(w[4 * j + 1]), "=r"(w[4 * j + 2]), "=r"(w[4 * j + 3]) : "r"(st + sfa_off + 512u * ja));
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                             : "=r"(w[16 + 4 * j]), "=r"(w[17 + 4 * j]), "=r"(w[18 + 4 * j]), "=r"(w[19 + 4 * j]) : "r"(st + sfb_off + 512u * ja));
+            }
+            tc::tmem_st32(tmem + quad_lane + 128u + 32u * b, w);
+            tc::tmem_st_wait();
+            tc::fence_before_sync();
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(sf_full + 8 * b);
+            if (++slot == p.stages) slot = 0, round++;
         }
     } else {
         // ---------------- epilogue warps: TMEM lane quadrant = warp % 4 = 32 weight rows ----------------

@@ -148,7 +148,7 @@ GLLMK_API const char *gllmk_last_error(gllmk_ctx ctx);
  * counters (which a kernel that gave up leaves non-zero) are cleared, so the next call on the context is
  * correct again.  Results of the call that gave up are incomplete.  Codes name the kernel and the wait: 1-2 decode GEMV (consumer, producer),
  * 10-14 fused-dequant prefill GEMM, 21-23 FP4 x FP4 GEMM, 31 gllmk_peer_barrier, 32 gllmk_gemv_exchange /
- * gllmk_exchange_wait (another rank's products), 41-43 W8A8 GEMM, 51-53 FP4
+ * gllmk_exchange_wait (another rank's products), 41-43 W8A8 GEMM, 51-54 FP4
  * decode GEMV on the tensor core. */
 GLLMK_API int32_t gllmk_ctx_status(gllmk_ctx ctx, int32_t *device_status);
 /* Tuning knobs, for experiments.  key: "gemv_ctas_per_sm" (resident CTAs per SM the decode grid is
