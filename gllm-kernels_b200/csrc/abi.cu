@@ -273,6 +273,7 @@ int32_t gllmk_ctx_set(gllmk_ctx ctx, const char *key, int64_t value) {
     else if (!strcmp(key, "gemv_pdl")) c->gemv_pdl = value;
     else if (!strcmp(key, "gemv_fp4_int")) c->gemv_fp4_int = value;
     else if (!strcmp(key, "gemm_fp4_pair")) c->gemm_fp4_pair = value;
+    else if (!strcmp(key, "gemm_i8_pair")) c->gemm_i8_pair = value;
     else if (!strcmp(key, "gemv_fuse")) c->gemv_fuse = value;
     else if (!strcmp(key, "gemm_tail_split")) c->gemm_tail_split = value;
     else if (!strcmp(key, "host_batch_graph")) c->host_batch_graph = value;

@@ -110,6 +110,8 @@ struct Ctx {
                                 // and two GPUs), 1 exchange products only, 2 every product
     int64_t gemm_fp4_pair = 1;  // FP4 x FP4 GEMM with m > 128 on CTA pairs (cta_group::2, persistent): 0 off, 1 one 256-token
                                 // accumulator (fastest measured), 2 two 192-token accumulators, 3 two 128-token accumulators
+    int64_t gemm_i8_pair = 1;   // W8A8 GEMM with m > 128 on CTA pairs (cta_group::2, persistent, two accumulators): 0 never,
+                                // 1 when the estimate favours it, 2 always
     int64_t peer_wait_spins = (int64_t)1 << 22;  // probes of another rank's flag before a wait gives up (status 31 / 32)
 };
 

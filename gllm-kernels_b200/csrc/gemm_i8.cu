@@ -195,6 +195,182 @@ __global__ void __launch_bounds__(I8_THREADS, 1) gemm_i8_kernel(const __grid_con
     if (warp == 1) tc::tmem_dealloc(tmem, TMEM_COLS);
 }
 
+// ---------------------------------------------------------------------------------------------
+// m > 128: CTA pairs (tcgen05 cta_group::2, MMA M = 256), persistent, two accumulators.
+//
+// The kernel above runs at what an SM can take in from L2: 64 KB per k-step for two 128 x 256 tiles.  As a pair, each
+// CTA brings in its own 128 weight rows and HALF of the 256-token activation tile (the tensor core reads the other half
+// from the partner's shared memory): 32 KB per k-step and tile.  One 256-column accumulator per tile leaves room for a
+// second one, so the eight epilogue warps store tile i while the MMA thread fills the accumulator of tile i + 1, and the
+// grid is the resident pairs with tiles dealt round robin.  Structure and hand-shakes are those of gemm_fp4_pair_kernel
+// (gemm_fp4.cu) without the scale-factor path: the partner's copy thread cannot signal the leader's barrier with a plain
+// bulk copy, so a relay thread forwards "my stage has landed"; stages go back to both CTAs with one commit per barrier.
+// ---------------------------------------------------------------------------------------------
+constexpr int I8P_STAGES = 6, I8P_STAGE_BYTES = 2 * I8_TILE, I8P_EPI_WARPS = 8;
+constexpr int I8P_THREADS = 64 + 32 * I8P_EPI_WARPS;
+constexpr size_t I8P_SMEM = (size_t)I8P_STAGES * I8P_STAGE_BYTES + (size_t)I8P_EPI_WARPS * 4096 + 1024;
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(I8P_THREADS, 1)
+gemm_i8_pair_kernel(const __grid_constant__ I8Params p, const int tok_tiles, const int x_tiles) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bars[3 * I8P_STAGES + 4];
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int abort_s;
+    const uint32_t smem_s = (tc::smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t full = tc::smem_u32(&bars[0]), empty = tc::smem_u32(&bars[I8P_STAGES]), full2 = tc::smem_u32(&bars[2 * I8P_STAGES]);
+    const uint32_t accum_full = tc::smem_u32(&bars[3 * I8P_STAGES]), accum_empty = accum_full + 16;  // two each
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = tc::cluster_ctarank();
+    const int pair = (int)(blockIdx.x >> 1), npairs = (int)(gridDim.x >> 1);
+    const int row_pairs = (p.row_tiles + 1) >> 1;
+    const int ntiles = row_pairs * tok_tiles;
+    volatile int *abort_flag = &abort_s;
+
+    if (threadIdx.x == 0) {
+        abort_s = 0;
+        for (int s = 0; s < I8P_STAGES; s++) {
+            tc::mbar_init(full + 8 * s, 1);
+            tc::mbar_init(empty + 8 * s, 1);
+            tc::mbar_init(full2 + 8 * s, 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            tc::mbar_init(accum_full + 8 * a, 1);
+            tc::mbar_init(accum_empty + 8 * a, 2 * I8P_EPI_WARPS);  // the epilogue warps of both CTAs (used in the leader only)
+        }
+        tc::mbar_init_fence();
+    }
+    if (warp == 1) tc::tmem_alloc_pair(tc::smem_u32(&tmem_base_s), 512);
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::cluster_arrive();  // both CTAs' barriers exist before either CTA arrives on the other's
+    tc::cluster_wait();
+    tc::fence_after_sync();
+    const uint32_t tmem = tmem_base_s;
+
+    if (warp == 0 && lane == 0) {
+        // ---------------- copies: own weight rows, own half of the activation tile ----------------
+        uint32_t g = 0;
+        for (int t = pair; t < ntiles && !*abort_flag; t += npairs) {
+            const int rp = t / tok_tiles, tt = t % tok_tiles;
+            const int my_row_tile = 2 * rp + (int)rank, my_x_tile = 2 * tt + (int)rank;
+            const bool a_ok = my_row_tile < p.row_tiles, b_ok = my_x_tile < x_tiles;
+            // rows / tokens that do not exist are not copied: what the stage holds there only reaches accumulator rows /
+            // columns that are never stored
+            const uint32_t tx = (a_ok ? (uint32_t)I8_TILE : 0u) + (b_ok ? (uint32_t)I8_TILE : 0u);
+            for (int ks = 0; ks < p.nks; ks++, g++) {
+                const uint32_t s = g % I8P_STAGES;
+                if (g >= (uint32_t)I8P_STAGES && !tc::mbar_wait_cluster(empty + 8 * s, (g / I8P_STAGES - 1) & 1u, abort_flag)) {
+                    abort_s = 1;
+                    atomicExch(p.status, 44);
+                    break;
+                }
+                const uint32_t st = smem_s + s * I8P_STAGE_BYTES;
+                tc::mbar_expect_tx(full + 8 * s, tx);
+                if (a_ok) i8_bulk(st, p.w + ((size_t)my_row_tile * p.nks + ks) * I8_TILE, I8_TILE, full + 8 * s);
+                if (b_ok) i8_bulk(st + I8_TILE, p.xt + ((size_t)my_x_tile * p.nks + ks) * I8_TILE, I8_TILE, full + 8 * s);
+            }
+        }
+    } else if (warp == 1 && lane == 0 && rank != 0) {
+        // ---------------- partner CTA: tell the leader when this CTA's stage has landed ----------------
+        uint32_t g = 0;
+        bool ok = true;
+        for (int t = pair; t < ntiles && ok && !*abort_flag; t += npairs)
+            for (int ks = 0; ks < p.nks; ks++, g++) {
+                const uint32_t s = g % I8P_STAGES;
+                if (!tc::mbar_wait(full + 8 * s, (g / I8P_STAGES) & 1u, abort_flag)) {
+                    abort_s = 1;
+                    atomicExch(p.status, 45);
+                    ok = false;
+                    break;
+                }
+                // the stage's bytes are in place before this arrive is issued (the barrier phase was observed)
+                tc::mbar_arrive_cluster_relaxed(tc::map_to_cta(full2 + 8 * s, 0));
+            }
+    } else if (warp == 1 && lane == 0) {
+        // ---------------- leader CTA: MMA issue for the pair, accumulator (tile & 1) ----------------
+        const uint32_t idesc = tc::idesc_i8(256, I8_BN, 1, 0);  // weights signed (operand A), activations unsigned (operand B)
+        uint32_t g = 0, it = 0;
+        for (int t = pair; t < ntiles && !*abort_flag; t += npairs, it++) {
+            const uint32_t acc = it & 1u;
+            // the tile before last used this accumulator: all sixteen epilogue warps of the pair have read it out
+            if (it >= 2 && !tc::mbar_wait_cluster(accum_empty + 8 * acc, ((it >> 1) - 1) & 1u, abort_flag)) {
+                abort_s = 1;
+                atomicExch(p.status, 46);
+                break;
+            }
+            tc::fence_after_sync();
+            const uint32_t td = tmem + 256u * acc;
+            bool ok = true;
+            for (int ks = 0; ks < p.nks; ks++, g++) {
+                const uint32_t s = g % I8P_STAGES, ph = (g / I8P_STAGES) & 1u;
+                if (!tc::mbar_wait(full + 8 * s, ph, abort_flag) || !tc::mbar_wait_cluster(full2 + 8 * s, ph, abort_flag)) {
+                    abort_s = 1;
+                    atomicExch(p.status, 42);
+                    ok = false;
+                    break;
+                }
+                tc::fence_after_sync();
+                const uint32_t st = smem_s + s * I8P_STAGE_BYTES;
+                const uint64_t ad = tc::smem_desc_sw128(st), bd = tc::smem_desc_sw128(st + I8_TILE);
+#pragma unroll
+                for (int j = 0; j < 4; j++) tc::mma_i8_pair(td, ad + 2 * j, bd + 2 * j, idesc, (uint32_t)((ks | j) != 0));
+                // once these MMAs have completed, stage s is free in BOTH CTAs
+                tc::mma_commit_pair(empty + 8 * s);
+                tc::mma_commit_pair(tc::map_to_cta(empty + 8 * s, 1));
+            }
+            if (!ok) break;
+            tc::mma_commit_pair(accum_full + 8 * acc);
+            tc::mma_commit_pair(tc::map_to_cta(accum_full + 8 * acc, 1));
+        }
+    }
+    __syncwarp();
+
+    if (warp >= 2) {
+        // ---------------- epilogue: this CTA's 128 rows x 256 tokens of accumulator (tile & 1) ----------------
+        // warp w reads TMEM lane quadrant w % 4; the two warps of a quadrant take 128 token columns each
+        const int quad = warp & 3, half = (warp - 2) >> 2;
+        uint8_t *stage = smem_raw + (smem_s - tc::smem_u32(smem_raw)) + (size_t)I8P_STAGES * I8P_STAGE_BYTES + (size_t)(warp - 2) * 4096;
+        const uint32_t accum_empty_leader = tc::map_to_cta(accum_empty, 0);
+        uint32_t it = 0;
+        for (int t = pair; t < ntiles; t += npairs, it++) {
+            const uint32_t acc = it & 1u;
+            bool ok = !abort_s && tc::mbar_wait_cluster(accum_full + 8 * acc, (it >> 1) & 1u, abort_flag);
+            if (!ok && !abort_s) {
+                abort_s = 1;
+                atomicExch(p.status, 43);
+            }
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc::fence_after_sync();
+            const int rp = t / tok_tiles, tt = t % tok_tiles;
+            const int64_t row0 = (int64_t)(2 * rp + (int)rank) * I8_BM + 32 * quad, tok0 = (int64_t)tt * I8_BN + 128 * half;
+            const uint32_t tbase = tmem + ((uint32_t)(32 * quad) << 16) + 256u * acc + (uint32_t)(128 * half);
+#pragma unroll 1
+            for (int c = 0; c < 128; c += 32) {
+                uint32_t v[32];
+                tc::tmem_ld32(tbase + (uint32_t)c, v);
+                tc::tmem_ld_wait();
+                if (row0 < p.n && tok0 + c < p.m) {
+                    float o[32];  // the s32 bit patterns travel through the 32-bit store helper unchanged
+#pragma unroll
+                    for (int j = 0; j < 32; j++) o[j] = __uint_as_float(v[j]);
+                    tc::store_block_32x32<false>(p.c, p.ldc, row0, tok0 + c, p.n, p.m, o, stage, lane, p.vec);
+                }
+            }
+            // this warp's reads of the accumulator are complete (wait::ld): the leader may reuse it for the tile after next
+            tc::fence_before_sync();
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive_cluster_relaxed(accum_empty_leader + 8 * acc);
+        }
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    // neither CTA may leave (or give TMEM back) while the pair's MMAs can still read its shared memory
+    tc::cluster_arrive();
+    tc::cluster_wait();
+    if (warp == 1) tc::tmem_dealloc_pair(tmem, 512);
+}
+
 // dequantize_i32_to_f32 (src/macros/matmul_x86_int8.rs:414-456, scalar tail semantics): (c as f32) * scale_a * scale_b
 // (+ bias[j]), then the activation of src/macros/gemm_epilogue.rs:131-152
 // scale_a_dev != nullptr: the activation scale is read from device memory (written by the activation quantizer of the
@@ -317,11 +493,44 @@ int32_t gemm_i8_launch(Ctx *c, const Weight *w, const uint8_t *a, int64_t lda, i
     p.xt = static_cast<const uint8_t *>(c->act);
     stage_act_u8_kernel<<<dim3((unsigned)p.nks, (unsigned)atiles), 256, 0, s>>>(a, lda, m, w->k, static_cast<uint8_t *>(c->act));
     GK_CUDA(c, cudaGetLastError());
-    // two row tiles per CTA when the estimated time (waves x (k-steps per CTA x relative step cost + a fixed
-    // prologue / epilogue worth ~8 steps)) is lower
+    // estimated times in k-steps of a 128 x 256 tile (waves x (k-steps per CTA x relative step cost + a fixed prologue /
+    // epilogue worth ~8 steps)): one row tile per CTA, two row tiles per CTA (a third fewer bytes per MAC), CTA pairs
+    // (half the bytes per MAC of one tile per CTA; measured 0.82 of the two-tile form on W[11008, 4096] x 2048, 1.06 x 512)
     const auto waves = [&](int ctas) { return (double)((ctas + c->sm_count - 1) / c->sm_count); };
     const int pairs = (p.row_tiles + 1) / 2;
     const double t1 = waves(mtiles * p.row_tiles) * (p.nks + 8.0), t2 = waves(mtiles * pairs) * (2.0 * p.nks * 0.75 + 8.0);
+    const int half_sms = c->sm_count / 2 > 0 ? c->sm_count / 2 : 1;
+    const double tp = (double)((mtiles * pairs + half_sms - 1) / half_sms) * (p.nks * 0.6 + 8.0);
+    if (m > 128 && (c->gemm_i8_pair == 2 || (c->gemm_i8_pair == 1 && tp < 0.9 * (t1 < t2 ? t1 : t2)))) {
+        const void *fn = (const void *)gemm_i8_pair_kernel;
+        static int pairs_resident[64] = {};  // per device: CTA pairs resident at once (0 = not yet asked)
+        const int dev_slot = c->device & 63;
+        if (!pairs_resident[dev_slot]) {
+            GK_CUDA(c, cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)I8P_SMEM));
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3((unsigned)c->sm_count & ~1u);
+            cfg.blockDim = dim3((unsigned)I8P_THREADS);
+            cfg.dynamicSmemBytes = I8P_SMEM;
+            cudaLaunchAttribute at[1];
+            at[0].id = cudaLaunchAttributeClusterDimension;
+            at[0].val.clusterDim.x = 2;
+            at[0].val.clusterDim.y = 1;
+            at[0].val.clusterDim.z = 1;
+            cfg.attrs = at;
+            cfg.numAttrs = 1;
+            int nclusters = 0;
+            if (cudaOccupancyMaxActiveClusters(&nclusters, fn, &cfg) != cudaSuccess || nclusters < 1) {
+                (void)cudaGetLastError();
+                nclusters = c->sm_count / 2;
+            }
+            pairs_resident[dev_slot] = nclusters < c->sm_count / 2 ? nclusters : c->sm_count / 2;
+        }
+        const int ntiles = ((p.row_tiles + 1) / 2) * mtiles;
+        const int npairs = ntiles < pairs_resident[dev_slot] ? ntiles : pairs_resident[dev_slot];
+        gemm_i8_pair_kernel<<<dim3(2u * (unsigned)npairs), I8P_THREADS, I8P_SMEM, s>>>(p, mtiles, atiles);
+        GK_CUDA(c, cudaGetLastError());
+        return GLLMK_STATUS_OK;
+    }
     if (ntok > 128 && t2 < t1) return i8_launch_mt<2>(c, p, dim3((unsigned)pairs, (unsigned)mtiles), ntok, s);
     return i8_launch_mt<1>(c, p, dim3((unsigned)p.row_tiles, (unsigned)mtiles), ntok, s);
 }

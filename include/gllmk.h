@@ -148,7 +148,7 @@ GLLMK_API const char *gllmk_last_error(gllmk_ctx ctx);
  * counters (which a kernel that gave up leaves non-zero) are cleared, so the next call on the context is
  * correct again.  Results of the call that gave up are incomplete.  Codes name the kernel and the wait: 1-2 decode GEMV (consumer, producer),
  * 10-14 fused-dequant prefill GEMM, 21-23 FP4 x FP4 GEMM, 31 gllmk_peer_barrier, 32 gllmk_gemv_exchange /
- * gllmk_exchange_wait (another rank's products), 41-43 W8A8 GEMM, 51-54 FP4
+ * gllmk_exchange_wait (another rank's products), 41-46 W8A8 GEMM, 51-54 FP4
  * decode GEMV on the tensor core. */
 GLLMK_API int32_t gllmk_ctx_status(gllmk_ctx ctx, int32_t *device_status);
 /* Tuning knobs, for experiments.  key: "gemv_ctas_per_sm" (resident CTAs per SM the decode grid is
@@ -157,7 +157,8 @@ GLLMK_API int32_t gllmk_ctx_status(gllmk_ctx ctx, int32_t *device_status);
  * the block-scaled tensor-core one), "gemv_fuse" (decode GEMV converting its own activation slices instead of a staging launch when a
  * block's share is small: 0 never (default), 1 products of an exchange chain only, 2 every product), "gemm_fp4_pair" (FP4 x FP4 GEMM with
  * m > 128: 0 the one-CTA kernel, 1 (default) CTA pairs with one 256-token accumulator, 2 CTA pairs with two 192-token
- * accumulators, 3 CTA pairs with two 128-token accumulators), "host_batch_graph" (gllmk_matmul_host_batch replays a captured graph for a repeated
+ * accumulators, 3 CTA pairs with two 128-token accumulators), "gemm_i8_pair" (W8A8 GEMM with m > 128 on the CTA-pair kernel: 0 never, 1 (default) when the estimate favours it, 2 always),
+ * "host_batch_graph" (gllmk_matmul_host_batch replays a captured graph for a repeated
  * argument list: 1 default, 0 never), "gemm_tail_split" (prefill GEMM, last partial wave of tiles cut along k:
  * 0 automatic, 1 never, n into n), "peer_wait_spins" (how many times a wait on another GPU's flag probes it
  * before it gives up with status 31; default 2^22, about a second), "inject_give_up" (testing aid, host side

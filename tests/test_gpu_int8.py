@@ -47,18 +47,49 @@ def test_gemm_int8_resident_weight_bit_exact(gk, K, m, n, k, layout_kn):
     w.free()
 
 
-def test_gemm_int8_two_row_tiles_per_cta(gk, K):
-    """299 row tiles and a 256-token tile: a CTA takes two row tiles (two accumulators share the activation stage),
-    the last CTA has one."""
+@pytest.mark.parametrize("pair", [0, 2])
+def test_gemm_int8_two_row_tiles_per_cta(gk, K, pair):
+    """299 row tiles and a 256-token tile.  One-CTA kernel: a CTA takes two row tiles (two accumulators share the
+    activation stage), the last CTA has one.  CTA-pair kernel: 150 row pairs on 74 resident pairs, the last pair's second
+    CTA has no rows."""
     import torch
     m, n, k = 200, 128 * 299 - 50, 256
     rng = np.random.default_rng(9)
     a = rng.integers(0, 256, size=(m, k), dtype=np.uint8)
     b = rng.integers(-128, 128, size=(k, n), dtype=np.int8)
     w = K.upload_int8(b)
-    c = K.gemm_int8(w, torch.from_numpy(a).cuda()).cpu().numpy()
+    K.set("gemm_i8_pair", pair)
+    try:
+        c = K.gemm_int8(w, torch.from_numpy(a).cuda()).cpu().numpy()
+    finally:
+        K.set("gemm_i8_pair", 1)
     assert np.array_equal(c, ref_i32(a, b))
     assert K.status() == 0
+    w.free()
+
+
+@pytest.mark.parametrize("m,n,k", [(129, 128, 128), (257, 300, 1000), (700, 2500, 1152), (2048, 4000, 640), (513, 130, 4096)])
+def test_gemm_int8_cta_pair_kernel(gk, K, m, n, k):
+    """m > 128 runs on the persistent CTA-pair kernel: token counts that leave the second half of a tile empty or ragged,
+    an odd number of 128-row groups, more k-steps than stages, more tiles than resident pairs (both accumulators in
+    rotation over many tiles) — bit-exact, and equal to the one-CTA kernel."""
+    import torch
+    rng = np.random.default_rng(m + n + k)
+    a = rng.integers(0, 256, size=(m, k), dtype=np.uint8)
+    b = rng.integers(-128, 128, size=(k, n), dtype=np.int8)
+    w = K.upload_int8(b)
+    ad = torch.from_numpy(a).cuda()
+    K.set("gemm_i8_pair", 2)  # always (the default picks the pair kernel when its estimate is lower)
+    try:
+        c_pair = K.gemm_int8(w, ad).clone()
+        c_again = K.gemm_int8(w, ad).clone()
+        K.set("gemm_i8_pair", 0)
+        c_one = K.gemm_int8(w, ad).clone()
+    finally:
+        K.set("gemm_i8_pair", 1)
+    assert K.status() == 0
+    assert np.array_equal(c_pair.cpu().numpy(), ref_i32(a, b))
+    assert torch.equal(c_pair, c_again) and torch.equal(c_pair, c_one)
     w.free()
 
 
