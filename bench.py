@@ -775,6 +775,7 @@ def decode_layers(K, gk, torch, dev, gen, peak, fused, layers=4, ffn=False):
 
 def extra_gemm(K, gk, torch, dev, gen):
     """Prefill configs: 3 (MXFP4 MoE experts, bf16 activations), 4 (NVFP4 x NVFP4), 5 at M = 32 / 512 (Q4_K)."""
+    import numpy as np
     res = {}
     QT = gk.QuantType
 
@@ -862,12 +863,19 @@ def extra_gemm(K, gk, torch, dev, gen):
     for n, k, m in ((11008, 4096, 2048), (28672, 8192, 2048)):
         b = torch.randint(-128, 128, (n, k), generator=gen, device=dev, dtype=torch.int8)
         w = K.upload_int8(b, layout_kn=False)
+        rows = sample_rows(n, 256, seed=n)
+        b_rows = b[torch.from_numpy(rows).to(dev)].cpu().numpy().astype(np.float64)
         del b
         a8 = torch.randint(0, 256, (m, k), generator=gen, device=dev, dtype=torch.uint8)
         c32 = torch.empty((m, n), dtype=torch.int32, device=dev)
         us = timeit(lambda: K.gemm_int8(w, a8, c=c32), 10)
+        # exact integer reference on 256 sampled weight rows x every token (f64 products and sums of 8-bit integers are exact)
+        ref = a8.cpu().numpy().astype(np.float64) @ b_rows.T
+        got = c32[:, torch.from_numpy(rows).to(dev)].cpu().numpy().astype(np.float64)
         res[f"w8a8_int8_{n}x{k}_M{m}"] = {"us": us, "tops": 2.0 * m * n * k / us / 1e6, "frac_of_nominal_int8_4500": 2.0 * m * n * k / us / 1e6 / 4500.0,
-                                          "mma": "tcgen05 kind::i8, s32 accumulate (bit-exact)"}
+                                          "mma": "tcgen05 kind::i8 on CTA pairs, s32 accumulate (bit-exact)",
+                                          "parity": {"metric": "s32 results equal to the exact integer product", "rows_sampled": int(len(rows)),
+                                                     "tokens": m, "mismatches": int((ref != got).sum()), "ok": bool((ref == got).all())}}
         w.free()
         del a8, c32
     # config 4: NVFP4 weights x NVFP4 activations, bf16 out, native block-scaled MMA

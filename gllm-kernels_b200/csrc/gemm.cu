@@ -201,6 +201,16 @@ __device__ __forceinline__ __half2 scale_h2(float s) {
 // Q4_K / Q8_0: warp wg handles the 16-row chunks wg and wg + 4; its lane reads the uint4 the device layout
 // keeps for it (rows g and g + 8, bytes 8t..8t+7 of the 32-byte group) and produces, for both rows, the
 // 16-byte fp16 groups t (low nibbles / even block) and 4 + t (high nibbles / odd block).
+// Which of a chunk's row pairs (g, g + 8) a lane works on.  With g = lane / 4 the eight lanes that a 16-byte shared-memory
+// access handles together (lanes 8i .. 8i+7) would write rows g and g + 1 of the swizzled A tile, whose four 16-byte
+// groups (t ^ g) fall on the same four bank groups: a two-way conflict on every store.  Pairing rows q and q ^ 5 in such
+// an octet puts its eight stores on eight different bank groups and keeps its eight loads of the raw chunk (16-byte
+// slots 4g + t) on eight different ones as well.
+__device__ __forceinline__ int wq_row_of_lane(int lane) {
+    const int q = lane >> 3;
+    return (lane & 4) ? (q ^ 5) : q;
+}
+
 template <int FMT>
 struct Dequant;
 
@@ -208,7 +218,7 @@ template <>
 struct Dequant<FMT_Q4K> {
     float global;
     __device__ __forceinline__ void step(const uint8_t *raw, int p, uint8_t *at, int wg, int lane) {
-        const int g = lane >> 2, t = lane & 3;
+        const int g = wq_row_of_lane(lane), t = lane & 3, vl = 4 * g + t;
         // (d*sc, -dmin*m) of sub-blocks 2p and 2p+1: lane t works them out for (chunk, row) pair t of the four
         // pairs its quad shares; everyone fetches all four pairs with shuffles
         __half2 mine_lo, mine_hi;
@@ -226,7 +236,7 @@ struct Dequant<FMT_Q4K> {
 #pragma unroll
         for (int ci = 0; ci < 2; ci++) {
             const int c = wg + 4 * ci;
-            const uint4 q = *reinterpret_cast<const uint4 *>(raw + c * Q4K_CHUNK + (p * 32 + lane) * 16);
+            const uint4 q = *reinterpret_cast<const uint4 *>(raw + c * Q4K_CHUNK + (p * 32 + vl) * 16);
 #pragma unroll
             for (int h = 0; h < 2; h++) {
                 const int src = (lane & ~3) | (2 * ci + h);
@@ -247,13 +257,13 @@ template <>
 struct Dequant<FMT_Q80> {
     float global;
     __device__ __forceinline__ void step(const uint8_t *raw, int p, uint8_t *at, int wg, int lane) {
-        const int g = lane >> 2, t = lane & 3;
+        const int g = wq_row_of_lane(lane), t = lane & 3, vl = 4 * g + t;
 #pragma unroll
         for (int ci = 0; ci < 2; ci++) {
             const int c = wg + 4 * ci;
             const uint8_t *chunk = raw + c * Q80_CHUNK;
-            const uint4 q0 = *reinterpret_cast<const uint4 *>(chunk + ((2 * p) * 32 + lane) * 16);
-            const uint4 q1 = *reinterpret_cast<const uint4 *>(chunk + ((2 * p + 1) * 32 + lane) * 16);
+            const uint4 q0 = *reinterpret_cast<const uint4 *>(chunk + ((2 * p) * 32 + vl) * 16);
+            const uint4 q1 = *reinterpret_cast<const uint4 *>(chunk + ((2 * p + 1) * 32 + vl) * 16);
 #pragma unroll
             for (int h = 0; h < 2; h++) {
                 const int rr = g + 8 * h;
