@@ -1028,6 +1028,10 @@ def run_prefill_case(args):
     QT = gk.QuantType
     if args.case == "decode_q6k":
         return run_gguf_case(args, K, gk, torch, dev, gen)
+    if args.case == "decode_nvfp4":
+        return run_fp4_decode_case(args, K, gk, torch, dev, gen)
+    if args.case == "prefill_w8a8":
+        return run_w8a8_case(args, K, gk, torch, dev, gen)
     if args.case == "prefill_q4k":
         n, k, m = N_FF, D_MODEL, 512
         W = torch.randn((n, k), generator=gen, device=dev) * 0.02
@@ -1099,6 +1103,71 @@ def run_prefill_case(args):
                       "gpu_launches": args.steps * launches, "status": K.status()}), flush=True)
 
 
+def run_fp4_decode_case(args, K, gk, torch, dev, gen):
+    """NVFP4 decode product on its own: W[28672, 8192] (the gate matrix of config 5), M = 1, on the block-scaled
+    tensor core; two weight copies in rotation (2 x 132 MB > L2)."""
+    qt = gk.QuantType.nvfp4()
+    n, k = N_FF, D_MODEL
+    ws = []
+    for _ in range(2):
+        W = torch.randn((n, k), generator=gen, device=dev) * 0.02
+        wb, gw = K.quantize(qt, W)
+        ws.append(K.upload(qt, n, k, wb, None, gw))
+        del W, wb
+    x = torch.randn((1, k), generator=gen, device=dev)
+    y = torch.empty((1, n), dtype=torch.float32, device=dev)
+    for i in range(max(args.warmup, 3)):
+        K.gemv(ws[i % 2], x, y=y)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        K.gemv(ws[i % 2], x, y=y)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    wbytes = n * k // 2 + n * k // 16
+    gbs = wbytes / (ms * 1e-3) / 1e9
+    peak, kind = measured_peaks()
+    print(json.dumps({"metric": "NVFP4 decode weight GB/s", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+                      "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "data": "synthetic",
+                      "config": {"workload": args.case, "n": n, "k": k, "m": 1, "l2": "two weight copies in rotation"},
+                      "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
+                                   "traffic": None, "peak_kind": kind, "kernel": "gemv_fp4_tc_kernel (+ fd_stage_kernel)"},
+                      "gpu_launches": args.steps * 2, "status": K.status()}), flush=True)
+
+
+def run_w8a8_case(args, K, gk, torch, dev, gen):
+    """W8A8 prefill product on its own: u8 activations [2048, 4096] x s8 W[11008, 4096] -> s32, exact (tcgen05 kind::i8
+    on CTA pairs)."""
+    n, k, m = 11008, 4096, 2048
+    b = torch.randint(-128, 128, (n, k), generator=gen, device=dev, dtype=torch.int8)
+    w = K.upload_int8(b, layout_kn=False)
+    a8 = torch.randint(0, 256, (m, k), generator=gen, device=dev, dtype=torch.uint8)
+    c32 = torch.empty((m, n), dtype=torch.int32, device=dev)
+    fn = lambda: K.gemm_int8(w, a8, c=c32)
+    for _ in range(max(args.warmup, 3)):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    tops = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+    rows = torch.arange(0, m, 64, device=dev)
+    exact = bool(torch.equal(c32[rows].to(torch.float64), a8[rows].to(torch.float64) @ b.to(torch.float64).t()))
+    print(json.dumps({"metric": "W8A8 prefill GEMM TOP/s", "value": tops, "unit": "TOP/s", "n_gpus": 1, "steps": args.steps,
+                      "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "data": "synthetic",
+                      "config": {"workload": args.case, "n": n, "k": k, "m": m},
+                      "roofline": {"bound": "tensor", "achieved": tops, "peak": 4500.0, "unit": "TOP/s", "frac": tops / 4500.0,
+                                   "traffic": None, "peak_kind": "nominal dense int8", "kernel": "gemm_i8_pair_kernel (+ stage_act_u8_kernel)"},
+                      "parity": {"exact_on_sampled_rows": exact, "rows": int(rows.numel())},
+                      "gpu_launches": args.steps * 2, "status": K.status()}), flush=True)
+
+
 def run_gguf_case(args, K, gk, torch, dev, gen):
     """Q6_K decode product on its own: W[8192, 28672] (the down projection of config 5), M = 1, two weight
     copies in rotation (2 x 193 MB > L2)."""
@@ -1152,8 +1221,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying a CUDA graph")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="N > 1: how the bands of y reach every rank (peer stores fused into the GEMV, or NCCL all-gather)")
-    ap.add_argument("--case", default="decode", choices=["decode", "prefill_q4k", "prefill_nvfp4", "decode_q6k"],
-                    help="decode = the headline workload; prefill_* = one prefill kernel on its own (1 GPU)")
+    ap.add_argument("--case", default="decode", choices=["decode", "prefill_q4k", "prefill_nvfp4", "prefill_w8a8", "decode_q6k", "decode_nvfp4"],
+                    help="decode = the headline workload; prefill_* / decode_* = one kernel on its own (1 GPU)")
     args = ap.parse_args()
     if args.case != "decode":
         run_prefill_case(args)

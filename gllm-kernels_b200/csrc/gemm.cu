@@ -33,7 +33,8 @@ constexpr int WQ_SA = 4;           // operand A (dequantized weight tiles) ring:
 constexpr int WQ_MAX_SB = 12;      // operand B (activation) stages, at most
 constexpr int WQ_MAX_R = 8;        // raw super-chunk ring, at most
 constexpr int WQ_DW = 16;          // dequant warps
-constexpr int WQ_THREADS = 96 + 32 * WQ_DW;  // warp 0: raw copies, warp 1: activation copies, warp 2: MMA + TMEM, then dequant / epilogue warps
+constexpr int WQ_CTRL = 4;         // warp 0: raw copies, warp 1: activation copies, warps 2 and 3: MMA issue (row tile 0 / row tile 1), warp 2: TMEM
+constexpr int WQ_THREADS = 32 * (WQ_CTRL + WQ_DW);  // then the dequant / epilogue warps
 constexpr int WQ_SMEM_LIMIT = 232448 - 1024 - 1024;  // ring space: 227 KB less the static variables' share and the alignment slack
 
 enum { FMT_Q4K = 0, FMT_Q80 = 1, FMT_NVFP4 = 2, FMT_MXFP4 = 3 };
@@ -211,13 +212,27 @@ __device__ __forceinline__ int wq_row_of_lane(int lane) {
     return (lane & 4) ? (q ^ 5) : q;
 }
 
+// Q4_K / Q8_0: the eight 16-byte groups a lane has made (o[4 * ci + 2 * h + {0, 1}] = groups t and 4 + t of row
+// 16 * (wg + 4 * ci) + 8 * h + g) go to the swizzled A tile
+__device__ __forceinline__ void store_kq(uint8_t *at, int wg, int lane, const uint4 (&o)[8]) {
+    const int g = wq_row_of_lane(lane), t = lane & 3;
+#pragma unroll
+    for (int ci = 0; ci < 2; ci++)
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            uint8_t *rowp = at + (16 * (wg + 4 * ci) + 8 * h + g) * 128;  // (row & 7) == g
+            *reinterpret_cast<uint4 *>(rowp + ((t ^ g) << 4)) = o[4 * ci + 2 * h];
+            *reinterpret_cast<uint4 *>(rowp + (((4 + t) ^ g) << 4)) = o[4 * ci + 2 * h + 1];
+        }
+}
+
 template <int FMT>
 struct Dequant;
 
 template <>
 struct Dequant<FMT_Q4K> {
     float global;
-    __device__ __forceinline__ void step(const uint8_t *raw, int p, uint8_t *at, int wg, int lane) {
+    __device__ __forceinline__ void compute(const uint8_t *raw, int p, int wg, int lane, uint4 (&o)[8]) {
         const int g = wq_row_of_lane(lane), t = lane & 3, vl = 4 * g + t;
         // (d*sc, -dmin*m) of sub-blocks 2p and 2p+1: lane t works them out for (chunk, row) pair t of the four
         // pairs its quad shares; everyone fetches all four pairs with shuffles
@@ -242,21 +257,19 @@ struct Dequant<FMT_Q4K> {
                 const int src = (lane & ~3) | (2 * ci + h);
                 const __half2 e_lo = u32_as_h2(__shfl_sync(0xffffffffu, h2_as_u32(mine_lo), src));
                 const __half2 e_hi = u32_as_h2(__shfl_sync(0xffffffffu, h2_as_u32(mine_hi), src));
-                uint4 lo, hi;
+                uint4 &lo = o[4 * ci + 2 * h], &hi = o[4 * ci + 2 * h + 1];
                 q4k_word(h ? q.z : q.x, e_lo, e_hi, lo.x, lo.y, hi.x, hi.y);
                 q4k_word(h ? q.w : q.y, e_lo, e_hi, lo.z, lo.w, hi.z, hi.w);
-                uint8_t *rowp = at + (16 * c + 8 * h + g) * 128;  // (row & 7) == g
-                *reinterpret_cast<uint4 *>(rowp + ((t ^ g) << 4)) = lo;
-                *reinterpret_cast<uint4 *>(rowp + (((4 + t) ^ g) << 4)) = hi;
             }
         }
     }
+    __device__ __forceinline__ void store(uint8_t *at, int wg, int lane, const uint4 (&o)[8]) { store_kq(at, wg, lane, o); }
 };
 
 template <>
 struct Dequant<FMT_Q80> {
     float global;
-    __device__ __forceinline__ void step(const uint8_t *raw, int p, uint8_t *at, int wg, int lane) {
+    __device__ __forceinline__ void compute(const uint8_t *raw, int p, int wg, int lane, uint4 (&o)[8]) {
         const int g = wq_row_of_lane(lane), t = lane & 3, vl = 4 * g + t;
 #pragma unroll
         for (int ci = 0; ci < 2; ci++) {
@@ -268,17 +281,15 @@ struct Dequant<FMT_Q80> {
             for (int h = 0; h < 2; h++) {
                 const int rr = g + 8 * h;
                 const __half2 dd = u32_as_h2(*reinterpret_cast<const uint32_t *>(chunk + 4096 + (rr * 8 + 2 * p) * 2));
-                uint4 lo, hi;
+                uint4 &lo = o[4 * ci + 2 * h], &hi = o[4 * ci + 2 * h + 1];
                 q80_word(h ? q0.z : q0.x, __low2half2(dd), lo.x, lo.y);
                 q80_word(h ? q0.w : q0.y, __low2half2(dd), lo.z, lo.w);
                 q80_word(h ? q1.z : q1.x, __high2half2(dd), hi.x, hi.y);
                 q80_word(h ? q1.w : q1.y, __high2half2(dd), hi.z, hi.w);
-                uint8_t *rowp = at + (16 * c + 8 * h + g) * 128;
-                *reinterpret_cast<uint4 *>(rowp + ((t ^ g) << 4)) = lo;
-                *reinterpret_cast<uint4 *>(rowp + (((4 + t) ^ g) << 4)) = hi;
             }
         }
     }
+    __device__ __forceinline__ void store(uint8_t *at, int wg, int lane, const uint4 (&o)[8]) { store_kq(at, wg, lane, o); }
 };
 
 // FP4: the raw super-chunk is the row tile's swizzled data image (16 KB) followed by its scale atoms (512 B
@@ -286,7 +297,7 @@ struct Dequant<FMT_Q80> {
 template <int FMT>
 struct DequantFp4 {
     float global;
-    __device__ __forceinline__ void step(const uint8_t *raw, int p, uint8_t *at, int wg, int lane) {
+    __device__ __forceinline__ void compute(const uint8_t *raw, int p, int wg, int lane, uint4 (&o)[8]) {
         const int r = 32 * wg + lane;
         const uint4 v0 = *reinterpret_cast<const uint4 *>(raw + tc::sw128_offset(r, 2 * p));
         const uint4 v1 = *reinterpret_cast<const uint4 *>(raw + tc::sw128_offset(r, 2 * p + 1));
@@ -301,9 +312,14 @@ struct DequantFp4 {
             s[0] = s[1] = scale_h2(e8m0_to_f32(sf & 0xFFu));
             s[2] = s[3] = scale_h2(e8m0_to_f32(sf >> 8));
         }
+#pragma unroll
+        for (int c = 0; c < 8; c++) o[c] = fp4_word(w[c], s[c >> 1]);
+    }
+    __device__ __forceinline__ void store(uint8_t *at, int wg, int lane, const uint4 (&o)[8]) {
+        const int r = 32 * wg + lane;
         uint8_t *rowp = at + r * 128;
 #pragma unroll
-        for (int c = 0; c < 8; c++) *reinterpret_cast<uint4 *>(rowp + ((c ^ (r & 7)) << 4)) = fp4_word(w[c], s[c >> 1]);
+        for (int c = 0; c < 8; c++) *reinterpret_cast<uint4 *>(rowp + ((c ^ (r & 7)) << 4)) = o[c];
     }
 };
 template <>
@@ -316,6 +332,25 @@ struct Dequant<FMT_MXFP4> : DequantFp4<FMT_MXFP4> {};
 // second reader finds the raw bytes in L2.
 // Sequence numbers: raw super-chunk q = j * mt + i (k-block j, row tile i of the CTA), A tile a = ks * mt + i
 // (k-step ks); B stage = ks.  Each ring slot is sequence % depth with the usual phase parity.
+#ifdef GLLMK_WQ_PROF
+// Development aid (not built by default): cycles each warp of gemm_wq_kernel spends in its phases.
+__device__ unsigned long long g_wq_prof[1024 * 20 * 8];
+#define WQP_DECL unsigned long long wqp_t = 0, wqp_a[7] = {0, 0, 0, 0, 0, 0, 0}, wqp_start = clock64()
+#define WQP_T0() wqp_t = clock64()
+#define WQP_ACC(i) do { const unsigned long long n_ = clock64(); wqp_a[i] += n_ - wqp_t; wqp_t = n_; } while (0)
+#define WQP_OUT() do { if (lane == 0 && blockIdx.y * gridDim.x + blockIdx.x < 1024) { unsigned long long *o_ = g_wq_prof + ((blockIdx.y * gridDim.x + blockIdx.x) * 20 + warp) * 8; \
+    for (int i_ = 0; i_ < 7; i_++) o_[i_] = wqp_a[i_]; o_[7] = clock64() - wqp_start; } } while (0)
+// timeline of CTA 0: event e of warp w at its i-th tile (i < 32)
+__device__ unsigned long long g_wq_tl[20 * 8 * 32];
+#define WQP_TL(e, i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (i) < 32) g_wq_tl[(warp * 8 + (e)) * 32 + (i)] = clock64(); } while (0)
+#else
+#define WQP_TL(e, i)
+#define WQP_DECL
+#define WQP_T0()
+#define WQP_ACC(i)
+#define WQP_OUT()
+#endif
+
 template <int FMT, int MT>
 __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ GemmGroups G) {
     extern __shared__ uint8_t smem_raw[];
@@ -363,13 +398,13 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
         }
         for (int s = 0; s < WQ_MAX_SB; s++) {
             tc::mbar_init(fullB + 8 * s, 1);
-            tc::mbar_init(emptyB + 8 * s, 1);
+            tc::mbar_init(emptyB + 8 * s, (uint32_t)mt);  // one commit per MMA issuer
         }
         for (int s = 0; s < WQ_MAX_R; s++) {
             tc::mbar_init(rawfull + 8 * s, 1);
             tc::mbar_init(rawempty + 8 * s, WQ_DW / mt);  // the warps that read a super-chunk
         }
-        tc::mbar_init(accum, 1);
+        tc::mbar_init(accum, (uint32_t)mt);
         tc::mbar_init_fence();
     }
     if (warp == 2) tc::tmem_alloc(tc::smem_u32(&tmem_base_s), TMEM_COLS);
@@ -377,6 +412,7 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
     __syncthreads();
     tc::fence_after_sync();
     const uint32_t tmem_d = tmem_base_s;
+    WQP_DECL;
 
     if (warp == 0) {
         // ---------------- raw weight super-chunks: one thread, bulk copies ----------------
@@ -385,12 +421,14 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
             for (int jl = 0; jl < njb; jl++) {
                 const int jb = jb0 + jl;
                 for (int ti = 0; ti < mt; ti++) {
+                    WQP_T0();
                     if (round > 0 && !tc::mbar_wait(rawempty + 8 * slot, (uint32_t)((round - 1) & 1), abort_flag)) {
                         abort_s = 1;
                         atomicExch(p.status, 10);
                         jl = njb;
                         break;
                     }
+                    WQP_ACC(0);
                     const int tile = tile0 + ti;
                     const uint32_t dst = smem_s + raw_off + (uint32_t)(slot * RAW);
                     tc::mbar_expect_tx(rawfull + 8 * slot, RAW);
@@ -414,11 +452,13 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
             const uint32_t hbytes[2] = {(uint32_t)(p.ntok > 128 ? WQ_TILE : bstage), (uint32_t)(bstage - WQ_TILE)};
             int slot = 0, round = 0;
             for (int ks = 0; ks < nks; ks++) {
+                WQP_T0();
                 if (round > 0 && !tc::mbar_wait(emptyB + 8 * slot, (uint32_t)((round - 1) & 1), abort_flag)) {
                     abort_s = 1;
                     atomicExch(p.status, 11);
                     break;
                 }
+                WQP_ACC(0);
                 const uint32_t dst = smem_s + b_off + (uint32_t)(slot * bstage);
                 tc::mbar_expect_tx(fullB + 8 * slot, (uint32_t)bstage);
                 for (int h = 0; h < halves; h++)
@@ -426,39 +466,43 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
                 if (++slot == p.sb) slot = 0, round++;
             }
         }
-    } else if (warp == 2) {
-        // ---------------- MMA issue: one thread ----------------
-        if (lane == 0) {
+    } else if (warp < WQ_CTRL) {
+        // ---------------- MMA issue: one thread per row tile ----------------
+        // Every step of this role (barrier probe, fence, MMA, commit) has a long issue latency, ~0.9 k cycles per A tile
+        // in all, against 0.25 - 0.5 k cycles of tensor-pipe time: with two row tiles, two threads in two warps — each with
+        // its own accumulator and its own A slots (tile a = 2 * ks + i lives in slot a % 4) — keep the pipe fed.
+        const int i = warp - 2;
+        if (lane == 0 && i < mt) {
             const uint32_t idesc = tc::idesc_f16(WQ_BM, p.ntok, 0, 0);  // fp16 x fp16 -> f32
             bool ok = true;
             int sb = 0, bround = 0;
             for (int ks = 0; ks < nks && ok; ks++) {
-                ok = tc::mbar_wait(fullB + 8 * sb, (uint32_t)(bround & 1), abort_flag);
+                WQP_T0();
                 const uint64_t bd = tc::smem_desc_sw128(smem_s + b_off + (uint32_t)(sb * bstage));
-                for (int i = 0; i < mt && ok; i++) {
-                    const int a = ks * mt + i, sa = a % WQ_SA;
-                    ok = tc::mbar_wait(fullA + 8 * sa, (uint32_t)((a / WQ_SA) & 1), abort_flag);
-                    if (!ok) break;
-                    tc::fence_after_sync();
-                    const uint64_t ad = tc::smem_desc_sw128(smem_s + a_off + sa * WQ_TILE);
-#pragma unroll
-                    for (int k4 = 0; k4 < 4; k4++)
-                        tc::mma_f16(tmem_d + 256u * (uint32_t)i, ad + 2 * k4, bd + 2 * k4, idesc, (uint32_t)((ks | k4) != 0));
-                    tc::mma_commit(emptyA + 8 * sa);  // the A tile is free when these MMAs have read it
-                }
+                const int a = ks * mt + i, sa = a % WQ_SA;
+                // probes that do not suspend the thread: its reaction time is on the critical path of every tile
+                ok = tc::mbar_spin(fullB + 8 * sb, (uint32_t)(bround & 1), abort_flag) &&
+                     tc::mbar_spin(fullA + 8 * sa, (uint32_t)((a / WQ_SA) & 1), abort_flag);
+                WQP_ACC(0);
                 if (!ok) {
                     abort_s = 1;
                     atomicExch(p.status, 12);
                     break;
                 }
-                tc::mma_commit(emptyB + 8 * sb);
+                tc::fence_after_sync();
+                const uint64_t ad = tc::smem_desc_sw128(smem_s + a_off + sa * WQ_TILE);
+#pragma unroll
+                for (int k4 = 0; k4 < 4; k4++)
+                    tc::mma_f16(tmem_d + 256u * (uint32_t)i, ad + 2 * k4, bd + 2 * k4, idesc, (uint32_t)((ks | k4) != 0));
+                tc::mma_commit(emptyA + 8 * sa);  // the A tile is free when these MMAs have read it
+                tc::mma_commit(emptyB + 8 * sb);  // the stage, when both issuers' MMAs have
                 if (++sb == p.sb) sb = 0, bround++;
             }
             if (ok) tc::mma_commit(accum);
         }
     } else {
         // ---------------- dequant warps, then epilogue ----------------
-        const int dw = warp - 3, grp = dw >> 2, wg = dw & 3;
+        const int dw = warp - WQ_CTRL, grp = dw >> 2, wg = dw & 3;
         Dequant<FMT> dq;
         dq.global = G.gs[grp_id];
         bool ok = true;
@@ -469,30 +513,49 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
         const int qstep = (MT == 2 && mt == 2) ? 2 : 1;  // raw sequence numbers between this group's super-chunks
         int rslot = (MT == 2 && mt == 2) ? (grp & 1) : 0, rround = 0;
         if (rslot >= p.r) rslot -= p.r, rround++;
+        // A tile = conversion into registers, then stores.  The group's first warp does the waiting — for this tile's A
+        // slot and for the raw super-chunk of the NEXT tile — between the two, so that the MMAs still reading the slot run
+        // under the conversion; the other three warps sleep on a hardware barrier.  The probes do not suspend the
+        // thread (a suspended thread wakes up late, and the group's reaction time is on the critical path).
+        if (wg == 0 && grp < na && !tc::mbar_spin(rawfull + 8 * rslot, (uint32_t)(rround & 1), abort_flag)) abort_s = 1;
+        tc::named_bar_sync(1 + grp, 128);
+        ok = !*abort_flag;
         for (int a = grp, it = 0; a < na && ok; a += 4, it++) {
             const int ks = (MT == 2 && mt == 2) ? (a >> 1) : a;
             const int pp = ks & 3;
-            // the group's first warp waits for the raw super-chunk and for the group's A slot; the other three
-            // sleep on a hardware barrier instead of polling (polling warps take issue slots from working ones)
-            if (wg == 0) {
-                const bool ready = tc::mbar_wait(rawfull + 8 * rslot, (uint32_t)(rround & 1), abort_flag) &&
-                                   (it == 0 || tc::mbar_wait(emptyA + 8 * grp, (uint32_t)((it - 1) & 1), abort_flag));
-                if (!ready) abort_s = 1;
-            }
-            tc::named_bar_sync(1 + grp, 128);
-            ok = !*abort_flag;
-            if (!ok) break;
-            dq.step(smem + raw_off + rslot * RAW, pp, smem + a_off + grp * WQ_TILE, wg, lane);
-            tc::fence_proxy_async();  // every writer makes its own stores visible to the tensor core's proxy
-            __syncwarp();
-            if (lane == 0) tc::mbar_arrive(fullA + 8 * grp);
+            uint4 o[8];
+            WQP_T0();
+            dq.compute(smem + raw_off + rslot * RAW, pp, wg, lane, o);
+            // the values are needed in registers HERE: without this the compiler moves the arithmetic below the waits
+#pragma unroll
+            for (int i = 0; i < 8; i++) asm volatile("" ::"r"(o[i].x), "r"(o[i].y), "r"(o[i].z), "r"(o[i].w));
             // last quarter this warp reads of the super-chunk: hand the slot back and move to the next one
             const bool last = !(MT == 2 && mt == 2) || pp >= 2;
             if (last) {
+                __syncwarp();
                 if (lane == 0) tc::mbar_arrive(rawempty + 8 * rslot);
                 rslot += qstep;
                 if (rslot >= p.r) rslot -= p.r, rround++;
             }
+            WQP_ACC(0);
+            if (wg == 0) {
+                bool ready = (it == 0 || tc::mbar_spin(emptyA + 8 * grp, (uint32_t)((it - 1) & 1), abort_flag));
+                WQP_ACC(1);
+                ready = ready && (a + 4 >= na || !last || tc::mbar_spin(rawfull + 8 * rslot, (uint32_t)(rround & 1), abort_flag));
+                if (!ready) abort_s = 1;
+                WQP_ACC(2);
+            }
+            tc::named_bar_sync(1 + grp, 128);
+            WQP_ACC(3);
+            ok = !*abort_flag;
+            if (!ok) break;
+            dq.store(smem + a_off + grp * WQ_TILE, wg, lane, o);
+            WQP_ACC(4);
+            tc::fence_proxy_async();  // every writer makes its own stores visible to the tensor core's proxy
+            WQP_ACC(5);
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(fullA + 8 * grp);
+            WQP_ACC(6);
         }
         if (!ok && !abort_s) {
             abort_s = 1;
@@ -569,6 +632,7 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
             atomicExch(p.status, 14);
         }
     }
+    WQP_OUT();
     tc::fence_before_sync();
     __syncthreads();
     if (warp == 2) tc::tmem_dealloc(tmem_d, TMEM_COLS);
@@ -638,11 +702,12 @@ static int32_t gemm_groups_chunk(Ctx *c, const Weight *const *ws, int ng, const 
     // a fixed prologue / epilogue worth ~16 steps).
     int mt = 1;
     if (row_tiles % 2 == 0) {
-        const double step2 = ntok > 128 ? 0.8 : 0.9;
+        const double step2 = ntok > 128 ? 0.68 : 0.62;  // measured: a pair step costs 1.36 / 1.24 single steps
         const int nks = 4 * p.nsc;
         const auto waves = [&](int ctas) { return (double)((ctas + c->sm_count - 1) / c->sm_count); };
         const double t1 = waves(ntiles * row_tiles) * (nks + 16.0), t2 = waves(ntiles * row_tiles / 2) * (2.0 * nks * step2 + 16.0);
         if (t2 < t1) mt = 2;
+        if (c->gemm_row_tiles == 1 || c->gemm_row_tiles == 2) mt = (int)c->gemm_row_tiles;
     }
     // Shared-memory plan: four A tiles; three B stages (activation tiles come from L2: ~1 us of latency against
     // 0.2 - 0.5 us per k-step); everything else goes to the raw ring, because the weight stream comes from HBM and
@@ -655,6 +720,7 @@ static int32_t gemm_groups_chunk(Ctx *c, const Weight *const *ws, int ng, const 
         if (p.r < mt + 1) mt = 1;
     }
     if (p.r > WQ_MAX_R) p.r = WQ_MAX_R;
+    if (c->gemm_raw_slots >= mt + 1 && c->gemm_raw_slots < p.r) p.r = (int)c->gemm_raw_slots;
     if (p.r < mt + 1) return fail(c, GLLMK_STATUS_RUNTIME_ERROR, "gemm: shared-memory plan does not fit");
     // what the raw ring cannot use goes back to B stages
     const int more_sb = (WQ_SMEM_LIMIT - WQ_SA * WQ_TILE - p.r * raw) / bstage;
@@ -671,10 +737,9 @@ static int32_t gemm_groups_chunk(Ctx *c, const Weight *const *ws, int ng, const 
     dim3 grid((unsigned)ntiles, (unsigned)((row_tiles + mt - 1) / mt));
     // Tail split: with more tiles than SMs the last, partly filled wave of tiles is cut along k so that its work
     // spreads over all SMs (224 tiles on 148 SMs: 148 whole tiles, then 76 tiles in thirds = 228 units in two short
-    // waves — 1.67 tile times instead of 2).  Only when the weights are one group (a plain GEMM) and a unit keeps at
-    // least four k-blocks.
+    // waves — 1.67 tile times instead of 2).  Only when a unit keeps at least four k-blocks.
     p.split_s = 1;
-    if (ng == 1 && c->gemm_tail_split != 1) {
+    if (c->gemm_tail_split != 1) {
         const int tiles = (int)(grid.x * grid.y), sms = c->sm_count;
         const int full = tiles / sms * sms, tail = tiles - full;
         if (full > 0 && tail > 0) {
@@ -761,3 +826,12 @@ int32_t gemm_launch(Ctx *c, const Weight *w, const void *a, int a_bf16, int64_t 
 }
 
 }  // namespace gllmk
+
+#ifdef GLLMK_WQ_PROF
+extern "C" __attribute__((visibility("default"))) int gllmk_debug_wq_tl(unsigned long long *out) {
+    return (int)cudaMemcpyFromSymbol(out, gllmk::g_wq_tl, sizeof(gllmk::g_wq_tl));
+}
+extern "C" __attribute__((visibility("default"))) int gllmk_debug_wq_prof(unsigned long long *out) {
+    return (int)cudaMemcpyFromSymbol(out, gllmk::g_wq_prof, sizeof(gllmk::g_wq_prof));
+}
+#endif

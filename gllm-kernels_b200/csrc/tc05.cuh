@@ -46,6 +46,25 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     return false;
 }
 
+// The same with back-to-back probes that do not suspend the thread: for a role whose warp has nothing else to do and
+// whose reaction time is on the critical path.
+__device__ __forceinline__ bool mbar_spin(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+#pragma unroll 1
+    for (uint32_t it = 0; it < (1u << 24); it++) {
+        uint32_t ok;
+        asm volatile(
+            "{\n.reg .pred p;\n"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        if ((it & 255u) == 255u && *abort_flag) return false;
+    }
+    return false;
+}
+
 // named barrier among `nthreads` threads of the CTA (ids 1..15; 0 is __syncthreads)
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) { asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(nthreads) : "memory"); }
 

@@ -160,7 +160,8 @@ GLLMK_API int32_t gllmk_ctx_status(gllmk_ctx ctx, int32_t *device_status);
  * accumulators, 3 CTA pairs with two 128-token accumulators), "gemm_i8_pair" (W8A8 GEMM with m > 128 on the CTA-pair kernel: 0 never, 1 (default) when the estimate favours it, 2 always),
  * "host_batch_graph" (gllmk_matmul_host_batch replays a captured graph for a repeated
  * argument list: 1 default, 0 never), "gemm_tail_split" (prefill GEMM, last partial wave of tiles cut along k:
- * 0 automatic, 1 never, n into n), "peer_wait_spins" (how many times a wait on another GPU's flag probes it
+ * 0 automatic, 1 never, n into n), "gemm_row_tiles" (prefill GEMM, 128-row weight tiles per CTA: 0 estimated, 1, 2),
+ * "gemm_raw_slots" (prefill GEMM, depth of the raw weight ring: 0 = what the shared-memory plan gives), "peer_wait_spins" (how many times a wait on another GPU's flag probes it
  * before it gives up with status 31; default 2^22, about a second), "inject_give_up" (testing aid, host side
  * only: leaves the context as a kernel that gave up a wait with that status code would — word set, arrival
  * counters dirty — without making any kernel wait). */
