@@ -50,7 +50,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 // whose reaction time is on the critical path.
 __device__ __forceinline__ bool mbar_spin(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
 #pragma unroll 1
-    for (uint32_t it = 0; it < (1u << 24); it++) {
+    for (uint32_t it = 0; it < (1u << 22); it++) {
         uint32_t ok;
         asm volatile(
             "{\n.reg .pred p;\n"

@@ -338,6 +338,36 @@ def test_gemm_grouped_matches_per_expert_products(gk, K, oracle, fmt, counts, a_
         w.free()
 
 
+@pytest.mark.parametrize("fmt,counts,split", [("mxfp4", [150, 97, 160], 0), ("q4k", [60, 1, 64, 33], 3), ("q8_0", [128, 128], 2)])
+def test_gemm_grouped_tail_tiles_split_along_k(gk, K, oracle, fmt, counts, split):
+    """A grouped launch with more tiles than SMs: the last wave's tiles are cut along k exactly as in a plain product (every
+    unit finds its expert's weights and token tile through the same tables).  Against the unsplit launch and the oracle."""
+    import torch
+    n, k = 12800, 1280  # 100 row tiles per expert
+    experts = [quantized(oracle, gk, fmt, n, k, 300 + e) for e in range(len(counts))]
+    ws = [K.upload(qt, n, k, b, s, g) for (qt, b, s, g, _) in experts]
+    offs = np.concatenate([[0], np.cumsum(counts)]).astype(np.int64)
+    xd = torch.from_numpy(np.random.default_rng(78).standard_normal((int(offs[-1]), k)).astype(np.float32)).cuda().to(torch.bfloat16)
+    x = xd.to(torch.float32).cpu().numpy()
+    K.set("gemm_tail_split", 1)
+    try:
+        y_whole = K.gemm_grouped(ws, xd, offs).cpu().numpy()
+        K.set("gemm_tail_split", split)
+        y_split = K.gemm_grouped(ws, xd, offs).cpu().numpy()
+        y_again = K.gemm_grouped(ws, xd, offs).cpu().numpy()
+    finally:
+        K.set("gemm_tail_split", 0)
+    assert K.status() == 0
+    assert np.array_equal(y_split, y_again)
+    rows = np.random.default_rng(9).choice(n, size=256, replace=False)
+    for e, (_, _, _, _, wd) in enumerate(experts):
+        ref = oracle.gemm_f32_nt(x[offs[e]:offs[e + 1]], wd[rows])
+        assert oracle.rel_err(y_split[offs[e]:offs[e + 1]][:, rows], ref) <= TOL, (fmt, e)
+        assert oracle.rel_err(y_split[offs[e]:offs[e + 1]], y_whole[offs[e]:offs[e + 1]]) <= 1e-5, (fmt, e)
+    for w in ws:
+        w.free()
+
+
 def test_gemm_grouped_rejects_mismatched_weights(gk, K, oracle):
     import torch
     qa, ba, _, _, _ = quantized(oracle, gk, "q8_0", 64, 64, 1)
