@@ -697,16 +697,28 @@ static int32_t gemm_groups_chunk(Ctx *c, const Weight *const *ws, int ng, const 
     if (ntiles == 0) return GLLMK_STATUS_OK;
     const int row_tiles = (int)(w->n_pad / WQ_BM);
     const int bstage = ntok * 128;
-    // Row tiles per CTA: two share one activation stage (less shared-memory fill traffic per flop, fixed costs
-    // paid once), but halve the CTA count.  Estimated time = waves x (tile steps per CTA x relative step cost +
-    // a fixed prologue / epilogue worth ~16 steps).
+    // Row tiles per CTA and how the last wave is cut along k, chosen together.  Two row tiles share one activation stage
+    // (less shared-memory fill traffic per flop, two issuing threads, fixed costs paid once) but halve the CTA count; a
+    // last — or only — wave that fills a fraction of the SMs is cut along k into units (tail split, below).  Estimated
+    // time, in k-steps of a single tile: whole waves + the tail, times (k-steps per CTA x relative step cost + a fixed
+    // prologue / epilogue worth ~16 steps).
+    const int sms = c->sm_count;
+    const auto estimate = [&](int m_t, int *split) -> double {
+        const double step = m_t == 2 ? 2.0 * (ntok > 128 ? 0.68 : 0.62) : 1.0;  // measured: a pair step costs 1.36 / 1.24 single steps
+        const int tiles = ntiles * ((row_tiles + m_t - 1) / m_t), full = tiles / sms, tail = tiles - full * sms;
+        double tail_t = tail > 0 ? 1.0 : 0.0;
+        *split = 1;
+        if (tail > 0 && c->gemm_tail_split != 1)
+            for (int sp = 2; sp <= 8 && p.nsc / sp >= 4; sp++) {
+                const double t = (double)((tail * sp + sms - 1) / sms) / sp + 0.05 * sp;  // + fill / drain and the partial traffic
+                if (t < tail_t) tail_t = t, *split = sp;
+            }
+        return (full + tail_t) * (4.0 * p.nsc * step + 16.0);
+    };
     int mt = 1;
     if (row_tiles % 2 == 0) {
-        const double step2 = ntok > 128 ? 0.68 : 0.62;  // measured: a pair step costs 1.36 / 1.24 single steps
-        const int nks = 4 * p.nsc;
-        const auto waves = [&](int ctas) { return (double)((ctas + c->sm_count - 1) / c->sm_count); };
-        const double t1 = waves(ntiles * row_tiles) * (nks + 16.0), t2 = waves(ntiles * row_tiles / 2) * (2.0 * nks * step2 + 16.0);
-        if (t2 < t1) mt = 2;
+        int s1, s2;
+        if (estimate(2, &s2) < estimate(1, &s1)) mt = 2;
         if (c->gemm_row_tiles == 1 || c->gemm_row_tiles == 2) mt = (int)c->gemm_row_tiles;
     }
     // Shared-memory plan: four A tiles; three B stages (activation tiles come from L2: ~1 us of latency against
@@ -735,33 +747,28 @@ static int32_t gemm_groups_chunk(Ctx *c, const Weight *const *ws, int ng, const 
     stage_act_kernel<<<dim3((unsigned)nks, (unsigned)nimg), 256, 0, s>>>(a, a_bf16, lda, w->k, static_cast<uint8_t *>(c->act), imgs, a_up);
     GK_CUDA(c, cudaGetLastError());
     dim3 grid((unsigned)ntiles, (unsigned)((row_tiles + mt - 1) / mt));
-    // Tail split: with more tiles than SMs the last, partly filled wave of tiles is cut along k so that its work
-    // spreads over all SMs (224 tiles on 148 SMs: 148 whole tiles, then 76 tiles in thirds = 228 units in two short
-    // waves — 1.67 tile times instead of 2).  Only when a unit keeps at least four k-blocks.
+    // Tail split: the last, partly filled wave of tiles — the only one, when there are fewer tiles than SMs — is cut along
+    // k so that its work spreads over all SMs (224 tiles on 148 SMs: 148 whole tiles, then 76 tiles in thirds = 228 units
+    // in two short waves — 1.67 tile times instead of 2; 64 two-tile CTAs: 128 half units).  Only when a unit keeps at
+    // least four k-blocks.
     p.split_s = 1;
     if (c->gemm_tail_split != 1) {
-        const int tiles = (int)(grid.x * grid.y), sms = c->sm_count;
+        const int tiles = (int)(grid.x * grid.y);
         const int full = tiles / sms * sms, tail = tiles - full;
-        if (full > 0 && tail > 0) {
-            int best_s = 1;
-            double best = 1.0;  // tail time in tile times, unsplit
-            for (int sp = 2; sp <= 8 && p.nsc / sp >= 4; sp++) {
-                const double t = (double)((tail * sp + sms - 1) / sms) / sp + 0.05 * sp;  // + fill / drain and the partial traffic
-                if (t < best) best = t, best_s = sp;
-            }
-            if (c->gemm_tail_split > 1 && p.nsc / (int)c->gemm_tail_split >= 1) best_s = (int)c->gemm_tail_split;
-            if (best_s > 1) {
-                const size_t unit_floats = (size_t)mt * ntok * WQ_BM;
-                rc = ensure_red(c, (size_t)tail * best_s * unit_floats * sizeof(float));
-                if (!rc) rc = ensure_cnt(c, (size_t)(tail + 1) * sizeof(int));
-                if (rc) return rc;
-                p.split_s = best_s;
-                p.split_f = full;
-                p.ntt = (int)grid.x;
-                p.partial = static_cast<float *>(c->red);
-                p.tail_cnt = static_cast<int *>(c->cnt);
-                grid = dim3((unsigned)(full + tail * best_s), 1u);
-            }
+        int best_s = 1;
+        estimate(mt, &best_s);
+        if (c->gemm_tail_split > 1 && p.nsc / (int)c->gemm_tail_split >= 1) best_s = (int)c->gemm_tail_split;
+        if (tail > 0 && best_s > 1) {
+            const size_t unit_floats = (size_t)mt * ntok * WQ_BM;
+            rc = ensure_red(c, (size_t)tail * best_s * unit_floats * sizeof(float));
+            if (!rc) rc = ensure_cnt(c, (size_t)(tail + 1) * sizeof(int));
+            if (rc) return rc;
+            p.split_s = best_s;
+            p.split_f = full;
+            p.ntt = (int)grid.x;
+            p.partial = static_cast<float *>(c->red);
+            p.tail_cnt = static_cast<int *>(c->cnt);
+            grid = dim3((unsigned)(full + tail * best_s), 1u);
         }
     }
     switch (fmt) {
