@@ -508,7 +508,7 @@ def multi_gpu_parity(args, K, gk, torch, dev, weights, ex, gbufs, x_model, M, wo
 
 def sharded_prefill_extra(K, gk, torch, dist, dev, world, rank):
     """The sharded gate matrix W[28672, 8192] (Q4_K) at M = 32 and M = 512: every rank multiplies its band of rows
-    (decode passes for 32 f32 tokens, the tensor-core kernel with bf16 output for 512) and ONE NCCL all-gather puts the
+    (the tensor-core kernel, bf16 output) and ONE NCCL all-gather puts the
     bands side by side.  Device time (CUDA events), max over ranks; parity on rank 0 against the oracle on rows sampled
     from every rank's band of the gathered result."""
     import numpy as np
@@ -814,7 +814,7 @@ def extra_gemm(K, gk, torch, dev, gen):
             us = timeit(lambda: K.gemm(w, a, y=y), 5)
             tc = m > K.GEMM_GEMV_MAX_M
             res[f"cfg5_q4k_{n}x{k}_M{m}"] = {"us": us, "tflops": 2.0 * m * n * k / us / 1e6, "weight_GBps": w.ref_bytes / us / 1e3,
-                                            "staging": "fp16 x fp16 -> f32 (kind::f16)" if tc else "passes of the decode kernel",
+                                            "staging": "fp16 x fp16 -> f32 (kind::f16)" if tc else "a pass of the decode kernel",
                                             "parity": sampled_parity(O, O.Q4K, packed[0], n, k, rows, a.cpu().numpy(), y,
                                                                      bar=1e-2 if tc else 2e-3, sequential=not tc)}
             if k == 8192:

@@ -78,7 +78,7 @@ class GpuKernels:
     """B200 implementation of the reference's quantized operators (one context = one device)."""
 
     GEMV_MAX_M = 16
-    GEMM_GEMV_MAX_M = 48  # f32 products up to this many tokens run as passes of the decode kernel
+    GEMM_GEMV_MAX_M = 16  # f32 products up to this many tokens run as a pass of the decode kernel
 
     def __init__(self, device: int = 0):
         h = C.c_void_p()

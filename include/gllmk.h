@@ -336,9 +336,10 @@ GLLMK_API int32_t gllmk_exchange_wait(gllmk_ctx ctx, void *flags_local, int32_t 
  * a_dtype / y_dtype: GLLMK_DTYPE_F32 or GLLMK_DTYPE_BF16.  Weights and activations are staged in fp16
  * (activations saturate at +-65504) and accumulated in f32: results within 1e-2 of the reference's f32
  * evaluation.  a and its rows must be 16-byte aligned.  With f32 in and out and
- * m <= GLLMK_GEMM_GEMV_MAX_M the call runs as passes of the decode kernel (gllmk_gemv), which is faster
- * there and meets its tighter bound. */
-#define GLLMK_GEMM_GEMV_MAX_M 48
+ * m <= GLLMK_GEMM_GEMV_MAX_M the call is one pass of the decode kernel (gllmk_gemv), which is faster
+ * there and meets its tighter bound (from 17 tokens on the tensor-core kernel is the faster one:
+ * W[28672, 8192] Q4_K at m = 32: 80 us against 113 us as two decode passes). */
+#define GLLMK_GEMM_GEMV_MAX_M 16
 GLLMK_API int32_t gllmk_gemm(gllmk_ctx ctx, gllmk_weight w, const void *a_dev, int32_t a_dtype, int64_t lda, int32_t m,
                              void *y_dev, int32_t y_dtype, int64_t ldy, void *stream);
 

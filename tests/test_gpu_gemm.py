@@ -70,16 +70,23 @@ def test_gemm_ragged_shapes(gk, K, oracle, fmt, n, k, m):
 
 @pytest.mark.parametrize("fmt,n,k,m", [("q4k", 100, 256, 17), ("q8_0", 128, 1024, 32), ("q4k", 260, 768, 48), ("q8_0", 129, 192, 33)])
 def test_gemm_few_tokens_tensor_core_path(gk, K, oracle, fmt, n, k, m):
-    # with f32 in and out a few dozen tokens run as passes of the decode kernel; bf16 activations keep the
+    # with f32 in and out up to 16 tokens run as a pass of the decode kernel; bf16 activations keep the
     # call on the tcgen05 kernel with a narrow MMA N (32 / 64)
     assert run_case(gk, K, oracle, fmt, n, k, m, seed=n + m + 1, a_bf16=True) <= TOL
 
 
-@pytest.mark.parametrize("m", [17, 32, 47, 48])
-def test_gemm_few_tokens_decode_passes(gk, K, oracle, m):
-    # f32, m <= 48: ceil(m / 16) passes of the decode kernel, tighter bound
+@pytest.mark.parametrize("m", [1, 7, 16])
+def test_gemm_few_tokens_decode_pass(gk, K, oracle, m):
+    # f32, m <= 16: one pass of the decode kernel, tighter bound
     assert run_case(gk, K, oracle, "q4k", 200, 512, m, seed=m) <= 2e-3
     assert run_case(gk, K, oracle, "q8_0", 200, 160, m, seed=m + 100) <= 2e-3
+
+
+@pytest.mark.parametrize("m", [17, 32, 47, 48])
+def test_gemm_few_tokens_f32_tensor_core(gk, K, oracle, m):
+    # f32, 17 tokens and more: the tcgen05 kernel with a narrow MMA N (faster than two or three decode passes)
+    assert run_case(gk, K, oracle, "q4k", 200, 512, m, seed=m) <= TOL
+    assert run_case(gk, K, oracle, "q8_0", 200, 160, m, seed=m + 100) <= TOL
 
 
 def test_gemm_bf16_in_bf16_out(gk, K, oracle):
@@ -277,8 +284,8 @@ def test_fp4_weights_decode_kernel(gk, K, oracle, fmt, n, k):
     ref = oracle.gemm_f32_nt(x, wd)
     assert oracle.rel_err(K.matmul_host(w, x), ref) <= 2e-3
     assert oracle.rel_err(K.matmul_host(w, np.ascontiguousarray(x.T), ref_layout=True), ref.T) <= 2e-3
-    # 33 f32 tokens through gllmk_gemm: three passes of the decode kernel
-    x = np.random.default_rng(98).standard_normal((33, k)).astype(np.float32)
+    # 16 f32 tokens through gllmk_gemm: one pass of the decode kernel
+    x = np.random.default_rng(98).standard_normal((16, k)).astype(np.float32)
     assert oracle.rel_err(K.gemm(w, torch.from_numpy(x).cuda()).cpu().numpy(), oracle.gemm_f32_nt(x, wd)) <= 2e-3
     assert K.status() == 0
     w.free()
