@@ -113,6 +113,7 @@ struct Ctx {
     int64_t gemm_i8_pair = 1;   // W8A8 GEMM with m > 128 on CTA pairs (cta_group::2, persistent, two accumulators): 0 never,
                                 // 1 when the estimate favours it, 2 always
     int64_t gemm_raw_slots = 0;  // weight-only GEMM: raw super-chunk ring depth (0 = chosen by the shared-memory plan)
+    int64_t gemm_pdl = 1;        // weight-only GEMM launched programmatically behind its activation staging kernel
     int64_t gemm_row_tiles = 0;  // weight-only GEMM: row tiles per CTA (0 = estimated, 1, 2)
     int64_t peer_wait_spins = (int64_t)1 << 22;  // probes of another rank's flag before a wait gives up (status 31 / 32)
 };

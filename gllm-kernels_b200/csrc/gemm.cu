@@ -90,6 +90,10 @@ __device__ __forceinline__ float swiglu_f32(float g, float u) { return (g / (1.0
 __global__ void __launch_bounds__(256) stage_act_kernel(const void *__restrict__ a, int a_bf16, int64_t lda, int64_t k_valid,
                                                         uint8_t *__restrict__ xt, const __grid_constant__ ImgTiles imgs,
                                                         const void *__restrict__ a_up) {
+    // The GEMM behind this launch may start now (programmatic dependent launch): its CTAs take the SMs this grid leaves,
+    // allocate tensor memory and stream raw weights; the one thread that reads these tile images orders itself after
+    // this grid with griddepcontrol.wait.
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     const int ks = blockIdx.x, tile = blockIdx.y;
     const int64_t img_tok0 = imgs.tok0[tile];
     const int img_cnt = imgs.cnt[tile];
@@ -451,6 +455,7 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
             const int halves = (p.ntok + 127) / 128, img0 = G.tile_img[bx];
             const uint32_t hbytes[2] = {(uint32_t)(p.ntok > 128 ? WQ_TILE : bstage), (uint32_t)(bstage - WQ_TILE)};
             int slot = 0, round = 0;
+            asm volatile("griddepcontrol.wait;\n" ::: "memory");  // the staging kernel's tile images are complete from here on
             for (int ks = 0; ks < nks; ks++) {
                 WQP_T0();
                 if (round > 0 && !tc::mbar_wait(emptyB + 8 * slot, (uint32_t)((round - 1) & 1), abort_flag)) {
@@ -647,8 +652,18 @@ static int32_t launch_wq(Ctx *c, const GemmParams &p, const GemmGroups &G, dim3 
         GK_CUDA(c, cudaFuncSetAttribute(gemm_wq_kernel<FMT, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, WQ_SMEM_LIMIT + 1024));
         attr_set[dev_slot] = true;
     }
-    gemm_wq_kernel<FMT, MT><<<grid, WQ_THREADS, smem, s>>>(p, G);
-    GK_CUDA(c, cudaGetLastError());
+    // launched programmatically behind the staging kernel (which everything earlier in the stream precedes)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(WQ_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = c->gemm_pdl ? 1 : 0;
+    GK_CUDA(c, cudaLaunchKernelEx(&cfg, gemm_wq_kernel<FMT, MT>, p, G));
     return GLLMK_STATUS_OK;
 }
 template <int FMT>
