@@ -1169,8 +1169,8 @@ def run_w8a8_case(args, K, gk, torch, dev, gen):
 
 
 def run_gguf_case(args, K, gk, torch, dev, gen):
-    """Q6_K decode product on its own: W[8192, 28672] (the down projection of config 5), M = 1, two weight
-    copies in rotation (2 x 193 MB > L2)."""
+    """Q6_K decode product on its own: W[8192, 28672] (the down projection of config 5), M = --m tokens (1: the dp2a kernel,
+    2 .. 16: the mma.sync kernel), two weight copies in rotation (2 x 193 MB > L2)."""
     qt = gk.QuantType.q6k()
     n, k = D_MODEL, N_FF
     nblk = n * (k // 256)
@@ -1181,8 +1181,9 @@ def run_gguf_case(args, K, gk, torch, dev, gen):
         b[:, 208:210] = d.view(torch.uint8)
         ws.append(K.upload(qt, n, k, b.reshape(-1)))
         del b, d
-    x = torch.randn((1, k), generator=gen, device=dev)
-    y = torch.empty((1, n), dtype=torch.float32, device=dev)
+    m = max(1, min(int(args.m), 16))
+    x = torch.randn((m, k), generator=gen, device=dev)
+    y = torch.empty((m, n), dtype=torch.float32, device=dev)
     for i in range(max(args.warmup, 3)):
         K.gemv(ws[i % 2], x, y=y)
     torch.cuda.synchronize()
@@ -1198,9 +1199,9 @@ def run_gguf_case(args, K, gk, torch, dev, gen):
     peak, kind = measured_peaks()
     print(json.dumps({"metric": "Q6_K decode weight GB/s", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
                       "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "data": "synthetic",
-                      "config": {"workload": args.case, "n": n, "k": k, "m": 1, "l2": "two weight copies in rotation"},
+                      "config": {"workload": args.case, "n": n, "k": k, "m": m, "l2": "two weight copies in rotation"},
                       "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
-                                   "traffic": None, "peak_kind": kind, "kernel": "raw_gemv_kernel<Q6_K, 1> (+ act_quant_kernel)"},
+                                   "traffic": None, "peak_kind": kind, "kernel": ("raw_gemv_kernel<Q6_K, 1>" if m == 1 else "q6k_gemv_mma_kernel") + " (+ act_quant_kernel)"},
                       "gpu_launches": args.steps * 2, "status": K.status()}), flush=True)
 
 

@@ -278,6 +278,7 @@ int32_t gllmk_ctx_set(gllmk_ctx ctx, const char *key, int64_t value) {
     else if (!strcmp(key, "gemm_tail_split")) c->gemm_tail_split = value;
     else if (!strcmp(key, "gemm_raw_slots")) c->gemm_raw_slots = value;
     else if (!strcmp(key, "gemm_row_tiles")) c->gemm_row_tiles = value;
+    else if (!strcmp(key, "raw_gemv_mma")) c->raw_gemv_mma = value;
     else if (!strcmp(key, "gemm_pdl")) c->gemm_pdl = value;
     else if (!strcmp(key, "host_batch_graph")) c->host_batch_graph = value;
     else if (!strcmp(key, "peer_wait_spins")) {

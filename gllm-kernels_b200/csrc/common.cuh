@@ -114,6 +114,7 @@ struct Ctx {
                                 // 1 when the estimate favours it, 2 always
     int64_t gemm_raw_slots = 0;  // weight-only GEMM: raw super-chunk ring depth (0 = chosen by the shared-memory plan)
     int64_t gemm_pdl = 1;        // weight-only GEMM launched programmatically behind its activation staging kernel
+    int64_t raw_gemv_mma = 1;    // Q6_K products of 2 tokens and more on the tensor-core kernel (0 = dp2a kernel, 2 = also a single token)
     int64_t gemm_row_tiles = 0;  // weight-only GEMM: row tiles per CTA (0 = estimated, 1, 2)
     int64_t peer_wait_spins = (int64_t)1 << 22;  // probes of another rank's flag before a wait gives up (status 31 / 32)
 };

@@ -449,6 +449,175 @@ __global__ void __launch_bounds__(RG_WARPS * 32) raw_gemv_kernel(const RawGemvPa
 }
 
 // Q6_K: reference blocks (210 bytes) <-> device slots (224 bytes); one thread per 2 bytes
+// ---- Q6_K, 2 tokens and more: the same integer dot products on the tensor core (mma.sync m16n8k16, s8) -------------
+// A CTA owns 16 weight rows (the MMA M) and its eight warps split the row's blocks between them; a warp stages one block
+// of each of the 16 rows and the same 256 activations of its tokens per pass (cp.async, two or three stages: operand B
+// fetched from L2 by every lane as it was needed left the warps waiting for loads most of the time) and issues, per
+// 16-element scale group, one MMA per digit of
+// the s16 activations (x = 256 * hi + lo, hi signed, lo unsigned: exact) and group of 8 tokens (the MMA N).  Fragment
+// layout of m16n8k16: lane (g = lane / 4, t = lane % 4) supplies rows g and g + 8 at k = 4t .. 4t + 3 — one assembled word
+// of four s8 values each, the same words the dp2a kernel builds — and token g at the same k; it receives rows g, g + 8
+// x tokens 2t, 2t + 1, which it scales by (d * sc of the row's group) x (the token's activation scale) and accumulates
+// in f32.  The dp2a kernel spends its time per TOKEN; this one per group of eight.
+constexpr int QM_ROWS = 16;
+constexpr int QM_ROW_STRIDE = 240;  // a block slot (224 bytes) padded so that eight rows' words fall on different banks
+constexpr int QM_TOK_STRIDE = 544;  // a token's 256 s16 activations (512 bytes) padded likewise (8-byte loads, half a warp at a time)
+constexpr int qm_stages(int tg) { return tg == 1 ? 3 : 2; }
+constexpr int qm_stage_bytes(int tg) { return QM_ROWS * QM_ROW_STRIDE + 8 * tg * QM_TOK_STRIDE; }
+constexpr size_t qm_smem_bytes(int tg) { return (size_t)RG_WARPS * qm_stages(tg) * qm_stage_bytes(tg); }
+
+// c = a x b (no accumulator input to keep zeroed: the C operand is one zero register four times)
+__device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0, bool b_unsigned) {
+    if (b_unsigned)
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.u8.s32 {%0, %1, %2, %3}, {%4, %5}, {%6}, {%7, %7, %7, %7};\n"
+                     : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+                     : "r"(a0), "r"(a1), "r"(b0), "r"(0));
+    else
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5}, {%6}, {%7, %7, %7, %7};\n"
+                     : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+                     : "r"(a0), "r"(a1), "r"(b0), "r"(0));
+}
+
+template <int TG>  // groups of 8 tokens per pass over the weights
+__global__ void __launch_bounds__(RG_WARPS * 32) q6k_gemv_mma_kernel(const RawGemvParams p) {
+    constexpr int DB = Fmt<GLLMK_QUANT_Q6_K>::DB, CPR = DB / 16, NCP = QM_ROWS * CPR / 32;  // 14 chunks of 16 bytes per row and block: 7 per lane
+    constexpr int QM_STAGES = qm_stages(TG), QM_STAGE_BYTES = qm_stage_bytes(TG), ACT_OFF = QM_ROWS * QM_ROW_STRIDE;
+    extern __shared__ __align__(16) uint8_t qm_smem[];
+    __shared__ float red[RG_WARPS][QM_ROWS][8 * TG];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int64_t row0 = (int64_t)blockIdx.x * QM_ROWS;
+    const int nb = (int)p.nb, k32 = (int)(p.k >> 5);
+    const int b_lo = (int)((int64_t)nb * warp / RG_WARPS), b_hi = (int)((int64_t)nb * (warp + 1) / RG_WARPS);
+    uint8_t *stages = qm_smem + (size_t)warp * QM_STAGES * QM_STAGE_BYTES;
+    // this lane's chunks of a pass: chunk i = lane + 32 j -> row i / 14 (a surplus row repeats the last one; not stored)
+    int soff[NCP];
+    const uint8_t *gsrc[NCP];
+#pragma unroll
+    for (int j = 0; j < NCP; j++) {
+        const int i = lane + 32 * j, r = i / CPR, ch = i % CPR;
+        const int64_t row = row0 + r < p.n ? row0 + r : p.n - 1;
+        soff[j] = r * QM_ROW_STRIDE + 16 * ch;
+        gsrc[j] = p.w + (size_t)row * nb * DB + 16 * ch;
+    }
+    for (int t0 = 0; t0 < p.m; t0 += 8 * TG) {
+        float acc[TG][4];
+        const float *xsa[TG], *xsb[TG];  // the tokens this lane receives (accumulator columns): t0 + 8 tg + 2t, + 1
+        // a pass's activations: 32 chunks of 16 bytes per token, lane = chunk; token tk of the pass = t0 + tk (a surplus
+        // column repeats the last token; not stored).  The lane SUPPLIES token 8 tg + g (operand B).
+        const auto issue = [&](int b, int st) {
+            uint8_t *dst = stages + st * QM_STAGE_BYTES;
+#pragma unroll
+            for (int j = 0; j < NCP; j++) cp_async16(dst + soff[j], gsrc[j] + (size_t)b * DB);
+#pragma unroll
+            for (int tk = 0; tk < 8 * TG; tk++) {
+                const int tok = t0 + tk < p.m ? t0 + tk : p.m - 1;
+                cp_async16(dst + ACT_OFF + tk * QM_TOK_STRIDE + 16 * lane, p.xq + (size_t)tok * p.k + (size_t)b * 256 + 8 * lane);
+            }
+        };
+#pragma unroll
+        for (int tg = 0; tg < TG; tg++) {
+            const int ta = t0 + 8 * tg + 2 * t;
+            xsa[tg] = p.xs + (size_t)(ta < p.m ? ta : p.m - 1) * k32;
+            xsb[tg] = p.xs + (size_t)(ta + 1 < p.m ? ta + 1 : p.m - 1) * k32;
+#pragma unroll
+            for (int i = 0; i < 4; i++) acc[tg][i] = 0.0f;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < QM_STAGES - 1; i++) {
+            if (b_lo + i < b_hi) issue(b_lo + i, i);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        }
+        int st = 0;
+        for (int b = b_lo; b < b_hi; b++) {
+            // the block's activation scales (eight 32-element groups per token): two 16-byte loads per column, early
+            float4 xs4[TG][2][2];
+#pragma unroll
+            for (int tg = 0; tg < TG; tg++) {
+                xs4[tg][0][0] = __ldg(reinterpret_cast<const float4 *>(xsa[tg] + 8 * b));
+                xs4[tg][0][1] = __ldg(reinterpret_cast<const float4 *>(xsa[tg] + 8 * b + 4));
+                xs4[tg][1][0] = __ldg(reinterpret_cast<const float4 *>(xsb[tg] + 8 * b));
+                xs4[tg][1][1] = __ldg(reinterpret_cast<const float4 *>(xsb[tg] + 8 * b + 4));
+            }
+            if (b + QM_STAGES - 1 < b_hi) issue(b + QM_STAGES - 1, st == 0 ? QM_STAGES - 1 : st - 1);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            asm volatile("cp.async.wait_group %0;" ::"n"(QM_STAGES - 1) : "memory");
+            __syncwarp();
+            const uint8_t *r0 = stages + st * QM_STAGE_BYTES + g * QM_ROW_STRIDE, *r8 = r0 + 8 * QM_ROW_STRIDE;
+            const uint8_t *xact = stages + st * QM_STAGE_BYTES + ACT_OFF + g * QM_TOK_STRIDE + 8 * t;  // token g, elements 4t .. 4t + 3 of a group
+            const uint4 S0 = *reinterpret_cast<const uint4 *>(r0 + FD_Q6K.sub_scales_offset);
+            const uint4 S8 = *reinterpret_cast<const uint4 *>(r8 + FD_Q6K.sub_scales_offset);
+            const uint32_t s0w[4] = {S0.x, S0.y, S0.z, S0.w}, s8w[4] = {S8.x, S8.y, S8.z, S8.w};
+            const float d0 = 0.25f * f16_even(r0 + FD_Q6K.scale_offset), d8 = 0.25f * f16_even(r8 + FD_Q6K.scale_offset);
+#pragma unroll
+            for (int hh = 0; hh < 2; hh++) {  // half of the block (128 elements)
+#pragma unroll
+                for (int is = 0; is < 2; is++) {  // which 16 of every 32-element run
+                    int2 xw[4][TG];  // operand B of the four runs: four s16 activations each
+#pragma unroll
+                    for (int j = 0; j < 4; j++)
+#pragma unroll
+                        for (int tg = 0; tg < TG; tg++)
+                            xw[j][tg] = *reinterpret_cast<const int2 *>(xact + 8 * tg * QM_TOK_STRIDE + 2 * (hh * 128 + 32 * j + 16 * is));
+                    const int lo_off = FD_Q6K.data_offset + hh * 64 + 16 * is + 4 * t, hi_off = FD_Q6K.data_high_offset + hh * 32 + 16 * is + 4 * t;
+                    const uint32_t A0 = *reinterpret_cast<const uint32_t *>(r0 + lo_off), B0 = *reinterpret_cast<const uint32_t *>(r0 + lo_off + 32),
+                                   H0 = *reinterpret_cast<const uint32_t *>(r0 + hi_off);
+                    const uint32_t A8 = *reinterpret_cast<const uint32_t *>(r8 + lo_off), B8 = *reinterpret_cast<const uint32_t *>(r8 + lo_off + 32),
+                                   H8 = *reinterpret_cast<const uint32_t *>(r8 + hi_off);
+                    const uint32_t q0[4] = {q6_word(A0, H0 << 4), q6_word(B0, H0 << 2), q6_word(A0 >> 4, H0), q6_word(B0 >> 4, H0 >> 2)};
+                    const uint32_t q8[4] = {q6_word(A8, H8 << 4), q6_word(B8, H8 << 2), q6_word(A8 >> 4, H8), q6_word(B8 >> 4, H8 >> 2)};
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {  // run j of the half: elements hh * 128 + 32 j + 16 is + (0 .. 15), scale byte hh * 8 + is + 2 j
+                        const int sb = hh * 8 + is + 2 * j;
+                        const float ws0 = d0 * (float)(int8_t)((s0w[sb >> 2] >> (8 * (sb & 3))) & 0xFF);
+                        const float ws8 = d8 * (float)(int8_t)((s8w[sb >> 2] >> (8 * (sb & 3))) & 0xFF);
+#pragma unroll
+                        for (int tg = 0; tg < TG; tg++) {
+                            const uint32_t xlo = __byte_perm((uint32_t)xw[j][tg].x, (uint32_t)xw[j][tg].y, 0x6420),
+                                           xhi = __byte_perm((uint32_t)xw[j][tg].x, (uint32_t)xw[j][tg].y, 0x7531);
+                            int chi[4], clo[4];
+                            mma_s8(chi, q0[j], q8[j], xhi, false);
+                            mma_s8(clo, q0[j], q8[j], xlo, true);
+                            const float4 va = xs4[tg][0][hh], vb = xs4[tg][1][hh];
+                            const float xa = j == 0 ? va.x : (j == 1 ? va.y : (j == 2 ? va.z : va.w));
+                            const float xb = j == 0 ? vb.x : (j == 1 ? vb.y : (j == 2 ? vb.z : vb.w));
+                            acc[tg][0] = fmaf((float)(chi[0] * 256 + clo[0]), ws0 * xa, acc[tg][0]);
+                            acc[tg][1] = fmaf((float)(chi[1] * 256 + clo[1]), ws0 * xb, acc[tg][1]);
+                            acc[tg][2] = fmaf((float)(chi[2] * 256 + clo[2]), ws8 * xa, acc[tg][2]);
+                            acc[tg][3] = fmaf((float)(chi[3] * 256 + clo[3]), ws8 * xb, acc[tg][3]);
+                        }
+                    }
+                }
+            }
+            __syncwarp();  // every lane is done with this stage before a later pass's copies overwrite it
+            st = st + 1 == QM_STAGES ? 0 : st + 1;
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        // the eight warps' partial sums meet in shared memory
+#pragma unroll
+        for (int tg = 0; tg < TG; tg++) {
+            red[warp][g][8 * tg + 2 * t] = acc[tg][0];
+            red[warp][g][8 * tg + 2 * t + 1] = acc[tg][1];
+            red[warp][g + 8][8 * tg + 2 * t] = acc[tg][2];
+            red[warp][g + 8][8 * tg + 2 * t + 1] = acc[tg][3];
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < QM_ROWS * 8 * TG; i += RG_WARPS * 32) {
+            const int r = i / (8 * TG), tk = i % (8 * TG);
+            const int64_t row = row0 + r;
+            if (row < p.n && t0 + tk < p.m) {
+                float a = 0.0f;
+#pragma unroll
+                for (int w = 0; w < RG_WARPS; w++) a += red[w][r][tk];
+                if (p.n_row_scales == 1) a *= p.row_scales[0];
+                else if (p.n_row_scales > 1) a *= p.row_scales[row];
+                p.y[(size_t)(t0 + tk) * p.yst + (size_t)row * p.ysr] = a;
+            }
+        }
+        __syncthreads();
+    }
+}
+
 __global__ void q6k_pad_kernel(const unsigned short *__restrict__ src, unsigned short *__restrict__ dst, size_t total, int to_device) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
@@ -470,8 +639,22 @@ int32_t dequant_t(Ctx *c, const uint8_t *w, int64_t n, int64_t nb, const int32_t
     return GLLMK_STATUS_OK;
 }
 
+template <int TG>
+int32_t q6k_mma_launch(Ctx *c, const RawGemvParams &p, cudaStream_t s) {
+    static bool attr_set[64] = {};  // function attributes are per device
+    if (!attr_set[c->device & 63]) {
+        GK_CUDA(c, cudaFuncSetAttribute(q6k_gemv_mma_kernel<TG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)qm_smem_bytes(TG)));
+        attr_set[c->device & 63] = true;
+    }
+    q6k_gemv_mma_kernel<TG><<<(unsigned)((p.n + QM_ROWS - 1) / QM_ROWS), RG_WARPS * 32, qm_smem_bytes(TG), s>>>(p);
+    GK_CUDA(c, cudaGetLastError());
+    return GLLMK_STATUS_OK;
+}
+
 template <int QT>
 int32_t gemv_t(Ctx *c, const RawGemvParams &p, cudaStream_t s) {
+    if (QT == GLLMK_QUANT_Q6_K && c->raw_gemv_mma && (p.m >= 2 || c->raw_gemv_mma == 2) && p.n <= (int64_t)0x7fffffff * QM_ROWS)
+        return p.m <= 8 ? q6k_mma_launch<1>(c, p, s) : q6k_mma_launch<2>(c, p, s);
     // 16 rows per CTA and pass; enough CTAs to fill every SM several times over, never more than the rows need
     int64_t ctas = (p.n + RG_WARPS * RG_ROWS - 1) / (RG_WARPS * RG_ROWS);
     const int64_t cap = (int64_t)c->sm_count * 6;

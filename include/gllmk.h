@@ -162,6 +162,7 @@ GLLMK_API int32_t gllmk_ctx_status(gllmk_ctx ctx, int32_t *device_status);
  * argument list: 1 default, 0 never), "gemm_tail_split" (prefill GEMM, last partial wave of tiles cut along k:
  * 0 automatic, 1 never, n into n), "gemm_row_tiles" (prefill GEMM, 128-row weight tiles per CTA: 0 estimated, 1, 2),
  * "gemm_raw_slots" (prefill GEMM, depth of the raw weight ring: 0 = what the shared-memory plan gives),
+ * "raw_gemv_mma" (Q6_K products of 2 tokens and more on the mma.sync kernel: 1 default, 0 the dp2a kernel, 2 a single token too),
  * "gemm_pdl" (prefill GEMM launched programmatically behind its activation staging kernel: 1 default, 0 plain launch), "peer_wait_spins" (how many times a wait on another GPU's flag probes it
  * before it gives up with status 31; default 2^22, about a second), "inject_give_up" (testing aid, host side
  * only: leaves the context as a kernel that gave up a wait with that status code would — word set, arrival

@@ -132,6 +132,58 @@ def test_gemv_parity(K, gk, oracle, torch, name, m):
     w.free()
 
 
+@pytest.mark.parametrize("n,k,m", [(203, 8 * 256, 2), (16, 256, 8), (33, 3 * 256, 9), (64, 40 * 256, 16), (100, 5 * 256, 70)])
+def test_q6k_batch_on_the_tensor_core(K, gk, oracle, torch, n, k, m):
+    """Q6_K with two tokens and more: mma.sync over the same assembled s8 words and s16 activation digits as the dp2a
+    kernel ("raw_gemv_mma" = 0), so both see the same integers; only the f32 summation order differs.  Shapes: rows not a
+    multiple of the 16 a CTA owns, one block per row (seven of the eight warps idle), blocks not a multiple of eight,
+    tokens not a multiple of eight, more tokens than one pass holds; row scales and the reference's transposed layout."""
+    qt = qtype(gk, "q6_k")
+    blocks = random_blocks("q6_k", qt, n, k, 300 + m)
+    rng = np.random.default_rng(31 + m)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    sc = rng.uniform(0.5, 2.0, n).astype(np.float32)
+    ref = oracle.quant_matmul(blocks, np.ascontiguousarray(x.T), qt.id, n, m, k, threads=4)  # [n, m]
+    w = K.upload(qt, n, k, blocks)
+    xd = torch.from_numpy(x).cuda()
+    run = (lambda: K.gemm(w, xd)) if m > 16 else (lambda: K.gemv(w, xd))
+    try:
+        K.set("raw_gemv_mma", 1)
+        y_tc = run().cpu().numpy()
+        K.set("raw_gemv_mma", 0)
+        y_dp = run().cpu().numpy()
+        K.set("raw_gemv_mma", 1)
+        if m <= 16:
+            y_sc = K.gemv(w, xd, row_scales=torch.from_numpy(sc).cuda()).cpu().numpy()
+            y_t = K.gemv(w, torch.from_numpy(np.ascontiguousarray(x.T)).cuda(), ref_layout=True).cpu().numpy()
+    finally:
+        K.set("raw_gemv_mma", 1)
+    assert K.status() == 0
+    assert oracle.rel_err(y_tc.T, ref) <= TOL
+    assert oracle.rel_err(y_tc.T, y_dp.T) <= 1e-5
+    if m <= 16:
+        assert oracle.rel_err(y_sc.T, ref * sc[:, None]) <= TOL
+        assert oracle.rel_err(y_t, ref) <= TOL
+    w.free()
+
+
+def test_q6k_single_token_on_the_tensor_core(K, gk, oracle, torch):
+    # "raw_gemv_mma" = 2 routes one token through the same kernel (seven of the eight MMA columns idle)
+    qt = qtype(gk, "q6_k")
+    n, k = 130, 6 * 256
+    blocks = random_blocks("q6_k", qt, n, k, 77)
+    x = np.random.default_rng(78).standard_normal((1, k)).astype(np.float32)
+    ref = oracle.quant_matmul(blocks, np.ascontiguousarray(x.T), qt.id, n, 1, k, threads=4)
+    w = K.upload(qt, n, k, blocks)
+    try:
+        K.set("raw_gemv_mma", 2)
+        y = K.gemv(w, torch.from_numpy(x).cuda()).cpu().numpy()
+    finally:
+        K.set("raw_gemv_mma", 1)
+    assert K.status() == 0 and oracle.rel_err(y.T, ref) <= TOL
+    w.free()
+
+
 @pytest.mark.parametrize("name", ["q6_k", "q4_0"])
 def test_gemv_long_rows_and_row_scales(K, gk, oracle, torch, name):
     """k large enough for several staging passes per row (a pass holds 4 KB of blocks); per-row scales."""
