@@ -659,6 +659,26 @@ def extra_configs(K, gk, torch, dev, peak):
     run(gk.QuantType.q8k(), D_MODEL, N_FF, [1], 2, "gguf_q8k_8192x28672")
     run(gk.QuantType.q4_0(), D_MODEL, N_FF, [1], 3, "gguf_q4_0_8192x28672")
     run(gk.QuantType.q5_0(), D_MODEL, N_FF, [1], 3, "gguf_q5_0_8192x28672")
+    # Q6_K prefill on the fused-dequant tensor-core GEMM, same shape at M = 512
+    q = random_gguf_blocks(gk.QuantType.q6k(), D_MODEL, N_FF)
+    w6 = K.upload(gk.QuantType.q6k(), D_MODEL, N_FF, q)
+    x6 = torch.randn((512, N_FF), generator=gen, device=dev)
+    y6 = torch.empty((512, D_MODEL), dtype=torch.float32, device=dev)
+    for _ in range(3):
+        K.gemm(w6, x6, y=y6)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(5):
+        K.gemm(w6, x6, y=y6)
+    e1.record()
+    torch.cuda.synchronize()
+    us6 = e0.elapsed_time(e1) * 1e3 / 5
+    res["gguf_q6k_8192x28672_M512"] = {"us": us6, "tflops": 2.0 * 512 * D_MODEL * N_FF / us6 / 1e6, "staging": "fp16 x fp16 -> f32 (kind::f16)",
+                                       "parity": sampled_parity(O, gk.QuantType.q6k().id, q, D_MODEL, N_FF, sample_rows(D_MODEL, 256, seed=6), x6.cpu().numpy(),
+                                                                y6, bar=1e-2, sequential=False)}
+    w6.free()
+    del q, x6, y6
     res.update(extra_gemm(K, gk, torch, dev, gen))
     res["cpu_bench_quant_kernels"] = bench_quant_cpu_all()
     return res

@@ -37,9 +37,11 @@ constexpr int WQ_CTRL = 4;         // warp 0: raw copies, warp 1: activation cop
 constexpr int WQ_THREADS = 32 * (WQ_CTRL + WQ_DW);  // then the dequant / epilogue warps
 constexpr int WQ_SMEM_LIMIT = 232448 - 1024 - 1024;  // ring space: 227 KB less the static variables' share and the alignment slack
 
-enum { FMT_Q4K = 0, FMT_Q80 = 1, FMT_NVFP4 = 2, FMT_MXFP4 = 3 };
+enum { FMT_Q4K = 0, FMT_Q80 = 1, FMT_NVFP4 = 2, FMT_MXFP4 = 3, FMT_Q6K = 4 };
+constexpr int Q6K_SLOT = 224;        // a Q6_K block (210 bytes) on the device: reference layout in a 16-byte aligned slot
+constexpr int Q6K_ROW_STRIDE = 240;  // and in shared memory, so that eight rows' 16-byte words fall on different banks
 __host__ __device__ constexpr int wq_raw_bytes(int fmt) {
-    return fmt == FMT_Q4K ? 8 * Q4K_CHUNK : (fmt == FMT_Q80 ? 8 * Q80_CHUNK : (fmt == FMT_NVFP4 ? WQ_TILE + 2048 : WQ_TILE + 1024));
+    return fmt == FMT_Q4K ? 8 * Q4K_CHUNK : (fmt == FMT_Q80 ? 8 * Q80_CHUNK : (fmt == FMT_NVFP4 ? WQ_TILE + 2048 : (fmt == FMT_MXFP4 ? WQ_TILE + 1024 : 128 * Q6K_ROW_STRIDE)));
 }
 
 constexpr int WQ_MAX_GROUPS = 32;      // weights (experts) per launch
@@ -331,6 +333,58 @@ struct Dequant<FMT_NVFP4> : DequantFp4<FMT_NVFP4> {};
 template <>
 struct Dequant<FMT_MXFP4> : DequantFp4<FMT_MXFP4> {};
 
+// Q6_K (k_quant.rs:441-472): the raw super-chunk is one reference-layout block (ql[128] @0, qh[64] @128, scales[16] i8 @192,
+// d f16 @208) of each of the tile's 128 rows, Q6K_ROW_STRIDE bytes apart.  Thread = weight row 32 * wg + lane.  k-step p of
+// the block (64 elements) is half hh = p / 2, runs j0 = 2 (p % 2) and j0 + 1 of that half: run j takes the nibble p % 2 of
+// ql[hh * 64 + (j % 2) * 32 + l] and bits 2j, 2j + 1 of qh[hh * 32 + l], l = 0 .. 31; scale sc[hh * 8 + l / 16 + 2 j].
+// A word of four 6-bit values becomes the s8 word 4 (q - 32) (bit 5 flipped, two places up), that the fp16 pairs
+// 4 (q - 32) exactly (the byte in the mantissa of 1024, as for Q8_0), times d * sc / 4 rounded to fp16.
+__device__ __forceinline__ uint32_t q6k_word(uint32_t lo4, uint32_t hi2_at_4) {
+    return ((((lo4 & 0x0F0F0F0Fu) | (hi2_at_4 & 0x30303030u)) ^ 0x20202020u) << 2) & 0xFCFCFCFCu;
+}
+template <>
+struct Dequant<FMT_Q6K> {
+    float global;
+    __device__ __forceinline__ void compute(const uint8_t *raw, int p, int wg, int lane, uint4 (&o)[8]) {
+        const uint8_t *b = raw + (32 * wg + lane) * Q6K_ROW_STRIDE;
+        const int hh = p >> 1, nib = 4 * (p & 1);  // low or high nibbles; qh bits 4 (p % 2) .. + 3
+        const uint4 S = *reinterpret_cast<const uint4 *>(b + 192);
+        // the four scale bytes this step uses: index hh * 8 + 4 (p % 2) + (half + 2 r), half, r = 0, 1
+        const uint32_t sw = (p & 1) ? (hh ? S.w : S.y) : (hh ? S.z : S.x);
+        const float d = 0.25f * __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(b + 208)));
+#pragma unroll
+        for (int half = 0; half < 2; half++) {  // l = 16 half .. 16 half + 15: one 16-byte word of each field
+            const uint4 A = *reinterpret_cast<const uint4 *>(b + hh * 64 + 16 * half);        // run j0
+            const uint4 B = *reinterpret_cast<const uint4 *>(b + hh * 64 + 32 + 16 * half);   // run j0 + 1
+            const uint4 H = *reinterpret_cast<const uint4 *>(b + 128 + hh * 32 + 16 * half);
+            const uint32_t aw[4] = {A.x, A.y, A.z, A.w}, bw[4] = {B.x, B.y, B.z, B.w}, hw[4] = {H.x, H.y, H.z, H.w};
+#pragma unroll
+            for (int r = 0; r < 2; r++) {  // run j0 + r
+                const __half2 sc2 = scale_h2(d * (float)(int8_t)((sw >> (8 * (half + 2 * r))) & 0xFF));
+#pragma unroll
+                for (int c = 0; c < 2; c++) {  // eight elements: words 2c, 2c + 1 of the 16
+                    uint32_t q[2];
+#pragma unroll
+                    for (int i = 0; i < 2; i++) {
+                        const uint32_t lo = (r ? bw[2 * c + i] : aw[2 * c + i]) >> nib;
+                        const uint32_t hi = nib ? (r ? hw[2 * c + i] >> 2 : hw[2 * c + i]) : (r ? hw[2 * c + i] << 2 : hw[2 * c + i] << 4);
+                        q[i] = q6k_word(lo, hi);
+                    }
+                    uint4 &out = o[4 * r + 2 * half + c];  // k = 32 r + 16 half + 8 c .. + 7 of the step
+                    q80_word(q[0], sc2, out.x, out.y);
+                    q80_word(q[1], sc2, out.z, out.w);
+                }
+            }
+        }
+    }
+    __device__ __forceinline__ void store(uint8_t *at, int wg, int lane, const uint4 (&o)[8]) {
+        const int r = 32 * wg + lane;
+        uint8_t *rowp = at + r * 128;
+#pragma unroll
+        for (int c = 0; c < 8; c++) *reinterpret_cast<uint4 *>(rowp + ((c ^ (r & 7)) << 4)) = o[c];
+    }
+};
+
 // ---- the kernel -----------------------------------------------------------------------------------
 // grid: (token tiles, groups of MT weight-row tiles): CTAs that share weight tiles run side by side, so the
 // second reader finds the raw bytes in L2.
@@ -418,7 +472,34 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
     const uint32_t tmem_d = tmem_base_s;
     WQP_DECL;
 
-    if (warp == 0) {
+    if (warp == 0 && FMT == FMT_Q6K) {
+        // ---------------- raw weight blocks: one block of each of the tile's 128 rows per super-chunk, four bulk copies per lane ----------------
+        int slot = 0, round = 0;
+        bool ok = true;
+        for (int jl = 0; jl < njb && ok; jl++) {
+            const int jb = jb0 + jl;
+            for (int ti = 0; ti < mt && ok; ti++) {
+                if (lane == 0 && round > 0 && !tc::mbar_wait(rawempty + 8 * slot, (uint32_t)((round - 1) & 1), abort_flag)) {
+                    abort_s = 1;
+                    atomicExch(p.status, 10);
+                    ok = false;
+                }
+                ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+                if (!ok) break;
+                const uint32_t dst = smem_s + raw_off + (uint32_t)(slot * RAW);
+                if (lane == 0) tc::mbar_expect_tx(rawfull + 8 * slot, 128u * Q6K_SLOT);
+                __syncwarp();
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int r = lane + 32 * i;
+                    int64_t row = (int64_t)(tile0 + ti) * WQ_BM + r;
+                    if (row >= p.n) row = p.n - 1;  // rows past the matrix repeat the last one; their results are not stored
+                    bulk_g2s(dst + (uint32_t)(r * Q6K_ROW_STRIDE), G.qs[grp_id] + ((size_t)row * p.nsc + jb) * Q6K_SLOT, Q6K_SLOT, rawfull + 8 * slot);
+                }
+                if (++slot == p.r) slot = 0, round++;
+            }
+        }
+    } else if (warp == 0) {
         // ---------------- raw weight super-chunks: one thread, bulk copies ----------------
         if (lane == 0) {
             int slot = 0, round = 0;
@@ -676,7 +757,7 @@ static int32_t gemm_groups_chunk(Ctx *c, const Weight *const *ws, int ng, const 
                                  const int64_t *tok_begin, const int64_t *tok_count, int ntok, void *y, int y_bf16, int64_t ldy,
                                  cudaStream_t s, const void *a_up) {
     const Weight *w = ws[0];
-    const int fmt = w->qt == GLLMK_QUANT_Q4K ? FMT_Q4K : (w->qt == GLLMK_QUANT_Q8_0 ? FMT_Q80 : (w->qt == GLLMK_QUANT_NVFP4 ? FMT_NVFP4 : FMT_MXFP4));
+    const int fmt = w->qt == GLLMK_QUANT_Q4K ? FMT_Q4K : (w->qt == GLLMK_QUANT_Q8_0 ? FMT_Q80 : (w->qt == GLLMK_QUANT_NVFP4 ? FMT_NVFP4 : (w->qt == GLLMK_QUANT_Q6_K ? FMT_Q6K : FMT_MXFP4)));
     const int raw = wq_raw_bytes(fmt);
     GemmParams p{};
     GemmGroups G{};
@@ -710,7 +791,7 @@ static int32_t gemm_groups_chunk(Ctx *c, const Weight *const *ws, int ng, const 
         }
     }
     if (ntiles == 0) return GLLMK_STATUS_OK;
-    const int row_tiles = (int)(w->n_pad / WQ_BM);
+    const int row_tiles = (int)((w->n_pad + WQ_BM - 1) / WQ_BM);  // (Q6_K rows are not padded on the device)
     const int bstage = ntok * 128;
     // Row tiles per CTA and how the last wave is cut along k, chosen together.  Two row tiles share one activation stage
     // (less shared-memory fill traffic per flop, two issuing threads, fixed costs paid once) but halve the CTA count; a
@@ -790,6 +871,7 @@ static int32_t gemm_groups_chunk(Ctx *c, const Weight *const *ws, int ng, const 
         case FMT_Q4K: return launch_wq_mt<FMT_Q4K>(c, p, G, mt, grid, smem, s);
         case FMT_Q80: return launch_wq_mt<FMT_Q80>(c, p, G, mt, grid, smem, s);
         case FMT_NVFP4: return launch_wq_mt<FMT_NVFP4>(c, p, G, mt, grid, smem, s);
+        case FMT_Q6K: return launch_wq_mt<FMT_Q6K>(c, p, G, mt, grid, smem, s);
         default: return launch_wq_mt<FMT_MXFP4>(c, p, G, mt, grid, smem, s);
     }
 }
@@ -798,7 +880,7 @@ static int32_t gemm_groups_chunk(Ctx *c, const Weight *const *ws, int ng, const 
 int32_t gemm_grouped_launch(Ctx *c, const Weight *const *ws, int n_groups, const void *a, int a_bf16, int64_t lda,
                             const int64_t *row_offsets, void *y, int y_bf16, int64_t ldy, cudaStream_t s, const void *a_up) {
     const int align = a_bf16 ? 8 : 4;
-    if (ws[0]->qt < GLLMK_QUANT_Q4K || ws[0]->qt > GLLMK_QUANT_NVFP4)
+    if ((ws[0]->qt < GLLMK_QUANT_Q4K || ws[0]->qt > GLLMK_QUANT_NVFP4) && ws[0]->qt != GLLMK_QUANT_Q6_K)
         return fail(c, GLLMK_STATUS_UNSUPPORTED, "gemm: weight type %d is not block-quantized (use gllmk_gemm_int8)", ws[0]->qt);
     if (((uintptr_t)a & 15) || (lda % align)) return fail(c, GLLMK_STATUS_INVALID_ARG, "gemm: activations must be 16-byte aligned rows");
     if (ws[0]->k % 8) return fail(c, GLLMK_STATUS_INVALID_ARG, "gemm: k=%lld is not a multiple of 8", (long long)ws[0]->k);

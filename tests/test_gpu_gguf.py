@@ -132,12 +132,12 @@ def test_gemv_parity(K, gk, oracle, torch, name, m):
     w.free()
 
 
-@pytest.mark.parametrize("n,k,m", [(203, 8 * 256, 2), (16, 256, 8), (33, 3 * 256, 9), (64, 40 * 256, 16), (100, 5 * 256, 70)])
+@pytest.mark.parametrize("n,k,m", [(203, 8 * 256, 2), (16, 256, 8), (33, 3 * 256, 9), (64, 40 * 256, 16), (100, 5 * 256, 13)])
 def test_q6k_batch_on_the_tensor_core(K, gk, oracle, torch, n, k, m):
     """Q6_K with two tokens and more: mma.sync over the same assembled s8 words and s16 activation digits as the dp2a
     kernel ("raw_gemv_mma" = 0), so both see the same integers; only the f32 summation order differs.  Shapes: rows not a
     multiple of the 16 a CTA owns, one block per row (seven of the eight warps idle), blocks not a multiple of eight,
-    tokens not a multiple of eight, more tokens than one pass holds; row scales and the reference's transposed layout."""
+    tokens not a multiple of eight; row scales and the reference's transposed layout."""
     qt = qtype(gk, "q6_k")
     blocks = random_blocks("q6_k", qt, n, k, 300 + m)
     rng = np.random.default_rng(31 + m)
@@ -200,12 +200,11 @@ def test_gemv_long_rows_and_row_scales(K, gk, oracle, torch, name):
     w.free()
 
 
-@pytest.mark.parametrize("name", ["q6_k", "q5_0"])
-def test_gemm_many_tokens_f32(K, gk, oracle, torch, name):
-    """gllmk_gemm with these formats runs the streaming kernel over token tiles; bf16 operands are refused."""
-    qt = qtype(gk, name)
+def test_gemm_many_tokens_f32(K, gk, oracle, torch):
+    """gllmk_gemm with a format that has no tensor-core kernel runs the streaming kernel over token tiles; bf16 operands are refused."""
+    qt = qtype(gk, "q5_0")
     n, k, m = 96, 512, 70
-    blocks = random_blocks(name, qt, n, k, 21)
+    blocks = random_blocks("q5_0", qt, n, k, 21)
     x = np.random.default_rng(22).standard_normal((m, k)).astype(np.float32)
     ref = oracle.quant_matmul(blocks, np.ascontiguousarray(x.T), qt.id, n, m, k, threads=4)
     w = K.upload(qt, n, k, blocks)
@@ -213,6 +212,32 @@ def test_gemm_many_tokens_f32(K, gk, oracle, torch, name):
     assert oracle.rel_err(y.T, ref) <= TOL
     with pytest.raises(gk.GllmkError):
         K.gemm(w, torch.from_numpy(x).cuda().to(torch.bfloat16))
+    w.free()
+
+
+@pytest.mark.parametrize("n,k,m,bf16", [(96, 512, 70, False), (300, 5 * 256, 33, True), (64, 2 * 256, 20, True), (130, 256, 300, False), (1000, 12 * 256, 130, True),
+                                        (20000, 512, 200, True)])
+def test_q6k_prefill_on_the_tensor_core(K, gk, oracle, torch, n, k, m, bf16):
+    """Q6_K with more than 32 tokens: the fused-dequant tcgen05 GEMM, reference-layout blocks copied row by row into shared
+    memory and converted to fp16 there (bar 1e-2 like the other weight-only formats).  Rows not a multiple of 128 (the
+    last tile repeats the last row, results not stored), one and many k-blocks, one and two row tiles per CTA, f32 and bf16."""
+    qt = qtype(gk, "q6_k")
+    blocks = random_blocks("q6_k", qt, n, k, 400 + m)
+    x = np.random.default_rng(41 + m).standard_normal((m, k)).astype(np.float32)
+    xd = torch.from_numpy(x).cuda()
+    if bf16:
+        xd = xd.to(torch.bfloat16)
+        x = xd.to(torch.float32).cpu().numpy()
+    w = K.upload(qt, n, k, blocks)
+    y = K.gemm(w, xd, out_dtype=torch.bfloat16 if bf16 else torch.float32).to(torch.float32).cpu().numpy()
+    assert K.status() == 0
+    rows = np.random.default_rng(3).choice(n, size=min(n, 256), replace=False)
+    wd = oracle_matrix(oracle, qt, blocks, n, k)[rows]
+    ref = oracle.gemm_f32_nt(x, wd)
+    assert oracle.rel_err(y[:, rows], ref) <= 1e-2 + (2.0 ** -8 if bf16 else 0.0)
+    # the decode kernels on the same weight stay within their bar of the same reference
+    y1 = K.gemv(w, torch.from_numpy(x[:4]).cuda()).cpu().numpy()
+    assert oracle.rel_err(y1[:, rows], ref[:4]) <= TOL
     w.free()
 
 
