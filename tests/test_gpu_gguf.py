@@ -241,6 +241,31 @@ def test_q6k_prefill_on_the_tensor_core(K, gk, oracle, torch, n, k, m, bf16):
     w.free()
 
 
+def test_q6k_grouped_experts(K, gk, oracle, torch):
+    """gllmk_gemm_grouped takes Q6_K experts through the same kernel (one launch for all groups); the four formats
+    without a tensor-core kernel are refused."""
+    qt = qtype(gk, "q6_k")
+    n, k, counts = 200, 3 * 256, [40, 0, 130, 7]
+    blocks = [random_blocks("q6_k", qt, n, k, 500 + e) for e in range(len(counts))]
+    ws = [K.upload(qt, n, k, b) for b in blocks]
+    offs = np.concatenate([[0], np.cumsum(counts)]).astype(np.int64)
+    xd = torch.from_numpy(np.random.default_rng(51).standard_normal((int(offs[-1]), k)).astype(np.float32)).cuda().to(torch.bfloat16)
+    x = xd.to(torch.float32).cpu().numpy()
+    y = K.gemm_grouped(ws, xd, offs).to(torch.float32).cpu().numpy()
+    assert K.status() == 0
+    for e, b in enumerate(blocks):
+        if counts[e]:
+            ref = oracle.gemm_f32_nt(x[offs[e]:offs[e + 1]], oracle_matrix(oracle, qt, b, n, k))
+            assert oracle.rel_err(y[offs[e]:offs[e + 1]], ref) <= 1e-2, e
+    for w in ws:
+        w.free()
+    q5 = qtype(gk, "q5_k")
+    w5 = K.upload(q5, 64, 256, random_blocks("q5_k", q5, 64, 256, 9))
+    with pytest.raises(gk.GllmkError):
+        K.gemm_grouped([w5], xd[:8, :256].contiguous(), [0, 8])
+    w5.free()
+
+
 @pytest.mark.parametrize("name", FORMATS)
 def test_family_matmul_host(K, gk, oracle, name):
     """kquant_matmul / classic_matmul with host arrays: m weight rows, n batch columns, input [k, n], output [m, n]."""
