@@ -339,6 +339,13 @@ struct Dequant<FMT_MXFP4> : DequantFp4<FMT_MXFP4> {};
 // ql[hh * 64 + (j % 2) * 32 + l] and bits 2j, 2j + 1 of qh[hh * 32 + l], l = 0 .. 31; scale sc[hh * 8 + l / 16 + 2 j].
 // A word of four 6-bit values becomes the s8 word 4 (q - 32) (bit 5 flipped, two places up), that the fp16 pairs
 // 4 (q - 32) exactly (the byte in the mantissa of 1024, as for Q8_0), times d * sc / 4 rounded to fp16.
+// 16 bytes global -> shared without passing registers; and "this thread's copies so far" as one arrival at an mbarrier
+__device__ __forceinline__ void cp_async16_s(uint32_t dst_smem, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst_smem), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(bar) : "memory");
+}
 __device__ __forceinline__ uint32_t q6k_word(uint32_t lo4, uint32_t hi2_at_4) {
     return ((((lo4 & 0x0F0F0F0Fu) | (hi2_at_4 & 0x30303030u)) ^ 0x20202020u) << 2) & 0xFCFCFCFCu;
 }
@@ -459,7 +466,7 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
             tc::mbar_init(emptyB + 8 * s, (uint32_t)mt);  // one commit per MMA issuer
         }
         for (int s = 0; s < WQ_MAX_R; s++) {
-            tc::mbar_init(rawfull + 8 * s, 1);
+            tc::mbar_init(rawfull + 8 * s, FMT == FMT_Q6K ? 32 : 1);  // Q6_K: one arrival per lane of the copy warp
             tc::mbar_init(rawempty + 8 * s, WQ_DW / mt);  // the warps that read a super-chunk
         }
         tc::mbar_init(accum, (uint32_t)mt);
@@ -473,7 +480,11 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
     WQP_DECL;
 
     if (warp == 0 && FMT == FMT_Q6K) {
-        // ---------------- raw weight blocks: one block of each of the tile's 128 rows per super-chunk, four bulk copies per lane ----------------
+        // ---------------- raw weight blocks: one block of each of the tile's 128 rows per super-chunk ----------------
+        // The blocks of a tile lie a whole row apart in memory, so a super-chunk is 128 pieces of 224 bytes.  As 128 bulk
+        // copies they paced the kernel (a copy engine request per piece: ~1.8 k cycles per tile step); the whole warp
+        // copies them with 16-byte cp.async instead — lane = consecutive chunk, 56 per lane — and every lane's copies
+        // arrive at the slot's barrier when they have landed (cp.async.mbarrier.arrive.noinc).
         int slot = 0, round = 0;
         bool ok = true;
         for (int jl = 0; jl < njb && ok; jl++) {
@@ -487,15 +498,19 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
                 ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
                 if (!ok) break;
                 const uint32_t dst = smem_s + raw_off + (uint32_t)(slot * RAW);
-                if (lane == 0) tc::mbar_expect_tx(rawfull + 8 * slot, 128u * Q6K_SLOT);
-                __syncwarp();
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const int r = lane + 32 * i;
-                    int64_t row = (int64_t)(tile0 + ti) * WQ_BM + r;
-                    if (row >= p.n) row = p.n - 1;  // rows past the matrix repeat the last one; their results are not stored
-                    bulk_g2s(dst + (uint32_t)(r * Q6K_ROW_STRIDE), G.qs[grp_id] + ((size_t)row * p.nsc + jb) * Q6K_SLOT, Q6K_SLOT, rawfull + 8 * slot);
+                const int64_t trow0 = (int64_t)(tile0 + ti) * WQ_BM;
+                const int rmax = (int)(p.n - 1 - trow0 < WQ_BM - 1 ? p.n - 1 - trow0 : WQ_BM - 1);  // rows past the matrix repeat the last one; not stored
+                const uint8_t *src = G.qs[grp_id] + ((size_t)trow0 * p.nsc + jb) * Q6K_SLOT;
+                const size_t row_bytes = (size_t)p.nsc * Q6K_SLOT;
+                int r = lane / 14, ch = lane % 14;  // chunk lane + 32 j of the tile's 128 x 14: row r, 16-byte chunk ch
+#pragma unroll 4
+                for (int j = 0; j < WQ_BM * (Q6K_SLOT / 16) / 32; j++) {
+                    const int rc = r < rmax ? r : rmax;
+                    cp_async16_s(dst + (uint32_t)(r * Q6K_ROW_STRIDE + 16 * ch), src + (size_t)rc * row_bytes + 16 * ch);
+                    r += 2, ch += 4;  // 32 chunks on: two rows and four chunks
+                    if (ch >= 14) ch -= 14, r++;
                 }
+                cp_async_arrive(rawfull + 8 * slot);
                 if (++slot == p.r) slot = 0, round++;
             }
         }
