@@ -37,11 +37,17 @@ constexpr int WQ_CTRL = 4;         // warp 0: raw copies, warp 1: activation cop
 constexpr int WQ_THREADS = 32 * (WQ_CTRL + WQ_DW);  // then the dequant / epilogue warps
 constexpr int WQ_SMEM_LIMIT = 232448 - 1024 - 1024;  // ring space: 227 KB less the static variables' share and the alignment slack
 
-enum { FMT_Q4K = 0, FMT_Q80 = 1, FMT_NVFP4 = 2, FMT_MXFP4 = 3, FMT_Q6K = 4 };
+enum { FMT_Q4K = 0, FMT_Q80 = 1, FMT_NVFP4 = 2, FMT_MXFP4 = 3, FMT_Q6K = 4, FMT_Q5K = 5 };
+// Q6_K and Q5_K stay on the device as the reference stores them, row after row of blocks (these kernels' other formats
+// are repacked into tile images): a raw super-chunk is then one block of each of a tile's 128 rows.
 constexpr int Q6K_SLOT = 224;        // a Q6_K block (210 bytes) on the device: reference layout in a 16-byte aligned slot
 constexpr int Q6K_ROW_STRIDE = 240;  // and in shared memory, so that eight rows' 16-byte words fall on different banks
+constexpr int Q5K_SLOT = 176;        // a Q5_K block: 11 x 16 bytes, an odd count, so its own size is a conflict-free stride
+constexpr bool wq_row_major(int fmt) { return fmt == FMT_Q6K || fmt == FMT_Q5K; }
+constexpr int wq_slot(int fmt) { return fmt == FMT_Q6K ? Q6K_SLOT : Q5K_SLOT; }
+constexpr int wq_row_stride(int fmt) { return fmt == FMT_Q6K ? Q6K_ROW_STRIDE : Q5K_SLOT; }
 __host__ __device__ constexpr int wq_raw_bytes(int fmt) {
-    return fmt == FMT_Q4K ? 8 * Q4K_CHUNK : (fmt == FMT_Q80 ? 8 * Q80_CHUNK : (fmt == FMT_NVFP4 ? WQ_TILE + 2048 : (fmt == FMT_MXFP4 ? WQ_TILE + 1024 : 128 * Q6K_ROW_STRIDE)));
+    return fmt == FMT_Q4K ? 8 * Q4K_CHUNK : (fmt == FMT_Q80 ? 8 * Q80_CHUNK : (fmt == FMT_NVFP4 ? WQ_TILE + 2048 : (fmt == FMT_MXFP4 ? WQ_TILE + 1024 : 128 * wq_row_stride(fmt))));
 }
 
 constexpr int WQ_MAX_GROUPS = 32;      // weights (experts) per launch
@@ -392,6 +398,56 @@ struct Dequant<FMT_Q6K> {
     }
 };
 
+// Q5_K (k_quant.rs:381-436): d f16 @0, dmin f16 @2, scales[12] @4, qh[32] @16, qs[128] @48.  Thread = weight row.  k-step p
+// is the 64-element group p: its first 32 elements are the low nibbles of qs[32 p + l] with bit 2p of qh[l] on top
+// (sub-block 2p), the next 32 the high nibbles with bit 2p + 1 (sub-block 2p + 1); value = q * d*sc - dmin*m as for Q4_K.
+template <>
+struct Dequant<FMT_Q5K> {
+    float global;
+    __device__ __forceinline__ void compute(const uint8_t *raw, int p, int wg, int lane, uint4 (&o)[8]) {
+        const uint8_t *b = raw + (32 * wg + lane) * Q5K_SLOT;
+        const uint4 hd = *reinterpret_cast<const uint4 *>(b);  // d, dmin and the twelve scale bytes
+        const float d = __half2float(__ushort_as_half((unsigned short)(hd.x & 0xFFFFu)));
+        const float dmin = __half2float(__ushort_as_half((unsigned short)(hd.x >> 16)));
+        __half2 e[2];  // (d*sc, -dmin*m) of sub-blocks 2p and 2p + 1 (get_scale_min_k4, k_quant.rs:388-397, without a branch)
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const int j = 2 * p + i, sh = 8 * (j & 3);
+            const uint32_t a = (hd.y >> sh) & 0xFFu, bb = (hd.z >> sh) & 0xFFu, c = (hd.w >> sh) & 0xFFu;
+            const uint32_t sc = j < 4 ? (a & 63u) : ((c & 0xFu) | ((a >> 6) << 4)), mn = j < 4 ? (bb & 63u) : ((c >> 4) | ((bb >> 6) << 4));
+            e[i] = __floats2half2_rn(d * (float)sc, -(dmin * (float)mn));
+        }
+#pragma unroll
+        for (int half = 0; half < 2; half++) {  // l = 16 half .. 16 half + 15
+            const uint4 Q = *reinterpret_cast<const uint4 *>(b + 48 + 32 * p + 16 * half);
+            const uint4 H = *reinterpret_cast<const uint4 *>(b + 16 + 16 * half);
+            const uint32_t qw[4] = {Q.x, Q.y, Q.z, Q.w}, hw[4] = {H.x, H.y, H.z, H.w};
+#pragma unroll
+            for (int i = 0; i < 2; i++)      // sub-block 2p + i: nibble i, qh bit 2p + i
+#pragma unroll
+                for (int c = 0; c < 2; c++) {  // eight elements: words 2c, 2c + 1
+                    uint4 &out = o[4 * i + 2 * half + c];  // k = 32 i + 16 half + 8 c .. + 7 of the step
+                    uint32_t r[4];
+#pragma unroll
+                    for (int w = 0; w < 2; w++) {
+                        const uint32_t q = ((qw[2 * c + w] >> (4 * i)) & 0x0F0F0F0Fu) | (((hw[2 * c + w] >> (2 * p + i)) & 0x01010101u) << 4);
+                        __half2 lo, hi;
+                        bytes_to_h2(q, 1024.0f, lo, hi);
+                        r[2 * w] = h2_as_u32(__hfma2(lo, __low2half2(e[i]), __high2half2(e[i])));
+                        r[2 * w + 1] = h2_as_u32(__hfma2(hi, __low2half2(e[i]), __high2half2(e[i])));
+                    }
+                    out = make_uint4(r[0], r[1], r[2], r[3]);
+                }
+        }
+    }
+    __device__ __forceinline__ void store(uint8_t *at, int wg, int lane, const uint4 (&o)[8]) {
+        const int r = 32 * wg + lane;
+        uint8_t *rowp = at + r * 128;
+#pragma unroll
+        for (int c = 0; c < 8; c++) *reinterpret_cast<uint4 *>(rowp + ((c ^ (r & 7)) << 4)) = o[c];
+    }
+};
+
 // ---- the kernel -----------------------------------------------------------------------------------
 // grid: (token tiles, groups of MT weight-row tiles): CTAs that share weight tiles run side by side, so the
 // second reader finds the raw bytes in L2.
@@ -466,7 +522,7 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
             tc::mbar_init(emptyB + 8 * s, (uint32_t)mt);  // one commit per MMA issuer
         }
         for (int s = 0; s < WQ_MAX_R; s++) {
-            tc::mbar_init(rawfull + 8 * s, FMT == FMT_Q6K ? 32 : 1);  // Q6_K: one arrival per lane of the copy warp
+            tc::mbar_init(rawfull + 8 * s, wq_row_major(FMT) ? 32 : 1);  // row-major formats: one arrival per lane of the copy warp
             tc::mbar_init(rawempty + 8 * s, WQ_DW / mt);  // the warps that read a super-chunk
         }
         tc::mbar_init(accum, (uint32_t)mt);
@@ -479,12 +535,13 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
     const uint32_t tmem_d = tmem_base_s;
     WQP_DECL;
 
-    if (warp == 0 && FMT == FMT_Q6K) {
+    if (warp == 0 && wq_row_major(FMT)) {
+        constexpr int SLOT = wq_slot(FMT), RSTRIDE = wq_row_stride(FMT), CPR = SLOT / 16;  // 16-byte chunks per row piece
         // ---------------- raw weight blocks: one block of each of the tile's 128 rows per super-chunk ----------------
-        // The blocks of a tile lie a whole row apart in memory, so a super-chunk is 128 pieces of 224 bytes.  As 128 bulk
-        // copies they paced the kernel (a copy engine request per piece: ~1.8 k cycles per tile step); the whole warp
-        // copies them with 16-byte cp.async instead — lane = consecutive chunk, 56 per lane — and every lane's copies
-        // arrive at the slot's barrier when they have landed (cp.async.mbarrier.arrive.noinc).
+        // The blocks of a tile lie a whole row apart in memory, so a super-chunk is 128 pieces of 224 (176) bytes.  As 128
+        // bulk copies they paced the kernel (a copy engine request per piece: ~1.8 k cycles per tile step); the whole warp
+        // copies them with 16-byte cp.async instead — lane = consecutive chunk, 56 (44) per lane — and every lane's
+        // copies arrive at the slot's barrier when they have landed (cp.async.mbarrier.arrive.noinc).
         int slot = 0, round = 0;
         bool ok = true;
         for (int jl = 0; jl < njb && ok; jl++) {
@@ -500,15 +557,15 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
                 const uint32_t dst = smem_s + raw_off + (uint32_t)(slot * RAW);
                 const int64_t trow0 = (int64_t)(tile0 + ti) * WQ_BM;
                 const int rmax = (int)(p.n - 1 - trow0 < WQ_BM - 1 ? p.n - 1 - trow0 : WQ_BM - 1);  // rows past the matrix repeat the last one; not stored
-                const uint8_t *src = G.qs[grp_id] + ((size_t)trow0 * p.nsc + jb) * Q6K_SLOT;
-                const size_t row_bytes = (size_t)p.nsc * Q6K_SLOT;
-                int r = lane / 14, ch = lane % 14;  // chunk lane + 32 j of the tile's 128 x 14: row r, 16-byte chunk ch
+                const uint8_t *src = G.qs[grp_id] + ((size_t)trow0 * p.nsc + jb) * SLOT;
+                const size_t row_bytes = (size_t)p.nsc * SLOT;
+                int r = lane / CPR, ch = lane % CPR;  // chunk lane + 32 j of the tile's 128 x CPR: row r, 16-byte chunk ch
 #pragma unroll 4
-                for (int j = 0; j < WQ_BM * (Q6K_SLOT / 16) / 32; j++) {
+                for (int j = 0; j < WQ_BM * CPR / 32; j++) {
                     const int rc = r < rmax ? r : rmax;
-                    cp_async16_s(dst + (uint32_t)(r * Q6K_ROW_STRIDE + 16 * ch), src + (size_t)rc * row_bytes + 16 * ch);
-                    r += 2, ch += 4;  // 32 chunks on: two rows and four chunks
-                    if (ch >= 14) ch -= 14, r++;
+                    cp_async16_s(dst + (uint32_t)(r * RSTRIDE + 16 * ch), src + (size_t)rc * row_bytes + 16 * ch);
+                    r += 32 / CPR, ch += 32 % CPR;  // 32 chunks on
+                    if (ch >= CPR) ch -= CPR, r++;
                 }
                 cp_async_arrive(rawfull + 8 * slot);
                 if (++slot == p.r) slot = 0, round++;
@@ -772,7 +829,7 @@ static int32_t gemm_groups_chunk(Ctx *c, const Weight *const *ws, int ng, const 
                                  const int64_t *tok_begin, const int64_t *tok_count, int ntok, void *y, int y_bf16, int64_t ldy,
                                  cudaStream_t s, const void *a_up) {
     const Weight *w = ws[0];
-    const int fmt = w->qt == GLLMK_QUANT_Q4K ? FMT_Q4K : (w->qt == GLLMK_QUANT_Q8_0 ? FMT_Q80 : (w->qt == GLLMK_QUANT_NVFP4 ? FMT_NVFP4 : (w->qt == GLLMK_QUANT_Q6_K ? FMT_Q6K : FMT_MXFP4)));
+    const int fmt = w->qt == GLLMK_QUANT_Q4K ? FMT_Q4K : (w->qt == GLLMK_QUANT_Q8_0 ? FMT_Q80 : (w->qt == GLLMK_QUANT_NVFP4 ? FMT_NVFP4 : (w->qt == GLLMK_QUANT_Q6_K ? FMT_Q6K : (w->qt == GLLMK_QUANT_Q5_K ? FMT_Q5K : FMT_MXFP4))));
     const int raw = wq_raw_bytes(fmt);
     GemmParams p{};
     GemmGroups G{};
@@ -887,6 +944,7 @@ static int32_t gemm_groups_chunk(Ctx *c, const Weight *const *ws, int ng, const 
         case FMT_Q80: return launch_wq_mt<FMT_Q80>(c, p, G, mt, grid, smem, s);
         case FMT_NVFP4: return launch_wq_mt<FMT_NVFP4>(c, p, G, mt, grid, smem, s);
         case FMT_Q6K: return launch_wq_mt<FMT_Q6K>(c, p, G, mt, grid, smem, s);
+        case FMT_Q5K: return launch_wq_mt<FMT_Q5K>(c, p, G, mt, grid, smem, s);
         default: return launch_wq_mt<FMT_MXFP4>(c, p, G, mt, grid, smem, s);
     }
 }
@@ -895,7 +953,7 @@ static int32_t gemm_groups_chunk(Ctx *c, const Weight *const *ws, int ng, const 
 int32_t gemm_grouped_launch(Ctx *c, const Weight *const *ws, int n_groups, const void *a, int a_bf16, int64_t lda,
                             const int64_t *row_offsets, void *y, int y_bf16, int64_t ldy, cudaStream_t s, const void *a_up) {
     const int align = a_bf16 ? 8 : 4;
-    if ((ws[0]->qt < GLLMK_QUANT_Q4K || ws[0]->qt > GLLMK_QUANT_NVFP4) && ws[0]->qt != GLLMK_QUANT_Q6_K)
+    if ((ws[0]->qt < GLLMK_QUANT_Q4K || ws[0]->qt > GLLMK_QUANT_NVFP4) && ws[0]->qt != GLLMK_QUANT_Q6_K && ws[0]->qt != GLLMK_QUANT_Q5_K)
         return fail(c, GLLMK_STATUS_UNSUPPORTED, "gemm: weight type %d is not block-quantized (use gllmk_gemm_int8)", ws[0]->qt);
     if (((uintptr_t)a & 15) || (lda % align)) return fail(c, GLLMK_STATUS_INVALID_ARG, "gemm: activations must be 16-byte aligned rows");
     if (ws[0]->k % 8) return fail(c, GLLMK_STATUS_INVALID_ARG, "gemm: k=%lld is not a multiple of 8", (long long)ws[0]->k);

@@ -241,9 +241,30 @@ def test_q6k_prefill_on_the_tensor_core(K, gk, oracle, torch, n, k, m, bf16):
     w.free()
 
 
+@pytest.mark.parametrize("n,k,m,bf16", [(96, 512, 70, False), (300, 5 * 256, 17, True), (130, 256, 300, False), (1000, 12 * 256, 130, True),
+                                        (20000, 512, 200, True)])
+def test_q5k_prefill_on_the_tensor_core(K, gk, oracle, torch, n, k, m, bf16):
+    """Q5_K with more than 16 tokens on the same kernel: reference-layout blocks (176 bytes), thread = weight row, the fifth
+    bit from qh on top of the nibble, value = q * d*sc - dmin*m in fp16 as for Q4_K."""
+    qt = qtype(gk, "q5_k")
+    blocks = random_blocks("q5_k", qt, n, k, 600 + m)
+    x = np.random.default_rng(61 + m).standard_normal((m, k)).astype(np.float32)
+    xd = torch.from_numpy(x).cuda()
+    if bf16:
+        xd = xd.to(torch.bfloat16)
+        x = xd.to(torch.float32).cpu().numpy()
+    w = K.upload(qt, n, k, blocks)
+    y = K.gemm(w, xd, out_dtype=torch.bfloat16 if bf16 else torch.float32).to(torch.float32).cpu().numpy()
+    assert K.status() == 0
+    rows = np.random.default_rng(4).choice(n, size=min(n, 256), replace=False)
+    ref = oracle.gemm_f32_nt(x, oracle_matrix(oracle, qt, blocks, n, k)[rows])
+    assert oracle.rel_err(y[:, rows], ref) <= 1e-2 + (2.0 ** -8 if bf16 else 0.0)
+    w.free()
+
+
 def test_q6k_grouped_experts(K, gk, oracle, torch):
-    """gllmk_gemm_grouped takes Q6_K experts through the same kernel (one launch for all groups); the four formats
-    without a tensor-core kernel are refused."""
+    """gllmk_gemm_grouped takes Q6_K experts through the same kernel (one launch for all groups); the formats without a
+    tensor-core kernel are refused."""
     qt = qtype(gk, "q6_k")
     n, k, counts = 200, 3 * 256, [40, 0, 130, 7]
     blocks = [random_blocks("q6_k", qt, n, k, 500 + e) for e in range(len(counts))]
@@ -259,11 +280,11 @@ def test_q6k_grouped_experts(K, gk, oracle, torch):
             assert oracle.rel_err(y[offs[e]:offs[e + 1]], ref) <= 1e-2, e
     for w in ws:
         w.free()
-    q5 = qtype(gk, "q5_k")
-    w5 = K.upload(q5, 64, 256, random_blocks("q5_k", q5, 64, 256, 9))
+    q4 = qtype(gk, "q4_0")
+    w4 = K.upload(q4, 64, 256, random_blocks("q4_0", q4, 64, 256, 9))
     with pytest.raises(gk.GllmkError):
-        K.gemm_grouped([w5], xd[:8, :256].contiguous(), [0, 8])
-    w5.free()
+        K.gemm_grouped([w4], xd[:8, :256].contiguous(), [0, 8])
+    w4.free()
 
 
 @pytest.mark.parametrize("name", FORMATS)
