@@ -242,9 +242,9 @@ def test_q6k_prefill_on_the_tensor_core(K, gk, oracle, torch, n, k, m, bf16):
 
 
 @pytest.mark.parametrize("n,k,m,bf16", [(96, 512, 70, False), (300, 5 * 256, 17, True), (130, 256, 300, False), (1000, 12 * 256, 130, True),
-                                        (20000, 512, 200, True)])
+                                        (20000, 512, 200, True), (64, 256, 2, False), (200, 3 * 256, 9, False)])
 def test_q5k_prefill_on_the_tensor_core(K, gk, oracle, torch, n, k, m, bf16):
-    """Q5_K with more than 16 tokens on the same kernel: reference-layout blocks (176 bytes), thread = weight row, the fifth
+    """Q5_K with two tokens and more (gllmk_gemm) on the same kernel: reference-layout blocks (176 bytes), thread = weight row, the fifth
     bit from qh on top of the nibble, value = q * d*sc - dmin*m in fp16 as for Q4_K."""
     qt = qtype(gk, "q5_k")
     blocks = random_blocks("q5_k", qt, n, k, 600 + m)
