@@ -481,7 +481,9 @@ int32_t gllmk_gemm(gllmk_ctx ctx, gllmk_weight wh, const void *a_dev, int32_t a_
     // Q6_K and Q5_K have a place in the fused-dequant tensor-core GEMM.  On W[8192, 28672]: Q6_K 160 - 172 us at 17 - 128
     // tokens (two passes of its batch GEMV: 256 us; one pass, up to 16 tokens: 100 - 135 us); Q5_K, which has no batch GEMV,
     // 141 us against 167 us (2 tokens) ... 590 us (16 tokens) on the dp2a kernel
-    if ((w->qt == GLLMK_QUANT_Q6_K && m > GLLMK_GEMM_GEMV_MAX_M) || (w->qt == GLLMK_QUANT_Q5_K && m >= 2))
+    // Q4_0 / Q5_0: when a row's blocks come in whole groups of eight (k a multiple of 256: rows 16-byte aligned)
+    if ((w->qt == GLLMK_QUANT_Q6_K && m > GLLMK_GEMM_GEMV_MAX_M) || (w->qt == GLLMK_QUANT_Q5_K && m >= 2) ||
+        ((w->qt == GLLMK_QUANT_Q4_0 || w->qt == GLLMK_QUANT_Q5_0) && w->k % 256 == 0 && m >= 2))  // 119 / 140 us against 150 / 157 us (2 tokens) on dp2a
         return gemm_launch(c, w, a_dev, a_dtype == GLLMK_DTYPE_BF16, lda, m, y_dev, y_dtype == GLLMK_DTYPE_BF16, ldy,
                            static_cast<cudaStream_t>(stream));
     if (raw_format(w->qt)) {

@@ -37,15 +37,17 @@ constexpr int WQ_CTRL = 4;         // warp 0: raw copies, warp 1: activation cop
 constexpr int WQ_THREADS = 32 * (WQ_CTRL + WQ_DW);  // then the dequant / epilogue warps
 constexpr int WQ_SMEM_LIMIT = 232448 - 1024 - 1024;  // ring space: 227 KB less the static variables' share and the alignment slack
 
-enum { FMT_Q4K = 0, FMT_Q80 = 1, FMT_NVFP4 = 2, FMT_MXFP4 = 3, FMT_Q6K = 4, FMT_Q5K = 5 };
+enum { FMT_Q4K = 0, FMT_Q80 = 1, FMT_NVFP4 = 2, FMT_MXFP4 = 3, FMT_Q6K = 4, FMT_Q5K = 5, FMT_Q40 = 6, FMT_Q50 = 7 };
 // Q6_K and Q5_K stay on the device as the reference stores them, row after row of blocks (these kernels' other formats
 // are repacked into tile images): a raw super-chunk is then one block of each of a tile's 128 rows.
 constexpr int Q6K_SLOT = 224;        // a Q6_K block (210 bytes) on the device: reference layout in a 16-byte aligned slot
 constexpr int Q6K_ROW_STRIDE = 240;  // and in shared memory, so that eight rows' 16-byte words fall on different banks
 constexpr int Q5K_SLOT = 176;        // a Q5_K block: 11 x 16 bytes, an odd count, so its own size is a conflict-free stride
-constexpr bool wq_row_major(int fmt) { return fmt == FMT_Q6K || fmt == FMT_Q5K; }
-constexpr int wq_slot(int fmt) { return fmt == FMT_Q6K ? Q6K_SLOT : Q5K_SLOT; }
-constexpr int wq_row_stride(int fmt) { return fmt == FMT_Q6K ? Q6K_ROW_STRIDE : Q5K_SLOT; }
+constexpr int Q40_SLOT = 144;        // eight Q4_0 blocks (18 bytes, 32 elements each) = 256 elements of a row whose k is a multiple of 256
+constexpr int Q50_SLOT = 176;        // eight Q5_0 blocks (22 bytes)
+constexpr bool wq_row_major(int fmt) { return fmt >= FMT_Q6K; }
+constexpr int wq_slot(int fmt) { return fmt == FMT_Q6K ? Q6K_SLOT : (fmt == FMT_Q40 ? Q40_SLOT : (fmt == FMT_Q5K ? Q5K_SLOT : Q50_SLOT)); }
+constexpr int wq_row_stride(int fmt) { return fmt == FMT_Q6K ? Q6K_ROW_STRIDE : wq_slot(fmt); }
 __host__ __device__ constexpr int wq_raw_bytes(int fmt) {
     return fmt == FMT_Q4K ? 8 * Q4K_CHUNK : (fmt == FMT_Q80 ? 8 * Q80_CHUNK : (fmt == FMT_NVFP4 ? WQ_TILE + 2048 : (fmt == FMT_MXFP4 ? WQ_TILE + 1024 : 128 * wq_row_stride(fmt))));
 }
@@ -448,6 +450,68 @@ struct Dequant<FMT_Q5K> {
     }
 };
 
+// Q4_0 / Q5_0 (classic.rs:15-29, 484-504): blocks of 32 elements, 18 / 22 bytes: d f16, (Q5_0: qh u32 = the fifth bits,)
+// qs[16]: byte j holds elements j (low nibble) and j + 16 (high).  Thread = weight row; k-step p is blocks 2p and 2p + 1 of
+// the row's eight.  A block starts on a 2-byte boundary only: an even block's fields are read as aligned words from the
+// block start and shifted down 16 bits; an odd block's qs (and qh) are word-aligned themselves.
+__device__ __forceinline__ uint32_t spread4_bits(uint32_t v) { return ((v & 0xFu) * 0x00204081u) & 0x01010101u; }  // bits 0..3 -> bit 0 of bytes 0..3
+template <int FMT>
+struct DequantClassic {
+    float global;
+    static constexpr int BB = FMT == FMT_Q40 ? 18 : 22, QS = FMT == FMT_Q40 ? 2 : 6, BIAS = FMT == FMT_Q40 ? 8 : 16;
+    __device__ __forceinline__ void compute(const uint8_t *raw, int p, int wg, int lane, uint4 (&o)[8]) {
+        const uint8_t *row = raw + (32 * wg + lane) * wq_slot(FMT);
+#pragma unroll
+        for (int i = 0; i < 2; i++) {  // block 2p + i; its parity is i
+            const uint8_t *b = row + (2 * p + i) * BB;
+            uint32_t qs[4], qh = 0, dbits;
+            if (i == 0) {  // block start word-aligned: words from the start, fields 16 bits further on
+                const uint32_t *w = reinterpret_cast<const uint32_t *>(b);
+                constexpr int NW = (BB + 2 + 3) / 4;
+                uint32_t v[NW];
+#pragma unroll
+                for (int j = 0; j < NW; j++) v[j] = w[j];
+                dbits = v[0] & 0xFFFFu;
+                if (FMT == FMT_Q50) qh = __funnelshift_r(v[0], v[1], 16);
+#pragma unroll
+                for (int j = 0; j < 4; j++) qs[j] = __funnelshift_r(v[QS / 4 + j], v[QS / 4 + j + 1], 16);
+            } else {  // block start = 2 mod 4: d is a half-word, everything after it word-aligned
+                dbits = *reinterpret_cast<const unsigned short *>(b);
+                if (FMT == FMT_Q50) qh = *reinterpret_cast<const uint32_t *>(b + 2);
+#pragma unroll
+                for (int j = 0; j < 4; j++) qs[j] = *reinterpret_cast<const uint32_t *>(b + QS + 4 * j);
+            }
+            const __half2 d2 = __half2half2(__ushort_as_half((unsigned short)dbits));
+#pragma unroll
+            for (int hi = 0; hi < 2; hi++)      // low nibbles = elements 0 .. 15, high = 16 .. 31
+#pragma unroll
+                for (int c = 0; c < 2; c++) {  // eight elements: words 2c, 2c + 1
+                    uint32_t r[4];
+#pragma unroll
+                    for (int w = 0; w < 2; w++) {
+                        uint32_t q = (qs[2 * c + w] >> (4 * hi)) & 0x0F0F0F0Fu;
+                        if (FMT == FMT_Q50) q |= spread4_bits(qh >> (16 * hi + 4 * (2 * c + w))) << 4;
+                        __half2 lo2, hi2;
+                        bytes_to_h2(q, 1024.0f + (float)BIAS, lo2, hi2);  // q - 8 (q - 16), exact
+                        r[2 * w] = h2_as_u32(__hmul2(lo2, d2));
+                        r[2 * w + 1] = h2_as_u32(__hmul2(hi2, d2));
+                    }
+                    o[4 * i + 2 * hi + c] = make_uint4(r[0], r[1], r[2], r[3]);  // k = 32 i + 16 hi + 8 c .. + 7 of the step
+                }
+        }
+    }
+    __device__ __forceinline__ void store(uint8_t *at, int wg, int lane, const uint4 (&o)[8]) {
+        const int r = 32 * wg + lane;
+        uint8_t *rowp = at + r * 128;
+#pragma unroll
+        for (int c = 0; c < 8; c++) *reinterpret_cast<uint4 *>(rowp + ((c ^ (r & 7)) << 4)) = o[c];
+    }
+};
+template <>
+struct Dequant<FMT_Q40> : DequantClassic<FMT_Q40> {};
+template <>
+struct Dequant<FMT_Q50> : DequantClassic<FMT_Q50> {};
+
 // ---- the kernel -----------------------------------------------------------------------------------
 // grid: (token tiles, groups of MT weight-row tiles): CTAs that share weight tiles run side by side, so the
 // second reader finds the raw bytes in L2.
@@ -829,7 +893,7 @@ static int32_t gemm_groups_chunk(Ctx *c, const Weight *const *ws, int ng, const 
                                  const int64_t *tok_begin, const int64_t *tok_count, int ntok, void *y, int y_bf16, int64_t ldy,
                                  cudaStream_t s, const void *a_up) {
     const Weight *w = ws[0];
-    const int fmt = w->qt == GLLMK_QUANT_Q4K ? FMT_Q4K : (w->qt == GLLMK_QUANT_Q8_0 ? FMT_Q80 : (w->qt == GLLMK_QUANT_NVFP4 ? FMT_NVFP4 : (w->qt == GLLMK_QUANT_Q6_K ? FMT_Q6K : (w->qt == GLLMK_QUANT_Q5_K ? FMT_Q5K : FMT_MXFP4))));
+    const int fmt = w->qt == GLLMK_QUANT_Q4K ? FMT_Q4K : (w->qt == GLLMK_QUANT_Q8_0 ? FMT_Q80 : (w->qt == GLLMK_QUANT_NVFP4 ? FMT_NVFP4 : (w->qt == GLLMK_QUANT_Q6_K ? FMT_Q6K : (w->qt == GLLMK_QUANT_Q5_K ? FMT_Q5K : (w->qt == GLLMK_QUANT_Q4_0 ? FMT_Q40 : (w->qt == GLLMK_QUANT_Q5_0 ? FMT_Q50 : FMT_MXFP4))))));
     const int raw = wq_raw_bytes(fmt);
     GemmParams p{};
     GemmGroups G{};
@@ -945,6 +1009,8 @@ static int32_t gemm_groups_chunk(Ctx *c, const Weight *const *ws, int ng, const 
         case FMT_NVFP4: return launch_wq_mt<FMT_NVFP4>(c, p, G, mt, grid, smem, s);
         case FMT_Q6K: return launch_wq_mt<FMT_Q6K>(c, p, G, mt, grid, smem, s);
         case FMT_Q5K: return launch_wq_mt<FMT_Q5K>(c, p, G, mt, grid, smem, s);
+        case FMT_Q40: return launch_wq_mt<FMT_Q40>(c, p, G, mt, grid, smem, s);
+        case FMT_Q50: return launch_wq_mt<FMT_Q50>(c, p, G, mt, grid, smem, s);
         default: return launch_wq_mt<FMT_MXFP4>(c, p, G, mt, grid, smem, s);
     }
 }
@@ -953,7 +1019,9 @@ static int32_t gemm_groups_chunk(Ctx *c, const Weight *const *ws, int ng, const 
 int32_t gemm_grouped_launch(Ctx *c, const Weight *const *ws, int n_groups, const void *a, int a_bf16, int64_t lda,
                             const int64_t *row_offsets, void *y, int y_bf16, int64_t ldy, cudaStream_t s, const void *a_up) {
     const int align = a_bf16 ? 8 : 4;
-    if ((ws[0]->qt < GLLMK_QUANT_Q4K || ws[0]->qt > GLLMK_QUANT_NVFP4) && ws[0]->qt != GLLMK_QUANT_Q6_K && ws[0]->qt != GLLMK_QUANT_Q5_K)
+    const bool row_major_ok = ws[0]->qt == GLLMK_QUANT_Q6_K || ws[0]->qt == GLLMK_QUANT_Q5_K ||
+                              ((ws[0]->qt == GLLMK_QUANT_Q4_0 || ws[0]->qt == GLLMK_QUANT_Q5_0) && ws[0]->k % 256 == 0);
+    if ((ws[0]->qt < GLLMK_QUANT_Q4K || ws[0]->qt > GLLMK_QUANT_NVFP4) && !row_major_ok)
         return fail(c, GLLMK_STATUS_UNSUPPORTED, "gemm: weight type %d is not block-quantized (use gllmk_gemm_int8)", ws[0]->qt);
     if (((uintptr_t)a & 15) || (lda % align)) return fail(c, GLLMK_STATUS_INVALID_ARG, "gemm: activations must be 16-byte aligned rows");
     if (ws[0]->k % 8) return fail(c, GLLMK_STATUS_INVALID_ARG, "gemm: k=%lld is not a multiple of 8", (long long)ws[0]->k);

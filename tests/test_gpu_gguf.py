@@ -202,9 +202,9 @@ def test_gemv_long_rows_and_row_scales(K, gk, oracle, torch, name):
 
 def test_gemm_many_tokens_f32(K, gk, oracle, torch):
     """gllmk_gemm with a format that has no tensor-core kernel runs the streaming kernel over token tiles; bf16 operands are refused."""
-    qt = qtype(gk, "q5_0")
+    qt = qtype(gk, "q8_k")
     n, k, m = 96, 512, 70
-    blocks = random_blocks("q5_0", qt, n, k, 21)
+    blocks = random_blocks("q8_k", qt, n, k, 21)
     x = np.random.default_rng(22).standard_normal((m, k)).astype(np.float32)
     ref = oracle.quant_matmul(blocks, np.ascontiguousarray(x.T), qt.id, n, m, k, threads=4)
     w = K.upload(qt, n, k, blocks)
@@ -262,6 +262,43 @@ def test_q5k_prefill_on_the_tensor_core(K, gk, oracle, torch, n, k, m, bf16):
     w.free()
 
 
+@pytest.mark.parametrize("name", ["q4_0", "q5_0"])
+@pytest.mark.parametrize("n,k,m,bf16", [(96, 512, 70, False), (300, 5 * 256, 2, False), (130, 256, 300, True), (1000, 12 * 256, 130, True),
+                                        (20000, 512, 200, True)])
+def test_classic_prefill_on_the_tensor_core(K, gk, oracle, torch, name, n, k, m, bf16):
+    """Q4_0 / Q5_0 with k a multiple of 256 (a row's blocks then come in 16-byte aligned groups of eight) and more than
+    one token: the same kernel; blocks start on 2-byte boundaries, so even blocks are read as words and shifted."""
+    qt = qtype(gk, name)
+    blocks = random_blocks(name, qt, n, k, 700 + m)
+    x = np.random.default_rng(71 + m).standard_normal((m, k)).astype(np.float32)
+    xd = torch.from_numpy(x).cuda()
+    if bf16:
+        xd = xd.to(torch.bfloat16)
+        x = xd.to(torch.float32).cpu().numpy()
+    w = K.upload(qt, n, k, blocks)
+    y = K.gemm(w, xd, out_dtype=torch.bfloat16 if bf16 else torch.float32).to(torch.float32).cpu().numpy()
+    assert K.status() == 0
+    rows = np.random.default_rng(5).choice(n, size=min(n, 256), replace=False)
+    ref = oracle.gemm_f32_nt(x, oracle_matrix(oracle, qt, blocks, n, k)[rows])
+    assert oracle.rel_err(y[:, rows], ref) <= 1e-2 + (2.0 ** -8 if bf16 else 0.0)
+    w.free()
+
+
+def test_classic_prefill_other_k_stays_on_the_streaming_kernel(K, gk, oracle, torch):
+    # k = 5 * 32: rows are not 16-byte aligned; gllmk_gemm runs token tiles through the dp2a kernel (f32 only, 2e-3)
+    qt = qtype(gk, "q4_0")
+    n, k, m = 64, 160, 40
+    blocks = random_blocks("q4_0", qt, n, k, 88)
+    x = np.random.default_rng(89).standard_normal((m, k)).astype(np.float32)
+    w = K.upload(qt, n, k, blocks)
+    y = K.gemm(w, torch.from_numpy(x).cuda()).cpu().numpy()
+    ref = oracle.quant_matmul(blocks, np.ascontiguousarray(x.T), qt.id, n, m, k, threads=4)
+    assert oracle.rel_err(y.T, ref) <= TOL
+    with pytest.raises(gk.GllmkError):
+        K.gemm(w, torch.from_numpy(x).cuda().to(torch.bfloat16))
+    w.free()
+
+
 def test_q6k_grouped_experts(K, gk, oracle, torch):
     """gllmk_gemm_grouped takes Q6_K experts through the same kernel (one launch for all groups); the formats without a
     tensor-core kernel are refused."""
@@ -280,11 +317,11 @@ def test_q6k_grouped_experts(K, gk, oracle, torch):
             assert oracle.rel_err(y[offs[e]:offs[e + 1]], ref) <= 1e-2, e
     for w in ws:
         w.free()
-    q4 = qtype(gk, "q4_0")
-    w4 = K.upload(q4, 64, 256, random_blocks("q4_0", q4, 64, 256, 9))
+    q8 = qtype(gk, "q8_k")
+    w8 = K.upload(q8, 64, 256, random_blocks("q8_k", q8, 64, 256, 9))
     with pytest.raises(gk.GllmkError):
-        K.gemm_grouped([w4], xd[:8, :256].contiguous(), [0, 8])
-    w4.free()
+        K.gemm_grouped([w8], xd[:8, :256].contiguous(), [0, 8])
+    w8.free()
 
 
 @pytest.mark.parametrize("name", FORMATS)
