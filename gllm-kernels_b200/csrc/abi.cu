@@ -433,7 +433,12 @@ int32_t gllmk_ffn_prefill(gllmk_ctx ctx, gllmk_weight w_gate_up, gllmk_weight w_
     if (wg->n % 2 || wg->n / 2 != wd->k || wd->n != wg->k)
         return fail(c, GLLMK_STATUS_INVALID_ARG, "ffn_prefill: shapes do not chain: gate||up [%lld, %lld], down [%lld, %lld]", (long long)wg->n,
                     (long long)wg->k, (long long)wd->n, (long long)wd->k);
-    if (raw_format(wg->qt) || raw_format(wd->qt) || wg->qt == GLLMK_QUANT_INT8 || wd->qt == GLLMK_QUANT_INT8)
+    // (a GGUF file may mix formats inside a block: Q4_K gate / up with a Q6_K down projection is common)
+    const auto has_tc_gemm = [](const Weight *w) {
+        return w->qt != GLLMK_QUANT_INT8 && (!raw_format(w->qt) || w->qt == GLLMK_QUANT_Q6_K || w->qt == GLLMK_QUANT_Q5_K ||
+                                             ((w->qt == GLLMK_QUANT_Q4_0 || w->qt == GLLMK_QUANT_Q5_0) && w->k % 256 == 0));
+    };
+    if (!has_tc_gemm(wg) || !has_tc_gemm(wd))
         return fail(c, GLLMK_STATUS_UNSUPPORTED, "ffn_prefill: weight type has no tensor-core prefill kernel");
     const int64_t f = wd->k;
     if (f % 8) return fail(c, GLLMK_STATUS_INVALID_ARG, "ffn_prefill: the intermediate width must be a multiple of 8");

@@ -241,7 +241,9 @@ GLLMK_API int32_t gllmk_ffn_decode(gllmk_ctx ctx, gllmk_weight w_gate_up, gllmk_
  *   y = W_down (silu(gate) * up)
  * SwiGLU (f32 arithmetic on the bf16 values of h) is applied by the second product's activation staging, so no
  * activation kernel runs and no third buffer exists.  x [m, k] f32 or bf16 (ldx), y [m, k] f32 or bf16 (ldy); the
- * Q4_K / Q8_0 / MXFP4 / NVFP4 weights of gllmk_gemm.  Each product is within 1e-2 of the reference's f32 evaluation. */
+ * Q4_K / Q8_0 / MXFP4 / NVFP4 weights of gllmk_gemm, and Q6_K / Q5_K / (k a multiple of 256:) Q4_0 / Q5_0; the two weights
+ * may differ in format (a GGUF file often pairs Q4_K gate / up with a Q6_K down projection).  Each product is within 1e-2
+ * of the reference's f32 evaluation. */
 GLLMK_API int32_t gllmk_ffn_prefill(gllmk_ctx ctx, gllmk_weight w_gate_up, gllmk_weight w_down, const void *x_dev, int32_t x_dtype,
                                     int64_t ldx, int32_t m, void *h_dev, void *y_dev, int32_t y_dtype, int64_t ldy, void *stream);
 

@@ -299,6 +299,40 @@ def test_classic_prefill_other_k_stays_on_the_streaming_kernel(K, gk, oracle, to
     w.free()
 
 
+@pytest.mark.parametrize("gu,dn", [("q4k", "q6_k"), ("q5_k", "q5_k"), ("q4_0", "q6_k")])
+def test_ffn_prefill_with_gguf_formats(K, gk, oracle, torch, gu, dn):
+    """The gated feed-forward block for a batch with the formats a GGUF file mixes inside a block (Q4_K gate / up with a
+    Q6_K down projection, all-Q5_K, legacy Q4_0): y = W_down (silu(gate) * up), each product within 1e-2 of the oracle's
+    f32 product of the same inputs."""
+    d, f, m = 512, 768, 96
+
+    def make(name, n, k, seed):
+        if name == "q4k":
+            W = (np.random.default_rng(seed).standard_normal((n, k)) * 0.02).astype(np.float32)
+            b = oracle.quantize_q4_k(W)
+            return gk.QuantType.q4k(), b, oracle.dequant_matrix(oracle.Q4K, b, n, k)
+        qt = qtype(gk, name)
+        b = random_blocks(name, qt, n, k, seed)
+        return qt, b, oracle_matrix(oracle, qt, b, n, k)
+    qg, bg, wg_ref = make(gu, 2 * f, d, 91)
+    qd, bd, wd_ref = make(dn, d, f, 92)
+    w_gu, w_dn = K.upload(qg, 2 * f, d, bg), K.upload(qd, d, f, bd)
+    scale = 2.5 if gu == "q4k" else 0.25  # random-byte blocks have weights of order 0.1 - 1: keep gate and up of order one
+    xd = torch.from_numpy((np.random.default_rng(93).standard_normal((m, d)) * scale).astype(np.float32)).cuda().to(torch.bfloat16)
+    x = xd.to(torch.float32).cpu().numpy()
+    h = torch.empty((m, 2 * f), dtype=torch.bfloat16, device="cuda")
+    y = K.ffn_prefill(w_gu, w_dn, xd, h=h).cpu().numpy()
+    assert K.status() == 0
+    def silu_mul(g):
+        with np.errstate(over="ignore"):  # exp(-gate) may overflow to inf for a very negative gate: gate / inf = -0, the limit
+            return ((g[:, :f] / (np.float32(1.0) + np.exp(-g[:, :f], dtype=np.float32))) * g[:, f:]).astype(np.float32)
+    h_dev = h.to(torch.float32).cpu().numpy()
+    assert oracle.rel_err(h_dev, oracle.gemm_f32_nt(x, wg_ref)) <= 1e-2 + 2.0 ** -8
+    assert oracle.rel_err(y, oracle.gemm_f32_nt(silu_mul(h_dev), wd_ref)) <= 1e-2
+    w_gu.free()
+    w_dn.free()
+
+
 def test_q6k_grouped_experts(K, gk, oracle, torch):
     """gllmk_gemm_grouped takes Q6_K experts through the same kernel (one launch for all groups); the formats without a
     tensor-core kernel are refused."""
