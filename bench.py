@@ -1052,7 +1052,19 @@ def run_prefill_case(args):
         return run_fp4_decode_case(args, K, gk, torch, dev, gen)
     if args.case == "prefill_w8a8":
         return run_w8a8_case(args, K, gk, torch, dev, gen)
-    if args.case == "prefill_q4k":
+    if args.case == "prefill_q6k":
+        # Q6_K down projection of the same model, reference-layout blocks with random payloads and small scales
+        n, k, m = D_MODEL, N_FF, 512
+        nblk = n * (k // 256)
+        b = torch.randint(0, 256, (nblk, 210), generator=gen, device=dev, dtype=torch.uint8)
+        b[:, 208:210] = ((torch.rand((nblk, 1), generator=gen, device=dev) - 0.5) * 0.04).to(torch.float16).view(torch.uint8)
+        w = K.upload(QT.q6k(), n, k, b.reshape(-1))
+        del b
+        a = torch.randn((m, k), generator=gen, device=dev)
+        y = torch.empty((m, n), dtype=torch.float32, device=dev)
+        fn = lambda: K.gemm(w, a, y=y)
+        kernel, peak_key, launches = "gemm_wq_kernel<Q6_K, 2 row tiles> (+ stage_act_kernel)", "bf16_tflops", 2
+    elif args.case == "prefill_q4k":
         n, k, m = N_FF, D_MODEL, 512
         W = torch.randn((n, k), generator=gen, device=dev) * 0.02
         w = K.upload(QT.q4k(), n, k, K.quantize(QT.q4k(), W))
@@ -1242,7 +1254,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying a CUDA graph")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="N > 1: how the bands of y reach every rank (peer stores fused into the GEMV, or NCCL all-gather)")
-    ap.add_argument("--case", default="decode", choices=["decode", "prefill_q4k", "prefill_nvfp4", "prefill_w8a8", "decode_q6k", "decode_nvfp4"],
+    ap.add_argument("--case", default="decode", choices=["decode", "prefill_q4k", "prefill_q6k", "prefill_nvfp4", "prefill_w8a8", "decode_q6k", "decode_nvfp4"],
                     help="decode = the headline workload; prefill_* / decode_* = one kernel on its own (1 GPU)")
     args = ap.parse_args()
     if args.case != "decode":
