@@ -483,12 +483,12 @@ int32_t gllmk_gemm(gllmk_ctx ctx, gllmk_weight wh, const void *a_dev, int32_t a_
     if (lda < w->k || ldy < w->n) return fail(c, GLLMK_STATUS_INVALID_ARG, "gemm: leading dimension smaller than the row");
     if (w->device != c->device) return fail(c, GLLMK_STATUS_INVALID_ARG, "weight lives on another device");
     DeviceGuard g(c->device);
-    // Q6_K and Q5_K have a place in the fused-dequant tensor-core GEMM.  On W[8192, 28672]: Q6_K 160 - 172 us at 17 - 128
-    // tokens (two passes of its batch GEMV: 256 us; one pass, up to 16 tokens: 100 - 135 us); Q5_K, which has no batch GEMV,
-    // 141 us against 167 us (2 tokens) ... 590 us (16 tokens) on the dp2a kernel
-    // Q4_0 / Q5_0: when a row's blocks come in whole groups of eight (k a multiple of 256: rows 16-byte aligned)
-    if ((w->qt == GLLMK_QUANT_Q6_K && m > GLLMK_GEMM_GEMV_MAX_M) || (w->qt == GLLMK_QUANT_Q5_K && m >= 2) ||
-        ((w->qt == GLLMK_QUANT_Q4_0 || w->qt == GLLMK_QUANT_Q5_0) && w->k % 256 == 0 && m >= 2))  // 119 / 140 us against 150 / 157 us (2 tokens) on dp2a
+    // Q6_K, Q5_K and (when a row's blocks come in whole 16-byte aligned groups of eight: k a multiple of 256) Q4_0 / Q5_0 have
+    // a place in the fused-dequant tensor-core GEMM.  On W[8192, 28672] it takes ~100 us up to 128 tokens; Q6_K's batch GEMV
+    // needs 100 us up to 8 tokens and 135 us up to 16, the dp2a kernel of the other three 150 - 170 us for 2 tokens and
+    // 590 us for 16
+    if ((w->qt == GLLMK_QUANT_Q6_K && m > 8) || (w->qt == GLLMK_QUANT_Q5_K && m >= 2) ||
+        ((w->qt == GLLMK_QUANT_Q4_0 || w->qt == GLLMK_QUANT_Q5_0) && w->k % 256 == 0 && m >= 2))
         return gemm_launch(c, w, a_dev, a_dtype == GLLMK_DTYPE_BF16, lda, m, y_dev, y_dtype == GLLMK_DTYPE_BF16, ldy,
                            static_cast<cudaStream_t>(stream));
     if (raw_format(w->qt)) {

@@ -604,8 +604,8 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
         // ---------------- raw weight blocks: one block of each of the tile's 128 rows per super-chunk ----------------
         // The blocks of a tile lie a whole row apart in memory, so a super-chunk is 128 pieces of 224 (176) bytes.  As 128
         // bulk copies they paced the kernel (a copy engine request per piece: ~1.8 k cycles per tile step); the whole warp
-        // copies them with 16-byte cp.async instead — lane = consecutive chunk, 56 (44) per lane — and every lane's
-        // copies arrive at the slot's barrier when they have landed (cp.async.mbarrier.arrive.noinc).
+        // copies them with 16-byte cp.async instead — 64 per lane — and every lane's copies arrive at the slot's barrier
+        // when they have landed (cp.async.mbarrier.arrive.noinc).
         int slot = 0, round = 0;
         bool ok = true;
         for (int jl = 0; jl < njb && ok; jl++) {
@@ -621,15 +621,21 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
                 const uint32_t dst = smem_s + raw_off + (uint32_t)(slot * RAW);
                 const int64_t trow0 = (int64_t)(tile0 + ti) * WQ_BM;
                 const int rmax = (int)(p.n - 1 - trow0 < WQ_BM - 1 ? p.n - 1 - trow0 : WQ_BM - 1);  // rows past the matrix repeat the last one; not stored
-                const uint8_t *src = G.qs[grp_id] + ((size_t)trow0 * p.nsc + jb) * SLOT;
+                // half a warp per row piece: lane % 16 = 16-byte chunk (the lanes past the piece's CPR chunks idle), rows 2 j +
+                // lane / 16 — constant strides, so an iteration is the copy and two additions
                 const size_t row_bytes = (size_t)p.nsc * SLOT;
-                int r = lane / CPR, ch = lane % CPR;  // chunk lane + 32 j of the tile's 128 x CPR: row r, 16-byte chunk ch
-#pragma unroll 4
-                for (int j = 0; j < WQ_BM * CPR / 32; j++) {
-                    const int rc = r < rmax ? r : rmax;
-                    cp_async16_s(dst + (uint32_t)(r * RSTRIDE + 16 * ch), src + (size_t)rc * row_bytes + 16 * ch);
-                    r += 32 / CPR, ch += 32 % CPR;  // 32 chunks on
-                    if (ch >= CPR) ch -= CPR, r++;
+                const int hrow = lane >> 4, ch = lane & 15;
+                const uint8_t *tile_src = G.qs[grp_id] + ((size_t)trow0 * p.nsc + jb) * SLOT + 16 * ch;
+                if (ch < CPR) {
+                    if (rmax == WQ_BM - 1) {
+                        const uint8_t *src = tile_src + (size_t)hrow * row_bytes;
+                        uint32_t d = dst + (uint32_t)(hrow * RSTRIDE + 16 * ch);
+#pragma unroll 8
+                        for (int j = 0; j < WQ_BM / 2; j++, src += 2 * row_bytes, d += 2 * RSTRIDE) cp_async16_s(d, src);
+                    } else {
+                        for (int r = hrow; r < WQ_BM; r += 2)
+                            cp_async16_s(dst + (uint32_t)(r * RSTRIDE + 16 * ch), tile_src + (size_t)(r < rmax ? r : rmax) * row_bytes);
+                    }
                 }
                 cp_async_arrive(rawfull + 8 * slot);
                 if (++slot == p.r) slot = 0, round++;

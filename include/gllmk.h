@@ -343,7 +343,7 @@ GLLMK_API int32_t gllmk_exchange_wait(gllmk_ctx ctx, void *flags_local, int32_t 
  * m <= GLLMK_GEMM_GEMV_MAX_M the call is one pass of the decode kernel (gllmk_gemv), which is faster
  * there and meets its tighter bound (from 17 tokens on the tensor-core kernel is the faster one:
  * W[28672, 8192] Q4_K at m = 32: 80 us against 113 us as two decode passes).  Of the other GGUF formats Q6_K and Q5_K
- * have a place in this kernel (Q6_K: more than 16 tokens, up to 16 its batch GEMV; Q5_K: 2 tokens and more; f32 only below),
+ * have a place in this kernel (Q6_K: more than 8 tokens, up to 8 its batch GEMV; Q5_K: 2 tokens and more; f32 only below),
  * and so have Q4_0 and Q5_0 when k is a multiple of 256 (2 tokens and more); Q8_K, and Q4_0 / Q5_0 with another k, run the
  * streaming GEMV over token tiles and take f32 only. */
 #define GLLMK_GEMM_GEMV_MAX_M 16

@@ -215,10 +215,10 @@ def test_gemm_many_tokens_f32(K, gk, oracle, torch):
     w.free()
 
 
-@pytest.mark.parametrize("n,k,m,bf16", [(96, 512, 70, False), (300, 5 * 256, 33, True), (64, 2 * 256, 17, False), (130, 256, 300, False), (1000, 12 * 256, 130, True),
+@pytest.mark.parametrize("n,k,m,bf16", [(96, 512, 70, False), (300, 5 * 256, 33, True), (64, 2 * 256, 9, False), (130, 256, 300, False), (1000, 12 * 256, 130, True),
                                         (20000, 512, 200, True)])
 def test_q6k_prefill_on_the_tensor_core(K, gk, oracle, torch, n, k, m, bf16):
-    """Q6_K with more than 16 tokens: the fused-dequant tcgen05 GEMM, reference-layout blocks copied row by row into shared
+    """Q6_K with more than 8 tokens (gllmk_gemm): the fused-dequant tcgen05 GEMM, reference-layout blocks copied row by row into shared
     memory and converted to fp16 there (bar 1e-2 like the other weight-only formats).  Rows not a multiple of 128 (the
     last tile repeats the last row, results not stored), one and many k-blocks, one and two row tiles per CTA, f32 and bf16."""
     qt = qtype(gk, "q6_k")
