@@ -602,7 +602,7 @@ __global__ void __launch_bounds__(WQ_THREADS, 1) gemm_wq_kernel(const __grid_con
     if (warp == 0 && wq_row_major(FMT)) {
         constexpr int SLOT = wq_slot(FMT), RSTRIDE = wq_row_stride(FMT), CPR = SLOT / 16;  // 16-byte chunks per row piece
         // ---------------- raw weight blocks: one block of each of the tile's 128 rows per super-chunk ----------------
-        // The blocks of a tile lie a whole row apart in memory, so a super-chunk is 128 pieces of 224 (176) bytes.  As 128
+        // The blocks of a tile lie a whole row apart in memory, so a super-chunk is 128 pieces of 224 / 176 / 144 bytes.  As 128
         // bulk copies they paced the kernel (a copy engine request per piece: ~1.8 k cycles per tile step); the whole warp
         // copies them with 16-byte cp.async instead — 64 per lane — and every lane's copies arrive at the slot's barrier
         // when they have landed (cp.async.mbarrier.arrive.noinc).
