@@ -525,11 +525,7 @@ __device__ unsigned long long g_wq_prof[1024 * 20 * 8];
 #define WQP_ACC(i) do { const unsigned long long n_ = clock64(); wqp_a[i] += n_ - wqp_t; wqp_t = n_; } while (0)
 #define WQP_OUT() do { if (lane == 0 && blockIdx.y * gridDim.x + blockIdx.x < 1024) { unsigned long long *o_ = g_wq_prof + ((blockIdx.y * gridDim.x + blockIdx.x) * 20 + warp) * 8; \
     for (int i_ = 0; i_ < 7; i_++) o_[i_] = wqp_a[i_]; o_[7] = clock64() - wqp_start; } } while (0)
-// timeline of CTA 0: event e of warp w at its i-th tile (i < 32)
-__device__ unsigned long long g_wq_tl[20 * 8 * 32];
-#define WQP_TL(e, i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (i) < 32) g_wq_tl[(warp * 8 + (e)) * 32 + (i)] = clock64(); } while (0)
 #else
-#define WQP_TL(e, i)
 #define WQP_DECL
 #define WQP_T0()
 #define WQP_ACC(i)
@@ -1079,9 +1075,6 @@ int32_t gemm_launch(Ctx *c, const Weight *w, const void *a, int a_bf16, int64_t 
 }  // namespace gllmk
 
 #ifdef GLLMK_WQ_PROF
-extern "C" __attribute__((visibility("default"))) int gllmk_debug_wq_tl(unsigned long long *out) {
-    return (int)cudaMemcpyFromSymbol(out, gllmk::g_wq_tl, sizeof(gllmk::g_wq_tl));
-}
 extern "C" __attribute__((visibility("default"))) int gllmk_debug_wq_prof(unsigned long long *out) {
     return (int)cudaMemcpyFromSymbol(out, gllmk::g_wq_prof, sizeof(gllmk::g_wq_prof));
 }
